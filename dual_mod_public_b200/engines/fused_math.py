@@ -1,0 +1,272 @@
+"""Explicit forward and hand-derived backward of the chunk cell, op by op.
+
+Each function here is the plain-torch statement of one device kernel of the
+fused engine (same arguments, same outputs, same accumulation semantics) and is
+what the kernels' numerics tests compare against.  It is also the engine's
+fallback on a device without the extension (CPU tests).
+
+Layout is token-major throughout: per-head tensors are [B, c, h, dh] views of
+[B, c, d] rows, the tape is [B, T, h, dh].
+
+Read algebra.  For one sweep, a chunk row's read is a softmax over
+[committed prefix | intra rows (strictly earlier) | raw self].  The prefix part
+is sweep-invariant, so it is reduced once per cell to (o_c, lse_c) — normalised
+output and log-sum-exp — and every sweep merges its tail against it:
+
+    lse = logaddexp(lse_c, logsumexp(tail));   P_c = exp(lse_c - lse)
+    o   = P_c o_c + sum_j P_j v_j,             P_j = exp(s_j - lse)
+
+Backward of the merge, with delta = dO . o:
+    d o_c = P_c dO;   d lse_c = P_c (dO . o_c - delta)
+    d s_j = P_j (dO . v_j - delta);   d v_j = P_j dO
+and of the prefix partial (p_j = exp(s_j - lse_c)):
+    d s_j = p_j (d o_c . v_j - d o_c . o_c + d lse_c)
+so no running-max bookkeeping is needed (the reference's (A, Z, m) form needs an
+argmax sub-gradient fix-up, engines/wavescan/cells/fused_sweep.py:1837-1850).
+
+Reference parity: the fused sweep path of engines/wavescan/cells/fused_sweep.py
+(`_comm_fwd_kernel` 154-208, `_attend_head_kernel` 367-420, `_rms_u_kernel` 423-445,
+`_refine2_kernel` 514-611 and their backward twins 211-357, 634-1052).
+"""
+
+from __future__ import annotations
+
+import torch
+
+NEG = -1e30
+
+
+# ---- rotary helpers on token-major [B, c, h, dh] ----------------------------------------
+
+def rope_tm(x, cos, sin):
+    """x [B,c,h,dh]; cos/sin [c, dh/2]. fp32 math, result in x.dtype."""
+    half = x.shape[-1] // 2
+    xf = x.float()
+    lo, hi = xf[..., :half], xf[..., half:]
+    c_, s_ = cos[None, :, None, :], sin[None, :, None, :]
+    return torch.cat((lo * c_ - hi * s_, hi * c_ + lo * s_), dim=-1).to(x.dtype)
+
+
+def unrope_tm(x, cos, sin):
+    return rope_tm(x, cos, -sin)
+
+
+# ---- masks ------------------------------------------------------------------------------
+
+def _prefix_mask(c, lo, hi, pos0, window, device):
+    """[c, hi-lo] bool or None: chunk row t (absolute pos0+t) reads committed j in
+    [lo, hi) iff j > pos0 + t - window."""
+    if not window:
+        return None
+    t = torch.arange(c, device=device)[:, None] + pos0
+    j = torch.arange(lo, hi, device=device)[None, :]
+    return j > t - window
+
+
+def _intra_mask(c, window, device):
+    i = torch.arange(c, device=device)
+    m = i[None, :] < i[:, None]
+    if window:
+        m = m & (i[None, :] > i[:, None] - window)
+    return m
+
+
+def prefix_lo(pos0: int, window: int) -> int:
+    """First committed row any chunk row can read."""
+    return max(0, pos0 - window + 1) if window else 0
+
+
+# ---- committed-prefix pass --------------------------------------------------------------
+
+def prefix_fwd(q_r, Kc, Vc, pos0, scale, window=0):
+    """q_r [B,c,h,dh]; Kc/Vc tape [B,T,h,dh].  Returns (o_c fp32 [B,c,h,dh],
+    lse_c fp32 [B,c,h]); an empty prefix gives (0, NEG)."""
+    B, c, h, dh = q_r.shape
+    lo = prefix_lo(pos0, window)
+    if pos0 - lo <= 0:
+        return (torch.zeros(B, c, h, dh, dtype=torch.float32, device=q_r.device),
+                torch.full((B, c, h), NEG, dtype=torch.float32, device=q_r.device))
+    K, V = Kc[:, lo:pos0], Vc[:, lo:pos0]
+    s = torch.einsum("bchd,bjhd->bhcj", q_r, K).float() * scale
+    m = _prefix_mask(c, lo, pos0, pos0, window, q_r.device)
+    if m is not None:
+        s = s.masked_fill(~m, NEG)
+    lse = torch.logsumexp(s, dim=-1)                                   # [B,h,c]
+    p = torch.exp(s - lse.unsqueeze(-1))
+    if m is not None:
+        p = p * m                                                       # dead rows contribute 0
+    o = torch.einsum("bhcj,bjhd->bchd", p.to(V.dtype), V).float()
+    return o, lse.permute(0, 2, 1).contiguous()
+
+
+def prefix_bwd(q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c, dq_acc, dKc, dVc):
+    """Backward of `prefix_fwd`.  do_c [B,c,h,dh], dlse_c [B,c,h] fp32 (summed over
+    sweeps).  Accumulates: dq_acc [B,c,h,dh] fp32 +=, dKc/dVc [B,T,h,dh] fp32 rows
+    [lo, pos0) +=."""
+    B, c, h, dh = q_r.shape
+    lo = prefix_lo(pos0, window)
+    if pos0 - lo <= 0:
+        return
+    K, V = Kc[:, lo:pos0], Vc[:, lo:pos0]
+    s = torch.einsum("bchd,bjhd->bhcj", q_r, K).float() * scale
+    m = _prefix_mask(c, lo, pos0, pos0, window, q_r.device)
+    if m is not None:
+        s = s.masked_fill(~m, NEG)
+    p = torch.exp(s - lse_c.permute(0, 2, 1).unsqueeze(-1))
+    if m is not None:
+        p = p * m
+    dov = torch.einsum("bchd,bjhd->bhcj", do_c, V.float())
+    corr = ((do_c * o_c).sum(-1) - dlse_c).permute(0, 2, 1).unsqueeze(-1)    # [B,h,c,1]
+    ds = p * (dov - corr) * scale
+    dq_acc += torch.einsum("bhcj,bjhd->bchd", ds, K.float())
+    dKc[:, lo:pos0] += torch.einsum("bhcj,bchd->bjhd", ds, q_r.float())
+    dVc[:, lo:pos0] += torch.einsum("bhcj,bchd->bjhd", p, do_c)
+
+
+# ---- per-sweep tail read ------------------------------------------------------------------
+
+def tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
+    """One sweep's merged read.  All per-head tensors [B,c,h,dh]; returns
+    (o [B,c,h,dh] in v_raw.dtype, lse fp32 [B,c,h])."""
+    c = q_r.shape[1]
+    s_in = torch.einsum("bchd,bjhd->bhcj", q_r, K_in).float() * scale
+    s_in = s_in.masked_fill(~_intra_mask(c, window, q_r.device), NEG)
+    s_self = (q_r.float() * kself_r.float()).sum(-1).permute(0, 2, 1) * scale     # [B,h,c]
+    lse_ch = lse_c.permute(0, 2, 1)
+    lse = torch.logsumexp(torch.cat((s_in, s_self.unsqueeze(-1), lse_ch.unsqueeze(-1)), dim=-1), dim=-1)
+    p_in = torch.exp(s_in - lse.unsqueeze(-1))
+    p_self = torch.exp(s_self - lse)
+    p_c = torch.exp(lse_ch - lse)
+    o = torch.einsum("bhcj,bjhd->bchd", p_in.to(V_in.dtype), V_in).float()
+    o = o + p_self.permute(0, 2, 1).unsqueeze(-1) * v_raw.float()
+    o = o + p_c.permute(0, 2, 1).unsqueeze(-1) * o_c
+    return o.to(v_raw.dtype), lse.permute(0, 2, 1).contiguous()
+
+
+def tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window=0):
+    """Backward of `tail_fwd` for upstream grad dO [B,c,h,dh].  Returns fp32
+    (dq, dkself, dvraw, dK_in, dV_in, do_c, dlse_c)."""
+    c = q_r.shape[1]
+    dOf = dO.float()
+    s_in = torch.einsum("bchd,bjhd->bhcj", q_r, K_in).float() * scale
+    s_in = s_in.masked_fill(~_intra_mask(c, window, q_r.device), NEG)
+    s_self = (q_r.float() * kself_r.float()).sum(-1).permute(0, 2, 1) * scale
+    lse_h = lse.permute(0, 2, 1)
+    p_in = torch.exp(s_in - lse_h.unsqueeze(-1))                       # [B,h,c,c]
+    p_self = torch.exp(s_self - lse_h).permute(0, 2, 1)               # [B,c,h]
+    p_c = torch.exp(lse_c - lse)                                       # [B,c,h]
+    delta = (dOf * o.float()).sum(-1)                                  # [B,c,h]
+    # prefix partial
+    do_c = p_c.unsqueeze(-1) * dOf
+    dlse_c = p_c * ((dOf * o_c).sum(-1) - delta)
+    # self column
+    ds_self = p_self * ((dOf * v_raw.float()).sum(-1) - delta) * scale
+    dvraw = p_self.unsqueeze(-1) * dOf
+    dq = ds_self.unsqueeze(-1) * kself_r.float()
+    dkself = ds_self.unsqueeze(-1) * q_r.float()
+    # intra block
+    dov = torch.einsum("bchd,bjhd->bhcj", dOf, V_in.float())
+    ds = p_in * (dov - delta.permute(0, 2, 1).unsqueeze(-1)) * scale
+    dq = dq + torch.einsum("bhcj,bjhd->bchd", ds, K_in.float())
+    dK_in = torch.einsum("bhcj,bchd->bjhd", ds, q_r.float())
+    dV_in = torch.einsum("bhcj,bchd->bjhd", p_in, dOf)
+    return dq, dkself, dvraw, dK_in, dV_in, do_c, dlse_c
+
+
+# ---- RMSNorm ------------------------------------------------------------------------------------
+
+def rms_fwd(x, w, eps=1e-5):
+    """y = x * rstd * w (fp32 math, y in x.dtype); returns (y, rstd fp32 [..., 1])."""
+    xf = x.float()
+    rstd = torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
+    return (xf * rstd * w.float()).to(x.dtype), rstd
+
+
+def rms_bwd(dy, x, w, rstd):
+    """Returns (dx fp32, dw fp32 [d])."""
+    xf, dyf = x.float(), dy.float()
+    xn = xf * rstd
+    g = dyf * w.float()
+    dx = rstd * (g - xn * (g * xn).mean(-1, keepdim=True))
+    dw = (dyf * xn).reshape(-1, x.shape[-1]).sum(0)
+    return dx, dw
+
+
+# ---- refine (gate, blend, rotate) ----------------------------------------------------------------
+
+def refine_fwd(cg, glx, k, v, cos, sin, h, pin_cols=0):
+    """Write law for the packed layout.
+
+    cg  [B,c,4d]: u @ W_pack^T = [k_ctx | v_ctx | gate-u logits k | gate-u logits v]
+    glx [B,c,2d]: x̂-half of the gate logits plus bias (sweep-invariant)
+    k, v [B,c,d] raw (unrotated) key / value.  `pin_cols`: the first pin_cols value
+    columns keep the raw value (kmod_vraw_heads * dh).
+    Returns (K_out [B,c,h,dh] rotated, V_out [B,c,h,dh]) in k.dtype.
+    """
+    B, c, d = k.shape
+    kc, vc, gku, gvu = cg.split(d, dim=-1)
+    gk = torch.sigmoid(glx[..., :d].float() + gku.float())
+    gv = torch.sigmoid(glx[..., d:].float() + gvu.float())
+    kpp = gk * k.float() + (1.0 - gk) * kc.float()
+    vpp = gv * v.float() + (1.0 - gv) * vc.float()
+    if pin_cols:
+        vpp = torch.cat((v[..., :pin_cols].float(), vpp[..., pin_cols:]), dim=-1)
+    K_out = rope_tm(kpp.view(B, c, h, d // h), cos, sin)
+    return K_out.to(k.dtype), vpp.view(B, c, h, d // h).to(k.dtype)
+
+
+def refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols=0):
+    """Backward of `refine_fwd`.  dK_out/dV_out [B,c,h,dh].  Returns fp32
+    (dcg [B,c,4d], dk [B,c,d], dv [B,c,d]); the gate-logit grads are dcg[..., 2d:]
+    (they are also the grads of glx)."""
+    B, c, d = k.shape
+    kc, vc, gku, gvu = cg.split(d, dim=-1)
+    gk = torch.sigmoid(glx[..., :d].float() + gku.float())
+    gv = torch.sigmoid(glx[..., d:].float() + gvu.float())
+    dkpp = unrope_tm(dK_out.float(), cos, sin).reshape(B, c, d)
+    dvpp = dV_out.float().reshape(B, c, d)
+    dv_pin = None
+    if pin_cols:
+        dv_pin = dvpp[..., :pin_cols]
+        dvpp = torch.cat((torch.zeros_like(dv_pin), dvpp[..., pin_cols:]), dim=-1)
+    kf, vf = k.float(), v.float()
+    dgk = dkpp * (kf - kc.float()) * gk * (1.0 - gk)
+    dgv = dvpp * (vf - vc.float()) * gv * (1.0 - gv)
+    dcg = torch.cat((dkpp * (1.0 - gk), dvpp * (1.0 - gv), dgk, dgv), dim=-1)
+    dk = dkpp * gk
+    dv = dvpp * gv
+    if pin_cols:
+        dv = torch.cat((dv_pin, dv[..., pin_cols:]), dim=-1)
+    return dcg, dk, dv
+
+
+# ---- SwiGLU pointwise ---------------------------------------------------------------------------
+
+def swiglu_fwd(h1, h3):
+    return (torch.nn.functional.silu(h1.float()) * h3.float()).to(h1.dtype)
+
+
+def swiglu_bwd(dg, h1, h3):
+    """g = silu(h1) * h3 -> (dh1, dh3) in h1.dtype."""
+    h1f, h3f, dgf = h1.float(), h3.float(), dg.float()
+    sg = torch.sigmoid(h1f)
+    silu = h1f * sg
+    dh1 = dgf * h3f * (sg * (1.0 + h1f * (1.0 - sg)))
+    return dh1.to(h1.dtype), (dgf * silu).to(h1.dtype)
+
+
+# ---- chunked cross-entropy head ---------------------------------------------------------------------
+
+def ce_chunk(logits, targets, inv_n):
+    """Sum-reduced CE * inv_n over one slab, and d(logits) for it.  logits [n,V]
+    (any float dtype), targets [n] with -1 = ignore.  Returns (loss fp32 scalar,
+    dlogits in logits.dtype)."""
+    lf = logits.float()
+    lse = torch.logsumexp(lf, dim=-1)
+    valid = targets >= 0
+    tgt = targets.clamp_min(0)
+    picked = lf.gather(-1, tgt[:, None]).squeeze(-1)
+    loss = ((lse - picked) * valid).sum() * inv_n
+    p = torch.exp(lf - lse[:, None])
+    p.scatter_add_(-1, tgt[:, None], -torch.ones_like(picked)[:, None])
+    return loss, (p * (valid[:, None] * inv_n)).to(logits.dtype)

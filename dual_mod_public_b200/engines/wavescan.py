@@ -1,0 +1,625 @@
+"""Layer-major chunked training engine ("wavescan" class).
+
+One layer at a time over the whole sequence: raw projections for all T
+positions as large GEMMs, then the chunk cells in order (committed-prefix pass
+once per cell, K Jacobi sweeps each = tail read -> RMSNorm -> packed ctx/gate
+GEMM -> refine/rotate/write), then W_O and the SwiGLU block over all T.  The
+backward is a reverse scan with exact per-cell recompute; gradients accumulate
+in fp32 in one flat buffer shaped for the fused data-parallel update.
+
+Two backends share the API:
+  fused    hand-derived backward over the op table (`ops.TorchOps` on CPU,
+           `ops.CudaOps` = sm_100a kernels on GPU).  Config family: linear ctx_mod,
+           convex gates on [x̂;u], key and value modulation on, optional raw-value
+           heads and sliding window, optional factored gates / ctx operators.
+  generic  every knob, by re-running `cell.chunk_cell_forward` under autograd.
+
+Reference parity: `WaveScanEngine` (engines/wavescan/engine/graphs.py:36-792) —
+`forward / backward / train_step / finish_grads / debug_scan`, static buffers,
+per-schedule CUDA graphs — and the reverse-scan backward of
+engines/wavescan/engine/backward.py:87-206.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from ..models.layers import LoRAGate, LoRALinear
+from . import cell as gcell
+from .gradbuf import GradBuffers
+from .schedule import check_schedule
+
+FUSED_CTX_MODS = ("linear",)
+
+
+def fused_supported(cfg) -> bool:
+    return (cfg.attn_mode != "vanilla" and cfg.enable_key_mod and cfg.enable_value_mod
+            and cfg.ctx_mod in FUSED_CTX_MODS and cfg.gate_type == "convex_sigmoid"
+            and cfg.gate_type_v == "convex" and cfg.gate_input == "xu" and cfg.rmsnorm_on_o
+            and cfg.v_norm == "none" and cfg.v_ctx_norm == "none" and cfg.k_ctx_norm == "none"
+            and not cfg.v_clamp_tau and not cfg.attn_logn_ref
+            and (cfg.kmod_vraw_heads == 0 or (cfg.kmod_mode == "raw" and cfg.kmod_vraw_bound == "none")))
+
+
+def _dense(mod):
+    """Dense [out, in] weight of a Linear / LoRALinear / LoRAGate."""
+    if isinstance(mod, LoRAGate):
+        return mod.dense_weight()
+    return mod.weight
+
+
+class _LayerPack:
+    """Compute-dtype copies of one layer's weights in the layouts the ops want.
+    Refreshed from the fp32 master parameters by `pack()` once per optimizer step."""
+
+    def __init__(self, blk, cfg, dtype, device):
+        d, hid = cfg.d_model, cfg.mlp_hidden
+        mk = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+        self.w_an, self.w_mn, self.w_ctx = mk(d), mk(d), mk(d)
+        self.wq, self.wk, self.wv, self.wo = mk(d, d), mk(d, d), mk(d, d), mk(d, d)
+        self.w1, self.w3, self.w2 = mk(hid, d), mk(hid, d), mk(d, hid)
+        self.W_pack = mk(4 * d, d)        # [W_kctx ; W_vctx ; W_gk[:, d:] ; W_gv[:, d:]]
+        self.W_gx = mk(2 * d, d)          # [W_gk[:, :d] ; W_gv[:, :d]]
+        self.b_g = mk(2 * d)
+
+    @torch.no_grad()
+    def pack(self, blk, cfg):
+        a, d = blk.attn, cfg.d_model
+        self.w_an.copy_(blk.attn_norm.weight)
+        self.w_mn.copy_(blk.mlp_norm.weight)
+        self.w_ctx.copy_(a.norm_ctx.weight)
+        for dst, src in ((self.wq, a.wq), (self.wk, a.wk), (self.wv, a.wv), (self.wo, a.wo),
+                         (self.w1, blk.mlp.w1), (self.w3, blk.mlp.w3), (self.w2, blk.mlp.w2)):
+            dst.copy_(src.weight)
+        gk, gv = _dense(a.w_gk), _dense(a.w_gv)
+        self.W_pack[:d].copy_(a.w_kctx.weight)
+        self.W_pack[d:2 * d].copy_(a.w_vctx.weight)
+        self.W_pack[2 * d:3 * d].copy_(gk[:, d:])
+        self.W_pack[3 * d:].copy_(gv[:, d:])
+        self.W_gx[:d].copy_(gk[:, :d])
+        self.W_gx[d:].copy_(gv[:, :d])
+        self.b_g[:d].copy_(a.w_gk.bias)
+        self.b_g[d:].copy_(a.w_gv.bias)
+
+
+class WaveScanEngine:
+    def __init__(self, model, schedules, B, T, device=None, autocast_bf16=False,
+                 keep_logits=False, loss_rows=4096, use_graphs=False, backend="auto",
+                 ops=None, grad_bf16_ids=None, grad_alloc=None, grad_pad_to=1, sat_tau=0.0):
+        cfg = model.cfg
+        self.model, self.cfg = model, cfg
+        self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        self.schedules = [list(s) for s in schedules]
+        for s in self.schedules:
+            check_schedule(s, T)
+        self.B, self.T, self.L = B, T, cfg.n_layers
+        self.autocast_bf16 = autocast_bf16
+        self.act = torch.bfloat16 if autocast_bf16 else torch.float32
+        self.keep_logits = keep_logits
+        self.loss_rows = loss_rows
+        self.window = cfg.local_window or 0
+        self.sat_tau = float(sat_tau)
+        assert not cfg.attn_logn_ref, "the engines do not implement the log-n logit scale"
+        if backend == "auto":
+            backend = "fused" if fused_supported(cfg) else "generic"
+        if backend == "fused":
+            assert fused_supported(cfg), "config outside the fused family; use backend='generic'"
+        self.backend = backend
+        if ops is None:
+            from ..ops import default_ops
+            ops = default_ops(self.device)
+        self.ops = ops
+
+        dev, act = self.device, self.act
+        L, h, dh, d = self.L, cfg.n_heads, cfg.head_dim, cfg.d_model
+        z = lambda *s, dt=act: torch.zeros(*s, dtype=dt, device=dev)
+        self.idx = torch.zeros(B, T, dtype=torch.long, device=dev)
+        self.targets = torch.zeros(B, T, dtype=torch.long, device=dev)
+        self.xl = [z(B, T, d) for _ in range(L + 1)]          # layer inputs, xl[L] feeds norm_f
+        self.loss = torch.zeros((), dtype=torch.float32, device=dev)
+        self.grads = GradBuffers(list(model.parameters()), bf16_ids=grad_bf16_ids,
+                                 alloc=grad_alloc, pad_total_to=grad_pad_to)
+        self.dx_top = z(B, T, d)                               # d loss / d xl[L]
+        if keep_logits:
+            self.logits = z(B, T, cfg.vocab_size)
+            self.d_logits = z(B, T, cfg.vocab_size)
+        if backend == "fused":
+            # token-major tapes [B, T, h, dh]
+            self.K_caches = [z(B, T, h, dh) for _ in range(L)]
+            self.V_caches = [z(B, T, h, dh) for _ in range(L)]
+            self.o_saved = [z(B, T, d) for _ in range(L)]      # last-sweep reads per layer
+            self.dK = z(B, T, h, dh, dt=torch.float32)        # one layer's tape grads (reused)
+            self.dV = z(B, T, h, dh, dt=torch.float32)
+            self.packs = [_LayerPack(b, cfg, act, dev) for b in model.blocks]
+            self.emb_c = z(cfg.vocab_size, d)
+            self.w_f = z(d)
+            self.head_w = None if cfg.tie_embeddings else z(cfg.vocab_size, d)
+            self.dW_pack = z(4 * d, d, dt=torch.float32)
+            self.dW_gx = z(2 * d, d, dt=torch.float32)
+            self._packed = False
+        else:
+            self.K_caches = [z(B, h, T, dh) for _ in range(L)]
+            self.V_caches = [z(B, h, T, dh) for _ in range(L)]
+            self.dK = z(B, h, T, dh, dt=torch.float32)
+            self.dV = z(B, h, T, dh, dt=torch.float32)
+        self._sid = 0
+        self._have_dx_top = False
+        self.stats = {"fwd_cells": 0, "bwd_cells": 0}
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self._graphs = {}
+
+    # =============================================================================
+    # public API
+    # =============================================================================
+    def pack(self):
+        """Refresh the compute-dtype weight copies from the master parameters."""
+        if self.backend != "fused":
+            return
+        for p, blk in zip(self.packs, self.model.blocks):
+            p.pack(blk, self.cfg)
+        with torch.no_grad():
+            self.emb_c.copy_(self.model.tok_emb.weight)
+            self.w_f.copy_(self.model.norm_f.weight)
+            if self.head_w is not None:
+                self.head_w.copy_(self.model.lm_head.weight)
+        self._packed = True
+
+    def zero_grads(self):
+        self.grads.zero_()
+
+    @torch.no_grad()
+    def forward(self, idx, targets=None, sid=0, train=False):
+        """Chunked forward at schedule `sid`.  Returns the mean CE loss (fp32 scalar
+        tensor) when targets are given, else None; with keep_logits the logits are
+        in `self.logits`.  `train=True` also produces d loss / d x_L during the head
+        pass so `backward()` needs no second head GEMM."""
+        self.idx.copy_(idx)
+        if targets is not None:
+            self.targets.copy_(targets)
+        self._sid = sid
+        if self.backend == "fused":
+            if not self._packed:
+                self.pack()
+            self._run("fwd", sid, lambda: self._fused_forward(sid))
+            if targets is not None or self.keep_logits:
+                self._run(("head", bool(train), targets is not None), 0,
+                          lambda: self._fused_head(train, targets is not None))
+            self._have_dx_top = bool(train) and targets is not None
+        else:
+            self._generic_forward(sid, targets is not None)
+            self._have_dx_top = False
+        return self.loss if targets is not None else None
+
+    @torch.no_grad()
+    def backward(self, d_logits=None):
+        """Reverse scan.  Default: gradient of the mean CE computed by `forward`.
+        With `d_logits` [B,T,V] (needs keep_logits): gradient of an external loss."""
+        if d_logits is not None:
+            assert self.keep_logits, "explicit d_logits needs keep_logits=True"
+            self.d_logits.copy_(d_logits)
+        if self.backend == "fused":
+            if d_logits is not None:
+                self._fused_head_bwd_from_dlogits()
+            elif not self._have_dx_top:
+                self._fused_head(True, True)
+            self._run("bwd", self._sid, lambda: self._fused_backward(self._sid))
+        else:
+            self._generic_backward(self._sid, d_logits is not None)
+        self._have_dx_top = False
+
+    def train_step(self, idx, targets, sid=0):
+        """forward + backward of one micro-batch; gradients ACCUMULATE in the flat
+        buffer (call `zero_grads()` at the start of an optimizer step)."""
+        loss = self.forward(idx, targets, sid=sid, train=True)
+        self.backward()
+        return loss
+
+    def finish_grads(self, world_size=1, process_group=None, bitwise_sync=True):
+        """Average the flat gradient buffers over data-parallel ranks with library
+        collectives (the baseline path; the fused reduce+AdamW kernels in
+        `parallel.fused_optim` replace it) and expose them as `p.grad`.
+        bitwise_sync: reduce to rank 0, divide, broadcast, so every rank holds
+        identical bytes."""
+        if world_size > 1:
+            import torch.distributed as dist
+            for flat in self.grads.flats:
+                if bitwise_sync:
+                    dist.reduce(flat, dst=0, group=process_group)
+                    flat.div_(world_size)
+                    dist.broadcast(flat, src=0, group=process_group)
+                else:
+                    dist.all_reduce(flat, group=process_group)
+                    flat.div_(world_size)
+        self.grads.to_param_grads()
+
+    def debug_scan(self):
+        """Names of persistent buffers holding non-finite values."""
+        bad = []
+        named = {"loss": self.loss, "dx_top": self.dx_top, "dK": self.dK, "dV": self.dV}
+        for i, t in enumerate(self.xl):
+            named[f"xl[{i}]"] = t
+        for i, (k, v) in enumerate(zip(self.K_caches, self.V_caches)):
+            named[f"K[{i}]"], named[f"V[{i}]"] = k, v
+        for i, f in enumerate(self.grads.flats):
+            named[f"grads.flat[{i}]"] = f
+        for name, t in named.items():
+            if not torch.isfinite(t.float()).all():
+                bad.append(name)
+        return bad
+
+    # =============================================================================
+    # CUDA graphs
+    # =============================================================================
+    def _run(self, key, sid, body):
+        if not self.use_graphs:
+            return body()
+        gkey = (key, sid)
+        g = self._graphs.get(gkey)
+        if g is not None:
+            g.replay()
+            return
+        # first use: run eagerly (this IS the step's result), then record the same
+        # body for later replays; recording executes nothing, so accumulating bodies
+        # (the backward) are not applied twice
+        body()
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self._graphs.get("pool")):
+            body()
+        self._graphs.setdefault("pool", g.pool())
+        self._graphs[gkey] = g
+
+    def capture(self, sids=None):
+        """Capture forward / head / backward graphs for the given schedule ids using
+        the current buffer contents as dummy inputs, then zero the gradients."""
+        if not self.use_graphs:
+            return
+        for sid in (range(len(self.schedules)) if sids is None else sids):
+            self.train_step(self.idx.clone(), self.targets.clone(), sid=sid)
+        self.zero_grads()
+
+    # =============================================================================
+    # fused backend
+    # =============================================================================
+    def _rows(self):
+        return self.B * self.T
+
+    def _fused_forward(self, sid):
+        ops, cfg = self.ops, self.cfg
+        B, T, h, dh, d = self.B, self.T, cfg.n_heads, cfg.head_dim, cfg.d_model
+        scale = 1.0 / dh ** 0.5
+        cos, sin = self.model.rope_cos[:T], self.model.rope_sin[:T]
+        pin = cfg.kmod_vraw_heads * dh
+        x = F.embedding(self.idx, self.emb_c)
+        for li in range(self.L):
+            P = self.packs[li]
+            self.xl[li].copy_(x)
+            xhat, _ = ops.rms_fwd(x, P.w_an)
+            q_r = ops.rope(ops.linear(xhat, P.wq).view(B, T, h, dh), cos, sin)
+            k = ops.linear(xhat, P.wk)
+            v = ops.linear(xhat, P.wv)
+            kself_r = ops.rope(k.view(B, T, h, dh), cos, sin)
+            glx = ops.linear(xhat, P.W_gx, bias=P.b_g)
+            Kc, Vc, o_all = self.K_caches[li], self.V_caches[li], self.o_saved[li]
+            v4 = v.view(B, T, h, dh)
+            for pos0, c, n_sweeps in self.schedules[sid]:
+                r = slice(pos0, pos0 + c)
+                o_c, lse_c = ops.prefix_fwd(q_r[:, r], Kc, Vc, pos0, scale, self.window)
+                K_in, V_in = kself_r[:, r], v4[:, r]
+                o = None
+                for _ in range(n_sweeps):
+                    o, _ = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
+                                        o_c, lse_c, scale, self.window)
+                    u, _ = ops.rms_fwd(o.reshape(B, c, d), P.w_ctx)
+                    cg = ops.linear(u, P.W_pack)
+                    K_in, V_in = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                                                h, pin)
+                Kc[:, r] = K_in
+                Vc[:, r] = V_in
+                o_all[:, r] = o.reshape(B, c, d)
+                self.stats["fwd_cells"] += 1
+            x_mid = x + ops.linear(o_all, P.wo)
+            xn, _ = ops.rms_fwd(x_mid, P.w_mn)
+            g = ops.swiglu_fwd(ops.linear(xn, P.w1), ops.linear(xn, P.w3))
+            x = x_mid + ops.linear(g, P.w2)
+        self.xl[self.L].copy_(x)
+
+    def _head_weight(self):
+        return self.emb_c if self.head_w is None else self.head_w
+
+    def _head_grad_view(self):
+        return self.grads.get(self.model.lm_head.weight)
+
+    def _fused_head(self, train, have_targets):
+        """norm_f + unembedding + fp32 CE over row slabs (no [B,T,V] tensor unless
+        keep_logits); with train=True also d x_L and the head weight gradients."""
+        ops, d = self.ops, self.cfg.d_model
+        N = self._rows()
+        x = self.xl[self.L].view(N, d)
+        tg = self.targets.view(N)
+        W = self._head_weight()
+        inv_n = 1.0 / max(1, N) if not have_targets else None
+        if have_targets:
+            inv_n = 1.0 / (tg >= 0).sum().clamp_min(1).float()
+        self.loss.zero_()
+        dxt = self.dx_top.view(N, d)
+        for r0 in range(0, N, self.loss_rows):
+            r = slice(r0, min(N, r0 + self.loss_rows))
+            xf, rstd = ops.rms_fwd(x[r], self.w_f)
+            logits = ops.linear(xf, W)
+            if self.keep_logits:
+                self.logits.view(N, -1)[r] = logits
+            if not have_targets:
+                continue
+            loss, dlog = ops.ce_chunk(logits, tg[r], inv_n)
+            self.loss += loss
+            if train:
+                ops.linear_dw_acc(self._head_grad_view(), dlog, xf)
+                dxf = ops.linear_dx(dlog, W)
+                dx, dw = ops.rms_bwd(dxf, x[r], self.w_f, rstd)
+                dxt[r] = dx
+                self.grads.get(self.model.norm_f.weight).add_(dw)
+
+    def _fused_head_bwd_from_dlogits(self):
+        ops, d = self.ops, self.cfg.d_model
+        N = self._rows()
+        x, W = self.xl[self.L].view(N, d), self._head_weight()
+        dl = self.d_logits.view(N, -1)
+        dxt = self.dx_top.view(N, d)
+        for r0 in range(0, N, self.loss_rows):
+            r = slice(r0, min(N, r0 + self.loss_rows))
+            xf, rstd = ops.rms_fwd(x[r], self.w_f)
+            ops.linear_dw_acc(self._head_grad_view(), dl[r], xf)
+            dx, dw = ops.rms_bwd(ops.linear_dx(dl[r], W), x[r], self.w_f, rstd)
+            dxt[r] = dx
+            self.grads.get(self.model.norm_f.weight).add_(dw)
+
+    def _fused_backward(self, sid):
+        ops, cfg, G = self.ops, self.cfg, self.grads
+        B, T, h, dh, d = self.B, self.T, cfg.n_heads, cfg.head_dim, cfg.d_model
+        act, f32 = self.act, torch.float32
+        scale = 1.0 / dh ** 0.5
+        cos, sin = self.model.rope_cos[:T], self.model.rope_sin[:T]
+        pin = cfg.kmod_vraw_heads * dh
+        dev = self.device
+        dx = self.dx_top.clone()                                   # d loss / d x_{l+1}
+        for li in range(self.L - 1, -1, -1):
+            P, blk = self.packs[li], self.model.blocks[li]
+            a = blk.attn
+            x = self.xl[li]
+            o_all = self.o_saved[li]
+            # ---- W_O + SwiGLU block, all T ------------------------------------------------
+            x_mid = x + ops.linear(o_all, P.wo)
+            xn, rstd_m = ops.rms_fwd(x_mid, P.w_mn)
+            h1, h3 = ops.linear(xn, P.w1), ops.linear(xn, P.w3)
+            g = ops.swiglu_fwd(h1, h3)
+            ops.linear_dw_acc(G.get(blk.mlp.w2.weight), dx, g)
+            dg = ops.linear_dx(dx, P.w2)
+            dh1, dh3 = ops.swiglu_bwd(dg, h1, h3)
+            ops.linear_dw_acc(G.get(blk.mlp.w1.weight), dh1, xn)
+            ops.linear_dw_acc(G.get(blk.mlp.w3.weight), dh3, xn)
+            dxn = ops.linear_dx(dh1, P.w1) + ops.linear_dx(dh3, P.w3)
+            dxm, dw = ops.rms_bwd(dxn, x_mid, P.w_mn, rstd_m)
+            G.get(blk.mlp_norm.weight).add_(dw)
+            dx_mid = (dx.float() + dxm).to(act)
+            ops.linear_dw_acc(G.get(a.wo.weight), dx_mid, o_all)
+            dO_all = ops.linear_dx(dx_mid, P.wo).view(B, T, h, dh)
+            # ---- recompute the layer projections ----------------------------------------------
+            xhat, rstd_a = ops.rms_fwd(x, P.w_an)
+            q = ops.linear(xhat, P.wq)
+            k = ops.linear(xhat, P.wk)
+            v = ops.linear(xhat, P.wv)
+            q_r = ops.rope(q.view(B, T, h, dh), cos, sin)
+            kself_r = ops.rope(k.view(B, T, h, dh), cos, sin)
+            glx = ops.linear(xhat, P.W_gx, bias=P.b_g)
+            v4 = v.view(B, T, h, dh)
+            Kc, Vc = self.K_caches[li], self.V_caches[li]
+            self.dK.zero_()
+            self.dV.zero_()
+            self.dW_pack.zero_()
+            dq_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
+            dks_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
+            dk = torch.zeros(B, T, d, dtype=f32, device=dev)
+            dv = torch.zeros(B, T, d, dtype=f32, device=dev)
+            dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev)
+            dw_ctx = G.get(a.norm_ctx.weight)
+            # ---- cells in reverse ---------------------------------------------------------------
+            for pos0, c, n_sweeps in reversed(self.schedules[sid]):
+                r = slice(pos0, pos0 + c)
+                qc, ksc, vc4 = q_r[:, r], kself_r[:, r], v4[:, r]
+                o_c, lse_c = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, self.window)
+                # forward recompute, keeping each sweep's state
+                st = []
+                K_in, V_in = ksc, vc4
+                for _ in range(n_sweeps):
+                    o, lse = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
+                    u, rstd = ops.rms_fwd(o.reshape(B, c, d), P.w_ctx)
+                    cg = ops.linear(u, P.W_pack)
+                    st.append((K_in, V_in, o, lse, u, rstd, cg))
+                    K_in, V_in = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                                                h, pin)
+                dK_out, dV_out = self.dK[:, r].clone(), self.dV[:, r].clone()
+                d_o = dO_all[:, r].float()
+                do_c = torch.zeros_like(o_c)
+                dlse_c = torch.zeros_like(lse_c)
+                dq_c = torch.zeros(B, c, h, dh, dtype=f32, device=dev)
+                for s in range(n_sweeps - 1, -1, -1):
+                    K_in, V_in, o, lse, u, rstd, cg = st[s]
+                    dcg, dk_s, dv_s = ops.refine_bwd(dK_out, dV_out, cg, glx[:, r], k[:, r], v[:, r],
+                                                     cos[r], sin[r], pin)
+                    dk[:, r] += dk_s
+                    dv[:, r] += dv_s
+                    dglx[:, r] += dcg[..., 2 * d:]
+                    dcg_a = dcg.to(act)
+                    ops.linear_dw_acc(self.dW_pack, dcg_a, u)
+                    du = ops.linear_dx(dcg_a, P.W_pack)
+                    do_n, dw = ops.rms_bwd(du, o.reshape(B, c, d), P.w_ctx, rstd)
+                    dw_ctx.add_(dw)
+                    d_o = d_o + do_n.view(B, c, h, dh) if s == n_sweeps - 1 else do_n.view(B, c, h, dh)
+                    dq_s, dks_s, dvr_s, dK_in, dV_in, do_c_s, dlse_s = ops.tail_bwd(
+                        d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window)
+                    dq_c += dq_s
+                    dks_r[:, r] += dks_s
+                    dv[:, r] += dvr_s.reshape(B, c, d)
+                    do_c += do_c_s
+                    dlse_c += dlse_s
+                    dK_out, dV_out = dK_in, dV_in
+                # sweep 0 read the raw rows
+                dks_r[:, r] += dK_out
+                dv[:, r] += dV_out.reshape(B, c, d)
+                ops.prefix_bwd(qc, Kc, Vc, pos0, scale, self.window, o_c, lse_c, do_c, dlse_c,
+                               dq_c, self.dK, self.dV)
+                dq_r[:, r] = dq_c
+                self.stats["bwd_cells"] += 1
+            # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
+            dq = ops.unrope(dq_r, cos, sin).reshape(B, T, d).to(act)
+            dk_t = (dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)).to(act)
+            dv_t = dv.to(act)
+            dglx_a = dglx.to(act)
+            ops.linear_dw_acc(G.get(a.wq.weight), dq, xhat)
+            ops.linear_dw_acc(G.get(a.wk.weight), dk_t, xhat)
+            ops.linear_dw_acc(G.get(a.wv.weight), dv_t, xhat)
+            self.dW_gx.zero_()
+            ops.linear_dw_acc(self.dW_gx, dglx_a, xhat)
+            db_g = dglx.reshape(-1, 2 * d).sum(0)
+            dxhat = (ops.linear_dx(dq, P.wq).float() + ops.linear_dx(dk_t, P.wk).float()
+                     + ops.linear_dx(dv_t, P.wv).float() + ops.linear_dx(dglx_a, P.W_gx).float())
+            dxa, dw = ops.rms_bwd(dxhat, x, P.w_an, rstd_a)
+            G.get(blk.attn_norm.weight).add_(dw)
+            dx = (dx_mid.float() + dxa).to(act)
+            self._scatter_packed_grads(a, db_g)
+        G.get(self.model.tok_emb.weight).index_add_(
+            0, self.idx.view(-1), dx.reshape(-1, d).float())
+
+    def _scatter_packed_grads(self, a, db_g):
+        """Route the packed-weight gradients of one layer to the parameters."""
+        G, d = self.grads, self.cfg.d_model
+        dWp, dWx = self.dW_pack, self.dW_gx
+        for mod, rows in ((a.w_kctx, slice(0, d)), (a.w_vctx, slice(d, 2 * d))):
+            if isinstance(mod, LoRALinear):
+                G.get(mod.up.weight).add_(dWp[rows] @ mod.down.weight.float().t())
+                G.get(mod.down.weight).add_(mod.up.weight.float().t() @ dWp[rows])
+            else:
+                G.get(mod.weight).add_(dWp[rows])
+        for mod, ru, rx, rb in ((a.w_gk, slice(2 * d, 3 * d), slice(0, d), slice(0, d)),
+                                (a.w_gv, slice(3 * d, 4 * d), slice(d, 2 * d), slice(d, 2 * d))):
+            dW = torch.cat((dWx[rx], dWp[ru]), dim=1)                 # [d, 2d] = [x half | u half]
+            if isinstance(mod, LoRAGate):
+                G.get(mod.b.weight).add_(dW @ mod.a.weight.float().t())
+                G.get(mod.a.weight).add_(mod.b.weight.float().t() @ dW)
+                G.get(mod.b.bias).add_(db_g[rb])
+            else:
+                G.get(mod.weight).add_(dW)
+                G.get(mod.bias).add_(db_g[rb])
+
+    # =============================================================================
+    # generic backend (every config knob; autograd re-run of the reference cell)
+    # =============================================================================
+    def _amp(self):
+        return torch.autocast(self.device.type, dtype=torch.bfloat16,
+                              enabled=self.autocast_bf16, cache_enabled=False)
+
+    def _generic_forward(self, sid, have_targets):
+        m = self.model
+        with self._amp():
+            x = m.tok_emb(self.idx)
+            cos, sin = m.rope_cos[:self.T], m.rope_sin[:self.T]
+            for li, blk in enumerate(m.blocks):
+                self.xl[li].copy_(x)
+                o = gcell.layer_forward(blk.attn, blk.attn_norm(x), cos, sin, self.schedules[sid],
+                                        self.K_caches[li], self.V_caches[li])
+                x = x + blk.attn.wo(o)
+                x = x + blk.mlp(blk.mlp_norm(x))
+                self.stats["fwd_cells"] += len(self.schedules[sid])
+            self.xl[self.L].copy_(x)
+            if have_targets or self.keep_logits:
+                self._generic_head(False, have_targets)
+
+    def _generic_head(self, with_grad, have_targets, d_logits=None):
+        m, d = self.model, self.cfg.d_model
+        N = self._rows()
+        x, tg = self.xl[self.L].view(N, d), self.targets.view(N)
+        hp = [m.norm_f.weight, m.lm_head.weight]
+        inv_n = 1.0 / (tg >= 0).sum().clamp_min(1).float() if have_targets else None
+        if not with_grad:
+            self.loss.zero_()
+        for r0 in range(0, N, self.loss_rows):
+            r = slice(r0, min(N, r0 + self.loss_rows))
+            with torch.set_grad_enabled(with_grad), self._amp():
+                xr = x[r].detach().requires_grad_(with_grad)
+                logits = m.lm_head(m.norm_f(xr))
+                if self.keep_logits and not with_grad:
+                    self.logits.view(N, -1)[r] = logits
+                if d_logits is None and have_targets:
+                    ls = F.cross_entropy(logits.float(), tg[r], ignore_index=-1,
+                                         reduction="sum") * inv_n
+            if not with_grad:
+                if have_targets:
+                    self.loss += ls
+                continue
+            if d_logits is None:
+                gs = torch.autograd.grad([ls], [xr] + hp, allow_unused=True)
+            else:
+                gs = torch.autograd.grad([logits], [xr] + hp, [d_logits.view(N, -1)[r].to(logits.dtype)],
+                                         allow_unused=True)
+            self.dx_top.view(N, d)[r] = gs[0]
+            for p, g in zip(hp, gs[1:]):
+                self.grads.add(p, g)
+
+    def _generic_backward(self, sid, from_dlogits):
+        m, G = self.model, self.grads
+        T = self.T
+        cos, sin = m.rope_cos[:T], m.rope_sin[:T]
+        self._generic_head(True, not from_dlogits, self.d_logits if from_dlogits else None)
+        dx = self.dx_top.clone()
+        for li in range(self.L - 1, -1, -1):
+            blk = m.blocks[li]
+            attn = blk.attn
+            params = list(blk.parameters())
+            x_l, Kc, Vc = self.xl[li], self.K_caches[li], self.V_caches[li]
+            self.dK.zero_()
+            self.dV.zero_()
+            dx_l = torch.zeros_like(x_l)
+            for pos0, c, n_sweeps in reversed(self.schedules[sid]):
+                r = slice(pos0, pos0 + c)
+                with torch.enable_grad(), self._amp():
+                    x_c = x_l[:, r].detach().requires_grad_(True)
+                    K_comm = Kc[:, :, :pos0].detach().requires_grad_(True)
+                    V_comm = Vc[:, :, :pos0].detach().requires_grad_(True)
+                    o_cat, K_rows, V_rows = gcell.chunk_cell_forward(
+                        attn, blk.attn_norm(x_c), cos[r], sin[r], K_comm, V_comm, n_sweeps)
+                    x_mid = x_c + attn.wo(o_cat)
+                    x_next = x_mid + blk.mlp(blk.mlp_norm(x_mid))
+                gs = torch.autograd.grad(
+                    [x_next, K_rows, V_rows], [x_c, K_comm, V_comm] + params,
+                    [dx[:, r].to(x_next.dtype), self.dK[:, :, r].to(K_rows.dtype),
+                     self.dV[:, :, r].to(V_rows.dtype)], allow_unused=True)
+                gx, gK, gV = gs[0], gs[1], gs[2]
+                if self.sat_tau > 0:
+                    gx, gK, gV = self._saturate(gx, gK, gV, dx[:, r])
+                dx_l[:, r] = gx
+                if pos0 > 0 and gK is not None:
+                    self.dK[:, :, :pos0] += gK.float()
+                    self.dV[:, :, :pos0] += gV.float()
+                for p, g in zip(params, gs[3:]):
+                    G.add(p, g)
+                self.stats["bwd_cells"] += 1
+            dx = dx_l
+        G.get(m.tok_emb.weight).index_add_(0, self.idx.view(-1),
+                                           dx.reshape(-1, self.cfg.d_model).float())
+
+    def _saturate(self, gx, gK, gV, dx_in):
+        """Saturating backward: cap each row of the gradients a cell hands to earlier
+        positions at sat_tau x the norm of the gradient entering that row, keeping
+        the direction; rows with non-finite entries become zero."""
+        ref = dx_in.float().norm(dim=-1).mean().clamp_min(1e-12) * self.sat_tau
+
+        def cap(g):
+            if g is None:
+                return g
+            gf = torch.nan_to_num(g.float(), nan=0.0, posinf=0.0, neginf=0.0)
+            n = gf.norm(dim=-1, keepdim=True)
+            return (gf * (ref / n.clamp_min(1e-20)).clamp(max=1.0)).to(g.dtype)
+
+        return cap(gx), cap(gK), cap(gV)
