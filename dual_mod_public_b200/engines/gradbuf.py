@@ -71,6 +71,17 @@ class GradBuffers:
                 self.buf[id(p)] = lay.view(flat, p)
         self.flat = self.flats[0]
 
+    @classmethod
+    def from_flat(cls, params, layout, flat):
+        """Views into an existing flat array placed by `layout` (anything with
+        `.view(flat, p)`), e.g. the fused optimizer's peer-mapped gradient buffer."""
+        self = cls.__new__(cls)
+        self.order = unique_params(params)
+        self.flats, self.layouts = [flat], [layout]
+        self.buf = {id(p): layout.view(flat, p) for p in self.order}
+        self.flat = flat
+        return self
+
     def zero_(self):
         for f in self.flats:
             f.zero_()

@@ -86,7 +86,8 @@ class _LayerPack:
 class WaveScanEngine:
     def __init__(self, model, schedules, B, T, device=None, autocast_bf16=False,
                  keep_logits=False, loss_rows=4096, use_graphs=False, backend="auto",
-                 ops=None, grad_bf16_ids=None, grad_alloc=None, grad_pad_to=1, sat_tau=0.0):
+                 ops=None, grad_bf16_ids=None, grad_alloc=None, grad_pad_to=1, sat_tau=0.0,
+                 grads=None, on_layer_grads_final=None):
         cfg = model.cfg
         self.model, self.cfg = model, cfg
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
@@ -118,8 +119,12 @@ class WaveScanEngine:
         self.targets = torch.zeros(B, T, dtype=torch.long, device=dev)
         self.xl = [z(B, T, d) for _ in range(L + 1)]          # layer inputs, xl[L] feeds norm_f
         self.loss = torch.zeros((), dtype=torch.float32, device=dev)
-        self.grads = GradBuffers(list(model.parameters()), bf16_ids=grad_bf16_ids,
-                                 alloc=grad_alloc, pad_total_to=grad_pad_to)
+        self.grads = grads if grads is not None else GradBuffers(
+            list(model.parameters()), bf16_ids=grad_bf16_ids, alloc=grad_alloc, pad_total_to=grad_pad_to)
+        # called as fn(layer_index) right after a layer's parameter gradients are complete
+        # (layer_index == -1: the head / final norm), so a data-parallel reducer can start
+        # that layer's bucket while the reverse scan continues
+        self.on_layer_grads_final = on_layer_grads_final
         self.dx_top = z(B, T, d)                               # d loss / d xl[L]
         if keep_logits:
             self.logits = z(B, T, cfg.vocab_size)
@@ -357,9 +362,8 @@ class WaveScanEngine:
             if train:
                 ops.linear_dw_acc(self._head_grad_view(), dlog, xf)
                 dxf = ops.linear_dx(dlog, W)
-                dx, dw = ops.rms_bwd(dxf, x[r], self.w_f, rstd)
-                dxt[r] = dx
-                self.grads.get(self.model.norm_f.weight).add_(dw)
+                dxt[r] = ops.rms_bwd(dxf, x[r], self.w_f, rstd, self.grads.get(self.model.norm_f.weight),
+                                     out_dtype=self.act)
 
     def _fused_head_bwd_from_dlogits(self):
         ops, d = self.ops, self.cfg.d_model
@@ -371,9 +375,8 @@ class WaveScanEngine:
             r = slice(r0, min(N, r0 + self.loss_rows))
             xf, rstd = ops.rms_fwd(x[r], self.w_f)
             ops.linear_dw_acc(self._head_grad_view(), dl[r], xf)
-            dx, dw = ops.rms_bwd(ops.linear_dx(dl[r], W), x[r], self.w_f, rstd)
-            dxt[r] = dx
-            self.grads.get(self.model.norm_f.weight).add_(dw)
+            dxt[r] = ops.rms_bwd(ops.linear_dx(dl[r], W), x[r], self.w_f, rstd,
+                                 self.grads.get(self.model.norm_f.weight), out_dtype=self.act)
 
     def _fused_backward(self, sid):
         ops, cfg, G = self.ops, self.cfg, self.grads
@@ -400,9 +403,8 @@ class WaveScanEngine:
             ops.linear_dw_acc(G.get(blk.mlp.w1.weight), dh1, xn)
             ops.linear_dw_acc(G.get(blk.mlp.w3.weight), dh3, xn)
             dxn = ops.linear_dx(dh1, P.w1) + ops.linear_dx(dh3, P.w3)
-            dxm, dw = ops.rms_bwd(dxn, x_mid, P.w_mn, rstd_m)
-            G.get(blk.mlp_norm.weight).add_(dw)
-            dx_mid = (dx.float() + dxm).to(act)
+            dx_mid = ops.rms_bwd(dxn, x_mid, P.w_mn, rstd_m, G.get(blk.mlp_norm.weight),
+                                 residual=dx, out_dtype=act)
             ops.linear_dw_acc(G.get(a.wo.weight), dx_mid, o_all)
             dO_all = ops.linear_dx(dx_mid, P.wo).view(B, T, h, dh)
             # ---- recompute the layer projections ----------------------------------------------
@@ -423,6 +425,7 @@ class WaveScanEngine:
             dk = torch.zeros(B, T, d, dtype=f32, device=dev)
             dv = torch.zeros(B, T, d, dtype=f32, device=dev)
             dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev)
+            dv4 = dv.view(B, T, h, dh)
             dw_ctx = G.get(a.norm_ctx.weight)
             # ---- cells in reverse ---------------------------------------------------------------
             for pos0, c, n_sweeps in reversed(self.schedules[sid]):
@@ -439,35 +442,26 @@ class WaveScanEngine:
                     st.append((K_in, V_in, o, lse, u, rstd, cg))
                     K_in, V_in = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
                                                 h, pin)
-                dK_out, dV_out = self.dK[:, r].clone(), self.dV[:, r].clone()
+                dK_out, dV_out = self.dK[:, r].contiguous(), self.dV[:, r].contiguous()
                 d_o = dO_all[:, r].float()
                 do_c = torch.zeros_like(o_c)
                 dlse_c = torch.zeros_like(lse_c)
                 dq_c = torch.zeros(B, c, h, dh, dtype=f32, device=dev)
                 for s in range(n_sweeps - 1, -1, -1):
                     K_in, V_in, o, lse, u, rstd, cg = st[s]
-                    dcg, dk_s, dv_s = ops.refine_bwd(dK_out, dV_out, cg, glx[:, r], k[:, r], v[:, r],
-                                                     cos[r], sin[r], pin)
-                    dk[:, r] += dk_s
-                    dv[:, r] += dv_s
-                    dglx[:, r] += dcg[..., 2 * d:]
-                    dcg_a = dcg.to(act)
-                    ops.linear_dw_acc(self.dW_pack, dcg_a, u)
-                    du = ops.linear_dx(dcg_a, P.W_pack)
-                    do_n, dw = ops.rms_bwd(du, o.reshape(B, c, d), P.w_ctx, rstd)
-                    dw_ctx.add_(dw)
-                    d_o = d_o + do_n.view(B, c, h, dh) if s == n_sweeps - 1 else do_n.view(B, c, h, dh)
-                    dq_s, dks_s, dvr_s, dK_in, dV_in, do_c_s, dlse_s = ops.tail_bwd(
-                        d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window)
-                    dq_c += dq_s
-                    dks_r[:, r] += dks_s
-                    dv[:, r] += dvr_s.reshape(B, c, d)
-                    do_c += do_c_s
-                    dlse_c += dlse_s
-                    dK_out, dV_out = dK_in, dV_in
+                    dcg = ops.refine_bwd(dK_out, dV_out, cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                                         pin, dk[:, r], dv[:, r], dglx[:, r])
+                    ops.linear_dw_acc(self.dW_pack, dcg, u)
+                    du = ops.linear_dx(dcg, P.W_pack)
+                    d_o = ops.rms_bwd(du, o.reshape(B, c, d), P.w_ctx, rstd, dw_ctx,
+                                      residual=d_o.view(B, c, d) if s == n_sweeps - 1 else None
+                                      ).view(B, c, h, dh)
+                    dK_out, dV_out = ops.tail_bwd(
+                        d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
+                        dq_c, dks_r[:, r], dv4[:, r], do_c, dlse_c)
                 # sweep 0 read the raw rows
                 dks_r[:, r] += dK_out
-                dv[:, r] += dV_out.reshape(B, c, d)
+                dv4[:, r] += dV_out
                 ops.prefix_bwd(qc, Kc, Vc, pos0, scale, self.window, o_c, lse_c, do_c, dlse_c,
                                dq_c, self.dK, self.dV)
                 dq_r[:, r] = dq_c
@@ -482,13 +476,15 @@ class WaveScanEngine:
             ops.linear_dw_acc(G.get(a.wv.weight), dv_t, xhat)
             self.dW_gx.zero_()
             ops.linear_dw_acc(self.dW_gx, dglx_a, xhat)
-            db_g = dglx.reshape(-1, 2 * d).sum(0)
+            db_g = torch.zeros(2 * d, dtype=f32, device=dev)
+            ops.col_sum_acc(db_g, dglx)
             dxhat = (ops.linear_dx(dq, P.wq).float() + ops.linear_dx(dk_t, P.wk).float()
                      + ops.linear_dx(dv_t, P.wv).float() + ops.linear_dx(dglx_a, P.W_gx).float())
-            dxa, dw = ops.rms_bwd(dxhat, x, P.w_an, rstd_a)
-            G.get(blk.attn_norm.weight).add_(dw)
-            dx = (dx_mid.float() + dxa).to(act)
+            dx = ops.rms_bwd(dxhat, x, P.w_an, rstd_a, G.get(blk.attn_norm.weight),
+                             residual=dx_mid, out_dtype=act)
             self._scatter_packed_grads(a, db_g)
+            if self.on_layer_grads_final is not None:
+                self.on_layer_grads_final(li)
         G.get(self.model.tok_emb.weight).index_add_(
             0, self.idx.view(-1), dx.reshape(-1, d).float())
 

@@ -1,0 +1,335 @@
+"""sm_100a op table: ctypes bindings of `libdmb200.so` behind the `TorchOps` interface.
+
+Every method runs the hand-written kernel when the operands are in the layout
+it was built for (bf16 activations, head_dim 64/128, chunk 16/32/64, ...), and
+otherwise defers to the plain-torch statement of the same op, so exotic shapes
+stay correct.  `launches` counts kernel launches issued by this table.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from .torch_ops import TorchOps
+
+_LIB = None
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class TView(ctypes.Structure):
+    _fields_ = [("bs", ctypes.c_longlong), ("rs", ctypes.c_longlong)]
+
+
+def load_library():
+    """Load (building if needed and possible) the kernel library; raises when it
+    cannot be had — a GPU run must never silently fall back."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = os.path.join(_HERE, "libdmb200.so")
+    if not os.path.exists(path):
+        from .build import build
+        build()
+    _LIB = ctypes.CDLL(path)
+    for name in dir(_Sigs):
+        if name.startswith("dmb_"):
+            fn = getattr(_LIB, name)
+            fn.restype = ctypes.c_int
+            fn.argtypes = getattr(_Sigs, name)
+    return _LIB
+
+
+_p, _i, _f, _ll, _v = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong, TView
+
+
+class _Sigs:
+    dmb_rms_fwd = [_p, _ll, _p, _p, _p, _i, _i, _f, _p]
+    dmb_rms_bwd_dx = [_p, _i, _p, _ll, _p, _p, _p, _p, _i, _i, _i, _p]
+    dmb_col_reduce_acc = [_p, _i, _p, _ll, _p, _p, _i, _p, _i, _i, _p]
+    dmb_rope = [_p, _i, _ll, _ll, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]
+    dmb_refine_fwd = [_p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]
+    dmb_refine_bwd = [_p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _v, _p, _v, _p, _v,
+                      _i, _i, _i, _i, _i, _p]
+    dmb_swiglu_fwd = [_p, _p, _p, _ll, _p]
+    dmb_swiglu_bwd = [_p, _p, _p, _p, _p, _ll, _p]
+    dmb_ce = [_p, _p, _p, _p, _p, _i, _i, _p]
+    dmb_tail_fwd = [_p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
+    dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _v, _p, _v,
+                    _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
+    dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
+    dmb_prefix_bwd = [_p, _v, _p, _p, _v, _p, _p, _p, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i,
+                      _f, _i, _p]
+
+
+BF16 = torch.bfloat16
+F32 = torch.float32
+
+
+def _tv(t: torch.Tensor) -> TView:
+    """(batch stride, row stride) of a [B, rows, ...] tensor whose trailing dims are dense."""
+    return TView(t.stride(0), t.stride(1))
+
+
+def _dense_tail(t: torch.Tensor, n_tail: int) -> bool:
+    """True when the last n_tail dims are laid out densely (row-contiguous)."""
+    exp = 1
+    for i in range(1, n_tail + 1):
+        if t.shape[-i] != 1 and t.stride(-i) != exp:
+            return False
+        exp *= t.shape[-i]
+    return True
+
+
+class CudaOps(TorchOps):
+    name = "sm100a"
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.lib = load_library()
+        self.launches = 0
+        self._scratch = {}
+        self.gemm = None                       # set by enable_gemm()
+        try:
+            from .gemm import Tcgen05Gemm
+            self.gemm = Tcgen05Gemm(self.lib, self.device)
+        except Exception:                      # the GEMM needs the driver's tensor-map entry point
+            self.gemm = None
+
+    # ---- helpers ---------------------------------------------------------------------------
+    def _st(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _ck(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what} failed with code {rc}")
+        self.launches += 1
+
+    def _scratch_f32(self, key, n):
+        buf = self._scratch.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(n, dtype=F32, device=self.device)
+            self._scratch[key] = buf
+        return buf
+
+    # ---- GEMMs -------------------------------------------------------------------------------
+    def linear(self, x, w, bias=None, out_dtype=None):
+        if self.gemm is not None and bias is None and self.gemm.ok_tn(x, w):
+            y = self.gemm.linear(x, w, out_dtype or x.dtype)
+            self.launches += 1
+            return y
+        return super().linear(x, w, bias, out_dtype)
+
+    def linear_dx(self, dy, w):
+        if self.gemm is not None and self.gemm.ok_nn(dy, w):
+            self.launches += 1
+            return self.gemm.linear_dx(dy, w)
+        return super().linear_dx(dy, w)
+
+    def linear_dw_acc(self, dW, dy, x):
+        if self.gemm is not None and self.gemm.ok_tn_dw(dW, dy, x):
+            self.launches += 1
+            return self.gemm.linear_dw_acc(dW, dy, x)
+        return super().linear_dw_acc(dW, dy, x)
+
+    # ---- norms ------------------------------------------------------------------------------------
+    def rms_fwd(self, x, w, eps=1e-5):
+        d = x.shape[-1]
+        if x.dtype != BF16 or d % 8:
+            return super().rms_fwd(x, w, eps)
+        if not x.is_contiguous():
+            x = x.contiguous()
+        x2 = x.view(-1, d)
+        rows = x2.shape[0]
+        y = torch.empty(rows, d, dtype=BF16, device=x.device)
+        rstd = torch.empty(rows, dtype=F32, device=x.device)
+        self._ck(self.lib.dmb_rms_fwd(x2.data_ptr(), x2.stride(0), w.data_ptr(), y.data_ptr(),
+                                      rstd.data_ptr(), rows, d, eps, self._st()), "rms_fwd")
+        return y.view(*x.shape), rstd.view(*x.shape[:-1], 1)
+
+    def rms_bwd(self, dy, x, w, rstd, dw_acc, residual=None, out_dtype=F32):
+        d = x.shape[-1]
+        ok = (x.dtype == BF16 and dy.dtype in (BF16, F32) and out_dtype in (BF16, F32)
+              and x.is_contiguous() and dy.is_contiguous()
+              and (residual is None or (residual.is_contiguous() and residual.dtype == out_dtype)))
+        if not ok:
+            return super().rms_bwd(dy, x, w, rstd, dw_acc, residual, out_dtype)
+        rows = x.numel() // d
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        rs = rstd.reshape(-1)
+        self._ck(self.lib.dmb_rms_bwd_dx(dy.data_ptr(), int(dy.dtype == F32), x.data_ptr(), d,
+                                         w.data_ptr(), rs.data_ptr(),
+                                         residual.data_ptr() if residual is not None else None,
+                                         out.data_ptr(), int(out_dtype == F32), rows, d, self._st()),
+                 "rms_bwd_dx")
+        nsplit = max(1, min(64, rows // 64))
+        part = self._scratch_f32("col", nsplit * d)
+        self._ck(self.lib.dmb_col_reduce_acc(dy.data_ptr(), int(dy.dtype == F32), x.data_ptr(), d,
+                                             rs.data_ptr(), part.data_ptr(), nsplit, dw_acc.data_ptr(),
+                                             rows, d, self._st()), "rms_bwd_dw")
+        self.launches += 1
+        return out
+
+    def col_sum_acc(self, out, dy):
+        n = dy.shape[-1]
+        if dy.dtype not in (BF16, F32) or not dy.is_contiguous():
+            return super().col_sum_acc(out, dy)
+        rows = dy.numel() // n
+        nsplit = max(1, min(64, rows // 64))
+        part = self._scratch_f32("col", nsplit * n)
+        self._ck(self.lib.dmb_col_reduce_acc(dy.data_ptr(), int(dy.dtype == F32), None, 0, None,
+                                             part.data_ptr(), nsplit, out.data_ptr(), rows, n,
+                                             self._st()), "col_sum")
+        self.launches += 1
+
+    # ---- rope -----------------------------------------------------------------------------------------
+    def _rope(self, x, cos, sin, sign, out_dtype):
+        B, T, H, DH = x.shape
+        if x.dtype not in (BF16, F32) or not _dense_tail(x, 2) or not cos.is_contiguous():
+            return None
+        out = torch.empty(B, T, H, DH, dtype=out_dtype, device=x.device)
+        self._ck(self.lib.dmb_rope(x.data_ptr(), int(x.dtype == F32), x.stride(0), x.stride(1),
+                                   cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
+                                   int(out_dtype == F32), B, T, H, DH, sign, self._st()), "rope")
+        return out
+
+    def rope(self, x, cos, sin):
+        out = self._rope(x, cos, sin, 1.0, x.dtype) if x.is_cuda else None
+        return out if out is not None else super().rope(x, cos, sin)
+
+    def unrope(self, x, cos, sin):
+        out = self._rope(x, cos, sin, -1.0, x.dtype) if x.is_cuda else None
+        return out if out is not None else super().unrope(x, cos, sin)
+
+    # ---- swiglu ------------------------------------------------------------------------------------------
+    def swiglu_fwd(self, h1, h3):
+        if h1.dtype != BF16 or not (h1.is_contiguous() and h3.is_contiguous()) or h1.numel() % 8:
+            return super().swiglu_fwd(h1, h3)
+        g = torch.empty_like(h1)
+        self._ck(self.lib.dmb_swiglu_fwd(h1.data_ptr(), h3.data_ptr(), g.data_ptr(), h1.numel(),
+                                         self._st()), "swiglu_fwd")
+        return g
+
+    def swiglu_bwd(self, dg, h1, h3):
+        if h1.dtype != BF16 or dg.dtype != BF16 or h1.numel() % 8 or not (
+                dg.is_contiguous() and h1.is_contiguous() and h3.is_contiguous()):
+            return super().swiglu_bwd(dg, h1, h3)
+        d1, d3 = torch.empty_like(h1), torch.empty_like(h3)
+        self._ck(self.lib.dmb_swiglu_bwd(dg.data_ptr(), h1.data_ptr(), h3.data_ptr(), d1.data_ptr(),
+                                         d3.data_ptr(), h1.numel(), self._st()), "swiglu_bwd")
+        return d1, d3
+
+    # ---- CE ---------------------------------------------------------------------------------------------------
+    def ce_chunk(self, logits, targets, inv_n):
+        if logits.dtype != BF16 or not logits.is_contiguous() or not torch.is_tensor(inv_n):
+            return super().ce_chunk(logits, targets, inv_n)
+        n, V = logits.shape
+        row_loss = torch.empty(n, dtype=F32, device=logits.device)
+        dlog = torch.empty_like(logits)
+        inv = inv_n.to(F32).reshape(1)
+        self._ck(self.lib.dmb_ce(logits.data_ptr(), targets.contiguous().data_ptr(), inv.data_ptr(),
+                                 row_loss.data_ptr(), dlog.data_ptr(), n, V, self._st()), "ce")
+        return row_loss.sum(), dlog
+
+    # ---- cell ops ------------------------------------------------------------------------------------------------
+    @staticmethod
+    def _cell_ok(q_r):
+        B, c, h, dh = q_r.shape
+        return q_r.dtype == BF16 and dh in (64, 128) and c in (16, 32, 64)
+
+    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0):
+        from ..engines.fused_math import prefix_lo
+        B, c, h, dh = q_r.shape
+        lo = prefix_lo(pos0, window)
+        if not self._cell_ok(q_r) or pos0 - lo <= 0 or not (_dense_tail(q_r, 2) and _dense_tail(Kc, 2)):
+            return super().prefix_fwd(q_r, Kc, Vc, pos0, scale, window)
+        o_c = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+        lse_c = torch.empty(B, c, h, dtype=F32, device=q_r.device)
+        self._ck(self.lib.dmb_prefix_fwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
+                                         o_c.data_ptr(), lse_c.data_ptr(), B, c, h, dh, lo, pos0,
+                                         scale, window, self._st()), "prefix_fwd")
+        return o_c, lse_c
+
+    def prefix_bwd(self, q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c, dq_acc, dKc, dVc):
+        from ..engines.fused_math import prefix_lo
+        B, c, h, dh = q_r.shape
+        lo = prefix_lo(pos0, window)
+        if pos0 - lo <= 0:
+            return
+        if not self._cell_ok(q_r) or not (_dense_tail(q_r, 2) and dq_acc.is_contiguous()):
+            return super().prefix_bwd(q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c,
+                                      dq_acc, dKc, dVc)
+        self._ck(self.lib.dmb_prefix_bwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
+                                         o_c.data_ptr(), lse_c.data_ptr(), do_c.data_ptr(),
+                                         dlse_c.data_ptr(), dq_acc.data_ptr(), dKc.data_ptr(),
+                                         dVc.data_ptr(), _tv(dKc), B, c, h, dh, lo, pos0, scale, window,
+                                         self._st()), "prefix_bwd")
+
+    def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
+        if not self._cell_ok(q_r) or not all(_dense_tail(t, 2) for t in (q_r, kself_r, v_raw, K_in, V_in)):
+            return super().tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window)
+        B, c, h, dh = q_r.shape
+        o = torch.empty(B, c, h, dh, dtype=BF16, device=q_r.device)
+        lse = torch.empty(B, c, h, dtype=F32, device=q_r.device)
+        o_c, lse_c = o_c.contiguous(), lse_c.contiguous()
+        self._ck(self.lib.dmb_tail_fwd(q_r.data_ptr(), _tv(q_r), kself_r.data_ptr(), _tv(kself_r),
+                                       v_raw.data_ptr(), _tv(v_raw), K_in.data_ptr(), _tv(K_in),
+                                       V_in.data_ptr(), _tv(V_in), o_c.data_ptr(), lse_c.data_ptr(),
+                                       o.data_ptr(), lse.data_ptr(), B, c, h, dh, scale, window,
+                                       self._st()), "tail_fwd")
+        return o, lse
+
+    def tail_bwd(self, dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window,
+                 dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
+        ok = (self._cell_ok(q_r) and dO.dtype == F32 and dO.is_contiguous() and o.is_contiguous()
+              and dq_acc.is_contiguous() and doc_acc.is_contiguous() and dlsec_acc.is_contiguous()
+              and all(_dense_tail(t, 2) for t in (q_r, kself_r, v_raw, K_in, V_in, dks_acc, dv_acc)))
+        if not ok:
+            return super().tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale,
+                                    window, dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc)
+        B, c, h, dh = q_r.shape
+        dK_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+        dV_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+        o_c, lse_c, lse = o_c.contiguous(), lse_c.contiguous(), lse.contiguous()
+        self._ck(self.lib.dmb_tail_bwd(
+            dO.data_ptr(), q_r.data_ptr(), _tv(q_r), kself_r.data_ptr(), _tv(kself_r), v_raw.data_ptr(),
+            _tv(v_raw), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), o_c.data_ptr(),
+            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), dks_acc.data_ptr(),
+            _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc), doc_acc.data_ptr(), dlsec_acc.data_ptr(),
+            dK_in.data_ptr(), dV_in.data_ptr(), B, c, h, dh, scale, window, self._st()), "tail_bwd")
+        return dK_in, dV_in
+
+    def refine_fwd(self, cg, glx, k, v, cos, sin, h, pin_cols=0):
+        B, c, d = k.shape
+        ok = (k.dtype == BF16 and cg.is_contiguous() and cos.is_contiguous()
+              and all(_dense_tail(t, 1) for t in (glx, k, v)))
+        if not ok:
+            return super().refine_fwd(cg, glx, k, v, cos, sin, h, pin_cols)
+        dh = d // h
+        K_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
+        V_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
+        self._ck(self.lib.dmb_refine_fwd(cg.data_ptr(), glx.data_ptr(), _tv(glx), k.data_ptr(), _tv(k),
+                                         v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
+                                         K_out.data_ptr(), V_out.data_ptr(), B, c, h, dh, pin_cols,
+                                         self._st()), "refine_fwd")
+        return K_out, V_out
+
+    def refine_bwd(self, dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc):
+        B, c, d = k.shape
+        ok = (k.dtype == BF16 and dK_out.dtype == F32 and dK_out.is_contiguous()
+              and dV_out.dtype == F32 and dV_out.is_contiguous() and cg.is_contiguous()
+              and cos.is_contiguous()
+              and all(_dense_tail(t, 1) for t in (glx, k, v, dk_acc, dv_acc, dglx_acc)))
+        if not ok:
+            return super().refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols, dk_acc,
+                                      dv_acc, dglx_acc)
+        h = dK_out.shape[2]
+        dcg = torch.empty(B, c, 4 * d, dtype=BF16, device=k.device)
+        self._ck(self.lib.dmb_refine_bwd(
+            dK_out.data_ptr(), dV_out.data_ptr(), cg.data_ptr(), glx.data_ptr(), _tv(glx), k.data_ptr(),
+            _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(), dcg.data_ptr(),
+            dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(), _tv(dv_acc), dglx_acc.data_ptr(),
+            _tv(dglx_acc), B, c, h, d // h, pin_cols, self._st()), "refine_bwd")
+        return dcg

@@ -38,8 +38,17 @@ class TorchOps:
     def rms_fwd(self, x, w, eps=1e-5):
         return fm.rms_fwd(x, w, eps)
 
-    def rms_bwd(self, dy, x, w, rstd):
-        return fm.rms_bwd(dy, x, w, rstd)
+    def rms_bwd(self, dy, x, w, rstd, dw_acc, residual=None, out_dtype=torch.float32):
+        """dw_acc (fp32 [d]) += weight grad; returns residual + dx in out_dtype."""
+        dx, dw = fm.rms_bwd(dy, x, w, rstd)
+        dw_acc.add_(dw)
+        if residual is not None:
+            dx = dx + residual.float()
+        return dx.to(out_dtype)
+
+    def col_sum_acc(self, out, dy):
+        """out (fp32 [n]) += column sums of dy [rows, n]."""
+        out.add_(dy.reshape(-1, dy.shape[-1]).float().sum(0))
 
     def rope(self, x, cos, sin):
         return fm.rope_tm(x, cos, sin)
@@ -64,14 +73,31 @@ class TorchOps:
     def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
         return fm.tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window)
 
-    def tail_bwd(self, dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window=0):
-        return fm.tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window)
+    def tail_bwd(self, dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window,
+                 dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
+        """Accumulates (+=) into the fp32 buffers dq_acc / dks_acc / dv_acc [B,c,h,dh],
+        doc_acc [B,c,h,dh], dlsec_acc [B,c,h]; returns fp32 (dK_in, dV_in)."""
+        dq, dks, dvr, dK_in, dV_in, doc, dlse = fm.tail_bwd(
+            dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window)
+        dq_acc += dq
+        dks_acc += dks
+        dv_acc += dvr
+        doc_acc += doc
+        dlsec_acc += dlse
+        return dK_in, dV_in
 
     def refine_fwd(self, cg, glx, k, v, cos, sin, h, pin_cols=0):
         return fm.refine_fwd(cg, glx, k, v, cos, sin, h, pin_cols)
 
-    def refine_bwd(self, dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols=0):
-        return fm.refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols)
+    def refine_bwd(self, dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc):
+        """Accumulates dk_acc / dv_acc [B,c,d] and dglx_acc [B,c,2d] (fp32, +=); returns dcg
+        [B,c,4d] in the activation dtype."""
+        dcg, dk, dv = fm.refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols)
+        d = k.shape[-1]
+        dk_acc += dk
+        dv_acc += dv
+        dglx_acc += dcg[..., 2 * d:]
+        return dcg.to(k.dtype)
 
     # ---- head ---------------------------------------------------------------------------
     def ce_chunk(self, logits, targets, inv_n):

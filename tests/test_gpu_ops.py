@@ -1,0 +1,176 @@
+"""Numerics of every sm_100a kernel against the plain-torch fp32 statement of the
+same op (engines/fused_math.py), on bf16 inputs of engine-like shapes."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from dual_mod_public_b200.engines import fused_math as fm
+from dual_mod_public_b200.models import build_rope_cache
+from dual_mod_public_b200.ops import TorchOps
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from dual_mod_public_b200.ops.cuda_ops import CudaOps
+    return CudaOps(torch.device("cuda:0"))
+
+
+DEV = "cuda:0"
+REF = TorchOps()
+
+
+def rnd(*shape, scale=1.0, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(DEV).to(dtype)
+
+
+def close(a, b, rtol=2e-2, atol=2e-2, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"{what}: max err {err:.4g} vs ref scale {ref:.4g}"
+
+
+def test_library_loaded(ops):
+    assert ops.name == "sm100a" and ops.lib is not None
+
+
+@pytest.mark.parametrize("rows,d", [(4096, 1024), (333, 2304), (64, 128)])
+def test_rms_fwd_bwd(ops, rows, d):
+    x, w, dy = rnd(rows, d), rnd(d, scale=0.3, seed=1) + 1, rnd(rows, d, seed=2)
+    n0 = ops.launches
+    y, rstd = ops.rms_fwd(x, w)
+    assert ops.launches > n0
+    y_ref, rstd_ref = fm.rms_fwd(x.float(), w.float())
+    close(y, y_ref, what="rms y")
+    close(rstd, rstd_ref, rtol=1e-3, atol=1e-4, what="rstd")
+    dw = torch.zeros(d, device=DEV)
+    res = rnd(rows, d, seed=3)
+    dx = ops.rms_bwd(dy, x, w, rstd, dw, residual=res, out_dtype=torch.bfloat16)
+    dx_ref, dw_ref = fm.rms_bwd(dy.float(), x.float(), w.float(), rstd_ref)
+    close(dx, dx_ref + res.float(), what="rms dx")
+    close(dw, dw_ref, rtol=2e-2, atol=0.05 * dw_ref.abs().mean().item() + 1e-3, what="rms dw")
+    dxf = ops.rms_bwd(dy.float(), x, w, rstd, torch.zeros(d, device=DEV))
+    close(dxf, dx_ref, rtol=1e-2, atol=1e-2, what="rms dx fp32")
+
+
+@pytest.mark.parametrize("dh", [64, 128])
+def test_rope_roundtrip(ops, dh):
+    B, T, H = 2, 96, 4
+    cos, sin = build_rope_cache(T, dh, 10000.0, device=DEV)
+    full = rnd(B, 128, H, dh)
+    x = full[:, 16:16 + T]                                    # batch-strided view
+    y = ops.rope(x, cos, sin)
+    close(y, fm.rope_tm(x.float(), cos, sin), what="rope")
+    xf = rnd(B, T, H, dh, dtype=torch.float32, seed=5)
+    close(ops.unrope(ops.rope(xf, cos, sin), cos, sin), xf, rtol=1e-5, atol=1e-5, what="unrope")
+
+
+def test_swiglu(ops):
+    h1, h3, dg = rnd(512, 2816), rnd(512, 2816, seed=1), rnd(512, 2816, seed=2)
+    close(ops.swiglu_fwd(h1, h3), fm.swiglu_fwd(h1.float(), h3.float()), what="swiglu")
+    d1, d3 = ops.swiglu_bwd(dg, h1, h3)
+    r1, r3 = fm.swiglu_bwd(dg.float(), h1.float(), h3.float())
+    close(d1, r1, what="dh1")
+    close(d3, r3, what="dh3")
+
+
+def test_ce_slab(ops):
+    n, V = 300, 32000
+    logits = rnd(n, V, scale=2.0)
+    tg = torch.randint(0, V, (n,), device=DEV)
+    tg[5] = -1
+    inv_n = 1.0 / (tg >= 0).sum().float()
+    loss, dl = ops.ce_chunk(logits, tg, inv_n)
+    loss_ref, dl_ref = fm.ce_chunk(logits.float(), tg, inv_n)
+    assert abs(loss.item() - loss_ref.item()) < 2e-3 * abs(loss_ref.item())
+    close(dl, dl_ref, rtol=2e-2, atol=1e-6, what="dlogits")
+
+
+def _cell_inputs(B, c, H, dh, T, seed=0):
+    q = rnd(B, T, H, dh, scale=1.0, seed=seed)
+    ks = rnd(B, T, H, dh, seed=seed + 1)
+    vr = rnd(B, T, H, dh, seed=seed + 2)
+    Kc = rnd(B, T, H, dh, seed=seed + 3)
+    Vc = rnd(B, T, H, dh, seed=seed + 4)
+    return q, ks, vr, Kc, Vc
+
+
+@pytest.mark.parametrize("c,dh,pos0,window", [(64, 64, 192, 0), (64, 128, 128, 0), (32, 64, 96, 0),
+                                              (16, 64, 48, 0), (64, 64, 192, 100), (64, 64, 0, 0)])
+def test_prefix_and_tail_fwd_bwd(ops, c, dh, pos0, window):
+    B, H, T = 3, 4, pos0 + c
+    scale = dh ** -0.5
+    q, ks, vr, Kc, Vc = _cell_inputs(B, c, H, dh, T)
+    r = slice(pos0, pos0 + c)
+    qc, ksc, vrc = q[:, r], ks[:, r], vr[:, r]
+    K_in, V_in = rnd(B, c, H, dh, seed=9), rnd(B, c, H, dh, seed=10)
+    f = lambda t: t.float()
+    # ---- forward
+    o_c, lse_c = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, window)
+    o_c_ref, lse_c_ref = fm.prefix_fwd(f(qc), f(Kc), f(Vc), pos0, scale, window)
+    close(o_c, o_c_ref, what="o_c")
+    live = lse_c_ref > -1e29
+    close(lse_c[live], lse_c_ref[live], rtol=1e-2, atol=2e-2, what="lse_c")
+    assert (lse_c[~live] < -1e29).all()
+    o, lse = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c_ref, lse_c_ref, scale, window)
+    o_ref, lse_ref = fm.tail_fwd(f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c_ref, lse_c_ref, scale, window)
+    close(o, o_ref, what="tail o")
+    close(lse, lse_ref, rtol=1e-2, atol=2e-2, what="tail lse")
+    # ---- tail backward
+    dO = rnd(B, c, H, dh, dtype=torch.float32, seed=11)
+    z = lambda *s: torch.zeros(*s, device=DEV)
+    acc = [z(B, c, H, dh), z(B, T, H, dh), z(B, T, H, dh), z(B, c, H, dh), z(B, c, H)]
+    dK_in, dV_in = ops.tail_bwd(dO, qc, ksc, vrc, K_in, V_in, o_c_ref, lse_c_ref, o_ref.to(torch.bfloat16),
+                                lse_ref, scale, window, acc[0], acc[1][:, r], acc[2][:, r], acc[3], acc[4])
+    ref = fm.tail_bwd(dO, f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c_ref, lse_c_ref, o_ref, lse_ref,
+                      scale, window)
+    names = ["dq", "dkself", "dvraw", "dK_in", "dV_in", "do_c", "dlse_c"]
+    got = [acc[0], acc[1][:, r], acc[2][:, r], dK_in, dV_in, acc[3], acc[4]]
+    for n_, g_, r_ in zip(names, got, ref):
+        close(g_, r_, rtol=3e-2, atol=3e-2, what=n_)
+    assert acc[1][:, :pos0].abs().max() == 0 if pos0 else True
+    # ---- prefix backward
+    do_c, dlse_c = ref[5], ref[6]
+    dq_acc, dKc, dVc = z(B, c, H, dh), z(B, T, H, dh), z(B, T, H, dh)
+    ops.prefix_bwd(qc, Kc, Vc, pos0, scale, window, o_c_ref, lse_c_ref, do_c, dlse_c, dq_acc, dKc, dVc)
+    dq_r, dK_r, dV_r = z(B, c, H, dh), z(B, T, H, dh), z(B, T, H, dh)
+    fm.prefix_bwd(f(qc), f(Kc), f(Vc), pos0, scale, window, o_c_ref, lse_c_ref, do_c, dlse_c, dq_r, dK_r, dV_r)
+    close(dq_acc, dq_r, rtol=3e-2, atol=3e-2, what="prefix dq")
+    close(dKc, dK_r, rtol=3e-2, atol=3e-2, what="prefix dK")
+    close(dVc, dV_r, rtol=3e-2, atol=3e-2, what="prefix dV")
+
+
+@pytest.mark.parametrize("pin", [0, 64])
+def test_refine_fwd_bwd(ops, pin):
+    B, c, H, dh, T = 2, 64, 16, 64, 128
+    d = H * dh
+    cos, sin = build_rope_cache(T, dh, 10000.0, device=DEV)
+    r = slice(64, 128)
+    cg = rnd(B, c, 4 * d)
+    glx, k, v = rnd(B, T, 2 * d, seed=1), rnd(B, T, d, seed=2), rnd(B, T, d, seed=3)
+    K_out, V_out = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], H, pin)
+    Kr, Vr = fm.refine_fwd(cg.float(), glx[:, r].float(), k[:, r].float(), v[:, r].float(), cos[r], sin[r], H, pin)
+    close(K_out, Kr, what="K''")
+    close(V_out, Vr, what="V''")
+    dK, dV = rnd(B, c, H, dh, dtype=torch.float32, seed=4), rnd(B, c, H, dh, dtype=torch.float32, seed=5)
+    z = lambda *s: torch.zeros(*s, device=DEV)
+    dk_acc, dv_acc, dg_acc = z(B, T, d), z(B, T, d), z(B, T, 2 * d)
+    dcg = ops.refine_bwd(dK, dV, cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], pin,
+                         dk_acc[:, r], dv_acc[:, r], dg_acc[:, r])
+    dcg_r, dk_r, dv_r = fm.refine_bwd(dK, dV, cg.float(), glx[:, r].float(), k[:, r].float(), v[:, r].float(),
+                                      cos[r], sin[r], pin)
+    close(dcg, dcg_r, what="dcg")
+    close(dk_acc[:, r], dk_r, what="dk")
+    close(dv_acc[:, r], dv_r, what="dv")
+    close(dg_acc[:, r], dcg_r[..., 2 * d:], what="dglx")
+    assert dk_acc[:, :64].abs().max() == 0
+
+
+def test_col_sum(ops):
+    x = rnd(1000, 2048, dtype=torch.float32)
+    out = torch.ones(2048, device=DEV)
+    ops.col_sum_acc(out, x)
+    close(out, 1 + x.sum(0), rtol=1e-4, atol=1e-3, what="colsum")
