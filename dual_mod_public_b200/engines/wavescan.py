@@ -126,6 +126,7 @@ class WaveScanEngine:
         # that layer's bucket while the reverse scan continues
         self.on_layer_grads_final = on_layer_grads_final
         self.dx_top = z(B, T, d)                               # d loss / d xl[L]
+        self.dx_cur = z(B, T, d)                               # gradient flowing down the layers
         if keep_logits:
             self.logits = z(B, T, cfg.vocab_size)
             self.d_logits = z(B, T, cfg.vocab_size)
@@ -153,6 +154,7 @@ class WaveScanEngine:
         self.stats = {"fwd_cells": 0, "bwd_cells": 0}
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self._graphs = {}
+        self._graph_launches = {}
 
     # =============================================================================
     # public API
@@ -186,7 +188,9 @@ class WaveScanEngine:
         if self.backend == "fused":
             if not self._packed:
                 self.pack()
-            self._run("fwd", sid, lambda: self._fused_forward(sid))
+            self._run("emb", 0, self._fused_embed)
+            for li in range(self.L):
+                self._run(("fwd", li), sid, lambda li=li: self._fused_layer_fwd(li, sid))
             if targets is not None or self.keep_logits:
                 self._run(("head", bool(train), targets is not None), 0,
                           lambda: self._fused_head(train, targets is not None))
@@ -208,7 +212,15 @@ class WaveScanEngine:
                 self._fused_head_bwd_from_dlogits()
             elif not self._have_dx_top:
                 self._fused_head(True, True)
-            self._run("bwd", self._sid, lambda: self._fused_backward(self._sid))
+            sid = self._sid
+            self.dx_cur.copy_(self.dx_top)
+            if self.on_layer_grads_final is not None:
+                self.on_layer_grads_final(-1)
+            for li in range(self.L - 1, -1, -1):
+                self._run(("bwd", li), sid, lambda li=li: self._fused_layer_bwd(li, sid))
+                if self.on_layer_grads_final is not None:
+                    self.on_layer_grads_final(li)
+            self._run("embb", 0, self._fused_embed_bwd)
         else:
             self._generic_backward(self._sid, d_logits is not None)
         self._have_dx_top = False
@@ -267,13 +279,20 @@ class WaveScanEngine:
         # first use: run eagerly (this IS the step's result), then record the same
         # body for later replays; recording executes nothing, so accumulating bodies
         # (the backward) are not applied twice
+        n0 = self.ops.launches
         body()
+        self._graph_launches[gkey] = self.ops.launches - n0
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, pool=self._graphs.get("pool")):
             body()
         self._graphs.setdefault("pool", g.pool())
         self._graphs[gkey] = g
+
+    def graph_kernel_count(self):
+        """Hand-written kernel launches recorded in the captured graphs of one
+        forward + backward (replays do not pass through the op table's counter)."""
+        return sum(self._graph_launches.values())
 
     def capture(self, sids=None):
         """Capture forward / head / backward graphs for the given schedule ids using
@@ -290,16 +309,22 @@ class WaveScanEngine:
     def _rows(self):
         return self.B * self.T
 
-    def _fused_forward(self, sid):
+    def _fused_embed(self):
+        self.xl[0].copy_(F.embedding(self.idx, self.emb_c))
+
+    def _fused_embed_bwd(self):
+        self.grads.get(self.model.tok_emb.weight).index_add_(
+            0, self.idx.view(-1), self.dx_cur.reshape(-1, self.cfg.d_model).float())
+
+    def _fused_layer_fwd(self, li, sid):
         ops, cfg = self.ops, self.cfg
         B, T, h, dh, d = self.B, self.T, cfg.n_heads, cfg.head_dim, cfg.d_model
         scale = 1.0 / dh ** 0.5
         cos, sin = self.model.rope_cos[:T], self.model.rope_sin[:T]
         pin = cfg.kmod_vraw_heads * dh
-        x = F.embedding(self.idx, self.emb_c)
-        for li in range(self.L):
+        if True:
             P = self.packs[li]
-            self.xl[li].copy_(x)
+            x = self.xl[li]
             xhat, _ = ops.rms_fwd(x, P.w_an)
             q_r = ops.rope(ops.linear(xhat, P.wq).view(B, T, h, dh), cos, sin)
             k = ops.linear(xhat, P.wk)
@@ -327,8 +352,7 @@ class WaveScanEngine:
             x_mid = x + ops.linear(o_all, P.wo)
             xn, _ = ops.rms_fwd(x_mid, P.w_mn)
             g = ops.swiglu_fwd(ops.linear(xn, P.w1), ops.linear(xn, P.w3))
-            x = x_mid + ops.linear(g, P.w2)
-        self.xl[self.L].copy_(x)
+            self.xl[li + 1].copy_(x_mid + ops.linear(g, P.w2))
 
     def _head_weight(self):
         return self.emb_c if self.head_w is None else self.head_w
@@ -378,7 +402,7 @@ class WaveScanEngine:
             dxt[r] = ops.rms_bwd(ops.linear_dx(dl[r], W), x[r], self.w_f, rstd,
                                  self.grads.get(self.model.norm_f.weight), out_dtype=self.act)
 
-    def _fused_backward(self, sid):
+    def _fused_layer_bwd(self, li, sid):
         ops, cfg, G = self.ops, self.cfg, self.grads
         B, T, h, dh, d = self.B, self.T, cfg.n_heads, cfg.head_dim, cfg.d_model
         act, f32 = self.act, torch.float32
@@ -386,8 +410,8 @@ class WaveScanEngine:
         cos, sin = self.model.rope_cos[:T], self.model.rope_sin[:T]
         pin = cfg.kmod_vraw_heads * dh
         dev = self.device
-        dx = self.dx_top.clone()                                   # d loss / d x_{l+1}
-        for li in range(self.L - 1, -1, -1):
+        dx = self.dx_cur                                           # d loss / d x_{l+1}
+        if True:
             P, blk = self.packs[li], self.model.blocks[li]
             a = blk.attn
             x = self.xl[li]
@@ -480,13 +504,9 @@ class WaveScanEngine:
             ops.col_sum_acc(db_g, dglx)
             dxhat = (ops.linear_dx(dq, P.wq).float() + ops.linear_dx(dk_t, P.wk).float()
                      + ops.linear_dx(dv_t, P.wv).float() + ops.linear_dx(dglx_a, P.W_gx).float())
-            dx = ops.rms_bwd(dxhat, x, P.w_an, rstd_a, G.get(blk.attn_norm.weight),
-                             residual=dx_mid, out_dtype=act)
+            self.dx_cur.copy_(ops.rms_bwd(dxhat, x, P.w_an, rstd_a, G.get(blk.attn_norm.weight),
+                                          residual=dx_mid, out_dtype=act))
             self._scatter_packed_grads(a, db_g)
-            if self.on_layer_grads_final is not None:
-                self.on_layer_grads_final(li)
-        G.get(self.model.tok_emb.weight).index_add_(
-            0, self.idx.view(-1), dx.reshape(-1, d).float())
 
     def _scatter_packed_grads(self, a, db_g):
         """Route the packed-weight gradients of one layer to the parameters."""

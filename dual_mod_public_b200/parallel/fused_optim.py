@@ -104,7 +104,12 @@ class PeerBuffer:
                     self.ptrs[r] = p.value
                     self._opened.append(p.value)
         self._holder = _RawCuda(self.own, nbytes)
-        self.bytes_tensor = torch.as_tensor(self._holder, device=device)
+        try:
+            self.bytes_tensor = torch.as_tensor(self._holder, device=device)
+        except Exception:
+            storage = torch._C._construct_storage_from_data_pointer(self.own, torch.device(device), nbytes)
+            self.bytes_tensor = torch.empty(0, dtype=torch.uint8, device=device).set_(storage)
+        assert self.bytes_tensor.data_ptr() == self.own and self.bytes_tensor.numel() == nbytes
 
     def view(self, dtype, numel=None):
         t = self.bytes_tensor.view(dtype)
@@ -220,7 +225,7 @@ class FusedDPAdamW:
             self._bind()
             mk = lambda nbytes: PeerBuffer(self.lib, nbytes, self.device, self.group, self.rank, self.world)
             self._pb_grads, self._pb_params = mk(4 * n), mk(4 * n)
-            self._pb_flags, self._pb_norms = mk(4 * nslots * self.world), mk(4 * 2 * self.world)
+            self._pb_flags, self._pb_norms = mk(4 * nslots * MAX_WORLD), mk(4 * 2 * MAX_WORLD)
             self.flat_grads = self._pb_grads.view(torch.float32, n)
             self.flat_params = self._pb_params.view(torch.float32, n)
         else:

@@ -1,0 +1,3 @@
+from .trainer import Trainer
+
+__all__ = ["Trainer"]

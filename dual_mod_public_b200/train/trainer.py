@@ -1,0 +1,106 @@
+"""Training step driver: model + engine + data-parallel optimizer behind one call.
+
+`Trainer.step(tokens)` is the call a user makes per optimizer step: it takes the
+rank's token block from (pinned) host memory, copies each micro-batch to the
+device, runs the engine's forward + reverse-scan backward at the schedule id of
+the step, lets finished layer buckets start their reduce-scatter, then runs the
+fused reduce + clip + AdamW + all-gather kernel, refreshes the bf16 weight packs
+and returns the loss read back to the host.
+
+Reference parity: the step bodies of lm/train_340m/train_flagship.py:864-1045
+(engine.train_step -> finish_grads -> clip -> skip -> opt.step) and
+lm/train_1p3b/train_hero_wave3d.py:848-997, without their logging and governors,
+which live in `governors.py` and wrap this class.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..engines.wavescan import WaveScanEngine
+from ..models import DualModLM
+from ..parallel.fused_optim import FusedDPAdamW, NcclAdamW, decay_groups, default_buckets
+
+
+class Trainer:
+    def __init__(self, cfg, schedules, *, seq_len, micro_batch, local_batch, lr=3e-4,
+                 betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, decay_all=False, max_norm=1.0,
+                 skip_norm=0.0, optimizer="fused", device=None, autocast_bf16=True, use_graphs=True,
+                 overlap_buckets=True, process_group=None, seed=1337, engine="wavescan",
+                 engine_kwargs=None, model=None):
+        assert local_batch % micro_batch == 0, "local batch must be a whole number of micro-batches"
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.cfg, self.T = cfg, seq_len
+        self.micro_batch, self.accum = micro_batch, local_batch // micro_batch
+        self.world = dist.get_world_size(process_group) if dist.is_available() and dist.is_initialized() else 1
+        if model is None:
+            torch.manual_seed(seed)
+            model = DualModLM(cfg)
+        self.model = model.to(self.device)
+        groups = decay_groups(self.model, weight_decay, decay_all=decay_all)
+        common = dict(lr=lr, betas=betas, eps=eps, max_norm=max_norm, skip_norm=skip_norm,
+                      grad_accum=self.accum, process_group=process_group)
+        if optimizer == "fused":
+            self.opt = FusedDPAdamW(groups, default_buckets(self.model), device=self.device, **common)
+        else:
+            self.opt = NcclAdamW(groups, **common)
+        self.overlap = overlap_buckets and optimizer == "fused" and self.opt.use_kernel and self.world > 1
+        self._side = torch.cuda.Stream(device=self.device) if self.overlap else None
+        self._last_micro = False
+        kw = dict(engine_kwargs or {})
+        if engine == "wavescan":
+            self.engine = WaveScanEngine(self.model, schedules, micro_batch, seq_len, device=self.device,
+                                         autocast_bf16=autocast_bf16, use_graphs=use_graphs,
+                                         grads=self.opt.grad_buffers(),
+                                         on_layer_grads_final=self._layer_done if self.overlap else None, **kw)
+        else:
+            from ..engines.wave3d import Wave3DEngine
+            self.engine = Wave3DEngine(self.model, schedules, micro_batch, seq_len, device=self.device,
+                                       autocast_bf16=autocast_bf16, grads=self.opt.grad_buffers(), **kw)
+        self.engine.pack()
+        self.steps_done = 0
+        self._loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
+        self._loss_host = torch.zeros((), dtype=torch.float32).pin_memory() if self.device.type == "cuda" \
+            else torch.zeros((), dtype=torch.float32)
+
+    # bucket b of `default_buckets` : 0 = head/final norm, 1 + (L-1-li) = layer li, last = embedding
+    def _layer_done(self, li):
+        if not self._last_micro:
+            return
+        b = 0 if li < 0 else 1 + (self.cfg.n_layers - 1 - li)
+        cur = torch.cuda.current_stream(self.device)
+        self._side.wait_stream(cur)
+        self.opt.bucket_ready(b, stream=self._side)
+
+    def step(self, tokens, sid=0, lr=None, read_loss=True):
+        """tokens: [local_batch, T+1] int64 (host, ideally pinned) — inputs are
+        tokens[:, :-1], targets tokens[:, 1:].  Returns the mean loss over the rank's
+        micro-batches as a Python float (or the device tensor when read_loss=False)."""
+        mb, T = self.micro_batch, self.T
+        self.opt.zero_grad()
+        self._loss_acc.zero_()
+        nb = self.device.type == "cuda"
+        for a in range(self.accum):
+            blk = tokens[a * mb:(a + 1) * mb].to(self.device, non_blocking=nb)   # one contiguous H2D copy
+            idx, tgt = blk[:, :T], blk[:, 1:T + 1]
+            self._last_micro = a == self.accum - 1
+            self._loss_acc += self.engine.train_step(idx, tgt, sid=sid)
+        if self._side is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._side)
+        self.opt.step(lr=lr)
+        self.engine.pack()
+        self.steps_done += 1
+        if not read_loss:
+            return self._loss_acc / self.accum
+        self._loss_host.copy_(self._loss_acc / self.accum, non_blocking=nb)
+        if nb:
+            torch.cuda.current_stream(self.device).synchronize()
+        return float(self._loss_host)
+
+    def h2d_bytes_per_step(self):
+        return self.micro_batch * self.accum * (self.T + 1) * 8
+
+    def d2h_bytes_per_step(self):
+        return 4
