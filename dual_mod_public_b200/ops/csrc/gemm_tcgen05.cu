@@ -1,0 +1,332 @@
+// bf16 GEMM on the 5th-generation tensor cores: TMA-fed shared-memory pipeline, tcgen05.mma issued
+// by one elected thread, fp32 accumulator in tensor memory, epilogue read back with tcgen05.ld.
+//
+//   C[M,N] (+)= op(A) . op(B)        fp32 accumulate, C stored as bf16 or fp32
+//
+// Operand layouts (both bf16, innermost dimension contiguous):
+//   A_MN = 0 : A stored [M][K]  (K-major)        A_MN = 1 : A stored [K][M]  (M-major)
+//   B_MN = 0 : B stored [N][K]  (K-major)        B_MN = 1 : B stored [K][N]  (N-major)
+// which covers y = x W^T (0,0), dx = dy W (0,1) and dW += dy^T x (1,1) without any transpose pass.
+//
+// One CTA computes a 128 x 256 tile: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner),
+// warps 2..5 = epilogue (each reads its own 32-lane quarter of TMEM).  4-stage ring of 128B-swizzled
+// tiles (48 KB per stage); no cluster multicast anywhere.  Every mbarrier wait is bounded: on expiry
+// the kernel raises a flag in global memory, stops waiting and runs to its end so TMEM is released.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 256;
+constexpr int NTHREADS = 192;
+constexpr unsigned long long WAIT_NS = 2000000000ull;  // every pipeline wait gives up after 2 s
+
+struct SmemLayout {
+  // tiles first (1024-byte aligned base), barriers after
+  static constexpr int bar_off = STAGES * STAGE_BYTES;
+  static constexpr int total = bar_off + 256;
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// wait bounded in time (WAIT_NS); returns false when it ran out or another role already gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* err) {
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (*err) return false;
+    if ((it & 63) == 63 && global_ns() - t0 > WAIT_NS) break;
+  }
+  *err = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// 64-bit shared-memory matrix descriptor, 128-byte swizzle
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+
+template <int A_MN, int B_MN>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+  return (1u << 4)                      // D = fp32
+         | (1u << 7) | (1u << 10)       // A, B = bf16
+         | ((uint32_t)A_MN << 15) | ((uint32_t)B_MN << 16)
+         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
+    const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout,
+    const bf16* __restrict__ bias, int M, int N, int K, long long ldc, int accumulate, int* __restrict__ gerr) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar0 = base + SmemLayout::bar_off;
+  // barriers: full[s] at bar0 + 8 s, empty[s] at bar0 + 8 (STAGES + s), tmem_full after them
+  auto full = [&](int s) { return bar0 + 8u * s; };
+  auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  const uint32_t tmem_full = bar0 + 8u * (2 * STAGES);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + SmemLayout::bar_off + 8 * (2 * STAGES + 1));
+  volatile int* serr = reinterpret_cast<volatile int*>(base_ptr + SmemLayout::bar_off + 8 * (2 * STAGES + 2));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int KB = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *serr = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), 1);
+    }
+    mbar_init(tmem_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < KB; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(empty(s), ((kb / STAGES) - 1) & 1, serr)) break;
+        const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+        mbar_expect_tx(full(s), STAGE_BYTES);
+        const int k0 = kb * BK;
+        if (A_MN == 0) {
+          tma_load_2d(sa, &tmA, full(s), k0, m0);                       // box {64 k, 128 m}
+        } else {
+#pragma unroll
+          for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmA, full(s), m0 + 64 * j, k0);  // box {64 m, 64 k}
+        }
+        if (B_MN == 0) {
+          tma_load_2d(sb, &tmB, full(s), k0, n0);                       // box {64 k, 256 n}
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmB, full(s), n0 + 64 * j, k0);  // box {64 n, 64 k}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<A_MN, B_MN>();
+      bool alive = true;
+      for (int kb = 0; kb < KB && alive; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(full(s), (kb / STAGES) & 1, serr)) { alive = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // K-major: 32 bytes further along the swizzled 128-byte row; MN-major: 16 k-rows of 128 bytes
+          const uint64_t da = A_MN == 0 ? make_desc(sa + k * 32, 16, 1024) : make_desc(sa + k * 2048, BK * 128, 1024);
+          const uint64_t db = B_MN == 0 ? make_desc(sb + k * 32, 16, 1024) : make_desc(sb + k * 2048, BK * 128, 1024);
+          umma_bf16(tmem_base, da, db, idesc, (kb | k) != 0);
+        }
+        umma_commit(empty(s));           // stage reusable once these MMAs have read it
+      }
+      umma_commit(tmem_full);            // accumulator complete
+    }
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const int q = warp & 3;              // TMEM lane quarter this warp may touch
+    const bool ok = mbar_wait(tmem_full, 0, serr);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int row = m0 + q * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col = n0 + c0;
+        if (row < M && col < N) {
+          if (OUT_F32) {
+            float* dst = reinterpret_cast<float*>(Cout) + (long long)row * ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < N) {      // N % 8 == 0 keeps groups of 4 whole
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (bias) {
+                  v.x += __bfloat162float(bias[col + j]); v.y += __bfloat162float(bias[col + j + 1]);
+                  v.z += __bfloat162float(bias[col + j + 2]); v.w += __bfloat162float(bias[col + j + 3]);
+                }
+                if (accumulate) {
+                  float4 o = *reinterpret_cast<float4*>(dst + j);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = v;
+              }
+            }
+          } else {
+            bf16* dst = reinterpret_cast<bf16*>(Cout) + (long long)row * ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  f[e] = __uint_as_float(r[j + e]);
+                  if (bias) f[e] += __bfloat162float(bias[col + j + e]);
+                }
+                uint4 o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                *reinterpret_cast<uint4*>(dst + j) = o;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+
+int get_encode() {
+  if (g_encode) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return -10;
+  g_encode = (EncodeFn)fn;
+  return 0;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of stride ld elements
+int make_map(CUtensorMap* m, const void* ptr, long long inner, long long outer, long long ld, int box_inner,
+             int box_outer) {
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* bias, int M, int N, int K,
+           long long ldc, int accumulate, int* gerr, cudaStream_t st) {
+  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  const int smem = SmemLayout::total + 1024;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  kern<<<grid, NTHREADS, smem, st>>>(ta, tb, C, (const bf16*)bias, M, N, K, ldc, accumulate, gerr);
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// C[M,N] (+)= op(A) op(B).  lda / ldb: row stride (elements) of A and B as stored.
+//   a_mn = 0: A stored [M][K];  a_mn = 1: A stored [K][M]      (same for B with N)
+// Requirements: pointers 16-byte aligned, lda/ldb/ldc multiples of 8 (bf16) resp. 4 (fp32 C),
+// N % 8 == 0.  out_f32: C is fp32 (else bf16).  accumulate needs out_f32.  `gerr` (device int) is
+// set to 1 if a pipeline wait ran out.
+int dmb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                  long long ldb, long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, int* gerr,
+                  cudaStream_t st) {
+  if (get_encode()) return -10;
+  if (N % 8 || (accumulate && !out_f32)) return -1;
+  CUtensorMap ta, tb;
+  int rc;
+  rc = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  rc = b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, BN);
+  if (rc) return rc;
+#define GO(a, b, o) return launch<a, b, o>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, st)
+  if (!a_mn && !b_mn) { if (out_f32) GO(0, 0, 1); else GO(0, 0, 0); }
+  if (!a_mn && b_mn) { if (out_f32) GO(0, 1, 1); else GO(0, 1, 0); }
+  if (a_mn && b_mn) { if (out_f32) GO(1, 1, 1); else GO(1, 1, 0); }
+  if (a_mn && !b_mn) { if (out_f32) GO(1, 0, 1); else GO(1, 0, 0); }
+#undef GO
+  return -1;
+}
+
+}  // extern "C"

@@ -92,11 +92,9 @@ class CudaOps(TorchOps):
         self.launches = 0
         self._scratch = {}
         self.gemm = None                       # set by enable_gemm()
-        try:
+        if os.environ.get("DMB_GEMM", "tcgen05") == "tcgen05":
             from .gemm import Tcgen05Gemm
             self.gemm = Tcgen05Gemm(self.lib, self.device)
-        except Exception:                      # the GEMM needs the driver's tensor-map entry point
-            self.gemm = None
 
     # ---- helpers ---------------------------------------------------------------------------
     def _st(self):
@@ -116,8 +114,8 @@ class CudaOps(TorchOps):
 
     # ---- GEMMs -------------------------------------------------------------------------------
     def linear(self, x, w, bias=None, out_dtype=None):
-        if self.gemm is not None and bias is None and self.gemm.ok_tn(x, w):
-            y = self.gemm.linear(x, w, out_dtype or x.dtype)
+        if self.gemm is not None and self.gemm.ok_tn(x, w) and (bias is None or bias.dtype == BF16):
+            y = self.gemm.linear(x, w, out_dtype or x.dtype, bias=bias)
             self.launches += 1
             return y
         return super().linear(x, w, bias, out_dtype)
