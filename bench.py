@@ -160,7 +160,8 @@ def run_ours(args):
                "vs_baseline": round(value / (PUBLISHED_TOK_S_PER_GPU * world), 3),
                "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
                "impl": "ours",
-               "config": {"model": "dm_340m (24L d1024 16x64 ffn2816 vocab32000 tied)",
+               "config": {"model": f"dm_340m ({MODEL['n_layers']}L d1024 16x64 ffn2816 vocab32000 tied)"
+                          + ("" if MODEL["n_layers"] == 24 and GLOBAL_SEQS == 256 else " PROFILING SHAPE, NOT A BENCH VALUE"),
                           "engine": "wavescan c=64 K=4", "global_batch": GLOBAL_SEQS, "seq_len": SEQ,
                           "micro_batch": micro, "parallelism": f"dp{world}", "optimizer": args.optimizer,
                           "cuda_graphs": tr.engine.use_graphs,
@@ -274,8 +275,20 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("DMB_MICRO_BATCH", 32)))
     ap.add_argument("--optimizer", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--profile-layers", type=int, default=0,
+                    help="PROFILING ONLY: shrink the model to this many layers (the printed line is then "
+                         "not a benchmark value and says so)")
+    ap.add_argument("--profile-seqs", type=int, default=0,
+                    help="PROFILING ONLY: global batch in sequences")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
+    global GLOBAL_SEQS
+    profiling = bool(args.profile_layers or args.profile_seqs)
+    if args.profile_layers:
+        MODEL["n_layers"] = args.profile_layers
+    if args.profile_seqs:
+        GLOBAL_SEQS = args.profile_seqs
+    if not profiling:
+        args.warmup = max(args.warmup, 3)
     (run_reference if args.impl == "reference" else run_ours)(args)
 
 

@@ -259,6 +259,7 @@ class CudaOps(TorchOps):
         if not self._cell_ok(q_r) or not (_dense_tail(q_r, 2) and dq_acc.is_contiguous()):
             return super().prefix_bwd(q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c,
                                       dq_acc, dKc, dVc)
+        o_c, lse_c, do_c, dlse_c = (t.contiguous() for t in (o_c, lse_c, do_c, dlse_c))
         self._ck(self.lib.dmb_prefix_bwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          o_c.data_ptr(), lse_c.data_ptr(), do_c.data_ptr(),
                                          dlse_c.data_ptr(), dq_acc.data_ptr(), dKc.data_ptr(),

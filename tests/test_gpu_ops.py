@@ -113,7 +113,8 @@ def test_prefix_and_tail_fwd_bwd(ops, c, dh, pos0, window):
     o_c_ref, lse_c_ref = fm.prefix_fwd(f(qc), f(Kc), f(Vc), pos0, scale, window)
     close(o_c, o_c_ref, what="o_c")
     live = lse_c_ref > -1e29
-    close(lse_c[live], lse_c_ref[live], rtol=1e-2, atol=2e-2, what="lse_c")
+    if live.any():
+        close(lse_c[live], lse_c_ref[live], rtol=1e-2, atol=2e-2, what="lse_c")
     assert (lse_c[~live] < -1e29).all()
     o, lse = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c_ref, lse_c_ref, scale, window)
     o_ref, lse_ref = fm.tail_fwd(f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c_ref, lse_c_ref, scale, window)
