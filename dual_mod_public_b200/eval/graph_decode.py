@@ -1,0 +1,175 @@
+"""Incremental decode over a static recurrent KV tape, one CUDA graph per token.
+
+The tape is [B, P, h, dh] per layer (token-major), the position lives on the device,
+and one captured graph is one full decode step of all layers, so the host issues a
+single graph launch per token.  Per layer the step is exactly `DualModAttention.decode_step`:
+project, rotate at `pos`, read the live tape rows plus the position's own RAW key/value,
+refine (key, value) from the read, rotate the blended key and write row `pos`.
+
+Unlike a masked softmax over all P slots, the read touches only the `pos` live rows
+(sm_100a kernel `dmb_decode_attend`, with the position read from device memory; the
+plain-torch path masks instead and is what runs on CPU).  With the modulation off
+(`attn_mode="vanilla"`) the same class is a plain KV-cache Transformer decoder: the
+Transformer++ control.
+
+Reference parity: `GraphDecoder` (lm/eval/graph_decode.py:15-125): static buffers,
+device-side `pos`, `capture / reset / step / generate(prompt, max_new, eos_id, stop_fn)`.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..models.rope import apply_rope
+
+
+class GraphDecoder:
+    def __init__(self, model, B, P_max, dtype=torch.bfloat16, use_kernel=None):
+        self.m = model
+        self.dev = next(model.parameters()).device
+        assert P_max <= model.cfg.max_seq_len, (P_max, model.cfg.max_seq_len)
+        a0 = model.blocks[0].attn
+        L, h, dh = len(model.blocks), a0.n_heads, a0.head_dim
+        self.B, self.P, self.dt, self.h, self.dh = B, P_max, dtype, h, dh
+        z = lambda: torch.zeros(B, P_max, h, dh, device=self.dev, dtype=dtype)
+        self.K, self.V = [z() for _ in range(L)], [z() for _ in range(L)]
+        self.tok = torch.zeros(B, 1, dtype=torch.long, device=self.dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)
+        self.pos32 = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.ar = torch.arange(P_max, device=self.dev)
+        self.logits = torch.zeros(B, 1, model.cfg.vocab_size, device=self.dev)
+        self.next = torch.zeros(B, 1, dtype=torch.long, device=self.dev)
+        self.graph = None
+        self.window = model.cfg.local_window or 0
+        ok = (self.dev.type == "cuda" and dtype == torch.bfloat16 and dh in (64, 128)
+              and a0.n_kv_heads == a0.n_heads and not model.cfg.attn_logn_ref)
+        self.use_kernel = ok if use_kernel is None else (use_kernel and ok)
+        self.kernel_launches = 0
+        if self.use_kernel:
+            from ..ops.cuda_ops import load_library
+            self.lib = load_library()
+            p, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+            self.lib.dmb_decode_attend.restype = i
+            self.lib.dmb_decode_attend.argtypes = [p, p, p, p, p, p, p, i, i, i, i, f, i, p]
+
+    # ---- the read ---------------------------------------------------------------------------
+    def _read(self, attn, q_r, k_r, v, l):
+        """q_r, k_r, v: [B, h, dh] (rotated query, rotated RAW self key, RAW self value)."""
+        Kb, Vb = self.K[l], self.V[l]
+        if self.use_kernel:
+            out = torch.empty_like(q_r)
+            st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+            rc = self.lib.dmb_decode_attend(q_r.data_ptr(), k_r.data_ptr(), v.data_ptr(), Kb.data_ptr(), Vb.data_ptr(),
+                                            self.pos32.data_ptr(), out.data_ptr(), self.B, self.P, self.h, self.dh,
+                                            attn.scale, self.window, st)
+            if rc != 0:
+                raise RuntimeError(f"decode read failed ({rc})")
+            self.kernel_launches += 1
+            return out
+        # plain torch: scores over every slot, live ones kept by a mask; self as an extra column
+        s = torch.einsum("bhd,bphd->bhp", q_r.float(), Kb.float()) * attn.scale
+        live = self.ar < self.pos
+        if self.window:
+            live = live & (self.ar > self.pos - self.window)
+        s = s.masked_fill(~live, float("-inf"))
+        s_self = (q_r.float() * k_r.float()).sum(-1, keepdim=True) * attn.scale
+        p = torch.softmax(torch.cat((s, s_self), dim=-1), dim=-1)
+        o = torch.einsum("bhp,bphd->bhd", p[..., :-1], Vb.float()) + p[..., -1:] * v.float()
+        return o.to(v.dtype)
+
+    def _attn(self, attn, xhat, l, cos_p, sin_p):
+        B, h, dh = self.B, self.h, self.dh
+        q, k, v = attn.wq(xhat), attn.wk(xhat), attn.project_v(xhat)            # [B,1,d]
+        rot = lambda t: apply_rope(t.view(B, 1, h, dh).transpose(1, 2), cos_p, sin_p).transpose(1, 2).reshape(B, h, dh)
+        q_r, k_r = rot(q).to(self.dt), rot(k).to(self.dt)
+        o = self._read(attn, q_r.contiguous(), k_r.contiguous(), v.view(B, h, dh).to(self.dt).contiguous(), l)
+        o_cat = o.reshape(B, 1, h * dh).to(xhat.dtype)
+        kpp, vpp = attn.refine_kv(xhat, o_cat, k, v)
+        self.K[l].index_copy_(1, self.pos, rot(kpp).to(self.dt).unsqueeze(1))
+        self.V[l].index_copy_(1, self.pos, vpp.view(B, 1, h, dh).to(self.dt))
+        return attn.wo(o_cat)
+
+    def _step(self):
+        m = self.m
+        cos_p, sin_p = m.rope_cos.index_select(0, self.pos), m.rope_sin.index_select(0, self.pos)
+        x = m.tok_emb(self.tok)
+        for l, blk in enumerate(m.blocks):
+            x = x + self._attn(blk.attn, blk.attn_norm(x), l, cos_p, sin_p)
+            x = x + blk.mlp(blk.mlp_norm(x))
+        lg = m.lm_head(m.norm_f(x))
+        self.logits.copy_(lg.float())
+        self.next.copy_(lg.argmax(-1))
+        self.pos += 1
+        self.pos32 += 1
+
+    def _run_step(self):
+        amp = self.dev.type == "cuda" and self.dt == torch.bfloat16
+        with torch.no_grad(), torch.autocast(self.dev.type, dtype=torch.bfloat16, enabled=amp, cache_enabled=False):
+            self._step()
+
+    def capture(self):
+        if self.dev.type != "cuda":
+            return self
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self._run_step()
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        self.reset()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._run_step()
+        self.reset()
+        self.graph = g
+        return self
+
+    def reset(self):
+        self.pos.zero_()
+        self.pos32.zero_()
+        for Kb, Vb in zip(self.K, self.V):
+            Kb.zero_()
+            Vb.zero_()
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._run_step()
+
+    @torch.no_grad()
+    def prefill(self, prompt):
+        """Token-by-token prefill (the tape is recurrent: row t depends on the read at t)."""
+        for p in range(prompt.shape[1]):
+            self.tok.copy_(prompt[:, p:p + 1])
+            self.step()
+
+    @torch.no_grad()
+    def generate(self, prompt, max_new, eos_id=None, stop_fn=None, check_every=16):
+        """Greedy continuation.  prompt [B, L] on the device, all rows the same length.
+        Returns (gen [B, k] on CPU, k = steps run).  `stop_fn(gen_cpu) -> bool [B]` marks
+        finished rows; generation ends when every row is finished."""
+        B, L = prompt.shape
+        assert B == self.B and L + max_new <= self.P, (B, L, max_new, self.P)
+        self.reset()
+        self.prefill(prompt)
+        gen = torch.zeros(B, max_new, dtype=torch.long, device=self.dev)
+        done = torch.zeros(B, dtype=torch.bool)
+        k = 0
+        while k < max_new:
+            gen[:, k].copy_(self.next[:, 0])
+            k += 1
+            if k % check_every == 0 or k == max_new:
+                g_cpu = gen[:, :k].cpu()
+                if eos_id is not None:
+                    done |= (g_cpu == eos_id).any(1)
+                if stop_fn is not None:
+                    done |= stop_fn(g_cpu)
+                if bool(done.all()):
+                    break
+            if k < max_new:
+                self.tok.copy_(self.next)
+                self.step()
+        return gen[:, :k].cpu(), k
