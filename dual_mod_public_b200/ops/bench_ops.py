@@ -1,0 +1,166 @@
+"""Micro-benchmarks of the sm_100a kernels at the shapes the 340M engine launches them with.
+
+  python -m dual_mod_public_b200.ops.bench_ops                 # every op
+  python -m dual_mod_public_b200.ops.bench_ops --only tail_bwd --iters 3 --no-flush   # for a profiler
+
+Each op is timed with CUDA events on the launching stream after warm-up; between timed
+iterations a 256 MB buffer is written so inputs come from HBM, not from the 126 MB L2.
+Printed per op: microseconds, and the achieved TFLOP/s or GB/s from the op's algorithmic
+FLOPs / bytes (with the fraction of the measured peaks when MEASURED_PEAKS.json is found).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..models.rope import build_rope_cache
+from .cuda_ops import CudaOps
+
+DEV = "cuda:0"
+BF = torch.bfloat16
+
+
+def peaks():
+    here = os.path.dirname(os.path.abspath(__file__))
+    p = os.path.join(here, "..", "..", "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+class Timer:
+    def __init__(self, iters, flush):
+        self.iters, self.flush = iters, flush
+        self.junk = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if flush else None
+
+    def __call__(self, fn, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        tot = 0.0
+        for _ in range(self.iters):
+            if self.junk is not None:
+                self.junk.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        return tot / self.iters * 1e3          # microseconds
+
+
+def rnd(*s, dtype=BF, scale=1.0):
+    return (torch.randn(*s, device=DEV) * scale).to(dtype)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--B", type=int, default=32)
+    ap.add_argument("--pos0", type=int, default=1024)
+    ap.add_argument("--d", type=int, default=1024)
+    ap.add_argument("--dh", type=int, default=64)
+    args = ap.parse_args()
+    ops = CudaOps(torch.device(DEV))
+    T = Timer(args.iters, not args.no_flush)
+    hbm, tf, tag = peaks()
+    B, c, d, dh = args.B, 64, args.d, args.dh
+    h = d // dh
+    pos0, Tlen = args.pos0, args.pos0 + 64
+    scale = dh ** -0.5
+    rows = []
+
+    def report(name, us, flops=0.0, bytes_=0.0):
+        msg = f"{name:28s} {us:9.1f} us"
+        if flops:
+            t = flops / us / 1e6
+            msg += f"  {t:8.1f} TFLOP/s ({t / tf:5.1%} {tag})"
+        if bytes_:
+            g = bytes_ / us / 1e3
+            msg += f"  {g:8.1f} GB/s ({g / hbm:5.1%} {tag})"
+        print(msg, flush=True)
+        rows.append((name, us))
+
+    want = lambda n: not args.only or args.only in n
+    # ---- cell tensors
+    q, ks, vr = rnd(B, Tlen, h, dh), rnd(B, Tlen, h, dh), rnd(B, Tlen, h, dh)
+    Kc, Vc = rnd(B, Tlen, h, dh), rnd(B, Tlen, h, dh)
+    r = slice(pos0, pos0 + c)
+    qc, ksc, vrc = q[:, r], ks[:, r], vr[:, r]
+    K_in, V_in = rnd(B, c, h, dh), rnd(B, c, h, dh)
+    o_c, lse_c = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, 0)
+    o, lse = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)
+    z = lambda *s: torch.zeros(*s, device=DEV)
+    att_f = 4.0 * B * h * c * dh          # flops per key for QK^T + PV
+    if want("prefix_fwd"):
+        report("prefix_fwd", T(lambda: ops.prefix_fwd(qc, Kc, Vc, pos0, scale, 0)), flops=att_f * pos0)
+    if want("tail_fwd"):
+        report("tail_fwd", T(lambda: ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)), flops=att_f * c / 2)
+    dO = rnd(B, c, h, dh, dtype=torch.float32)
+    acc = [z(B, c, h, dh), z(B, Tlen, h, dh), z(B, Tlen, h, dh), z(B, c, h, dh), z(B, c, h)]
+    if want("tail_bwd"):
+        report("tail_bwd", T(lambda: ops.tail_bwd(dO, qc, ksc, vrc, K_in, V_in, o_c, lse_c, o, lse, scale, 0,
+                                                  acc[0], acc[1][:, r], acc[2][:, r], acc[3], acc[4])),
+               flops=2.5 * att_f * c / 2)
+    dKc, dVc = z(B, Tlen, h, dh), z(B, Tlen, h, dh)
+    if want("prefix_bwd"):
+        report("prefix_bwd", T(lambda: ops.prefix_bwd(qc, Kc, Vc, pos0, scale, 0, o_c, lse_c, acc[3], acc[4],
+                                                      acc[0], dKc, dVc)), flops=2.5 * att_f * pos0)
+    # ---- refine / norms
+    cos, sin = build_rope_cache(Tlen, dh, 10000.0, device=DEV)
+    cg, glx, k, v = rnd(B, c, 4 * d), rnd(B, Tlen, 2 * d), rnd(B, Tlen, d), rnd(B, Tlen, d)
+    N = B * c
+    if want("refine_fwd"):
+        report("refine_fwd", T(lambda: ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, 0)),
+               bytes_=N * d * 2 * 10)
+    dK, dV = rnd(B, c, h, dh, dtype=torch.float32), rnd(B, c, h, dh, dtype=torch.float32)
+    dk_a, dv_a, dg_a = z(B, Tlen, d), z(B, Tlen, d), z(B, Tlen, 2 * d)
+    if want("refine_bwd"):
+        report("refine_bwd", T(lambda: ops.refine_bwd(dK, dV, cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], 0,
+                                                      dk_a[:, r], dv_a[:, r], dg_a[:, r])), bytes_=N * d * 64)
+    x2, w = rnd(N, d), rnd(d) + 1
+    if want("rms_fwd"):
+        report("rms_fwd", T(lambda: ops.rms_fwd(x2, w)), bytes_=N * d * 4)
+    y, rstd = ops.rms_fwd(x2, w)
+    dwa = z(d)
+    if want("rms_bwd"):
+        report("rms_bwd (+dw)", T(lambda: ops.rms_bwd(x2, x2, w, rstd, dwa)), bytes_=N * d * (2 + 2 + 4 + 4))
+    if want("ce"):
+        lg, tg = rnd(4096, 32000), torch.randint(0, 32000, (4096,), device=DEV)
+        inv = torch.tensor(1.0 / 4096, device=DEV)
+        report("ce slab 4096x32000", T(lambda: ops.ce_chunk(lg, tg, inv)), bytes_=4096 * 32000 * 2 * 2)
+    # ---- GEMMs: ours vs torch.matmul (cuBLAS)
+    if want("gemm") and ops.gemm is not None:
+        g = ops.gemm
+        shapes = [("sweep y=uW^T", 2048, 4096, 1024), ("qkv", 65536, 1024, 1024), ("mlp up", 65536, 2816, 1024),
+                  ("mlp down", 65536, 1024, 2816), ("head", 4096, 32000, 1024)]
+        for name, M, Nn, K in shapes:
+            a, wt = rnd(M, K), rnd(Nn, K)
+            f = 2.0 * M * Nn * K
+            report(f"gemm tn {name}", T(lambda: g.linear(a, wt)), flops=f)
+            report(f"  cublas {name}", T(lambda: a @ wt.t()), flops=f)
+        dy, wt = rnd(2048, 4096), rnd(4096, 1024)
+        f = 2.0 * 2048 * 4096 * 1024
+        report("gemm nn sweep du", T(lambda: g.linear_dx(dy, wt)), flops=f)
+        report("  cublas sweep du", T(lambda: dy @ wt), flops=f)
+        dW, xx = z(4096, 1024), rnd(2048, 1024)
+        report("gemm dw sweep", T(lambda: g.linear_dw_acc(dW, dy, xx)), flops=f)
+        report("  cublas dw sweep", T(lambda: dW.add_(torch.mm(dy.t(), xx, out_dtype=torch.float32))), flops=f)
+        dyb, xb, dWb = rnd(65536, 1024), rnd(65536, 1024), z(1024, 1024)
+        fb = 2.0 * 65536 * 1024 * 1024
+        report("gemm dw layer", T(lambda: g.linear_dw_acc(dWb, dyb, xb)), flops=fb)
+        report("  cublas dw layer", T(lambda: dWb.add_(torch.mm(dyb.t(), xb, out_dtype=torch.float32))), flops=fb)
+        g.check()
+    return rows
+
+
+if __name__ == "__main__":
+    main()
