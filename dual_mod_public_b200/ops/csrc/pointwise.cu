@@ -1,7 +1,10 @@
 // Bandwidth-bound fused kernels: RMSNorm fwd/bwd, RoPE, the refine write law fwd/bwd, SwiGLU
 // fwd/bwd, the cross-entropy slab (loss + d logits) and column reductions.  All activations are
 // bf16, all statistics and gradients of parameters fp32.
+#include <stdio.h>
+
 #include "common.cuh"
+#include "noalloc.h"
 
 namespace {
 
@@ -350,6 +353,48 @@ int dmb_col_reduce_acc(const void* dy, int dy_f32, const void* x, long long xs, 
   reduce_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, out, nsplit, d);
   DMB_CHECK_LAUNCH();
   return 0;
+}
+
+// ---- column reduction for callers that cannot allocate ---------------------------------------
+// See noalloc.h.  The partial sums live in a fixed array inside this library instead of caller
+// memory.  Every entry the second kernel reads is written by the first one in the same call, so
+// nothing in the array has to start at zero and the previous call's contents do not matter.
+static __device__ __align__(256) float g_noalloc_partials[DMB_NOALLOC_MAX_SPLIT * DMB_NOALLOC_MAX_COLS];
+static float* g_noalloc_ptr[DMB_NOALLOC_MAX_DEVICES] = {nullptr};
+static char g_noalloc_err[256] = "";
+
+const char* dmb_noalloc_last_error() { return g_noalloc_err; }
+
+int dmb_col_reduce_acc_noalloc(const void* dy, int dy_f32, const void* x, long long xs, const float* rstd,
+                               float* out, int rows, int d, cudaStream_t st) {
+  g_noalloc_err[0] = 0;
+  if (d <= 0 || rows <= 0 || d > DMB_NOALLOC_MAX_COLS) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err),
+             "dmb_col_reduce_acc_noalloc: %d columns / %d rows not supported (1 <= columns <= %d, rows >= 1); "
+             "use dmb_col_reduce_acc with caller scratch for wider inputs", d, rows, DMB_NOALLOC_MAX_COLS);
+    return DMB_NOALLOC_E_SIZE;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= DMB_NOALLOC_MAX_DEVICES) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "dmb_col_reduce_acc_noalloc: no usable current device (%d, CUDA error %d)", dev, (int)e);
+    return DMB_NOALLOC_E_DEVICE;
+  }
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // one-time set-up for this device: in host code the array's name is only a handle, the device
+    // address has to be asked for while that device is current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_partials);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_noalloc_err, sizeof(g_noalloc_err), "dmb_col_reduce_acc_noalloc: cudaGetSymbolAddress failed on device %d (CUDA error %d)", dev, (int)e);
+      return DMB_NOALLOC_E_DEVICE;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  int nsplit = rows / 64;
+  if (nsplit < 1) nsplit = 1;
+  if (nsplit > DMB_NOALLOC_MAX_SPLIT) nsplit = DMB_NOALLOC_MAX_SPLIT;
+  return dmb_col_reduce_acc(dy, dy_f32, x, xs, rstd, g_noalloc_ptr[dev], nsplit, out, rows, d, st);
 }
 
 int dmb_rope(const void* x, int in_f32, long long bs, long long rs, const float* cosb, const float* sinb,
