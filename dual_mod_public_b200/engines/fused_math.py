@@ -123,6 +123,55 @@ def prefix_bwd(q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c, dq_ac
     dVc[:, lo:pos0] += torch.einsum("bhcj,bchd->bjhd", p, do_c)
 
 
+def prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
+    """Query side of the prefix backward for one cell: dq_acc [B,c,h,dh] fp32 += dS K over the
+    committed rows.  do_c [B,c,h,dh] (any float dtype), corr [B,c,h] fp32 = do_c.o_c - dlse_c."""
+    B, c, h, dh = q_r.shape
+    lo = prefix_lo(pos0, window)
+    if pos0 - lo <= 0:
+        return
+    K, V = Kc[:, lo:pos0], Vc[:, lo:pos0]
+    s = torch.einsum("bchd,bjhd->bhcj", q_r, K).float() * scale
+    m = _prefix_mask(c, lo, pos0, pos0, window, q_r.device)
+    if m is not None:
+        s = s.masked_fill(~m, NEG)
+    p = torch.exp(s - lse_c.permute(0, 2, 1).unsqueeze(-1))
+    if m is not None:
+        p = p * m
+    dov = torch.einsum("bchd,bjhd->bhcj", do_c.float(), V.float())
+    ds = p * (dov - corr.permute(0, 2, 1).unsqueeze(-1)) * scale
+    dq_acc += torch.einsum("bhcj,bjhd->bchd", ds, K.float())
+
+
+def prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0):
+    """Key side of the prefix backward, owner-computes: the gradient of tape rows
+    [pos0, pos0+c) from every later query (absolute rows >= q_start of the full-sequence
+    arrays q_all / doc_all [B,T,h,dh], corr_all / lsec_all [B,T,h]).  Returns fp32
+    (dK, dV) [B,c,h,dh]; nothing is accumulated in global memory."""
+    B, T, h, dh = q_all.shape
+    dK = torch.zeros(B, c, h, dh, dtype=torch.float32, device=q_all.device)
+    dV = torch.zeros_like(dK)
+    if q_start >= T:
+        return dK, dV
+    q, do = q_all[:, q_start:], doc_all[:, q_start:].float()
+    K, V = Kc[:, pos0:pos0 + c], Vc[:, pos0:pos0 + c]
+    s = torch.einsum("bthd,bjhd->bhtj", q, K).float() * scale
+    vis = None
+    if window:
+        t = torch.arange(q_start, T, device=q_all.device)[:, None]
+        j = torch.arange(pos0, pos0 + c, device=q_all.device)[None, :]
+        vis = j > t - window
+        s = s.masked_fill(~vis, NEG)
+    p = torch.exp(s - lsec_all[:, q_start:].permute(0, 2, 1).unsqueeze(-1))
+    if vis is not None:
+        p = p * vis
+    dov = torch.einsum("bthd,bjhd->bhtj", do, V.float())
+    ds = p * (dov - corr_all[:, q_start:].permute(0, 2, 1).unsqueeze(-1)) * scale
+    dK += torch.einsum("bhtj,bthd->bjhd", ds, q.float())
+    dV += torch.einsum("bhtj,bthd->bjhd", p, do)
+    return dK, dV
+
+
 # ---- per-sweep tail read ------------------------------------------------------------------
 
 def tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):

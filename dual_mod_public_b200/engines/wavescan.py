@@ -135,14 +135,24 @@ class WaveScanEngine:
             self.K_caches = [z(B, T, h, dh) for _ in range(L)]
             self.V_caches = [z(B, T, h, dh) for _ in range(L)]
             self.o_saved = [z(B, T, d) for _ in range(L)]      # last-sweep reads per layer
-            self.dK = z(B, T, h, dh, dt=torch.float32)        # one layer's tape grads (reused)
-            self.dV = z(B, T, h, dh, dt=torch.float32)
+            # prefix-backward inputs of one layer, indexed by absolute position (reused per layer):
+            # d o_c of every row, corr = d o_c . o_c - d lse_c, and lse_c
+            self.doc_all = z(B, T, h, dh)
+            self.corr_all = z(B, T, h, dt=torch.float32)
+            self.lsec_all = z(B, T, h, dt=torch.float32)
+            self.dK = self.dV = None
             self.packs = [_LayerPack(b, cfg, act, dev) for b in model.blocks]
             self.emb_c = z(cfg.vocab_size, d)
             self.w_f = z(d)
             self.head_w = None if cfg.tie_embeddings else z(cfg.vocab_size, d)
             self.dW_pack = z(4 * d, d, dt=torch.float32)
             self.dW_gx = z(2 * d, d, dt=torch.float32)
+            # committed-prefix partials of every cell, kept from the forward so the backward
+            # does not redo the prefix pass: per schedule, [L][n_cells] dense slots
+            self._prefix_saved = {}
+            # per-layer stash of (d ctx/gate logits, u) of every sweep: the packed weight
+            # gradient is ONE GEMM over all of a layer's sweep rows instead of one per sweep
+            self._dw_stash = {}
             self._packed = False
         else:
             self.K_caches = [z(B, h, T, dh) for _ in range(L)]
@@ -253,7 +263,9 @@ class WaveScanEngine:
     def debug_scan(self):
         """Names of persistent buffers holding non-finite values."""
         bad = []
-        named = {"loss": self.loss, "dx_top": self.dx_top, "dK": self.dK, "dV": self.dV}
+        named = {"loss": self.loss, "dx_top": self.dx_top}
+        if self.dK is not None:
+            named["dK"], named["dV"] = self.dK, self.dV
         for i, t in enumerate(self.xl):
             named[f"xl[{i}]"] = t
         for i, (k, v) in enumerate(zip(self.K_caches, self.V_caches)):
@@ -333,9 +345,12 @@ class WaveScanEngine:
             glx = ops.linear(xhat, P.W_gx, bias=P.b_g)
             Kc, Vc, o_all = self.K_caches[li], self.V_caches[li], self.o_saved[li]
             v4 = v.view(B, T, h, dh)
-            for pos0, c, n_sweeps in self.schedules[sid]:
+            saved = self._prefix_slots(sid, li)
+            for ci, (pos0, c, n_sweeps) in enumerate(self.schedules[sid]):
                 r = slice(pos0, pos0 + c)
                 o_c, lse_c = ops.prefix_fwd(q_r[:, r], Kc, Vc, pos0, scale, self.window)
+                saved[ci][0].copy_(o_c)
+                saved[ci][1].copy_(lse_c)
                 K_in, V_in = kself_r[:, r], v4[:, r]
                 o = None
                 for _ in range(n_sweeps):
@@ -353,6 +368,30 @@ class WaveScanEngine:
             xn, _ = ops.rms_fwd(x_mid, P.w_mn)
             g = ops.swiglu_fwd(ops.linear(xn, P.w1), ops.linear(xn, P.w3))
             self.xl[li + 1].copy_(x_mid + ops.linear(g, P.w2))
+
+    def _prefix_slots(self, sid, li):
+        """[(o_c [B,c,h,dh] fp32, lse_c [B,c,h] fp32)] per cell of layer li at schedule sid."""
+        key = (sid, li)
+        if key not in self._prefix_saved:
+            cfg, f32 = self.cfg, torch.float32
+            self._prefix_saved[key] = [
+                (torch.zeros(self.B, c, cfg.n_heads, cfg.head_dim, dtype=f32, device=self.device),
+                 torch.zeros(self.B, c, cfg.n_heads, dtype=f32, device=self.device))
+                for _, c, _ in self.schedules[sid]]
+        return self._prefix_saved[key]
+
+    def _stash_for(self, sid):
+        """(dcg stash [rows, 4d], u stash [rows, d], row offset of every (cell, sweep)) shared by all
+        layers of a schedule; rows = B * sum_cells c * sweeps."""
+        if sid not in self._dw_stash:
+            d, offs, n = self.cfg.d_model, {}, 0
+            for ci, (_, c, k) in enumerate(self.schedules[sid]):
+                for s_ in range(k):
+                    offs[(ci, s_)] = n
+                    n += self.B * c
+            self._dw_stash[sid] = (torch.zeros(n, 4 * d, dtype=self.act, device=self.device),
+                                   torch.zeros(n, d, dtype=self.act, device=self.device), offs)
+        return self._dw_stash[sid]
 
     def _head_weight(self):
         return self.emb_c if self.head_w is None else self.head_w
@@ -441,8 +480,6 @@ class WaveScanEngine:
             glx = ops.linear(xhat, P.W_gx, bias=P.b_g)
             v4 = v.view(B, T, h, dh)
             Kc, Vc = self.K_caches[li], self.V_caches[li]
-            self.dK.zero_()
-            self.dV.zero_()
             self.dW_pack.zero_()
             dq_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
             dks_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
@@ -452,10 +489,14 @@ class WaveScanEngine:
             dv4 = dv.view(B, T, h, dh)
             dw_ctx = G.get(a.norm_ctx.weight)
             # ---- cells in reverse ---------------------------------------------------------------
-            for pos0, c, n_sweeps in reversed(self.schedules[sid]):
+            saved = self._prefix_slots(sid, li)
+            dcg_stash, u_stash, stash_off = self._stash_for(sid)
+            n_cells = len(self.schedules[sid])
+            for ci in range(n_cells - 1, -1, -1):
+                pos0, c, n_sweeps = self.schedules[sid][ci]
                 r = slice(pos0, pos0 + c)
                 qc, ksc, vc4 = q_r[:, r], kself_r[:, r], v4[:, r]
-                o_c, lse_c = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, self.window)
+                o_c, lse_c = saved[ci]
                 # forward recompute, keeping each sweep's state
                 st = []
                 K_in, V_in = ksc, vc4
@@ -466,7 +507,10 @@ class WaveScanEngine:
                     st.append((K_in, V_in, o, lse, u, rstd, cg))
                     K_in, V_in = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
                                                 h, pin)
-                dK_out, dV_out = self.dK[:, r].contiguous(), self.dV[:, r].contiguous()
+                self.lsec_all[:, r] = lse_c
+                # gradient of this cell's committed rows from every later cell's prefix read
+                dK_out, dV_out = ops.prefix_dkv(q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
+                                                pos0, c, pos0 + c, scale, self.window)
                 d_o = dO_all[:, r].float()
                 do_c = torch.zeros_like(o_c)
                 dlse_c = torch.zeros_like(lse_c)
@@ -475,7 +519,9 @@ class WaveScanEngine:
                     K_in, V_in, o, lse, u, rstd, cg = st[s]
                     dcg = ops.refine_bwd(dK_out, dV_out, cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
                                          pin, dk[:, r], dv[:, r], dglx[:, r])
-                    ops.linear_dw_acc(self.dW_pack, dcg, u)
+                    off = stash_off[(ci, s)]
+                    dcg_stash[off:off + B * c].copy_(dcg.reshape(B * c, 4 * d))
+                    u_stash[off:off + B * c].copy_(u.reshape(B * c, d))
                     du = ops.linear_dx(dcg, P.W_pack)
                     d_o = ops.rms_bwd(du, o.reshape(B, c, d), P.w_ctx, rstd, dw_ctx,
                                       residual=d_o.view(B, c, d) if s == n_sweeps - 1 else None
@@ -486,10 +532,13 @@ class WaveScanEngine:
                 # sweep 0 read the raw rows
                 dks_r[:, r] += dK_out
                 dv4[:, r] += dV_out
-                ops.prefix_bwd(qc, Kc, Vc, pos0, scale, self.window, o_c, lse_c, do_c, dlse_c,
-                               dq_c, self.dK, self.dV)
+                corr = (do_c * o_c).sum(-1) - dlse_c
+                self.doc_all[:, r] = do_c
+                self.corr_all[:, r] = corr
+                ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_c)
                 dq_r[:, r] = dq_c
                 self.stats["bwd_cells"] += 1
+            ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
             # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
             dq = ops.unrope(dq_r, cos, sin).reshape(B, T, d).to(act)
             dk_t = (dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)).to(act)

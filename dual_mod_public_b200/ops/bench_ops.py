@@ -110,10 +110,18 @@ def main():
         report("tail_bwd", T(lambda: ops.tail_bwd(dO, qc, ksc, vrc, K_in, V_in, o_c, lse_c, o, lse, scale, 0,
                                                   acc[0], acc[1][:, r], acc[2][:, r], acc[3], acc[4])),
                flops=2.5 * att_f * c / 2)
-    dKc, dVc = z(B, Tlen, h, dh), z(B, Tlen, h, dh)
-    if want("prefix_bwd"):
-        report("prefix_bwd", T(lambda: ops.prefix_bwd(qc, Kc, Vc, pos0, scale, 0, o_c, lse_c, acc[3], acc[4],
-                                                      acc[0], dKc, dVc)), flops=2.5 * att_f * pos0)
+    if want("prefix_dq"):
+        doc_c, corr = rnd(B, c, h, dh), rnd(B, c, h, dtype=torch.float32)
+        report("prefix_dq", T(lambda: ops.prefix_dq(qc, Kc, Vc, pos0, scale, 0, lse_c, doc_c, corr, acc[0])),
+               flops=1.5 * att_f * pos0)
+    if want("prefix_dkv"):
+        Tq = 2048
+        qa, da = rnd(B, Tq, h, dh), rnd(B, Tq, h, dh)
+        Ka, Va = rnd(B, Tq, h, dh), rnd(B, Tq, h, dh)
+        ca, la = rnd(B, Tq, h, dtype=torch.float32), rnd(B, Tq, h, dtype=torch.float32) + 8.0
+        p0 = Tq - pos0 - c                       # as many later query rows as `pos0` keys elsewhere
+        report("prefix_dkv", T(lambda: ops.prefix_dkv(qa, da, ca, la, Ka, Va, p0, c, p0 + c, scale, 0)),
+               flops=2.0 * att_f * (Tq - p0 - c))
     # ---- refine / norms
     cos, sin = build_rope_cache(Tlen, dh, 10000.0, device=DEV)
     cg, glx, k, v = rnd(B, c, 4 * d), rnd(B, Tlen, 2 * d), rnd(B, Tlen, d), rnd(B, Tlen, d)

@@ -5,113 +5,11 @@
 // Read algebra (per chunk row i, all in fp32):
 //   lse = log( exp(lse_c) + sum_{j<i} exp(s_ij) + exp(s_self) ),  o = P_c o_c + sum_j P_j v_j + P_self v_raw
 // and its hand-derived backward; see engines/fused_math.py for the plain-torch statement.
-#include "common.cuh"
+#include "attn_tiles.cuh"
+
+using namespace attn;
 
 namespace {
-
-template <int DH>
-struct Tile {
-  static constexpr int PITCH = DH + 8;  // +16 B per row: conflict-free ldmatrix
-};
-
-// ---- fragment loaders --------------------------------------------------------------------
-template <int PITCH>
-__device__ __forceinline__ void load_a(uint32_t (&a)[4], const bf16* t, int row0, int k0, int lane) {
-  int r = row0 + (lane & 15), c = k0 + ((lane >> 4) << 3);
-  ldsm_x4(a[0], a[1], a[2], a[3], smem_u32(t + r * PITCH + c));
-}
-// B for n-blocks [n0, n0+16) x k [k0, k0+16) from a tile stored [n][k]
-template <int PITCH>
-__device__ __forceinline__ void load_b_nk(uint32_t (&b)[4], const bf16* t, int n0, int k0, int lane) {
-  int n = n0 + (lane & 7) + ((lane >> 4) << 3), k = k0 + (((lane >> 3) & 1) << 3);
-  ldsm_x4(b[0], b[1], b[2], b[3], smem_u32(t + n * PITCH + k));
-}
-// B for k [k0, k0+16) x n-blocks [n0, n0+16) from a tile stored [k][n]
-template <int PITCH>
-__device__ __forceinline__ void load_b_kn(uint32_t (&b)[4], const bf16* t, int k0, int n0, int lane) {
-  int k = k0 + (lane & 7) + (((lane >> 3) & 1) << 3), n = n0 + ((lane >> 4) << 3);
-  ldsm_x4_t(b[0], b[1], b[2], b[3], smem_u32(t + k * PITCH + n));
-}
-// A = X^T block (m [m0,m0+16), k [k0,k0+16)) from X stored [k][m]
-template <int PITCH>
-__device__ __forceinline__ void load_a_t(uint32_t (&a)[4], const bf16* t, int m0, int k0, int lane) {
-  int i = lane >> 3;
-  int r = k0 + (lane & 7) + ((i >> 1) << 3), c = m0 + ((i & 1) << 3);
-  ldsm_x4_t(a[0], a[1], a[2], a[3], smem_u32(t + r * PITCH + c));
-}
-
-// rows x DH bf16 from global (row stride rs elements) into a padded tile
-template <int DH, int NT>
-__device__ __forceinline__ void load_tile_bf16(bf16* dst, const bf16* src, long long rs, int rows,
-                                               int tid) {
-  constexpr int P = Tile<DH>::PITCH, CH = DH / 8;
-  for (int i = tid; i < rows * CH; i += NT) {
-    int r = i / CH, c = (i % CH) * 8;
-    *reinterpret_cast<uint4*>(dst + r * P + c) = *reinterpret_cast<const uint4*>(src + r * rs + c);
-  }
-}
-template <int DH, int NT>
-__device__ __forceinline__ void load_tile_f32(bf16* dst, const float* src, long long rs, int rows,
-                                              int tid) {
-  constexpr int P = Tile<DH>::PITCH, CH = DH / 4;
-  for (int i = tid; i < rows * CH; i += NT) {
-    int r = i / CH, c = (i % CH) * 4;
-    float4 v = *reinterpret_cast<const float4*>(src + r * rs + c);
-    uint2 u = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
-    *reinterpret_cast<uint2*>(dst + r * P + c) = u;
-  }
-}
-template <int DH, int NT>
-__device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, long long rs, int rows,
-                                                int tid) {
-  constexpr int P = Tile<DH>::PITCH, CH = DH / 8;
-  for (int i = tid; i < rows * CH; i += NT) {
-    int r = i / CH, c = (i % CH) * 8;
-    cp_async16(dst + r * P + c, src + r * rs + c);
-  }
-}
-
-// per-row dot product of two DH-vectors split over the 4 lanes of a quad
-template <int DH>
-__device__ __forceinline__ float quad_dot_bf16(const bf16* a, const bf16* b, int t) {
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < DH / 8; ++i) {
-    int d = (i * 4 + t) * 2;
-    float2 x = __bfloat1622float2(*reinterpret_cast<const bf162*>(a + d));
-    float2 y = __bfloat1622float2(*reinterpret_cast<const bf162*>(b + d));
-    s += x.x * y.x + x.y * y.y;
-  }
-  return quad_sum(s);
-}
-template <int DH>
-__device__ __forceinline__ float quad_dot_f32_bf16(const float* a, const bf16* b, int t) {
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < DH / 8; ++i) {
-    int d = (i * 4 + t) * 2;
-    float2 x = *reinterpret_cast<const float2*>(a + d);
-    float2 y = __bfloat1622float2(*reinterpret_cast<const bf162*>(b + d));
-    s += x.x * y.x + x.y * y.y;
-  }
-  return quad_sum(s);
-}
-template <int DH>
-__device__ __forceinline__ float quad_dot_f32(const float* a, const float* b, int t) {
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < DH / 8; ++i) {
-    int d = (i * 4 + t) * 2;
-    float2 x = *reinterpret_cast<const float2*>(a + d);
-    float2 y = *reinterpret_cast<const float2*>(b + d);
-    s += x.x * y.x + x.y * y.y;
-  }
-  return quad_sum(s);
-}
-
-__device__ __forceinline__ bool intra_ok(int i, int j, int window) {
-  return j < i && (window == 0 || j > i - window);
-}
 
 // =============================================================================================
 // tail forward
@@ -438,7 +336,6 @@ __global__ void __launch_bounds__(C * 2) tail_bwd_kernel(
 // =============================================================================================
 // committed-prefix forward: chunk queries against tape rows [lo, pos0)
 // =============================================================================================
-constexpr int KT = 64;  // keys per tile
 
 template <int DH, int C>
 __global__ void __launch_bounds__(C * 2) prefix_fwd_kernel(
@@ -576,194 +473,7 @@ __global__ void __launch_bounds__(C * 2) prefix_fwd_kernel(
   }
 }
 
-// =============================================================================================
-// committed-prefix backward
-// =============================================================================================
-template <int DH, int C>
-__global__ void __launch_bounds__(C * 2) prefix_bwd_kernel(
-    const bf16* __restrict__ q, TView vq, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc,
-    TView vc, const float* __restrict__ o_c, const float* __restrict__ lse_c,
-    const float* __restrict__ do_c, const float* __restrict__ dlse_c, float* __restrict__ dq_acc,
-    float* __restrict__ dKc, float* __restrict__ dVc, TView vdc, int H, int lo, int pos0,
-    float scale, int window) {
-  constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = KT / 8, PC = KT + 8, NW = C / 16;
-  constexpr int KPW = KT / NW;  // keys per warp in the transposed phase (16, 32 or 64)
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
-  bf16* sdO = sQ + C * P;
-  bf16* sK = sdO + C * P;
-  bf16* sV = sK + KT * P;
-  bf16* sP = sV + KT * P;    // [C][PC]
-  bf16* sdS = sP + C * PC;   // [C][PC]
-  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const long long hoff = (long long)h * DH;
-  const long long dense_rs = (long long)H * DH, dense_b = (long long)b * C * dense_rs + hoff;
-  const bf16* Kb = Kc + b * vc.bs + hoff;
-  const bf16* Vb = Vc + b * vc.bs + hoff;
-  float* dKb = dKc + b * vdc.bs + hoff;
-  float* dVb = dVc + b * vdc.bs + hoff;
-  load_tile_bf16<DH, NT>(sQ, q + b * vq.bs + hoff, vq.rs, C, tid);
-  load_tile_f32<DH, NT>(sdO, do_c + dense_b, dense_rs, C, tid);
-  const int row0 = warp * 16, i0 = row0 + g, i1 = i0 + 8;
-  const long long orow0 = ((long long)(b * C + i0) * H + h), orow1 = ((long long)(b * C + i1) * H + h);
-  const float L0 = lse_c[orow0], L1 = lse_c[orow1];
-  const float corr0 = quad_dot_f32<DH>(do_c + orow0 * DH, o_c + orow0 * DH, t) - dlse_c[orow0];
-  const float corr1 = quad_dot_f32<DH>(do_c + orow1 * DH, o_c + orow1 * DH, t) - dlse_c[orow1];
-  float A[DH / 8][4];
-#pragma unroll
-  for (int n = 0; n < DH / 8; ++n) A[n][0] = A[n][1] = A[n][2] = A[n][3] = 0.f;
-  const int n_keys = pos0 - lo, n_tiles = (n_keys + KT - 1) / KT;
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const int kbase = lo + tile * KT, rows = min(KT, pos0 - kbase);
-    __syncthreads();  // previous tile's readers are done with sK/sV/sP/sdS
-    load_tile_bf16<DH, NT>(sK, Kb + (long long)kbase * vc.rs, vc.rs, rows, tid);
-    load_tile_bf16<DH, NT>(sV, Vb + (long long)kbase * vc.rs, vc.rs, rows, tid);
-    if (rows < KT) {  // zero the unused rows so 0-probability products stay finite
-      constexpr int CH = DH / 8;
-      for (int i = tid; i < (KT - rows) * CH; i += NT) {
-        int r = rows + i / CH, c = (i % CH) * 8;
-        *reinterpret_cast<uint4*>(sK + r * P + c) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(sV + r * P + c) = make_uint4(0, 0, 0, 0);
-      }
-    }
-    __syncthreads();
-    float S[NB][4], dP[NB][4];
-#pragma unroll
-    for (int n = 0; n < NB; ++n) {
-      S[n][0] = S[n][1] = S[n][2] = S[n][3] = 0.f;
-      dP[n][0] = dP[n][1] = dP[n][2] = dP[n][3] = 0.f;
-    }
-#pragma unroll
-    for (int k0 = 0; k0 < DH; k0 += 16) {
-      uint32_t a[4], ad[4];
-      load_a<P>(a, sQ, row0, k0, lane);
-      load_a<P>(ad, sdO, row0, k0, lane);
-#pragma unroll
-      for (int n = 0; n < NB; n += 2) {
-        uint32_t bb[4];
-        load_b_nk<P>(bb, sK, n * 8, k0, lane);
-        mma16816(S[n], a, bb[0], bb[1]);
-        mma16816(S[n + 1], a, bb[2], bb[3]);
-        load_b_nk<P>(bb, sV, n * 8, k0, lane);
-        mma16816(dP[n], ad, bb[0], bb[1]);
-        mma16816(dP[n + 1], ad, bb[2], bb[3]);
-      }
-    }
-#pragma unroll
-    for (int n = 0; n < NB; ++n) {
-      int jl = n * 8 + 2 * t, j = kbase + jl;
-      bool in0 = jl < rows, in1 = jl + 1 < rows;
-      bool a0 = in0 && (window == 0 || j > pos0 + i0 - window);
-      bool a1 = in1 && (window == 0 || j + 1 > pos0 + i0 - window);
-      bool a2 = in0 && (window == 0 || j > pos0 + i1 - window);
-      bool a3 = in1 && (window == 0 || j + 1 > pos0 + i1 - window);
-      float p0 = a0 ? __expf(S[n][0] * scale - L0) : 0.f;
-      float p1 = a1 ? __expf(S[n][1] * scale - L0) : 0.f;
-      float p2 = a2 ? __expf(S[n][2] * scale - L1) : 0.f;
-      float p3 = a3 ? __expf(S[n][3] * scale - L1) : 0.f;
-      dP[n][0] = p0 * (dP[n][0] - corr0) * scale;
-      dP[n][1] = p1 * (dP[n][1] - corr0) * scale;
-      dP[n][2] = p2 * (dP[n][2] - corr1) * scale;
-      dP[n][3] = p3 * (dP[n][3] - corr1) * scale;
-      *reinterpret_cast<uint32_t*>(sP + i0 * PC + jl) = pack_bf16(p0, p1);
-      *reinterpret_cast<uint32_t*>(sP + i1 * PC + jl) = pack_bf16(p2, p3);
-      *reinterpret_cast<uint32_t*>(sdS + i0 * PC + jl) = pack_bf16(dP[n][0], dP[n][1]);
-      *reinterpret_cast<uint32_t*>(sdS + i1 * PC + jl) = pack_bf16(dP[n][2], dP[n][3]);
-    }
-    // dq += dS K
-#pragma unroll
-    for (int kk = 0; kk < KT / 16; ++kk) {
-      uint32_t a[4] = {pack_bf16(dP[2 * kk][0], dP[2 * kk][1]), pack_bf16(dP[2 * kk][2], dP[2 * kk][3]),
-                       pack_bf16(dP[2 * kk + 1][0], dP[2 * kk + 1][1]),
-                       pack_bf16(dP[2 * kk + 1][2], dP[2 * kk + 1][3])};
-#pragma unroll
-      for (int n = 0; n < DH / 8; n += 2) {
-        uint32_t bb[4];
-        load_b_kn<P>(bb, sK, kk * 16, n * 8, lane);
-        mma16816(A[n], a, bb[0], bb[1]);
-        mma16816(A[n + 1], a, bb[2], bb[3]);
-      }
-    }
-    __syncthreads();
-    // dK_tile = dS^T Q, dV_tile = P^T dO_c; this warp owns keys [warp*KPW, (warp+1)*KPW)
-#pragma unroll
-    for (int sub = 0; sub < KPW / 16; ++sub) {
-      const int key0 = warp * KPW + sub * 16;
-      if (key0 < rows) {
-        float GK[DH / 8][4], GV[DH / 8][4];
-#pragma unroll
-        for (int n = 0; n < DH / 8; ++n) {
-          GK[n][0] = GK[n][1] = GK[n][2] = GK[n][3] = 0.f;
-          GV[n][0] = GV[n][1] = GV[n][2] = GV[n][3] = 0.f;
-        }
-#pragma unroll
-        for (int kk = 0; kk < C / 16; ++kk) {
-          uint32_t as[4], ap[4];
-          load_a_t<PC>(as, sdS, key0, kk * 16, lane);
-          load_a_t<PC>(ap, sP, key0, kk * 16, lane);
-#pragma unroll
-          for (int n = 0; n < DH / 8; n += 2) {
-            uint32_t bb[4];
-            load_b_kn<P>(bb, sQ, kk * 16, n * 8, lane);
-            mma16816(GK[n], as, bb[0], bb[1]);
-            mma16816(GK[n + 1], as, bb[2], bb[3]);
-            load_b_kn<P>(bb, sdO, kk * 16, n * 8, lane);
-            mma16816(GV[n], ap, bb[0], bb[1]);
-            mma16816(GV[n + 1], ap, bb[2], bb[3]);
-          }
-        }
-        const int ka = key0 + g, kb2 = ka + 8;
-#pragma unroll
-        for (int n = 0; n < DH / 8; ++n) {
-          int d = n * 8 + 2 * t;
-          if (ka < rows) {
-            float2* pk = reinterpret_cast<float2*>(dKb + (long long)(kbase + ka) * vdc.rs + d);
-            float2* pv = reinterpret_cast<float2*>(dVb + (long long)(kbase + ka) * vdc.rs + d);
-            float2 x = *pk; x.x += GK[n][0]; x.y += GK[n][1]; *pk = x;
-            x = *pv; x.x += GV[n][0]; x.y += GV[n][1]; *pv = x;
-          }
-          if (kb2 < rows) {
-            float2* pk = reinterpret_cast<float2*>(dKb + (long long)(kbase + kb2) * vdc.rs + d);
-            float2* pv = reinterpret_cast<float2*>(dVb + (long long)(kbase + kb2) * vdc.rs + d);
-            float2 x = *pk; x.x += GK[n][2]; x.y += GK[n][3]; *pk = x;
-            x = *pv; x.x += GV[n][2]; x.y += GV[n][3]; *pv = x;
-          }
-        }
-      }
-    }
-  }
-  float* dq0 = dq_acc + orow0 * DH;
-  float* dq1 = dq_acc + orow1 * DH;
-#pragma unroll
-  for (int n = 0; n < DH / 8; ++n) {
-    int d = n * 8 + 2 * t;
-    float2 x = *reinterpret_cast<float2*>(dq0 + d);
-    x.x += A[n][0]; x.y += A[n][1];
-    *reinterpret_cast<float2*>(dq0 + d) = x;
-    x = *reinterpret_cast<float2*>(dq1 + d);
-    x.x += A[n][2]; x.y += A[n][3];
-    *reinterpret_cast<float2*>(dq1 + d) = x;
-  }
-}
-
-template <typename K>
-int set_smem(K kernel, size_t bytes) {
-  if (bytes > 48 * 1024)
-    return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  return 0;
-}
-
 }  // namespace
-
-#define DISPATCH_DH_C(DH_, C_, ...)                                  \
-  if (DH_ == 64 && C_ == 16) { constexpr int DH = 64, C = 16; __VA_ARGS__ }   \
-  else if (DH_ == 64 && C_ == 32) { constexpr int DH = 64, C = 32; __VA_ARGS__ }   \
-  else if (DH_ == 64 && C_ == 64) { constexpr int DH = 64, C = 64; __VA_ARGS__ }   \
-  else if (DH_ == 128 && C_ == 16) { constexpr int DH = 128, C = 16; __VA_ARGS__ } \
-  else if (DH_ == 128 && C_ == 32) { constexpr int DH = 128, C = 32; __VA_ARGS__ } \
-  else if (DH_ == 128 && C_ == 64) { constexpr int DH = 128, C = 64; __VA_ARGS__ } \
-  else return -1;
 
 extern "C" {
 
@@ -811,22 +521,6 @@ int dmb_prefix_fwd(const void* q, TView vq, const void* Kc, const void* Vc, TVie
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)Kc, (const bf16*)Vc, vc, o_c,
                                          lse_c, H, lo, pos0, scale, window);
-  })
-  DMB_CHECK_LAUNCH();
-  return 0;
-}
-
-int dmb_prefix_bwd(const void* q, TView vq, const void* Kc, const void* Vc, TView vc,
-                   const float* o_c, const float* lse_c, const float* do_c, const float* dlse_c,
-                   float* dq_acc, float* dKc, float* dVc, TView vdc, int B, int c, int H, int dh,
-                   int lo, int pos0, float scale, int window, cudaStream_t st) {
-  DISPATCH_DH_C(dh, c, {
-    size_t smem = (((size_t)2 * C + 2 * KT) * Tile<DH>::PITCH + (size_t)2 * C * (KT + 8)) * sizeof(bf16);
-    auto kern = prefix_bwd_kernel<DH, C>;
-    if (set_smem(kern, smem)) return -2;
-    kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)Kc, (const bf16*)Vc, vc, o_c,
-                                         lse_c, do_c, dlse_c, dq_acc, dKc, dVc, vdc, H, lo, pos0, scale,
-                                         window);
   })
   DMB_CHECK_LAUNCH();
   return 0;

@@ -60,8 +60,8 @@ class _Sigs:
     dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _v, _p, _v,
                     _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
     dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
-    dmb_prefix_bwd = [_p, _v, _p, _p, _v, _p, _p, _p, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i,
-                      _f, _i, _p]
+    dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]
+    dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
 
 
 BF16 = torch.bfloat16
@@ -250,21 +250,36 @@ class CudaOps(TorchOps):
                                          scale, window, self._st()), "prefix_fwd")
         return o_c, lse_c
 
-    def prefix_bwd(self, q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c, dq_acc, dKc, dVc):
+    def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
         from ..engines.fused_math import prefix_lo
         B, c, h, dh = q_r.shape
         lo = prefix_lo(pos0, window)
         if pos0 - lo <= 0:
             return
-        if not self._cell_ok(q_r) or not (_dense_tail(q_r, 2) and dq_acc.is_contiguous()):
-            return super().prefix_bwd(q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c,
-                                      dq_acc, dKc, dVc)
-        o_c, lse_c, do_c, dlse_c = (t.contiguous() for t in (o_c, lse_c, do_c, dlse_c))
-        self._ck(self.lib.dmb_prefix_bwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
-                                         o_c.data_ptr(), lse_c.data_ptr(), do_c.data_ptr(),
-                                         dlse_c.data_ptr(), dq_acc.data_ptr(), dKc.data_ptr(),
-                                         dVc.data_ptr(), _tv(dKc), B, c, h, dh, lo, pos0, scale, window,
-                                         self._st()), "prefix_bwd")
+        ok = (self._cell_ok(q_r) and do_c.dtype == BF16 and dq_acc.is_contiguous() and _dense_tail(q_r, 2)
+              and _dense_tail(do_c, 2) and _dense_tail(Kc, 2))
+        if not ok:
+            return super().prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc)
+        lse_c, corr = lse_c.contiguous(), corr.contiguous()
+        self._ck(self.lib.dmb_prefix_dq(q_r.data_ptr(), _tv(q_r), do_c.data_ptr(), _tv(do_c), Kc.data_ptr(),
+                                        Vc.data_ptr(), _tv(Kc), lse_c.data_ptr(), corr.data_ptr(),
+                                        dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, self._st()),
+                 "prefix_dq")
+
+    def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0):
+        B, T, h, dh = q_all.shape
+        ok = (q_all.dtype == BF16 and doc_all.dtype == BF16 and dh in (64, 128) and c in (16, 32, 64)
+              and q_all.is_contiguous() and doc_all.is_contiguous() and corr_all.is_contiguous()
+              and lsec_all.is_contiguous() and _dense_tail(Kc, 2))
+        if not ok:
+            return super().prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window)
+        dK = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
+        dV = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
+        self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(),
+                                         lsec_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
+                                         dK.data_ptr(), dV.data_ptr(), B, T, c, h, dh, pos0, q_start, scale,
+                                         window, self._st()), "prefix_dkv")
+        return dK, dV
 
     def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
         if not self._cell_ok(q_r) or not all(_dense_tail(t, 2) for t in (q_r, kself_r, v_raw, K_in, V_in)):

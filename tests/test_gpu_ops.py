@@ -133,15 +133,32 @@ def test_prefix_and_tail_fwd_bwd(ops, c, dh, pos0, window):
     for n_, g_, r_ in zip(names, got, ref):
         close(g_, r_, rtol=3e-2, atol=3e-2, what=n_)
     assert acc[1][:, :pos0].abs().max() == 0 if pos0 else True
-    # ---- prefix backward
+    # ---- prefix backward, query side
     do_c, dlse_c = ref[5], ref[6]
-    dq_acc, dKc, dVc = z(B, c, H, dh), z(B, T, H, dh), z(B, T, H, dh)
-    ops.prefix_bwd(qc, Kc, Vc, pos0, scale, window, o_c_ref, lse_c_ref, do_c, dlse_c, dq_acc, dKc, dVc)
-    dq_r, dK_r, dV_r = z(B, c, H, dh), z(B, T, H, dh), z(B, T, H, dh)
-    fm.prefix_bwd(f(qc), f(Kc), f(Vc), pos0, scale, window, o_c_ref, lse_c_ref, do_c, dlse_c, dq_r, dK_r, dV_r)
+    corr = (do_c * o_c_ref).sum(-1) - dlse_c
+    dq_acc, dq_r = z(B, c, H, dh), z(B, c, H, dh)
+    ops.prefix_dq(qc, Kc, Vc, pos0, scale, window, lse_c_ref, do_c.to(torch.bfloat16), corr, dq_acc)
+    fm.prefix_dq(f(qc), f(Kc), f(Vc), pos0, scale, window, lse_c_ref, do_c, corr, dq_r)
     close(dq_acc, dq_r, rtol=3e-2, atol=3e-2, what="prefix dq")
-    close(dKc, dK_r, rtol=3e-2, atol=3e-2, what="prefix dK")
-    close(dVc, dV_r, rtol=3e-2, atol=3e-2, what="prefix dV")
+
+
+@pytest.mark.parametrize("c,dh,pos0,T,window", [(64, 64, 128, 512, 0), (64, 128, 64, 300, 0), (32, 64, 32, 200, 0),
+                                                (16, 64, 48, 128, 0), (64, 64, 128, 512, 150), (64, 64, 448, 512, 0)])
+def test_prefix_dkv_owner_computes(ops, c, dh, pos0, T, window):
+    B, H = 2, 4
+    scale = dh ** -0.5
+    q, doc = rnd(B, T, H, dh), rnd(B, T, H, dh, seed=1)
+    Kc, Vc = rnd(B, T, H, dh, seed=2), rnd(B, T, H, dh, seed=3)
+    corr = rnd(B, T, H, dtype=torch.float32, seed=4)
+    # a plausible lse_c per row: log-sum-exp of that row's scores over its whole prefix
+    s = torch.einsum("bthd,bjhd->bhtj", q.float(), Kc.float()) * scale
+    lsec = torch.logsumexp(s, dim=-1).permute(0, 2, 1).contiguous() + 1.0
+    q_start = pos0 + c
+    dK, dV = ops.prefix_dkv(q, doc, corr, lsec, Kc, Vc, pos0, c, q_start, scale, window)
+    dK_r, dV_r = fm.prefix_dkv(q.float(), doc.float(), corr, lsec, Kc.float(), Vc.float(), pos0, c, q_start,
+                               scale, window)
+    close(dK, dK_r, rtol=3e-2, atol=3e-2, what="dK")
+    close(dV, dV_r, rtol=3e-2, atol=3e-2, what="dV")
 
 
 @pytest.mark.parametrize("pin", [0, 64])
