@@ -176,7 +176,8 @@ def prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, sca
 
 def tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
     """One sweep's merged read.  All per-head tensors [B,c,h,dh]; returns
-    (o [B,c,h,dh] in v_raw.dtype, lse fp32 [B,c,h])."""
+    (o [B,c,h,dh] in v_raw.dtype, lse fp32 [B,c,h], ssq fp32 [B,c,h] = sum_d o^2 per head,
+    from which the row's RMS over all heads follows without another pass over o)."""
     c = q_r.shape[1]
     s_in = torch.einsum("bchd,bjhd->bhcj", q_r, K_in).float() * scale
     s_in = s_in.masked_fill(~_intra_mask(c, window, q_r.device), NEG)
@@ -189,7 +190,8 @@ def tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
     o = torch.einsum("bhcj,bjhd->bchd", p_in.to(V_in.dtype), V_in).float()
     o = o + p_self.permute(0, 2, 1).unsqueeze(-1) * v_raw.float()
     o = o + p_c.permute(0, 2, 1).unsqueeze(-1) * o_c
-    return o.to(v_raw.dtype), lse.permute(0, 2, 1).contiguous()
+    ssq = o.square().sum(-1)                              # [B,c,h]: per-head sum of squares of the read
+    return o.to(v_raw.dtype), lse.permute(0, 2, 1).contiguous(), ssq
 
 
 def tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window=0):
@@ -243,35 +245,45 @@ def rms_bwd(dy, x, w, rstd):
 
 # ---- refine (gate, blend, rotate) ----------------------------------------------------------------
 
-def refine_fwd(cg, glx, k, v, cos, sin, h, pin_cols=0):
-    """Write law for the packed layout.
+def row_rstd(ssq, d, eps=1e-5):
+    """1/rms of each row over all heads, from the per-head sums of squares: [B,c,h] -> [B,c,1]."""
+    return torch.rsqrt(ssq.sum(-1, keepdim=True) / d + eps)
 
-    cg  [B,c,4d]: u @ W_pack^T = [k_ctx | v_ctx | gate-u logits k | gate-u logits v]
-    glx [B,c,2d]: x̂-half of the gate logits plus bias (sweep-invariant)
+
+def refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, eps=1e-5):
+    """Write law for the packed layout, with the context norm folded in.
+
+    raw [B,c,4d] = o @ W'^T where W' = W_pack * w_ctx (norm gain folded into the weight
+    columns) and o is the UN-normalised read; the row's 1/rms (from ssq [B,c,h]) is applied
+    here, so cg = rstd * raw = [k_ctx | v_ctx | gate-u logits k | gate-u logits v].
+    glx [B,c,2d]: x̂-half of the gate logits plus bias (sweep-invariant).
     k, v [B,c,d] raw (unrotated) key / value.  `pin_cols`: the first pin_cols value
     columns keep the raw value (kmod_vraw_heads * dh).
     Returns (K_out [B,c,h,dh] rotated, V_out [B,c,h,dh]) in k.dtype.
     """
     B, c, d = k.shape
+    cg = raw.float() * row_rstd(ssq, d, eps)
     kc, vc, gku, gvu = cg.split(d, dim=-1)
-    gk = torch.sigmoid(glx[..., :d].float() + gku.float())
-    gv = torch.sigmoid(glx[..., d:].float() + gvu.float())
-    kpp = gk * k.float() + (1.0 - gk) * kc.float()
-    vpp = gv * v.float() + (1.0 - gv) * vc.float()
+    gk = torch.sigmoid(glx[..., :d].float() + gku)
+    gv = torch.sigmoid(glx[..., d:].float() + gvu)
+    kpp = gk * k.float() + (1.0 - gk) * kc
+    vpp = gv * v.float() + (1.0 - gv) * vc
     if pin_cols:
         vpp = torch.cat((v[..., :pin_cols].float(), vpp[..., pin_cols:]), dim=-1)
     K_out = rope_tm(kpp.view(B, c, h, d // h), cos, sin)
     return K_out.to(k.dtype), vpp.view(B, c, h, d // h).to(k.dtype)
 
 
-def refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols=0):
-    """Backward of `refine_fwd`.  dK_out/dV_out [B,c,h,dh].  Returns fp32
-    (dcg [B,c,4d], dk [B,c,d], dv [B,c,d]); the gate-logit grads are dcg[..., 2d:]
-    (they are also the grads of glx)."""
+def refine_bwd(dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols=0, eps=1e-5):
+    """Backward of `refine_fwd`.  dK_out/dV_out [B,c,h,dh]; o [B,c,d] the read.  Returns fp32
+    (dcg [B,c,4d] = gradient w.r.t. cg = rstd*raw, dk [B,c,d], dv [B,c,d], uhat [B,c,d] = o*rstd);
+    the gate-logit grads dcg[..., 2d:] are also the grads of glx."""
     B, c, d = k.shape
+    rstd = row_rstd(ssq, d, eps)
+    cg = raw.float() * rstd
     kc, vc, gku, gvu = cg.split(d, dim=-1)
-    gk = torch.sigmoid(glx[..., :d].float() + gku.float())
-    gv = torch.sigmoid(glx[..., d:].float() + gvu.float())
+    gk = torch.sigmoid(glx[..., :d].float() + gku)
+    gv = torch.sigmoid(glx[..., d:].float() + gvu)
     dkpp = unrope_tm(dK_out.float(), cos, sin).reshape(B, c, d)
     dvpp = dV_out.float().reshape(B, c, d)
     dv_pin = None
@@ -279,14 +291,23 @@ def refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols=0):
         dv_pin = dvpp[..., :pin_cols]
         dvpp = torch.cat((torch.zeros_like(dv_pin), dvpp[..., pin_cols:]), dim=-1)
     kf, vf = k.float(), v.float()
-    dgk = dkpp * (kf - kc.float()) * gk * (1.0 - gk)
-    dgv = dvpp * (vf - vc.float()) * gv * (1.0 - gv)
+    dgk = dkpp * (kf - kc) * gk * (1.0 - gk)
+    dgv = dvpp * (vf - vc) * gv * (1.0 - gv)
     dcg = torch.cat((dkpp * (1.0 - gk), dvpp * (1.0 - gv), dgk, dgv), dim=-1)
     dk = dkpp * gk
     dv = dvpp * gv
     if pin_cols:
         dv = torch.cat((dv_pin, dv[..., pin_cols:]), dim=-1)
-    return dcg, dk, dv
+    return dcg, dk, dv, o.float() * rstd
+
+
+def rmsn_bwd(du, o, ssq, eps=1e-5):
+    """Backward of uhat = o * rstd(o) (no gain): d o = rstd * (du - uhat * mean(du * uhat)). fp32."""
+    d = o.shape[-1]
+    rstd = row_rstd(ssq, d, eps)
+    uhat = o.float() * rstd
+    duf = du.float()
+    return rstd * (duf - uhat * (duf * uhat).mean(-1, keepdim=True))
 
 
 # ---- SwiGLU pointwise ---------------------------------------------------------------------------

@@ -73,10 +73,13 @@ class _LayerPack:
                          (self.w1, blk.mlp.w1), (self.w3, blk.mlp.w3), (self.w2, blk.mlp.w2)):
             dst.copy_(src.weight)
         gk, gv = _dense(a.w_gk), _dense(a.w_gv)
-        self.W_pack[:d].copy_(a.w_kctx.weight)
-        self.W_pack[d:2 * d].copy_(a.w_vctx.weight)
-        self.W_pack[2 * d:3 * d].copy_(gk[:, d:])
-        self.W_pack[3 * d:].copy_(gv[:, d:])
+        # the context-norm gain is folded into the packed weight's columns: the sweeps feed the
+        # GEMM with the un-normalised read and apply 1/rms afterwards, row by row
+        wc = a.norm_ctx.weight.float()[None, :]
+        self.W_pack[:d].copy_(a.w_kctx.weight.float() * wc)
+        self.W_pack[d:2 * d].copy_(a.w_vctx.weight.float() * wc)
+        self.W_pack[2 * d:3 * d].copy_(gk[:, d:].float() * wc)
+        self.W_pack[3 * d:].copy_(gv[:, d:].float() * wc)
         self.W_gx[:d].copy_(gk[:, :d])
         self.W_gx[d:].copy_(gv[:, :d])
         self.b_g[:d].copy_(a.w_gk.bias)
@@ -354,11 +357,10 @@ class WaveScanEngine:
                 K_in, V_in = kself_r[:, r], v4[:, r]
                 o = None
                 for _ in range(n_sweeps):
-                    o, _ = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
-                                        o_c, lse_c, scale, self.window)
-                    u, _ = ops.rms_fwd(o.reshape(B, c, d), P.w_ctx)
-                    cg = ops.linear(u, P.W_pack)
-                    K_in, V_in = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                    o, _, ssq = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
+                                             o_c, lse_c, scale, self.window)
+                    raw = ops.linear(o.reshape(B, c, d), P.W_pack)
+                    K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
                                                 h, pin)
                 Kc[:, r] = K_in
                 Vc[:, r] = V_in
@@ -487,7 +489,6 @@ class WaveScanEngine:
             dv = torch.zeros(B, T, d, dtype=f32, device=dev)
             dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev)
             dv4 = dv.view(B, T, h, dh)
-            dw_ctx = G.get(a.norm_ctx.weight)
             # ---- cells in reverse ---------------------------------------------------------------
             saved = self._prefix_slots(sid, li)
             dcg_stash, u_stash, stash_off = self._stash_for(sid)
@@ -501,11 +502,10 @@ class WaveScanEngine:
                 st = []
                 K_in, V_in = ksc, vc4
                 for _ in range(n_sweeps):
-                    o, lse = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
-                    u, rstd = ops.rms_fwd(o.reshape(B, c, d), P.w_ctx)
-                    cg = ops.linear(u, P.W_pack)
-                    st.append((K_in, V_in, o, lse, u, rstd, cg))
-                    K_in, V_in = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                    o, lse, ssq = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
+                    raw = ops.linear(o.reshape(B, c, d), P.W_pack)
+                    st.append((K_in, V_in, o, lse, ssq, raw))
+                    K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
                                                 h, pin)
                 self.lsec_all[:, r] = lse_c
                 # gradient of this cell's committed rows from every later cell's prefix read
@@ -516,16 +516,16 @@ class WaveScanEngine:
                 dlse_c = torch.zeros_like(lse_c)
                 dq_c = torch.zeros(B, c, h, dh, dtype=f32, device=dev)
                 for s in range(n_sweeps - 1, -1, -1):
-                    K_in, V_in, o, lse, u, rstd, cg = st[s]
-                    dcg = ops.refine_bwd(dK_out, dV_out, cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
-                                         pin, dk[:, r], dv[:, r], dglx[:, r])
+                    K_in, V_in, o, lse, ssq, raw = st[s]
                     off = stash_off[(ci, s)]
-                    dcg_stash[off:off + B * c].copy_(dcg.reshape(B * c, 4 * d))
-                    u_stash[off:off + B * c].copy_(u.reshape(B * c, d))
+                    dcg = dcg_stash[off:off + B * c].view(B, c, 4 * d)
+                    ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), glx[:, r], k[:, r], v[:, r],
+                                   cos[r], sin[r], pin, dk[:, r], dv[:, r], dglx[:, r], dcg,
+                                   u_stash[off:off + B * c].view(B, c, d))
                     du = ops.linear_dx(dcg, P.W_pack)
-                    d_o = ops.rms_bwd(du, o.reshape(B, c, d), P.w_ctx, rstd, dw_ctx,
-                                      residual=d_o.view(B, c, d) if s == n_sweeps - 1 else None
-                                      ).view(B, c, h, dh)
+                    d_o = ops.rmsn_bwd(du, o.reshape(B, c, d), ssq,
+                                       residual=d_o.view(B, c, d) if s == n_sweeps - 1 else None
+                                       ).view(B, c, h, dh)
                     dK_out, dV_out = ops.tail_bwd(
                         d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
                         dq_c, dks_r[:, r], dv4[:, r], do_c, dlse_c)
@@ -539,6 +539,7 @@ class WaveScanEngine:
                 dq_r[:, r] = dq_c
                 self.stats["bwd_cells"] += 1
             ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
+            self._unfold_packed_grad(a)
             # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
             dq = ops.unrope(dq_r, cos, sin).reshape(B, T, d).to(act)
             dk_t = (dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)).to(act)
@@ -556,6 +557,15 @@ class WaveScanEngine:
             self.dx_cur.copy_(ops.rms_bwd(dxhat, x, P.w_an, rstd_a, G.get(blk.attn_norm.weight),
                                           residual=dx_mid, out_dtype=act))
             self._scatter_packed_grads(a, db_g)
+
+    def _unfold_packed_grad(self, a):
+        """dW_pack holds the gradient of the FOLDED weight W' = W * w_ctx (per column).  Recover
+        d w_ctx = sum_rows dW' * W and dW = dW' * w_ctx."""
+        d = self.cfg.d_model
+        gk, gv = _dense(a.w_gk), _dense(a.w_gv)
+        W = torch.cat((a.w_kctx.weight, a.w_vctx.weight, gk[:, d:], gv[:, d:]), dim=0).float()
+        self.grads.get(a.norm_ctx.weight).add_((self.dW_pack * W).sum(0))
+        self.dW_pack.mul_(a.norm_ctx.weight.float()[None, :])
 
     def _scatter_packed_grads(self, a, db_g):
         """Route the packed-weight gradients of one layer to the parameters."""

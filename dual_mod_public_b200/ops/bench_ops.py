@@ -97,7 +97,7 @@ def main():
     qc, ksc, vrc = q[:, r], ks[:, r], vr[:, r]
     K_in, V_in = rnd(B, c, h, dh), rnd(B, c, h, dh)
     o_c, lse_c = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, 0)
-    o, lse = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)
+    o, lse, ssq = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)
     z = lambda *s: torch.zeros(*s, device=DEV)
     att_f = 4.0 * B * h * c * dh          # flops per key for QK^T + PV
     if want("prefix_fwd"):
@@ -127,13 +127,17 @@ def main():
     cg, glx, k, v = rnd(B, c, 4 * d), rnd(B, Tlen, 2 * d), rnd(B, Tlen, d), rnd(B, Tlen, d)
     N = B * c
     if want("refine_fwd"):
-        report("refine_fwd", T(lambda: ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, 0)),
+        report("refine_fwd", T(lambda: ops.refine_fwd(cg, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, 0)),
                bytes_=N * d * 2 * 10)
     dK, dV = rnd(B, c, h, dh, dtype=torch.float32), rnd(B, c, h, dh, dtype=torch.float32)
     dk_a, dv_a, dg_a = z(B, Tlen, d), z(B, Tlen, d), z(B, Tlen, 2 * d)
     if want("refine_bwd"):
-        report("refine_bwd", T(lambda: ops.refine_bwd(dK, dV, cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], 0,
-                                                      dk_a[:, r], dv_a[:, r], dg_a[:, r])), bytes_=N * d * 64)
+        dcg_o, uh_o, o2 = torch.empty_like(cg), rnd(B, c, d), o.reshape(B, c, d)
+        report("refine_bwd", T(lambda: ops.refine_bwd(dK, dV, cg, ssq, o2, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], 0,
+                                                      dk_a[:, r], dv_a[:, r], dg_a[:, r], dcg_o, uh_o)),
+               bytes_=N * d * 68)
+        du = rnd(B, c, d)
+        report("rmsn_bwd", T(lambda: ops.rmsn_bwd(du, o2, ssq)), bytes_=N * d * 8)
     x2, w = rnd(N, d), rnd(d) + 1
     if want("rms_fwd"):
         report("rms_fwd", T(lambda: ops.rms_fwd(x2, w)), bytes_=N * d * 4)

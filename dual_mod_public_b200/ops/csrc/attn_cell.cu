@@ -19,8 +19,8 @@ __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ ks, TView vks,
     const bf16* __restrict__ vr, TView vvr, const bf16* __restrict__ Kin, TView vKin,
     const bf16* __restrict__ Vin, TView vVin, const float* __restrict__ o_c,
-    const float* __restrict__ lse_c, bf16* __restrict__ o, float* __restrict__ lse, int H,
-    float scale, int window) {
+    const float* __restrict__ lse_c, bf16* __restrict__ o, float* __restrict__ lse,
+    float* __restrict__ ssq, int H, float scale, int window) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = C / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
   const float* oc1 = o_c + orow1 * DH;
   bf16* out0 = o + orow0 * DH;
   bf16* out1 = o + orow1 * DH;
+  float sq0 = 0.f, sq1 = 0.f;
 #pragma unroll
   for (int n = 0; n < DH / 8; ++n) {
     int d = n * 8 + 2 * t;
@@ -121,14 +122,20 @@ __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
     float2 v1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(vr1 + d));
     float2 c0 = *reinterpret_cast<const float2*>(oc0 + d);
     float2 c1 = *reinterpret_cast<const float2*>(oc1 + d);
-    *reinterpret_cast<bf162*>(out0 + d) = __floats2bfloat162_rn(
-        (O[n][0] + es0 * v0.x + ec0 * c0.x) * r0, (O[n][1] + es0 * v0.y + ec0 * c0.y) * r0);
-    *reinterpret_cast<bf162*>(out1 + d) = __floats2bfloat162_rn(
-        (O[n][2] + es1 * v1.x + ec1 * c1.x) * r1, (O[n][3] + es1 * v1.y + ec1 * c1.y) * r1);
+    const float a0 = (O[n][0] + es0 * v0.x + ec0 * c0.x) * r0, a1 = (O[n][1] + es0 * v0.y + ec0 * c0.y) * r0;
+    const float b0 = (O[n][2] + es1 * v1.x + ec1 * c1.x) * r1, b1 = (O[n][3] + es1 * v1.y + ec1 * c1.y) * r1;
+    sq0 += a0 * a0 + a1 * a1;
+    sq1 += b0 * b0 + b1 * b1;
+    *reinterpret_cast<bf162*>(out0 + d) = __floats2bfloat162_rn(a0, a1);
+    *reinterpret_cast<bf162*>(out1 + d) = __floats2bfloat162_rn(b0, b1);
   }
+  sq0 = quad_sum(sq0);
+  sq1 = quad_sum(sq1);
   if (t == 0) {
     lse[orow0] = m0 + __logf(z0);
     lse[orow1] = m1 + __logf(z1);
+    ssq[orow0] = sq0;      // per-head sum of squares of the read: the row norm needs no pass over o
+    ssq[orow1] = sq1;
   }
 }
 
@@ -479,15 +486,15 @@ extern "C" {
 
 int dmb_tail_fwd(const void* q, TView vq, const void* ks, TView vks, const void* vr, TView vvr,
                  const void* Kin, TView vKin, const void* Vin, TView vVin, const float* o_c,
-                 const float* lse_c, void* o, float* lse, int B, int c, int H, int dh, float scale,
-                 int window, cudaStream_t st) {
+                 const float* lse_c, void* o, float* lse, float* ssq, int B, int c, int H, int dh,
+                 float scale, int window, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = (size_t)3 * C * Tile<DH>::PITCH * sizeof(bf16);
     auto kern = tail_fwd_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr, vvr,
                                          (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c, lse_c,
-                                         (bf16*)o, lse, H, scale, window);
+                                         (bf16*)o, lse, ssq, H, scale, window);
   })
   DMB_CHECK_LAUNCH();
   return 0;

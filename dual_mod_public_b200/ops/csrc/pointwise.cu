@@ -1,4 +1,4 @@
-// Bandwidth-bound fused kernels: RMSNorm fwd/bwd, RoPE, the refine write law fwd/bwd, SwiGLU
+// Bandwidth-bound fused kernels: RMSNorm fwd/bwd, RoPE, SwiGLU
 // fwd/bwd, the cross-entropy slab (loss + d logits) and column reductions.  All activations are
 // bf16, all statistics and gradients of parameters fp32.
 #include <stdio.h>
@@ -130,100 +130,6 @@ __global__ void rope_kernel(const TI* __restrict__ x, long long bs, long long rs
   float a = lo * c - hi * s, bb = hi * c + lo * s;
   if constexpr (sizeof(TO) == 4) { out[o + p] = a; out[o + p + half] = bb; }
   else { out[o + p] = __float2bfloat16(a); out[o + p + half] = __float2bfloat16(bb); }
-}
-
-// ---- refine: gates, convex blend, rotate-at-write -------------------------------------------------------
-// per row: cg [4d] = [k_ctx | v_ctx | gk_u | gv_u] (contiguous), glx [2d] (strided), k, v [d] (strided).
-// One thread handles the rotation pair (p, p+half) of one head for both K and V.
-__global__ void refine_fwd_kernel(const bf16* __restrict__ cg, const bf16* __restrict__ glx, TView vg,
-                                  const bf16* __restrict__ k, TView vk, const bf16* __restrict__ v,
-                                  TView vv, const float* __restrict__ cosb, const float* __restrict__ sinb,
-                                  bf16* __restrict__ Kout, bf16* __restrict__ Vout, int B, int C, int H,
-                                  int DH, int pin_cols) {
-  const int half = DH >> 1, d = H * DH;
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  long long total = (long long)B * C * H * half;
-  if (i >= total) return;
-  int p = i % half;
-  long long r = i / half;
-  int h = r % H;
-  r /= H;
-  int t = r % C, b = r / C;
-  const long long row = (long long)b * C + t;
-  const bf16* cgr = cg + row * 4 * d;
-  const bf16* gr = glx + b * vg.bs + t * vg.rs;
-  const bf16* kr = k + b * vk.bs + t * vk.rs;
-  const bf16* vr = v + b * vv.bs + t * vv.rs;
-  const float c = cosb[t * half + p], s = sinb[t * half + p];
-  float kk[2], vo[2];
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    int col = h * DH + p + e * half;
-    float gk = sigmoidf_(__bfloat162float(gr[col]) + __bfloat162float(cgr[2 * d + col]));
-    float gv = sigmoidf_(__bfloat162float(gr[d + col]) + __bfloat162float(cgr[3 * d + col]));
-    float kraw = __bfloat162float(kr[col]), vraw = __bfloat162float(vr[col]);
-    kk[e] = gk * kraw + (1.f - gk) * __bfloat162float(cgr[col]);
-    vo[e] = col < pin_cols ? vraw : gv * vraw + (1.f - gv) * __bfloat162float(cgr[d + col]);
-  }
-  long long o = row * d + h * DH + p;
-  Kout[o] = __float2bfloat16(kk[0] * c - kk[1] * s);
-  Kout[o + half] = __float2bfloat16(kk[1] * c + kk[0] * s);
-  Vout[o] = __float2bfloat16(vo[0]);
-  Vout[o + half] = __float2bfloat16(vo[1]);
-}
-
-// backward: dK_out/dV_out fp32 contiguous [B,C,H,DH]; writes dcg bf16 [B,C,4d]; accumulates
-// dk_acc / dv_acc [.., d] and dglx_acc [.., 2d] (fp32, strided) with +=.
-__global__ void refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV,
-                                  const bf16* __restrict__ cg, const bf16* __restrict__ glx, TView vg,
-                                  const bf16* __restrict__ k, TView vk, const bf16* __restrict__ v,
-                                  TView vv, const float* __restrict__ cosb, const float* __restrict__ sinb,
-                                  bf16* __restrict__ dcg, float* __restrict__ dk_acc, TView vdk,
-                                  float* __restrict__ dv_acc, TView vdv, float* __restrict__ dglx_acc,
-                                  TView vdg, int B, int C, int H, int DH, int pin_cols) {
-  const int half = DH >> 1, d = H * DH;
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  long long total = (long long)B * C * H * half;
-  if (i >= total) return;
-  int p = i % half;
-  long long r = i / half;
-  int h = r % H;
-  r /= H;
-  int t = r % C, b = r / C;
-  const long long row = (long long)b * C + t;
-  const bf16* cgr = cg + row * 4 * d;
-  bf16* dcr = dcg + row * 4 * d;
-  const bf16* gr = glx + b * vg.bs + t * vg.rs;
-  const bf16* kr = k + b * vk.bs + t * vk.rs;
-  const bf16* vr = v + b * vv.bs + t * vv.rs;
-  float* dkr = dk_acc + b * vdk.bs + t * vdk.rs;
-  float* dvr = dv_acc + b * vdv.bs + t * vdv.rs;
-  float* dgr = dglx_acc + b * vdg.bs + t * vdg.rs;
-  const float c = cosb[t * half + p], s = sinb[t * half + p];
-  long long o = row * d + h * DH + p;
-  const float a = dK[o], bb = dK[o + half];
-  float dkpp[2] = {a * c + bb * s, bb * c - a * s};  // transpose of the rotation
-  float dvpp[2] = {dV[o], dV[o + half]};
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    int col = h * DH + p + e * half;
-    float gk = sigmoidf_(__bfloat162float(gr[col]) + __bfloat162float(cgr[2 * d + col]));
-    float gv = sigmoidf_(__bfloat162float(gr[d + col]) + __bfloat162float(cgr[3 * d + col]));
-    float kraw = __bfloat162float(kr[col]), vraw = __bfloat162float(vr[col]);
-    float kc = __bfloat162float(cgr[col]), vc = __bfloat162float(cgr[d + col]);
-    bool pinned = col < pin_cols;
-    float dvp = pinned ? 0.f : dvpp[e];
-    float dgk = dkpp[e] * (kraw - kc) * gk * (1.f - gk);
-    float dgv = dvp * (vraw - vc) * gv * (1.f - gv);
-    dcr[col] = __float2bfloat16(dkpp[e] * (1.f - gk));
-    dcr[d + col] = __float2bfloat16(dvp * (1.f - gv));
-    dcr[2 * d + col] = __float2bfloat16(dgk);
-    dcr[3 * d + col] = __float2bfloat16(dgv);
-    dkr[col] += dkpp[e] * gk;
-    dvr[col] += pinned ? dvpp[e] : dvp * gv;
-    dgr[col] += dgk;
-    dgr[d + col] += dgv;
-  }
 }
 
 // ---- SwiGLU ---------------------------------------------------------------------------------------------------
@@ -409,29 +315,6 @@ int dmb_rope(const void* x, int in_f32, long long bs, long long rs, const float*
     rope_kernel<bf16, float><<<grid, blk, 0, st>>>((const bf16*)x, bs, rs, cosb, sinb, (float*)out, B, T, H, DH, sign);
   else
     rope_kernel<bf16, bf16><<<grid, blk, 0, st>>>((const bf16*)x, bs, rs, cosb, sinb, (bf16*)out, B, T, H, DH, sign);
-  DMB_CHECK_LAUNCH();
-  return 0;
-}
-
-int dmb_refine_fwd(const void* cg, const void* glx, TView vg, const void* k, TView vk, const void* v,
-                   TView vv, const float* cosb, const float* sinb, void* Kout, void* Vout, int B, int C,
-                   int H, int DH, int pin_cols, cudaStream_t st) {
-  long long total = (long long)B * C * H * (DH / 2);
-  refine_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-      (const bf16*)cg, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv, cosb, sinb,
-      (bf16*)Kout, (bf16*)Vout, B, C, H, DH, pin_cols);
-  DMB_CHECK_LAUNCH();
-  return 0;
-}
-
-int dmb_refine_bwd(const float* dK, const float* dV, const void* cg, const void* glx, TView vg,
-                   const void* k, TView vk, const void* v, TView vv, const float* cosb, const float* sinb,
-                   void* dcg, float* dk_acc, TView vdk, float* dv_acc, TView vdv, float* dglx_acc,
-                   TView vdg, int B, int C, int H, int DH, int pin_cols, cudaStream_t st) {
-  long long total = (long long)B * C * H * (DH / 2);
-  refine_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-      dK, dV, (const bf16*)cg, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv, cosb, sinb,
-      (bf16*)dcg, dk_acc, vdk, dv_acc, vdv, dglx_acc, vdg, B, C, H, DH, pin_cols);
   DMB_CHECK_LAUNCH();
   return 0;
 }

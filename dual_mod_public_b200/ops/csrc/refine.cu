@@ -1,0 +1,254 @@
+// The Dual-Mod write law, forward and backward, fused into one pass over a chunk's rows.
+//
+// Inputs per row: raw[4d] = o @ W'^T (W' = packed ctx/gate weights with the context-norm gain
+// folded into their columns, o the UN-normalised read), ssq[H] = per-head sums of squares of o
+// (so rstd = rsqrt(sum(ssq)/d + eps) needs no pass over o), glx[2d] = x-half of the gate logits
+// + bias, raw key k[d] and value v[d].  With cg = rstd * raw = [k_ctx | v_ctx | gk_u | gv_u]:
+//   g = sigmoid(glx + g_u);  k'' = g_k k + (1-g_k) k_ctx;  v'' = g_v v + (1-g_v) v_ctx
+//   K_out = RoPE(k'') (rotated once, at write), V_out = v'' (first pin_cols columns keep raw v).
+// One thread owns 8 adjacent rotation pairs of one head: columns [c0, c0+8) and [c0+half, ..+8),
+// so every access is a 16-byte vector.
+#include "common.cuh"
+
+namespace {
+
+struct V8 {
+  float x[8];
+};
+__device__ __forceinline__ V8 ld8(const bf16* p) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  return V8{{a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y}};
+}
+__device__ __forceinline__ void st8(bf16* p, const V8& v) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(v.x[0], v.x[1]), pack_bf16(v.x[2], v.x[3]),
+                                            pack_bf16(v.x[4], v.x[5]), pack_bf16(v.x[6], v.x[7]));
+}
+__device__ __forceinline__ V8 ld8f(const float* p) {
+  float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  return V8{{a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w}};
+}
+__device__ __forceinline__ void st8f(float* p, const V8& v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v.x[0], v.x[1], v.x[2], v.x[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v.x[4], v.x[5], v.x[6], v.x[7]);
+}
+__device__ __forceinline__ void acc8f(float* p, const V8& v) {
+  V8 o = ld8f(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o.x[i] += v.x[i];
+  st8f(p, o);
+}
+__device__ __forceinline__ float row_rstd(const float* ssq_row, int H, int d, float eps) {
+  float s = 0.f;
+  for (int i = 0; i < H; i += 4) {
+    float4 v = *reinterpret_cast<const float4*>(ssq_row + i);
+    s += v.x + v.y + v.z + v.w;
+  }
+  return rsqrtf(s / d + eps);
+}
+
+struct Where {
+  long long row;   // b * C + t
+  int b, t, c0, c1; // chunk-local position and this thread's two column bases
+  int p0;          // first rotation pair index inside the head
+};
+__device__ __forceinline__ bool locate(Where& w, long long i, int B, int C, int H, int DH) {
+  const int half = DH >> 1, per_head = half >> 3;   // threads per head
+  const long long total = (long long)B * C * H * per_head;
+  if (i >= total) return false;
+  const int q = i % per_head;
+  long long r = i / per_head;
+  const int h = r % H;
+  r /= H;
+  w.t = r % C;
+  w.b = r / C;
+  w.row = (long long)w.b * C + w.t;
+  w.p0 = q * 8;
+  w.c0 = h * DH + w.p0;
+  w.c1 = w.c0 + half;
+  return true;
+}
+
+__global__ void refine_fwd_kernel(const bf16* __restrict__ raw, const float* __restrict__ ssq,
+                                  const bf16* __restrict__ glx, TView vg, const bf16* __restrict__ k, TView vk,
+                                  const bf16* __restrict__ v, TView vv, const float* __restrict__ cosb,
+                                  const float* __restrict__ sinb, bf16* __restrict__ Kout,
+                                  bf16* __restrict__ Vout, int B, int C, int H, int DH, int pin_cols, float eps) {
+  Where w;
+  if (!locate(w, (long long)blockIdx.x * blockDim.x + threadIdx.x, B, C, H, DH)) return;
+  const int d = H * DH, half = DH >> 1;
+  const float rs = row_rstd(ssq + w.row * H, H, d, eps);
+  const bf16* rr = raw + w.row * 4 * d;
+  const bf16* gr = glx + w.b * vg.bs + w.t * vg.rs;
+  const bf16* kr = k + w.b * vk.bs + w.t * vk.rs;
+  const bf16* vr = v + w.b * vv.bs + w.t * vv.rs;
+  const V8 cs = ld8f(cosb + w.t * half + w.p0), sn = ld8f(sinb + w.t * half + w.p0);
+  V8 kk[2], vo[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int col = e ? w.c1 : w.c0;
+    const V8 kc = ld8(rr + col), vc = ld8(rr + d + col), gku = ld8(rr + 2 * d + col), gvu = ld8(rr + 3 * d + col);
+    const V8 gxk = ld8(gr + col), gxv = ld8(gr + d + col), kraw = ld8(kr + col), vraw = ld8(vr + col);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float gk = sigmoidf_(gxk.x[i] + rs * gku.x[i]), gv = sigmoidf_(gxv.x[i] + rs * gvu.x[i]);
+      kk[e].x[i] = gk * kraw.x[i] + (1.f - gk) * rs * kc.x[i];
+      vo[e].x[i] = (col + i < pin_cols) ? vraw.x[i] : gv * vraw.x[i] + (1.f - gv) * rs * vc.x[i];
+    }
+  }
+  V8 k0, k1;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    k0.x[i] = kk[0].x[i] * cs.x[i] - kk[1].x[i] * sn.x[i];
+    k1.x[i] = kk[1].x[i] * cs.x[i] + kk[0].x[i] * sn.x[i];
+  }
+  const long long o = w.row * d;
+  st8(Kout + o + w.c0, k0);
+  st8(Kout + o + w.c1, k1);
+  st8(Vout + o + w.c0, vo[0]);
+  st8(Vout + o + w.c1, vo[1]);
+}
+
+// dK / dV fp32 dense [B,C,H,DH]; writes dcg (bf16 [rows,4d], gradient w.r.t. cg = rstd*raw) and
+// uhat = o * rstd (bf16 [rows,d]); accumulates dk_acc / dv_acc [.., d] and dglx_acc [.., 2d] (fp32, +=).
+__global__ void refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV,
+                                  const bf16* __restrict__ raw, const float* __restrict__ ssq,
+                                  const bf16* __restrict__ o, const bf16* __restrict__ glx, TView vg,
+                                  const bf16* __restrict__ k, TView vk, const bf16* __restrict__ v, TView vv,
+                                  const float* __restrict__ cosb, const float* __restrict__ sinb,
+                                  bf16* __restrict__ dcg, bf16* __restrict__ uhat, float* __restrict__ dk_acc,
+                                  TView vdk, float* __restrict__ dv_acc, TView vdv, float* __restrict__ dglx_acc,
+                                  TView vdg, int B, int C, int H, int DH, int pin_cols, float eps) {
+  Where w;
+  if (!locate(w, (long long)blockIdx.x * blockDim.x + threadIdx.x, B, C, H, DH)) return;
+  const int d = H * DH, half = DH >> 1;
+  const float rs = row_rstd(ssq + w.row * H, H, d, eps);
+  const bf16* rr = raw + w.row * 4 * d;
+  bf16* dr = dcg + w.row * 4 * d;
+  const bf16* gr = glx + w.b * vg.bs + w.t * vg.rs;
+  const bf16* kr = k + w.b * vk.bs + w.t * vk.rs;
+  const bf16* vr = v + w.b * vv.bs + w.t * vv.rs;
+  float* dkr = dk_acc + w.b * vdk.bs + w.t * vdk.rs;
+  float* dvr = dv_acc + w.b * vdv.bs + w.t * vdv.rs;
+  float* dgr = dglx_acc + w.b * vdg.bs + w.t * vdg.rs;
+  const V8 cs = ld8f(cosb + w.t * half + w.p0), sn = ld8f(sinb + w.t * half + w.p0);
+  const long long ob = w.row * d;
+  const V8 a = ld8f(dK + ob + w.c0), bq = ld8f(dK + ob + w.c1);
+  V8 dkpp[2], dvpp[2] = {ld8f(dV + ob + w.c0), ld8f(dV + ob + w.c1)};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {            // transpose of the rotation
+    dkpp[0].x[i] = a.x[i] * cs.x[i] + bq.x[i] * sn.x[i];
+    dkpp[1].x[i] = bq.x[i] * cs.x[i] - a.x[i] * sn.x[i];
+  }
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int col = e ? w.c1 : w.c0;
+    const V8 kc = ld8(rr + col), vc = ld8(rr + d + col), gku = ld8(rr + 2 * d + col), gvu = ld8(rr + 3 * d + col);
+    const V8 gxk = ld8(gr + col), gxv = ld8(gr + d + col), kraw = ld8(kr + col), vraw = ld8(vr + col);
+    const V8 ov = ld8(o + ob + col);
+    V8 dkc, dvc, dgk, dgv, dkk, dvv, uh;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float gk = sigmoidf_(gxk.x[i] + rs * gku.x[i]), gv = sigmoidf_(gxv.x[i] + rs * gvu.x[i]);
+      const bool pinned = col + i < pin_cols;
+      const float dvp = pinned ? 0.f : dvpp[e].x[i];
+      dgk.x[i] = dkpp[e].x[i] * (kraw.x[i] - rs * kc.x[i]) * gk * (1.f - gk);
+      dgv.x[i] = dvp * (vraw.x[i] - rs * vc.x[i]) * gv * (1.f - gv);
+      dkc.x[i] = dkpp[e].x[i] * (1.f - gk);
+      dvc.x[i] = dvp * (1.f - gv);
+      dkk.x[i] = dkpp[e].x[i] * gk;
+      dvv.x[i] = pinned ? dvpp[e].x[i] : dvp * gv;
+      uh.x[i] = ov.x[i] * rs;
+    }
+    st8(dr + col, dkc);
+    st8(dr + d + col, dvc);
+    st8(dr + 2 * d + col, dgk);
+    st8(dr + 3 * d + col, dgv);
+    st8(uhat + ob + col, uh);
+    acc8f(dkr + col, dkk);
+    acc8f(dvr + col, dvv);
+    acc8f(dgr + col, dgk);
+    acc8f(dgr + d + col, dgv);
+  }
+}
+
+// d o of uhat = o * rstd (no gain): out = residual + rstd * (du - uhat * mean(du * uhat)); warp per row
+template <typename TOUT>
+__global__ void rmsn_bwd_kernel(const bf16* __restrict__ du, const bf16* __restrict__ o,
+                                const float* __restrict__ ssq, const TOUT* __restrict__ residual,
+                                TOUT* __restrict__ out, int rows, int d, int H, float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float rs = row_rstd(ssq + (long long)row * H, H, d, eps);
+  const bf16* dur = du + (long long)row * d;
+  const bf16* orow = o + (long long)row * d;
+  float acc = 0.f;
+  for (int c = lane * 8; c < d; c += 256) {
+    const V8 g = ld8(dur + c), x = ld8(orow + c);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += g.x[i] * x.x[i];
+  }
+  const float mean = warp_sum(acc) * rs / d;     // mean(du * uhat)
+  for (int c = lane * 8; c < d; c += 256) {
+    const V8 g = ld8(dur + c), x = ld8(orow + c);
+    V8 r;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.x[i] = rs * (g.x[i] - x.x[i] * rs * mean);
+    const long long off = (long long)row * d + c;
+    if constexpr (sizeof(TOUT) == 4) {
+      if (residual) { V8 q = ld8f((const float*)residual + off);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.x[i] += q.x[i]; }
+      st8f((float*)out + off, r);
+    } else {
+      if (residual) { V8 q = ld8((const bf16*)residual + off);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.x[i] += q.x[i]; }
+      st8((bf16*)out + off, r);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int dmb_refine_fwd(const void* raw, const float* ssq, const void* glx, TView vg, const void* k, TView vk,
+                   const void* v, TView vv, const float* cosb, const float* sinb, void* Kout, void* Vout, int B,
+                   int C, int H, int DH, int pin_cols, float eps, cudaStream_t st) {
+  if (DH % 16 || H % 4) return -1;
+  long long total = (long long)B * C * H * (DH / 16);
+  refine_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+      (const bf16*)raw, ssq, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv, cosb, sinb,
+      (bf16*)Kout, (bf16*)Vout, B, C, H, DH, pin_cols, eps);
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+int dmb_refine_bwd(const float* dK, const float* dV, const void* raw, const float* ssq, const void* o,
+                   const void* glx, TView vg, const void* k, TView vk, const void* v, TView vv, const float* cosb,
+                   const float* sinb, void* dcg, void* uhat, float* dk_acc, TView vdk, float* dv_acc, TView vdv,
+                   float* dglx_acc, TView vdg, int B, int C, int H, int DH, int pin_cols, float eps,
+                   cudaStream_t st) {
+  if (DH % 16 || H % 4) return -1;
+  long long total = (long long)B * C * H * (DH / 16);
+  refine_bwd_kernel<<<(unsigned)((total + 127) / 128), 128, 0, st>>>(
+      dK, dV, (const bf16*)raw, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv,
+      cosb, sinb, (bf16*)dcg, (bf16*)uhat, dk_acc, vdk, dv_acc, vdv, dglx_acc, vdg, B, C, H, DH, pin_cols, eps);
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+int dmb_rmsn_bwd(const void* du, const void* o, const float* ssq, const void* residual, void* out, int out_f32,
+                 int rows, int d, int H, float eps, cudaStream_t st) {
+  if (d % 8 || H % 4) return -1;
+  dim3 grid((rows + 7) / 8), blk(256);
+  if (out_f32)
+    rmsn_bwd_kernel<float><<<grid, blk, 0, st>>>((const bf16*)du, (const bf16*)o, ssq, (const float*)residual, (float*)out, rows, d, H, eps);
+  else
+    rmsn_bwd_kernel<bf16><<<grid, blk, 0, st>>>((const bf16*)du, (const bf16*)o, ssq, (const bf16*)residual, (bf16*)out, rows, d, H, eps);
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

@@ -50,13 +50,14 @@ class _Sigs:
     dmb_rms_bwd_dx = [_p, _i, _p, _ll, _p, _p, _p, _p, _i, _i, _i, _p]
     dmb_col_reduce_acc = [_p, _i, _p, _ll, _p, _p, _i, _p, _i, _i, _p]
     dmb_rope = [_p, _i, _ll, _ll, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]
-    dmb_refine_fwd = [_p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]
-    dmb_refine_bwd = [_p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _v, _p, _v, _p, _v,
-                      _i, _i, _i, _i, _i, _p]
+    dmb_refine_fwd = [_p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]
+    dmb_refine_bwd = [_p, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
+                      _i, _i, _i, _i, _i, _f, _p]
+    dmb_rmsn_bwd = [_p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p]
     dmb_swiglu_fwd = [_p, _p, _p, _ll, _p]
     dmb_swiglu_bwd = [_p, _p, _p, _p, _p, _ll, _p]
     dmb_ce = [_p, _p, _p, _p, _p, _i, _i, _p]
-    dmb_tail_fwd = [_p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
+    dmb_tail_fwd = [_p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
     dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _v, _p, _v,
                     _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
     dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
@@ -287,13 +288,14 @@ class CudaOps(TorchOps):
         B, c, h, dh = q_r.shape
         o = torch.empty(B, c, h, dh, dtype=BF16, device=q_r.device)
         lse = torch.empty(B, c, h, dtype=F32, device=q_r.device)
+        ssq = torch.empty(B, c, h, dtype=F32, device=q_r.device)
         o_c, lse_c = o_c.contiguous(), lse_c.contiguous()
         self._ck(self.lib.dmb_tail_fwd(q_r.data_ptr(), _tv(q_r), kself_r.data_ptr(), _tv(kself_r),
                                        v_raw.data_ptr(), _tv(v_raw), K_in.data_ptr(), _tv(K_in),
                                        V_in.data_ptr(), _tv(V_in), o_c.data_ptr(), lse_c.data_ptr(),
-                                       o.data_ptr(), lse.data_ptr(), B, c, h, dh, scale, window,
+                                       o.data_ptr(), lse.data_ptr(), ssq.data_ptr(), B, c, h, dh, scale, window,
                                        self._st()), "tail_fwd")
-        return o, lse
+        return o, lse, ssq
 
     def tail_bwd(self, dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window,
                  dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
@@ -315,35 +317,54 @@ class CudaOps(TorchOps):
             dK_in.data_ptr(), dV_in.data_ptr(), B, c, h, dh, scale, window, self._st()), "tail_bwd")
         return dK_in, dV_in
 
-    def refine_fwd(self, cg, glx, k, v, cos, sin, h, pin_cols=0):
+    def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0):
         B, c, d = k.shape
-        ok = (k.dtype == BF16 and cg.is_contiguous() and cos.is_contiguous()
+        dh = d // h
+        ok = (k.dtype == BF16 and raw.dtype == BF16 and raw.is_contiguous() and cos.is_contiguous()
+              and ssq.is_contiguous() and dh % 16 == 0 and h % 4 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v)))
         if not ok:
-            return super().refine_fwd(cg, glx, k, v, cos, sin, h, pin_cols)
-        dh = d // h
+            return super().refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols)
         K_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
         V_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
-        self._ck(self.lib.dmb_refine_fwd(cg.data_ptr(), glx.data_ptr(), _tv(glx), k.data_ptr(), _tv(k),
-                                         v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
-                                         K_out.data_ptr(), V_out.data_ptr(), B, c, h, dh, pin_cols,
+        self._ck(self.lib.dmb_refine_fwd(raw.data_ptr(), ssq.data_ptr(), glx.data_ptr(), _tv(glx), k.data_ptr(),
+                                         _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
+                                         K_out.data_ptr(), V_out.data_ptr(), B, c, h, dh, pin_cols, 1e-5,
                                          self._st()), "refine_fwd")
         return K_out, V_out
 
-    def refine_bwd(self, dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc):
+    def refine_bwd(self, dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc,
+                   dcg_out, uhat_out):
         B, c, d = k.shape
-        ok = (k.dtype == BF16 and dK_out.dtype == F32 and dK_out.is_contiguous()
-              and dV_out.dtype == F32 and dV_out.is_contiguous() and cg.is_contiguous()
-              and cos.is_contiguous()
+        h = dK_out.shape[2]
+        dh = d // h
+        ok = (k.dtype == BF16 and raw.dtype == BF16 and o.dtype == BF16 and dK_out.dtype == F32
+              and dV_out.dtype == F32 and dK_out.is_contiguous() and dV_out.is_contiguous()
+              and raw.is_contiguous() and o.is_contiguous() and ssq.is_contiguous() and cos.is_contiguous()
+              and dcg_out.is_contiguous() and uhat_out.is_contiguous() and dcg_out.dtype == BF16
+              and dh % 16 == 0 and h % 4 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v, dk_acc, dv_acc, dglx_acc)))
         if not ok:
-            return super().refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols, dk_acc,
-                                      dv_acc, dglx_acc)
-        h = dK_out.shape[2]
-        dcg = torch.empty(B, c, 4 * d, dtype=BF16, device=k.device)
+            return super().refine_bwd(dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc,
+                                      dglx_acc, dcg_out, uhat_out)
         self._ck(self.lib.dmb_refine_bwd(
-            dK_out.data_ptr(), dV_out.data_ptr(), cg.data_ptr(), glx.data_ptr(), _tv(glx), k.data_ptr(),
-            _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(), dcg.data_ptr(),
-            dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(), _tv(dv_acc), dglx_acc.data_ptr(),
-            _tv(dglx_acc), B, c, h, d // h, pin_cols, self._st()), "refine_bwd")
-        return dcg
+            dK_out.data_ptr(), dV_out.data_ptr(), raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), glx.data_ptr(),
+            _tv(glx), k.data_ptr(), _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
+            dcg_out.data_ptr(), uhat_out.data_ptr(), dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(),
+            _tv(dv_acc), dglx_acc.data_ptr(), _tv(dglx_acc), B, c, h, dh, pin_cols, 1e-5, self._st()),
+            "refine_bwd")
+
+    def rmsn_bwd(self, du, o, ssq, residual=None, out_dtype=F32):
+        d = o.shape[-1]
+        h = ssq.shape[-1]
+        ok = (du.dtype == BF16 and o.dtype == BF16 and du.is_contiguous() and o.is_contiguous()
+              and ssq.is_contiguous() and d % 8 == 0 and h % 4 == 0 and out_dtype in (BF16, F32)
+              and (residual is None or (residual.is_contiguous() and residual.dtype == out_dtype)))
+        if not ok:
+            return super().rmsn_bwd(du, o, ssq, residual, out_dtype)
+        rows = o.numel() // d
+        out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+        self._ck(self.lib.dmb_rmsn_bwd(du.data_ptr(), o.data_ptr(), ssq.data_ptr(),
+                                       residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                       int(out_dtype == F32), rows, d, h, 1e-5, self._st()), "rmsn_bwd")
+        return out

@@ -92,18 +92,28 @@ class TorchOps:
         dlsec_acc += dlse
         return dK_in, dV_in
 
-    def refine_fwd(self, cg, glx, k, v, cos, sin, h, pin_cols=0):
-        return fm.refine_fwd(cg, glx, k, v, cos, sin, h, pin_cols)
+    def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0):
+        return fm.refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols)
 
-    def refine_bwd(self, dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc):
-        """Accumulates dk_acc / dv_acc [B,c,d] and dglx_acc [B,c,2d] (fp32, +=); returns dcg
-        [B,c,4d] in the activation dtype."""
-        dcg, dk, dv = fm.refine_bwd(dK_out, dV_out, cg, glx, k, v, cos, sin, pin_cols)
+    def refine_bwd(self, dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc,
+                   dcg_out, uhat_out):
+        """Accumulates dk_acc / dv_acc [B,c,d] and dglx_acc [B,c,2d] (fp32, +=); writes the
+        gradient of the ctx/gate logits into dcg_out [B,c,4d] and the normalised read o*rstd
+        into uhat_out [B,c,d] (both activation dtype; rows of the layer's deferred-dW stash)."""
+        dcg, dk, dv, uhat = fm.refine_bwd(dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols)
         d = k.shape[-1]
         dk_acc += dk
         dv_acc += dv
         dglx_acc += dcg[..., 2 * d:]
-        return dcg.to(k.dtype)
+        dcg_out.copy_(dcg)
+        uhat_out.copy_(uhat)
+
+    def rmsn_bwd(self, du, o, ssq, residual=None, out_dtype=torch.float32):
+        """d o of the gain-free row normalisation (+ residual), in out_dtype."""
+        dx = fm.rmsn_bwd(du, o, ssq)
+        if residual is not None:
+            dx = dx + residual.float()
+        return dx.to(out_dtype)
 
     # ---- head ---------------------------------------------------------------------------
     def ce_chunk(self, logits, targets, inv_n):

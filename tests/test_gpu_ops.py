@@ -116,10 +116,11 @@ def test_prefix_and_tail_fwd_bwd(ops, c, dh, pos0, window):
     if live.any():
         close(lse_c[live], lse_c_ref[live], rtol=1e-2, atol=2e-2, what="lse_c")
     assert (lse_c[~live] < -1e29).all()
-    o, lse = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c_ref, lse_c_ref, scale, window)
-    o_ref, lse_ref = fm.tail_fwd(f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c_ref, lse_c_ref, scale, window)
+    o, lse, ssq = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c_ref, lse_c_ref, scale, window)
+    o_ref, lse_ref, ssq_ref = fm.tail_fwd(f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c_ref, lse_c_ref, scale, window)
     close(o, o_ref, what="tail o")
     close(lse, lse_ref, rtol=1e-2, atol=2e-2, what="tail lse")
+    close(ssq, ssq_ref, rtol=2e-2, atol=1e-3, what="tail ssq")
     # ---- tail backward
     dO = rnd(B, c, H, dh, dtype=torch.float32, seed=11)
     z = lambda *s: torch.zeros(*s, device=DEV)
@@ -167,24 +168,32 @@ def test_refine_fwd_bwd(ops, pin):
     d = H * dh
     cos, sin = build_rope_cache(T, dh, 10000.0, device=DEV)
     r = slice(64, 128)
-    cg = rnd(B, c, 4 * d)
+    raw, o = rnd(B, c, 4 * d, scale=2.0), rnd(B, c, d, scale=1.5, seed=7)
+    ssq = o.float().view(B, c, H, dh).square().sum(-1)
     glx, k, v = rnd(B, T, 2 * d, seed=1), rnd(B, T, d, seed=2), rnd(B, T, d, seed=3)
-    K_out, V_out = ops.refine_fwd(cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], H, pin)
-    Kr, Vr = fm.refine_fwd(cg.float(), glx[:, r].float(), k[:, r].float(), v[:, r].float(), cos[r], sin[r], H, pin)
+    f = lambda t: t.float()
+    K_out, V_out = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], H, pin)
+    Kr, Vr = fm.refine_fwd(f(raw), ssq, f(glx[:, r]), f(k[:, r]), f(v[:, r]), cos[r], sin[r], H, pin)
     close(K_out, Kr, what="K''")
     close(V_out, Vr, what="V''")
     dK, dV = rnd(B, c, H, dh, dtype=torch.float32, seed=4), rnd(B, c, H, dh, dtype=torch.float32, seed=5)
     z = lambda *s: torch.zeros(*s, device=DEV)
     dk_acc, dv_acc, dg_acc = z(B, T, d), z(B, T, d), z(B, T, 2 * d)
-    dcg = ops.refine_bwd(dK, dV, cg, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], pin,
-                         dk_acc[:, r], dv_acc[:, r], dg_acc[:, r])
-    dcg_r, dk_r, dv_r = fm.refine_bwd(dK, dV, cg.float(), glx[:, r].float(), k[:, r].float(), v[:, r].float(),
-                                      cos[r], sin[r], pin)
+    dcg = torch.empty(B, c, 4 * d, dtype=torch.bfloat16, device=DEV)
+    uhat = torch.empty(B, c, d, dtype=torch.bfloat16, device=DEV)
+    ops.refine_bwd(dK, dV, raw, ssq, o, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], pin,
+                   dk_acc[:, r], dv_acc[:, r], dg_acc[:, r], dcg, uhat)
+    dcg_r, dk_r, dv_r, uh_r = fm.refine_bwd(dK, dV, f(raw), ssq, f(o), f(glx[:, r]), f(k[:, r]), f(v[:, r]),
+                                            cos[r], sin[r], pin)
     close(dcg, dcg_r, what="dcg")
+    close(uhat, uh_r, what="uhat")
     close(dk_acc[:, r], dk_r, what="dk")
     close(dv_acc[:, r], dv_r, what="dv")
     close(dg_acc[:, r], dcg_r[..., 2 * d:], what="dglx")
     assert dk_acc[:, :64].abs().max() == 0
+    du, res = rnd(B, c, d, seed=8), rnd(B, c, d, dtype=torch.float32, seed=9)
+    close(ops.rmsn_bwd(du, o, ssq, residual=res), fm.rmsn_bwd(f(du), f(o), ssq) + res, what="rmsn_bwd")
+    close(ops.rmsn_bwd(du, o, ssq, out_dtype=torch.bfloat16), fm.rmsn_bwd(f(du), f(o), ssq), what="rmsn_bwd bf16")
 
 
 def test_col_sum(ops):
