@@ -57,11 +57,15 @@ class _LayerPack:
         d, hid = cfg.d_model, cfg.mlp_hidden
         mk = lambda *s: torch.empty(*s, dtype=dtype, device=device)
         self.w_an, self.w_mn, self.w_ctx = mk(d), mk(d), mk(d)
-        self.wq, self.wk, self.wv, self.wo = mk(d, d), mk(d, d), mk(d, d), mk(d, d)
+        self.wo = mk(d, d)
+        # one input projection for q, k, v and the x-half of both gates: [wq ; wk ; wv ; W_gx], bias
+        # [0 ; 0 ; 0 ; b_g] -- a single GEMM forward, a single dX and a single dW GEMM backward
+        self.W_in, self.b_in = mk(5 * d, d), torch.zeros(5 * d, dtype=dtype, device=device)
+        self.wq, self.wk, self.wv = self.W_in[:d], self.W_in[d:2 * d], self.W_in[2 * d:3 * d]
         self.w1, self.w3, self.w2 = mk(hid, d), mk(hid, d), mk(d, hid)
         self.W_pack = mk(4 * d, d)        # [W_kctx ; W_vctx ; W_gk[:, d:] ; W_gv[:, d:]]
-        self.W_gx = mk(2 * d, d)          # [W_gk[:, :d] ; W_gv[:, :d]]
-        self.b_g = mk(2 * d)
+        self.W_gx = self.W_in[3 * d:]     # [W_gk[:, :d] ; W_gv[:, :d]]
+        self.b_g = self.b_in[3 * d:]
 
     @torch.no_grad()
     def pack(self, blk, cfg):
@@ -149,7 +153,8 @@ class WaveScanEngine:
             self.w_f = z(d)
             self.head_w = None if cfg.tie_embeddings else z(cfg.vocab_size, d)
             self.dW_pack = z(4 * d, d, dt=torch.float32)
-            self.dW_gx = z(2 * d, d, dt=torch.float32)
+            self.dW_in = z(5 * d, d, dt=torch.float32)
+            self.dW_gx = self.dW_in[3 * d:]
             # committed-prefix partials of every cell, kept from the forward so the backward
             # does not redo the prefix pass: per schedule, [L][n_cells] dense slots
             self._prefix_saved = {}
@@ -341,13 +346,12 @@ class WaveScanEngine:
             P = self.packs[li]
             x = self.xl[li]
             xhat, _ = ops.rms_fwd(x, P.w_an)
-            q_r = ops.rope(ops.linear(xhat, P.wq).view(B, T, h, dh), cos, sin)
-            k = ops.linear(xhat, P.wk)
-            v = ops.linear(xhat, P.wv)
-            kself_r = ops.rope(k.view(B, T, h, dh), cos, sin)
-            glx = ops.linear(xhat, P.W_gx, bias=P.b_g)
+            qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
+            k, v, glx = qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d], qkvg[..., 3 * d:]
+            q_r = ops.rope(qkvg[..., :d].unflatten(-1, (h, dh)), cos, sin)
+            kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
             Kc, Vc, o_all = self.K_caches[li], self.V_caches[li], self.o_saved[li]
-            v4 = v.view(B, T, h, dh)
+            v4 = v.unflatten(-1, (h, dh))
             saved = self._prefix_slots(sid, li)
             for ci, (pos0, c, n_sweeps) in enumerate(self.schedules[sid]):
                 r = slice(pos0, pos0 + c)
@@ -474,13 +478,11 @@ class WaveScanEngine:
             dO_all = ops.linear_dx(dx_mid, P.wo).view(B, T, h, dh)
             # ---- recompute the layer projections ----------------------------------------------
             xhat, rstd_a = ops.rms_fwd(x, P.w_an)
-            q = ops.linear(xhat, P.wq)
-            k = ops.linear(xhat, P.wk)
-            v = ops.linear(xhat, P.wv)
-            q_r = ops.rope(q.view(B, T, h, dh), cos, sin)
-            kself_r = ops.rope(k.view(B, T, h, dh), cos, sin)
-            glx = ops.linear(xhat, P.W_gx, bias=P.b_g)
-            v4 = v.view(B, T, h, dh)
+            qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
+            q, k, v, glx = qkvg[..., :d], qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d], qkvg[..., 3 * d:]
+            q_r = ops.rope(q.unflatten(-1, (h, dh)), cos, sin)
+            kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
+            v4 = v.unflatten(-1, (h, dh))
             Kc, Vc = self.K_caches[li], self.V_caches[li]
             self.dW_pack.zero_()
             dq_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
@@ -541,19 +543,19 @@ class WaveScanEngine:
             ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
             self._unfold_packed_grad(a)
             # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
-            dq = ops.unrope(dq_r, cos, sin).reshape(B, T, d).to(act)
-            dk_t = (dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)).to(act)
-            dv_t = dv.to(act)
-            dglx_a = dglx.to(act)
-            ops.linear_dw_acc(G.get(a.wq.weight), dq, xhat)
-            ops.linear_dw_acc(G.get(a.wk.weight), dk_t, xhat)
-            ops.linear_dw_acc(G.get(a.wv.weight), dv_t, xhat)
-            self.dW_gx.zero_()
-            ops.linear_dw_acc(self.dW_gx, dglx_a, xhat)
+            dY = torch.empty(B, T, 5 * d, dtype=act, device=dev)      # [dq | dk | dv | dglx]
+            dY[..., :d] = ops.unrope(dq_r, cos, sin).reshape(B, T, d)
+            dY[..., d:2 * d] = dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)
+            dY[..., 2 * d:3 * d] = dv
+            dY[..., 3 * d:] = dglx
+            self.dW_in.zero_()
+            ops.linear_dw_acc(self.dW_in, dY, xhat)
+            G.get(a.wq.weight).add_(self.dW_in[:d])
+            G.get(a.wk.weight).add_(self.dW_in[d:2 * d])
+            G.get(a.wv.weight).add_(self.dW_in[2 * d:3 * d])
             db_g = torch.zeros(2 * d, dtype=f32, device=dev)
             ops.col_sum_acc(db_g, dglx)
-            dxhat = (ops.linear_dx(dq, P.wq).float() + ops.linear_dx(dk_t, P.wk).float()
-                     + ops.linear_dx(dv_t, P.wv).float() + ops.linear_dx(dglx_a, P.W_gx).float())
+            dxhat = ops.linear_dx(dY, P.W_in)
             self.dx_cur.copy_(ops.rms_bwd(dxhat, x, P.w_an, rstd_a, G.get(blk.attn_norm.weight),
                                           residual=dx_mid, out_dtype=act))
             self._scatter_packed_grads(a, db_g)

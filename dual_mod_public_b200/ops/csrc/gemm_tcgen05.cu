@@ -8,30 +8,39 @@
 //   B_MN = 0 : B stored [N][K]  (K-major)        B_MN = 1 : B stored [K][N]  (N-major)
 // which covers y = x W^T (0,0), dx = dy W (0,1) and dW += dy^T x (1,1) without any transpose pass.
 //
-// One CTA computes a 128 x 256 tile: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner),
-// warps 2..5 = epilogue (each reads its own 32-lane quarter of TMEM).  4-stage ring of 128B-swizzled
-// tiles (48 KB per stage); no cluster multicast anywhere.  Every mbarrier wait is bounded: on expiry
-// the kernel raises a flag in global memory, stops waiting and runs to its end so TMEM is released.
+// Persistent kernel, one CTA per SM, 128 x BN output tiles (BN = 256, or 128 for narrow problems)
+// handed out round-robin.  warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2..5 =
+// epilogue (each reads its own 32-lane quarter of TMEM).  The shared-memory ring of 128B-swizzled
+// tiles runs on across tile boundaries, and the accumulator is double-buffered in TMEM (2 x BN
+// columns), so the epilogue of tile i overlaps the main loop of tile i+1.  No cluster multicast
+// anywhere.  Every mbarrier wait is bounded in time: on expiry the kernel raises a flag in global
+// memory, stops waiting and runs to its end so TMEM is released.
 #include <cuda.h>
 
 #include "common.cuh"
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = 256;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int NTHREADS = 192;
-constexpr unsigned long long WAIT_NS = 2000000000ull;  // every pipeline wait gives up after 2 s
 
-struct SmemLayout {
-  // tiles first (1024-byte aligned base), barriers after
-  static constexpr int bar_off = STAGES * STAGE_BYTES;
+template <int BN>
+struct Cfg {
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;              // two accumulators
+  static constexpr int bar_off = STAGES * STAGE_BYTES;  // tiles first (1024-byte aligned base), barriers after
   static constexpr int total = bar_off + 256;
 };
+constexpr unsigned long long WAIT_NS = 2000000000ull;  // every pipeline wait gives up after 2 s
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -105,7 +114,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, int BN>
 __device__ __forceinline__ constexpr uint32_t instr_desc() {
   return (1u << 4)                      // D = fp32
          | (1u << 7) | (1u << 10)       // A, B = bf16
@@ -113,23 +122,26 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
          | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-template <int A_MN, int B_MN, int OUT_F32>
+template <int A_MN, int B_MN, int OUT_F32, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout,
     const bf16* __restrict__ bias, int M, int N, int K, long long ldc, int accumulate, int* __restrict__ gerr) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t bar0 = base + SmemLayout::bar_off;
-  // barriers: full[s] at bar0 + 8 s, empty[s] at bar0 + 8 (STAGES + s), tmem_full after them
+  const uint32_t bar0 = base + C::bar_off;
+  // barriers: full[s], empty[s], tmem_full[2], tmem_empty[2], then the TMEM address slot and the error word
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  const uint32_t tmem_full = bar0 + 8u * (2 * STAGES);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + SmemLayout::bar_off + 8 * (2 * STAGES + 1));
-  volatile int* serr = reinterpret_cast<volatile int*>(base_ptr + SmemLayout::bar_off + 8 * (2 * STAGES + 2));
+  auto tmem_full = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tmem_empty = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + C::bar_off + 8 * (2 * STAGES + 4));
+  volatile int* serr = reinterpret_cast<volatile int*>(base_ptr + C::bar_off + 8 * (2 * STAGES + 5));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM, n_tiles = tiles_n * tiles_m;
   const int KB = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -138,12 +150,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
       mbar_init(full(s), 1);
       mbar_init(empty(s), 1);
     }
-    mbar_init(tmem_full, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full(a), 1);
+      mbar_init(tmem_empty(a), 4);       // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(C::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -152,60 +167,77 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer: the ring position `it` runs on across tiles ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < KB; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(empty(s), ((kb / STAGES) - 1) & 1, serr)) break;
-        const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
-        mbar_expect_tx(full(s), STAGE_BYTES);
-        const int k0 = kb * BK;
-        if (A_MN == 0) {
-          tma_load_2d(sa, &tmA, full(s), k0, m0);                       // box {64 k, 128 m}
-        } else {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(empty(s), ((it / STAGES) & 1) ^ 1, serr)) { alive = false; break; }
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          mbar_expect_tx(full(s), STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d(sa, &tmA, full(s), k0, m0);                       // box {64 k, 128 m}
+          } else {
 #pragma unroll
-          for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmA, full(s), m0 + 64 * j, k0);  // box {64 m, 64 k}
-        }
-        if (B_MN == 0) {
-          tma_load_2d(sb, &tmB, full(s), k0, n0);                       // box {64 k, 256 n}
-        } else {
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmA, full(s), m0 + 64 * j, k0);  // box {64 m, 64 k}
+          }
+          if (B_MN == 0) {
+            tma_load_2d(sb, &tmB, full(s), k0, n0);                       // box {64 k, BN n}
+          } else {
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmB, full(s), n0 + 64 * j, k0);  // box {64 n, 64 k}
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmB, full(s), n0 + 64 * j, k0);  // box {64 n, 64 k}
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc<A_MN, B_MN>();
+      constexpr uint32_t idesc = instr_desc<A_MN, B_MN, BN>();
+      uint32_t it = 0, ti = 0;
       bool alive = true;
-      for (int kb = 0; kb < KB && alive; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(full(s), (kb / STAGES) & 1, serr)) { alive = false; break; }
+      for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++ti) {
+        const uint32_t acc = ti & 1;
+        // the epilogue must have drained this accumulator (two tiles ago)
+        if (!mbar_wait(tmem_empty(acc), ((ti >> 1) & 1) ^ 1, serr)) { alive = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+        const uint32_t tacc = tmem_base + acc * BN;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full(s), (it / STAGES) & 1, serr)) { alive = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // K-major: 32 bytes further along the swizzled 128-byte row; MN-major: 16 k-rows of 128 bytes
-          const uint64_t da = A_MN == 0 ? make_desc(sa + k * 32, 16, 1024) : make_desc(sa + k * 2048, BK * 128, 1024);
-          const uint64_t db = B_MN == 0 ? make_desc(sb + k * 32, 16, 1024) : make_desc(sb + k * 2048, BK * 128, 1024);
-          umma_bf16(tmem_base, da, db, idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 32 bytes further along the swizzled 128-byte row; MN-major: 16 k-rows of 128 bytes
+            const uint64_t da = A_MN == 0 ? make_desc(sa + k * 32, 16, 1024) : make_desc(sa + k * 2048, BK * 128, 1024);
+            const uint64_t db = B_MN == 0 ? make_desc(sb + k * 32, 16, 1024) : make_desc(sb + k * 2048, BK * 128, 1024);
+            umma_bf16(tacc, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(empty(s));           // stage reusable once these MMAs have read it
         }
-        umma_commit(empty(s));           // stage reusable once these MMAs have read it
+        if (alive) umma_commit(tmem_full(acc));   // accumulator complete
       }
-      umma_commit(tmem_full);            // accumulator complete
     }
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
-    const bool ok = mbar_wait(tmem_full, 0, serr);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int row = m0 + q * 32 + lane;
-    if (ok) {
+    uint32_t ti = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++ti) {
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const uint32_t acc = ti & 1;
+      if (!mbar_wait(tmem_full(acc), (ti >> 1) & 1, serr)) { alive = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = m0 + q * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col = n0 + c0;
         if (row < M && col < N) {
@@ -244,13 +276,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
           }
         }
       }
+      // this warp has read its quarter of the accumulator: hand it back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty(acc));
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
   }
   if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
 }
@@ -283,19 +319,21 @@ int make_map(CUtensorMap* m, const void* ptr, long long inner, long long outer, 
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-template <int A_MN, int B_MN, int OUT_F32>
+int g_sms = 0;
+
+template <int A_MN, int B_MN, int OUT_F32, int BN>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* bias, int M, int N, int K,
            long long ldc, int accumulate, int* gerr, cudaStream_t st) {
-  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32>;
+  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, BN>;
   static bool configured = false;
-  const int smem = SmemLayout::total + 1024;
+  const int smem = Cfg<BN>::total + 1024;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  kern<<<grid, NTHREADS, smem, st>>>(ta, tb, C, (const bf16*)bias, M, N, K, ldc, accumulate, gerr);
+  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  kern<<<tiles < g_sms ? tiles : g_sms, NTHREADS, smem, st>>>(ta, tb, C, (const bf16*)bias, M, N, K, ldc, accumulate, gerr);
   DMB_CHECK_LAUNCH();
   return 0;
 }
@@ -306,6 +344,7 @@ extern "C" {
 
 // C[M,N] (+)= op(A) op(B).  lda / ldb: row stride (elements) of A and B as stored.
 //   a_mn = 0: A stored [M][K];  a_mn = 1: A stored [K][M]      (same for B with N)
+// Supported layouts: (0,0) y = x W^T, (0,1) dx = dy W, (1,1) dW += dy^T x.
 // Requirements: pointers 16-byte aligned, lda/ldb/ldc multiples of 8 (bf16) resp. 4 (fp32 C),
 // N % 8 == 0.  out_f32: C is fp32 (else bf16).  accumulate needs out_f32.  `gerr` (device int) is
 // set to 1 if a pipeline wait ran out.
@@ -313,20 +352,29 @@ int dmb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
                   long long ldb, long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, int* gerr,
                   cudaStream_t st) {
   if (get_encode()) return -10;
-  if (N % 8 || (accumulate && !out_f32)) return -1;
+  if (N % 8 || (accumulate && !out_f32) || (a_mn && !b_mn)) return -1;
+  if (!g_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sms <= 0)
+      return -12;
+  }
+  // narrow tiles when wide ones would leave SMs idle or the last wave mostly empty
+  const long long t256 = (long long)((N + 255) / 256) * ((M + BM - 1) / BM);
+  const int bn = (N <= 128 || t256 < 2LL * g_sms) ? 128 : 256;
   CUtensorMap ta, tb;
   int rc;
   rc = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM);
   if (rc) return rc;
-  rc = b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, BN);
+  rc = b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc;
-#define GO(a, b, o) return launch<a, b, o>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, st)
+#define GO(a, b, o)                                                                               \
+  return bn == 256 ? launch<a, b, o, 256>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, st)    \
+                   : launch<a, b, o, 128>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, st)
   if (!a_mn && !b_mn) { if (out_f32) GO(0, 0, 1); else GO(0, 0, 0); }
   if (!a_mn && b_mn) { if (out_f32) GO(0, 1, 1); else GO(0, 1, 0); }
-  if (a_mn && b_mn) { if (out_f32) GO(1, 1, 1); else GO(1, 1, 0); }
-  if (a_mn && !b_mn) { if (out_f32) GO(1, 0, 1); else GO(1, 0, 0); }
+  if (out_f32) GO(1, 1, 1); else GO(1, 1, 0);
 #undef GO
-  return -1;
 }
 
 }  // extern "C"
