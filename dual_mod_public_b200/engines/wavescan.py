@@ -94,7 +94,7 @@ class WaveScanEngine:
     def __init__(self, model, schedules, B, T, device=None, autocast_bf16=False,
                  keep_logits=False, loss_rows=4096, use_graphs=False, backend="auto",
                  ops=None, grad_bf16_ids=None, grad_alloc=None, grad_pad_to=1, sat_tau=0.0,
-                 grads=None, on_layer_grads_final=None):
+                 grads=None, on_layer_grads_final=None, keep_sweeps="auto"):
         cfg = model.cfg
         self.model, self.cfg = model, cfg
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
@@ -161,6 +161,13 @@ class WaveScanEngine:
             # per-layer stash of (d ctx/gate logits, u) of every sweep: the packed weight
             # gradient is ONE GEMM over all of a layer's sweep rows instead of one per sweep
             self._dw_stash = {}
+            # per (schedule, layer): every sweep's (K_in, V_in, read, lse, ssq, ctx logits) kept from
+            # a training forward, so the reverse scan starts each cell's backward at once instead
+            # of re-running its sweeps.  `keep_sweeps`: number of layers (from layer 0) that keep
+            # them, "auto" = as many as fit in about half of the device memory, 0 = recompute.
+            self._sweep_saved = {}
+            self._sweeps_valid = False
+            self.keep_layers = self._keep_layers(keep_sweeps)
             self._packed = False
         else:
             self.K_caches = [z(B, h, T, dh) for _ in range(L)]
@@ -177,6 +184,16 @@ class WaveScanEngine:
     # =============================================================================
     # public API
     # =============================================================================
+    def _keep_layers(self, keep_sweeps):
+        if keep_sweeps != "auto":
+            return max(0, min(self.L, int(keep_sweeps)))
+        if self.device.type != "cuda":
+            return self.L
+        per_row = 7 * self.cfg.d_model * (2 if self.autocast_bf16 else 4)
+        rows = max(self.B * sum(c * k for _, c, k in sch) for sch in self.schedules)
+        budget = 0.5 * torch.cuda.get_device_properties(self.device).total_memory
+        return max(0, min(self.L, int(budget // max(1, rows * per_row * len(self.schedules)))))
+
     def pack(self):
         """Refresh the compute-dtype weight copies from the master parameters."""
         if self.backend != "fused":
@@ -208,7 +225,10 @@ class WaveScanEngine:
                 self.pack()
             self._run("emb", 0, self._fused_embed)
             for li in range(self.L):
-                self._run(("fwd", li), sid, lambda li=li: self._fused_layer_fwd(li, sid))
+                keep = bool(train) and li < self.keep_layers
+                self._run(("fwd", li, keep), sid, lambda li=li, keep=keep: self._fused_layer_fwd(li, sid, keep),
+                          replay_after_capture=True)
+            self._sweeps_valid = bool(train)
             if targets is not None or self.keep_logits:
                 self._run(("head", bool(train), targets is not None), 0,
                           lambda: self._fused_head(train, targets is not None))
@@ -235,7 +255,8 @@ class WaveScanEngine:
             if self.on_layer_grads_final is not None:
                 self.on_layer_grads_final(-1)
             for li in range(self.L - 1, -1, -1):
-                self._run(("bwd", li), sid, lambda li=li: self._fused_layer_bwd(li, sid))
+                kept = self._sweeps_valid and li < self.keep_layers
+                self._run(("bwd", li, kept), sid, lambda li=li, kept=kept: self._fused_layer_bwd(li, sid, kept))
                 if self.on_layer_grads_final is not None:
                     self.on_layer_grads_final(li)
             self._run("embb", 0, self._fused_embed_bwd)
@@ -288,7 +309,7 @@ class WaveScanEngine:
     # =============================================================================
     # CUDA graphs
     # =============================================================================
-    def _run(self, key, sid, body):
+    def _run(self, key, sid, body, replay_after_capture=False):
         if not self.use_graphs:
             return body()
         gkey = (key, sid)
@@ -308,6 +329,10 @@ class WaveScanEngine:
             body()
         self._graphs.setdefault("pool", g.pool())
         self._graphs[gkey] = g
+        if replay_after_capture:
+            # tensors the body left for later bodies now live in the graph's pool and were not
+            # written by the recording: run the (idempotent) body once more through the graph
+            g.replay()
 
     def graph_kernel_count(self):
         """Hand-written kernel launches recorded in the captured graphs of one
@@ -336,7 +361,7 @@ class WaveScanEngine:
         self.grads.get(self.model.tok_emb.weight).index_add_(
             0, self.idx.view(-1), self.dx_cur.reshape(-1, self.cfg.d_model).float())
 
-    def _fused_layer_fwd(self, li, sid):
+    def _fused_layer_fwd(self, li, sid, keep=False):
         ops, cfg = self.ops, self.cfg
         B, T, h, dh, d = self.B, self.T, cfg.n_heads, cfg.head_dim, cfg.d_model
         scale = 1.0 / dh ** 0.5
@@ -353,23 +378,31 @@ class WaveScanEngine:
             Kc, Vc, o_all = self.K_caches[li], self.V_caches[li], self.o_saved[li]
             v4 = v.unflatten(-1, (h, dh))
             saved = self._prefix_slots(sid, li)
+            kept = [] if keep else None
             for ci, (pos0, c, n_sweeps) in enumerate(self.schedules[sid]):
                 r = slice(pos0, pos0 + c)
                 o_c, lse_c = ops.prefix_fwd(q_r[:, r], Kc, Vc, pos0, scale, self.window)
                 saved[ci][0].copy_(o_c)
                 saved[ci][1].copy_(lse_c)
                 K_in, V_in = kself_r[:, r], v4[:, r]
-                o = None
-                for _ in range(n_sweeps):
-                    o, _, ssq = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
-                                             o_c, lse_c, scale, self.window)
+                o, st = None, []
+                for s in range(n_sweeps):
+                    o, lse, ssq = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
+                                               o_c, lse_c, scale, self.window)
                     raw = ops.linear(o.reshape(B, c, d), P.W_pack)
+                    if keep:
+                        # sweep 0 reads the raw rows, which the backward re-projects anyway
+                        st.append((K_in if s else None, V_in if s else None, o, lse, ssq, raw))
                     K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
                                                 h, pin)
+                if keep:
+                    kept.append(st)
                 Kc[:, r] = K_in
                 Vc[:, r] = V_in
                 o_all[:, r] = o.reshape(B, c, d)
                 self.stats["fwd_cells"] += 1
+            if keep:
+                self._sweep_saved[(sid, li)] = kept
             x_mid = x + ops.linear(o_all, P.wo)
             xn, _ = ops.rms_fwd(x_mid, P.w_mn)
             g = ops.swiglu_fwd(ops.linear(xn, P.w1), ops.linear(xn, P.w3))
@@ -447,7 +480,7 @@ class WaveScanEngine:
             dxt[r] = ops.rms_bwd(ops.linear_dx(dl[r], W), x[r], self.w_f, rstd,
                                  self.grads.get(self.model.norm_f.weight), out_dtype=self.act)
 
-    def _fused_layer_bwd(self, li, sid):
+    def _fused_layer_bwd(self, li, sid, kept=False):
         ops, cfg, G = self.ops, self.cfg, self.grads
         B, T, h, dh, d = self.B, self.T, cfg.n_heads, cfg.head_dim, cfg.d_model
         act, f32 = self.act, torch.float32
@@ -500,15 +533,18 @@ class WaveScanEngine:
                 r = slice(pos0, pos0 + c)
                 qc, ksc, vc4 = q_r[:, r], kself_r[:, r], v4[:, r]
                 o_c, lse_c = saved[ci]
-                # forward recompute, keeping each sweep's state
-                st = []
-                K_in, V_in = ksc, vc4
-                for _ in range(n_sweeps):
-                    o, lse, ssq = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
-                    raw = ops.linear(o.reshape(B, c, d), P.W_pack)
-                    st.append((K_in, V_in, o, lse, ssq, raw))
-                    K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
-                                                h, pin)
+                if kept:
+                    st = [(ksc, vc4) + t[2:] if t[0] is None else t for t in self._sweep_saved[(sid, li)][ci]]
+                else:
+                    # forward recompute, keeping each sweep's state
+                    st = []
+                    K_in, V_in = ksc, vc4
+                    for _ in range(n_sweeps):
+                        o, lse, ssq = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
+                        raw = ops.linear(o.reshape(B, c, d), P.W_pack)
+                        st.append((K_in, V_in, o, lse, ssq, raw))
+                        K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                                                    h, pin)
                 self.lsec_all[:, r] = lse_c
                 # gradient of this cell's committed rows from every later cell's prefix read
                 dK_out, dV_out = ops.prefix_dkv(q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,

@@ -125,7 +125,8 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 template <int A_MN, int B_MN, int OUT_F32, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout,
-    const bf16* __restrict__ bias, int M, int N, int K, long long ldc, int accumulate, int* __restrict__ gerr) {
+    const bf16* __restrict__ bias, int M, int N, int K, long long ldc, int accumulate, int* __restrict__ gerr,
+    int splits, float* __restrict__ ws) {
   using C = Cfg<BN>;
   constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -141,8 +142,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
   volatile int* serr = reinterpret_cast<volatile int*>(base_ptr + C::bar_off + 8 * (2 * STAGES + 5));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM, n_tiles = tiles_n * tiles_m;
-  const int KB = (K + BK - 1) / BK;
+  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
+  // split-K: work item w = tile * splits + ks covers k-blocks [ks * KBS, min(KBT, (ks + 1) * KBS)) and
+  // writes its partial product to slice ks of the fp32 workspace; a second kernel sums the slices
+  const int KBT = (K + BK - 1) / BK, KBS = (KBT + splits - 1) / splits;
+  const int n_tiles = tiles_n * tiles_m * splits;
 
   if (threadIdx.x == 0) {
     *serr = 0;
@@ -172,8 +176,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
       uint32_t it = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int t2 = tile / splits, ks = tile - t2 * splits;
+        const int m0 = (t2 / tiles_n) * BM, n0 = (t2 % tiles_n) * BN;
+        const int kb0 = ks * KBS, kb1 = min(KBT, kb0 + KBS);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(empty(s), ((it / STAGES) & 1) ^ 1, serr)) { alive = false; break; }
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
@@ -206,7 +212,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
         if (!mbar_wait(tmem_empty(acc), ((ti >> 1) & 1) ^ 1, serr)) { alive = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tacc = tmem_base + acc * BN;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int ks = tile % splits, kb0 = ks * KBS, kb1 = min(KBT, kb0 + KBS);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(full(s), (it / STAGES) & 1, serr)) { alive = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -216,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
             // K-major: 32 bytes further along the swizzled 128-byte row; MN-major: 16 k-rows of 128 bytes
             const uint64_t da = A_MN == 0 ? make_desc(sa + k * 32, 16, 1024) : make_desc(sa + k * 2048, BK * 128, 1024);
             const uint64_t db = B_MN == 0 ? make_desc(sb + k * 32, 16, 1024) : make_desc(sb + k * 2048, BK * 128, 1024);
-            umma_bf16(tacc, da, db, idesc, (kb | k) != 0);
+            umma_bf16(tacc, da, db, idesc, ((kb - kb0) | k) != 0);
           }
           umma_commit(empty(s));           // stage reusable once these MMAs have read it
         }
@@ -229,7 +236,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
     uint32_t ti = 0;
     bool alive = true;
     for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++ti) {
-      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int t2 = tile / splits, ks = tile - t2 * splits;
+      const int m0 = (t2 / tiles_n) * BM, n0 = (t2 % tiles_n) * BN;
       const uint32_t acc = ti & 1;
       if (!mbar_wait(tmem_full(acc), (ti >> 1) & 1, serr)) { alive = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -242,7 +250,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
         const int col = n0 + c0;
         if (row < M && col < N) {
           if (OUT_F32) {
-            float* dst = reinterpret_cast<float*>(Cout) + (long long)row * ldc + col;
+            float* dst = splits > 1 ? ws + ((long long)ks * M + row) * N + col
+                                    : reinterpret_cast<float*>(Cout) + (long long)row * ldc + col;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col + j < N) {      // N % 8 == 0 keeps groups of 4 whole
@@ -251,7 +260,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
                   v.x += __bfloat162float(bias[col + j]); v.y += __bfloat162float(bias[col + j + 1]);
                   v.z += __bfloat162float(bias[col + j + 2]); v.w += __bfloat162float(bias[col + j + 3]);
                 }
-                if (accumulate) {
+                if (accumulate && splits == 1) {
                   float4 o = *reinterpret_cast<float4*>(dst + j);
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                 }
@@ -291,6 +300,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
   if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
 }
 
+// C[row, col] (+)= sum over slices of the split-K workspace (slices summed in index order)
+__global__ void splitk_reduce_kernel(float* __restrict__ Cout, const float* __restrict__ ws, int M, int N, long long ldc,
+                                     int splits, int accumulate) {
+  const long long n4 = (long long)M * N / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 4, row = e / N, col = e - row * N;
+    float4 a = *reinterpret_cast<const float4*>(ws + e);
+    for (int s = 1; s < splits; ++s) {
+      const float4 b = *reinterpret_cast<const float4*>(ws + (long long)s * M * N + e);
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    float* dst = Cout + row * ldc + col;
+    if (accumulate) {
+      const float4 o = *reinterpret_cast<const float4*>(dst);
+      a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w;
+    }
+    *reinterpret_cast<float4*>(dst) = a;
+  }
+}
+
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -320,10 +349,12 @@ int make_map(CUtensorMap* m, const void* ptr, long long inner, long long outer, 
 }
 
 int g_sms = 0;
+constexpr size_t WS_BYTES = (size_t)64 << 20;    // split-K workspace, one per device, allocated on first use
+float* g_ws[16] = {};
 
 template <int A_MN, int B_MN, int OUT_F32, int BN>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* bias, int M, int N, int K,
-           long long ldc, int accumulate, int* gerr, cudaStream_t st) {
+           long long ldc, int accumulate, int* gerr, float* ws, int splits, cudaStream_t st) {
   auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, BN>;
   static bool configured = false;
   const int smem = Cfg<BN>::total + 1024;
@@ -333,8 +364,14 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* bi
     configured = true;
   }
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
-  kern<<<tiles < g_sms ? tiles : g_sms, NTHREADS, smem, st>>>(ta, tb, C, (const bf16*)bias, M, N, K, ldc, accumulate, gerr);
+  const int items = tiles * splits;
+  kern<<<items < g_sms ? items : g_sms, NTHREADS, smem, st>>>(ta, tb, C, (const bf16*)bias, M, N, K, ldc, accumulate,
+                                                             gerr, splits, ws);
   DMB_CHECK_LAUNCH();
+  if (splits > 1) {
+    splitk_reduce_kernel<<<g_sms * 2, 256, 0, st>>>((float*)C, ws, M, N, ldc, splits, accumulate);
+    DMB_CHECK_LAUNCH();
+  }
   return 0;
 }
 
@@ -359,9 +396,43 @@ int dmb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
         cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sms <= 0)
       return -12;
   }
-  // narrow tiles when wide ones would leave SMs idle or the last wave mostly empty
-  const long long t256 = (long long)((N + 255) / 256) * ((M + BM - 1) / BM);
-  const int bn = (N <= 128 || t256 < 2LL * g_sms) ? 128 : 256;
+  float* ws = nullptr;
+  if (out_f32) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return -12;
+    if (!g_ws[dev]) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      cudaStreamIsCapturing(st, &cs);
+      if (cs == cudaStreamCaptureStatusNone && cudaMalloc(&g_ws[dev], WS_BYTES) != cudaSuccess) g_ws[dev] = nullptr;
+    }
+    ws = g_ws[dev];                                  // null: no split-K (allocation failed or capturing)
+  }
+  // tile width and K split from a small cost model, in units of one 128x256x64 k-block: a work item
+  // costs kbs * a + e (a: k-block cost, e: epilogue), items run in ceil(items / SMs) rounds, and a
+  // split adds the workspace round trip.  Splitting is for the weight-gradient shapes (small M x N,
+  // very long K) and needs the fp32 output path.
+  int bn = 256, splits = 1;
+  {
+    const int KBT = (K + BK - 1) / BK;
+    const int tm = (M + BM - 1) / BM;
+    double best = 1e30;
+    for (int cand = 0; cand < 2; ++cand) {
+      const int w = cand ? 128 : 256;
+      if (N <= 128 && w == 256) continue;
+      const long long tiles = (long long)((N + w - 1) / w) * tm;
+      const double a = w == 256 ? 1.0 : 0.6, e = w == 256 ? 8.0 : 4.0;
+      const int smax = (ws && !bias && N % 4 == 0) ? 16 : 1;
+      for (int sp = 1; sp <= smax; ++sp) {
+        if (sp > 1 && (KBT / sp < 16 || (size_t)sp * M * N * sizeof(float) > WS_BYTES)) break;
+        const int kbs = (KBT + sp - 1) / sp;
+        if (sp > 1 && (KBT + kbs - 1) / kbs != sp) continue;          // would leave an empty slice
+        const long long rounds = (tiles * sp + g_sms - 1) / g_sms;
+        double cost = rounds * (kbs * a + e);
+        if (sp > 1) cost += (sp + 1.0) * M * N * 4.0 / 5e12 / 0.41e-6;
+        if (cost < best) { best = cost; bn = w; splits = sp; }
+      }
+    }
+  }
   CUtensorMap ta, tb;
   int rc;
   rc = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM);
@@ -369,8 +440,8 @@ int dmb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
   rc = b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc;
 #define GO(a, b, o)                                                                               \
-  return bn == 256 ? launch<a, b, o, 256>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, st)    \
-                   : launch<a, b, o, 128>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, st)
+  return bn == 256 ? launch<a, b, o, 256>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)    \
+                   : launch<a, b, o, 128>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)
   if (!a_mn && !b_mn) { if (out_f32) GO(0, 0, 1); else GO(0, 0, 0); }
   if (!a_mn && b_mn) { if (out_f32) GO(0, 1, 1); else GO(0, 1, 0); }
   if (out_f32) GO(1, 1, 1); else GO(1, 1, 0);

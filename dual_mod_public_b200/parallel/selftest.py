@@ -1,0 +1,231 @@
+"""Multi-GPU self-test and micro-benchmark of the fused data-parallel optimizer.
+
+Run as one process per GPU on one node:
+
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+      --master-port 29611 -m dual_mod_public_b200.parallel.selftest            # checks
+  ... -m dual_mod_public_b200.parallel.selftest --bench --numel 340000000       # timing
+
+Checks (each prints `ok <name>` on rank 0, the run ends with `SELFTEST PASS`):
+
+  optim        the cooperative reduce-scatter + clip + AdamW + all-gather kernel against the torch
+               statement of the same plan (library all-reduce + per-slice AdamW) over 3 steps,
+               including a step the skip predicate rejects
+  early        the same with every bucket's reduce-scatter issued early on a side stream
+  bitwise      all ranks hold identical parameter bytes after the steps
+  trainer      `Trainer` sharded over the ranks against a one-rank `Trainer` fed the whole batch:
+               loss and parameters after 2 steps, and bitwise-equal weights across ranks
+
+Reference parity: engines/wavescan/tests/ddp_equiv.py:94-141 (sharded == single process, bitwise
+weight sync).  `--bench` times `FusedDPAdamW.step()` against the library chain `NcclAdamW.step()`
+on a flat buffer of `--numel` fp32 elements with CUDA events (max over ranks) and prints the
+fraction of the NVLink roofline: each rank must load (W-1)/W of the gradient bytes from its peers
+and store (W-1)/W of the parameter bytes to them.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .fused_optim import FusedDPAdamW, NcclAdamW
+
+LINK_GBS = 770.0          # measured peer copy bandwidth per direction per GPU on this class of box
+
+
+def _toy_params(dev, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    shapes = [(257, 64), (64,), (128, 96), (96,), (1000, 33), (7,), (512, 512), (512,)]
+    return [torch.nn.Parameter(torch.randn(*s, generator=g).to(dev)) for s in shapes]
+
+
+def _groups(ps):
+    return [{"params": [p for p in ps if p.dim() >= 2], "weight_decay": 0.1},
+            {"params": [p for p in ps if p.dim() < 2], "weight_decay": 0.0, "lr_mult": 0.5}]
+
+
+def _buckets(ps):
+    return [ps[:2], ps[2:5], ps[5:]]
+
+
+def _max_rel(a, b):
+    return ((a - b).abs().max() / (b.abs().max() + 1e-12)).item()
+
+
+def check_optim(dev, rank, world, early):
+    pk, ph = _toy_params(dev), _toy_params(dev)
+    kw = dict(lr=1e-2, max_norm=1.0, skip_norm=50.0, grad_accum=2, device=dev)
+    ok = FusedDPAdamW(_groups(pk), _buckets(pk), use_kernel=True, **kw)
+    oh = FusedDPAdamW(_groups(ph), _buckets(ph), use_kernel=False, **kw)
+    side = torch.cuda.Stream(device=dev)
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    worst = 0.0
+    for step in range(4):
+        ok.zero_grad()
+        oh.zero_grad()
+        boost = 500.0 if step == 2 else 0.05                     # step 2 trips the skip predicate
+        for p_k, p_h in zip(ok.layout.params, oh.layout.params):
+            gr = (torch.randn(p_k.shape, generator=g) * boost).to(dev)
+            ok.layout.view(ok.flat_grads, p_k).copy_(gr)
+            oh.layout.view(oh.flat_grads, p_h).copy_(gr)
+        if early:
+            side.wait_stream(torch.cuda.current_stream(dev))
+            for b in range(len(ok.layout.buckets)):
+                ok.bucket_ready(b, stream=side)
+            torch.cuda.current_stream(dev).wait_stream(side)
+        ck, ch = ok.step().clone(), oh.step().clone()
+        ok.check_status()
+        assert abs(ck[0].item() - ch[0].item()) <= 1e-4 * ch[0].item(), (step, ck, ch)
+        assert ck[2].item() == ch[2].item() == (1.0 if step == 2 else 0.0), (step, ck, ch)
+        worst = max(worst, _max_rel(ok.flat_params, oh.flat_params))
+    assert worst < 2e-6, worst
+    # every rank holds the same bytes
+    mine = ok.flat_params.view(torch.int32).clone()
+    ref = mine.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(mine, ref), "parameter bytes differ across ranks"
+    sd = ok.state_dict()
+    assert len(sd["state"]) == len(pk)
+    ok.close()
+    return worst
+
+
+def check_trainer(dev, rank, world):
+    from ..config import DualModConfig
+    from ..engines.schedule import uniform_chunks
+    from ..models import DualModLM
+    from ..train.trainer import Trainer
+    cfg = DualModConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=2, max_seq_len=128,
+                        mlp_hidden_override=256)
+    T, lb = 128, 2
+    sched = [uniform_chunks(T, 64, 2)]
+    groups = [dist.new_group([r]) for r in range(world)]        # every rank creates every group
+    solo = groups[rank]
+    torch.manual_seed(7)
+    m_ref, m_dp = DualModLM(cfg), DualModLM(cfg)
+    m_dp.load_state_dict(m_ref.state_dict())
+    common = dict(seq_len=T, lr=1e-4, max_norm=1.0, use_graphs=False, device=dev)
+    t_ref = Trainer(cfg, sched, micro_batch=lb, local_batch=lb * world, process_group=solo, model=m_ref,
+                    **common)
+    t_dp = Trainer(cfg, sched, micro_batch=lb, local_batch=lb, model=m_dp, **common)
+    assert t_ref.opt.world == 1 and t_dp.opt.world == world
+    g = torch.Generator().manual_seed(11)
+    for step in range(2):
+        toks = torch.randint(0, cfg.vocab_size, (lb * world, T + 1), generator=g).pin_memory()
+        l_ref = t_ref.step(toks)
+        l_dp = torch.tensor(t_dp.step(toks[rank * lb:(rank + 1) * lb]), device=dev)
+        dist.all_reduce(l_dp)
+        l_dp = l_dp.item() / world
+        assert abs(l_ref - l_dp) < 2e-3 * abs(l_ref), (step, l_ref, l_dp)
+        gn_ref, gn_dp = t_ref.opt.ctrl[0].item(), t_dp.opt.ctrl[0].item()
+        assert abs(gn_ref - gn_dp) < 5e-3 * gn_ref, (step, gn_ref, gn_dp)    # same averaged gradient
+    t_dp.opt.check_status()
+    worst = 0.0
+    for (n, a), (_, b) in zip(m_ref.named_parameters(), m_dp.named_parameters()):
+        worst = max(worst, _max_rel(a.detach(), b.detach()))
+    assert worst < 2e-2, worst                                   # bf16 engine, different batch split
+    mine = t_dp.opt.flat_params.view(torch.int32).clone()
+    ref = mine.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(mine, ref), "trainer weights differ across ranks"
+    return worst
+
+
+def _time(fn, iters, dev):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    junk = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    tot = 0.0
+    for _ in range(iters):
+        junk.fill_(1)
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        tot += e0.elapsed_time(e1)
+    t = torch.tensor(tot / iters, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def bench(dev, rank, world, numel, iters, n_buckets):
+    per = max(64, numel // n_buckets // 64 * 64)
+    mk = lambda: [torch.nn.Parameter(torch.zeros(per, device=dev)) for _ in range(n_buckets)]
+    pf, pn = mk(), mk()
+    kw = dict(lr=1e-4, max_norm=1.0)
+    of = FusedDPAdamW([{"params": pf, "weight_decay": 0.1}], [[p] for p in pf], device=dev, **kw)
+    on = NcclAdamW([{"params": pn, "weight_decay": 0.1}], **kw)
+    of.flat_grads.normal_()
+    on.grad_buffers().flat.normal_()
+    side = torch.cuda.Stream(device=dev)
+
+    def fused_early():
+        side.wait_stream(torch.cuda.current_stream(dev))
+        for b in range(n_buckets):
+            of.bucket_ready(b, stream=side)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        of.step()
+
+    t_f = _time(lambda: of.step(), iters, dev)
+    t_e = _time(fused_early, iters, dev)
+    t_n = _time(lambda: on.step(), iters, dev)
+    of.check_status()
+    n = of.layout.numel
+    wire = 4.0 * n * (world - 1) / world                         # bytes per direction per GPU
+    hbm = 4.0 * n * (2.0 + 5.0 / world)                          # local reads/writes of the fused kernel (approx.)
+    ideal_ms = wire / (LINK_GBS * 1e6) if world > 1 else hbm / (6650.0 * 1e6)
+    out = {"what": "fused reduce-scatter + clip + AdamW + all-gather vs library chain", "world": world,
+           "numel": n, "buckets": n_buckets, "fused_ms": round(t_f, 4), "fused_early_buckets_ms": round(t_e, 4),
+           "nccl_chain_ms": round(t_n, 4), "speedup_vs_nccl_chain": round(t_n / t_f, 3),
+           "wire_bytes_per_direction_per_gpu": int(wire), "roofline_ms": round(ideal_ms, 4),
+           "fraction_of_roofline": round(ideal_ms / t_f, 4),
+           "roofline": f"bytes over NVLink at {LINK_GBS:.0f} GB/s per direction" if world > 1 else "HBM copy"}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    of.close()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--numel", type=int, default=340_000_000)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--buckets", type=int, default=26)
+    ap.add_argument("--skip-trainer", action="store_true")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 or "MASTER_ADDR" in os.environ:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29611")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    else:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29611")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    say = (lambda *a: print(*a, flush=True)) if rank == 0 else (lambda *a: None)
+    if args.bench:
+        bench(dev, rank, world, args.numel, args.iters, args.buckets)
+    else:
+        say("ok optim", check_optim(dev, rank, world, early=False))
+        say("ok early", check_optim(dev, rank, world, early=True))
+        say("ok bitwise")
+        if not args.skip_trainer:
+            say("ok trainer", check_trainer(dev, rank, world))
+        say("SELFTEST PASS")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

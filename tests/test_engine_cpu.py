@@ -189,6 +189,28 @@ def test_fused_backward_matches_autograd_for_few_sweeps(kw):
         assert relerr(gf[n], gg[n]) < 1e-4, n
 
 
+def test_kept_sweep_states_equal_recompute():
+    """Keeping every sweep's state from the forward (all layers, one layer, none) gives the same
+    gradients as re-running the sweeps in the reverse scan."""
+    cfg, m = build(local_window=7)
+    B, T = 2, 32
+    g = torch.Generator().manual_seed(8)
+    idx = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    sched = uniform_chunks(T, 8, 3)
+    out = []
+    for keep in (0, 1, "auto"):
+        eng = WaveScanEngine(m, [sched], B, T, backend="fused", ops=TorchOps(), keep_sweeps=keep)
+        assert eng.keep_layers == {0: 0, 1: 1, "auto": cfg.n_layers}[keep]
+        out.append(_engine_grads(m, eng, idx, tgt))
+        l2, g2 = _engine_grads(m, eng, idx, tgt)                 # second step reuses the slots
+        assert torch.equal(l2, out[-1][0]) and all(torch.equal(g2[n], out[-1][1][n]) for n in g2)
+    for l, gr in out[1:]:
+        assert torch.equal(l, out[0][0])
+        for n in gr:
+            assert torch.equal(gr[n], out[0][1][n]), n
+
+
 def test_explicit_dlogits_backward_and_accumulation():
     cfg, m = build()
     B, T = 2, 16

@@ -52,7 +52,8 @@ def test_linear_dx(gemm, M, N, K):
     check(dx, dy.float() @ w.float(), "dx")
 
 
-@pytest.mark.parametrize("M,N,K", SHAPES[:5] + [(136, 264, 72)])
+# the last two have a long reduction and few output tiles: the split-K path with even and ragged slices
+@pytest.mark.parametrize("M,N,K", SHAPES[:5] + [(136, 264, 72), (16384, 512, 256), (8256, 264, 136)])
 def test_linear_dw_acc(gemm, M, N, K):
     rows = M
     dy, x = rnd(rows, N), rnd(rows, K, seed=1)
