@@ -17,7 +17,7 @@
 // Buckets whose reduce-scatter already ran (launched early, overlapped with the backward, by
 // dmb_opt_reduce_bucket) are skipped in phase 1.  Every cross-GPU wait is bounded in time; on
 // expiry the kernel records where it gave up in `status` and carries on without hanging, the host
-// reads the status word.  No TMA, no multicast loads: peers are touched only by ld/st.global.
+// reads the status word.  Peers are touched only by plain ld/st.global (no bulk-copy engine).
 #include <cooperative_groups.h>
 #include <string.h>
 

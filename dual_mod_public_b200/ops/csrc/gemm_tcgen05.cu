@@ -12,8 +12,8 @@
 // handed out round-robin.  warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2..5 =
 // epilogue (each reads its own 32-lane quarter of TMEM).  The shared-memory ring of 128B-swizzled
 // tiles runs on across tile boundaries, and the accumulator is double-buffered in TMEM (2 x BN
-// columns), so the epilogue of tile i overlaps the main loop of tile i+1.  No cluster multicast
-// anywhere.  Every mbarrier wait is bounded in time: on expiry the kernel raises a flag in global
+// columns), so the epilogue of tile i overlaps the main loop of tile i+1.  Each CTA
+// loads its own tiles.  Every mbarrier wait is bounded in time: on expiry the kernel raises a flag in global
 // memory, stops waiting and runs to its end so TMEM is released.
 #include <cuda.h>
 

@@ -37,6 +37,15 @@ from .fused_optim import FusedDPAdamW, NcclAdamW
 LINK_GBS = 770.0          # measured peer copy bandwidth per direction per GPU on this class of box
 
 
+def _hbm_gbs():
+    """Measured copy bandwidth of this pool's GPUs when the peaks file sits at the repository root."""
+    p = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
 def _toy_params(dev, seed=0):
     g = torch.Generator(device="cpu").manual_seed(seed)
     shapes = [(257, 64), (64,), (128, 96), (96,), (1000, 33), (7,), (512, 512), (512,)]
@@ -179,15 +188,24 @@ def bench(dev, rank, world, numel, iters, n_buckets):
     t_n = _time(lambda: on.step(), iters, dev)
     of.check_status()
     n = of.layout.numel
-    wire = 4.0 * n * (world - 1) / world                         # bytes per direction per GPU
-    hbm = 4.0 * n * (2.0 + 5.0 / world)                          # local reads/writes of the fused kernel (approx.)
-    ideal_ms = wire / (LINK_GBS * 1e6) if world > 1 else hbm / (6650.0 * 1e6)
+    # roofline: the slower of (bytes each rank moves over NVLink per direction) / link bandwidth and
+    # (bytes that touch this rank's HBM) / copy bandwidth.  Per rank, with n elements in total:
+    #   NVLink in  = peers' shares of my slice            4n (W-1)/W      (reduce-scatter loads)
+    #   NVLink out = my updated slice to every peer       4n (W-1)/W      (all-gather stores)
+    #   HBM        = 4n (everyone reads my gradients) + 4n/W (reduced slice written back)
+    #              + 16n/W (g, p, m, v read) + 8n/W (m, v written) + 4n (all ranks store parameters here)
+    wire = 4.0 * n * (world - 1) / world
+    hbm = 4.0 * n * (2.0 + 7.0 / world)
+    hbm_gbs = _hbm_gbs()
+    t_wire, t_hbm = wire / (LINK_GBS * 1e6), hbm / (hbm_gbs * 1e6)
+    ideal_ms = max(t_wire, t_hbm)
     out = {"what": "fused reduce-scatter + clip + AdamW + all-gather vs library chain", "world": world,
            "numel": n, "buckets": n_buckets, "fused_ms": round(t_f, 4), "fused_early_buckets_ms": round(t_e, 4),
            "nccl_chain_ms": round(t_n, 4), "speedup_vs_nccl_chain": round(t_n / t_f, 3),
-           "wire_bytes_per_direction_per_gpu": int(wire), "roofline_ms": round(ideal_ms, 4),
-           "fraction_of_roofline": round(ideal_ms / t_f, 4),
-           "roofline": f"bytes over NVLink at {LINK_GBS:.0f} GB/s per direction" if world > 1 else "HBM copy"}
+           "wire_bytes_per_direction_per_gpu": int(wire), "hbm_bytes_per_gpu": int(hbm),
+           "nvlink_ms_at_%d_gbs" % LINK_GBS: round(t_wire, 4), "hbm_ms_at_%d_gbs" % hbm_gbs: round(t_hbm, 4),
+           "roofline_ms": round(ideal_ms, 4), "fraction_of_roofline": round(ideal_ms / t_f, 4),
+           "bound": "nvlink" if t_wire >= t_hbm else "hbm"}
     if rank == 0:
         print(json.dumps(out), flush=True)
     of.close()
