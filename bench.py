@@ -36,6 +36,7 @@ PUBLISHED_TOK_S_PER_GPU = 107000.0 / 8      # reference README: 15.36 B tokens i
 MODEL = dict(d_model=1024, n_layers=24, n_heads=16, mlp_hidden_override=2816, vocab_size=32000,
              max_seq_len=2048, gate_bias_init=0.0, checkpoint_chunk=64)
 SEQ, CHUNK, SWEEPS, GLOBAL_SEQS = 2048, 64, 4, 256
+MODEL_NAME = "dm_340m (24L d1024 16x64 ffn2816 vocab32000 tied)"
 
 
 class ClockSampler:
@@ -130,9 +131,11 @@ def run_ours(args):
     local_seqs = GLOBAL_SEQS // world
     micro = min(args.micro_batch, local_seqs)
     cfg = DualModConfig(**MODEL)
-    tr = Trainer(cfg, [uniform_chunks(SEQ, CHUNK, SWEEPS)], seq_len=SEQ, micro_batch=micro,
+    wave3d = args.config == "1p3b"
+    tr = Trainer(cfg, [SWEEPS] if wave3d else [uniform_chunks(SEQ, CHUNK, SWEEPS)], seq_len=SEQ, micro_batch=micro,
                  local_batch=local_seqs, lr=3e-4, weight_decay=0.01, max_norm=1.0,
-                 optimizer=args.optimizer, device=f"cuda:{local}", use_graphs=not args.no_graphs)
+                 optimizer=args.optimizer, device=f"cuda:{local}", use_graphs=not args.no_graphs,
+                 engine="wave3d" if wave3d else "wavescan", engine_kwargs=dict(C=CHUNK) if wave3d else None)
     host = synthetic_tokens(torch, local_seqs, rank, 2, cfg.vocab_size)
     dev = [t.cuda() for t in host]
     for i in range(args.warmup):
@@ -160,9 +163,10 @@ def run_ours(args):
                "vs_baseline": round(value / (PUBLISHED_TOK_S_PER_GPU * world), 3),
                "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
                "impl": "ours",
-               "config": {"model": f"dm_340m ({MODEL['n_layers']}L d1024 16x64 ffn2816 vocab32000 tied)"
+               "config": {"model": MODEL_NAME
                           + ("" if MODEL["n_layers"] == 24 and GLOBAL_SEQS == 256 else " PROFILING SHAPE, NOT A BENCH VALUE"),
-                          "engine": "wavescan c=64 K=4", "global_batch": GLOBAL_SEQS, "seq_len": SEQ,
+                          "engine": f"{'wavefront (wave3d operator)' if wave3d else 'wavescan'} c={CHUNK} K={SWEEPS}",
+                          "global_batch": GLOBAL_SEQS, "seq_len": SEQ,
                           "micro_batch": micro, "parallelism": f"dp{world}", "optimizer": args.optimizer,
                           "cuda_graphs": tr.engine.use_graphs,
                           "l2": "per-step working set is tens of GB (>> 126 MB L2); no explicit flush",
@@ -275,13 +279,24 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("DMB_MICRO_BATCH", 32)))
     ap.add_argument("--optimizer", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--config", default="340m", choices=["340m", "1p3b"],
+                    help="340m: 24L d1024 wavescan c=64 K=4 at 256 x 2048 tokens per step (the headline); "
+                         "1p3b: 24L d2048 16x128 ffn5632 wavefront engine c=64 at 256 x 4096 tokens per step")
+    ap.add_argument("--sweeps", type=int, default=0, help="sweeps K (default 4; the 1.3B ladder is 2 / 4 / 8)")
     ap.add_argument("--profile-layers", type=int, default=0,
                     help="PROFILING ONLY: shrink the model to this many layers (the printed line is then "
                          "not a benchmark value and says so)")
     ap.add_argument("--profile-seqs", type=int, default=0,
                     help="PROFILING ONLY: global batch in sequences")
     args = ap.parse_args()
-    global GLOBAL_SEQS
+    global GLOBAL_SEQS, SEQ, SWEEPS, MODEL_NAME
+    if args.config == "1p3b":
+        MODEL.update(d_model=2048, n_heads=16, mlp_hidden_override=5632, max_seq_len=4096)
+        SEQ, MODEL_NAME = 4096, "dm_1p3b (24L d2048 16x128 ffn5632 vocab32000 tied)"
+        if "DMB_MICRO_BATCH" not in os.environ and args.micro_batch == 32:
+            args.micro_batch = 16
+    if args.sweeps:
+        SWEEPS = args.sweeps
     profiling = bool(args.profile_layers or args.profile_seqs)
     if args.profile_layers:
         MODEL["n_layers"] = args.profile_layers

@@ -143,17 +143,18 @@ def prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
     dq_acc += torch.einsum("bhcj,bjhd->bchd", ds, K.float())
 
 
-def prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0):
+def prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
     """Key side of the prefix backward, owner-computes: the gradient of tape rows
     [pos0, pos0+c) from every later query (absolute rows >= q_start of the full-sequence
     arrays q_all / doc_all [B,T,h,dh], corr_all / lsec_all [B,T,h]).  Returns fp32
     (dK, dV) [B,c,h,dh]; nothing is accumulated in global memory."""
     B, T, h, dh = q_all.shape
+    T = T if q_end is None else min(T, q_end)          # queries [q_start, q_end) only
     dK = torch.zeros(B, c, h, dh, dtype=torch.float32, device=q_all.device)
     dV = torch.zeros_like(dK)
     if q_start >= T:
         return dK, dV
-    q, do = q_all[:, q_start:], doc_all[:, q_start:].float()
+    q, do = q_all[:, q_start:T], doc_all[:, q_start:T].float()
     K, V = Kc[:, pos0:pos0 + c], Vc[:, pos0:pos0 + c]
     s = torch.einsum("bthd,bjhd->bhtj", q, K).float() * scale
     vis = None
@@ -162,11 +163,11 @@ def prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, sca
         j = torch.arange(pos0, pos0 + c, device=q_all.device)[None, :]
         vis = j > t - window
         s = s.masked_fill(~vis, NEG)
-    p = torch.exp(s - lsec_all[:, q_start:].permute(0, 2, 1).unsqueeze(-1))
+    p = torch.exp(s - lsec_all[:, q_start:T].permute(0, 2, 1).unsqueeze(-1))
     if vis is not None:
         p = p * vis
     dov = torch.einsum("bthd,bjhd->bhtj", do, V.float())
-    ds = p * (dov - corr_all[:, q_start:].permute(0, 2, 1).unsqueeze(-1)) * scale
+    ds = p * (dov - corr_all[:, q_start:T].permute(0, 2, 1).unsqueeze(-1)) * scale
     dK += torch.einsum("bhtj,bthd->bjhd", ds, q.float())
     dV += torch.einsum("bhtj,bthd->bjhd", p, do)
     return dK, dV

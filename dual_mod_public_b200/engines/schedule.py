@@ -22,11 +22,11 @@ class Cell(NamedTuple):
     sweeps: int
 
 
-def check_schedule(cells: Sequence[Cell], T: int) -> None:
+def check_schedule(cells: Sequence[Cell], T: int, max_sweeps: int | None = None) -> None:
     pos = 0
     for cell in cells:
         p, c, k = cell
-        assert p == pos and c > 0 and 1 <= k <= c, f"bad cell {cell} at {pos}"
+        assert p == pos and c > 0 and 1 <= k <= (c if max_sweeps is None else max_sweeps), f"bad cell {cell} at {pos}"
         pos += c
     assert pos == T, f"schedule covers {pos} of {T} positions"
 

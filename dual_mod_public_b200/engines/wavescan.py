@@ -22,6 +22,8 @@ engines/wavescan/engine/backward.py:87-206.
 
 from __future__ import annotations
 
+from types import SimpleNamespace
+
 import torch
 import torch.nn.functional as F
 
@@ -91,6 +93,8 @@ class _LayerPack:
 
 
 class WaveScanEngine:
+    MAX_SWEEPS = None            # per cell: sweeps <= chunk length (K = c is already exact)
+
     def __init__(self, model, schedules, B, T, device=None, autocast_bf16=False,
                  keep_logits=False, loss_rows=4096, use_graphs=False, backend="auto",
                  ops=None, grad_bf16_ids=None, grad_alloc=None, grad_pad_to=1, sat_tau=0.0,
@@ -100,7 +104,7 @@ class WaveScanEngine:
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         self.schedules = [list(s) for s in schedules]
         for s in self.schedules:
-            check_schedule(s, T)
+            check_schedule(s, T, self.MAX_SWEEPS)
         self.B, self.T, self.L = B, T, cfg.n_layers
         self.autocast_bf16 = autocast_bf16
         self.act = torch.bfloat16 if autocast_bf16 else torch.float32
@@ -377,36 +381,46 @@ class WaveScanEngine:
             kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
             Kc, Vc, o_all = self.K_caches[li], self.V_caches[li], self.o_saved[li]
             v4 = v.unflatten(-1, (h, dh))
-            saved = self._prefix_slots(sid, li)
-            kept = [] if keep else None
-            for ci, (pos0, c, n_sweeps) in enumerate(self.schedules[sid]):
-                r = slice(pos0, pos0 + c)
-                o_c, lse_c = ops.prefix_fwd(q_r[:, r], Kc, Vc, pos0, scale, self.window)
-                saved[ci][0].copy_(o_c)
-                saved[ci][1].copy_(lse_c)
-                K_in, V_in = kself_r[:, r], v4[:, r]
-                o, st = None, []
-                for s in range(n_sweeps):
-                    o, lse, ssq = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
-                                               o_c, lse_c, scale, self.window)
-                    raw = ops.linear(o.reshape(B, c, d), P.W_pack)
-                    if keep:
-                        # sweep 0 reads the raw rows, which the backward re-projects anyway
-                        st.append((K_in if s else None, V_in if s else None, o, lse, ssq, raw))
-                    K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
-                                                h, pin)
-                if keep:
-                    kept.append(st)
-                Kc[:, r] = K_in
-                Vc[:, r] = V_in
-                o_all[:, r] = o.reshape(B, c, d)
-                self.stats["fwd_cells"] += 1
-            if keep:
-                self._sweep_saved[(sid, li)] = kept
+            S = SimpleNamespace(P=P, q_r=q_r, kself_r=kself_r, v4=v4, k=k, v=v, glx=glx, Kc=Kc, Vc=Vc,
+                                o_all=o_all, cos=cos, sin=sin, scale=scale, pin=pin)
+            self._cells_fwd(li, sid, S, keep)
             x_mid = x + ops.linear(o_all, P.wo)
             xn, _ = ops.rms_fwd(x_mid, P.w_mn)
             g = ops.swiglu_fwd(ops.linear(xn, P.w1), ops.linear(xn, P.w3))
             self.xl[li + 1].copy_(x_mid + ops.linear(g, P.w2))
+
+    def _cells_fwd(self, li, sid, S, keep):
+        """The cells of one layer in order: committed-prefix read once per cell, K Jacobi sweeps, commit."""
+        ops, cfg = self.ops, self.cfg
+        B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
+        P, q_r, kself_r, v4, k, v, glx = S.P, S.q_r, S.kself_r, S.v4, S.k, S.v, S.glx
+        Kc, Vc, o_all, cos, sin, scale, pin = S.Kc, S.Vc, S.o_all, S.cos, S.sin, S.scale, S.pin
+        saved = self._prefix_slots(sid, li)
+        kept = [] if keep else None
+        for ci, (pos0, c, n_sweeps) in enumerate(self.schedules[sid]):
+            r = slice(pos0, pos0 + c)
+            o_c, lse_c = ops.prefix_fwd(q_r[:, r], Kc, Vc, pos0, scale, self.window)
+            saved[ci][0].copy_(o_c)
+            saved[ci][1].copy_(lse_c)
+            K_in, V_in = kself_r[:, r], v4[:, r]
+            o, st = None, []
+            for s in range(n_sweeps):
+                o, lse, ssq = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
+                                           o_c, lse_c, scale, self.window)
+                raw = ops.linear(o.reshape(B, c, d), P.W_pack)
+                if keep:
+                    # sweep 0 reads the raw rows, which the backward re-projects anyway
+                    st.append((K_in if s else None, V_in if s else None, o, lse, ssq, raw))
+                K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                                            h, pin)
+            if keep:
+                kept.append(st)
+            Kc[:, r] = K_in
+            Vc[:, r] = V_in
+            o_all[:, r] = o.reshape(B, c, d)
+            self.stats["fwd_cells"] += 1
+        if keep:
+            self._sweep_saved[(sid, li)] = kept
 
     def _prefix_slots(self, sid, li):
         """[(o_c [B,c,h,dh] fp32, lse_c [B,c,h] fp32)] per cell of layer li at schedule sid."""
@@ -524,58 +538,10 @@ class WaveScanEngine:
             dv = torch.zeros(B, T, d, dtype=f32, device=dev)
             dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev)
             dv4 = dv.view(B, T, h, dh)
-            # ---- cells in reverse ---------------------------------------------------------------
-            saved = self._prefix_slots(sid, li)
-            dcg_stash, u_stash, stash_off = self._stash_for(sid)
-            n_cells = len(self.schedules[sid])
-            for ci in range(n_cells - 1, -1, -1):
-                pos0, c, n_sweeps = self.schedules[sid][ci]
-                r = slice(pos0, pos0 + c)
-                qc, ksc, vc4 = q_r[:, r], kself_r[:, r], v4[:, r]
-                o_c, lse_c = saved[ci]
-                if kept:
-                    st = [(ksc, vc4) + t[2:] if t[0] is None else t for t in self._sweep_saved[(sid, li)][ci]]
-                else:
-                    # forward recompute, keeping each sweep's state
-                    st = []
-                    K_in, V_in = ksc, vc4
-                    for _ in range(n_sweeps):
-                        o, lse, ssq = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
-                        raw = ops.linear(o.reshape(B, c, d), P.W_pack)
-                        st.append((K_in, V_in, o, lse, ssq, raw))
-                        K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
-                                                    h, pin)
-                self.lsec_all[:, r] = lse_c
-                # gradient of this cell's committed rows from every later cell's prefix read
-                dK_out, dV_out = ops.prefix_dkv(q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
-                                                pos0, c, pos0 + c, scale, self.window)
-                d_o = dO_all[:, r].float()
-                do_c = torch.zeros_like(o_c)
-                dlse_c = torch.zeros_like(lse_c)
-                dq_c = torch.zeros(B, c, h, dh, dtype=f32, device=dev)
-                for s in range(n_sweeps - 1, -1, -1):
-                    K_in, V_in, o, lse, ssq, raw = st[s]
-                    off = stash_off[(ci, s)]
-                    dcg = dcg_stash[off:off + B * c].view(B, c, 4 * d)
-                    ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), glx[:, r], k[:, r], v[:, r],
-                                   cos[r], sin[r], pin, dk[:, r], dv[:, r], dglx[:, r], dcg,
-                                   u_stash[off:off + B * c].view(B, c, d))
-                    du = ops.linear_dx(dcg, P.W_pack)
-                    d_o = ops.rmsn_bwd(du, o.reshape(B, c, d), ssq,
-                                       residual=d_o.view(B, c, d) if s == n_sweeps - 1 else None
-                                       ).view(B, c, h, dh)
-                    dK_out, dV_out = ops.tail_bwd(
-                        d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
-                        dq_c, dks_r[:, r], dv4[:, r], do_c, dlse_c)
-                # sweep 0 read the raw rows
-                dks_r[:, r] += dK_out
-                dv4[:, r] += dV_out
-                corr = (do_c * o_c).sum(-1) - dlse_c
-                self.doc_all[:, r] = do_c
-                self.corr_all[:, r] = corr
-                ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_c)
-                dq_r[:, r] = dq_c
-                self.stats["bwd_cells"] += 1
+            S = SimpleNamespace(P=P, q_r=q_r, kself_r=kself_r, v4=v4, k=k, v=v, glx=glx, Kc=Kc, Vc=Vc,
+                                cos=cos, sin=sin, scale=scale, pin=pin, dO_all=dO_all, dq_r=dq_r, dks_r=dks_r,
+                                dk=dk, dv=dv, dglx=dglx, dv4=dv4)
+            dcg_stash, u_stash = self._cells_bwd(li, sid, S, kept)
             ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
             self._unfold_packed_grad(a)
             # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
@@ -595,6 +561,69 @@ class WaveScanEngine:
             self.dx_cur.copy_(ops.rms_bwd(dxhat, x, P.w_an, rstd_a, G.get(blk.attn_norm.weight),
                                           residual=dx_mid, out_dtype=act))
             self._scatter_packed_grads(a, db_g)
+
+    def _cells_bwd(self, li, sid, S, kept):
+        """Reverse scan over the cells of one layer.  Accumulates into S.dq_r / dks_r / dk / dv / dglx and
+        returns the (d ctx-gate logits, u) stashes of every sweep for the deferred packed-weight GEMM."""
+        ops, cfg = self.ops, self.cfg
+        B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
+        f32, dev = torch.float32, self.device
+        P, q_r, kself_r, v4, k, v, glx = S.P, S.q_r, S.kself_r, S.v4, S.k, S.v, S.glx
+        Kc, Vc, cos, sin, scale, pin = S.Kc, S.Vc, S.cos, S.sin, S.scale, S.pin
+        dO_all, dq_r, dks_r, dk, dv, dglx, dv4 = S.dO_all, S.dq_r, S.dks_r, S.dk, S.dv, S.dglx, S.dv4
+        # ---- cells in reverse ---------------------------------------------------------------
+        saved = self._prefix_slots(sid, li)
+        dcg_stash, u_stash, stash_off = self._stash_for(sid)
+        n_cells = len(self.schedules[sid])
+        for ci in range(n_cells - 1, -1, -1):
+            pos0, c, n_sweeps = self.schedules[sid][ci]
+            r = slice(pos0, pos0 + c)
+            qc, ksc, vc4 = q_r[:, r], kself_r[:, r], v4[:, r]
+            o_c, lse_c = saved[ci]
+            if kept:
+                st = [(ksc, vc4) + t[2:] if t[0] is None else t for t in self._sweep_saved[(sid, li)][ci]]
+            else:
+                # forward recompute, keeping each sweep's state
+                st = []
+                K_in, V_in = ksc, vc4
+                for _ in range(n_sweeps):
+                    o, lse, ssq = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
+                    raw = ops.linear(o.reshape(B, c, d), P.W_pack)
+                    st.append((K_in, V_in, o, lse, ssq, raw))
+                    K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
+                                                h, pin)
+            self.lsec_all[:, r] = lse_c
+            # gradient of this cell's committed rows from every later cell's prefix read
+            dK_out, dV_out = ops.prefix_dkv(q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
+                                            pos0, c, pos0 + c, scale, self.window)
+            d_o = dO_all[:, r].float()
+            do_c = torch.zeros_like(o_c)
+            dlse_c = torch.zeros_like(lse_c)
+            dq_c = torch.zeros(B, c, h, dh, dtype=f32, device=dev)
+            for s in range(n_sweeps - 1, -1, -1):
+                K_in, V_in, o, lse, ssq, raw = st[s]
+                off = stash_off[(ci, s)]
+                dcg = dcg_stash[off:off + B * c].view(B, c, 4 * d)
+                ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), glx[:, r], k[:, r], v[:, r],
+                               cos[r], sin[r], pin, dk[:, r], dv[:, r], dglx[:, r], dcg,
+                               u_stash[off:off + B * c].view(B, c, d))
+                du = ops.linear_dx(dcg, P.W_pack)
+                d_o = ops.rmsn_bwd(du, o.reshape(B, c, d), ssq,
+                                   residual=d_o.view(B, c, d) if s == n_sweeps - 1 else None
+                                   ).view(B, c, h, dh)
+                dK_out, dV_out = ops.tail_bwd(
+                    d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
+                    dq_c, dks_r[:, r], dv4[:, r], do_c, dlse_c)
+            # sweep 0 read the raw rows
+            dks_r[:, r] += dK_out
+            dv4[:, r] += dV_out
+            corr = (do_c * o_c).sum(-1) - dlse_c
+            self.doc_all[:, r] = do_c
+            self.corr_all[:, r] = corr
+            ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_c)
+            dq_r[:, r] = dq_c
+            self.stats["bwd_cells"] += 1
+        return dcg_stash, u_stash
 
     def _unfold_packed_grad(self, a):
         """dW_pack holds the gradient of the FOLDED weight W' = W * w_ctx (per column).  Recover

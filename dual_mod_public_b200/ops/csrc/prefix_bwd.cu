@@ -23,8 +23,8 @@ template <int DH, int C>
 __global__ void __launch_bounds__(C * 2) prefix_dkv_kernel(
     const bf16* __restrict__ q_all, const bf16* __restrict__ doc_all, const float* __restrict__ corr_all,
     const float* __restrict__ lsec_all, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc,
-    float* __restrict__ dK, float* __restrict__ dV, int T, int H, int pos0, int q_start, float scale,
-    int window) {
+    float* __restrict__ dK, float* __restrict__ dV, int T, int H, int pos0, int q_start, int q_end,
+    float scale, int window) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = C / 8, PC = C + 8, QT = C;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sK = reinterpret_cast<bf16*>(smem_raw);
@@ -42,9 +42,9 @@ __global__ void __launch_bounds__(C * 2) prefix_dkv_kernel(
   const float* Cb = corr_all + (long long)b * T * H + h;
   load_tile_bf16<DH, NT>(sK, Kc + b * vc.bs + (long long)pos0 * vc.rs + hoff, vc.rs, C, tid);
   load_tile_bf16<DH, NT>(sV, Vc + b * vc.bs + (long long)pos0 * vc.rs + hoff, vc.rs, C, tid);
-  const int n_rows = T - q_start, n_tiles = (n_rows + QT - 1) / QT;
+  const int n_rows = q_end - q_start, n_tiles = (n_rows + QT - 1) / QT;
   auto issue = [&](int tile, int stage) {
-    const int t0 = q_start + tile * QT, rows = min(QT, T - t0);
+    const int t0 = q_start + tile * QT, rows = min(QT, q_end - t0);
     load_tile_async<DH, NT>(sQ + stage * QT * P, Qb + (long long)t0 * rs, rs, rows, tid);
     load_tile_async<DH, NT>(sdO + stage * QT * P, Ob + (long long)t0 * rs, rs, rows, tid);
     cp_async_commit();
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(C * 2) prefix_dkv_kernel(
     }
     const int i0 = row0 + g, i1 = i0 + 8;             // rows inside the tile
     const int ta = t0 + i0, tb = t0 + i1;             // absolute query positions
-    const bool va = ta < T, vb = tb < T;
+    const bool va = ta < q_end, vb = tb < q_end;
     const float L0 = va ? Lb[(long long)ta * H] : 0.f, L1 = vb ? Lb[(long long)tb * H] : 0.f;
     const float c0 = va ? Cb[(long long)ta * H] : 0.f, c1 = vb ? Cb[(long long)tb * H] : 0.f;
 #pragma unroll
@@ -282,14 +282,14 @@ extern "C" {
 
 int dmb_prefix_dkv(const void* q_all, const void* doc_all, const float* corr_all, const float* lsec_all,
                    const void* Kc, const void* Vc, TView vc, float* dK, float* dV, int B, int T, int c, int H,
-                   int dh, int pos0, int q_start, float scale, int window, cudaStream_t st) {
+                   int dh, int pos0, int q_start, int q_end, float scale, int window, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = (((size_t)2 * C + 4 * C) * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
     auto kern = prefix_dkv_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q_all, (const bf16*)doc_all, corr_all, lsec_all,
                                          (const bf16*)Kc, (const bf16*)Vc, vc, dK, dV, T, H, pos0, q_start,
-                                         scale, window);
+                                         q_end < T ? q_end : T, scale, window);
   })
   DMB_CHECK_LAUNCH();
   return 0;

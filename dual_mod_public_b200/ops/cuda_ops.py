@@ -61,7 +61,7 @@ class _Sigs:
     dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _v, _p, _v,
                     _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
     dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
-    dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]
+    dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
 
 
@@ -267,18 +267,19 @@ class CudaOps(TorchOps):
                                         dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, self._st()),
                  "prefix_dq")
 
-    def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0):
+    def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
         B, T, h, dh = q_all.shape
+        q_end = T if q_end is None else min(q_end, T)
         ok = (q_all.dtype == BF16 and doc_all.dtype == BF16 and dh in (64, 128) and c in (16, 32, 64)
               and q_all.is_contiguous() and doc_all.is_contiguous() and corr_all.is_contiguous()
               and lsec_all.is_contiguous() and _dense_tail(Kc, 2))
         if not ok:
-            return super().prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window)
+            return super().prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end)
         dK = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
         dV = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(),
                                          lsec_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
-                                         dK.data_ptr(), dV.data_ptr(), B, T, c, h, dh, pos0, q_start, scale,
+                                         dK.data_ptr(), dV.data_ptr(), B, T, c, h, dh, pos0, q_start, q_end, scale,
                                          window, self._st()), "prefix_dkv")
         return dK, dV
 

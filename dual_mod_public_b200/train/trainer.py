@@ -50,15 +50,16 @@ class Trainer:
         self._side = torch.cuda.Stream(device=self.device) if self.overlap else None
         self._last_micro = False
         kw = dict(engine_kwargs or {})
+        common_e = dict(device=self.device, autocast_bf16=autocast_bf16, use_graphs=use_graphs,
+                        grads=self.opt.grad_buffers(),
+                        on_layer_grads_final=self._layer_done if self.overlap else None)
         if engine == "wavescan":
-            self.engine = WaveScanEngine(self.model, schedules, micro_batch, seq_len, device=self.device,
-                                         autocast_bf16=autocast_bf16, use_graphs=use_graphs,
-                                         grads=self.opt.grad_buffers(),
-                                         on_layer_grads_final=self._layer_done if self.overlap else None, **kw)
+            # schedules: list of cell lists [(pos0, c, sweeps), ...], one per schedule id
+            self.engine = WaveScanEngine(self.model, schedules, micro_batch, seq_len, **common_e, **kw)
         else:
+            # schedules: the K-ladder (sweep counts) of the wavefront engine, one per schedule id
             from ..engines.wave3d import Wave3DEngine
-            self.engine = Wave3DEngine(self.model, schedules, micro_batch, seq_len, device=self.device,
-                                       autocast_bf16=autocast_bf16, grads=self.opt.grad_buffers(), **kw)
+            self.engine = Wave3DEngine(self.model, schedules, micro_batch, seq_len, **common_e, **kw)
         self.engine.pack()
         self.steps_done = 0
         self._loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)

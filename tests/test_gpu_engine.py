@@ -63,6 +63,26 @@ def test_kernel_engine_matches_fp32_torch_engine(kw, c, K):
     assert e_k.debug_scan() == []
 
 
+@pytest.mark.parametrize("dh,K", [(64, 3), (128, 2)])
+def test_wavefront_kernel_engine_matches_fp32_torch_engine(dh, K):
+    from dual_mod_public_b200.engines.wave3d import Wave3DEngine
+    cfg, m = build(d=256, heads=256 // dh)
+    B, T = 4, 256
+    idx, tgt = batch(cfg, B, T)
+    e_k = Wave3DEngine(m, [K], B, T, C=64, autocast_bf16=True, backend="fused")
+    e_r = Wave3DEngine(m, [K], B, T, C=64, autocast_bf16=False, backend="fused", ops=TorchOps())
+    n0 = e_k.ops.launches
+    lk, gk = grads_of(e_k, m, idx, tgt)
+    assert e_k.ops.launches - n0 > 50, "the kernel table was not used"
+    lr, gr = grads_of(e_r, m, idx, tgt)
+    assert abs(lk.item() - lr.item()) < 3e-2, (lk.item(), lr.item())
+    for n in gr:
+        a, b = gk[n].flatten().double(), gr[n].flatten().double()
+        cos = (a @ b) / (a.norm() * b.norm() + 1e-30)
+        assert cos > 0.98, f"{n}: cos {cos:.4f}"
+        assert (a.norm() / (b.norm() + 1e-30) - 1).abs() < 0.1, n
+
+
 def test_graph_replay_equals_eager_bitwise():
     cfg, m = build()
     B, T = 2, 256
