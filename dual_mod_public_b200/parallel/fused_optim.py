@@ -216,6 +216,9 @@ class FusedDPAdamW:
         self.use_kernel = self.device.type == "cuda" if use_kernel is None else use_kernel
         self.step_count = 0
         self.epoch = 0
+        # set for one step by a caller that excluded ranks from the average (their gradients zeroed):
+        # 1 / (ranks kept * micro-batches); None = 1 / (world * micro-batches)
+        self.grad_scale_override = None
         self.wait_seconds = wait_seconds
         n = self.layout.numel
         nslots = SLOT_BUCKET0 + len(self.layout.buckets)
@@ -313,8 +316,9 @@ class FusedDPAdamW:
         self.step_count += 1
         self.epoch += 1
         b1, b2 = self.betas
+        scale = self.grad_scale_override or 1.0 / (self.world * self.grad_accum)
         return dict(lr=lr, beta1=b1, beta2=b2, eps=self.eps, bias1=1 - b1 ** self.step_count,
-                    bias2=1 - b2 ** self.step_count, grad_scale=1.0 / (self.world * self.grad_accum),
+                    bias2=1 - b2 ** self.step_count, grad_scale=scale,
                     max_norm=self.max_norm or 0.0, skip_norm=self.skip_norm or 0.0)
 
     def bucket_ready(self, b, stream=None):
@@ -484,6 +488,7 @@ class NcclAdamW:
         self.opt = torch.optim.AdamW(groups, lr=lr, betas=betas, eps=eps, fused=dev.type == "cuda")
         self.base_lrs = [g["lr"] / lr for g in groups]
         self.lr, self.max_norm, self.skip_norm, self.grad_accum = lr, max_norm, skip_norm, grad_accum
+        self.grad_scale_override = None
         self.bitwise_sync = bitwise_sync
         self.grads = GradBuffers(self.params)
         self.ctrl = torch.zeros(4, dtype=torch.float32, device=dev)
@@ -502,7 +507,7 @@ class NcclAdamW:
                 dist.broadcast(flat, src=0, group=self.group)
             else:
                 dist.all_reduce(flat, group=self.group)
-        flat.mul_(1.0 / (self.world * self.grad_accum))
+        flat.mul_(self.grad_scale_override or 1.0 / (self.world * self.grad_accum))
         self.grads.to_param_grads()
         gn = flat.norm()
         if self.max_norm and self.max_norm > 0:

@@ -28,7 +28,7 @@ class Trainer:
                  betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, decay_all=False, max_norm=1.0,
                  skip_norm=0.0, optimizer="fused", device=None, autocast_bf16=True, use_graphs=True,
                  overlap_buckets=True, process_group=None, seed=1337, engine="wavescan",
-                 engine_kwargs=None, model=None):
+                 engine_kwargs=None, model=None, rank_outlier_factor=0.0, rank_outlier_max=1):
         assert local_batch % micro_batch == 0, "local batch must be a whole number of micro-batches"
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
@@ -46,7 +46,11 @@ class Trainer:
             self.opt = FusedDPAdamW(groups, default_buckets(self.model), device=self.device, **common)
         else:
             self.opt = NcclAdamW(groups, **common)
-        self.overlap = overlap_buckets and optimizer == "fused" and self.opt.use_kernel and self.world > 1
+        # per-rank rejection needs every rank's LOCAL norm before anything is reduced: no early buckets then
+        self.rank_outlier = (rank_outlier_factor, rank_outlier_max) if rank_outlier_factor > 0 and self.world > 1 else None
+        self.group, self.rank_excluded = process_group, 0
+        self.overlap = (overlap_buckets and optimizer == "fused" and self.opt.use_kernel and self.world > 1
+                        and self.rank_outlier is None)
         self._side = torch.cuda.Stream(device=self.device) if self.overlap else None
         self._last_micro = False
         kw = dict(engine_kwargs or {})
@@ -90,7 +94,11 @@ class Trainer:
             self._loss_acc += self.engine.train_step(idx, tgt, sid=sid)
         if self._side is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._side)
+        keep_skip = self.opt.skip_norm
+        if self.rank_outlier is not None:
+            self._reject_outlier_ranks()
         self.opt.step(lr=lr)
+        self.opt.grad_scale_override, self.opt.skip_norm = None, keep_skip
         self.engine.pack()
         self.steps_done += 1
         if not read_loss:
@@ -99,6 +107,25 @@ class Trainer:
         if nb:
             torch.cuda.current_stream(self.device).synchronize()
         return float(self._loss_host)
+
+    def _reject_outlier_ranks(self):
+        """All-gather the local gradient norms; ranks far above the median zero their gradients and the
+        average is taken over the ranks kept (the same mask on every rank); too many outliers void the
+        step through the optimizer's skip predicate (train_hero_wave3d.py:894-920)."""
+        from .governors import rank_outlier_mask
+        flat = self.opt.grad_buffers().flat if not hasattr(self.opt, "flat_grads") else self.opt.flat_grads
+        mine = flat.norm().float().reshape(1)
+        allv = [torch.zeros_like(mine) for _ in range(self.world)]
+        dist.all_gather(allv, mine, group=self.group)
+        norms = [float(v) for v in torch.cat(allv).tolist()]
+        keep, void = rank_outlier_mask(norms, *self.rank_outlier)
+        self.rank_excluded = len(keep) - sum(keep)
+        if not keep[dist.get_rank(self.group)]:
+            flat.zero_()
+        if void:
+            self.opt.skip_norm = 1e-30                       # every finite norm exceeds it: the step is void
+        elif self.rank_excluded:
+            self.opt.grad_scale_override = 1.0 / (sum(keep) * self.accum)
 
     def h2d_bytes_per_step(self):
         return self.micro_batch * self.accum * (self.T + 1) * 8

@@ -99,6 +99,8 @@ class AsyncCheckpointWriter:
     on mutating the live tensors) and serialises it on a worker thread.  At most one
     write is pending; `submit` waits for the previous one."""
 
+    to_cpu = staticmethod(_to_cpu)      # host copy of a checkpoint dict (also used for resident snapshots)
+
     def __init__(self):
         self._q = queue.Queue(maxsize=1)
         self._err = None
