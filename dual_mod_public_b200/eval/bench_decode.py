@@ -1,0 +1,162 @@
+"""Incremental-decode benchmark and validator for the static-tape graph decoder.
+
+  python -m dual_mod_public_b200.eval.bench_decode                      # 1.3B shape, B=64, 2048 + 512
+  python -m dual_mod_public_b200.eval.bench_decode --validate --model tiny
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+      -m dual_mod_public_b200.eval.bench_decode                         # data-parallel: one batch per GPU
+
+Benchmark: random-init weights of the named shape, a prompt of uniform random ids prefilled token by token
+through the captured decode graph (the tape is recurrent: row t depends on the read at t), then `gen`
+greedy tokens.  The generated tokens are timed with CUDA events around the graph replays (max over
+ranks); printed per arm: ms per token, tokens/s (whole job) and the prefill time.  Arms: Dual-Mod, and
+the same-shape Transformer++ control (`attn_mode="vanilla"`: `refine_kv` returns the raw key/value, so
+the step is a plain KV-cache decoder step).
+
+Validator (`--validate`): graph decode against the eager `decode_step` loop and against one
+teacher-forced forward of the exact scan on the same tokens: arg-max agreement and max |delta logit|.
+
+Reference parity: lm/eval/validate_graph_decode.py:40-97 (validation protocol, per-token latency print),
+lm/eval/graph_decode.py:97-125 (greedy generate).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..config import DualModConfig, preset
+from ..models import DualModLM
+from .graph_decode import GraphDecoder
+
+
+def _dist():
+    world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29517")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def build(name, mode, device, max_len):
+    cfg = preset(name, max_seq_len=max_len) if name != "tiny" else DualModConfig(
+        d_model=128, n_layers=2, n_heads=2, vocab_size=256, max_seq_len=max_len, gate_bias_init=0.0)
+    cfg.attn_mode = mode
+    torch.manual_seed(1337)
+    dt = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
+    return cfg, DualModLM(cfg).to(device=device).eval(), dt
+
+
+def time_decode(model, B, prompt_len, gen, dtype, device, rank, world):
+    dec = GraphDecoder(model, B, prompt_len + gen, dtype=dtype).capture()
+    g = torch.Generator().manual_seed(99 + rank)
+    prompt = torch.randint(0, model.cfg.vocab_size, (B, prompt_len), generator=g).to(device)
+    cuda = torch.device(device).type == "cuda"
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    sync = (lambda: torch.cuda.synchronize()) if cuda else (lambda: None)
+    dec.reset()
+    sync()
+    if cuda:
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+    import time
+    t0 = time.perf_counter()
+    dec.prefill(prompt)
+    if cuda:
+        e1.record()
+    t1 = time.perf_counter()
+    for _ in range(gen):
+        dec.tok.copy_(dec.next)
+        dec.step()
+    if cuda:
+        e2.record()
+    sync()
+    t2 = time.perf_counter()
+    pre_ms, gen_ms = (e0.elapsed_time(e1), e1.elapsed_time(e2)) if cuda else ((t1 - t0) * 1e3, (t2 - t1) * 1e3)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([pre_ms, gen_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pre_ms, gen_ms = t.tolist()
+    return {"ms_per_token": gen_ms / gen, "tokens_per_s": world * B * gen / (gen_ms / 1e3),
+            "prefill_ms": pre_ms, "prefill_tokens_per_s": world * B * prompt_len / (pre_ms / 1e3),
+            "kernel_read": bool(dec.use_kernel), "graph": dec.graph is not None}
+
+
+@torch.no_grad()
+def validate(model, B, L, dtype, device):
+    """(argmax agreement graph vs eager, max |dlogit| graph vs eager, argmax agreement graph vs teacher
+    forcing, max |dlogit| vs teacher forcing) over L positions."""
+    cfg = model.cfg
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, cfg.vocab_size, (B, L), generator=g).to(device)
+    dec = GraphDecoder(model, B, L, dtype=dtype).capture()
+    dec.reset()
+    lg_graph = []
+    for t in range(L):
+        dec.tok.copy_(toks[:, t:t + 1])
+        dec.step()
+        lg_graph.append(dec.logits[:, 0].float().clone())
+    lg_graph = torch.stack(lg_graph, 1)
+    amp = torch.device(device).type == "cuda"
+    with torch.autocast(torch.device(device).type, dtype=torch.bfloat16, enabled=amp):
+        caches, lg_eager = model.decode_init(), []
+        for t in range(L):
+            lg_eager.append(model.decode_step(toks[:, t:t + 1], t, caches)[:, 0].float())
+        mode = cfg.attn_mode
+        if mode != "vanilla":
+            cfg.attn_mode = "sequential"
+        lg_tf = model(toks)[0].float()
+        cfg.attn_mode = mode
+    out = {"agree_tf": (lg_graph.argmax(-1) == lg_tf.argmax(-1)).float().mean().item(),
+           "max_dlogit_tf": (lg_graph - lg_tf).abs().max().item()}
+    if lg_eager:
+        lg_eager = torch.stack(lg_eager, 1)
+        out.update(agree_eager=(lg_graph.argmax(-1) == lg_eager.argmax(-1)).float().mean().item(),
+                   max_dlogit_eager=(lg_graph - lg_eager).abs().max().item())
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="dm_1p3b", help="preset name (dm_1p3b, dm_340m, ...) or 'tiny'")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--gen", type=int, default=512)
+    ap.add_argument("--validate", action="store_true")
+    ap.add_argument("--device", default="")
+    ap.add_argument("--arms", default="dualmod,vanilla")
+    args = ap.parse_args(argv)
+    rank, world, local = _dist()
+    device = args.device or (f"cuda:{local}" if torch.cuda.is_available() else "cpu")
+    out = {"metric": "decode_ms_per_token", "model": args.model, "batch_per_gpu": args.batch, "n_gpus": world,
+           "prompt": args.prompt, "gen": args.gen, "dtype": "bf16" if "cuda" in device else "fp32",
+           "data": "uniform random prompt ids, random-init weights"}
+    for arm in args.arms.split(","):
+        mode = "vanilla" if arm == "vanilla" else "sequential"
+        cfg, model, dt = build(args.model, mode, device, args.prompt + args.gen)
+        if args.validate:
+            out[arm] = validate(model, min(args.batch, 4), min(args.prompt + args.gen, 96), dt, device)
+        else:
+            out[arm] = {k: (round(v, 4) if isinstance(v, float) else v)
+                        for k, v in time_decode(model, args.batch, args.prompt, args.gen, dt, device, rank, world).items()}
+        del model
+        if "cuda" in device:
+            torch.cuda.empty_cache()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,279 @@
+"""Evaluation-harness adapter: a checkpoint behind the `lm_eval` model interface.
+
+  from dual_mod_public_b200.eval.lm_eval_adapter import DualModEval
+  lm = DualModEval("out/run/ckpt_latest.pt", tokenizer="data/llama2_tok")
+  lm.loglikelihood([("The capital of France is", " Paris")])        # [(logprob, is_greedy)]
+  lm.generate_until([("Q: 2+2=\nA:", {"until": ["\n"], "max_gen_toks": 8})])
+
+`DualModEval` subclasses `lm_eval.api.model.LM` when that package is importable (then
+`lm_eval.simple_evaluate(model=lm, tasks=[...])` works, see `run_lm_eval`), and is a plain class with
+the same three request methods otherwise.  Requests are `(context, continuation)` / `(context, gen_kwargs)`
+tuples or objects with `.args`.
+
+  likelihood   exact operator on whole sequences, batched in length buckets (lengths rounded up to
+               `EVAL_LEN_QUANT`, default 64, so batches share shapes); `engine_K` scores through the cell
+               engine at K sweeps instead of the eager scan (K = chunk is exact and much faster on a GPU)
+  generation   greedy through the static-tape `GraphDecoder` (one graph launch per token) on a GPU,
+               through `decode_step` otherwise; prompts longer than the context keep head + tail
+               (`GEN_TRUNC=head`) or the tail
+  cache        `EVAL_GEN_CACHE=<jsonl>`: finished generations are appended and served on restart;
+               `EVAL_CACHE_ONLY=1` answers uncached requests with "<UNCACHED>"
+  ranks        under torchrun the harness shards requests by `rank / world_size` (exposed as properties)
+
+Reference parity: lm/eval/lm_eval_adapter.py:69-781 (`DualModEval`: likelihood :244-273, generation
+:361-602, cache :117-140, distributed hooks :185-210; `Wave3DEval`: scoring through the engine at K
+:605-781), lm/eval/run_lm_eval.py (driver).
+"""
+
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+
+import torch
+import torch.nn.functional as F
+
+from ..utils.checkpoint import load_checkpoint, model_from_checkpoint
+
+try:                                                     # optional dependency
+    from lm_eval.api.model import LM as _Base
+except Exception:                                        # the harness is not installed: same methods, no base
+    _Base = object
+
+
+class ByteTokenizer:
+    """Fallback tokenizer: UTF-8 bytes shifted by 3 (0 pad, 1 bos, 2 eos).  Needs vocab >= 259."""
+    bos_token_id, eos_token_id = 1, 2
+
+    def encode(self, text, add_special_tokens=False):
+        return [b + 3 for b in text.encode("utf-8")]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return bytes(i - 3 for i in ids if i >= 3).decode("utf-8", errors="replace")
+
+
+def load_tokenizer(spec):
+    if spec is None or spec == "bytes":
+        return ByteTokenizer()
+    if hasattr(spec, "encode"):
+        return spec
+    from transformers import AutoTokenizer
+    return AutoTokenizer.from_pretrained(spec)
+
+
+def _args(req):
+    return req.args if hasattr(req, "args") else req
+
+
+def trunc_keep_head(toks, cap):
+    """Keep the head and a short tail when a prompt exceeds the context (answers of recall documents
+    sit near the start); plain tail truncation unless GEN_TRUNC=head."""
+    if len(toks) <= cap:
+        return toks
+    if os.environ.get("GEN_TRUNC", "tail") != "head":
+        return toks[-cap:]
+    keep_tail = min(128, cap // 4)
+    return toks[:cap - keep_tail] + toks[-keep_tail:]
+
+
+class DualModEval(_Base):
+    def __init__(self, ckpt, tokenizer=None, batch_rows=16, device=None, max_length=2048, ctx_len=None,
+                 engine_K=0, engine_chunk=64, model=None):
+        if _Base is not object:
+            super().__init__()
+        self.dev = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        if model is None:
+            ck = load_checkpoint(ckpt)
+            self.arch = os.environ.get("EVAL_ARCH") or ck.get("arch", "dualmod")
+            self.ckpt_engine_kwargs = ck.get("engine_kwargs")
+            model = model_from_checkpoint(ck, device=self.dev, ctx_len=ctx_len)
+        else:
+            self.arch, self.ckpt_engine_kwargs = "dualmod", None
+            model = model.to(self.dev)
+        self.model = model.eval()
+        cfg = self.model.cfg
+        if cfg.attn_mode not in ("vanilla", "static"):
+            cfg.attn_mode = "sequential"
+        self.max_length = min(ctx_len or max_length, cfg.max_seq_len)
+        self.tok = load_tokenizer(tokenizer)
+        self.bos = self.tok.bos_token_id if self.tok.bos_token_id is not None else 1
+        self.batch_rows, self.engine_K, self.engine_chunk = batch_rows, engine_K, engine_chunk
+        self.len_quant = int(os.environ.get("EVAL_LEN_QUANT", "64"))
+        self._engines = {}
+        self._rank, self._world_size = 0, 1
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            self._rank, self._world_size = dist.get_rank(), dist.get_world_size()
+        self._gcache_path = os.environ.get("EVAL_GEN_CACHE", "")
+        self._gcache_only = os.environ.get("EVAL_CACHE_ONLY", "0") == "1"
+        self._gcache = {}
+        if self._gcache_path and os.path.exists(self._gcache_path):
+            for line in open(self._gcache_path):
+                try:
+                    d = json.loads(line)
+                    self._gcache[d["k"]] = d["g"]
+                except ValueError:
+                    pass
+
+    # ---- harness hooks ----------------------------------------------------------------------------
+    @property
+    def rank(self):
+        return self._rank
+
+    @property
+    def world_size(self):
+        return self._world_size
+
+    @property
+    def eot_token_id(self):
+        return self.tok.eos_token_id
+
+    def tok_encode(self, s):
+        return list(self.tok.encode(s, add_special_tokens=False))
+
+    # ---- scoring -----------------------------------------------------------------------------------
+    def _amp(self):
+        t = torch.device(self.dev).type
+        return torch.autocast(t, dtype=torch.bfloat16, enabled=t == "cuda")
+
+    @torch.no_grad()
+    def _logits(self, x):
+        """x [B, L] -> logits [B, L, V] by the exact operator (or the engine at `engine_K`)."""
+        B, L = x.shape
+        cfg = self.model.cfg
+        use_engine = self.engine_K > 0 and cfg.attn_mode != "vanilla" and L % self.engine_chunk == 0
+        if not use_engine:
+            with self._amp():
+                return self.model(x)[0].float()
+        from ..engines.schedule import uniform_chunks
+        from ..engines.wavescan import WaveScanEngine
+        key = (B, L)
+        if key not in self._engines:
+            c = self.engine_chunk
+            self._engines[key] = WaveScanEngine(self.model, [uniform_chunks(L, c, min(c, self.engine_K))], B, L,
+                                                device=self.dev, keep_logits=True,
+                                                autocast_bf16=torch.device(self.dev).type == "cuda")
+            self._engines[key].pack()
+        eng = self._engines[key]
+        eng.forward(x)
+        return eng.logits.float()
+
+    def _score_rows(self, rows):
+        """rows: list of (tokens, n_continuation).  Returns [(sum logprob of the continuation, greedy?)] in
+        the given order; batches are formed inside length buckets."""
+        order = sorted(range(len(rows)), key=lambda i: len(rows[i][0]))
+        out = [None] * len(rows)
+        q = self.len_quant
+        for b0 in range(0, len(order), self.batch_rows):
+            ids = order[b0:b0 + self.batch_rows]
+            L = max(len(rows[i][0]) for i in ids)
+            L = min(self.max_length, -(-L // q) * q)
+            x = torch.zeros(len(ids), L, dtype=torch.long)
+            for r, i in enumerate(ids):
+                t = rows[i][0][-L:]
+                x[r, :len(t)] = torch.tensor(t)
+            logp = F.log_softmax(self._logits(x.to(self.dev)), dim=-1).cpu()
+            for r, i in enumerate(ids):
+                toks, n_c = rows[i]
+                toks = toks[-L:]
+                n_c = min(n_c, len(toks) - 1)
+                pos = torch.arange(len(toks) - n_c - 1, len(toks) - 1)
+                tgt = torch.tensor(toks[len(toks) - n_c:])
+                lp = logp[r, pos]
+                out[i] = (lp.gather(1, tgt[:, None]).sum().item(), bool((lp.argmax(-1) == tgt).all()))
+        return out
+
+    def loglikelihood(self, requests):
+        rows = []
+        for req in requests:
+            ctx, cont = _args(req)[:2]
+            c, k = ([self.bos] + self.tok_encode(ctx)) if ctx else [self.bos], self.tok_encode(cont)
+            rows.append((c + k, len(k)))
+        return self._score_rows(rows)
+
+    def loglikelihood_rolling(self, requests):
+        """Whole-document log-likelihood in windows of the context length (disjoint windows, each
+        conditioned on BOS only)."""
+        out = []
+        for req in requests:
+            toks = self.tok_encode(_args(req)[0])
+            tot, W = 0.0, self.max_length - 1
+            rows = [([self.bos] + toks[s:s + W], len(toks[s:s + W])) for s in range(0, max(1, len(toks)), W)]
+            tot = sum(lp for lp, _ in self._score_rows(rows))
+            out.append(tot)
+        return out
+
+    # ---- generation ---------------------------------------------------------------------------------
+    def _gen_key(self, prompt, until, max_new):
+        return hashlib.md5(json.dumps([prompt, until, max_new]).encode()).hexdigest()
+
+    @torch.no_grad()
+    def _greedy(self, prompt_ids, max_new, stop_strs):
+        """Greedy continuation of one prompt -> text (cut at the first stop string)."""
+        cap = self.max_length - max_new
+        ids = trunc_keep_head(prompt_ids, max(1, cap))
+        x = torch.tensor([ids], dtype=torch.long, device=self.dev)
+        gen = []
+        if torch.device(self.dev).type == "cuda":
+            from .graph_decode import GraphDecoder
+            P = len(ids) + max_new
+            key = ("dec", -(-P // 256) * 256)
+            if key not in self._engines:
+                self._engines[key] = GraphDecoder(self.model, 1, min(key[1], self.model.cfg.max_seq_len)).capture()
+            dec = self._engines[key]
+
+            def stop_fn(g_cpu):
+                text = self.tok.decode(g_cpu[0].tolist())
+                return torch.tensor([any(s in text for s in stop_strs)])
+            g, k = dec.generate(x, max_new, eos_id=self.tok.eos_token_id, stop_fn=stop_fn if stop_strs else None)
+            gen = g[0, :k].tolist()
+        else:
+            caches, logits = self.model.decode_init(), None
+            for t in range(x.shape[1]):
+                logits = self.model.decode_step(x[:, t:t + 1], t, caches)
+            for j in range(max_new):
+                nxt = int(logits[0, -1].argmax())
+                gen.append(nxt)
+                text = self.tok.decode(gen)
+                if nxt == self.tok.eos_token_id or any(s in text for s in stop_strs):
+                    break
+                logits = self.model.decode_step(torch.tensor([[nxt]], device=self.dev), x.shape[1] + j, caches)
+        text = self.tok.decode(gen)
+        for s in stop_strs:
+            if s in text:
+                text = text[:text.index(s)]
+        return text
+
+    def generate_until(self, requests):
+        out = []
+        for req in requests:
+            prompt, kw = _args(req)[:2]
+            kw = dict(kw or {})
+            until = kw.get("until") or []
+            until = [until] if isinstance(until, str) else list(until)
+            max_new = int(kw.get("max_gen_toks", kw.get("max_new_tokens", 64)))
+            key = self._gen_key(prompt, until, max_new)
+            if key in self._gcache:
+                out.append(self._gcache[key])
+                continue
+            if self._gcache_only:
+                out.append("<UNCACHED>")
+                continue
+            text = self._greedy([self.bos] + self.tok_encode(prompt), max_new, until)
+            self._gcache[key] = text
+            if self._gcache_path:
+                with open(self._gcache_path, "a") as f:
+                    f.write(json.dumps({"k": key, "g": text}) + "\n")
+            out.append(text)
+        return out
+
+
+def run_lm_eval(ckpt, tasks, tokenizer, num_fewshot=0, limit=None, out_path=None, **kw):
+    """Drive `lm_eval.simple_evaluate` with a checkpoint (needs the `lm_eval` package)."""
+    import lm_eval
+    lm = DualModEval(ckpt, tokenizer=tokenizer, **kw)
+    res = lm_eval.simple_evaluate(model=lm, tasks=list(tasks), num_fewshot=num_fewshot, limit=limit)
+    if out_path and lm.rank == 0:
+        json.dump(res["results"], open(out_path, "w"), indent=1)
+    return res

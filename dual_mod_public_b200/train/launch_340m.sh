@@ -1,0 +1,22 @@
+#!/usr/bin/env bash
+# 340M Dual-Mod run on one node (cell engine, c=64, K-ladder 8/16/32 with K=64 probes).
+#   DATA_BIN=/data/slimpj_train.bin VAL_BIN=/data/slimpj_val.bin OUT=out/dm340 NGPU=8 bash launch_340m.sh
+# Every knob is an environment variable with a default; extra flags are passed through ("$@").
+# Reference parity: lm/train_340m/scripts/launch_dm_d960.sh, scripts/launch_torchrun.sh.
+set -euo pipefail
+NGPU=${NGPU:-8}
+OUT=${OUT:-out/dm340}
+DATA_BIN=${DATA_BIN:-}
+VAL_BIN=${VAL_BIN:-}
+STEPS=${STEPS:-30000}
+WARMUP=${WARMUP:-1000}
+PORT=${PORT:-29500}
+export TORCH_NCCL_ASYNC_ERROR_HANDLING=1
+export PYTORCH_CUDA_ALLOC_CONF=${PYTORCH_CUDA_ALLOC_CONF:-expandable_segments:True}
+DATA_ARGS=(--synthetic)
+[ -n "$DATA_BIN" ] && DATA_ARGS=(--data_bin "$DATA_BIN")
+[ -n "$VAL_BIN" ] && DATA_ARGS+=(--val_bin "$VAL_BIN" --val_every 500)
+exec python -m torch.distributed.run --nnodes=1 --nproc-per-node "$NGPU" --master-addr 127.0.0.1 --master-port "$PORT" \
+  -m dual_mod_public_b200.train.train_lm --recipe 340m --out_dir "$OUT" --total_steps "$STEPS" \
+  --warmup_steps "$WARMUP" --weight_decay 0.01 --ckpt_every 500 --async_ckpt --resume auto --auto_rewind \
+  "${DATA_ARGS[@]}" "$@"
