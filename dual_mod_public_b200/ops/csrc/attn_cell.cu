@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
 // tail backward
 // =============================================================================================
 template <int DH, int C>
-__global__ void __launch_bounds__(C * 2) tail_bwd_kernel(
+__global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
     const float* __restrict__ dO, const bf16* __restrict__ q, TView vq, const bf16* __restrict__ ks,
     TView vks, const bf16* __restrict__ vr, TView vvr, const bf16* __restrict__ Kin, TView vKin,
     const bf16* __restrict__ Vin, TView vVin, const float* __restrict__ o_c,
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(C * 2) tail_bwd_kernel(
 // =============================================================================================
 
 template <int DH, int C>
-__global__ void __launch_bounds__(C * 2) prefix_fwd_kernel(
+__global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_fwd_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc,
     TView vc, float* __restrict__ o_c, float* __restrict__ lse_c, int H, int lo, int pos0,
     float scale, int window) {

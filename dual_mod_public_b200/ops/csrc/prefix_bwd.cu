@@ -20,7 +20,7 @@ namespace {
 // key side.  q_all / doc_all: [B, T, H, DH] bf16 (dense);  corr_all / lsec_all: [B, T, H] fp32.
 // Tape rows [pos0, pos0 + C) of Kc / Vc;  queries t in [q_start, T).
 template <int DH, int C>
-__global__ void __launch_bounds__(C * 2) prefix_dkv_kernel(
+__global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dkv_kernel(
     const bf16* __restrict__ q_all, const bf16* __restrict__ doc_all, const float* __restrict__ corr_all,
     const float* __restrict__ lsec_all, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc,
     float* __restrict__ dK, float* __restrict__ dV, int T, int H, int pos0, int q_start, int q_end,
@@ -29,9 +29,12 @@ __global__ void __launch_bounds__(C * 2) prefix_dkv_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sK = reinterpret_cast<bf16*>(smem_raw);
   bf16* sV = sK + C * P;
-  bf16* sQ = sV + C * P;            // 2 stages of [QT][P]
-  bf16* sdO = sQ + 2 * QT * P;      // 2 stages
-  bf16* sP = sdO + 2 * QT * P;      // [QT][PC]
+  // ST stages of query / d o_c tiles: one at head dim 64, so that four CTAs fit an SM (the other CTAs
+  // cover the load latency), two at head dim 128 where registers allow two CTAs anyway
+  constexpr int ST = DH <= 64 ? 1 : 2;
+  bf16* sQ = sV + C * P;            // ST stages of [QT][P]
+  bf16* sdO = sQ + ST * QT * P;     // ST stages
+  bf16* sP = sdO + ST * QT * P;     // [QT][PC]
   bf16* sdS = sP + QT * PC;
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -66,11 +69,12 @@ __global__ void __launch_bounds__(C * 2) prefix_dkv_kernel(
     GV[n][0] = GV[n][1] = GV[n][2] = GV[n][3] = 0.f;
   }
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int stage = tile & 1;
-    if (tile + 1 < n_tiles) {
+    const int stage = ST == 2 ? (tile & 1) : 0;
+    if (ST == 2 && tile + 1 < n_tiles) {
       issue(tile + 1, stage ^ 1);
       cp_async_wait<1>();
     } else {
+      if (ST == 1 && tile > 0) issue(tile, 0);       // the single buffer was released by the sync below
       cp_async_wait<0>();
     }
     __syncthreads();
@@ -158,12 +162,13 @@ __global__ void __launch_bounds__(C * 2) prefix_dkv_kernel(
 // query side for one cell.  q: [B, C, H, DH] view; do_c: bf16 view with the same strides class;
 // lse_c / corr: dense [B, C, H] fp32; dq_acc: dense [B, C, H, DH] fp32, accumulated into.
 template <int DH, int C>
-__global__ void __launch_bounds__(C * 2) prefix_dq_kernel(
+__global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ do_c, TView vdo,
     const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc, const float* __restrict__ lse_c,
     const float* __restrict__ corr, float* __restrict__ dq_acc, int H, int lo, int pos0, float scale,
     int window) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = KT / 8;
+  constexpr int ST = 2;            // key / value tiles are double-buffered
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
   bf16* sdO = sQ + C * P;
@@ -199,11 +204,12 @@ __global__ void __launch_bounds__(C * 2) prefix_dq_kernel(
 #pragma unroll
   for (int n = 0; n < DH / 8; ++n) A[n][0] = A[n][1] = A[n][2] = A[n][3] = 0.f;
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int stage = tile & 1;
-    if (tile + 1 < n_tiles) {
+    const int stage = ST == 2 ? (tile & 1) : 0;
+    if (ST == 2 && tile + 1 < n_tiles) {
       issue(tile + 1, stage ^ 1);
       cp_async_wait<1>();
     } else {
+      if (ST == 1 && tile > 0) issue(tile, 0);       // the single buffer was released by the sync below
       cp_async_wait<0>();
     }
     __syncthreads();
@@ -284,7 +290,8 @@ int dmb_prefix_dkv(const void* q_all, const void* doc_all, const float* corr_all
                    const void* Kc, const void* Vc, TView vc, float* dK, float* dV, int B, int T, int c, int H,
                    int dh, int pos0, int q_start, int q_end, float scale, int window, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
-    size_t smem = (((size_t)2 * C + 4 * C) * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
+    constexpr int ST = DH <= 64 ? 1 : 2;
+    size_t smem = (((size_t)2 * C + 2 * ST * C) * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
     auto kern = prefix_dkv_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q_all, (const bf16*)doc_all, corr_all, lsec_all,
