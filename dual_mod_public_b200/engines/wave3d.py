@@ -28,11 +28,15 @@ lower-right-causal attention call per step does (wave3d_x.py `_AttendGroup`).  O
 before i ("near") are re-read per sweep.  Attention work per chunk drops from K full-prefix passes to one
 full-prefix pass plus K passes over at most (K-1)*C + C keys.
 
-Backward.  Reverse over steps.  The tape is rolled back one version per step (every version of the
-current layer is kept from a forward re-run, so memory is one layer's worth), gradients of tape rows
-wait in a pending fp32 buffer until the sweep that produced that version is reached, far reads are
-back-propagated owner-computes once per chunk (`prefix_dkv` over all far readers), near reads by a
-gather per (step, key chunk).  No atomics; every accumulation has one owner.
+One launch per op and step.  All chunks of the window sweep at once: the window's rows are contiguous in
+time, so the packed GEMM, the refine chain and the norm backward see one [B, G*C, d] block, and the
+attention kernels take a group dimension (grid z = chunk of the window, each with its own key range).
+
+Backward.  Reverse over steps.  A forward re-run of the layer keeps what every step read from the tape's
+window (so rolling the tape back one step is one block copy; memory is one layer's worth) and every
+step's sweep state; gradients of tape rows wait in a pending fp32 buffer until the step that wrote that
+version is reached; far reads are back-propagated owner-computes once per chunk (`prefix_dkv` over all
+far readers), near reads by a gather per (step, key chunk).  No atomics; every accumulation has one owner.
 
 `wavefront_layer_reference` is the same operator in plain autograd torch through `refine_kv`
 (any configuration); it is the oracle of the fused path and the generic backend.
@@ -139,16 +143,31 @@ class Wave3DEngine(WaveScanEngine):
             # gradient of the tape rows' current version, waiting for the sweep that wrote it
             self.dKp = z(B, T, h, dh, dt=torch.float32)
             self.dVp = z(B, T, h, dh, dt=torch.float32)
+            # far partial of every chunk (computed when it enters) and the accumulators of its gradient
+            self.ofar_all = z(B, T, h, dh, dt=torch.float32)
+            self.lsefar_all = z(B, T, h, dt=torch.float32)
+            self.DOf_all = z(B, T, h, dh, dt=torch.float32)
+            self.DLf_all = z(B, T, h, dt=torch.float32)
             self._versions = {}
 
-    def _version_store(self, K):
-        """Tape rows after 1 .. K-1 refinements of the layer in flight: [K-1, B, T, h, dh] x 2."""
+    def _window_store(self, K):
+        """What every step read from the tape's window (K_in, V_in of all window chunks, the entering chunk
+        raw): [steps, B, K*C, h, dh] x 2 for the layer in flight.  Rolling the tape back one step in the
+        backward is one copy of a block."""
         if K not in self._versions:
             cfg = self.cfg
-            shape = (max(1, K - 1), self.B, self.T, cfg.n_heads, cfg.head_dim)
+            shape = (self.T // self.C + K - 1, self.B, K * self.C, cfg.n_heads, cfg.head_dim)
             self._versions[K] = (torch.zeros(shape, dtype=self.act, device=self.device),
                                  torch.zeros(shape, dtype=self.act, device=self.device))
         return self._versions[K]
+
+    def _step_offsets(self, K):
+        """Row offset of every step's block in the (d logits, u) stashes of the deferred weight gradient."""
+        n, offs, tot = self.T // self.C, [], 0
+        for s in range(n + K - 1):
+            offs.append(tot)
+            tot += self.B * self.C * (min(s, n - 1) - max(0, s - K + 1) + 1)
+        return offs
 
     # ---- generic backend: autograd through the plain-torch operator (any configuration) -------------
     def _generic_forward(self, sid, have_targets):
@@ -187,50 +206,44 @@ class Wave3DEngine(WaveScanEngine):
         G.get(m.tok_emb.weight).index_add_(0, self.idx.view(-1), dx.reshape(-1, self.cfg.d_model).float())
 
     # ---- forward ----------------------------------------------------------------------------------------
-    def _wave_step_chunk(self, S, i, m, K, far, verK=None, verV=None, save=None):
-        """One sweep of chunk i (its m-th, 0-based) against the tape as it stands.  Writes the new rows
-        in place; with `save` also records what the backward needs."""
+    def _wave_step(self, S, s, K, save=None, win=None):
+        """Step s of one layer: the chunk entering (if any) computes its far partial and puts its raw rows
+        on the tape; then ALL window chunks do one sweep in one launch per op (window tensors are
+        [B, G*C, ...], G = chunks in the window) and their new rows replace the old ones."""
         ops, cfg = self.ops, self.cfg
         B, h, dh, d, C = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model, self.C
-        r = slice(i * C, (i + 1) * C)
-        qc, ksc, vc4 = S.q_r[:, r], S.kself_r[:, r], S.v4[:, r]
-        fe = max(0, i - K + 1) * C                              # far rows: [0, fe), near rows: [fe, i*C)
-        if m == 0:
-            far[i] = ops.prefix_fwd(qc, S.Kc, S.Vc, fe, S.scale, 0)
-            K_in, V_in = ksc, vc4
-        else:
-            K_in, V_in = S.Kc[:, r], S.Vc[:, r]
-        o_f, lse_f = far[i]
-        if i * C - fe > 0:
-            o_n, lse_n = ops.prefix_fwd(qc, S.Kc[:, fe:], S.Vc[:, fe:], i * C - fe, S.scale, 0)
-            o_c, lse_c, w_f, w_n = _merge_partials(o_f, lse_f, o_n, lse_n)
-        else:
-            o_n = lse_n = w_f = w_n = None
-            o_c, lse_c = o_f, lse_f
-        o, lse, ssq = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, S.scale, 0)
-        raw = ops.linear(o.reshape(B, C, d), S.P.W_pack)
-        K_new, V_new = ops.refine_fwd(raw, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h, S.pin)
-        S.Kc[:, r] = K_new
-        S.Vc[:, r] = V_new
-        if verK is not None and m + 1 <= K - 1:
-            verK[m][:, r] = K_new                              # version after m+1 refinements
-            verV[m][:, r] = V_new
-        if m == K - 1 and getattr(S, "o_all", None) is not None:
-            S.o_all[:, r] = o.reshape(B, C, d)
+        n = self.T // C
+        lo, hi = max(0, s - K + 1), min(s, n - 1)
+        G, w = hi - lo + 1, slice(lo * C, (hi + 1) * C)
+        if s < n:
+            r = slice(s * C, (s + 1) * C)
+            o_f, lse_f = ops.prefix_fwd(S.q_r[:, r], S.Kc, S.Vc, max(0, s - K + 1) * C, S.scale, 0)
+            self.ofar_all[:, r] = o_f
+            self.lsefar_all[:, r] = lse_f
+            S.Kc[:, r] = S.kself_r[:, r]
+            S.Vc[:, r] = S.v4[:, r]
+        K_in, V_in = S.Kc[:, w], S.Vc[:, w]
+        if win is not None:
+            win[0][s][:, :G * C] = K_in
+            win[1][s][:, :G * C] = V_in
+        qw = S.q_r[:, w]
+        o_n, lse_n = ops.win_near_fwd(qw, S.Kc, S.Vc, lo * C, (lo - K + 1) * C, C, S.scale)
+        o_c, lse_c, w_f, w_n = ops.merge_partials(self.ofar_all[:, w], self.lsefar_all[:, w], o_n, lse_n)
+        o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale)
+        raw = ops.linear(o.reshape(B, G * C, d), S.P.W_pack)
+        K_new, V_new = ops.refine_fwd(raw, ssq, S.glx[:, w], S.k[:, w], S.v[:, w], S.cos[w], S.sin[w], h, S.pin)
+        S.Kc[:, w] = K_new
+        S.Vc[:, w] = V_new
+        if s - K + 1 >= 0 and getattr(S, "o_all", None) is not None:
+            S.o_all[:, lo * C:(lo + 1) * C] = o[:, :C].reshape(B, C, d)      # chunk lo's K-th read is final
         if save is not None:
-            save[(i, m)] = (o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n)
+            save[s] = (o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n)
+        self.stats["fwd_cells"] += G
 
     def _cells_fwd(self, li, sid, S, keep):
-        K, C = self.ladder[sid], self.C
-        n = self.T // C
-        far = {}
-        for s in range(n + K - 1):
-            lo, hi = max(0, s - K + 1), min(s, n - 1)
-            for i in range(hi, lo - 1, -1):                     # descending: lower chunks are still at step s-1
-                self._wave_step_chunk(S, i, s - i, K, far)
-            if s - K + 1 >= 0:
-                far.pop(s - K + 1, None)
-            self.stats["fwd_cells"] += hi - lo + 1
+        K = self.ladder[sid]
+        for s in range(self.T // self.C + K - 1):
+            self._wave_step(S, s, K)
 
     # ---- backward -------------------------------------------------------------------------------------------
     def _cells_bwd(self, li, sid, S, kept):
@@ -239,101 +252,79 @@ class Wave3DEngine(WaveScanEngine):
         K, n = self.ladder[sid], self.T // self.C
         f32, dev = torch.float32, self.device
         Kc, Vc, scale = S.Kc, S.Vc, S.scale
-        dcg_stash, u_stash, stash_off = self._stash_for(sid)
-        verK, verV = self._version_store(K)
-        # ---- forward re-run of this layer, keeping every version and every sweep's state
-        far, save = {}, {}
-        for s in range(n + K - 1):
-            lo, hi = max(0, s - K + 1), min(s, n - 1)
-            for i in range(hi, lo - 1, -1):
-                self._wave_step_chunk(S, i, s - i, K, far, verK, verV, save)
-        self.dKp.zero_()
-        self.dVp.zero_()
-        dq_c, DOf, DLf = {}, {}, {}
+        dcg_stash, u_stash, _ = self._stash_for(sid)
+        offs = self._step_offsets(K)
+        win = self._window_store(K)
         rows = lambda i: slice(i * C, (i + 1) * C)
+        # ---- forward re-run of this layer, keeping what every step read and produced
+        save = {}
+        for s in range(n + K - 1):
+            self._wave_step(S, s, K, save, win)
+        for t in (self.dKp, self.dVp, self.DOf_all, self.DLf_all):
+            t.zero_()
         for s in range(n + K - 2, -1, -1):
             lo, hi = max(0, s - K + 1), min(s, n - 1)
+            G, w, j = hi - lo + 1, slice(lo * C, (hi + 1) * C), s - K + 1
             # the chunk whose commit is this step: gather the far reads of its final rows (still on the tape)
             far_grad = None
-            j = s - K + 1
             if j >= 0 and (j + K) * C < self.T:
                 far_grad = ops.prefix_dkv(S.q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
                                           j * C, C, (j + K) * C, scale, 0)
-            # roll the window back to the tape of step s-1
-            for i in range(lo, hi + 1):
-                m, r = s - i, rows(i)
-                if m >= 1:
-                    Kc[:, r] = verK[m - 1][:, r]
-                    Vc[:, r] = verV[m - 1][:, r]
-            for i in range(lo, hi + 1):
-                m, r = s - i, rows(i)
-                qc, ksc, vc4 = S.q_r[:, r], S.kself_r[:, r], S.v4[:, r]
-                o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n = save.pop((i, m))
-                o_f, lse_f = far[i]
-                dK_out, dV_out = self.dKp[:, r].clone(), self.dVp[:, r].clone()
-                if m == K - 1:
-                    if far_grad is not None:
-                        dK_out += far_grad[0]
-                        dV_out += far_grad[1]
-                    dq_c[i] = torch.zeros(B, C, h, dh, dtype=f32, device=dev)
-                    DOf[i] = torch.zeros(B, C, h, dh, dtype=f32, device=dev)
-                    DLf[i] = torch.zeros(B, C, h, dtype=f32, device=dev)
-                off = stash_off[(i, m)]
-                dcg = dcg_stash[off:off + B * C].view(B, C, 4 * d)
-                ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, C, d), S.glx[:, r], S.k[:, r], S.v[:, r],
-                               S.cos[r], S.sin[r], S.pin, S.dk[:, r], S.dv[:, r], S.dglx[:, r], dcg,
-                               u_stash[off:off + B * C].view(B, C, d))
-                du = ops.linear_dx(dcg, S.P.W_pack)
-                d_o = ops.rmsn_bwd(du, o.reshape(B, C, d), ssq,
-                                   residual=S.dO_all[:, r].float().reshape(B, C, d) if m == K - 1 else None
-                                   ).view(B, C, h, dh)
-                do_c = torch.zeros(B, C, h, dh, dtype=f32, device=dev)
-                dlse_c = torch.zeros(B, C, h, dtype=f32, device=dev)
-                K_in, V_in = (ksc, vc4) if m == 0 else (Kc[:, r], Vc[:, r])
-                dK_in, dV_in = ops.tail_bwd(d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, 0,
-                                            dq_c[i], S.dks_r[:, r], S.dv4[:, r], do_c, dlse_c)
-                if m == 0:                                      # the first sweep read the raw rows
-                    S.dks_r[:, r] += dK_in
-                    S.dv4[:, r] += dV_in
-                    self.dKp[:, r] = 0
-                    self.dVp[:, r] = 0
-                else:
-                    self.dKp[:, r] = dK_in
-                    self.dVp[:, r] = dV_in
-                # split d(o_c, lse_c) between the far and the near partial
-                if o_n is None:
-                    DOf[i] += do_c
-                    DLf[i] += dlse_c
-                else:
-                    g_f = (do_c * (o_f - o_c)).sum(-1) + dlse_c
-                    g_n = (do_c * (o_n - o_c)).sum(-1) + dlse_c
-                    DOf[i] += w_f.unsqueeze(-1) * do_c
-                    DLf[i] += w_f * g_f
-                    do_n = w_n.unsqueeze(-1) * do_c
-                    corr_n = (do_n * o_n).sum(-1) - w_n * g_n
-                    self.docn_all[:, r] = do_n
-                    self.corrn_all[:, r] = corr_n
-                    self.lsen_all[:, r] = lse_n
-                    fe = max(0, i - K + 1) * C
-                    ops.prefix_dq(qc, Kc[:, fe:], Vc[:, fe:], i * C - fe, scale, 0, lse_n,
-                                  self.docn_all[:, r], corr_n.contiguous(), dq_c[i])
-                if m == 0:                                      # every sweep of chunk i has been processed
-                    corr_f = (DOf[i] * o_f).sum(-1) - DLf[i]
-                    self.doc_all[:, r] = DOf[i]
-                    self.corr_all[:, r] = corr_f
-                    self.lsec_all[:, r] = lse_f
-                    fe = max(0, i - K + 1) * C
-                    ops.prefix_dq(qc, Kc, Vc, fe, scale, 0, lse_f, self.doc_all[:, r], corr_f.contiguous(),
-                                  dq_c[i])
-                    S.dq_r[:, r] = dq_c.pop(i)
-                    del DOf[i], DLf[i], far[i]
-                self.stats["bwd_cells"] += 1
-            # near reads of this step, key side: chunk j was read by window chunks (j, j+K-1]
-            for j in range(max(0, lo - K + 1), hi):
-                q0, q1 = max(j + 1, lo) * C, min(j + K, hi + 1) * C
-                if q0 < q1:
-                    dK, dV = ops.prefix_dkv(S.q_r, self.docn_all, self.corrn_all, self.lsen_all, Kc, Vc,
-                                            j * C, C, q0, scale, 0, q_end=q1)
-                    self.dKp[:, rows(j)] += dK
-                    self.dVp[:, rows(j)] += dV
+            Kc[:, w] = win[0][s][:, :G * C]                     # the tape as step s read it
+            Vc[:, w] = win[1][s][:, :G * C]
+            o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n = save.pop(s)
+            dK_out, dV_out = self.dKp[:, w].clone(), self.dVp[:, w].clone()
+            if far_grad is not None:
+                dK_out[:, :C] += far_grad[0]
+                dV_out[:, :C] += far_grad[1]
+            nr = B * G * C
+            dcg = dcg_stash[offs[s]:offs[s] + nr].view(B, G * C, 4 * d)
+            ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, G * C, d), S.glx[:, w], S.k[:, w], S.v[:, w],
+                           S.cos[w], S.sin[w], S.pin, S.dk[:, w], S.dv[:, w], S.dglx[:, w], dcg,
+                           u_stash[offs[s]:offs[s] + nr].view(B, G * C, d))
+            du = ops.linear_dx(dcg, S.P.W_pack)
+            d_o = ops.rmsn_bwd(du, o.reshape(B, G * C, d), ssq, residual=None)
+            if j >= 0:                                          # chunk j's K-th read is the layer's output
+                d_o[:, :C] += S.dO_all[:, rows(j)].reshape(B, C, d)
+            d_o = d_o.view(B, G * C, h, dh)
+            do_c = torch.zeros(B, G * C, h, dh, dtype=f32, device=dev)
+            dlse_c = torch.zeros(B, G * C, h, dtype=f32, device=dev)
+            dq_w = torch.zeros(B, G * C, h, dh, dtype=f32, device=dev)
+            dK_in, dV_in = ops.win_tail_bwd(d_o, S.q_r[:, w], S.kself_r[:, w], S.v4[:, w], Kc[:, w], Vc[:, w],
+                                            o_c, lse_c, o, lse, C, scale, dq_w, S.dks_r[:, w], S.dv4[:, w],
+                                            do_c, dlse_c)
+            self.dKp[:, w] = dK_in                              # gradient of what step s read = rows of step s-1
+            self.dVp[:, w] = dV_in
+            if s < n:                                           # chunk s entered here: it read its raw rows
+                r = rows(s)
+                S.dks_r[:, r] += self.dKp[:, r]
+                S.dv4[:, r] += self.dVp[:, r]
+                self.dKp[:, r] = 0
+                self.dVp[:, r] = 0
+            # split d(o_c, lse_c) between the far and the near partial
+            ops.split_partials(do_c, dlse_c, self.ofar_all[:, w], o_c, o_n, lse_n, w_f, w_n, self.DOf_all[:, w],
+                               self.DLf_all[:, w], self.docn_all[:, w], self.corrn_all[:, w], self.lsen_all[:, w])
+            corr_n = self.corrn_all[:, w].contiguous()
+            ops.win_near_dq(S.q_r[:, w], Kc, Vc, lo * C, (lo - K + 1) * C, C, scale, lse_n.contiguous(),
+                            self.docn_all[:, w], corr_n, dq_w)
+            S.dq_r[:, w] += dq_w
+            if s < n:                                           # every sweep of chunk s has been processed
+                r, fe = rows(s), max(0, s - K + 1) * C
+                corr_f = ((self.DOf_all[:, r] * self.ofar_all[:, r]).sum(-1) - self.DLf_all[:, r]).contiguous()
+                self.doc_all[:, r] = self.DOf_all[:, r]
+                self.corr_all[:, r] = corr_f
+                self.lsec_all[:, r] = self.lsefar_all[:, r]
+                dq_s = torch.zeros(B, C, h, dh, dtype=f32, device=dev)
+                ops.prefix_dq(S.q_r[:, r], Kc, Vc, fe, scale, 0, self.lsefar_all[:, r].contiguous(),
+                              self.doc_all[:, r], corr_f, dq_s)
+                S.dq_r[:, r] += dq_s
+            # near reads of this step, key side: chunk jk was read by the window chunks in (jk, jk+K-1]
+            j0 = max(0, lo - K + 1)
+            if hi > j0:
+                wk = slice(j0 * C, hi * C)
+                dK, dV = ops.win_near_dkv(S.q_r, self.docn_all, self.corrn_all, self.lsen_all, Kc, Vc, j0, hi - j0, C,
+                                          lo * C, (hi + 1) * C, K * C, scale)
+                self.dKp[:, wk] += dK
+                self.dVp[:, wk] += dV
+            self.stats["bwd_cells"] += G
         return dcg_stash, u_stash

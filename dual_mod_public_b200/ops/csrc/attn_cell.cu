@@ -14,19 +14,27 @@ namespace {
 // =============================================================================================
 // tail forward
 // =============================================================================================
+// Groups (gridDim.z > 1): one launch covers G consecutive chunks of the same sequences.  Strided tensors
+// (slices of [B, T, ...] buffers) advance `grow` rows per group; dense tensors are [B, G, C, ...]
+// (equivalently [B, G*C, ...]), indexed with bd = b * G + group.
 template <int DH, int C>
 __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ ks, TView vks,
     const bf16* __restrict__ vr, TView vvr, const bf16* __restrict__ Kin, TView vKin,
     const bf16* __restrict__ Vin, TView vVin, const float* __restrict__ o_c,
     const float* __restrict__ lse_c, bf16* __restrict__ o, float* __restrict__ lse,
-    float* __restrict__ ssq, int H, float scale, int window) {
+    float* __restrict__ ssq, int H, float scale, int window, int grow) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = C / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
   bf16* sK = sQ + C * P;
   bf16* sV = sK + C * P;
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bd = b * gridDim.z + blockIdx.z;
+  {
+    const long long go = (long long)blockIdx.z * grow;
+    q += go * vq.rs; ks += go * vks.rs; vr += go * vvr.rs; Kin += go * vKin.rs; Vin += go * vVin.rs;
+  }
   const int g = lane >> 2, t = lane & 3;
   const long long hoff = (long long)h * DH;
   load_tile_bf16<DH, NT>(sQ, q + b * vq.bs + hoff, vq.rs, C, tid);
@@ -55,7 +63,7 @@ __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
   }
   // rows owned by this thread: i0 = row0 + g, i1 = i0 + 8
   const int i0 = row0 + g, i1 = i0 + 8;
-  const long long orow0 = ((long long)(b * C + i0) * H + h), orow1 = ((long long)(b * C + i1) * H + h);
+  const long long orow0 = ((long long)(bd * C + i0) * H + h), orow1 = ((long long)(bd * C + i1) * H + h);
   float ss0 = quad_dot_bf16<DH>(sQ + i0 * P, ks + b * vks.bs + i0 * vks.rs + hoff, t) * scale;
   float ss1 = quad_dot_bf16<DH>(sQ + i1 * P, ks + b * vks.bs + i1 * vks.rs + hoff, t) * scale;
   const float lc0 = lse_c[orow0], lc1 = lse_c[orow1];
@@ -150,7 +158,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
     const float* __restrict__ lse_c, const bf16* __restrict__ o, const float* __restrict__ lse,
     float* __restrict__ dq_acc, float* __restrict__ dks_acc, TView vdks, float* __restrict__ dv_acc,
     TView vdv, float* __restrict__ doc_acc, float* __restrict__ dlsec_acc, float* __restrict__ dKin,
-    float* __restrict__ dVin, int H, float scale, int window) {
+    float* __restrict__ dVin, int H, float scale, int window, int grow) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = C / 8, PC = C + 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
@@ -162,8 +170,14 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const long long hoff = (long long)h * DH;
+  const int bd = b * gridDim.z + blockIdx.z;
+  {
+    const long long go = (long long)blockIdx.z * grow;
+    q += go * vq.rs; ks += go * vks.rs; vr += go * vvr.rs; Kin += go * vKin.rs; Vin += go * vVin.rs;
+    dks_acc += go * vdks.rs; dv_acc += go * vdv.rs;
+  }
   const long long dense_rs = (long long)H * DH;  // contiguous [B,C,H,DH] tensors
-  const long long dense_b = (long long)b * C * dense_rs + hoff;
+  const long long dense_b = (long long)bd * C * dense_rs + hoff;
   load_tile_bf16<DH, NT>(sQ, q + b * vq.bs + hoff, vq.rs, C, tid);
   load_tile_bf16<DH, NT>(sK, Kin + b * vKin.bs + hoff, vKin.rs, C, tid);
   load_tile_bf16<DH, NT>(sV, Vin + b * vVin.bs + hoff, vVin.rs, C, tid);
@@ -196,7 +210,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
       }
     }
   }
-  const long long orow0 = ((long long)(b * C + i0) * H + h), orow1 = ((long long)(b * C + i1) * H + h);
+  const long long orow0 = ((long long)(bd * C + i0) * H + h), orow1 = ((long long)(bd * C + i1) * H + h);
   const float* dO0 = dO + orow0 * DH;
   const float* dO1 = dO + orow1 * DH;
   const bf16* ks0 = ks + b * vks.bs + i0 * vks.rs + hoff;
@@ -348,13 +362,18 @@ template <int DH, int C>
 __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_fwd_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc,
     TView vc, float* __restrict__ o_c, float* __restrict__ lse_c, int H, int lo, int pos0,
-    float scale, int window) {
+    float scale, int window, int grow) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = KT / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
   bf16* sK = sQ + C * P;        // 2 stages
   bf16* sV = sK + 2 * KT * P;   // 2 stages
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bd = b * gridDim.z + blockIdx.z;
+  // group z reads the tape rows [max(0, lo + z * grow), pos0 + z * grow) for the queries of chunk z
+  q += (long long)blockIdx.z * grow * vq.rs;
+  pos0 += blockIdx.z * grow;
+  lo = max(0, lo + (int)blockIdx.z * grow);
   const int g = lane >> 2, t = lane & 3;
   const long long hoff = (long long)h * DH;
   const bf16* Kb = Kc + b * vc.bs + hoff;
@@ -464,7 +483,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_fwd_kernel(
     }
     __syncthreads();
   }
-  const long long orow0 = ((long long)(b * C + i0) * H + h), orow1 = ((long long)(b * C + i1) * H + h);
+  const long long orow0 = ((long long)(bd * C + i0) * H + h), orow1 = ((long long)(bd * C + i1) * H + h);
   const float r0 = l0 > 0.f ? 1.f / l0 : 0.f, r1 = l1 > 0.f ? 1.f / l1 : 0.f;
   float* out0 = o_c + orow0 * DH;
   float* out1 = o_c + orow1 * DH;
@@ -487,14 +506,14 @@ extern "C" {
 int dmb_tail_fwd(const void* q, TView vq, const void* ks, TView vks, const void* vr, TView vvr,
                  const void* Kin, TView vKin, const void* Vin, TView vVin, const float* o_c,
                  const float* lse_c, void* o, float* lse, float* ssq, int B, int c, int H, int dh,
-                 float scale, int window, cudaStream_t st) {
+                 float scale, int window, int G, int grow, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = (size_t)3 * C * Tile<DH>::PITCH * sizeof(bf16);
     auto kern = tail_fwd_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
-    kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr, vvr,
-                                         (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c, lse_c,
-                                         (bf16*)o, lse, ssq, H, scale, window);
+    kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr, vvr,
+                                            (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c, lse_c,
+                                            (bf16*)o, lse, ssq, H, scale, window, grow);
   })
   DMB_CHECK_LAUNCH();
   return 0;
@@ -505,15 +524,15 @@ int dmb_tail_bwd(const float* dO, const void* q, TView vq, const void* ks, TView
                  const float* o_c, const float* lse_c, const void* o, const float* lse, float* dq_acc,
                  float* dks_acc, TView vdks, float* dv_acc, TView vdv, float* doc_acc,
                  float* dlsec_acc, float* dKin, float* dVin, int B, int c, int H, int dh, float scale,
-                 int window, cudaStream_t st) {
+                 int window, int G, int grow, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)4 * C * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
     auto kern = tail_bwd_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
-    kern<<<dim3(H, B), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
-                                         vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
-                                         lse_c, (const bf16*)o, lse, dq_acc, dks_acc, vdks, dv_acc, vdv,
-                                         doc_acc, dlsec_acc, dKin, dVin, H, scale, window);
+    kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
+                                            vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
+                                            lse_c, (const bf16*)o, lse, dq_acc, dks_acc, vdks, dv_acc, vdv,
+                                            doc_acc, dlsec_acc, dKin, dVin, H, scale, window, grow);
   })
   DMB_CHECK_LAUNCH();
   return 0;
@@ -521,13 +540,13 @@ int dmb_tail_bwd(const float* dO, const void* q, TView vq, const void* ks, TView
 
 int dmb_prefix_fwd(const void* q, TView vq, const void* Kc, const void* Vc, TView vc, float* o_c,
                    float* lse_c, int B, int c, int H, int dh, int lo, int pos0, float scale,
-                   int window, cudaStream_t st) {
+                   int window, int G, int grow, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)C + 4 * KT) * Tile<DH>::PITCH * sizeof(bf16);
     auto kern = prefix_fwd_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
-    kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)Kc, (const bf16*)Vc, vc, o_c,
-                                         lse_c, H, lo, pos0, scale, window);
+    kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)Kc, (const bf16*)Vc, vc, o_c,
+                                         lse_c, H, lo, pos0, scale, window, grow);
   })
   DMB_CHECK_LAUNCH();
   return 0;

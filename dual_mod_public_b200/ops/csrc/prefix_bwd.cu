@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dkv_kernel(
     const bf16* __restrict__ q_all, const bf16* __restrict__ doc_all, const float* __restrict__ corr_all,
     const float* __restrict__ lsec_all, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc,
     float* __restrict__ dK, float* __restrict__ dV, int T, int H, int pos0, int q_start, int q_end,
-    float scale, int window) {
+    float scale, int window, int grow, int span) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = C / 8, PC = C + 8, QT = C;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sK = reinterpret_cast<bf16*>(smem_raw);
@@ -38,6 +38,12 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dkv_kernel(
   bf16* sdS = sP + QT * PC;
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
+  // groups (gridDim.z > 1): key chunk z of a run of consecutive chunks; its readers are the query rows
+  // [max(q_start, chunk end), min(q_end, chunk start + span)); outputs are dense [B, G, C, H, DH]
+  const int bd = b * gridDim.z + blockIdx.z;
+  pos0 += blockIdx.z * grow;
+  q_start = max(q_start, pos0 + C);
+  q_end = min(q_end, pos0 + span);
   const long long hoff = (long long)h * DH, rs = (long long)H * DH;
   const bf16* Qb = q_all + (long long)b * T * rs + hoff;
   const bf16* Ob = doc_all + (long long)b * T * rs + hoff;
@@ -144,10 +150,10 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dkv_kernel(
     __syncthreads();   // sP / sdS and this stage's tiles are free again
   }
   const int ka = row0 + g, kb = ka + 8;
-  float* k0p = dK + (((long long)b * C + ka) * H + h) * DH;
-  float* k1p = dK + (((long long)b * C + kb) * H + h) * DH;
-  float* v0p = dV + (((long long)b * C + ka) * H + h) * DH;
-  float* v1p = dV + (((long long)b * C + kb) * H + h) * DH;
+  float* k0p = dK + (((long long)bd * C + ka) * H + h) * DH;
+  float* k1p = dK + (((long long)bd * C + kb) * H + h) * DH;
+  float* v0p = dV + (((long long)bd * C + ka) * H + h) * DH;
+  float* v1p = dV + (((long long)bd * C + kb) * H + h) * DH;
 #pragma unroll
   for (int n = 0; n < DH / 8; ++n) {
     const int d = n * 8 + 2 * t4;
@@ -166,7 +172,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ do_c, TView vdo,
     const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc, const float* __restrict__ lse_c,
     const float* __restrict__ corr, float* __restrict__ dq_acc, int H, int lo, int pos0, float scale,
-    int window) {
+    int window, int grow) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = KT / 8;
   constexpr int ST = 2;            // key / value tiles are double-buffered
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -176,6 +182,13 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
   bf16* sV = sK + 2 * KT * P;    // 2 stages
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
+  // groups (gridDim.z > 1): chunk z of the same sequences; strided tensors advance `grow` rows per group,
+  // dense ones are [B, G, C, ...]; the key range is [max(0, lo + z * grow), pos0 + z * grow)
+  const int bd = b * gridDim.z + blockIdx.z;
+  q += (long long)blockIdx.z * grow * vq.rs;
+  do_c += (long long)blockIdx.z * grow * vdo.rs;
+  pos0 += blockIdx.z * grow;
+  lo = max(0, lo + (int)blockIdx.z * grow);
   const long long hoff = (long long)h * DH;
   const bf16* Kb = Kc + b * vc.bs + hoff;
   const bf16* Vb = Vc + b * vc.bs + hoff;
@@ -198,7 +211,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
   };
   if (n_tiles > 0) issue(0, 0);
   const int row0 = warp * 16, i0 = row0 + g, i1 = i0 + 8;
-  const long long orow0 = ((long long)(b * C + i0) * H + h), orow1 = ((long long)(b * C + i1) * H + h);
+  const long long orow0 = ((long long)(bd * C + i0) * H + h), orow1 = ((long long)(bd * C + i1) * H + h);
   const float L0 = lse_c[orow0], L1 = lse_c[orow1], c0 = corr[orow0], c1 = corr[orow1];
   float A[DH / 8][4];
 #pragma unroll
@@ -288,15 +301,16 @@ extern "C" {
 
 int dmb_prefix_dkv(const void* q_all, const void* doc_all, const float* corr_all, const float* lsec_all,
                    const void* Kc, const void* Vc, TView vc, float* dK, float* dV, int B, int T, int c, int H,
-                   int dh, int pos0, int q_start, int q_end, float scale, int window, cudaStream_t st) {
+                   int dh, int pos0, int q_start, int q_end, float scale, int window, int G, int grow, int span,
+                   cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     constexpr int ST = DH <= 64 ? 1 : 2;
     size_t smem = (((size_t)2 * C + 2 * ST * C) * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
     auto kern = prefix_dkv_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
-    kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q_all, (const bf16*)doc_all, corr_all, lsec_all,
+    kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q_all, (const bf16*)doc_all, corr_all, lsec_all,
                                          (const bf16*)Kc, (const bf16*)Vc, vc, dK, dV, T, H, pos0, q_start,
-                                         q_end < T ? q_end : T, scale, window);
+                                         q_end < T ? q_end : T, scale, window, grow, span);
   })
   DMB_CHECK_LAUNCH();
   return 0;
@@ -304,13 +318,13 @@ int dmb_prefix_dkv(const void* q_all, const void* doc_all, const float* corr_all
 
 int dmb_prefix_dq(const void* q, TView vq, const void* do_c, TView vdo, const void* Kc, const void* Vc, TView vc,
                   const float* lse_c, const float* corr, float* dq_acc, int B, int c, int H, int dh, int lo,
-                  int pos0, float scale, int window, cudaStream_t st) {
+                  int pos0, float scale, int window, int G, int grow, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)2 * C + 4 * KT) * Tile<DH>::PITCH * sizeof(bf16);
     auto kern = prefix_dq_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
-    kern<<<dim3(H, B), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)do_c, vdo, (const bf16*)Kc,
-                                         (const bf16*)Vc, vc, lse_c, corr, dq_acc, H, lo, pos0, scale, window);
+    kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)do_c, vdo, (const bf16*)Kc,
+                                         (const bf16*)Vc, vc, lse_c, corr, dq_acc, H, lo, pos0, scale, window, grow);
   })
   DMB_CHECK_LAUNCH();
   return 0;

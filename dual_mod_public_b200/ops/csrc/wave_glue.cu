@@ -1,0 +1,146 @@
+// Far / near partial algebra of the wavefront engine, one kernel each way.
+//
+// A window chunk's committed-prefix read is the log-sum-exp merge of a FAR partial (rows committed before
+// the chunk entered; computed once per chunk, stored by absolute position) and a NEAR partial (the K-1
+// chunks just before it; recomputed every sweep):
+//
+//   lse_c = log(exp(lse_f) + exp(lse_n)),  w_f = exp(lse_f - lse_c),  w_n = exp(lse_n - lse_c)
+//   o_c   = w_f o_f + w_n o_n
+//
+// merge_fwd forms (o_c, lse_c, w_f, w_n); split_bwd takes d(o_c), d(lse_c) and produces, per (row, head),
+//   d o_f = w_f d o_c          d lse_f = w_f (d o_c . (o_f - o_c) + d lse_c)      (accumulated over sweeps)
+//   d o_n = w_n d o_c          corr_n  = d o_n . o_n - w_n (d o_c . (o_n - o_c) + d lse_c)
+// which is what the prefix backward kernels consume (d o, corr = d o . o - d lse, lse).
+//
+// Layout: window tensors are dense [B, R, H, DH] / [B, R, H] (R rows of the window); tensors stored by
+// absolute position are slices of [B, T, H, DH] / [B, T, H] buffers starting at the window's first row,
+// so only their batch stride differs (bs_vec, bs_sca elements).  One warp per (batch, row, head).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+template <typename T> __device__ __forceinline__ T cvt(float x);
+template <> __device__ __forceinline__ float cvt<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 cvt<bf16>(float x) { return __float2bfloat16(x); }
+
+template <int DH>
+__global__ void __launch_bounds__(256) merge_fwd_kernel(
+    const float* __restrict__ o_f, const float* __restrict__ lse_f, long long bs_vec, long long bs_sca,
+    const float* __restrict__ o_n, const float* __restrict__ lse_n, float* __restrict__ o_c,
+    float* __restrict__ lse_c, float* __restrict__ w_f, float* __restrict__ w_n, int B, int R, int H) {
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)B * R * H) return;
+  const int h = (int)(wid % H);
+  const long long br = wid / H;
+  const int r = (int)(br % R), b = (int)(br / R);
+  const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
+  const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
+  const float lf = lse_f[s_abs], ln = lse_n[wid];
+  const float m = fmaxf(lf, ln);
+  const float lc = m + __logf(__expf(lf - m) + __expf(ln - m));
+  const float wf = __expf(lf - lc), wn = __expf(ln - lc);
+  constexpr int PER = DH / 32;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int d = lane + 32 * e;
+    o_c[wid * DH + d] = wf * o_f[v_abs + d] + wn * o_n[wid * DH + d];
+  }
+  if (lane == 0) {
+    lse_c[wid] = lc;
+    w_f[wid] = wf;
+    w_n[wid] = wn;
+  }
+}
+
+template <int DH, typename TD>
+__global__ void __launch_bounds__(256) split_bwd_kernel(
+    const float* __restrict__ do_c, const float* __restrict__ dlse_c, const float* __restrict__ o_c,
+    const float* __restrict__ o_n, const float* __restrict__ lse_n, const float* __restrict__ w_f,
+    const float* __restrict__ w_n, const float* __restrict__ o_f, float* __restrict__ DOf,
+    float* __restrict__ DLf, TD* __restrict__ docn, float* __restrict__ corrn, float* __restrict__ lsen,
+    long long bs_vec, long long bs_sca, int B, int R, int H) {
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)B * R * H) return;
+  const int h = (int)(wid % H);
+  const long long br = wid / H;
+  const int r = (int)(br % R), b = (int)(br / R);
+  const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
+  const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
+  const float wf = w_f[wid], wn = w_n[wid], dl = dlse_c[wid];
+  constexpr int PER = DH / 32;
+  float g[PER], on[PER], dotf = 0.f, dotn = 0.f, donon = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int d = lane + 32 * e;
+    g[e] = do_c[wid * DH + d];
+    on[e] = o_n[wid * DH + d];
+    const float oc = o_c[wid * DH + d], of = o_f[v_abs + d];
+    dotf += g[e] * (of - oc);
+    dotn += g[e] * (on[e] - oc);
+    donon += g[e] * on[e];
+  }
+  dotf = warp_sum(dotf);
+  dotn = warp_sum(dotn);
+  donon = warp_sum(donon);
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int d = lane + 32 * e;
+    DOf[v_abs + d] += wf * g[e];
+    docn[v_abs + d] = cvt<TD>(wn * g[e]);
+  }
+  if (lane == 0) {
+    DLf[s_abs] += wf * (dotf + dl);
+    corrn[s_abs] = wn * donon - wn * (dotn + dl);
+    lsen[s_abs] = lse_n[wid];
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int dmb_wave_merge_fwd(const float* o_f, const float* lse_f, long long bs_vec, long long bs_sca, const float* o_n,
+                       const float* lse_n, float* o_c, float* lse_c, float* w_f, float* w_n, int B, int R, int H,
+                       int DH, cudaStream_t st) {
+  const long long warps = (long long)B * R * H;
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  if (DH == 64)
+    merge_fwd_kernel<64><<<blocks, 256, 0, st>>>(o_f, lse_f, bs_vec, bs_sca, o_n, lse_n, o_c, lse_c, w_f, w_n, B, R, H);
+  else if (DH == 128)
+    merge_fwd_kernel<128><<<blocks, 256, 0, st>>>(o_f, lse_f, bs_vec, bs_sca, o_n, lse_n, o_c, lse_c, w_f, w_n, B, R, H);
+  else
+    return -1;
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+// docn_bf16: 1 = the near d o buffer is bf16, 0 = fp32
+int dmb_wave_split_bwd(const float* do_c, const float* dlse_c, const float* o_c, const float* o_n, const float* lse_n,
+                       const float* w_f, const float* w_n, const float* o_f, float* DOf, float* DLf, void* docn,
+                       int docn_bf16, float* corrn, float* lsen, long long bs_vec, long long bs_sca, int B, int R,
+                       int H, int DH, cudaStream_t st) {
+  const long long warps = (long long)B * R * H;
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+#define GO(D, T)                                                                                              \
+  split_bwd_kernel<D, T><<<blocks, 256, 0, st>>>(do_c, dlse_c, o_c, o_n, lse_n, w_f, w_n, o_f, DOf, DLf,      \
+                                                 (T*)docn, corrn, lsen, bs_vec, bs_sca, B, R, H)
+  if (DH == 64) {
+    if (docn_bf16) GO(64, bf16); else GO(64, float);
+  } else if (DH == 128) {
+    if (docn_bf16) GO(128, bf16); else GO(128, float);
+  } else {
+    return -1;
+  }
+#undef GO
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

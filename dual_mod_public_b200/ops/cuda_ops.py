@@ -57,12 +57,14 @@ class _Sigs:
     dmb_swiglu_fwd = [_p, _p, _p, _ll, _p]
     dmb_swiglu_bwd = [_p, _p, _p, _p, _p, _ll, _p]
     dmb_ce = [_p, _p, _p, _p, _p, _i, _i, _p]
-    dmb_tail_fwd = [_p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
+    dmb_tail_fwd = [_p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p]
     dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _v, _p, _v,
-                    _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]
-    dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
-    dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]
-    dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p]
+                    _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p]
+    dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p]
+    dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
+    dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
+    dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p]
 
 
 BF16 = torch.bfloat16
@@ -248,7 +250,7 @@ class CudaOps(TorchOps):
         lse_c = torch.empty(B, c, h, dtype=F32, device=q_r.device)
         self._ck(self.lib.dmb_prefix_fwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          o_c.data_ptr(), lse_c.data_ptr(), B, c, h, dh, lo, pos0,
-                                         scale, window, self._st()), "prefix_fwd")
+                                         scale, window, 1, 0, self._st()), "prefix_fwd")
         return o_c, lse_c
 
     def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
@@ -264,7 +266,7 @@ class CudaOps(TorchOps):
         lse_c, corr = lse_c.contiguous(), corr.contiguous()
         self._ck(self.lib.dmb_prefix_dq(q_r.data_ptr(), _tv(q_r), do_c.data_ptr(), _tv(do_c), Kc.data_ptr(),
                                         Vc.data_ptr(), _tv(Kc), lse_c.data_ptr(), corr.data_ptr(),
-                                        dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, self._st()),
+                                        dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, 1, 0, self._st()),
                  "prefix_dq")
 
     def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
@@ -280,7 +282,7 @@ class CudaOps(TorchOps):
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(),
                                          lsec_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          dK.data_ptr(), dV.data_ptr(), B, T, c, h, dh, pos0, q_start, q_end, scale,
-                                         window, self._st()), "prefix_dkv")
+                                         window, 1, 0, 1 << 30, self._st()), "prefix_dkv")
         return dK, dV
 
     def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
@@ -295,7 +297,7 @@ class CudaOps(TorchOps):
                                        v_raw.data_ptr(), _tv(v_raw), K_in.data_ptr(), _tv(K_in),
                                        V_in.data_ptr(), _tv(V_in), o_c.data_ptr(), lse_c.data_ptr(),
                                        o.data_ptr(), lse.data_ptr(), ssq.data_ptr(), B, c, h, dh, scale, window,
-                                       self._st()), "tail_fwd")
+                                       1, 0, self._st()), "tail_fwd")
         return o, lse, ssq
 
     def tail_bwd(self, dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window,
@@ -315,7 +317,116 @@ class CudaOps(TorchOps):
             _tv(v_raw), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), o_c.data_ptr(),
             lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), dks_acc.data_ptr(),
             _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc), doc_acc.data_ptr(), dlsec_acc.data_ptr(),
-            dK_in.data_ptr(), dV_in.data_ptr(), B, c, h, dh, scale, window, self._st()), "tail_bwd")
+            dK_in.data_ptr(), dV_in.data_ptr(), B, c, h, dh, scale, window, 1, 0, self._st()), "tail_bwd")
+        return dK_in, dV_in
+
+    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale):
+        B, T, h, dh = q_all.shape
+        ok = (q_all.dtype == BF16 and docn_all.dtype == BF16 and dh in (64, 128) and C in (16, 32, 64)
+              and q_all.is_contiguous() and docn_all.is_contiguous() and corrn_all.is_contiguous()
+              and lsen_all.is_contiguous() and _dense_tail(Kc, 2))
+        if not ok:
+            return super().win_near_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale)
+        dK = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
+        dV = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
+        self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), docn_all.data_ptr(), corrn_all.data_ptr(),
+                                         lsen_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), dK.data_ptr(),
+                                         dV.data_ptr(), B, T, C, h, dh, j0 * C, q_lo, min(q_hi, T), scale, 0,
+                                         G, C, span, self._st()), "win_near_dkv")
+        return dK, dV
+
+    @staticmethod
+    def _abs_view_ok(t, n_tail):
+        """A [B, R, ...] slice of a contiguous [B, T, ...] buffer: dense rows, only the batch stride differs."""
+        return t.dtype == F32 and _dense_tail(t, n_tail) and t.stride(1) == (t.shape[2] * (t.shape[3] if t.dim() == 4 else 1))
+
+    def merge_partials(self, o_f, lse_f, o_n, lse_n):
+        B, R, h, dh = o_n.shape
+        ok = (dh in (64, 128) and self._abs_view_ok(o_f, 2) and self._abs_view_ok(lse_f, 1)
+              and o_n.is_contiguous() and lse_n.is_contiguous() and o_n.dtype == F32 and o_n.is_cuda)
+        if not ok:
+            return super().merge_partials(o_f, lse_f, o_n, lse_n)
+        o_c, lse_c = torch.empty_like(o_n), torch.empty_like(lse_n)
+        w_f, w_n = torch.empty_like(lse_n), torch.empty_like(lse_n)
+        self._ck(self.lib.dmb_wave_merge_fwd(o_f.data_ptr(), lse_f.data_ptr(), o_f.stride(0), lse_f.stride(0),
+                                             o_n.data_ptr(), lse_n.data_ptr(), o_c.data_ptr(), lse_c.data_ptr(),
+                                             w_f.data_ptr(), w_n.data_ptr(), B, R, h, dh, self._st()), "merge_partials")
+        return o_c, lse_c, w_f, w_n
+
+    def split_partials(self, do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen):
+        B, R, h, dh = o_n.shape
+        vec = (o_f, DOf)
+        ok = (dh in (64, 128) and all(self._abs_view_ok(t, 2) for t in vec) and _dense_tail(docn, 2)
+              and docn.dtype in (BF16, F32) and all(self._abs_view_ok(t, 1) for t in (DLf, corrn, lsen))
+              and len({o_f.stride(0), DOf.stride(0), docn.stride(0)}) == 1
+              and len({DLf.stride(0), corrn.stride(0), lsen.stride(0)}) == 1
+              and all(t.is_contiguous() and t.dtype == F32 for t in (do_c, dlse_c, o_c, o_n, lse_n, w_f, w_n)))
+        if not ok:
+            return super().split_partials(do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen)
+        self._ck(self.lib.dmb_wave_split_bwd(do_c.data_ptr(), dlse_c.data_ptr(), o_c.data_ptr(), o_n.data_ptr(),
+                                             lse_n.data_ptr(), w_f.data_ptr(), w_n.data_ptr(), o_f.data_ptr(),
+                                             DOf.data_ptr(), DLf.data_ptr(), docn.data_ptr(), int(docn.dtype == BF16),
+                                             corrn.data_ptr(), lsen.data_ptr(), o_f.stride(0), DLf.stride(0), B, R, h, dh,
+                                             self._st()), "split_partials")
+
+    # ---- window ops: G consecutive chunks of the same sequences in one launch ----------------------------
+    def _win_ok(self, q_win, C, *views):
+        B, rows, h, dh = q_win.shape
+        return (q_win.dtype == BF16 and dh in (64, 128) and C in (16, 32, 64) and rows % C == 0
+                and all(_dense_tail(t, 2) for t in (q_win,) + views))
+
+    def win_near_fwd(self, q_win, Kc, Vc, pos0, lo, C, scale):
+        if not self._win_ok(q_win, C, Kc):
+            return super().win_near_fwd(q_win, Kc, Vc, pos0, lo, C, scale)
+        B, rows, h, dh = q_win.shape
+        o_n = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
+        lse_n = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
+        self._ck(self.lib.dmb_prefix_fwd(q_win.data_ptr(), _tv(q_win), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
+                                         o_n.data_ptr(), lse_n.data_ptr(), B, C, h, dh, lo, pos0, scale, 0,
+                                         rows // C, C, self._st()), "win_near_fwd")
+        return o_n, lse_n
+
+    def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc):
+        ok = (self._win_ok(q_win, C, Kc, do_n) and do_n.dtype == BF16 and dq_acc.is_contiguous()
+              and lse_n.is_contiguous() and corr_n.is_contiguous())
+        if not ok:
+            return super().win_near_dq(q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc)
+        B, rows, h, dh = q_win.shape
+        self._ck(self.lib.dmb_prefix_dq(q_win.data_ptr(), _tv(q_win), do_n.data_ptr(), _tv(do_n), Kc.data_ptr(),
+                                        Vc.data_ptr(), _tv(Kc), lse_n.data_ptr(), corr_n.data_ptr(),
+                                        dq_acc.data_ptr(), B, C, h, dh, lo, pos0, scale, 0, rows // C, C,
+                                        self._st()), "win_near_dq")
+
+    def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale):
+        if not self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in) or not (o_c.is_contiguous() and lse_c.is_contiguous()):
+            return super().win_tail_fwd(q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale)
+        B, rows, h, dh = q_win.shape
+        o = torch.empty(B, rows, h, dh, dtype=BF16, device=q_win.device)
+        lse = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
+        ssq = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
+        self._ck(self.lib.dmb_tail_fwd(q_win.data_ptr(), _tv(q_win), ks_win.data_ptr(), _tv(ks_win),
+                                       vr_win.data_ptr(), _tv(vr_win), K_in.data_ptr(), _tv(K_in),
+                                       V_in.data_ptr(), _tv(V_in), o_c.data_ptr(), lse_c.data_ptr(),
+                                       o.data_ptr(), lse.data_ptr(), ssq.data_ptr(), B, C, h, dh, scale, 0,
+                                       rows // C, C, self._st()), "win_tail_fwd")
+        return o, lse, ssq
+
+    def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
+        ok = (self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in, dks_acc, dv_acc) and dO.dtype == F32
+              and all(t.is_contiguous() for t in (dO, o, o_c, lse_c, lse, dq_acc, doc_acc, dlsec_acc)))
+        if not ok:
+            return super().win_tail_bwd(dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
+                                        dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc)
+        B, rows, h, dh = q_win.shape
+        dK_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
+        dV_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
+        self._ck(self.lib.dmb_tail_bwd(
+            dO.data_ptr(), q_win.data_ptr(), _tv(q_win), ks_win.data_ptr(), _tv(ks_win), vr_win.data_ptr(),
+            _tv(vr_win), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), o_c.data_ptr(),
+            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), dks_acc.data_ptr(),
+            _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc), doc_acc.data_ptr(), dlsec_acc.data_ptr(),
+            dK_in.data_ptr(), dV_in.data_ptr(), B, C, h, dh, scale, 0, rows // C, C, self._st()), "win_tail_bwd")
         return dK_in, dV_in
 
     def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0):

@@ -76,6 +76,71 @@ class TorchOps:
     def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
         return fm.prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end)
 
+    # ---- window ops: G consecutive chunks of C rows of the same sequences (statement: a loop over the
+    # chunks; the kernel table does each in one launch).  Window tensors are [B, G*C, ...]; group z reads
+    # the tape rows [max(0, lo + z*C), pos0 + z*C).
+    def win_near_fwd(self, q_win, Kc, Vc, pos0, lo, C, scale):
+        outs = []
+        for z in range(q_win.shape[1] // C):
+            l, p = max(0, lo + z * C), pos0 + z * C
+            outs.append(fm.prefix_fwd(q_win[:, z * C:(z + 1) * C], Kc[:, l:], Vc[:, l:], p - l, scale, 0))
+        return torch.cat([o for o, _ in outs], 1), torch.cat([l for _, l in outs], 1)
+
+    def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc):
+        for z in range(q_win.shape[1] // C):
+            l, p, r = max(0, lo + z * C), pos0 + z * C, slice(z * C, (z + 1) * C)
+            fm.prefix_dq(q_win[:, r], Kc[:, l:], Vc[:, l:], p - l, scale, 0, lse_n[:, r], do_n[:, r], corr_n[:, r],
+                         dq_acc[:, r])
+
+    def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale):
+        outs = []
+        for z in range(q_win.shape[1] // C):
+            r = slice(z * C, (z + 1) * C)
+            outs.append(fm.tail_fwd(q_win[:, r], ks_win[:, r], vr_win[:, r], K_in[:, r], V_in[:, r], o_c[:, r],
+                                    lse_c[:, r], scale, 0))
+        return tuple(torch.cat([t[i] for t in outs], 1) for i in range(3))
+
+    def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
+        dKs, dVs = [], []
+        for z in range(q_win.shape[1] // C):
+            r = slice(z * C, (z + 1) * C)
+            dk, dv = self.tail_bwd(dO[:, r], q_win[:, r], ks_win[:, r], vr_win[:, r], K_in[:, r], V_in[:, r],
+                                   o_c[:, r], lse_c[:, r], o[:, r], lse[:, r], scale, 0, dq_acc[:, r],
+                                   dks_acc[:, r], dv_acc[:, r], doc_acc[:, r], dlsec_acc[:, r])
+            dKs.append(dk)
+            dVs.append(dv)
+        return torch.cat(dKs, 1), torch.cat(dVs, 1)
+
+    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale):
+        """Key side of the near reads of one step for the G key chunks j0 .. j0+G-1: chunk j is read by the
+        query rows [max(q_lo, (j+1)C), min(q_hi, jC + span)).  Returns dense (dK, dV) [B, G*C, h, dh]."""
+        outs = []
+        for z in range(G):
+            p0 = (j0 + z) * C
+            outs.append(self.prefix_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, p0, C, max(q_lo, p0 + C), scale, 0,
+                                        q_end=min(q_hi, p0 + span)))
+        return torch.cat([a for a, _ in outs], 1), torch.cat([b for _, b in outs], 1)
+
+    def merge_partials(self, o_f, lse_f, o_n, lse_n):
+        """Log-sum-exp merge of the far partial (views by absolute position) and the near partial (dense):
+        (o_c, lse_c, w_f, w_n), all dense fp32."""
+        lse = torch.logaddexp(lse_f, lse_n)
+        wf, wn = torch.exp(lse_f - lse), torch.exp(lse_n - lse)
+        return wf.unsqueeze(-1) * o_f + wn.unsqueeze(-1) * o_n, lse, wf, wn
+
+    def split_partials(self, do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen):
+        """Backward of `merge_partials`: accumulates the far gradients into DOf / DLf (+=) and writes the
+        near read's (d o, corr, lse) into docn / corrn / lsen (views by absolute position)."""
+        g_f = (do_c * (o_f - o_c)).sum(-1) + dlse_c
+        g_n = (do_c * (o_n - o_c)).sum(-1) + dlse_c
+        DOf += w_f.unsqueeze(-1) * do_c
+        DLf += w_f * g_f
+        do_n = w_n.unsqueeze(-1) * do_c
+        docn.copy_(do_n)
+        corrn.copy_((do_n * o_n).sum(-1) - w_n * g_n)
+        lsen.copy_(lse_n)
+
     def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
         return fm.tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window)
 

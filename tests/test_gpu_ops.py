@@ -201,3 +201,66 @@ def test_col_sum(ops):
     out = torch.ones(2048, device=DEV)
     ops.col_sum_acc(out, x)
     close(out, 1 + x.sum(0), rtol=1e-4, atol=1e-3, what="colsum")
+
+
+@pytest.mark.parametrize("dh,C,G,lo_chunk,K", [(64, 64, 3, 2, 4), (128, 64, 2, 0, 4), (64, 32, 4, 5, 3)])
+def test_window_ops_match_per_chunk_statement(ops, dh, C, G, lo_chunk, K):
+    """The group-dimension launches (G window chunks at once) against the per-chunk torch statement."""
+    B, H = 2, 4
+    T = (lo_chunk + G + 1) * C
+    scale = dh ** -0.5
+    q, ks, vr, Kc, Vc = _cell_inputs(B, C, H, dh, T)
+    w = slice(lo_chunk * C, (lo_chunk + G) * C)
+    f = lambda t: t.float()
+    pos0, lo = lo_chunk * C, (lo_chunk - K + 1) * C
+    # near read
+    o_n, lse_n = ops.win_near_fwd(q[:, w], Kc, Vc, pos0, lo, C, scale)
+    o_nr, lse_nr = REF.win_near_fwd(f(q[:, w]), f(Kc), f(Vc), pos0, lo, C, scale)
+    close(o_n, o_nr, what="near o")
+    live = lse_nr > -1e29
+    close(lse_n[live], lse_nr[live], rtol=1e-2, atol=2e-2, what="near lse")
+    assert (lse_n[~live] < -1e29).all()
+    # merge with a far partial stored by absolute position
+    ofar, lsefar = rnd(B, T, H, dh, dtype=torch.float32, seed=21), rnd(B, T, H, dtype=torch.float32, seed=22) + 3.0
+    got = ops.merge_partials(ofar[:, w], lsefar[:, w], o_nr, lse_nr)
+    ref = REF.merge_partials(ofar[:, w], lsefar[:, w], o_nr, lse_nr)
+    for a, b_, n_ in zip(got, ref, ("o_c", "lse_c", "w_f", "w_n")):
+        close(a, b_, rtol=1e-4, atol=1e-4, what=n_)
+    o_c, lse_c, w_f, w_n = ref
+    # tail forward / backward over the window
+    o, lse, ssq = ops.win_tail_fwd(q[:, w], ks[:, w], vr[:, w], Kc[:, w], Vc[:, w], o_c, lse_c, C, scale)
+    o_r, lse_r, ssq_r = REF.win_tail_fwd(f(q[:, w]), f(ks[:, w]), f(vr[:, w]), f(Kc[:, w]), f(Vc[:, w]), o_c, lse_c, C, scale)
+    close(o, o_r, what="win tail o")
+    close(lse, lse_r, rtol=1e-2, atol=2e-2, what="win tail lse")
+    dO = rnd(B, G * C, H, dh, dtype=torch.float32, seed=23)
+    z = lambda *s: torch.zeros(*s, device=DEV)
+    acc = [z(B, G * C, H, dh), z(B, T, H, dh), z(B, T, H, dh), z(B, G * C, H, dh), z(B, G * C, H)]
+    accr = [t.clone() for t in acc]
+    dK, dV = ops.win_tail_bwd(dO, q[:, w], ks[:, w], vr[:, w], Kc[:, w], Vc[:, w], o_c, lse_c, o_r.to(torch.bfloat16),
+                              lse_r, C, scale, acc[0], acc[1][:, w], acc[2][:, w], acc[3], acc[4])
+    dKr, dVr = REF.win_tail_bwd(dO, f(q[:, w]), f(ks[:, w]), f(vr[:, w]), f(Kc[:, w]), f(Vc[:, w]), o_c, lse_c, o_r,
+                                lse_r, C, scale, accr[0], accr[1][:, w], accr[2][:, w], accr[3], accr[4])
+    for a, b_, n_ in zip([dK, dV] + acc, [dKr, dVr] + accr, ("dK_in", "dV_in", "dq", "dks", "dv", "do_c", "dlse_c")):
+        close(a, b_, rtol=3e-2, atol=3e-2, what=n_)
+    # split + near backward (query side and key side)
+    DOf, DLf = z(B, T, H, dh), z(B, T, H)
+    docn, corrn, lsen = torch.zeros(B, T, H, dh, device=DEV, dtype=torch.bfloat16), z(B, T, H), z(B, T, H)
+    R_ = [t.clone() for t in (DOf, DLf, docn, corrn, lsen)]
+    ops.split_partials(accr[3], accr[4], ofar[:, w], o_c, o_nr, lse_nr, w_f, w_n, DOf[:, w], DLf[:, w], docn[:, w],
+                       corrn[:, w], lsen[:, w])
+    REF.split_partials(accr[3], accr[4], ofar[:, w], o_c, o_nr, lse_nr, w_f, w_n, R_[0][:, w], R_[1][:, w], R_[2][:, w],
+                       R_[3][:, w], R_[4][:, w])
+    for a, b_, n_ in zip((DOf, DLf, docn, corrn, lsen), R_, ("DOf", "DLf", "docn", "corrn", "lsen")):
+        close(a, b_, rtol=1e-2, atol=1e-3, what=n_)
+    dq, dqr = z(B, G * C, H, dh), z(B, G * C, H, dh)
+    ops.win_near_dq(q[:, w], Kc, Vc, pos0, lo, C, scale, lse_nr, R_[2][:, w], R_[3][:, w].contiguous(), dq)
+    REF.win_near_dq(f(q[:, w]), f(Kc), f(Vc), pos0, lo, C, scale, lse_nr, R_[2][:, w].float(), R_[3][:, w].contiguous(), dqr)
+    close(dq, dqr, rtol=3e-2, atol=3e-2, what="near dq")
+    j0 = max(0, lo_chunk - K + 1)
+    Gk = lo_chunk + G - 1 - j0
+    if Gk > 0:
+        lsen_full = torch.where(R_[4] == 0, torch.full_like(R_[4], 5.0), R_[4])
+        a = ops.win_near_dkv(q, R_[2], R_[3], lsen_full, Kc, Vc, j0, Gk, C, pos0, (lo_chunk + G) * C, K * C, scale)
+        b_ = REF.win_near_dkv(f(q), R_[2].float(), R_[3], lsen_full, f(Kc), f(Vc), j0, Gk, C, pos0, (lo_chunk + G) * C, K * C, scale)
+        close(a[0], b_[0], rtol=3e-2, atol=3e-2, what="near dK")
+        close(a[1], b_[1], rtol=3e-2, atol=3e-2, what="near dV")
