@@ -99,30 +99,6 @@ def prefix_fwd(q_r, Kc, Vc, pos0, scale, window=0):
     return o, lse.permute(0, 2, 1).contiguous()
 
 
-def prefix_bwd(q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c, dq_acc, dKc, dVc):
-    """Backward of `prefix_fwd`.  do_c [B,c,h,dh], dlse_c [B,c,h] fp32 (summed over
-    sweeps).  Accumulates: dq_acc [B,c,h,dh] fp32 +=, dKc/dVc [B,T,h,dh] fp32 rows
-    [lo, pos0) +=."""
-    B, c, h, dh = q_r.shape
-    lo = prefix_lo(pos0, window)
-    if pos0 - lo <= 0:
-        return
-    K, V = Kc[:, lo:pos0], Vc[:, lo:pos0]
-    s = torch.einsum("bchd,bjhd->bhcj", q_r, K).float() * scale
-    m = _prefix_mask(c, lo, pos0, pos0, window, q_r.device)
-    if m is not None:
-        s = s.masked_fill(~m, NEG)
-    p = torch.exp(s - lse_c.permute(0, 2, 1).unsqueeze(-1))
-    if m is not None:
-        p = p * m
-    dov = torch.einsum("bchd,bjhd->bhcj", do_c, V.float())
-    corr = ((do_c * o_c).sum(-1) - dlse_c).permute(0, 2, 1).unsqueeze(-1)    # [B,h,c,1]
-    ds = p * (dov - corr) * scale
-    dq_acc += torch.einsum("bhcj,bjhd->bchd", ds, K.float())
-    dKc[:, lo:pos0] += torch.einsum("bhcj,bchd->bjhd", ds, q_r.float())
-    dVc[:, lo:pos0] += torch.einsum("bhcj,bchd->bjhd", p, do_c)
-
-
 def prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
     """Query side of the prefix backward for one cell: dq_acc [B,c,h,dh] fp32 += dS K over the
     committed rows.  do_c [B,c,h,dh] (any float dtype), corr [B,c,h] fp32 = do_c.o_c - dlse_c."""

@@ -54,8 +54,6 @@ from ..models.rope import apply_rope
 from .cell import PrefixRead, intra_mask, merged_read
 from .wavescan import WaveScanEngine
 
-NEG = -1e30
-
 
 # =================================================================================================
 # plain-torch statement of the operator (autograd; every config knob through refine_kv)
@@ -104,13 +102,6 @@ def wavefront_model_forward(model, idx, C, K):
         x = x + blk.attn.wo(o)
         x = x + blk.mlp(blk.mlp_norm(x))
     return model.lm_head(model.norm_f(x))
-
-
-def _merge_partials(o_a, lse_a, o_b, lse_b):
-    """Log-sum-exp merge of two softmax partials ([B,c,h,dh] fp32, [B,c,h] fp32)."""
-    lse = torch.logaddexp(lse_a, lse_b)
-    wa, wb = torch.exp(lse_a - lse), torch.exp(lse_b - lse)
-    return wa.unsqueeze(-1) * o_a + wb.unsqueeze(-1) * o_b, lse, wa, wb
 
 
 # =================================================================================================

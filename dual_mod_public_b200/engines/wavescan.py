@@ -112,6 +112,8 @@ class WaveScanEngine:
         self.loss_rows = loss_rows
         self.window = cfg.local_window or 0
         self.sat_tau = float(sat_tau)
+        self.track_rho = False                       # set True to fill `chain_rho_max` without saturating
+        self.chain_rho_max = torch.zeros((), dtype=torch.float32, device=self.device)
         assert not cfg.attn_logn_ref, "the engines do not implement the log-n logit scale"
         if backend == "auto":
             backend = "fused" if fused_supported(cfg) else "generic"
@@ -195,8 +197,8 @@ class WaveScanEngine:
             return self.L
         per_row = 7 * self.cfg.d_model * (2 if self.autocast_bf16 else 4)
         rows = max(self.B * sum(c * k for _, c, k in sch) for sch in self.schedules)
-        budget = 0.5 * torch.cuda.get_device_properties(self.device).total_memory
-        return max(0, min(self.L, int(budget // max(1, rows * per_row * len(self.schedules)))))
+        room = 0.5 * torch.cuda.get_device_properties(self.device).total_memory
+        return max(0, min(self.L, int(room // max(1, rows * per_row * len(self.schedules)))))
 
     def pack(self):
         """Refresh the compute-dtype weight copies from the master parameters."""
@@ -213,6 +215,7 @@ class WaveScanEngine:
 
     def zero_grads(self):
         self.grads.zero_()
+        self.chain_rho_max.zero_()
 
     @torch.no_grad()
     def forward(self, idx, targets=None, sid=0, train=False):
@@ -597,6 +600,8 @@ class WaveScanEngine:
             dK_out, dV_out = ops.prefix_dkv(q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
                                             pos0, c, pos0 + c, scale, self.window)
             d_o = dO_all[:, r].float()
+            if self.sat_tau > 0 or self.track_rho:
+                dK_out, dV_out = self._saturate_carry(dK_out, dV_out, d_o)
             do_c = torch.zeros_like(o_c)
             dlse_c = torch.zeros_like(lse_c)
             dq_c = torch.zeros(B, c, h, dh, dtype=f32, device=dev)
@@ -624,6 +629,23 @@ class WaveScanEngine:
             dq_r[:, r] = dq_c
             self.stats["bwd_cells"] += 1
         return dcg_stash, u_stash
+
+    def _saturate_carry(self, dK, dV, d_o):
+        """Gradient carried into a cell's committed rows from all later cells, measured against the
+        gradient entering the cell directly: rho = (largest row norm of the carry) / (mean row norm of
+        d o).  `chain_rho_max` keeps the largest rho of the backward (the LR governor's signal); with
+        sat_tau > 0 rows of the carry above sat_tau x that mean are scaled down to it (direction kept,
+        non-finite rows zeroed).  Reference parity: engines/wavescan/engine/graphs.py:345-371."""
+        ref = d_o.norm(dim=-1).mean().clamp_min(1e-12)
+        out = []
+        for g in (dK, dV):
+            g = torch.nan_to_num(g, nan=0.0, posinf=0.0, neginf=0.0)
+            n = g.flatten(2).norm(dim=-1)                                   # [B, c] row norms over all heads
+            self.chain_rho_max.copy_(torch.maximum(self.chain_rho_max, n.max() / ref))
+            if self.sat_tau > 0:
+                g = g * (self.sat_tau * ref / n.clamp_min(1e-20)).clamp(max=1.0)[..., None, None]
+            out.append(g)
+        return out
 
     def _unfold_packed_grad(self, a):
         """dW_pack holds the gradient of the FOLDED weight W' = W * w_ctx (per column).  Recover

@@ -4,7 +4,9 @@
   python -m dual_mod_public_b200.ops.bench_ops --only tail_bwd --iters 3 --no-flush   # for a profiler
 
 Each op is timed with CUDA events on the launching stream after warm-up; between timed
-iterations a 256 MB buffer is written so inputs come from HBM, not from the 126 MB L2.
+iterations a 512 MB buffer is written twice, so inputs come from HBM, not from the 126 MB L2, and the
+GPU is still busy while the host prepares the launch (the interval then holds the kernel, not the
+host's launch latency).
 Printed per op: microseconds, and the achieved TFLOP/s or GB/s from the op's algorithmic
 FLOPs / bytes (with the fraction of the measured peaks when MEASURED_PEAKS.json is found).
 """
@@ -36,7 +38,7 @@ def peaks():
 class Timer:
     def __init__(self, iters, flush):
         self.iters, self.flush = iters, flush
-        self.junk = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if flush else None
+        self.junk = torch.empty(512 << 20, dtype=torch.uint8, device=DEV) if flush else None
 
     def __call__(self, fn, warm=3):
         for _ in range(warm):
@@ -46,6 +48,7 @@ class Timer:
         for _ in range(self.iters):
             if self.junk is not None:
                 self.junk.fill_(1)
+                self.junk.fill_(2)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()

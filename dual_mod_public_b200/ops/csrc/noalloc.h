@@ -3,7 +3,7 @@
 //
 // Who that is: code that runs where cudaMalloc is forbidden or unavailable - a host thread inside
 // a real-time or signal-like context, a plug-in loaded into a process whose memory pool is owned
-// and budgeted by someone else (an inference server with a fixed arena), or a caller that hands
+// and sized by someone else (an inference server with a fixed arena), or a caller that hands
 // this library raw pointers and must be sure no hidden allocation can fail or fragment its pool
 // in the middle of a step.  The ordinary entry point, dmb_col_reduce_acc, needs the caller to
 // bring `nsplit * d` floats of scratch; this one brings its own.

@@ -66,10 +66,6 @@ class TorchOps:
     def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0):
         return fm.prefix_fwd(q_r, Kc, Vc, pos0, scale, window)
 
-    def prefix_bwd(self, q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c, dq_acc, dKc, dVc):
-        return fm.prefix_bwd(q_r, Kc, Vc, pos0, scale, window, o_c, lse_c, do_c, dlse_c,
-                             dq_acc, dKc, dVc)
-
     def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
         return fm.prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc)
 

@@ -200,7 +200,7 @@ class RewindGovernor:
     `add_snapshot(step, handle)` registers it (handle = path or an in-memory checkpoint); `wedged()`
     is True when the window holds `skip_thresh` skips; `choose(step)` returns (snap_step, handle,
     new_seed) for the newest snapshot at least `lookback` steps old that is not tainted, or None when
-    the rewind budget is spent.  Steps rewound over become tainted targets: a later rewind never lands
+    the rewind limit is reached.  Steps rewound over become tainted targets: a later rewind never lands
     on a snapshot that already led into a wedge (never-regress policy)."""
 
     def __init__(self, window=50, skip_thresh=10, ring=4, snap_interval=100, lookback=100, max_rewinds=8,

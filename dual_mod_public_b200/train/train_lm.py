@@ -154,6 +154,8 @@ def run(args):
                  optimizer=args.optimizer, device=dev, autocast_bf16=not args.fp32 and dev.type == "cuda",
                  use_graphs=not args.no_graphs, seed=args.seed, engine=engine, engine_kwargs=ekw,
                  rank_outlier_factor=args.rank_outlier_factor, rank_outlier_max=args.rank_outlier_max)
+    if args.lr_gov and hasattr(tr.engine, "track_rho"):
+        tr.engine.track_rho = True                       # before the first step: the graphs record it
     skip = SkipRule(skip_factor=args.skip_factor, grace_steps=args.skip_grace_steps, gn_hard=args.gn_hard)
     clip = CalibratedClip(max_norm=args.max_norm, clip_mult=args.clip_mult, grace_steps=args.skip_grace_steps)
     gov, creep, inject = ChainRhoGovernor(), CreepDetector(), FaultInjector()
@@ -242,8 +244,11 @@ def run(args):
             clip.update(gn, is_probe)
             final_loss = loss
         if args.lr_gov and step >= args.warmup_steps:
+            # the engine's largest carried-gradient amplification of this backward when it tracks it
+            # (1-step lag), else the norm against its running level
+            rho = float(tr.engine.chain_rho_max) if getattr(tr.engine, "track_rho", False) else 0.0
             e = skip.ema[is_probe]
-            gov.update(gn_seen / e if e else 1.0)
+            gov.update(rho if rho > 0 else (gn_seen / e if e else 1.0))
         creeping = creep.update(gn) if not skipped else False
         tokens_seen += gseqs * T
         c_r, k_r = rung_of(sid)
@@ -277,7 +282,7 @@ def run(args):
                 pick = rewind.choose(step, extra={"skips_in_window": sum(rewind.recent), "rho_ema": gov.rho_ema or 0.0})
                 if pick is None:
                     if master:
-                        print(f"[auto-rewind] giving up at step {step}: rewind budget spent", flush=True)
+                        print(f"[auto-rewind] giving up at step {step}: rewind limit reached", flush=True)
                     break
                 snap_step, ck, new_seed = pick
                 restore(ck)

@@ -211,6 +211,28 @@ def test_kept_sweep_states_equal_recompute():
             assert torch.equal(gr[n], out[0][1][n]), n
 
 
+def test_saturating_carry_and_rho_signal():
+    """A loose cap changes nothing and fills the governor's signal; a tight cap bounds the gradient that
+    later cells hand to earlier rows (finite, smaller, different)."""
+    cfg, m = build()
+    B, T = 2, 32
+    g = torch.Generator().manual_seed(9)
+    idx = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    sched = uniform_chunks(T, 8, 3)
+    base = WaveScanEngine(m, [sched], B, T, backend="fused", ops=TorchOps())
+    l0, g0 = _engine_grads(m, base, idx, tgt)
+    assert base.chain_rho_max.item() == 0.0
+    loose = WaveScanEngine(m, [sched], B, T, backend="fused", ops=TorchOps(), sat_tau=1e6)
+    l1, g1 = _engine_grads(m, loose, idx, tgt)
+    assert loose.chain_rho_max.item() > 0 and all(torch.allclose(g1[n], g0[n], rtol=1e-5, atol=1e-8) for n in g0)
+    tight = WaveScanEngine(m, [sched], B, T, backend="fused", ops=TorchOps(), sat_tau=1e-3)
+    l2, g2 = _engine_grads(m, tight, idx, tgt)
+    n = "blocks.0.attn.wk.weight"
+    assert torch.isfinite(g2[n]).all() and not torch.allclose(g2[n], g0[n], rtol=1e-3, atol=1e-9)
+    assert torch.equal(l0, l2)
+
+
 def test_explicit_dlogits_backward_and_accumulation():
     cfg, m = build()
     B, T = 2, 16

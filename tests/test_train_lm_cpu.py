@@ -70,7 +70,7 @@ def test_governor_creep_rewind_injector(tmp_path):
     assert rw.wedged()
     snap, handle, seed = rw.choose(43)
     assert (snap, handle, seed) == (30, "h30", 105) and 40 in rw.tainted and not rw.wedged()
-    assert rw.choose(50) is not None and rw.choose(60) is None                       # budget of 2
+    assert rw.choose(50) is not None and rw.choose(60) is None                       # at most 2 rewinds
     assert len(open(tmp_path / "rw.jsonl").read().strip().splitlines()) == 2
     inj = G.FaultInjector({"DMB_FAKE_SPIKE_STEPS": "3,4", "DMB_FAKE_STORM": "10:12", "DMB_FAKE_NAN_STEPS": "7"})
     assert inj.active and inj.spiked(3) and inj.spiked(11) and not inj.spiked(12)

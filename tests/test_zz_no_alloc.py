@@ -1,7 +1,7 @@
 """The allocation-free column reduction (`dmb_col_reduce_acc_noalloc`, csrc/noalloc.h).
 
 Some users of the kernel library may not allocate device memory at all: code running
-inside somebody else's fixed memory arena (a serving process that budgets every byte),
+inside somebody else's fixed memory arena (a serving process that accounts for every byte),
 or code that must be certain no hidden allocation can fail in the middle of a step.
 For them the library exports one entry point that carries its own scratch in a fixed
 array inside the library image.  This test calls that entry point through its exported
