@@ -53,8 +53,28 @@ def build(name, mode, device, max_len):
     return cfg, DualModLM(cfg).to(device=device).eval(), dt
 
 
-def time_decode(model, B, prompt_len, gen, dtype, device, rank, world):
-    dec = GraphDecoder(model, B, prompt_len + gen, dtype=dtype).capture()
+def build_reference(name, mode, device, max_len):
+    """The unmodified reference model + its GraphDecoder class from `baseline/_ref` (same shape, random init)."""
+    import sys
+    ref = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "lm", "eval")):
+        raise FileNotFoundError("baseline/_ref is not installed")
+    sys.path.insert(0, ref)
+    from dataclasses import fields
+
+    from lm.eval.graph_decode import GraphDecoder as RefDecoder
+    from models.dualmod.config import DualModConfig as RefConfig
+    from models.dualmod.model import DualModLM as RefLM
+    mine = preset(name, max_seq_len=max_len).to_dict()
+    keep = {f.name for f in fields(RefConfig)}
+    cfg = RefConfig(**{k: v for k, v in mine.items() if k in keep})
+    cfg.attn_mode = mode
+    torch.manual_seed(1337)
+    return cfg, RefLM(cfg).to(device).eval(), RefDecoder
+
+
+def time_decode(model, B, prompt_len, gen, dtype, device, rank, world, decoder_cls=None):
+    dec = (decoder_cls or GraphDecoder)(model, B, prompt_len + gen, dtype=dtype).capture()
     g = torch.Generator().manual_seed(99 + rank)
     prompt = torch.randint(0, model.cfg.vocab_size, (B, prompt_len), generator=g).to(device)
     cuda = torch.device(device).type == "cuda"
@@ -67,7 +87,9 @@ def time_decode(model, B, prompt_len, gen, dtype, device, rank, world):
         e0.record()
     import time
     t0 = time.perf_counter()
-    dec.prefill(prompt)
+    for p in range(prompt_len):                          # token by token: the tape is recurrent
+        dec.tok.copy_(prompt[:, p:p + 1])
+        dec.step()
     if cuda:
         e1.record()
     t1 = time.perf_counter()
@@ -86,7 +108,7 @@ def time_decode(model, B, prompt_len, gen, dtype, device, rank, world):
         pre_ms, gen_ms = t.tolist()
     return {"ms_per_token": gen_ms / gen, "tokens_per_s": world * B * gen / (gen_ms / 1e3),
             "prefill_ms": pre_ms, "prefill_tokens_per_s": world * B * prompt_len / (pre_ms / 1e3),
-            "kernel_read": bool(dec.use_kernel), "graph": dec.graph is not None}
+            "kernel_read": bool(getattr(dec, "use_kernel", False)), "graph": dec.graph is not None}
 
 
 @torch.no_grad()
@@ -132,20 +154,32 @@ def main(argv=None):
     ap.add_argument("--validate", action="store_true")
     ap.add_argument("--device", default="")
     ap.add_argument("--arms", default="dualmod,vanilla")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
+                    help="reference: the unmodified reference model and GraphDecoder from baseline/_ref")
     args = ap.parse_args(argv)
     rank, world, local = _dist()
     device = args.device or (f"cuda:{local}" if torch.cuda.is_available() else "cpu")
     out = {"metric": "decode_ms_per_token", "model": args.model, "batch_per_gpu": args.batch, "n_gpus": world,
            "prompt": args.prompt, "gen": args.gen, "dtype": "bf16" if "cuda" in device else "fp32",
            "data": "uniform random prompt ids, random-init weights"}
+    out["impl"] = args.impl
     for arm in args.arms.split(","):
         mode = "vanilla" if arm == "vanilla" else "sequential"
-        cfg, model, dt = build(args.model, mode, device, args.prompt + args.gen)
+        dec_cls = None
+        if args.impl == "reference":
+            try:
+                cfg, model, dec_cls = build_reference(args.model, mode, device, args.prompt + args.gen)
+                dt = torch.bfloat16
+            except Exception as e:
+                out = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
+                break
+        else:
+            cfg, model, dt = build(args.model, mode, device, args.prompt + args.gen)
         if args.validate:
             out[arm] = validate(model, min(args.batch, 4), min(args.prompt + args.gen, 96), dt, device)
         else:
             out[arm] = {k: (round(v, 4) if isinstance(v, float) else v)
-                        for k, v in time_decode(model, args.batch, args.prompt, args.gen, dt, device, rank, world).items()}
+                        for k, v in time_decode(model, args.batch, args.prompt, args.gen, dt, device, rank, world, dec_cls).items()}
         del model
         if "cuda" in device:
             torch.cuda.empty_cache()

@@ -26,9 +26,18 @@ from ..models.rope import apply_rope
 
 
 class GraphDecoder:
-    def __init__(self, model, B, P_max, dtype=torch.bfloat16, use_kernel=None):
-        self.m = model
+    def __init__(self, model, B, P_max, dtype=torch.bfloat16, use_kernel=None, cast_weights=True):
         self.dev = next(model.parameters()).device
+        if (cast_weights and dtype == torch.bfloat16 and self.dev.type == "cuda"
+                and next(model.parameters()).dtype == torch.float32):
+            # decode from a bf16 copy of the weights: under autocast every step would otherwise re-cast
+            # all fp32 master weights (hundreds of copy kernels and 3x the weight traffic per token)
+            import copy
+            src, model = model, copy.deepcopy(model).to(dtype)
+            for name, buf in src.named_buffers():           # tables (RoPE) stay in their own precision
+                mod, _, leaf = name.rpartition(".")
+                setattr(model.get_submodule(mod) if mod else model, leaf, buf.clone())
+        self.m = model
         assert P_max <= model.cfg.max_seq_len, (P_max, model.cfg.max_seq_len)
         a0 = model.blocks[0].attn
         L, h, dh = len(model.blocks), a0.n_heads, a0.head_dim

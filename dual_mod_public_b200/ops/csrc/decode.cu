@@ -37,30 +37,42 @@ __global__ void __launch_bounds__(128) decode_attend_kernel(
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  // the loop bound is warp-uniform (all lanes run the shuffles); a group past the end is masked
-  for (int j0 = lo + warp * KPW; j0 < pos; j0 += NW * KPW) {
-    const int j = j0 + grp;
-    const bool live = j < pos;
-    uint4 ku = make_uint4(0, 0, 0, 0), vu = make_uint4(0, 0, 0, 0);
-    if (live) {
-      ku = *reinterpret_cast<const uint4*>(Kb + (long long)j * row_stride);
-      vu = *reinterpret_cast<const uint4*>(Vb + (long long)j * row_stride);
-    }
-    float2 k0 = unpack_bf16(ku.x), k1 = unpack_bf16(ku.y), k2 = unpack_bf16(ku.z), k3 = unpack_bf16(ku.w);
-    float s = qv[0] * k0.x + qv[1] * k0.y + qv[2] * k1.x + qv[3] * k1.y + qv[4] * k2.x + qv[5] * k2.y +
-              qv[6] * k3.x + qv[7] * k3.y;
+  // the loop bound is warp-uniform (all lanes run the shuffles); a group past the end is masked.
+  // U key steps per iteration: all their loads are issued before the first use, so every thread keeps
+  // U x 32 bytes in flight (the kernel is a pure HBM stream; one step at a time left the bus half idle)
+  constexpr int U = 4;
+  for (int j0 = lo + warp * KPW; j0 < pos; j0 += U * NW * KPW) {
+    uint4 ku[U], vu[U];
+    bool live[U];
 #pragma unroll
-    for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    s *= scale;
-    if (!live) continue;
-    const float mn = fmaxf(m, s), c = __expf(m - mn), p = __expf(s - mn);
-    float2 v0 = unpack_bf16(vu.x), v1 = unpack_bf16(vu.y), v2 = unpack_bf16(vu.z), v3 = unpack_bf16(vu.w);
-    l = l * c + p;
-    acc[0] = acc[0] * c + p * v0.x; acc[1] = acc[1] * c + p * v0.y;
-    acc[2] = acc[2] * c + p * v1.x; acc[3] = acc[3] * c + p * v1.y;
-    acc[4] = acc[4] * c + p * v2.x; acc[5] = acc[5] * c + p * v2.y;
-    acc[6] = acc[6] * c + p * v3.x; acc[7] = acc[7] * c + p * v3.y;
-    m = mn;
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * NW * KPW + grp;
+      live[u] = j < pos;
+      ku[u] = make_uint4(0, 0, 0, 0);
+      vu[u] = make_uint4(0, 0, 0, 0);
+      if (live[u]) {
+        ku[u] = *reinterpret_cast<const uint4*>(Kb + (long long)j * row_stride);
+        vu[u] = *reinterpret_cast<const uint4*>(Vb + (long long)j * row_stride);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float2 k0 = unpack_bf16(ku[u].x), k1 = unpack_bf16(ku[u].y), k2 = unpack_bf16(ku[u].z), k3 = unpack_bf16(ku[u].w);
+      float s = qv[0] * k0.x + qv[1] * k0.y + qv[2] * k1.x + qv[3] * k1.y + qv[4] * k2.x + qv[5] * k2.y +
+                qv[6] * k3.x + qv[7] * k3.y;
+#pragma unroll
+      for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      s *= scale;
+      if (!live[u]) continue;
+      const float mn = fmaxf(m, s), c = __expf(m - mn), p = __expf(s - mn);
+      float2 v0 = unpack_bf16(vu[u].x), v1 = unpack_bf16(vu[u].y), v2 = unpack_bf16(vu[u].z), v3 = unpack_bf16(vu[u].w);
+      l = l * c + p;
+      acc[0] = acc[0] * c + p * v0.x; acc[1] = acc[1] * c + p * v0.y;
+      acc[2] = acc[2] * c + p * v1.x; acc[3] = acc[3] * c + p * v1.y;
+      acc[4] = acc[4] * c + p * v2.x; acc[5] = acc[5] * c + p * v2.y;
+      acc[6] = acc[6] * c + p * v3.x; acc[7] = acc[7] * c + p * v3.y;
+      m = mn;
+    }
   }
   const int slot = warp * KPW + grp;
   if (sub == 0) { s_m[slot] = m; s_l[slot] = l; }
