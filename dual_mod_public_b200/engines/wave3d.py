@@ -222,9 +222,9 @@ class Wave3DEngine(WaveScanEngine):
         o_c, lse_c, w_f, w_n = ops.merge_partials(self.ofar_all[:, w], self.lsefar_all[:, w], o_n, lse_n)
         o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale)
         raw = ops.linear(o.reshape(B, G * C, d), S.P.W_pack)
-        K_new, V_new = ops.refine_fwd(raw, ssq, S.glx[:, w], S.k[:, w], S.v[:, w], S.cos[w], S.sin[w], h, S.pin)
-        S.Kc[:, w] = K_new
-        S.Vc[:, w] = V_new
+        # every window chunk's new rows replace the old ones (all reads of this step are done)
+        ops.refine_fwd(raw, ssq, S.glx[:, w], S.k[:, w], S.v[:, w], S.cos[w], S.sin[w], h, S.pin,
+                       out=(S.Kc[:, w], S.Vc[:, w]))
         if s - K + 1 >= 0 and getattr(S, "o_all", None) is not None:
             S.o_all[:, lo * C:(lo + 1) * C] = o[:, :C].reshape(B, C, d)      # chunk lo's K-th read is final
         if save is not None:

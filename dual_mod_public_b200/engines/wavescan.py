@@ -402,9 +402,7 @@ class WaveScanEngine:
         kept = [] if keep else None
         for ci, (pos0, c, n_sweeps) in enumerate(self.schedules[sid]):
             r = slice(pos0, pos0 + c)
-            o_c, lse_c = ops.prefix_fwd(q_r[:, r], Kc, Vc, pos0, scale, self.window)
-            saved[ci][0].copy_(o_c)
-            saved[ci][1].copy_(lse_c)
+            o_c, lse_c = ops.prefix_fwd(q_r[:, r], Kc, Vc, pos0, scale, self.window, out=saved[ci])
             K_in, V_in = kself_r[:, r], v4[:, r]
             o, st = None, []
             for s in range(n_sweeps):
@@ -414,12 +412,12 @@ class WaveScanEngine:
                 if keep:
                     # sweep 0 reads the raw rows, which the backward re-projects anyway
                     st.append((K_in if s else None, V_in if s else None, o, lse, ssq, raw))
-                K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
-                                            h, pin)
+                # the last sweep's refinement is the commit: written straight into the tape rows
+                last = s == n_sweeps - 1
+                K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, pin,
+                                            out=(Kc[:, r], Vc[:, r]) if last else None)
             if keep:
                 kept.append(st)
-            Kc[:, r] = K_in
-            Vc[:, r] = V_in
             o_all[:, r] = o.reshape(B, c, d)
             self.stats["fwd_cells"] += 1
         if keep:
@@ -595,16 +593,16 @@ class WaveScanEngine:
                     st.append((K_in, V_in, o, lse, ssq, raw))
                     K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
                                                 h, pin)
-            self.lsec_all[:, r] = lse_c
             # gradient of this cell's committed rows from every later cell's prefix read
             dK_out, dV_out = ops.prefix_dkv(q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
                                             pos0, c, pos0 + c, scale, self.window)
             d_o = dO_all[:, r].float()
             if self.sat_tau > 0 or self.track_rho:
                 dK_out, dV_out = self._saturate_carry(dK_out, dV_out, d_o)
-            do_c = torch.zeros_like(o_c)
-            dlse_c = torch.zeros_like(lse_c)
-            dq_c = torch.zeros(B, c, h, dh, dtype=f32, device=dev)
+            nv = B * c * h * dh                                 # one zeroed scratch, three accumulators
+            acc = torch.zeros(2 * nv + B * c * h, dtype=f32, device=dev)
+            do_c, dq_c = acc[:nv].view(B, c, h, dh), acc[nv:2 * nv].view(B, c, h, dh)
+            dlse_c = acc[2 * nv:].view(B, c, h)
             for s in range(n_sweeps - 1, -1, -1):
                 K_in, V_in, o, lse, ssq, raw = st[s]
                 off = stash_off[(ci, s)]
@@ -619,12 +617,9 @@ class WaveScanEngine:
                 dK_out, dV_out = ops.tail_bwd(
                     d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
                     dq_c, dks_r[:, r], dv4[:, r], do_c, dlse_c)
-            # sweep 0 read the raw rows
-            dks_r[:, r] += dK_out
-            dv4[:, r] += dV_out
-            corr = (do_c * o_c).sum(-1) - dlse_c
-            self.doc_all[:, r] = do_c
-            self.corr_all[:, r] = corr
+            # sweep 0 read the raw rows; publish this cell's (d o_c, corr, lse_c) for the earlier cells' gathers
+            corr = ops.cell_finish(do_c, dlse_c, o_c, lse_c, dK_out, dV_out, self.doc_all[:, r],
+                                   self.corr_all[:, r], self.lsec_all[:, r], dks_r[:, r], dv4[:, r])
             ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_c)
             dq_r[:, r] = dq_c
             self.stats["bwd_cells"] += 1

@@ -73,7 +73,8 @@ __global__ void refine_fwd_kernel(const bf16* __restrict__ raw, const float* __r
                                   const bf16* __restrict__ glx, TView vg, const bf16* __restrict__ k, TView vk,
                                   const bf16* __restrict__ v, TView vv, const float* __restrict__ cosb,
                                   const float* __restrict__ sinb, bf16* __restrict__ Kout,
-                                  bf16* __restrict__ Vout, int B, int C, int H, int DH, int pin_cols, float eps) {
+                                  bf16* __restrict__ Vout, TView vo_, int B, int C, int H, int DH, int pin_cols,
+                                  float eps) {
   Where w;
   if (!locate(w, (long long)blockIdx.x * blockDim.x + threadIdx.x, B, C, H, DH)) return;
   const int d = H * DH, half = DH >> 1;
@@ -102,7 +103,7 @@ __global__ void refine_fwd_kernel(const bf16* __restrict__ raw, const float* __r
     k0.x[i] = kk[0].x[i] * cs.x[i] - kk[1].x[i] * sn.x[i];
     k1.x[i] = kk[1].x[i] * cs.x[i] + kk[0].x[i] * sn.x[i];
   }
-  const long long o = w.row * d;
+  const long long o = w.b * vo_.bs + w.t * vo_.rs;      // outputs may be rows of the tape itself
   st8(Kout + o + w.c0, k0);
   st8(Kout + o + w.c1, k1);
   st8(Vout + o + w.c0, vo[0]);
@@ -214,13 +215,13 @@ __global__ void rmsn_bwd_kernel(const bf16* __restrict__ du, const bf16* __restr
 extern "C" {
 
 int dmb_refine_fwd(const void* raw, const float* ssq, const void* glx, TView vg, const void* k, TView vk,
-                   const void* v, TView vv, const float* cosb, const float* sinb, void* Kout, void* Vout, int B,
-                   int C, int H, int DH, int pin_cols, float eps, cudaStream_t st) {
+                   const void* v, TView vv, const float* cosb, const float* sinb, void* Kout, void* Vout, TView vo,
+                   int B, int C, int H, int DH, int pin_cols, float eps, cudaStream_t st) {
   if (DH % 16 || H % 4) return -1;
   long long total = (long long)B * C * H * (DH / 16);
   refine_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
       (const bf16*)raw, ssq, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv, cosb, sinb,
-      (bf16*)Kout, (bf16*)Vout, B, C, H, DH, pin_cols, eps);
+      (bf16*)Kout, (bf16*)Vout, vo, B, C, H, DH, pin_cols, eps);
   DMB_CHECK_LAUNCH();
   return 0;
 }

@@ -1,4 +1,5 @@
-// Far / near partial algebra of the wavefront engine, one kernel each way.
+// Glue between the attention kernels: the far / near partial algebra of the wavefront engine (one kernel
+// each way) and the cell-end bookkeeping of the reverse scan.
 //
 // A window chunk's committed-prefix read is the log-sum-exp merge of a FAR partial (rows committed before
 // the chunk entered; computed once per chunk, stored by absolute position) and a NEAR partial (the K-1
@@ -102,9 +103,70 @@ __global__ void __launch_bounds__(256) split_bwd_kernel(
   }
 }
 
+// End of a cell's backward.  do_c / dlse_c: gradient of the committed-prefix partial summed over the
+// cell's sweeps (dense [B, R, H, DH] / [B, R, H]); o_c / lse_c: the partial itself; dK0 / dV0: gradient
+// of the rows sweep 0 read (the raw rows).  Writes, at the cell's rows of the per-layer arrays indexed by
+// absolute position (batch strides bs_vec / bs_sca): doc = d o_c (compute dtype), corr = d o_c . o_c -
+// d lse_c (also as a dense [B, R, H] copy for the query-side kernel), lsec = lse_c; and adds dK0 / dV0
+// into the raw-row gradients dks / dv.
+template <int DH, typename TD>
+__global__ void __launch_bounds__(256) cell_finish_kernel(
+    const float* __restrict__ do_c, const float* __restrict__ dlse_c, const float* __restrict__ o_c,
+    const float* __restrict__ lse_c, const float* __restrict__ dK0, const float* __restrict__ dV0,
+    TD* __restrict__ doc, float* __restrict__ corr, float* __restrict__ corr_dense, float* __restrict__ lsec,
+    float* __restrict__ dks, float* __restrict__ dv, long long bs_vec, long long bs_sca, int B, int R, int H) {
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)B * R * H) return;
+  const int h = (int)(wid % H);
+  const long long br = wid / H;
+  const int r = (int)(br % R), b = (int)(br / R);
+  const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
+  const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
+  constexpr int PER = DH / 32;
+  float dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int d = lane + 32 * e;
+    const float g = do_c[wid * DH + d];
+    dot += g * o_c[wid * DH + d];
+    doc[v_abs + d] = cvt<TD>(g);
+    dks[v_abs + d] += dK0[wid * DH + d];
+    dv[v_abs + d] += dV0[wid * DH + d];
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) {
+    const float cv = dot - dlse_c[wid];
+    corr[s_abs] = cv;
+    corr_dense[wid] = cv;
+    lsec[s_abs] = lse_c[wid];
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+int dmb_cell_finish(const float* do_c, const float* dlse_c, const float* o_c, const float* lse_c, const float* dK0,
+                    const float* dV0, void* doc, int doc_bf16, float* corr, float* corr_dense, float* lsec, float* dks,
+                    float* dv,
+                    long long bs_vec, long long bs_sca, int B, int R, int H, int DH, cudaStream_t st) {
+  const long long warps = (long long)B * R * H;
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+#define GO(D, T)                                                                                            \
+  cell_finish_kernel<D, T><<<blocks, 256, 0, st>>>(do_c, dlse_c, o_c, lse_c, dK0, dV0, (T*)doc, corr,       \
+                                                   corr_dense, lsec, dks, dv, bs_vec, bs_sca, B, R, H)
+  if (DH == 64) {
+    if (doc_bf16) GO(64, bf16); else GO(64, float);
+  } else if (DH == 128) {
+    if (doc_bf16) GO(128, bf16); else GO(128, float);
+  } else {
+    return -1;
+  }
+#undef GO
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
 
 int dmb_wave_merge_fwd(const float* o_f, const float* lse_f, long long bs_vec, long long bs_sca, const float* o_n,
                        const float* lse_n, float* o_c, float* lse_c, float* w_f, float* w_n, int B, int R, int H,

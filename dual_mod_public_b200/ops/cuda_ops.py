@@ -50,7 +50,7 @@ class _Sigs:
     dmb_rms_bwd_dx = [_p, _i, _p, _ll, _p, _p, _p, _p, _i, _i, _i, _p]
     dmb_col_reduce_acc = [_p, _i, _p, _ll, _p, _p, _i, _p, _i, _i, _p]
     dmb_rope = [_p, _i, _ll, _ll, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]
-    dmb_refine_fwd = [_p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]
+    dmb_refine_fwd = [_p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _f, _p]
     dmb_refine_bwd = [_p, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
                       _i, _i, _i, _i, _i, _f, _p]
     dmb_rmsn_bwd = [_p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p]
@@ -62,6 +62,7 @@ class _Sigs:
                     _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p]
     dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p]
     dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
+    dmb_cell_finish = [_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p]
@@ -240,17 +241,24 @@ class CudaOps(TorchOps):
         B, c, h, dh = q_r.shape
         return q_r.dtype == BF16 and dh in (64, 128) and c in (16, 32, 64)
 
-    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0):
+    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0, out=None):
         from ..engines.fused_math import prefix_lo
         B, c, h, dh = q_r.shape
         lo = prefix_lo(pos0, window)
         if not self._cell_ok(q_r) or pos0 - lo <= 0 or not (_dense_tail(q_r, 2) and _dense_tail(Kc, 2)):
-            return super().prefix_fwd(q_r, Kc, Vc, pos0, scale, window)
-        o_c = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
-        lse_c = torch.empty(B, c, h, dtype=F32, device=q_r.device)
+            return super().prefix_fwd(q_r, Kc, Vc, pos0, scale, window, out)
+        if out is not None and out[0].is_contiguous() and out[1].is_contiguous() and out[0].dtype == F32:
+            o_c, lse_c = out
+        else:
+            o_c = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+            lse_c = torch.empty(B, c, h, dtype=F32, device=q_r.device)
         self._ck(self.lib.dmb_prefix_fwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          o_c.data_ptr(), lse_c.data_ptr(), B, c, h, dh, lo, pos0,
                                          scale, window, 1, 0, self._st()), "prefix_fwd")
+        if out is not None and o_c is not out[0]:
+            out[0].copy_(o_c)
+            out[1].copy_(lse_c)
+            return out
         return o_c, lse_c
 
     def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
@@ -339,6 +347,22 @@ class CudaOps(TorchOps):
     def _abs_view_ok(t, n_tail):
         """A [B, R, ...] slice of a contiguous [B, T, ...] buffer: dense rows, only the batch stride differs."""
         return t.dtype == F32 and _dense_tail(t, n_tail) and t.stride(1) == (t.shape[2] * (t.shape[3] if t.dim() == 4 else 1))
+
+    def cell_finish(self, do_c, dlse_c, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv):
+        B, R, h, dh = do_c.shape
+        ok = (dh in (64, 128) and do_c.is_cuda and doc.dtype in (BF16, F32) and _dense_tail(doc, 2)
+              and all(t.is_contiguous() and t.dtype == F32 for t in (do_c, dlse_c, o_c, lse_c, dK0, dV0))
+              and all(self._abs_view_ok(t, 2) for t in (dks, dv)) and all(self._abs_view_ok(t, 1) for t in (corr, lsec))
+              and doc.stride(1) == h * dh and len({doc.stride(0), dks.stride(0), dv.stride(0)}) == 1
+              and corr.stride(0) == lsec.stride(0))
+        if not ok:
+            return super().cell_finish(do_c, dlse_c, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv)
+        cv = torch.empty(B, R, h, dtype=F32, device=do_c.device)
+        self._ck(self.lib.dmb_cell_finish(do_c.data_ptr(), dlse_c.data_ptr(), o_c.data_ptr(), lse_c.data_ptr(),
+                                          dK0.data_ptr(), dV0.data_ptr(), doc.data_ptr(), int(doc.dtype == BF16),
+                                          corr.data_ptr(), cv.data_ptr(), lsec.data_ptr(), dks.data_ptr(), dv.data_ptr(),
+                                          doc.stride(0), corr.stride(0), B, R, h, dh, self._st()), "cell_finish")
+        return cv
 
     def merge_partials(self, o_f, lse_f, o_n, lse_n):
         B, R, h, dh = o_n.shape
@@ -429,20 +453,28 @@ class CudaOps(TorchOps):
             dK_in.data_ptr(), dV_in.data_ptr(), B, C, h, dh, scale, 0, rows // C, C, self._st()), "win_tail_bwd")
         return dK_in, dV_in
 
-    def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0):
+    def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):
         B, c, d = k.shape
         dh = d // h
         ok = (k.dtype == BF16 and raw.dtype == BF16 and raw.is_contiguous() and cos.is_contiguous()
               and ssq.is_contiguous() and dh % 16 == 0 and h % 4 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v)))
         if not ok:
-            return super().refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols)
-        K_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
-        V_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
+            return super().refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols, out)
+        if (out is not None and all(t.dtype == BF16 and _dense_tail(t, 2) for t in out)
+                and out[0].stride() == out[1].stride()):
+            K_out, V_out = out                                # e.g. the cell's rows of the tape itself
+        else:
+            K_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
+            V_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
         self._ck(self.lib.dmb_refine_fwd(raw.data_ptr(), ssq.data_ptr(), glx.data_ptr(), _tv(glx), k.data_ptr(),
                                          _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
-                                         K_out.data_ptr(), V_out.data_ptr(), B, c, h, dh, pin_cols, 1e-5,
+                                         K_out.data_ptr(), V_out.data_ptr(), _tv(K_out), B, c, h, dh, pin_cols, 1e-5,
                                          self._st()), "refine_fwd")
+        if out is not None and K_out is not out[0]:
+            out[0].copy_(K_out)
+            out[1].copy_(V_out)
+            return out
         return K_out, V_out
 
     def refine_bwd(self, dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc,

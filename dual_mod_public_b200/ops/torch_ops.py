@@ -63,8 +63,14 @@ class TorchOps:
         return fm.swiglu_bwd(dg, h1, h3)
 
     # ---- cell ops -------------------------------------------------------------------
-    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0):
-        return fm.prefix_fwd(q_r, Kc, Vc, pos0, scale, window)
+    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0, out=None):
+        """`out`: optional (o_c, lse_c) fp32 tensors to write into (and return)."""
+        o_c, lse_c = fm.prefix_fwd(q_r, Kc, Vc, pos0, scale, window)
+        if out is None:
+            return o_c, lse_c
+        out[0].copy_(o_c)
+        out[1].copy_(lse_c)
+        return out
 
     def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
         return fm.prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc)
@@ -118,6 +124,18 @@ class TorchOps:
                                         q_end=min(q_hi, p0 + span)))
         return torch.cat([a for a, _ in outs], 1), torch.cat([b for _, b in outs], 1)
 
+    def cell_finish(self, do_c, dlse_c, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv):
+        """End of a cell's backward: doc = d o_c, corr = d o_c . o_c - d lse_c, lsec = lse_c at the cell's rows
+        of the per-layer arrays (views by absolute position), and dks += dK0, dv += dV0 (sweep 0 read the
+        raw rows).  Returns corr as a dense [B, c, h] tensor."""
+        doc.copy_(do_c)
+        cv = (do_c * o_c).sum(-1) - dlse_c
+        corr.copy_(cv)
+        lsec.copy_(lse_c)
+        dks += dK0
+        dv += dV0
+        return cv
+
     def merge_partials(self, o_f, lse_f, o_n, lse_n):
         """Log-sum-exp merge of the far partial (views by absolute position) and the near partial (dense):
         (o_c, lse_c, w_f, w_n), all dense fp32."""
@@ -153,8 +171,14 @@ class TorchOps:
         dlsec_acc += dlse
         return dK_in, dV_in
 
-    def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0):
-        return fm.refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols)
+    def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):
+        """`out`: optional (K, V) [B,c,h,dh] views to write into (e.g. the cell's rows of the tape)."""
+        K, V = fm.refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols)
+        if out is None:
+            return K, V
+        out[0].copy_(K)
+        out[1].copy_(V)
+        return out
 
     def refine_bwd(self, dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc,
                    dcg_out, uhat_out):

@@ -264,3 +264,22 @@ def test_window_ops_match_per_chunk_statement(ops, dh, C, G, lo_chunk, K):
         b_ = REF.win_near_dkv(f(q), R_[2].float(), R_[3], lsen_full, f(Kc), f(Vc), j0, Gk, C, pos0, (lo_chunk + G) * C, K * C, scale)
         close(a[0], b_[0], rtol=3e-2, atol=3e-2, what="near dK")
         close(a[1], b_[1], rtol=3e-2, atol=3e-2, what="near dV")
+
+
+@pytest.mark.parametrize("dh", [64, 128])
+def test_cell_finish(ops, dh):
+    B, T, c, H, pos0 = 2, 160, 64, 4, 64
+    r = slice(pos0, pos0 + c)
+    f = lambda *s, seed: rnd(*s, dtype=torch.float32, seed=seed)
+    do_c, dlse_c, o_c, lse_c = f(B, c, H, dh, seed=1), f(B, c, H, seed=2), f(B, c, H, dh, seed=3), f(B, c, H, seed=4)
+    dK0, dV0 = f(B, c, H, dh, seed=5), f(B, c, H, dh, seed=6)
+
+    def arrays():
+        return (torch.zeros(B, T, H, dh, device=DEV, dtype=torch.bfloat16), torch.zeros(B, T, H, device=DEV),
+                torch.zeros(B, T, H, device=DEV), f(B, T, H, dh, seed=7), f(B, T, H, dh, seed=8))
+    a, b_ = arrays(), arrays()
+    cv = ops.cell_finish(do_c, dlse_c, o_c, lse_c, dK0, dV0, a[0][:, r], a[1][:, r], a[2][:, r], a[3][:, r], a[4][:, r])
+    cr = REF.cell_finish(do_c, dlse_c, o_c, lse_c, dK0, dV0, b_[0][:, r], b_[1][:, r], b_[2][:, r], b_[3][:, r], b_[4][:, r])
+    close(cv, cr, rtol=1e-4, atol=1e-4, what="corr")
+    for x, y, n_ in zip(a, b_, ("doc", "corr_all", "lsec", "dks", "dv")):
+        close(x, y, rtol=1e-2, atol=1e-4, what=n_)
