@@ -178,14 +178,38 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
   }
   const long long dense_rs = (long long)H * DH;  // contiguous [B,C,H,DH] tensors
   const long long dense_b = (long long)bd * C * dense_rs + hoff;
+  const int row0 = warp * 16, nb_lim = 2 * (warp + 1);
+  const int i0 = row0 + g, i1 = i0 + 8;
+  // per-row scalars first (self score, delta = dO.o, dO.v_raw, dO.o_c): their global loads are in flight
+  // together with the tile loads below instead of sitting between the two MMA phases
+  const long long orow0 = ((long long)(bd * C + i0) * H + h), orow1 = ((long long)(bd * C + i1) * H + h);
+  const float* dO0 = dO + orow0 * DH;
+  const float* dO1 = dO + orow1 * DH;
+  const bf16* ks0 = ks + b * vks.bs + i0 * vks.rs + hoff;
+  const bf16* ks1 = ks + b * vks.bs + i1 * vks.rs + hoff;
+  const bf16* vr0 = vr + b * vvr.bs + i0 * vvr.rs + hoff;
+  const bf16* vr1 = vr + b * vvr.bs + i1 * vvr.rs + hoff;
+  const float L0 = lse[orow0], L1 = lse[orow1];
+  const float ss0 = quad_dot_bf16<DH>(q + b * vq.bs + i0 * vq.rs + hoff, ks0, t) * scale;
+  const float ss1 = quad_dot_bf16<DH>(q + b * vq.bs + i1 * vq.rs + hoff, ks1, t) * scale;
+  const float ps0 = __expf(ss0 - L0), ps1 = __expf(ss1 - L1);
+  const float pc0 = __expf(lse_c[orow0] - L0), pc1 = __expf(lse_c[orow1] - L1);
+  const float delta0 = quad_dot_f32_bf16<DH>(dO0, o + orow0 * DH, t);
+  const float delta1 = quad_dot_f32_bf16<DH>(dO1, o + orow1 * DH, t);
+  const float dsv0 = quad_dot_f32_bf16<DH>(dO0, vr0, t), dsv1 = quad_dot_f32_bf16<DH>(dO1, vr1, t);
+  const float doc0 = quad_dot_f32<DH>(dO0, o_c + orow0 * DH, t);
+  const float doc1 = quad_dot_f32<DH>(dO1, o_c + orow1 * DH, t);
+  const float dss0 = ps0 * (dsv0 - delta0) * scale, dss1 = ps1 * (dsv1 - delta1) * scale;
+  if (t == 0) {
+    dlsec_acc[orow0] += pc0 * (doc0 - delta0);
+    dlsec_acc[orow1] += pc1 * (doc1 - delta1);
+  }
   load_tile_bf16<DH, NT>(sQ, q + b * vq.bs + hoff, vq.rs, C, tid);
   load_tile_bf16<DH, NT>(sK, Kin + b * vKin.bs + hoff, vKin.rs, C, tid);
   load_tile_bf16<DH, NT>(sV, Vin + b * vVin.bs + hoff, vVin.rs, C, tid);
   load_tile_f32<DH, NT>(sdO, dO + dense_b, dense_rs, C, tid);
   __syncthreads();
 
-  const int row0 = warp * 16, nb_lim = 2 * (warp + 1);
-  const int i0 = row0 + g, i1 = i0 + 8;
   float S[NB][4], dP[NB][4];
 #pragma unroll
   for (int n = 0; n < NB; ++n) {
@@ -209,28 +233,6 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
         mma16816(dP[n + 1], ad, bb[2], bb[3]);
       }
     }
-  }
-  const long long orow0 = ((long long)(bd * C + i0) * H + h), orow1 = ((long long)(bd * C + i1) * H + h);
-  const float* dO0 = dO + orow0 * DH;
-  const float* dO1 = dO + orow1 * DH;
-  const bf16* ks0 = ks + b * vks.bs + i0 * vks.rs + hoff;
-  const bf16* ks1 = ks + b * vks.bs + i1 * vks.rs + hoff;
-  const bf16* vr0 = vr + b * vvr.bs + i0 * vvr.rs + hoff;
-  const bf16* vr1 = vr + b * vvr.bs + i1 * vvr.rs + hoff;
-  const float L0 = lse[orow0], L1 = lse[orow1];
-  const float ss0 = quad_dot_bf16<DH>(sQ + i0 * P, ks0, t) * scale;
-  const float ss1 = quad_dot_bf16<DH>(sQ + i1 * P, ks1, t) * scale;
-  const float ps0 = __expf(ss0 - L0), ps1 = __expf(ss1 - L1);
-  const float pc0 = __expf(lse_c[orow0] - L0), pc1 = __expf(lse_c[orow1] - L1);
-  const float delta0 = quad_dot_f32_bf16<DH>(dO0, o + orow0 * DH, t);
-  const float delta1 = quad_dot_f32_bf16<DH>(dO1, o + orow1 * DH, t);
-  const float dsv0 = quad_dot_f32_bf16<DH>(dO0, vr0, t), dsv1 = quad_dot_f32_bf16<DH>(dO1, vr1, t);
-  const float doc0 = quad_dot_f32<DH>(dO0, o_c + orow0 * DH, t);
-  const float doc1 = quad_dot_f32<DH>(dO1, o_c + orow1 * DH, t);
-  const float dss0 = ps0 * (dsv0 - delta0) * scale, dss1 = ps1 * (dsv1 - delta1) * scale;
-  if (t == 0) {
-    dlsec_acc[orow0] += pc0 * (doc0 - delta0);
-    dlsec_acc[orow1] += pc1 * (doc1 - delta1);
   }
   // P and dS for the intra block (zero where masked or skipped), kept as bf16 A-fragments and in smem
 #pragma unroll

@@ -67,40 +67,53 @@ __device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, long
   }
 }
 
-// per-row dot product of two DH-vectors split over the 4 lanes of a quad
+// per-row dot product of two DH-vectors split over the 4 lanes of a quad: lane t takes the contiguous
+// elements [t * DH/4, (t+1) * DH/4) with 16-byte loads (both rows must be 16-byte aligned: they are rows
+// of head slices of tensors whose head dim is a multiple of 32)
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(&u.x));
+  float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(&u.y));
+  float2 c = __bfloat1622float2(*reinterpret_cast<const bf162*>(&u.z));
+  float2 d = __bfloat1622float2(*reinterpret_cast<const bf162*>(&u.w));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
 template <int DH>
 __device__ __forceinline__ float quad_dot_bf16(const bf16* a, const bf16* b, int t) {
+  constexpr int PER = DH / 4;
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < DH / 8; ++i) {
-    int d = (i * 4 + t) * 2;
-    float2 x = __bfloat1622float2(*reinterpret_cast<const bf162*>(a + d));
-    float2 y = __bfloat1622float2(*reinterpret_cast<const bf162*>(b + d));
-    s += x.x * y.x + x.y * y.y;
+  for (int i = 0; i < PER / 8; ++i) {
+    float x[8], y[8];
+    unpack8(*reinterpret_cast<const uint4*>(a + t * PER + 8 * i), x);
+    unpack8(*reinterpret_cast<const uint4*>(b + t * PER + 8 * i), y);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += x[e] * y[e];
   }
   return quad_sum(s);
 }
 template <int DH>
 __device__ __forceinline__ float quad_dot_f32_bf16(const float* a, const bf16* b, int t) {
+  constexpr int PER = DH / 4;
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < DH / 8; ++i) {
-    int d = (i * 4 + t) * 2;
-    float2 x = *reinterpret_cast<const float2*>(a + d);
-    float2 y = __bfloat1622float2(*reinterpret_cast<const bf162*>(b + d));
-    s += x.x * y.x + x.y * y.y;
+  for (int i = 0; i < PER / 8; ++i) {
+    float y[8];
+    const float4 x0 = *reinterpret_cast<const float4*>(a + t * PER + 8 * i);
+    const float4 x1 = *reinterpret_cast<const float4*>(a + t * PER + 8 * i + 4);
+    unpack8(*reinterpret_cast<const uint4*>(b + t * PER + 8 * i), y);
+    s += x0.x * y[0] + x0.y * y[1] + x0.z * y[2] + x0.w * y[3] + x1.x * y[4] + x1.y * y[5] + x1.z * y[6] + x1.w * y[7];
   }
   return quad_sum(s);
 }
 template <int DH>
 __device__ __forceinline__ float quad_dot_f32(const float* a, const float* b, int t) {
+  constexpr int PER = DH / 4;
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < DH / 8; ++i) {
-    int d = (i * 4 + t) * 2;
-    float2 x = *reinterpret_cast<const float2*>(a + d);
-    float2 y = *reinterpret_cast<const float2*>(b + d);
-    s += x.x * y.x + x.y * y.y;
+  for (int i = 0; i < PER / 4; ++i) {
+    const float4 x = *reinterpret_cast<const float4*>(a + t * PER + 4 * i);
+    const float4 y = *reinterpret_cast<const float4*>(b + t * PER + 4 * i);
+    s += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
   }
   return quad_sum(s);
 }
