@@ -80,6 +80,7 @@ def parse_args(argv=None):
     a("--gn_hard", type=float, default=0.0)
     a("--rank_outlier_factor", type=float, default=0.0)
     a("--rank_outlier_max", type=int, default=1)
+    a("--peer_watch_s", type=float, default=0.0, help="> 0: host-side peer check before every step, with this timeout")
     a("--lr_gov", action="store_true")
     a("--auto_rewind", action="store_true")
     a("--rewind_window", type=int, default=50)
@@ -122,6 +123,14 @@ def _dist_setup(device_arg):
     return rank, world, dev
 
 
+def _peer_watch(args, rank, world):
+    if args.peer_watch_s <= 0 or world == 1:
+        return None
+    from ..parallel.heartbeat import PeerWatch
+    store = dist.distributed_c10d._get_default_store()
+    return PeerWatch(store, rank, world, timeout=args.peer_watch_s)
+
+
 def run(args):
     rank, world, dev = _dist_setup(args.device)
     master = rank == 0
@@ -153,7 +162,8 @@ def run(args):
                  weight_decay=args.weight_decay, decay_all=args.decay_all, max_norm=args.max_norm,
                  optimizer=args.optimizer, device=dev, autocast_bf16=not args.fp32 and dev.type == "cuda",
                  use_graphs=not args.no_graphs, seed=args.seed, engine=engine, engine_kwargs=ekw,
-                 rank_outlier_factor=args.rank_outlier_factor, rank_outlier_max=args.rank_outlier_max)
+                 rank_outlier_factor=args.rank_outlier_factor, rank_outlier_max=args.rank_outlier_max,
+                 peer_watch=_peer_watch(args, rank, world))
     if args.lr_gov and hasattr(tr.engine, "track_rho"):
         tr.engine.track_rho = True                       # before the first step: the graphs record it
     skip = SkipRule(skip_factor=args.skip_factor, grace_steps=args.skip_grace_steps, gn_hard=args.gn_hard)

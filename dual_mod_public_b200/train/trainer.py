@@ -28,7 +28,7 @@ class Trainer:
                  betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, decay_all=False, max_norm=1.0,
                  skip_norm=0.0, optimizer="fused", device=None, autocast_bf16=True, use_graphs=True,
                  overlap_buckets=True, process_group=None, seed=1337, engine="wavescan",
-                 engine_kwargs=None, model=None, rank_outlier_factor=0.0, rank_outlier_max=1):
+                 engine_kwargs=None, model=None, rank_outlier_factor=0.0, rank_outlier_max=1, peer_watch=None):
         assert local_batch % micro_batch == 0, "local batch must be a whole number of micro-batches"
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
@@ -64,6 +64,8 @@ class Trainer:
             # schedules: the K-ladder (sweep counts) of the wavefront engine, one per schedule id
             from ..engines.wave3d import Wave3DEngine
             self.engine = Wave3DEngine(self.model, schedules, micro_batch, seq_len, **common_e, **kw)
+        # optional host-side check that every peer is about to run the same step (parallel/heartbeat.py)
+        self.peer_watch = peer_watch
         self.engine.pack()
         self.steps_done = 0
         self._loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -84,6 +86,8 @@ class Trainer:
         tokens[:, :-1], targets tokens[:, 1:].  Returns the mean loss over the rank's
         micro-batches as a Python float (or the device tensor when read_loss=False)."""
         mb, T = self.micro_batch, self.T
+        if self.peer_watch is not None:
+            self.peer_watch.sync(self.steps_done)            # raises PeerLost before anything is launched
         self.opt.zero_grad()
         self._loss_acc.zero_()
         nb = self.device.type == "cuda"
