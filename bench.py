@@ -37,6 +37,7 @@ MODEL = dict(d_model=1024, n_layers=24, n_heads=16, mlp_hidden_override=2816, vo
              max_seq_len=2048, gate_bias_init=0.0, checkpoint_chunk=64)
 SEQ, CHUNK, SWEEPS, GLOBAL_SEQS = 2048, 64, 4, 256
 MODEL_NAME = "dm_340m (24L d1024 16x64 ffn2816 vocab32000 tied)"
+PROFILING = False
 
 
 class ClockSampler:
@@ -131,7 +132,7 @@ def run_ours(args):
     local_seqs = GLOBAL_SEQS // world
     micro = min(args.micro_batch, local_seqs)
     cfg = DualModConfig(**MODEL)
-    wave3d = args.config == "1p3b"
+    wave3d = args.config in ("1p3b", "hero")
     tr = Trainer(cfg, [SWEEPS] if wave3d else [uniform_chunks(SEQ, CHUNK, SWEEPS)], seq_len=SEQ, micro_batch=micro,
                  local_batch=local_seqs, lr=3e-4, weight_decay=0.01, max_norm=1.0,
                  optimizer=args.optimizer, device=f"cuda:{local}", use_graphs=not args.no_graphs,
@@ -164,7 +165,7 @@ def run_ours(args):
                "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
                "impl": "ours",
                "config": {"model": MODEL_NAME
-                          + ("" if MODEL["n_layers"] == 24 and GLOBAL_SEQS == 256 else " PROFILING SHAPE, NOT A BENCH VALUE"),
+                          + (" PROFILING SHAPE, NOT A BENCH VALUE" if PROFILING else ""),
                           "engine": f"{'wavefront (wave3d operator)' if wave3d else 'wavescan'} c={CHUNK} K={SWEEPS}",
                           "global_batch": GLOBAL_SEQS, "seq_len": SEQ,
                           "micro_batch": micro, "parallelism": f"dp{world}", "optimizer": args.optimizer,
@@ -279,9 +280,11 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("DMB_MICRO_BATCH", 32)))
     ap.add_argument("--optimizer", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--config", default="340m", choices=["340m", "1p3b"],
+    ap.add_argument("--config", default="340m", choices=["340m", "1p3b", "hero"],
                     help="340m: 24L d1024 wavescan c=64 K=4 at 256 x 2048 tokens per step (the headline); "
-                         "1p3b: 24L d2048 16x128 ffn5632 wavefront engine c=64 at 256 x 4096 tokens per step")
+                         "1p3b: 24L d2048 16x128 ffn5632 wavefront engine c=64 at 256 x 4096 tokens per step; "
+                         "hero: the reference's 1.3B recipe (18L d2304 36x64, rank-144 mult_res write law) on the "
+                         "wavefront engine at 128 x 4096 tokens per step, K=8")
     ap.add_argument("--sweeps", type=int, default=0, help="sweeps K (default 4; the 1.3B ladder is 2 / 4 / 8)")
     ap.add_argument("--profile-layers", type=int, default=0,
                     help="PROFILING ONLY: shrink the model to this many layers (the printed line is then "
@@ -295,9 +298,19 @@ def main():
         SEQ, MODEL_NAME = 4096, "dm_1p3b (24L d2048 16x128 ffn5632 vocab32000 tied)"
         if "DMB_MICRO_BATCH" not in os.environ and args.micro_batch == 32:
             args.micro_batch = 16
+    if args.config == "hero":
+        MODEL.clear()
+        MODEL.update(d_model=2304, n_layers=18, n_heads=36, vocab_size=32000, max_seq_len=4096, ctx_mod="mult_res",
+                     gate_rank=144, ctx_rank=144, k_ctx_norm="rms", kmod_vraw_heads=1, v_clamp_tau=150.0,
+                     gate_bias_init=0.0)
+        SEQ, SWEEPS, GLOBAL_SEQS = 4096, 8, 128
+        MODEL_NAME = "hero_1p3b (18L d2304 36x64 rank-144 mult_res, k_ctx_norm rms, v_clamp 150, 1 raw head)"
+        if "DMB_MICRO_BATCH" not in os.environ and args.micro_batch == 32:
+            args.micro_batch = 8
     if args.sweeps:
         SWEEPS = args.sweeps
-    profiling = bool(args.profile_layers or args.profile_seqs)
+    global PROFILING
+    profiling = PROFILING = bool(args.profile_layers or args.profile_seqs)
     if args.profile_layers:
         MODEL["n_layers"] = args.profile_layers
     if args.profile_seqs:

@@ -221,10 +221,8 @@ class Wave3DEngine(WaveScanEngine):
         o_n, lse_n = ops.win_near_fwd(qw, S.Kc, S.Vc, lo * C, (lo - K + 1) * C, C, S.scale)
         o_c, lse_c, w_f, w_n = ops.merge_partials(self.ofar_all[:, w], self.lsefar_all[:, w], o_n, lse_n)
         o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale)
-        raw = ops.linear(o.reshape(B, G * C, d), S.P.W_pack)
         # every window chunk's new rows replace the old ones (all reads of this step are done)
-        ops.refine_fwd(raw, ssq, S.glx[:, w], S.k[:, w], S.v[:, w], S.cos[w], S.sin[w], h, S.pin,
-                       out=(S.Kc[:, w], S.Vc[:, w]))
+        _, _, raw = self._refine_fwd(S, w, o, ssq, out=(S.Kc[:, w], S.Vc[:, w]))
         if s - K + 1 >= 0 and getattr(S, "o_all", None) is not None:
             S.o_all[:, lo * C:(lo + 1) * C] = o[:, :C].reshape(B, C, d)      # chunk lo's K-th read is final
         if save is not None:
@@ -244,6 +242,7 @@ class Wave3DEngine(WaveScanEngine):
         f32, dev = torch.float32, self.device
         Kc, Vc, scale = S.Kc, S.Vc, S.scale
         dcg_stash, u_stash, _ = self._stash_for(sid)
+        S.dcg_stash, S.u_stash = dcg_stash, u_stash
         offs = self._step_offsets(K)
         win = self._window_store(K)
         rows = lambda i: slice(i * C, (i + 1) * C)
@@ -268,13 +267,7 @@ class Wave3DEngine(WaveScanEngine):
             if far_grad is not None:
                 dK_out[:, :C] += far_grad[0]
                 dV_out[:, :C] += far_grad[1]
-            nr = B * G * C
-            dcg = dcg_stash[offs[s]:offs[s] + nr].view(B, G * C, 4 * d)
-            ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, G * C, d), S.glx[:, w], S.k[:, w], S.v[:, w],
-                           S.cos[w], S.sin[w], S.pin, S.dk[:, w], S.dv[:, w], S.dglx[:, w], dcg,
-                           u_stash[offs[s]:offs[s] + nr].view(B, G * C, d))
-            du = ops.linear_dx(dcg, S.P.W_pack)
-            d_o = ops.rmsn_bwd(du, o.reshape(B, G * C, d), ssq, residual=None)
+            d_o = self._refine_bwd(S, w, o, ssq, raw, dK_out, dV_out, offs[s], None)
             if j >= 0:                                          # chunk j's K-th read is the layer's output
                 d_o[:, :C] += S.dO_all[:, rows(j)].reshape(B, C, d)
             d_o = d_o.view(B, G * C, h, dh)

@@ -35,13 +35,24 @@ from .schedule import check_schedule
 FUSED_CTX_MODS = ("linear",)
 
 
-def fused_supported(cfg) -> bool:
+def packed_refine_supported(cfg) -> bool:
+    """The write law family with a fully hand-written refine step: one packed GEMM of the read, then the
+    fused gate / blend / RoPE kernels and their explicit backward."""
     return (cfg.attn_mode != "vanilla" and cfg.enable_key_mod and cfg.enable_value_mod
             and cfg.ctx_mod in FUSED_CTX_MODS and cfg.gate_type == "convex_sigmoid"
             and cfg.gate_type_v == "convex" and cfg.gate_input == "xu" and cfg.rmsnorm_on_o
             and cfg.v_norm == "none" and cfg.v_ctx_norm == "none" and cfg.k_ctx_norm == "none"
             and not cfg.v_clamp_tau and not cfg.attn_logn_ref
             and (cfg.kmod_vraw_heads == 0 or (cfg.kmod_mode == "raw" and cfg.kmod_vraw_bound == "none")))
+
+
+def fused_supported(cfg) -> bool:
+    """Configurations the kernel backend runs.  Outside the packed family the attention, projections,
+    MLP and head still run on the kernels; only the per-sweep write law `refine_kv` (any ctx_mod, gate
+    type, ctx norms, clamp, ...) runs as the module's own torch code on a compute-dtype copy of the layer,
+    differentiated per sweep by autograd."""
+    return (cfg.attn_mode != "vanilla" and cfg.dual_mod_active and cfg.v_norm == "none"
+            and not cfg.attn_logn_ref and cfg.n_kv_heads_eff == cfg.n_heads)
 
 
 def _dense(mod):
@@ -55,16 +66,32 @@ class _LayerPack:
     """Compute-dtype copies of one layer's weights in the layouts the ops want.
     Refreshed from the fp32 master parameters by `pack()` once per optimizer step."""
 
-    def __init__(self, blk, cfg, dtype, device):
+    def __init__(self, blk, cfg, dtype, device, packed=True):
         d, hid = cfg.d_model, cfg.mlp_hidden
         mk = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+        self.packed = packed
         self.w_an, self.w_mn, self.w_ctx = mk(d), mk(d), mk(d)
         self.wo = mk(d, d)
+        self.w1, self.w3, self.w2 = mk(hid, d), mk(hid, d), mk(d, hid)
+        if not packed:
+            # the write law runs as module code on `shadow`, a compute-dtype copy of the attention block
+            import copy
+            self.W_in, self.b_in = mk(3 * d, d), None
+            self.wq, self.wk, self.wv = self.W_in[:d], self.W_in[d:2 * d], self.W_in[2 * d:]
+            self.shadow = copy.deepcopy(blk.attn).to(device=device, dtype=dtype)
+            skip = {"wq.weight", "wk.weight", "wv.weight", "wo.weight"}
+            self.shadow_names = [n for n, _ in self.shadow.named_parameters() if n not in skip]
+            self.shadow_set = set(self.shadow_names)
+            for p_ in self.shadow.parameters():
+                p_.requires_grad_(False)
+            # fp32 gradient accumulators of the write law's weights, in the order of shadow_names
+            src = dict(self.shadow.named_parameters())
+            self.shadow_gacc = [torch.zeros_like(src[n], dtype=torch.float32) for n in self.shadow_names]
+            return
         # one input projection for q, k, v and the x-half of both gates: [wq ; wk ; wv ; W_gx], bias
         # [0 ; 0 ; 0 ; b_g] -- a single GEMM forward, a single dX and a single dW GEMM backward
         self.W_in, self.b_in = mk(5 * d, d), torch.zeros(5 * d, dtype=dtype, device=device)
         self.wq, self.wk, self.wv = self.W_in[:d], self.W_in[d:2 * d], self.W_in[2 * d:3 * d]
-        self.w1, self.w3, self.w2 = mk(hid, d), mk(hid, d), mk(d, hid)
         self.W_pack = mk(4 * d, d)        # [W_kctx ; W_vctx ; W_gk[:, d:] ; W_gv[:, d:]]
         self.W_gx = self.W_in[3 * d:]     # [W_gk[:, :d] ; W_gv[:, :d]]
         self.b_g = self.b_in[3 * d:]
@@ -74,10 +101,16 @@ class _LayerPack:
         a, d = blk.attn, cfg.d_model
         self.w_an.copy_(blk.attn_norm.weight)
         self.w_mn.copy_(blk.mlp_norm.weight)
-        self.w_ctx.copy_(a.norm_ctx.weight)
+        if self.packed:
+            self.w_ctx.copy_(a.norm_ctx.weight)
         for dst, src in ((self.wq, a.wq), (self.wk, a.wk), (self.wv, a.wv), (self.wo, a.wo),
                          (self.w1, blk.mlp.w1), (self.w3, blk.mlp.w3), (self.w2, blk.mlp.w2)):
             dst.copy_(src.weight)
+        if not self.packed:
+            src = dict(a.named_parameters())
+            for n, p_ in self.shadow.named_parameters():
+                p_.copy_(src[n])
+            return
         gk, gv = _dense(a.w_gk), _dense(a.w_gv)
         # the context-norm gain is folded into the packed weight's columns: the sweeps feed the
         # GEMM with the un-normalised read and apply 1/rms afterwards, row by row
@@ -154,7 +187,8 @@ class WaveScanEngine:
             self.corr_all = z(B, T, h, dt=torch.float32)
             self.lsec_all = z(B, T, h, dt=torch.float32)
             self.dK = self.dV = None
-            self.packs = [_LayerPack(b, cfg, act, dev) for b in model.blocks]
+            self.packed_refine = packed_refine_supported(cfg)
+            self.packs = [_LayerPack(b, cfg, act, dev, self.packed_refine) for b in model.blocks]
             self.emb_c = z(cfg.vocab_size, d)
             self.w_f = z(d)
             self.head_w = None if cfg.tie_embeddings else z(cfg.vocab_size, d)
@@ -379,13 +413,14 @@ class WaveScanEngine:
             x = self.xl[li]
             xhat, _ = ops.rms_fwd(x, P.w_an)
             qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
-            k, v, glx = qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d], qkvg[..., 3 * d:]
+            k, v = qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d]
+            glx = qkvg[..., 3 * d:] if self.packed_refine else None
             q_r = ops.rope(qkvg[..., :d].unflatten(-1, (h, dh)), cos, sin)
             kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
             Kc, Vc, o_all = self.K_caches[li], self.V_caches[li], self.o_saved[li]
             v4 = v.unflatten(-1, (h, dh))
             S = SimpleNamespace(P=P, q_r=q_r, kself_r=kself_r, v4=v4, k=k, v=v, glx=glx, Kc=Kc, Vc=Vc,
-                                o_all=o_all, cos=cos, sin=sin, scale=scale, pin=pin)
+                                o_all=o_all, cos=cos, sin=sin, scale=scale, pin=pin, xhat=xhat)
             self._cells_fwd(li, sid, S, keep)
             x_mid = x + ops.linear(o_all, P.wo)
             xn, _ = ops.rms_fwd(x_mid, P.w_mn)
@@ -408,20 +443,85 @@ class WaveScanEngine:
             for s in range(n_sweeps):
                 o, lse, ssq = ops.tail_fwd(q_r[:, r], kself_r[:, r], v4[:, r], K_in, V_in,
                                            o_c, lse_c, scale, self.window)
-                raw = ops.linear(o.reshape(B, c, d), P.W_pack)
-                if keep:
-                    # sweep 0 reads the raw rows, which the backward re-projects anyway
-                    st.append((K_in if s else None, V_in if s else None, o, lse, ssq, raw))
                 # the last sweep's refinement is the commit: written straight into the tape rows
                 last = s == n_sweeps - 1
-                K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, pin,
-                                            out=(Kc[:, r], Vc[:, r]) if last else None)
+                K_prev, V_prev = K_in, V_in
+                K_in, V_in, raw = self._refine_fwd(S, r, o, ssq, out=(Kc[:, r], Vc[:, r]) if last else None)
+                if keep:
+                    # sweep 0 reads the raw rows, which the backward re-projects anyway
+                    st.append((K_prev if s else None, V_prev if s else None, o, lse, ssq, raw))
             if keep:
                 kept.append(st)
             o_all[:, r] = o.reshape(B, c, d)
             self.stats["fwd_cells"] += 1
         if keep:
             self._sweep_saved[(sid, li)] = kept
+
+    # ---- the write law of one sweep -------------------------------------------------------------------
+    def _refine_fwd(self, S, r, o, ssq, out=None):
+        """(k'', v'') rows [B, c, h, dh] from the read `o` of the rows `r` (key rotated), written into `out`
+        when given.  Also returns what the backward wants besides (o, ssq): the packed ctx / gate logits
+        in the packed family, nothing when the write law runs as module code."""
+        ops, cfg = self.ops, self.cfg
+        B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
+        c = o.shape[1]
+        if self.packed_refine:
+            raw = ops.linear(o.reshape(B, c, d), S.P.W_pack)
+            K_new, V_new = ops.refine_fwd(raw, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h, S.pin,
+                                          out=out)
+            return K_new, V_new, raw
+        with torch.no_grad(), self._amp():
+            kpp, vpp = S.P.shadow.refine_kv(S.xhat[:, r], o.reshape(B, c, d), S.k[:, r], S.v[:, r])
+        K_new = ops.rope(kpp.unflatten(-1, (h, dh)), S.cos[r], S.sin[r])
+        V_new = vpp.unflatten(-1, (h, dh))
+        if out is not None:
+            out[0].copy_(K_new)
+            out[1].copy_(V_new)
+            return out[0], out[1], None
+        return K_new, V_new, None
+
+    def _refine_bwd(self, S, r, o, ssq, raw, dK_out, dV_out, stash_row, residual):
+        """Backward of `_refine_fwd` for one sweep: returns d loss / d o [B, c, d] fp32 (plus `residual`)
+        and accumulates the gradients of the layer-level inputs (S.dk, S.dv and, per family, the gate
+        x-logits S.dglx or the normed input S.dxhat_acc) and of the write law's weights (packed family:
+        stashed for one deferred GEMM per layer; module code: into the pack's fp32 accumulators)."""
+        ops, cfg = self.ops, self.cfg
+        B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
+        c = o.shape[1]
+        if self.packed_refine:
+            n = B * c
+            dcg = S.dcg_stash[stash_row:stash_row + n].view(B, c, 4 * d)
+            ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), S.glx[:, r], S.k[:, r], S.v[:, r],
+                           S.cos[r], S.sin[r], S.pin, S.dk[:, r], S.dv[:, r], S.dglx[:, r], dcg,
+                           S.u_stash[stash_row:stash_row + n].view(B, c, d))
+            du = ops.linear_dx(dcg, S.P.W_pack)
+            return ops.rmsn_bwd(du, o.reshape(B, c, d), ssq, residual=residual)
+        from ..models.rope import apply_rope
+        sh = S.P.shadow
+        params = [p_ for n_, p_ in sh.named_parameters() if n_ in S.P.shadow_set]
+        with torch.enable_grad(), self._amp():
+            ins = [t.detach().requires_grad_(True) for t in (o.reshape(B, c, d), S.xhat[:, r], S.k[:, r], S.v[:, r])]
+            for p_ in params:
+                p_.requires_grad_(True)
+            kpp, vpp = sh.refine_kv(ins[1], ins[0], ins[2], ins[3])
+            K_new = apply_rope(kpp.view(B, c, h, dh).transpose(1, 2), S.cos[r], S.sin[r])
+            V_new = vpp.view(B, c, h, dh)
+        gs = torch.autograd.grad([K_new, V_new], ins + params,
+                                 [dK_out.transpose(1, 2).to(K_new.dtype), dV_out.to(V_new.dtype)], allow_unused=True)
+        for p_ in params:
+            p_.requires_grad_(False)
+        zero = lambda t: torch.zeros_like(t, dtype=torch.float32)
+        d_o = gs[0].float() if gs[0] is not None else zero(ins[0])
+        if gs[1] is not None:
+            S.dxhat_acc[:, r] += gs[1]
+        if gs[2] is not None:
+            S.dk[:, r] += gs[2]
+        if gs[3] is not None:
+            S.dv[:, r] += gs[3]
+        for acc, g_ in zip(S.P.shadow_gacc, gs[4:]):
+            if g_ is not None:
+                acc += g_
+        return d_o if residual is None else d_o + residual
 
     def _prefix_slots(self, sid, li):
         """[(o_c [B,c,h,dh] fp32, lse_c [B,c,h] fp32)] per cell of layer li at schedule sid."""
@@ -527,41 +627,60 @@ class WaveScanEngine:
             # ---- recompute the layer projections ----------------------------------------------
             xhat, rstd_a = ops.rms_fwd(x, P.w_an)
             qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
-            q, k, v, glx = qkvg[..., :d], qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d], qkvg[..., 3 * d:]
+            q, k, v = qkvg[..., :d], qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d]
+            packed = self.packed_refine
+            glx = qkvg[..., 3 * d:] if packed else None
             q_r = ops.rope(q.unflatten(-1, (h, dh)), cos, sin)
             kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
             v4 = v.unflatten(-1, (h, dh))
             Kc, Vc = self.K_caches[li], self.V_caches[li]
-            self.dW_pack.zero_()
             dq_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
             dks_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
             dk = torch.zeros(B, T, d, dtype=f32, device=dev)
             dv = torch.zeros(B, T, d, dtype=f32, device=dev)
-            dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev)
+            dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev) if packed else None
+            dxhat_acc = None if packed else torch.zeros(B, T, d, dtype=f32, device=dev)
             dv4 = dv.view(B, T, h, dh)
+            if packed:
+                self.dW_pack.zero_()
+            else:
+                for acc in P.shadow_gacc:
+                    acc.zero_()
             S = SimpleNamespace(P=P, q_r=q_r, kself_r=kself_r, v4=v4, k=k, v=v, glx=glx, Kc=Kc, Vc=Vc,
                                 cos=cos, sin=sin, scale=scale, pin=pin, dO_all=dO_all, dq_r=dq_r, dks_r=dks_r,
-                                dk=dk, dv=dv, dglx=dglx, dv4=dv4)
+                                dk=dk, dv=dv, dglx=dglx, dv4=dv4, xhat=xhat, dxhat_acc=dxhat_acc)
             dcg_stash, u_stash = self._cells_bwd(li, sid, S, kept)
-            ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
-            self._unfold_packed_grad(a)
+            if packed:
+                ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
+                self._unfold_packed_grad(a)
             # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
-            dY = torch.empty(B, T, 5 * d, dtype=act, device=dev)      # [dq | dk | dv | dglx]
+            n_in = P.W_in.shape[0]
+            dY = torch.empty(B, T, n_in, dtype=act, device=dev)       # [dq | dk | dv (| dglx)]
             dY[..., :d] = ops.unrope(dq_r, cos, sin).reshape(B, T, d)
             dY[..., d:2 * d] = dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)
             dY[..., 2 * d:3 * d] = dv
-            dY[..., 3 * d:] = dglx
-            self.dW_in.zero_()
-            ops.linear_dw_acc(self.dW_in, dY, xhat)
-            G.get(a.wq.weight).add_(self.dW_in[:d])
-            G.get(a.wk.weight).add_(self.dW_in[d:2 * d])
-            G.get(a.wv.weight).add_(self.dW_in[2 * d:3 * d])
-            db_g = torch.zeros(2 * d, dtype=f32, device=dev)
-            ops.col_sum_acc(db_g, dglx)
+            if packed:
+                dY[..., 3 * d:] = dglx
+            dW_in = self.dW_in[:n_in]
+            dW_in.zero_()
+            ops.linear_dw_acc(dW_in, dY, xhat)
+            G.get(a.wq.weight).add_(dW_in[:d])
+            G.get(a.wk.weight).add_(dW_in[d:2 * d])
+            G.get(a.wv.weight).add_(dW_in[2 * d:3 * d])
             dxhat = ops.linear_dx(dY, P.W_in)
+            if packed:
+                db_g = torch.zeros(2 * d, dtype=f32, device=dev)
+                ops.col_sum_acc(db_g, dglx)
+            else:
+                dxhat = (dxhat.float() + dxhat_acc).to(act)           # the write law read the normed input too
             self.dx_cur.copy_(ops.rms_bwd(dxhat, x, P.w_an, rstd_a, G.get(blk.attn_norm.weight),
                                           residual=dx_mid, out_dtype=act))
-            self._scatter_packed_grads(a, db_g)
+            if packed:
+                self._scatter_packed_grads(a, db_g)
+            else:
+                master = dict(a.named_parameters())
+                for name, acc in zip(P.shadow_names, P.shadow_gacc):
+                    G.get(master[name]).add_(acc)
 
     def _cells_bwd(self, li, sid, S, kept):
         """Reverse scan over the cells of one layer.  Accumulates into S.dq_r / dks_r / dk / dv / dglx and
@@ -575,6 +694,7 @@ class WaveScanEngine:
         # ---- cells in reverse ---------------------------------------------------------------
         saved = self._prefix_slots(sid, li)
         dcg_stash, u_stash, stash_off = self._stash_for(sid)
+        S.dcg_stash, S.u_stash = dcg_stash, u_stash
         n_cells = len(self.schedules[sid])
         for ci in range(n_cells - 1, -1, -1):
             pos0, c, n_sweeps = self.schedules[sid][ci]
@@ -589,10 +709,9 @@ class WaveScanEngine:
                 K_in, V_in = ksc, vc4
                 for _ in range(n_sweeps):
                     o, lse, ssq = ops.tail_fwd(qc, ksc, vc4, K_in, V_in, o_c, lse_c, scale, self.window)
-                    raw = ops.linear(o.reshape(B, c, d), P.W_pack)
+                    K_new, V_new, raw = self._refine_fwd(S, r, o, ssq)
                     st.append((K_in, V_in, o, lse, ssq, raw))
-                    K_in, V_in = ops.refine_fwd(raw, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r],
-                                                h, pin)
+                    K_in, V_in = K_new, V_new
             # gradient of this cell's committed rows from every later cell's prefix read
             dK_out, dV_out = ops.prefix_dkv(q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
                                             pos0, c, pos0 + c, scale, self.window)
@@ -605,15 +724,8 @@ class WaveScanEngine:
             dlse_c = acc[2 * nv:].view(B, c, h)
             for s in range(n_sweeps - 1, -1, -1):
                 K_in, V_in, o, lse, ssq, raw = st[s]
-                off = stash_off[(ci, s)]
-                dcg = dcg_stash[off:off + B * c].view(B, c, 4 * d)
-                ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), glx[:, r], k[:, r], v[:, r],
-                               cos[r], sin[r], pin, dk[:, r], dv[:, r], dglx[:, r], dcg,
-                               u_stash[off:off + B * c].view(B, c, d))
-                du = ops.linear_dx(dcg, P.W_pack)
-                d_o = ops.rmsn_bwd(du, o.reshape(B, c, d), ssq,
-                                   residual=d_o.view(B, c, d) if s == n_sweeps - 1 else None
-                                   ).view(B, c, h, dh)
+                d_o = self._refine_bwd(S, r, o, ssq, raw, dK_out, dV_out, stash_off[(ci, s)],
+                                       d_o.view(B, c, d) if s == n_sweeps - 1 else None).view(B, c, h, dh)
                 dK_out, dV_out = ops.tail_bwd(
                     d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
                     dq_c, dks_r[:, r], dv4[:, r], do_c, dlse_c)

@@ -151,6 +151,11 @@ ENGINE_VARIANTS = [
     ("generic", dict()),
     ("generic", dict(ctx_mod="mult_res", gate_rank=8, ctx_rank=8, k_ctx_norm="rms",
                      kmod_vraw_heads=1, v_clamp_tau=0.8)),
+    # outside the packed family the kernel backend runs the write law as module code per sweep
+    ("fused", dict(ctx_mod="mult_res", gate_rank=8, ctx_rank=8, k_ctx_norm="rms",
+                   kmod_vraw_heads=1, v_clamp_tau=0.8)),
+    ("fused", dict(ctx_mod="fusion", gate_type_v="independent", v_ctx_norm="rms")),
+    ("fused", dict(gate_input="u", enable_key_mod=False)),
 ]
 
 

@@ -41,7 +41,11 @@ def grads_of(eng, model, idx, tgt):
     return loss, {n: eng.grads.get(p).clone() for n, p in model.named_parameters()}
 
 
-@pytest.mark.parametrize("kw,c,K", [(dict(), 64, 4), (dict(kmod_vraw_heads=1), 32, 32), (dict(local_window=100), 64, 2)])
+MRK = dict(ctx_mod="mult_res", gate_rank=16, ctx_rank=16, k_ctx_norm="rms", kmod_vraw_heads=1, v_clamp_tau=2.0)
+
+
+@pytest.mark.parametrize("kw,c,K", [(dict(), 64, 4), (dict(kmod_vraw_heads=1), 32, 32), (dict(local_window=100), 64, 2),
+                                    (MRK, 64, 3)])
 def test_kernel_engine_matches_fp32_torch_engine(kw, c, K):
     cfg, m = build(**kw)
     B, T = 4, 256
@@ -83,8 +87,9 @@ def test_wavefront_kernel_engine_matches_fp32_torch_engine(dh, K):
         assert (a.norm() / (b.norm() + 1e-30) - 1).abs() < 0.1, n
 
 
-def test_graph_replay_equals_eager_bitwise():
-    cfg, m = build()
+@pytest.mark.parametrize("kw", [dict(), MRK])
+def test_graph_replay_equals_eager_bitwise(kw):
+    cfg, m = build(**kw)
     B, T = 2, 256
     idx, tgt = batch(cfg, B, T)
     sched = uniform_chunks(T, 64, 4)

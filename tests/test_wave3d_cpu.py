@@ -32,7 +32,9 @@ def _engine(model, eng, idx, tgt, sid=0):
 
 
 @pytest.mark.parametrize("K,C,T", [(1, 4, 16), (2, 4, 24), (3, 4, 32), (4, 8, 32), (6, 4, 16)])
-@pytest.mark.parametrize("kw", [dict(), dict(kmod_vraw_heads=1)])
+@pytest.mark.parametrize("kw", [dict(), dict(kmod_vraw_heads=1),
+                                dict(ctx_mod="mult_res", gate_rank=8, ctx_rank=8, k_ctx_norm="rms", kmod_vraw_heads=1,
+                                     v_clamp_tau=0.8)])
 def test_fused_wavefront_matches_autograd(K, C, T, kw):
     cfg, m = build(**kw)
     idx, tgt = _data(cfg, 2, T, 3)
