@@ -278,6 +278,117 @@ def refine_bwd(dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols=0, eps
     return dcg, dk, dv, o.float() * rstd
 
 
+# ---- write law of the mult_res family (the reference's 1.3B recipe) ------------------------------
+#
+#   u    = rstd(o) * o * w_ctx                                    (context norm)
+#   cg   = rstd * (o @ W'^T) = [k_c | v_m | gate-u logits k | gate-u logits v],   W' = [W_kctx ; V_map ; W_gk_u ; W_gv_u] * w_ctx
+#   v_in = lam * u + sigmoid(vgx) * tanh(v_m)                     (vgx = v_gate(x) + bias, sweep-invariant)
+#   v_c  = v_in @ W_vctx^T                                        (second GEMM, outside these functions)
+#   k_n  = per-head rms(k_c) * k_gain                             (k_ctx_norm = rms, eps 1e-6)
+#   k''  = g_k k + (1 - g_k) k_n ,  v'' = g_v v + (1 - g_v) v_c  (convex sigmoid gates, fp32)
+#   v''  : first pin_cols columns keep the raw value; each head is projected onto the L2 ball of radius tau
+#   K    = rope(k'')
+
+def mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam, eps=1e-5):
+    """v_in [B,c,d] in o.dtype.  raw [B,c,4d] un-normalised packed logits; vgx [B,c,d] the x-logits of the
+    multiplicative branch's gate (bias included)."""
+    d = o.shape[-1]
+    rstd = row_rstd(ssq, d, eps)
+    u = o.float() * rstd * w_ctx.float()
+    vm = raw[..., d:2 * d].float() * rstd
+    return (lam * u + torch.sigmoid(vgx.float()) * torch.tanh(vm)).to(o.dtype)
+
+
+def mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam, eps=1e-5):
+    """Returns fp32 (dvm [B,c,d] = gradient w.r.t. cg[..., d:2d], dvgx [B,c,d], du_hat [B,c,d] = the direct path's
+    gradient w.r.t. uhat = rstd * o, dw_ctx [d] = the direct path's gradient of the context-norm gain)."""
+    d = o.shape[-1]
+    rstd = row_rstd(ssq, d, eps)
+    uhat = o.float() * rstd
+    t = torch.tanh(raw[..., d:2 * d].float() * rstd)
+    sg = torch.sigmoid(vgx.float())
+    g = dvin.float()
+    dvm = g * sg * (1.0 - t * t)
+    dvgx = g * t * sg * (1.0 - sg)
+    du_hat = lam * g * w_ctx.float()
+    dw_ctx = lam * (g * uhat).flatten(0, -2).sum(0)
+    return dvm, dvgx, du_hat, dw_ctx
+
+
+def _mrk_parts(raw, vc, ssq, glx, k, v, h, pin_cols, k_gain, tau, eps, eps_h):
+    B, c, d = k.shape
+    dh = d // h
+    rstd = row_rstd(ssq, d, eps)
+    cg = raw.float() * rstd
+    kc, gku, gvu = cg[..., :d], cg[..., 2 * d:3 * d], cg[..., 3 * d:]
+    kch = kc.view(B, c, h, dh)
+    rh = torch.rsqrt(kch.pow(2).mean(-1, keepdim=True) + eps_h)                # [B,c,h,1]
+    kn = (kch * rh * k_gain.float().view(1, 1, h, 1)).view(B, c, d)
+    gk = torch.sigmoid(glx[..., :d].float() + gku)
+    gv = torch.sigmoid(glx[..., d:].float() + gvu)
+    vcf = vc.float()
+    vpre = gv * v.float() + (1.0 - gv) * vcf
+    if pin_cols:
+        vpre = torch.cat((v[..., :pin_cols].float(), vpre[..., pin_cols:]), dim=-1)
+    vh = vpre.view(B, c, h, dh)
+    if tau and tau > 0:
+        nrm = vh.norm(dim=-1, keepdim=True).clamp_min(1e-20)
+        shrink = (tau / nrm).clamp(max=1.0)
+    else:
+        nrm, shrink = None, None
+    return rstd, kc, kch, rh, kn, gk, gv, vcf, vpre, vh, nrm, shrink
+
+
+def mrk_refine_fwd(raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, eps=1e-5, eps_h=1e-6):
+    """(K_out [B,c,h,dh] rotated, V_out [B,c,h,dh]) in k.dtype."""
+    B, c, d = k.shape
+    _, _, _, _, kn, gk, _, _, _, vh, _, shrink = _mrk_parts(raw, vc, ssq, glx, k, v, h, pin_cols, k_gain, tau, eps, eps_h)
+    kpp = gk * k.float() + (1.0 - gk) * kn
+    if shrink is not None:
+        vh = vh * shrink
+    K_out = rope_tm(kpp.view(B, c, h, d // h), cos, sin)
+    return K_out.to(k.dtype), vh.to(k.dtype)
+
+
+def mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, eps=1e-5, eps_h=1e-6):
+    """Returns fp32 (dcg [B,c,4d] with the v_m block left zero, dvc [B,c,d], dk [B,c,d], dv [B,c,d],
+    uhat [B,c,d], dk_gain [h]); dcg[..., 2d:] are also the gradients of glx."""
+    B, c, d = k.shape
+    dh = d // h
+    rstd, kc, kch, rh, kn, gk, gv, vcf, vpre, vh, nrm, shrink = _mrk_parts(
+        raw, vc, ssq, glx, k, v, h, pin_cols, k_gain, tau, eps, eps_h)
+    dkpp = unrope_tm(dK_out.float(), cos, sin).reshape(B, c, d)
+    dvo = dV_out.float()                                                        # [B,c,h,dh]
+    if shrink is not None:                                                      # projection onto the ball
+        inside = (nrm <= tau)
+        proj = (dvo * vh).sum(-1, keepdim=True) / (nrm * nrm)
+        dvpre = torch.where(inside, dvo, shrink * (dvo - vh * proj))
+    else:
+        dvpre = dvo
+    dvpre = dvpre.reshape(B, c, d)
+    dv_pin = None
+    if pin_cols:
+        dv_pin = dvpre[..., :pin_cols]
+        dvpre = torch.cat((torch.zeros_like(dv_pin), dvpre[..., pin_cols:]), dim=-1)
+    kf, vf = k.float(), v.float()
+    dgk = dkpp * (kf - kn) * gk * (1.0 - gk)
+    dgv = dvpre * (vf - vcf) * gv * (1.0 - gv)
+    dvc = dvpre * (1.0 - gv)
+    dk = dkpp * gk
+    dv = dvpre * gv
+    if pin_cols:
+        dv = torch.cat((dv_pin, dv[..., pin_cols:]), dim=-1)
+    # per-head rms + gain backward
+    dkn = (dkpp * (1.0 - gk)).view(B, c, h, dh)
+    gn = k_gain.float().view(1, 1, h, 1)
+    xhat_h = kch * rh
+    dk_gain = (dkn * xhat_h).sum(-1).flatten(0, 1).sum(0)
+    dx = dkn * gn
+    dkc = (rh * (dx - xhat_h * (dx * xhat_h).mean(-1, keepdim=True))).view(B, c, d)
+    dcg = torch.cat((dkc, torch.zeros_like(dkc), dgk, dgv), dim=-1)
+    return dcg, dvc, dk, dv, o.float() * rstd, dk_gain
+
+
 def rmsn_bwd(du, o, ssq, eps=1e-5):
     """Backward of uhat = o * rstd(o) (no gain): d o = rstd * (du - uhat * mean(du * uhat)). fp32."""
     d = o.shape[-1]

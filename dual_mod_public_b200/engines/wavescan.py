@@ -46,6 +46,21 @@ def packed_refine_supported(cfg) -> bool:
             and (cfg.kmod_vraw_heads == 0 or (cfg.kmod_mode == "raw" and cfg.kmod_vraw_bound == "none")))
 
 
+def mrk_refine_supported(cfg) -> bool:
+    """The mult_res family of the reference's 1.3B recipe (wave3d_ops.check_cfg, engines/wave3d/wave3d_ops.py:31-43):
+    multiplicative-residual value branch, per-head rms on the ctx key, optional value clamp and raw-pinned
+    heads, convex sigmoid gates on [x;u]; any LoRA rank.  Explicit forward / backward (fused_math.mrk_*)."""
+    return (cfg.attn_mode != "vanilla" and cfg.enable_key_mod and cfg.enable_value_mod
+            and cfg.ctx_mod == "mult_res" and cfg.gate_type == "convex_sigmoid" and cfg.gate_type_v == "convex"
+            and cfg.gate_input == "xu" and cfg.rmsnorm_on_o and cfg.k_ctx_norm == "rms"
+            and cfg.v_norm == "none" and cfg.v_ctx_norm == "none" and not cfg.attn_logn_ref
+            and (cfg.kmod_vraw_heads == 0 or (cfg.kmod_mode == "raw" and cfg.kmod_vraw_bound == "none")))
+
+
+def refine_family(cfg) -> str:
+    return "packed" if packed_refine_supported(cfg) else "mrk" if mrk_refine_supported(cfg) else "module"
+
+
 def fused_supported(cfg) -> bool:
     """Configurations the kernel backend runs.  Outside the packed family the attention, projections,
     MLP and head still run on the kernels; only the per-sweep write law `refine_kv` (any ctx_mod, gate
@@ -66,10 +81,12 @@ class _LayerPack:
     """Compute-dtype copies of one layer's weights in the layouts the ops want.
     Refreshed from the fp32 master parameters by `pack()` once per optimizer step."""
 
-    def __init__(self, blk, cfg, dtype, device, packed=True):
+    def __init__(self, blk, cfg, dtype, device, family="packed"):
         d, hid = cfg.d_model, cfg.mlp_hidden
         mk = lambda *s: torch.empty(*s, dtype=dtype, device=device)
-        self.packed = packed
+        self.family = family
+        self.packed = packed = family != "module"
+        n_in = 6 * d if family == "mrk" else 5 * d          # mrk: + the x-logits of the multiplicative branch's gate
         self.w_an, self.w_mn, self.w_ctx = mk(d), mk(d), mk(d)
         self.wo = mk(d, d)
         self.w1, self.w3, self.w2 = mk(hid, d), mk(hid, d), mk(d, hid)
@@ -90,11 +107,15 @@ class _LayerPack:
             return
         # one input projection for q, k, v and the x-half of both gates: [wq ; wk ; wv ; W_gx], bias
         # [0 ; 0 ; 0 ; b_g] -- a single GEMM forward, a single dX and a single dW GEMM backward
-        self.W_in, self.b_in = mk(5 * d, d), torch.zeros(5 * d, dtype=dtype, device=device)
+        self.W_in, self.b_in = mk(n_in, d), torch.zeros(n_in, dtype=dtype, device=device)
         self.wq, self.wk, self.wv = self.W_in[:d], self.W_in[d:2 * d], self.W_in[2 * d:3 * d]
-        self.W_pack = mk(4 * d, d)        # [W_kctx ; W_vctx ; W_gk[:, d:] ; W_gv[:, d:]]
-        self.W_gx = self.W_in[3 * d:]     # [W_gk[:, :d] ; W_gv[:, :d]]
-        self.b_g = self.b_in[3 * d:]
+        self.W_pack = mk(4 * d, d)        # [W_kctx ; W_vctx (mrk: V_map) ; W_gk[:, d:] ; W_gv[:, d:]]
+        self.W_gx = self.W_in[3 * d:5 * d]    # [W_gk[:, :d] ; W_gv[:, :d]]
+        self.b_g = self.b_in[3 * d:5 * d]
+        if family == "mrk":
+            self.W_vgate, self.b_vgate = self.W_in[5 * d:], self.b_in[5 * d:]
+            self.W_vctx = mk(d, d)
+            self.k_gain = torch.ones(cfg.n_heads, dtype=torch.float32, device=device)
 
     @torch.no_grad()
     def pack(self, blk, cfg):
@@ -116,7 +137,14 @@ class _LayerPack:
         # GEMM with the un-normalised read and apply 1/rms afterwards, row by row
         wc = a.norm_ctx.weight.float()[None, :]
         self.W_pack[:d].copy_(a.w_kctx.weight.float() * wc)
-        self.W_pack[d:2 * d].copy_(a.w_vctx.weight.float() * wc)
+        if self.family == "mrk":
+            self.W_pack[d:2 * d].copy_(a.v_map.weight.float() * wc)
+            self.W_vctx.copy_(a.w_vctx.weight)
+            self.W_vgate.copy_(a.v_gate.weight)
+            self.b_vgate.copy_(a.v_gate.bias)
+            self.k_gain.copy_(a.k_gain)
+        else:
+            self.W_pack[d:2 * d].copy_(a.w_vctx.weight.float() * wc)
         self.W_pack[2 * d:3 * d].copy_(gk[:, d:].float() * wc)
         self.W_pack[3 * d:].copy_(gv[:, d:].float() * wc)
         self.W_gx[:d].copy_(gk[:, :d])
@@ -187,14 +215,20 @@ class WaveScanEngine:
             self.corr_all = z(B, T, h, dt=torch.float32)
             self.lsec_all = z(B, T, h, dt=torch.float32)
             self.dK = self.dV = None
-            self.packed_refine = packed_refine_supported(cfg)
-            self.packs = [_LayerPack(b, cfg, act, dev, self.packed_refine) for b in model.blocks]
+            self.family = refine_family(cfg)
+            self.packed_refine = self.family != "module"      # packed GEMM + explicit backward (both kernel families)
+            self.packs = [_LayerPack(b, cfg, act, dev, self.family) for b in model.blocks]
             self.emb_c = z(cfg.vocab_size, d)
             self.w_f = z(d)
             self.head_w = None if cfg.tie_embeddings else z(cfg.vocab_size, d)
             self.dW_pack = z(4 * d, d, dt=torch.float32)
-            self.dW_in = z(5 * d, d, dt=torch.float32)
-            self.dW_gx = self.dW_in[3 * d:]
+            self.dW_in = z(6 * d, d, dt=torch.float32)
+            self.dW_gx = self.dW_in[3 * d:5 * d]
+            if refine_family(cfg) == "mrk":
+                self.dW_vctx = z(d, d, dt=torch.float32)
+                self.dkgain_acc = z(cfg.n_heads, dt=torch.float32)
+                self.dwctx_acc = z(d, dt=torch.float32)
+                self._stash2 = {}
             # committed-prefix partials of every cell, kept from the forward so the backward
             # does not redo the prefix pass: per schedule, [L][n_cells] dense slots
             self._prefix_saved = {}
@@ -414,13 +448,14 @@ class WaveScanEngine:
             xhat, _ = ops.rms_fwd(x, P.w_an)
             qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
             k, v = qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d]
-            glx = qkvg[..., 3 * d:] if self.packed_refine else None
+            glx = qkvg[..., 3 * d:5 * d] if self.packed_refine else None
+            vgx = qkvg[..., 5 * d:] if self.family == "mrk" else None
             q_r = ops.rope(qkvg[..., :d].unflatten(-1, (h, dh)), cos, sin)
             kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
             Kc, Vc, o_all = self.K_caches[li], self.V_caches[li], self.o_saved[li]
             v4 = v.unflatten(-1, (h, dh))
             S = SimpleNamespace(P=P, q_r=q_r, kself_r=kself_r, v4=v4, k=k, v=v, glx=glx, Kc=Kc, Vc=Vc,
-                                o_all=o_all, cos=cos, sin=sin, scale=scale, pin=pin, xhat=xhat)
+                                o_all=o_all, cos=cos, sin=sin, scale=scale, pin=pin, xhat=xhat, vgx=vgx)
             self._cells_fwd(li, sid, S, keep)
             x_mid = x + ops.linear(o_all, P.wo)
             xn, _ = ops.rms_fwd(x_mid, P.w_mn)
@@ -465,11 +500,19 @@ class WaveScanEngine:
         ops, cfg = self.ops, self.cfg
         B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
         c = o.shape[1]
-        if self.packed_refine:
+        if self.family == "packed":
             raw = ops.linear(o.reshape(B, c, d), S.P.W_pack)
             K_new, V_new = ops.refine_fwd(raw, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h, S.pin,
                                           out=out)
             return K_new, V_new, raw
+        if self.family == "mrk":
+            o2 = o.reshape(B, c, d)
+            raw = ops.linear(o2, S.P.W_pack)
+            vin = ops.mrk_vin_fwd(raw, ssq, o2, S.P.w_ctx, S.vgx[:, r], cfg.mult_res_lambda)
+            vc = ops.linear(vin, S.P.W_vctx)
+            K_new, V_new = ops.mrk_refine_fwd(raw, vc, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h,
+                                              S.pin, S.P.k_gain, cfg.v_clamp_tau, out=out)
+            return K_new, V_new, (raw, vc)
         with torch.no_grad(), self._amp():
             kpp, vpp = S.P.shadow.refine_kv(S.xhat[:, r], o.reshape(B, c, d), S.k[:, r], S.v[:, r])
         K_new = ops.rope(kpp.unflatten(-1, (h, dh)), S.cos[r], S.sin[r])
@@ -488,7 +531,23 @@ class WaveScanEngine:
         ops, cfg = self.ops, self.cfg
         B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
         c = o.shape[1]
-        if self.packed_refine:
+        if self.family == "mrk":
+            n, o2, P = B * c, o.reshape(B, c, d), S.P
+            raw, vc = raw
+            lam = cfg.mult_res_lambda
+            dcg = S.dcg_stash[stash_row:stash_row + n].view(B, c, 4 * d)
+            dvc = S.dvc_stash[stash_row:stash_row + n].view(B, c, d)
+            ops.mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o2, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r],
+                               S.pin, P.k_gain, cfg.v_clamp_tau, S.dk[:, r], S.dv[:, r], S.dglx[:, r], self.dkgain_acc,
+                               dcg, S.u_stash[stash_row:stash_row + n].view(B, c, d), dvc)
+            dvin = ops.linear_dx(dvc, P.W_vctx)
+            # v_in again (cheap) for the deferred W_vctx gradient: one GEMM per layer over all sweeps' rows
+            S.vin_stash[stash_row:stash_row + n].view(B, c, d).copy_(
+                ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam))
+            du_hat = ops.mrk_vin_bwd(dvin, raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam, dcg, S.dvgx[:, r], self.dwctx_acc)
+            du = (ops.linear_dx(dcg, P.W_pack).float() + du_hat).to(self.act)
+            return ops.rmsn_bwd(du, o2, ssq, residual=residual)
+        if self.family == "packed":
             n = B * c
             dcg = S.dcg_stash[stash_row:stash_row + n].view(B, c, 4 * d)
             ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), S.glx[:, r], S.k[:, r], S.v[:, r],
@@ -546,6 +605,16 @@ class WaveScanEngine:
             self._dw_stash[sid] = (torch.zeros(n, 4 * d, dtype=self.act, device=self.device),
                                    torch.zeros(n, d, dtype=self.act, device=self.device), offs)
         return self._dw_stash[sid]
+
+    def _stash2_for(self, sid):
+        """(d v_c stash, v_in stash) [rows, d] of every sweep of a layer: the W_vctx gradient of the mult_res
+        family is one deferred GEMM per layer, like the packed weight's."""
+        if sid not in self._stash2:
+            n = self._stash_for(sid)[0].shape[0]
+            d = self.cfg.d_model
+            self._stash2[sid] = (torch.zeros(n, d, dtype=self.act, device=self.device),
+                                 torch.zeros(n, d, dtype=self.act, device=self.device))
+        return self._stash2[sid]
 
     def _head_weight(self):
         return self.emb_c if self.head_w is None else self.head_w
@@ -628,8 +697,9 @@ class WaveScanEngine:
             xhat, rstd_a = ops.rms_fwd(x, P.w_an)
             qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
             q, k, v = qkvg[..., :d], qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d]
-            packed = self.packed_refine
-            glx = qkvg[..., 3 * d:] if packed else None
+            packed, mrk = self.packed_refine, self.family == "mrk"
+            glx = qkvg[..., 3 * d:5 * d] if packed else None
+            vgx = qkvg[..., 5 * d:] if mrk else None
             q_r = ops.rope(q.unflatten(-1, (h, dh)), cos, sin)
             kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
             v4 = v.unflatten(-1, (h, dh))
@@ -648,10 +718,17 @@ class WaveScanEngine:
                     acc.zero_()
             S = SimpleNamespace(P=P, q_r=q_r, kself_r=kself_r, v4=v4, k=k, v=v, glx=glx, Kc=Kc, Vc=Vc,
                                 cos=cos, sin=sin, scale=scale, pin=pin, dO_all=dO_all, dq_r=dq_r, dks_r=dks_r,
-                                dk=dk, dv=dv, dglx=dglx, dv4=dv4, xhat=xhat, dxhat_acc=dxhat_acc)
+                                dk=dk, dv=dv, dglx=dglx, dv4=dv4, xhat=xhat, dxhat_acc=dxhat_acc, vgx=vgx)
+            if mrk:
+                S.dvgx = torch.zeros(B, T, d, dtype=f32, device=dev)
+                S.dvc_stash, S.vin_stash = self._stash2_for(sid)
+                for t_ in (self.dW_vctx, self.dkgain_acc, self.dwctx_acc):
+                    t_.zero_()
             dcg_stash, u_stash = self._cells_bwd(li, sid, S, kept)
             if packed:
                 ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
+                if mrk:
+                    ops.linear_dw_acc(self.dW_vctx, S.dvc_stash, S.vin_stash)
                 self._unfold_packed_grad(a)
             # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
             n_in = P.W_in.shape[0]
@@ -660,7 +737,9 @@ class WaveScanEngine:
             dY[..., d:2 * d] = dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)
             dY[..., 2 * d:3 * d] = dv
             if packed:
-                dY[..., 3 * d:] = dglx
+                dY[..., 3 * d:5 * d] = dglx
+            if mrk:
+                dY[..., 5 * d:] = S.dvgx
             dW_in = self.dW_in[:n_in]
             dW_in.zero_()
             ops.linear_dw_acc(dW_in, dY, xhat)
@@ -677,6 +756,8 @@ class WaveScanEngine:
                                           residual=dx_mid, out_dtype=act))
             if packed:
                 self._scatter_packed_grads(a, db_g)
+                if mrk:
+                    self._scatter_mrk_grads(a, S.dvgx)
             else:
                 master = dict(a.named_parameters())
                 for name, acc in zip(P.shadow_names, P.shadow_gacc):
@@ -759,20 +840,20 @@ class WaveScanEngine:
         d w_ctx = sum_rows dW' * W and dW = dW' * w_ctx."""
         d = self.cfg.d_model
         gk, gv = _dense(a.w_gk), _dense(a.w_gv)
-        W = torch.cat((a.w_kctx.weight, a.w_vctx.weight, gk[:, d:], gv[:, d:]), dim=0).float()
+        second = a.v_map if self.family == "mrk" else a.w_vctx
+        W = torch.cat((a.w_kctx.weight, second.weight, gk[:, d:], gv[:, d:]), dim=0).float()
         self.grads.get(a.norm_ctx.weight).add_((self.dW_pack * W).sum(0))
+        if self.family == "mrk":
+            self.grads.get(a.norm_ctx.weight).add_(self.dwctx_acc)      # u also enters v_in directly
         self.dW_pack.mul_(a.norm_ctx.weight.float()[None, :])
 
     def _scatter_packed_grads(self, a, db_g):
         """Route the packed-weight gradients of one layer to the parameters."""
         G, d = self.grads, self.cfg.d_model
         dWp, dWx = self.dW_pack, self.dW_gx
-        for mod, rows in ((a.w_kctx, slice(0, d)), (a.w_vctx, slice(d, 2 * d))):
-            if isinstance(mod, LoRALinear):
-                G.get(mod.up.weight).add_(dWp[rows] @ mod.down.weight.float().t())
-                G.get(mod.down.weight).add_(mod.up.weight.float().t() @ dWp[rows])
-            else:
-                G.get(mod.weight).add_(dWp[rows])
+        second = a.v_map if self.family == "mrk" else a.w_vctx
+        for mod, rows in ((a.w_kctx, slice(0, d)), (second, slice(d, 2 * d))):
+            self._add_linear_grad(mod, dWp[rows])
         for mod, ru, rx, rb in ((a.w_gk, slice(2 * d, 3 * d), slice(0, d), slice(0, d)),
                                 (a.w_gv, slice(3 * d, 4 * d), slice(d, 2 * d), slice(d, 2 * d))):
             dW = torch.cat((dWx[rx], dWp[ru]), dim=1)                 # [d, 2d] = [x half | u half]
@@ -783,6 +864,29 @@ class WaveScanEngine:
             else:
                 G.get(mod.weight).add_(dW)
                 G.get(mod.bias).add_(db_g[rb])
+
+    def _add_linear_grad(self, mod, dW, db=None):
+        """Route the gradient of a dense [out, in] weight to a Linear or to the two factors of a LoRALinear."""
+        G = self.grads
+        if isinstance(mod, LoRALinear):
+            G.get(mod.up.weight).add_(dW @ mod.down.weight.float().t())
+            G.get(mod.down.weight).add_(mod.up.weight.float().t() @ dW)
+            if db is not None:
+                G.get(mod.up.bias).add_(db)
+        else:
+            G.get(mod.weight).add_(dW)
+            if db is not None:
+                G.get(mod.bias).add_(db)
+
+    def _scatter_mrk_grads(self, a, dvgx):
+        """Weights only the mult_res family has: W_vctx (deferred GEMM), the gate of the multiplicative branch
+        (rows 5d:6d of the input projection's gradient, bias = column sums of its logits' gradient), k_gain."""
+        d = self.cfg.d_model
+        self._add_linear_grad(a.w_vctx, self.dW_vctx)
+        db = torch.zeros(d, dtype=torch.float32, device=self.device)
+        self.ops.col_sum_acc(db, dvgx)
+        self._add_linear_grad(a.v_gate, self.dW_in[5 * d:6 * d], db)
+        self.grads.get(a.k_gain).add_(self.dkgain_acc)
 
     # =============================================================================
     # generic backend (every config knob; autograd re-run of the reference cell)

@@ -180,6 +180,44 @@ class TorchOps:
         out[1].copy_(V)
         return out
 
+    # ---- write law of the mult_res family (engines/fused_math.py: mrk_*) ------------------------------------
+    def mrk_vin_fwd(self, raw, ssq, o, w_ctx, vgx, lam):
+        return fm.mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
+
+    def mrk_vin_bwd(self, dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc, dwctx_acc):
+        """Writes d v_m into dcg[..., d:2d], accumulates dvgx_acc [B,c,d] and dwctx_acc [d] (fp32, +=); returns
+        the direct path's gradient w.r.t. uhat [B,c,d] fp32."""
+        d = o.shape[-1]
+        dvm, dvgx, du_hat, dwc = fm.mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam)
+        dcg[..., d:2 * d].copy_(dvm)
+        dvgx_acc += dvgx
+        dwctx_acc += dwc
+        return du_hat
+
+    def mrk_refine_fwd(self, raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, out=None):
+        K, V = fm.mrk_refine_fwd(raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau)
+        if out is None:
+            return K, V
+        out[0].copy_(K)
+        out[1].copy_(V)
+        return out
+
+    def mrk_refine_bwd(self, dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, pin_cols, k_gain, tau,
+                       dk_acc, dv_acc, dglx_acc, dkgain_acc, dcg_out, uhat_out, dvc_out):
+        """Accumulates dk_acc / dv_acc [B,c,d], dglx_acc [B,c,2d], dkgain_acc [h] (fp32, +=); writes dcg_out
+        [B,c,4d] (its v_m block is filled by `mrk_vin_bwd`), uhat_out [B,c,d] and dvc_out [B,c,d]."""
+        h = dK_out.shape[2]
+        d = k.shape[-1]
+        dcg, dvc, dk, dv, uhat, dkg = fm.mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, h,
+                                                         pin_cols, k_gain, tau)
+        dk_acc += dk
+        dv_acc += dv
+        dglx_acc += dcg[..., 2 * d:]
+        dkgain_acc += dkg
+        dcg_out.copy_(dcg)
+        uhat_out.copy_(uhat)
+        dvc_out.copy_(dvc)
+
     def refine_bwd(self, dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc, dglx_acc,
                    dcg_out, uhat_out):
         """Accumulates dk_acc / dv_acc [B,c,d] and dglx_acc [B,c,2d] (fp32, +=); writes the

@@ -194,6 +194,16 @@ def test_fused_backward_matches_autograd_for_few_sweeps(kw):
         assert relerr(gf[n], gg[n]) < 1e-4, n
 
 
+def test_write_law_families():
+    from dual_mod_public_b200 import preset
+    from dual_mod_public_b200.engines.wavescan import refine_family
+    assert refine_family(cfg_small()) == "packed"
+    assert refine_family(cfg_small(ctx_mod="mult_res", gate_rank=8, ctx_rank=8, k_ctx_norm="rms", kmod_vraw_heads=1,
+                                   v_clamp_tau=0.8)) == "mrk"
+    assert refine_family(preset("hero_1p3b")) == "mrk"
+    assert refine_family(cfg_small(ctx_mod="fusion", gate_type_v="independent", v_ctx_norm="rms")) == "module"
+
+
 def test_kept_sweep_states_equal_recompute():
     """Keeping every sweep's state from the forward (all layers, one layer, none) gives the same
     gradients as re-running the sweeps in the reverse scan."""
