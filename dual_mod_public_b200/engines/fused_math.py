@@ -301,18 +301,17 @@ def mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam, eps=1e-5):
 
 def mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam, eps=1e-5):
     """Returns fp32 (dvm [B,c,d] = gradient w.r.t. cg[..., d:2d], dvgx [B,c,d], du_hat [B,c,d] = the direct path's
-    gradient w.r.t. uhat = rstd * o, dw_ctx [d] = the direct path's gradient of the context-norm gain)."""
+    gradient w.r.t. uhat = rstd * o).  The direct path's gradient of the context-norm gain is
+    lam * sum_rows(dvin * uhat), formed once per layer from the stashed rows."""
     d = o.shape[-1]
     rstd = row_rstd(ssq, d, eps)
-    uhat = o.float() * rstd
     t = torch.tanh(raw[..., d:2 * d].float() * rstd)
     sg = torch.sigmoid(vgx.float())
     g = dvin.float()
     dvm = g * sg * (1.0 - t * t)
     dvgx = g * t * sg * (1.0 - sg)
     du_hat = lam * g * w_ctx.float()
-    dw_ctx = lam * (g * uhat).flatten(0, -2).sum(0)
-    return dvm, dvgx, du_hat, dw_ctx
+    return dvm, dvgx, du_hat
 
 
 def _mrk_parts(raw, vc, ssq, glx, k, v, h, pin_cols, k_gain, tau, eps, eps_h):
@@ -352,7 +351,7 @@ def mrk_refine_fwd(raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, 
 
 def mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, eps=1e-5, eps_h=1e-6):
     """Returns fp32 (dcg [B,c,4d] with the v_m block left zero, dvc [B,c,d], dk [B,c,d], dv [B,c,d],
-    uhat [B,c,d], dk_gain [h]); dcg[..., 2d:] are also the gradients of glx."""
+    uhat [B,c,d], dkg [B,c,h] = per-row gradient of k_gain); dcg[..., 2d:] are also the gradients of glx."""
     B, c, d = k.shape
     dh = d // h
     rstd, kc, kch, rh, kn, gk, gv, vcf, vpre, vh, nrm, shrink = _mrk_parts(
@@ -382,7 +381,7 @@ def mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, h, pin_
     dkn = (dkpp * (1.0 - gk)).view(B, c, h, dh)
     gn = k_gain.float().view(1, 1, h, 1)
     xhat_h = kch * rh
-    dk_gain = (dkn * xhat_h).sum(-1).flatten(0, 1).sum(0)
+    dk_gain = (dkn * xhat_h).sum(-1)
     dx = dkn * gn
     dkc = (rh * (dx - xhat_h * (dx * xhat_h).mean(-1, keepdim=True))).view(B, c, d)
     dcg = torch.cat((dkc, torch.zeros_like(dkc), dgk, dgv), dim=-1)

@@ -534,19 +534,18 @@ class WaveScanEngine:
         if self.family == "mrk":
             n, o2, P = B * c, o.reshape(B, c, d), S.P
             raw, vc = raw
-            lam = cfg.mult_res_lambda
-            dcg = S.dcg_stash[stash_row:stash_row + n].view(B, c, 4 * d)
-            dvc = S.dvc_stash[stash_row:stash_row + n].view(B, c, d)
+            lam, rows = cfg.mult_res_lambda, slice(stash_row, stash_row + n)
+            dcg = S.dcg_stash[rows].view(B, c, 4 * d)
+            dvc = S.dvc_stash[rows].view(B, c, d)
             ops.mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o2, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r],
-                               S.pin, P.k_gain, cfg.v_clamp_tau, S.dk[:, r], S.dv[:, r], S.dglx[:, r], self.dkgain_acc,
-                               dcg, S.u_stash[stash_row:stash_row + n].view(B, c, d), dvc)
-            dvin = ops.linear_dx(dvc, P.W_vctx)
+                               S.pin, P.k_gain, cfg.v_clamp_tau, S.dk[:, r], S.dv[:, r], S.dglx[:, r], dcg,
+                               S.u_stash[rows].view(B, c, d), dvc, S.dkg_stash[rows].view(B, c, h))
+            dvin = S.dvin_stash[rows].view(B, c, d)
+            dvin.copy_(ops.linear_dx(dvc, P.W_vctx))
             # v_in again (cheap) for the deferred W_vctx gradient: one GEMM per layer over all sweeps' rows
-            S.vin_stash[stash_row:stash_row + n].view(B, c, d).copy_(
-                ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam))
-            du_hat = ops.mrk_vin_bwd(dvin, raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam, dcg, S.dvgx[:, r], self.dwctx_acc)
-            du = (ops.linear_dx(dcg, P.W_pack).float() + du_hat).to(self.act)
-            return ops.rmsn_bwd(du, o2, ssq, residual=residual)
+            S.vin_stash[rows].view(B, c, d).copy_(ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam))
+            du_hat = ops.mrk_vin_bwd(dvin, raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam, dcg, S.dvgx[:, r])
+            return ops.rmsn_bwd(ops.linear_dx(dcg, P.W_pack), o2, ssq, residual=residual, extra=du_hat)
         if self.family == "packed":
             n = B * c
             dcg = S.dcg_stash[stash_row:stash_row + n].view(B, c, 4 * d)
@@ -607,13 +606,13 @@ class WaveScanEngine:
         return self._dw_stash[sid]
 
     def _stash2_for(self, sid):
-        """(d v_c stash, v_in stash) [rows, d] of every sweep of a layer: the W_vctx gradient of the mult_res
-        family is one deferred GEMM per layer, like the packed weight's."""
+        """(d v_c, v_in, d v_in) [rows, d] and the per-row k_gain gradient [rows, h] of every sweep of a layer:
+        the mult_res family's W_vctx gradient is one deferred GEMM per layer like the packed weight's, and its
+        two small reductions over rows (context-norm gain, k_gain) are done once per layer too."""
         if sid not in self._stash2:
             n = self._stash_for(sid)[0].shape[0]
-            d = self.cfg.d_model
-            self._stash2[sid] = (torch.zeros(n, d, dtype=self.act, device=self.device),
-                                 torch.zeros(n, d, dtype=self.act, device=self.device))
+            d, z = self.cfg.d_model, lambda w, dt: torch.zeros(n, w, dtype=dt, device=self.device)
+            self._stash2[sid] = (z(d, self.act), z(d, self.act), z(d, self.act), z(self.cfg.n_heads, torch.float32))
         return self._stash2[sid]
 
     def _head_weight(self):
@@ -721,7 +720,7 @@ class WaveScanEngine:
                                 dk=dk, dv=dv, dglx=dglx, dv4=dv4, xhat=xhat, dxhat_acc=dxhat_acc, vgx=vgx)
             if mrk:
                 S.dvgx = torch.zeros(B, T, d, dtype=f32, device=dev)
-                S.dvc_stash, S.vin_stash = self._stash2_for(sid)
+                S.dvc_stash, S.vin_stash, S.dvin_stash, S.dkg_stash = self._stash2_for(sid)
                 for t_ in (self.dW_vctx, self.dkgain_acc, self.dwctx_acc):
                     t_.zero_()
             dcg_stash, u_stash = self._cells_bwd(li, sid, S, kept)
@@ -729,6 +728,10 @@ class WaveScanEngine:
                 ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
                 if mrk:
                     ops.linear_dw_acc(self.dW_vctx, S.dvc_stash, S.vin_stash)
+                    # u enters v_in directly as well: d w_ctx += lam * sum_rows(d v_in * uhat); k_gain: sum of the rows
+                    ops.col_dot_acc(self.dwctx_acc, S.dvin_stash, u_stash)
+                    self.dwctx_acc.mul_(cfg.mult_res_lambda)
+                    ops.col_sum_acc(self.dkgain_acc, S.dkg_stash)
                 self._unfold_packed_grad(a)
             # ---- close the layer: projections, gate-x logits, attn_norm -----------------------------
             n_in = P.W_in.shape[0]

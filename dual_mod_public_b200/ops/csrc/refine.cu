@@ -8,66 +8,9 @@
 //   K_out = RoPE(k'') (rotated once, at write), V_out = v'' (first pin_cols columns keep raw v).
 // One thread owns 8 adjacent rotation pairs of one head: columns [c0, c0+8) and [c0+half, ..+8),
 // so every access is a 16-byte vector.
-#include "common.cuh"
+#include "refine_common.cuh"
 
 namespace {
-
-struct V8 {
-  float x[8];
-};
-__device__ __forceinline__ V8 ld8(const bf16* p) {
-  uint4 u = *reinterpret_cast<const uint4*>(p);
-  float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
-  return V8{{a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y}};
-}
-__device__ __forceinline__ void st8(bf16* p, const V8& v) {
-  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(v.x[0], v.x[1]), pack_bf16(v.x[2], v.x[3]),
-                                            pack_bf16(v.x[4], v.x[5]), pack_bf16(v.x[6], v.x[7]));
-}
-__device__ __forceinline__ V8 ld8f(const float* p) {
-  float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  return V8{{a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w}};
-}
-__device__ __forceinline__ void st8f(float* p, const V8& v) {
-  *reinterpret_cast<float4*>(p) = make_float4(v.x[0], v.x[1], v.x[2], v.x[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(v.x[4], v.x[5], v.x[6], v.x[7]);
-}
-__device__ __forceinline__ void acc8f(float* p, const V8& v) {
-  V8 o = ld8f(p);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) o.x[i] += v.x[i];
-  st8f(p, o);
-}
-__device__ __forceinline__ float row_rstd(const float* ssq_row, int H, int d, float eps) {
-  float s = 0.f;
-  for (int i = 0; i < H; i += 4) {
-    float4 v = *reinterpret_cast<const float4*>(ssq_row + i);
-    s += v.x + v.y + v.z + v.w;
-  }
-  return rsqrtf(s / d + eps);
-}
-
-struct Where {
-  long long row;   // b * C + t
-  int b, t, c0, c1; // chunk-local position and this thread's two column bases
-  int p0;          // first rotation pair index inside the head
-};
-__device__ __forceinline__ bool locate(Where& w, long long i, int B, int C, int H, int DH) {
-  const int half = DH >> 1, per_head = half >> 3;   // threads per head
-  const long long total = (long long)B * C * H * per_head;
-  if (i >= total) return false;
-  const int q = i % per_head;
-  long long r = i / per_head;
-  const int h = r % H;
-  r /= H;
-  w.t = r % C;
-  w.b = r / C;
-  w.row = (long long)w.b * C + w.t;
-  w.p0 = q * 8;
-  w.c0 = h * DH + w.p0;
-  w.c1 = w.c0 + half;
-  return true;
-}
 
 __global__ void refine_fwd_kernel(const bf16* __restrict__ raw, const float* __restrict__ ssq,
                                   const bf16* __restrict__ glx, TView vg, const bf16* __restrict__ k, TView vk,
@@ -177,21 +120,31 @@ __global__ void refine_bwd_kernel(const float* __restrict__ dK, const float* __r
 template <typename TOUT>
 __global__ void rmsn_bwd_kernel(const bf16* __restrict__ du, const bf16* __restrict__ o,
                                 const float* __restrict__ ssq, const TOUT* __restrict__ residual,
-                                TOUT* __restrict__ out, int rows, int d, int H, float eps) {
+                                const float* __restrict__ extra, TOUT* __restrict__ out, int rows, int d, int H,
+                                float eps) {
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= rows) return;
   const float rs = row_rstd(ssq + (long long)row * H, H, d, eps);
   const bf16* dur = du + (long long)row * d;
   const bf16* orow = o + (long long)row * d;
   float acc = 0.f;
+  const float* er = extra ? extra + (long long)row * d : nullptr;     // optional fp32 term added to du
   for (int c = lane * 8; c < d; c += 256) {
-    const V8 g = ld8(dur + c), x = ld8(orow + c);
+    V8 g = ld8(dur + c);
+    const V8 x = ld8(orow + c);
+    if (er) { const V8 q = ld8f(er + c);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g.x[i] += q.x[i]; }
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc += g.x[i] * x.x[i];
   }
   const float mean = warp_sum(acc) * rs / d;     // mean(du * uhat)
   for (int c = lane * 8; c < d; c += 256) {
-    const V8 g = ld8(dur + c), x = ld8(orow + c);
+    V8 g = ld8(dur + c);
+    const V8 x = ld8(orow + c);
+    if (er) { const V8 q = ld8f(er + c);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g.x[i] += q.x[i]; }
     V8 r;
 #pragma unroll
     for (int i = 0; i < 8; ++i) r.x[i] = rs * (g.x[i] - x.x[i] * rs * mean);
@@ -240,14 +193,14 @@ int dmb_refine_bwd(const float* dK, const float* dV, const void* raw, const floa
   return 0;
 }
 
-int dmb_rmsn_bwd(const void* du, const void* o, const float* ssq, const void* residual, void* out, int out_f32,
-                 int rows, int d, int H, float eps, cudaStream_t st) {
+int dmb_rmsn_bwd(const void* du, const void* o, const float* ssq, const void* residual, const float* extra, void* out,
+                 int out_f32, int rows, int d, int H, float eps, cudaStream_t st) {
   if (d % 8 || H % 4) return -1;
   dim3 grid((rows + 7) / 8), blk(256);
   if (out_f32)
-    rmsn_bwd_kernel<float><<<grid, blk, 0, st>>>((const bf16*)du, (const bf16*)o, ssq, (const float*)residual, (float*)out, rows, d, H, eps);
+    rmsn_bwd_kernel<float><<<grid, blk, 0, st>>>((const bf16*)du, (const bf16*)o, ssq, (const float*)residual, extra, (float*)out, rows, d, H, eps);
   else
-    rmsn_bwd_kernel<bf16><<<grid, blk, 0, st>>>((const bf16*)du, (const bf16*)o, ssq, (const bf16*)residual, (bf16*)out, rows, d, H, eps);
+    rmsn_bwd_kernel<bf16><<<grid, blk, 0, st>>>((const bf16*)du, (const bf16*)o, ssq, (const bf16*)residual, extra, (bf16*)out, rows, d, H, eps);
   DMB_CHECK_LAUNCH();
   return 0;
 }

@@ -53,7 +53,12 @@ class _Sigs:
     dmb_refine_fwd = [_p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _f, _p]
     dmb_refine_bwd = [_p, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
                       _i, _i, _i, _i, _i, _f, _p]
-    dmb_rmsn_bwd = [_p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p]
+    dmb_rmsn_bwd = [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p]
+    dmb_mrk_vin_fwd = [_p, _p, _p, _p, _p, _v, _p, _i, _i, _i, _i, _f, _f, _p]
+    dmb_mrk_vin_bwd = [_p, _p, _p, _p, _p, _v, _p, _p, _v, _p, _i, _i, _i, _i, _f, _f, _p]
+    dmb_mrk_refine_fwd = [_p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _f, _f, _p]
+    dmb_mrk_refine_bwd = [_p, _p, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _p, _p, _v, _p, _v,
+                          _p, _v, _i, _i, _i, _i, _i, _f, _f, _p]
     dmb_swiglu_fwd = [_p, _p, _p, _ll, _p]
     dmb_swiglu_bwd = [_p, _p, _p, _p, _p, _ll, _p]
     dmb_ce = [_p, _p, _p, _p, _p, _i, _i, _p]
@@ -184,6 +189,102 @@ class CudaOps(TorchOps):
         self._ck(self.lib.dmb_col_reduce_acc(dy.data_ptr(), int(dy.dtype == F32), None, 0, None,
                                              part.data_ptr(), nsplit, out.data_ptr(), rows, n,
                                              self._st()), "col_sum")
+        self.launches += 1
+
+    def col_dot_acc(self, out, a, b):
+        n = a.shape[-1]
+        if a.dtype != BF16 or b.dtype != BF16 or not a.is_contiguous() or not b.is_contiguous():
+            return super().col_dot_acc(out, a, b)
+        rows = a.numel() // n
+        nsplit = max(1, min(64, rows // 64))
+        part = self._scratch_f32("col", nsplit * n)
+        ones = self._scratch_f32("ones", rows)
+        if not getattr(self, "_ones_rows", 0) >= rows:
+            ones.fill_(1.0)
+            self._ones_rows = rows
+        self._ck(self.lib.dmb_col_reduce_acc(a.data_ptr(), 0, b.data_ptr(), n, ones.data_ptr(), part.data_ptr(), nsplit,
+                                             out.data_ptr(), rows, n, self._st()), "col_dot")
+        self.launches += 1
+
+    # ---- write law of the mult_res family ---------------------------------------------------------------------
+    def _mrk_ok(self, k, raw, *views):
+        B, c, d = k.shape
+        return (k.dtype == BF16 and raw.dtype == BF16 and raw.is_contiguous()
+                and all(_dense_tail(t, 1) for t in (k,) + views))
+
+    def mrk_vin_fwd(self, raw, ssq, o, w_ctx, vgx, lam):
+        B, c, d = o.shape
+        h = ssq.shape[-1]
+        dh = d // h
+        if not (self._mrk_ok(o, raw, vgx) and o.is_contiguous() and ssq.is_contiguous() and w_ctx.dtype == BF16
+                and vgx.dtype == BF16 and dh % 16 == 0 and h % 4 == 0):
+            return super().mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
+        vin = torch.empty(B, c, d, dtype=BF16, device=o.device)
+        self._ck(self.lib.dmb_mrk_vin_fwd(raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), w_ctx.data_ptr(), vgx.data_ptr(),
+                                          _tv(vgx), vin.data_ptr(), B, c, h, dh, lam, 1e-5, self._st()), "mrk_vin_fwd")
+        self.launches += 1
+        return vin
+
+    def mrk_vin_bwd(self, dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc):
+        B, c, d = o.shape
+        h = ssq.shape[-1]
+        dh = d // h
+        ok = (self._mrk_ok(o, raw, vgx, dvgx_acc) and dvin.dtype == BF16 and dvin.is_contiguous() and dcg.is_contiguous()
+              and dcg.dtype == BF16 and ssq.is_contiguous() and w_ctx.dtype == BF16 and vgx.dtype == BF16
+              and dvgx_acc.dtype == F32 and dh % 16 == 0 and h % 4 == 0)
+        if not ok:
+            return super().mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc)
+        du_hat = torch.empty(B, c, d, dtype=F32, device=o.device)
+        self._ck(self.lib.dmb_mrk_vin_bwd(dvin.data_ptr(), raw.data_ptr(), ssq.data_ptr(), w_ctx.data_ptr(), vgx.data_ptr(),
+                                          _tv(vgx), dcg.data_ptr(), dvgx_acc.data_ptr(), _tv(dvgx_acc), du_hat.data_ptr(),
+                                          B, c, h, dh, lam, 1e-5, self._st()), "mrk_vin_bwd")
+        self.launches += 1
+        return du_hat
+
+    def mrk_refine_fwd(self, raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, out=None):
+        B, c, d = k.shape
+        dh = d // h
+        ok = (self._mrk_ok(k, raw, glx, v) and vc.dtype == BF16 and vc.is_contiguous() and cos.is_contiguous()
+              and ssq.is_contiguous() and k_gain.dtype == F32 and dh % 16 == 0 and h % 4 == 0)
+        if not ok:
+            return super().mrk_refine_fwd(raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, out)
+        if (out is not None and all(t.dtype == BF16 and _dense_tail(t, 2) for t in out)
+                and out[0].stride() == out[1].stride()):
+            K_out, V_out = out
+        else:
+            K_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
+            V_out = torch.empty(B, c, h, dh, dtype=BF16, device=k.device)
+        self._ck(self.lib.dmb_mrk_refine_fwd(raw.data_ptr(), vc.data_ptr(), ssq.data_ptr(), glx.data_ptr(), _tv(glx),
+                                             k.data_ptr(), _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
+                                             k_gain.data_ptr(), K_out.data_ptr(), V_out.data_ptr(), _tv(K_out), B, c, h, dh,
+                                             pin_cols, float(tau or 0.0), 1e-5, self._st()), "mrk_refine_fwd")
+        self.launches += 1
+        if out is not None and K_out is not out[0]:
+            out[0].copy_(K_out)
+            out[1].copy_(V_out)
+            return out
+        return K_out, V_out
+
+    def mrk_refine_bwd(self, dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, pin_cols, k_gain, tau,
+                       dk_acc, dv_acc, dglx_acc, dcg_out, uhat_out, dvc_out, dkg_out):
+        B, c, d = k.shape
+        h = dK_out.shape[2]
+        dh = d // h
+        ok = (self._mrk_ok(k, raw, glx, v, dk_acc, dv_acc, dglx_acc) and vc.dtype == BF16 and vc.is_contiguous()
+              and o.dtype == BF16 and o.is_contiguous() and dK_out.dtype == F32 and dV_out.dtype == F32
+              and dK_out.is_contiguous() and dV_out.is_contiguous() and ssq.is_contiguous()
+              and all(t.is_contiguous() and t.dtype == BF16 for t in (dcg_out, uhat_out, dvc_out))
+              and dkg_out.is_contiguous() and dkg_out.dtype == F32 and k_gain.dtype == F32
+              and dh % 16 == 0 and h % 4 == 0)
+        if not ok:
+            return super().mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, pin_cols, k_gain, tau,
+                                          dk_acc, dv_acc, dglx_acc, dcg_out, uhat_out, dvc_out, dkg_out)
+        self._ck(self.lib.dmb_mrk_refine_bwd(
+            dK_out.data_ptr(), dV_out.data_ptr(), raw.data_ptr(), vc.data_ptr(), ssq.data_ptr(), o.data_ptr(),
+            glx.data_ptr(), _tv(glx), k.data_ptr(), _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
+            k_gain.data_ptr(), dcg_out.data_ptr(), uhat_out.data_ptr(), dvc_out.data_ptr(), dkg_out.data_ptr(),
+            dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(), _tv(dv_acc), dglx_acc.data_ptr(), _tv(dglx_acc),
+            B, c, h, dh, pin_cols, float(tau or 0.0), 1e-5, self._st()), "mrk_refine_bwd")
         self.launches += 1
 
     # ---- rope -----------------------------------------------------------------------------------------
@@ -498,17 +599,19 @@ class CudaOps(TorchOps):
             _tv(dv_acc), dglx_acc.data_ptr(), _tv(dglx_acc), B, c, h, dh, pin_cols, 1e-5, self._st()),
             "refine_bwd")
 
-    def rmsn_bwd(self, du, o, ssq, residual=None, out_dtype=F32):
+    def rmsn_bwd(self, du, o, ssq, residual=None, out_dtype=F32, extra=None):
         d = o.shape[-1]
         h = ssq.shape[-1]
         ok = (du.dtype == BF16 and o.dtype == BF16 and du.is_contiguous() and o.is_contiguous()
               and ssq.is_contiguous() and d % 8 == 0 and h % 4 == 0 and out_dtype in (BF16, F32)
-              and (residual is None or (residual.is_contiguous() and residual.dtype == out_dtype)))
+              and (residual is None or (residual.is_contiguous() and residual.dtype == out_dtype))
+              and (extra is None or (extra.is_contiguous() and extra.dtype == F32)))
         if not ok:
-            return super().rmsn_bwd(du, o, ssq, residual, out_dtype)
+            return super().rmsn_bwd(du, o, ssq, residual, out_dtype, extra)
         rows = o.numel() // d
         out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
         self._ck(self.lib.dmb_rmsn_bwd(du.data_ptr(), o.data_ptr(), ssq.data_ptr(),
-                                       residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                       residual.data_ptr() if residual is not None else None,
+                                       extra.data_ptr() if extra is not None else None, out.data_ptr(),
                                        int(out_dtype == F32), rows, d, h, 1e-5, self._st()), "rmsn_bwd")
         return out

@@ -184,14 +184,13 @@ class TorchOps:
     def mrk_vin_fwd(self, raw, ssq, o, w_ctx, vgx, lam):
         return fm.mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
 
-    def mrk_vin_bwd(self, dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc, dwctx_acc):
-        """Writes d v_m into dcg[..., d:2d], accumulates dvgx_acc [B,c,d] and dwctx_acc [d] (fp32, +=); returns
-        the direct path's gradient w.r.t. uhat [B,c,d] fp32."""
+    def mrk_vin_bwd(self, dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc):
+        """Writes d v_m into dcg[..., d:2d], accumulates dvgx_acc [B,c,d] (fp32, +=); returns the direct
+        path's gradient w.r.t. uhat [B,c,d] fp32."""
         d = o.shape[-1]
-        dvm, dvgx, du_hat, dwc = fm.mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam)
+        dvm, dvgx, du_hat = fm.mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam)
         dcg[..., d:2 * d].copy_(dvm)
         dvgx_acc += dvgx
-        dwctx_acc += dwc
         return du_hat
 
     def mrk_refine_fwd(self, raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, out=None):
@@ -203,9 +202,10 @@ class TorchOps:
         return out
 
     def mrk_refine_bwd(self, dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, pin_cols, k_gain, tau,
-                       dk_acc, dv_acc, dglx_acc, dkgain_acc, dcg_out, uhat_out, dvc_out):
-        """Accumulates dk_acc / dv_acc [B,c,d], dglx_acc [B,c,2d], dkgain_acc [h] (fp32, +=); writes dcg_out
-        [B,c,4d] (its v_m block is filled by `mrk_vin_bwd`), uhat_out [B,c,d] and dvc_out [B,c,d]."""
+                       dk_acc, dv_acc, dglx_acc, dcg_out, uhat_out, dvc_out, dkg_out):
+        """Accumulates dk_acc / dv_acc [B,c,d], dglx_acc [B,c,2d] (fp32, +=); writes dcg_out [B,c,4d] (its v_m
+        block is filled by `mrk_vin_bwd`), uhat_out [B,c,d], dvc_out [B,c,d] and dkg_out [B,c,h] (per-row
+        gradient of k_gain, summed over rows once per layer)."""
         h = dK_out.shape[2]
         d = k.shape[-1]
         dcg, dvc, dk, dv, uhat, dkg = fm.mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, h,
@@ -213,8 +213,10 @@ class TorchOps:
         dk_acc += dk
         dv_acc += dv
         dglx_acc += dcg[..., 2 * d:]
-        dkgain_acc += dkg
+        dkg_out.copy_(dkg)
+        blk = dcg_out[..., d:2 * d].clone()
         dcg_out.copy_(dcg)
+        dcg_out[..., d:2 * d].copy_(blk)                 # leave the v_m block to mrk_vin_bwd
         uhat_out.copy_(uhat)
         dvc_out.copy_(dvc)
 
@@ -231,8 +233,14 @@ class TorchOps:
         dcg_out.copy_(dcg)
         uhat_out.copy_(uhat)
 
-    def rmsn_bwd(self, du, o, ssq, residual=None, out_dtype=torch.float32):
-        """d o of the gain-free row normalisation (+ residual), in out_dtype."""
+    def col_dot_acc(self, out, a, b):
+        """out (fp32 [n]) += column sums of a * b, both [rows, n]."""
+        out.add_((a.reshape(-1, a.shape[-1]).float() * b.reshape(-1, b.shape[-1]).float()).sum(0))
+
+    def rmsn_bwd(self, du, o, ssq, residual=None, out_dtype=torch.float32, extra=None):
+        """d o of the gain-free row normalisation (+ residual), in out_dtype.  `extra`: fp32 term added to du."""
+        if extra is not None:
+            du = du.float() + extra
         dx = fm.rmsn_bwd(du, o, ssq)
         if residual is not None:
             dx = dx + residual.float()

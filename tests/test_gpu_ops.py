@@ -283,3 +283,50 @@ def test_cell_finish(ops, dh):
     close(cv, cr, rtol=1e-4, atol=1e-4, what="corr")
     for x, y, n_ in zip(a, b_, ("doc", "corr_all", "lsec", "dks", "dv")):
         close(x, y, rtol=1e-2, atol=1e-4, what=n_)
+
+
+@pytest.mark.parametrize("dh,pin,tau", [(64, 64, 0.8), (128, 0, 0.0), (64, 0, 50.0)])
+def test_mult_res_write_law_kernels(ops, dh, pin, tau):
+    """The four pointwise kernels of the mult_res family against their fp32 torch statement."""
+    B, c, H = 2, 64, 4
+    d = H * dh
+    T = 128
+    r = slice(32, 32 + c)
+    raw, o, vc = rnd(B, c, 4 * d, seed=1), rnd(B, c, d, seed=2), rnd(B, c, d, seed=3)
+    ssq = o.float().view(B, c, H, dh).pow(2).sum(-1)
+    glx, k, v, vgx = rnd(B, T, 2 * d, seed=4), rnd(B, T, d, seed=5), rnd(B, T, d, seed=6), rnd(B, T, d, seed=7)
+    w_ctx, k_gain = rnd(d, seed=8) * 0.1 + 1, (torch.rand(H, device=DEV) + 0.5)
+    cos, sin = build_rope_cache(T, dh, 10000.0, device=DEV)
+    lam = 0.7
+    f = lambda t: t.float()
+    vin = ops.mrk_vin_fwd(raw, ssq, o, w_ctx, vgx[:, r], lam)
+    vin_r = REF.mrk_vin_fwd(f(raw), ssq, f(o), f(w_ctx), f(vgx[:, r]), lam)
+    close(vin, vin_r, what="v_in")
+    K1, V1 = ops.mrk_refine_fwd(raw, vc, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], H, pin, k_gain, tau)
+    K2, V2 = REF.mrk_refine_fwd(f(raw), f(vc), ssq, f(glx[:, r]), f(k[:, r]), f(v[:, r]), cos[r], sin[r], H, pin, k_gain, tau)
+    close(K1, K2, what="K")
+    close(V1, V2, what="V")
+    dK, dV = rnd(B, c, H, dh, dtype=torch.float32, seed=9), rnd(B, c, H, dh, dtype=torch.float32, seed=10)
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, device=DEV, dtype=dt)
+
+    def run(o_, fl, dt):
+        acc = [z(B, T, d), z(B, T, d), z(B, T, 2 * d)]
+        dcg, uh, dvc, dkg = z(B, c, 4 * d, dt=dt), z(B, c, d, dt=dt), z(B, c, d, dt=dt), z(B, c, H)
+        o_.mrk_refine_bwd(dK, dV, fl(raw), fl(vc), ssq, fl(o), fl(glx[:, r]), fl(k[:, r]), fl(v[:, r]), cos[r], sin[r], pin,
+                          k_gain, tau, acc[0][:, r], acc[1][:, r], acc[2][:, r], dcg, uh, dvc, dkg)
+        dvin = fl(rnd(B, c, d, seed=11))
+        dvgx = z(B, T, d)
+        duh = o_.mrk_vin_bwd(dvin, fl(raw), ssq, fl(o), fl(w_ctx), fl(vgx[:, r]), lam, dcg, dvgx[:, r])
+        return acc + [dcg, uh, dvc, dkg, dvgx, duh]
+    got = run(ops, lambda t: t, torch.bfloat16)
+    ref = run(REF, f, torch.float32)
+    for a, b_, n_ in zip(got, ref, ("dk", "dv", "dglx", "dcg", "uhat", "dvc", "dkg", "dvgx", "du_hat")):
+        close(a, b_, rtol=3e-2, atol=3e-2, what=n_)
+    # column dot and the norm backward with the extra term
+    a_, b2 = rnd(4096, d, seed=12), rnd(4096, d, seed=13)
+    out1, out2 = z(d), z(d)
+    ops.col_dot_acc(out1, a_, b2)
+    REF.col_dot_acc(out2, a_, b2)
+    close(out1, out2, rtol=1e-2, atol=1e-1, what="col_dot")
+    du, extra = rnd(B, c, d, seed=14), rnd(B, c, d, dtype=torch.float32, seed=15)
+    close(ops.rmsn_bwd(du, o, ssq, extra=extra), REF.rmsn_bwd(f(du), f(o), ssq, extra=extra), what="rmsn extra")
