@@ -80,6 +80,8 @@ def parse_args(argv=None):
     a("--gn_hard", type=float, default=0.0)
     a("--rank_outlier_factor", type=float, default=0.0)
     a("--rank_outlier_max", type=int, default=1)
+    a("--curv_every", type=int, default=0, help="> 0: log curv/ctx_top_eig (Hessian power iteration, eager scan on a short slice) and gradnorm/L%%02d every this many steps")
+    a("--curv_len", type=int, default=256, help="tokens of the first micro-batch rows used for the curvature probe")
     a("--peer_watch_s", type=float, default=0.0, help="> 0: host-side peer check before every step, with this timeout")
     a("--lr_gov", action="store_true")
     a("--auto_rewind", action="store_true")
@@ -276,6 +278,14 @@ def run(args):
             rec["val/loss"], rec["val/base_K"] = validate(base_sid), rung_of(base_sid)[1]
             rec["val/loss_deep"] = validate(n_sid - 1)
             rec["val/base_minus_deep"] = rec["val/loss"] - rec["val/loss_deep"]
+        if args.curv_every and step % args.curv_every == 0 and step > 0:
+            from .curvature import ctx_top_eig, layer_grad_norms
+            rec.update(layer_grad_norms(tr.model, tr.opt.grad_buffers()))
+            if master:
+                blk = next(make_stream(10 ** 9 + 77, args.seed))[:2, :args.curv_len + 1].to(dev)
+                mode, tr.model.cfg.attn_mode = tr.model.cfg.attn_mode, "sequential"
+                rec["curv/ctx_top_eig"] = ctx_top_eig(tr.model, blk[:, :-1], blk[:, 1:], n_iter=3)
+                tr.model.cfg.attn_mode = mode
         log.log(step, **rec)
         if master and (step % args.log_every == 0 or skipped):
             dt = time.time() - t_last
