@@ -71,24 +71,25 @@ def _intra_mask(c, window, device):
     return m
 
 
-def prefix_lo(pos0: int, window: int) -> int:
-    """First committed row any chunk row can read."""
-    return max(0, pos0 - window + 1) if window else 0
+def prefix_lo(pos0: int, window: int, qoff: int = 0) -> int:
+    """First committed row any chunk row can read.  `qoff`: the chunk's first query sits qoff rows after
+    the end of the key range (0 for a cell reading its own committed prefix)."""
+    return min(pos0, max(0, pos0 + qoff - window + 1)) if window else 0
 
 
 # ---- committed-prefix pass --------------------------------------------------------------
 
-def prefix_fwd(q_r, Kc, Vc, pos0, scale, window=0):
-    """q_r [B,c,h,dh]; Kc/Vc tape [B,T,h,dh].  Returns (o_c fp32 [B,c,h,dh],
-    lse_c fp32 [B,c,h]); an empty prefix gives (0, NEG)."""
+def prefix_fwd(q_r, Kc, Vc, pos0, scale, window=0, qoff=0):
+    """q_r [B,c,h,dh]; Kc/Vc tape [B,T,h,dh]; keys are the rows [lo, pos0), query row t sits at absolute
+    position pos0 + qoff + t.  Returns (o_c fp32 [B,c,h,dh], lse_c fp32 [B,c,h]); an empty prefix gives (0, NEG)."""
     B, c, h, dh = q_r.shape
-    lo = prefix_lo(pos0, window)
+    lo = prefix_lo(pos0, window, qoff)
     if pos0 - lo <= 0:
         return (torch.zeros(B, c, h, dh, dtype=torch.float32, device=q_r.device),
                 torch.full((B, c, h), NEG, dtype=torch.float32, device=q_r.device))
     K, V = Kc[:, lo:pos0], Vc[:, lo:pos0]
     s = torch.einsum("bchd,bjhd->bhcj", q_r, K).float() * scale
-    m = _prefix_mask(c, lo, pos0, pos0, window, q_r.device)
+    m = _prefix_mask(c, lo, pos0, pos0 + qoff, window, q_r.device)
     if m is not None:
         s = s.masked_fill(~m, NEG)
     lse = torch.logsumexp(s, dim=-1)                                   # [B,h,c]
@@ -99,16 +100,16 @@ def prefix_fwd(q_r, Kc, Vc, pos0, scale, window=0):
     return o, lse.permute(0, 2, 1).contiguous()
 
 
-def prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
+def prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff=0):
     """Query side of the prefix backward for one cell: dq_acc [B,c,h,dh] fp32 += dS K over the
     committed rows.  do_c [B,c,h,dh] (any float dtype), corr [B,c,h] fp32 = do_c.o_c - dlse_c."""
     B, c, h, dh = q_r.shape
-    lo = prefix_lo(pos0, window)
+    lo = prefix_lo(pos0, window, qoff)
     if pos0 - lo <= 0:
         return
     K, V = Kc[:, lo:pos0], Vc[:, lo:pos0]
     s = torch.einsum("bchd,bjhd->bhcj", q_r, K).float() * scale
-    m = _prefix_mask(c, lo, pos0, pos0, window, q_r.device)
+    m = _prefix_mask(c, lo, pos0, pos0 + qoff, window, q_r.device)
     if m is not None:
         s = s.masked_fill(~m, NEG)
     p = torch.exp(s - lse_c.permute(0, 2, 1).unsqueeze(-1))

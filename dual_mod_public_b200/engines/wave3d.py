@@ -39,7 +39,7 @@ version is reached; far reads are back-propagated owner-computes once per chunk 
 far readers), near reads by a gather per (step, key chunk).  No atomics; every accumulation has one owner.
 
 `wavefront_layer_reference` is the same operator in plain autograd torch through `refine_kv`
-(any configuration); it is the oracle of the fused path and the generic backend.
+(any configuration, sliding window included); it is the oracle of the fused path and the generic backend.
 
 Reference parity: engines/wave3d/wave3d.py:213-543 (operator, schedule `n_steps = n - 1 + L*K` per
 pipeline = `n + K - 1` per layer), wave3d_x.py:738-1471 (production engine: write-once caches, (o, lse)
@@ -64,8 +64,7 @@ def wavefront_layer_reference(attn, xhat, cos, sin, C, K):
     B, T, _ = xhat.shape
     assert T % C == 0, "sequence length must be a whole number of chunks"
     n, W = T // C, attn.cfg.local_window or 0
-    assert W == 0 or W >= T, "the wavefront statement covers full attention"
-    mask = intra_mask(C, xhat.device, 0)
+    mask = intra_mask(C, xhat.device, W)
     q_r = apply_rope(attn._split(attn.wq(xhat)), cos, sin)
     k_flat, v_flat = attn.wk(xhat), attn.project_v(xhat)
     ks_r, v_raw = apply_rope(attn._split(k_flat), cos, sin), attn._split(v_flat)
@@ -80,7 +79,7 @@ def wavefront_layer_reference(attn, xhat, cos, sin, C, K):
             r = rows[i]
             Kp = torch.cat(Kv[:i], dim=2) if i else None
             Vp = torch.cat(Vv[:i], dim=2) if i else None
-            pre = PrefixRead(q_r[:, :, r], Kp, Vp, attn.scale, 0)
+            pre = PrefixRead(q_r[:, :, r], Kp, Vp, attn.scale, W)
             o = merged_read(q_r[:, :, r], ks_r[:, :, r], v_raw[:, :, r], Kv[i], Vv[i], pre, mask, attn.scale)
             o_cat = attn._merge(o)
             kpp, vpp = attn.refine_kv(xhat[:, r], o_cat, k_flat[:, r], v_flat[:, r])
@@ -117,8 +116,6 @@ class Wave3DEngine(WaveScanEngine):
     def __init__(self, model, ladder, B, T, C=64, **kw):
         ladder = [int(k) for k in (ladder if isinstance(ladder, (list, tuple)) else [ladder])]
         assert T % C == 0, "sequence length must be a whole number of chunks"
-        assert (model.cfg.local_window or 0) in (0,) or model.cfg.local_window >= T, \
-            "sliding-window attention is not covered by the wavefront engine"
         kw.setdefault("keep_sweeps", 0)
         # sweeps may exceed the chunk length here (in-flight predecessors deepen the dependency chain)
         super().__init__(model, [[(p, C, k) for p in range(0, T, C)] for k in ladder], B, T, **kw)
@@ -208,7 +205,8 @@ class Wave3DEngine(WaveScanEngine):
         G, w = hi - lo + 1, slice(lo * C, (hi + 1) * C)
         if s < n:
             r = slice(s * C, (s + 1) * C)
-            o_f, lse_f = ops.prefix_fwd(S.q_r[:, r], S.Kc, S.Vc, max(0, s - K + 1) * C, S.scale, 0)
+            fe = max(0, s - K + 1) * C
+            o_f, lse_f = ops.prefix_fwd(S.q_r[:, r], S.Kc, S.Vc, fe, S.scale, self.window, qoff=s * C - fe)
             self.ofar_all[:, r] = o_f
             self.lsefar_all[:, r] = lse_f
             S.Kc[:, r] = S.kself_r[:, r]
@@ -218,9 +216,9 @@ class Wave3DEngine(WaveScanEngine):
             win[0][s][:, :G * C] = K_in
             win[1][s][:, :G * C] = V_in
         qw = S.q_r[:, w]
-        o_n, lse_n = ops.win_near_fwd(qw, S.Kc, S.Vc, lo * C, (lo - K + 1) * C, C, S.scale)
+        o_n, lse_n = ops.win_near_fwd(qw, S.Kc, S.Vc, lo * C, (lo - K + 1) * C, C, S.scale, self.window)
         o_c, lse_c, w_f, w_n = ops.merge_partials(self.ofar_all[:, w], self.lsefar_all[:, w], o_n, lse_n)
-        o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale)
+        o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale, self.window)
         # every window chunk's new rows replace the old ones (all reads of this step are done)
         _, _, raw = self._refine_fwd(S, w, o, ssq, out=(S.Kc[:, w], S.Vc[:, w]))
         if s - K + 1 >= 0 and getattr(S, "o_all", None) is not None:
@@ -259,7 +257,7 @@ class Wave3DEngine(WaveScanEngine):
             far_grad = None
             if j >= 0 and (j + K) * C < self.T:
                 far_grad = ops.prefix_dkv(S.q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
-                                          j * C, C, (j + K) * C, scale, 0)
+                                          j * C, C, (j + K) * C, scale, self.window)
             Kc[:, w] = win[0][s][:, :G * C]                     # the tape as step s read it
             Vc[:, w] = win[1][s][:, :G * C]
             o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n = save.pop(s)
@@ -276,7 +274,7 @@ class Wave3DEngine(WaveScanEngine):
             dq_w = torch.zeros(B, G * C, h, dh, dtype=f32, device=dev)
             dK_in, dV_in = ops.win_tail_bwd(d_o, S.q_r[:, w], S.kself_r[:, w], S.v4[:, w], Kc[:, w], Vc[:, w],
                                             o_c, lse_c, o, lse, C, scale, dq_w, S.dks_r[:, w], S.dv4[:, w],
-                                            do_c, dlse_c)
+                                            do_c, dlse_c, self.window)
             self.dKp[:, w] = dK_in                              # gradient of what step s read = rows of step s-1
             self.dVp[:, w] = dV_in
             if s < n:                                           # chunk s entered here: it read its raw rows
@@ -290,7 +288,7 @@ class Wave3DEngine(WaveScanEngine):
                                self.DLf_all[:, w], self.docn_all[:, w], self.corrn_all[:, w], self.lsen_all[:, w])
             corr_n = self.corrn_all[:, w].contiguous()
             ops.win_near_dq(S.q_r[:, w], Kc, Vc, lo * C, (lo - K + 1) * C, C, scale, lse_n.contiguous(),
-                            self.docn_all[:, w], corr_n, dq_w)
+                            self.docn_all[:, w], corr_n, dq_w, self.window)
             S.dq_r[:, w] += dq_w
             if s < n:                                           # every sweep of chunk s has been processed
                 r, fe = rows(s), max(0, s - K + 1) * C
@@ -299,15 +297,15 @@ class Wave3DEngine(WaveScanEngine):
                 self.corr_all[:, r] = corr_f
                 self.lsec_all[:, r] = self.lsefar_all[:, r]
                 dq_s = torch.zeros(B, C, h, dh, dtype=f32, device=dev)
-                ops.prefix_dq(S.q_r[:, r], Kc, Vc, fe, scale, 0, self.lsefar_all[:, r].contiguous(),
-                              self.doc_all[:, r], corr_f, dq_s)
+                ops.prefix_dq(S.q_r[:, r], Kc, Vc, fe, scale, self.window, self.lsefar_all[:, r].contiguous(),
+                              self.doc_all[:, r], corr_f, dq_s, qoff=s * C - fe)
                 S.dq_r[:, r] += dq_s
             # near reads of this step, key side: chunk jk was read by the window chunks in (jk, jk+K-1]
             j0 = max(0, lo - K + 1)
             if hi > j0:
                 wk = slice(j0 * C, hi * C)
                 dK, dV = ops.win_near_dkv(S.q_r, self.docn_all, self.corrn_all, self.lsen_all, Kc, Vc, j0, hi - j0, C,
-                                          lo * C, (hi + 1) * C, K * C, scale)
+                                          lo * C, (hi + 1) * C, K * C, scale, self.window)
                 self.dKp[:, wk] += dK
                 self.dVp[:, wk] += dV
             self.stats["bwd_cells"] += G

@@ -364,7 +364,7 @@ template <int DH, int C>
 __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_fwd_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc,
     TView vc, float* __restrict__ o_c, float* __restrict__ lse_c, int H, int lo, int pos0,
-    float scale, int window, int grow) {
+    float scale, int window, int grow, int qoff) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = KT / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
@@ -376,6 +376,10 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_fwd_kernel(
   q += (long long)blockIdx.z * grow * vq.rs;
   pos0 += blockIdx.z * grow;
   lo = max(0, lo + (int)blockIdx.z * grow);
+  // query row t sits at absolute position pos0 + qoff + t (qoff > 0: the key range ends before the chunk);
+  // with a sliding window no row can see a key before qpos - window + 1
+  const int qpos = pos0 + qoff;
+  if (window) lo = min(pos0, max(lo, qpos - window + 1));
   const int g = lane >> 2, t = lane & 3;
   const long long hoff = (long long)h * DH;
   const bf16* Kb = Kc + b * vc.bs + hoff;
@@ -434,10 +438,10 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_fwd_kernel(
     for (int n = 0; n < NB; ++n) {
       int jl = n * 8 + 2 * t, j = kbase + jl;
       bool in0 = jl < rows, in1 = jl + 1 < rows;
-      bool a0 = in0 && (window == 0 || j > pos0 + i0 - window);
-      bool a1 = in1 && (window == 0 || j + 1 > pos0 + i0 - window);
-      bool a2 = in0 && (window == 0 || j > pos0 + i1 - window);
-      bool a3 = in1 && (window == 0 || j + 1 > pos0 + i1 - window);
+      bool a0 = in0 && (window == 0 || j > qpos + i0 - window);
+      bool a1 = in1 && (window == 0 || j + 1 > qpos + i0 - window);
+      bool a2 = in0 && (window == 0 || j > qpos + i1 - window);
+      bool a3 = in1 && (window == 0 || j + 1 > qpos + i1 - window);
       S[n][0] = a0 ? S[n][0] * scale : -INFINITY;
       S[n][1] = a1 ? S[n][1] * scale : -INFINITY;
       S[n][2] = a2 ? S[n][2] * scale : -INFINITY;
@@ -542,13 +546,13 @@ int dmb_tail_bwd(const float* dO, const void* q, TView vq, const void* ks, TView
 
 int dmb_prefix_fwd(const void* q, TView vq, const void* Kc, const void* Vc, TView vc, float* o_c,
                    float* lse_c, int B, int c, int H, int dh, int lo, int pos0, float scale,
-                   int window, int G, int grow, cudaStream_t st) {
+                   int window, int G, int grow, int qoff, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)C + 4 * KT) * Tile<DH>::PITCH * sizeof(bf16);
     auto kern = prefix_fwd_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)Kc, (const bf16*)Vc, vc, o_c,
-                                         lse_c, H, lo, pos0, scale, window, grow);
+                                         lse_c, H, lo, pos0, scale, window, grow, qoff);
   })
   DMB_CHECK_LAUNCH();
   return 0;

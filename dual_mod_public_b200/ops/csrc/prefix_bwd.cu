@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ do_c, TView vdo,
     const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc, const float* __restrict__ lse_c,
     const float* __restrict__ corr, float* __restrict__ dq_acc, int H, int lo, int pos0, float scale,
-    int window, int grow) {
+    int window, int grow, int qoff) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = KT / 8;
   constexpr int ST = 2;            // key / value tiles are double-buffered
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -189,6 +189,8 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
   do_c += (long long)blockIdx.z * grow * vdo.rs;
   pos0 += blockIdx.z * grow;
   lo = max(0, lo + (int)blockIdx.z * grow);
+  const int qpos = pos0 + qoff;            // absolute position of query row 0
+  if (window) lo = min(pos0, max(lo, qpos - window + 1));
   const long long hoff = (long long)h * DH;
   const bf16* Kb = Kc + b * vc.bs + hoff;
   const bf16* Vb = Vc + b * vc.bs + hoff;
@@ -255,10 +257,10 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
     for (int n = 0; n < NB; ++n) {
       const int jl = n * 8 + 2 * t4, j = kbase + jl;
       const bool in0 = jl < rows, in1 = jl + 1 < rows;
-      const bool a0 = in0 && (window == 0 || j > pos0 + i0 - window);
-      const bool a1 = in1 && (window == 0 || j + 1 > pos0 + i0 - window);
-      const bool a2 = in0 && (window == 0 || j > pos0 + i1 - window);
-      const bool a3 = in1 && (window == 0 || j + 1 > pos0 + i1 - window);
+      const bool a0 = in0 && (window == 0 || j > qpos + i0 - window);
+      const bool a1 = in1 && (window == 0 || j + 1 > qpos + i0 - window);
+      const bool a2 = in0 && (window == 0 || j > qpos + i1 - window);
+      const bool a3 = in1 && (window == 0 || j + 1 > qpos + i1 - window);
       dP[n][0] = a0 ? __expf(S[n][0] * scale - L0) * (dP[n][0] - c0) * scale : 0.f;
       dP[n][1] = a1 ? __expf(S[n][1] * scale - L0) * (dP[n][1] - c0) * scale : 0.f;
       dP[n][2] = a2 ? __expf(S[n][2] * scale - L1) * (dP[n][2] - c1) * scale : 0.f;
@@ -318,13 +320,13 @@ int dmb_prefix_dkv(const void* q_all, const void* doc_all, const float* corr_all
 
 int dmb_prefix_dq(const void* q, TView vq, const void* do_c, TView vdo, const void* Kc, const void* Vc, TView vc,
                   const float* lse_c, const float* corr, float* dq_acc, int B, int c, int H, int dh, int lo,
-                  int pos0, float scale, int window, int G, int grow, cudaStream_t st) {
+                  int pos0, float scale, int window, int G, int grow, int qoff, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)2 * C + 4 * KT) * Tile<DH>::PITCH * sizeof(bf16);
     auto kern = prefix_dq_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)do_c, vdo, (const bf16*)Kc,
-                                         (const bf16*)Vc, vc, lse_c, corr, dq_acc, H, lo, pos0, scale, window, grow);
+                                         (const bf16*)Vc, vc, lse_c, corr, dq_acc, H, lo, pos0, scale, window, grow, qoff);
   })
   DMB_CHECK_LAUNCH();
   return 0;

@@ -65,12 +65,12 @@ class _Sigs:
     dmb_tail_fwd = [_p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p]
     dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _v, _p, _v,
                     _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p]
-    dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p]
+    dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_cell_finish = [_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
-    dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p]
+    dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
 
 
 BF16 = torch.bfloat16
@@ -342,12 +342,12 @@ class CudaOps(TorchOps):
         B, c, h, dh = q_r.shape
         return q_r.dtype == BF16 and dh in (64, 128) and c in (16, 32, 64)
 
-    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0, out=None):
+    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0, out=None, qoff=0):
         from ..engines.fused_math import prefix_lo
         B, c, h, dh = q_r.shape
-        lo = prefix_lo(pos0, window)
+        lo = prefix_lo(pos0, window, qoff)
         if not self._cell_ok(q_r) or pos0 - lo <= 0 or not (_dense_tail(q_r, 2) and _dense_tail(Kc, 2)):
-            return super().prefix_fwd(q_r, Kc, Vc, pos0, scale, window, out)
+            return super().prefix_fwd(q_r, Kc, Vc, pos0, scale, window, out, qoff)
         if out is not None and out[0].is_contiguous() and out[1].is_contiguous() and out[0].dtype == F32:
             o_c, lse_c = out
         else:
@@ -355,27 +355,27 @@ class CudaOps(TorchOps):
             lse_c = torch.empty(B, c, h, dtype=F32, device=q_r.device)
         self._ck(self.lib.dmb_prefix_fwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          o_c.data_ptr(), lse_c.data_ptr(), B, c, h, dh, lo, pos0,
-                                         scale, window, 1, 0, self._st()), "prefix_fwd")
+                                         scale, window, 1, 0, qoff, self._st()), "prefix_fwd")
         if out is not None and o_c is not out[0]:
             out[0].copy_(o_c)
             out[1].copy_(lse_c)
             return out
         return o_c, lse_c
 
-    def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
+    def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff=0):
         from ..engines.fused_math import prefix_lo
         B, c, h, dh = q_r.shape
-        lo = prefix_lo(pos0, window)
+        lo = prefix_lo(pos0, window, qoff)
         if pos0 - lo <= 0:
             return
         ok = (self._cell_ok(q_r) and do_c.dtype == BF16 and dq_acc.is_contiguous() and _dense_tail(q_r, 2)
               and _dense_tail(do_c, 2) and _dense_tail(Kc, 2))
         if not ok:
-            return super().prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc)
+            return super().prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff)
         lse_c, corr = lse_c.contiguous(), corr.contiguous()
         self._ck(self.lib.dmb_prefix_dq(q_r.data_ptr(), _tv(q_r), do_c.data_ptr(), _tv(do_c), Kc.data_ptr(),
                                         Vc.data_ptr(), _tv(Kc), lse_c.data_ptr(), corr.data_ptr(),
-                                        dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, 1, 0, self._st()),
+                                        dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, 1, 0, qoff, self._st()),
                  "prefix_dq")
 
     def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
@@ -429,18 +429,18 @@ class CudaOps(TorchOps):
             dK_in.data_ptr(), dV_in.data_ptr(), B, c, h, dh, scale, window, 1, 0, self._st()), "tail_bwd")
         return dK_in, dV_in
 
-    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale):
+    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window=0):
         B, T, h, dh = q_all.shape
         ok = (q_all.dtype == BF16 and docn_all.dtype == BF16 and dh in (64, 128) and C in (16, 32, 64)
               and q_all.is_contiguous() and docn_all.is_contiguous() and corrn_all.is_contiguous()
               and lsen_all.is_contiguous() and _dense_tail(Kc, 2))
         if not ok:
-            return super().win_near_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale)
+            return super().win_near_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window)
         dK = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
         dV = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), docn_all.data_ptr(), corrn_all.data_ptr(),
                                          lsen_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), dK.data_ptr(),
-                                         dV.data_ptr(), B, T, C, h, dh, j0 * C, q_lo, min(q_hi, T), scale, 0,
+                                         dV.data_ptr(), B, T, C, h, dh, j0 * C, q_lo, min(q_hi, T), scale, window,
                                          G, C, span, self._st()), "win_near_dkv")
         return dK, dV
 
@@ -500,31 +500,31 @@ class CudaOps(TorchOps):
         return (q_win.dtype == BF16 and dh in (64, 128) and C in (16, 32, 64) and rows % C == 0
                 and all(_dense_tail(t, 2) for t in (q_win,) + views))
 
-    def win_near_fwd(self, q_win, Kc, Vc, pos0, lo, C, scale):
+    def win_near_fwd(self, q_win, Kc, Vc, pos0, lo, C, scale, window=0):
         if not self._win_ok(q_win, C, Kc):
-            return super().win_near_fwd(q_win, Kc, Vc, pos0, lo, C, scale)
+            return super().win_near_fwd(q_win, Kc, Vc, pos0, lo, C, scale, window)
         B, rows, h, dh = q_win.shape
         o_n = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
         lse_n = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
         self._ck(self.lib.dmb_prefix_fwd(q_win.data_ptr(), _tv(q_win), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
-                                         o_n.data_ptr(), lse_n.data_ptr(), B, C, h, dh, lo, pos0, scale, 0,
-                                         rows // C, C, self._st()), "win_near_fwd")
+                                         o_n.data_ptr(), lse_n.data_ptr(), B, C, h, dh, lo, pos0, scale, window,
+                                         rows // C, C, 0, self._st()), "win_near_fwd")
         return o_n, lse_n
 
-    def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc):
+    def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window=0):
         ok = (self._win_ok(q_win, C, Kc, do_n) and do_n.dtype == BF16 and dq_acc.is_contiguous()
               and lse_n.is_contiguous() and corr_n.is_contiguous())
         if not ok:
-            return super().win_near_dq(q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc)
+            return super().win_near_dq(q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window)
         B, rows, h, dh = q_win.shape
         self._ck(self.lib.dmb_prefix_dq(q_win.data_ptr(), _tv(q_win), do_n.data_ptr(), _tv(do_n), Kc.data_ptr(),
                                         Vc.data_ptr(), _tv(Kc), lse_n.data_ptr(), corr_n.data_ptr(),
-                                        dq_acc.data_ptr(), B, C, h, dh, lo, pos0, scale, 0, rows // C, C,
+                                        dq_acc.data_ptr(), B, C, h, dh, lo, pos0, scale, window, rows // C, C, 0,
                                         self._st()), "win_near_dq")
 
-    def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale):
+    def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale, window=0):
         if not self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in) or not (o_c.is_contiguous() and lse_c.is_contiguous()):
-            return super().win_tail_fwd(q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale)
+            return super().win_tail_fwd(q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale, window)
         B, rows, h, dh = q_win.shape
         o = torch.empty(B, rows, h, dh, dtype=BF16, device=q_win.device)
         lse = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
@@ -532,17 +532,17 @@ class CudaOps(TorchOps):
         self._ck(self.lib.dmb_tail_fwd(q_win.data_ptr(), _tv(q_win), ks_win.data_ptr(), _tv(ks_win),
                                        vr_win.data_ptr(), _tv(vr_win), K_in.data_ptr(), _tv(K_in),
                                        V_in.data_ptr(), _tv(V_in), o_c.data_ptr(), lse_c.data_ptr(),
-                                       o.data_ptr(), lse.data_ptr(), ssq.data_ptr(), B, C, h, dh, scale, 0,
+                                       o.data_ptr(), lse.data_ptr(), ssq.data_ptr(), B, C, h, dh, scale, window,
                                        rows // C, C, self._st()), "win_tail_fwd")
         return o, lse, ssq
 
     def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0):
         ok = (self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in, dks_acc, dv_acc) and dO.dtype == F32
               and all(t.is_contiguous() for t in (dO, o, o_c, lse_c, lse, dq_acc, doc_acc, dlsec_acc)))
         if not ok:
             return super().win_tail_bwd(dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                                        dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc)
+                                        dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window)
         B, rows, h, dh = q_win.shape
         dK_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
         dV_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
@@ -551,7 +551,7 @@ class CudaOps(TorchOps):
             _tv(vr_win), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), o_c.data_ptr(),
             lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), dks_acc.data_ptr(),
             _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc), doc_acc.data_ptr(), dlsec_acc.data_ptr(),
-            dK_in.data_ptr(), dV_in.data_ptr(), B, C, h, dh, scale, 0, rows // C, C, self._st()), "win_tail_bwd")
+            dK_in.data_ptr(), dV_in.data_ptr(), B, C, h, dh, scale, window, rows // C, C, self._st()), "win_tail_bwd")
         return dK_in, dV_in
 
     def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):

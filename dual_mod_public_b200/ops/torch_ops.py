@@ -63,17 +63,18 @@ class TorchOps:
         return fm.swiglu_bwd(dg, h1, h3)
 
     # ---- cell ops -------------------------------------------------------------------
-    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0, out=None):
-        """`out`: optional (o_c, lse_c) fp32 tensors to write into (and return)."""
-        o_c, lse_c = fm.prefix_fwd(q_r, Kc, Vc, pos0, scale, window)
+    def prefix_fwd(self, q_r, Kc, Vc, pos0, scale, window=0, out=None, qoff=0):
+        """`out`: optional (o_c, lse_c) fp32 tensors to write into (and return).  `qoff`: rows between the end
+        of the key range and the first query (0 for a cell reading its own committed prefix)."""
+        o_c, lse_c = fm.prefix_fwd(q_r, Kc, Vc, pos0, scale, window, qoff)
         if out is None:
             return o_c, lse_c
         out[0].copy_(o_c)
         out[1].copy_(lse_c)
         return out
 
-    def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc):
-        return fm.prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc)
+    def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff=0):
+        fm.prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff)
 
     def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
         return fm.prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end)
@@ -81,47 +82,47 @@ class TorchOps:
     # ---- window ops: G consecutive chunks of C rows of the same sequences (statement: a loop over the
     # chunks; the kernel table does each in one launch).  Window tensors are [B, G*C, ...]; group z reads
     # the tape rows [max(0, lo + z*C), pos0 + z*C).
-    def win_near_fwd(self, q_win, Kc, Vc, pos0, lo, C, scale):
+    def win_near_fwd(self, q_win, Kc, Vc, pos0, lo, C, scale, window=0):
         outs = []
         for z in range(q_win.shape[1] // C):
             l, p = max(0, lo + z * C), pos0 + z * C
-            outs.append(fm.prefix_fwd(q_win[:, z * C:(z + 1) * C], Kc[:, l:], Vc[:, l:], p - l, scale, 0))
+            outs.append(fm.prefix_fwd(q_win[:, z * C:(z + 1) * C], Kc[:, l:], Vc[:, l:], p - l, scale, window))
         return torch.cat([o for o, _ in outs], 1), torch.cat([l for _, l in outs], 1)
 
-    def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc):
+    def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window=0):
         for z in range(q_win.shape[1] // C):
             l, p, r = max(0, lo + z * C), pos0 + z * C, slice(z * C, (z + 1) * C)
-            fm.prefix_dq(q_win[:, r], Kc[:, l:], Vc[:, l:], p - l, scale, 0, lse_n[:, r], do_n[:, r], corr_n[:, r],
+            fm.prefix_dq(q_win[:, r], Kc[:, l:], Vc[:, l:], p - l, scale, window, lse_n[:, r], do_n[:, r], corr_n[:, r],
                          dq_acc[:, r])
 
-    def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale):
+    def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale, window=0):
         outs = []
         for z in range(q_win.shape[1] // C):
             r = slice(z * C, (z + 1) * C)
             outs.append(fm.tail_fwd(q_win[:, r], ks_win[:, r], vr_win[:, r], K_in[:, r], V_in[:, r], o_c[:, r],
-                                    lse_c[:, r], scale, 0))
+                                    lse_c[:, r], scale, window))
         return tuple(torch.cat([t[i] for t in outs], 1) for i in range(3))
 
     def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0):
         dKs, dVs = [], []
         for z in range(q_win.shape[1] // C):
             r = slice(z * C, (z + 1) * C)
             dk, dv = self.tail_bwd(dO[:, r], q_win[:, r], ks_win[:, r], vr_win[:, r], K_in[:, r], V_in[:, r],
-                                   o_c[:, r], lse_c[:, r], o[:, r], lse[:, r], scale, 0, dq_acc[:, r],
+                                   o_c[:, r], lse_c[:, r], o[:, r], lse[:, r], scale, window, dq_acc[:, r],
                                    dks_acc[:, r], dv_acc[:, r], doc_acc[:, r], dlsec_acc[:, r])
             dKs.append(dk)
             dVs.append(dv)
         return torch.cat(dKs, 1), torch.cat(dVs, 1)
 
-    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale):
+    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window=0):
         """Key side of the near reads of one step for the G key chunks j0 .. j0+G-1: chunk j is read by the
         query rows [max(q_lo, (j+1)C), min(q_hi, jC + span)).  Returns dense (dK, dV) [B, G*C, h, dh]."""
         outs = []
         for z in range(G):
             p0 = (j0 + z) * C
-            outs.append(self.prefix_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, p0, C, max(q_lo, p0 + C), scale, 0,
-                                        q_end=min(q_hi, p0 + span)))
+            outs.append(self.prefix_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, p0, C, max(q_lo, p0 + C), scale,
+                                        window, q_end=min(q_hi, p0 + span)))
         return torch.cat([a for a, _ in outs], 1), torch.cat([b for _, b in outs], 1)
 
     def cell_finish(self, do_c, dlse_c, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv):

@@ -17,6 +17,7 @@ from dual_mod_public_b200.parallel.fused_optim import FusedDPAdamW, decay_groups
 from helpers import perturb
 
 DEV = "cuda:0"
+MRK = dict(ctx_mod="mult_res", gate_rank=16, ctx_rank=16, k_ctx_norm="rms", kmod_vraw_heads=1, v_clamp_tau=2.0)
 
 
 def build(d=256, heads=4, L=2, T=256, **kw):
@@ -39,9 +40,6 @@ def grads_of(eng, model, idx, tgt):
     eng.pack()
     loss = eng.train_step(idx, tgt).clone()
     return loss, {n: eng.grads.get(p).clone() for n, p in model.named_parameters()}
-
-
-MRK = dict(ctx_mod="mult_res", gate_rank=16, ctx_rank=16, k_ctx_norm="rms", kmod_vraw_heads=1, v_clamp_tau=2.0)
 
 
 @pytest.mark.parametrize("kw,c,K", [(dict(), 64, 4), (dict(kmod_vraw_heads=1), 32, 32), (dict(local_window=100), 64, 2),
@@ -67,10 +65,10 @@ def test_kernel_engine_matches_fp32_torch_engine(kw, c, K):
     assert e_k.debug_scan() == []
 
 
-@pytest.mark.parametrize("dh,K", [(64, 3), (128, 2)])
-def test_wavefront_kernel_engine_matches_fp32_torch_engine(dh, K):
+@pytest.mark.parametrize("dh,K,kw", [(64, 3, dict()), (128, 2, dict()), (64, 3, dict(local_window=100)), (64, 2, MRK)])
+def test_wavefront_kernel_engine_matches_fp32_torch_engine(dh, K, kw):
     from dual_mod_public_b200.engines.wave3d import Wave3DEngine
-    cfg, m = build(d=256, heads=256 // dh)
+    cfg, m = build(d=256, heads=256 // dh, **kw)
     B, T = 4, 256
     idx, tgt = batch(cfg, B, T)
     e_k = Wave3DEngine(m, [K], B, T, C=64, autocast_bf16=True, backend="fused")

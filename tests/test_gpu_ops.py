@@ -330,3 +330,29 @@ def test_mult_res_write_law_kernels(ops, dh, pin, tau):
     close(out1, out2, rtol=1e-2, atol=1e-1, what="col_dot")
     du, extra = rnd(B, c, d, seed=14), rnd(B, c, d, dtype=torch.float32, seed=15)
     close(ops.rmsn_bwd(du, o, ssq, extra=extra), REF.rmsn_bwd(f(du), f(o), ssq, extra=extra), what="rmsn extra")
+
+
+@pytest.mark.parametrize("window", [0, 90])
+def test_prefix_read_with_a_gap_between_keys_and_queries(ops, window):
+    """Far read of the wavefront engine: keys end at pos0, the query chunk starts qoff rows later."""
+    B, H, dh, c, pos0, qoff = 2, 4, 64, 64, 128, 128
+    T = pos0 + qoff + c
+    scale = dh ** -0.5
+    q, ks, vr, Kc, Vc = _cell_inputs(B, c, H, dh, T)
+    qc = q[:, pos0 + qoff:pos0 + qoff + c]
+    f = lambda t: t.float()
+    o, lse = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, window, qoff=qoff)
+    o_r, lse_r = fm.prefix_fwd(f(qc), f(Kc), f(Vc), pos0, scale, window, qoff)
+    live = lse_r > -1e29
+    close(o, o_r, what="o")
+    if live.any():
+        close(lse[live], lse_r[live], rtol=1e-2, atol=2e-2, what="lse")
+    assert (lse[~live] < -1e29).all()
+    if window:                                   # rows further than the window from every key see nothing
+        assert (~live).any() and live.any()
+    do, corr = rnd(B, c, H, dh, seed=3), rnd(B, c, H, dtype=torch.float32, seed=4)
+    lse_use = torch.where(live, lse_r, torch.full_like(lse_r, 30.0))
+    dq, dq_r = torch.zeros(B, c, H, dh, device=DEV), torch.zeros(B, c, H, dh, device=DEV)
+    ops.prefix_dq(qc, Kc, Vc, pos0, scale, window, lse_use, do, corr, dq, qoff=qoff)
+    fm.prefix_dq(f(qc), f(Kc), f(Vc), pos0, scale, window, lse_use, f(do), corr, dq_r, qoff)
+    close(dq, dq_r, rtol=3e-2, atol=3e-2, what="dq")

@@ -32,7 +32,7 @@ def _engine(model, eng, idx, tgt, sid=0):
 
 
 @pytest.mark.parametrize("K,C,T", [(1, 4, 16), (2, 4, 24), (3, 4, 32), (4, 8, 32), (6, 4, 16)])
-@pytest.mark.parametrize("kw", [dict(), dict(kmod_vraw_heads=1),
+@pytest.mark.parametrize("kw", [dict(), dict(kmod_vraw_heads=1), dict(local_window=7), dict(local_window=13, kmod_vraw_heads=1),
                                 dict(ctx_mod="mult_res", gate_rank=8, ctx_rank=8, k_ctx_norm="rms", kmod_vraw_heads=1,
                                      v_clamp_tau=0.8)])
 def test_fused_wavefront_matches_autograd(K, C, T, kw):
@@ -46,6 +46,18 @@ def test_fused_wavefront_matches_autograd(K, C, T, kw):
         assert relerr(g[n], gr) < 1e-4, n
     l2, g2 = _engine(m, eng, idx, tgt)                              # buffers are reusable
     assert torch.equal(l, l2) and all(torch.equal(g[n], g2[n]) for n in g)
+
+
+def test_windowed_wavefront_reaches_the_windowed_scan():
+    """With a sliding window the operator still converges to the exact scan of the windowed model."""
+    cfg, m = build(local_window=6)
+    T, C = 16, 4
+    idx, tgt = _data(cfg, 2, T, 6)
+    m.cfg.attn_mode = "sequential"
+    with torch.no_grad():
+        ref, _ = m(idx)
+        got = wavefront_model_forward(m, idx, C, 13)
+    assert (got - ref).abs().max().item() < 1e-5
 
 
 def test_generic_backend_and_ladder():
