@@ -433,8 +433,8 @@ class WaveScanEngine:
         self.xl[0].copy_(F.embedding(self.idx, self.emb_c))
 
     def _fused_embed_bwd(self):
-        self.grads.get(self.model.tok_emb.weight).index_add_(
-            0, self.idx.view(-1), self.dx_cur.reshape(-1, self.cfg.d_model).float())
+        self.ops.embed_bwd(self.grads.get(self.model.tok_emb.weight), self.idx,
+                           self.dx_cur.reshape(-1, self.cfg.d_model))
 
     def _fused_layer_fwd(self, li, sid, keep=False):
         ops, cfg = self.ops, self.cfg

@@ -215,6 +215,36 @@ __global__ void ce_kernel(const bf16* __restrict__ logits, const long long* __re
   }
 }
 
+// ---- embedding backward, run-to-run deterministic ----------------------------------------------
+// tok_sorted: the batch's token ids in ascending order, order[p]: the flat position whose id is
+// tok_sorted[p] (a stable sort, so equal ids keep position order).  The block at the first slot of a
+// run of equal ids adds that run's rows of dx, in position order, into the id's row of the fp32
+// table gradient; every other block exits.  No atomics: each table row has exactly one writer and a
+// fixed summation order.  One thread per 4 columns.
+template <typename TD>
+__global__ void embed_bwd_sorted_kernel(const long long* __restrict__ tok_sorted,
+                                        const long long* __restrict__ order, const TD* __restrict__ dx,
+                                        float* __restrict__ gw, int n, int d) {
+  const int p = blockIdx.x;
+  const long long tok = tok_sorted[p];
+  if (p > 0 && tok_sorted[p - 1] == tok) return;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(gw + tok * d + c);
+    for (int q = p; q < n && tok_sorted[q] == tok; ++q) {
+      const TD* r = dx + order[q] * d + c;
+      if constexpr (sizeof(TD) == 2) {
+        uint2 u = *reinterpret_cast<const uint2*>(r);
+        float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+        acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+      } else {
+        float4 v = *reinterpret_cast<const float4*>(r);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    *reinterpret_cast<float4*>(gw + tok * d + c) = acc;
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -339,6 +369,19 @@ int dmb_swiglu_bwd(const void* dg, const void* h1, const void* h3, void* dh1, vo
 int dmb_ce(const void* logits, const long long* targets, const float* inv_n, float* row_loss,
            void* dlogits, int rows, int V, cudaStream_t st) {
   ce_kernel<<<rows, 512, 0, st>>>((const bf16*)logits, targets, inv_n, row_loss, (bf16*)dlogits, V);
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+// gw[tok] += sum of dx rows whose token id is tok, in position order (see the kernel's comment)
+int dmb_embed_bwd_sorted(const long long* tok_sorted, const long long* order, const void* dx, int dx_f32,
+                         float* gw, int n, int d, cudaStream_t st) {
+  if (d % 4 || n <= 0) return -1;
+  int threads = d / 4 < 256 ? ((d / 4 + 31) / 32) * 32 : 256;
+  if (dx_f32)
+    embed_bwd_sorted_kernel<float><<<n, threads, 0, st>>>(tok_sorted, order, (const float*)dx, gw, n, d);
+  else
+    embed_bwd_sorted_kernel<bf16><<<n, threads, 0, st>>>(tok_sorted, order, (const bf16*)dx, gw, n, d);
   DMB_CHECK_LAUNCH();
   return 0;
 }

@@ -49,6 +49,7 @@ class _Sigs:
     dmb_rms_fwd = [_p, _ll, _p, _p, _p, _i, _i, _f, _p]
     dmb_rms_bwd_dx = [_p, _i, _p, _ll, _p, _p, _p, _p, _i, _i, _i, _p]
     dmb_col_reduce_acc = [_p, _i, _p, _ll, _p, _p, _i, _p, _i, _i, _p]
+    dmb_embed_bwd_sorted = [_p, _p, _p, _i, _p, _i, _i, _p]
     dmb_rope = [_p, _i, _ll, _ll, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]
     dmb_refine_fwd = [_p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _f, _p]
     dmb_refine_bwd = [_p, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
@@ -190,6 +191,14 @@ class CudaOps(TorchOps):
                                              part.data_ptr(), nsplit, out.data_ptr(), rows, n,
                                              self._st()), "col_sum")
         self.launches += 1
+
+    def embed_bwd(self, gw, idx, dx):
+        d = dx.shape[-1]
+        if dx.dtype not in (BF16, F32) or not dx.is_contiguous() or not gw.is_contiguous() or d % 4:
+            return super().embed_bwd(gw, idx, dx)
+        tok, order = torch.sort(idx.reshape(-1), stable=True)
+        self._ck(self.lib.dmb_embed_bwd_sorted(tok.data_ptr(), order.data_ptr(), dx.data_ptr(), int(dx.dtype == F32),
+                                               gw.data_ptr(), tok.numel(), d, self._st()), "embed_bwd")
 
     def col_dot_acc(self, out, a, b):
         n = a.shape[-1]

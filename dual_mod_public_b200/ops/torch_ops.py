@@ -234,6 +234,10 @@ class TorchOps:
         dcg_out.copy_(dcg)
         uhat_out.copy_(uhat)
 
+    def embed_bwd(self, gw, idx, dx):
+        """gw (fp32 [V, d]) += scatter of dx rows [N, d] by token id idx [N]."""
+        gw.index_add_(0, idx.reshape(-1), dx.reshape(-1, dx.shape[-1]).float())
+
     def col_dot_acc(self, out, a, b):
         """out (fp32 [n]) += column sums of a * b, both [rows, n]."""
         out.add_((a.reshape(-1, a.shape[-1]).float() * b.reshape(-1, b.shape[-1]).float()).sum(0))

@@ -203,6 +203,24 @@ def test_col_sum(ops):
     close(out, 1 + x.sum(0), rtol=1e-4, atol=1e-3, what="colsum")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_embedding_backward_is_exact_and_repeatable(ops, dtype):
+    """Sorted-run scatter: fp32 sums of the rows per id, the same bits on every call."""
+    V, d, n = 97, 256, 5000
+    idx = torch.randint(0, V, (n,), device=DEV)
+    idx[:1500] = 3                                  # one long run
+    dx = rnd(n, d, dtype=dtype)
+    ref = torch.ones(V, d, device=DEV, dtype=torch.float64)
+    ref.index_add_(0, idx, dx.double())
+    outs = []
+    for _ in range(2):
+        gw = torch.ones(V, d, device=DEV)
+        ops.embed_bwd(gw, idx, dx)
+        outs.append(gw)
+    close(outs[0], ref.float(), rtol=1e-5, atol=1e-4, what="embed_bwd")
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("dh,C,G,lo_chunk,K", [(64, 64, 3, 2, 4), (128, 64, 2, 0, 4), (64, 32, 4, 5, 3)])
 def test_window_ops_match_per_chunk_statement(ops, dh, C, G, lo_chunk, K):
     """The group-dimension launches (G window chunks at once) against the per-chunk torch statement."""
@@ -335,7 +353,7 @@ def test_mult_res_write_law_kernels(ops, dh, pin, tau):
 @pytest.mark.parametrize("window", [0, 90])
 def test_prefix_read_with_a_gap_between_keys_and_queries(ops, window):
     """Far read of the wavefront engine: keys end at pos0, the query chunk starts qoff rows later."""
-    B, H, dh, c, pos0, qoff = 2, 4, 64, 64, 128, 128
+    B, H, dh, c, pos0, qoff = 2, 4, 64, 64, 128, 64
     T = pos0 + qoff + c
     scale = dh ** -0.5
     q, ks, vr, Kc, Vc = _cell_inputs(B, c, H, dh, T)
