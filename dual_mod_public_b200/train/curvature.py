@@ -72,3 +72,83 @@ def layer_grad_norms(model, grads):
         sq = sum(grads.get(p).float().pow(2).sum() for p in blk.parameters())
         out[f"gradnorm/L{li:02d}"] = float(torch.sqrt(sq))
     return out
+
+
+@torch.no_grad()
+def gate_stats_layerwise(model, x):
+    """Per-layer write-law telemetry on a fixed batch `x` (eager forward with collection hooks):
+    gates/g_{k,v}_Lxx (mean gate), gates/rf_* (share of tokens whose mean gate is below 0.5: mostly
+    context), gates/fraclt03_* (share of gate entries below 0.3), vtail/p999_Lxx and vtail/max (norm of
+    the written value per position and head: what `v_clamp_tau` governs), attnlogit/p999_Lxx (largest
+    read logit per position and head), kgain/* (learned key gain), and their all-layer summaries.
+    Key names follow lm/train_340m/train_flagship.py:211-294."""
+    was_training = model.training
+    model.eval()
+    collect = [dict() for _ in model.blocks]
+    model(x, collect=collect)
+    model.train(was_training)
+    out = {}
+    hd = model.blocks[0].attn.head_dim
+    mean = lambda v: float(sum(v) / len(v))
+
+    def quantile(t, q):                                   # torch.quantile caps its input size
+        t = t.flatten().float()
+        k = min(t.numel(), max(1, int(round(q * t.numel()))))
+        return float(t.kthvalue(k).values)
+
+    p999, vmax = [], []
+    for li, c in enumerate(collect):
+        if "vpp" not in c:
+            break
+        v = torch.cat([t if t.dim() == 3 else t.unsqueeze(1) for t in c["vpp"]], dim=1)
+        rn = v.reshape(v.shape[0], v.shape[1], -1, hd).norm(dim=-1)
+        p999.append(quantile(rn, 0.999))
+        vmax.append(float(rn.max()))
+        out[f"vtail/p999_L{li:02d}"] = p999[-1]
+    if p999:
+        out["vtail/p999_all_layers"], out["vtail/p999_max_layer"] = mean(p999), max(p999)
+        out["vtail/max_all_layers"] = max(vmax)
+    lp, lmax = [], []
+    for li, c in enumerate(collect):
+        if "attn_logit_max" not in c:
+            break
+        sm = torch.cat([t.flatten() for t in c["attn_logit_max"]])
+        lp.append(quantile(sm, 0.999))
+        lmax.append(float(sm.max()))
+        out[f"attnlogit/p999_L{li:02d}"] = lp[-1]
+    if lp:
+        out["attnlogit/p999_all_layers"], out["attnlogit/p999_max_layer"] = mean(lp), max(lp)
+        out["attnlogit/max_all_layers"] = max(lmax)
+    gains = [blk.attn.k_gain.detach().float().flatten() for blk in model.blocks
+             if getattr(blk.attn, "k_gain", None) is not None]
+    if gains:
+        allg = torch.cat(gains)
+        out.update({"kgain/mean_all_layers": float(allg.mean()), "kgain/max_all_layers": float(allg.max()),
+                    "kgain/min_all_layers": float(allg.min()),
+                    "kgain/std_all_layers": float(allg.std()) if allg.numel() > 1 else 0.0,
+                    "kgain/spread_all_layers": float(allg.max() / (allg.min() + 1e-6))})
+        for li, g in enumerate(gains):
+            out[f"kgain/mean_L{li:02d}"] = float(g.mean())
+    for tag in ("k", "v"):
+        gm, rf, lo, ratios, effs = [], [], [], [], []
+        for li, c in enumerate(collect):
+            if f"g_{tag}" not in c:
+                continue
+            g = torch.cat([t if t.dim() == 3 else t.unsqueeze(1) for t in c[f"g_{tag}"]], dim=1).float()
+            gbar = float(g.mean())
+            if f"ratio_{tag}" in c:
+                r = mean([float(t.float().mean()) if torch.is_tensor(t) else float(t) for t in c[f"ratio_{tag}"]])
+                ratios.append(r)
+                effs.append((1 - gbar) * r / (gbar + (1 - gbar) * r + 1e-8))
+            gm.append(gbar)
+            rf.append(float(((1 - g.mean(dim=-1)) > 0.5).float().mean()))
+            lo.append(float((g < 0.3).float().mean()))
+            out[f"gates/g_{tag}_L{li:02d}"], out[f"gates/rf_{tag}_L{li:02d}"] = gm[-1], rf[-1]
+            out[f"gates/fraclt03_{tag}_L{li:02d}"] = lo[-1]
+        if gm:
+            out[f"telemetry/g_{tag}_mean_all_layers"] = mean(gm)
+            out[f"telemetry/register_frac_{tag}_all_layers"] = mean(rf)
+            out[f"telemetry/fraclt03_{tag}_all_layers"] = mean(lo)
+        if ratios:
+            out[f"telemetry/ratio_{tag}_mean"], out[f"telemetry/eff_ctx_share_{tag}"] = mean(ratios), mean(effs)
+    return out

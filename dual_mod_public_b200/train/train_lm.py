@@ -73,6 +73,21 @@ def parse_args(argv=None):
     a("--min_lr", type=float, default=3e-5)
     a("--weight_decay", type=float, default=0.1)
     a("--decay_all", action="store_true")
+    a("--eps", type=float, default=1e-8)
+    a("--wd_doctrine", default="", choices=["", "split", "all", "branch"],
+      help="weight-decay layout: matrices only / every parameter / grown-branch parameters at 10x in a group of their own")
+    a("--protocol", default="", choices=["", "fs1", "pdn"],
+      help="pdn: batch 256, 30000 steps, lr 4e-4 -> 0.1 lr, warm-up 1024, decay on every parameter, skip only non-finite steps")
+    a("--dm_accum", type=int, default=1, help="> 1: the Dual-Mod parameters step every this many iterations on the mean gradient")
+    a("--dm_lr", type=float, default=None, help="learning rate of the Dual-Mod parameters (two-speed optimizer)")
+    a("--cooldown_steps", type=int, default=0, help="> 0: only the write-law parameters move, for this many applied steps")
+    a("--cooldown_lr_start", type=float, default=5e-5)
+    a("--cooldown_lr_end", type=float, default=1e-6)
+    a("--sam", action="store_true", help="sharpness-aware step on the ctx operators (two backward passes)")
+    a("--sam_rho", type=float, default=0.05)
+    a("--sam_every", type=int, default=1)
+    a("--telemetry_every", type=int, default=0, help="> 0: per-layer gate / value-tail / logit telemetry on a fixed batch")
+    a("--sat_tau", type=float, default=0.0, help="> 0: saturating backward of the engine")
     a("--max_norm", type=float, default=1.0)
     a("--clip_mult", type=float, default=0.0, help="> 0: calibrated clip at clip_mult x EMA of the norm")
     a("--skip_factor", type=float, default=5.0)
@@ -107,7 +122,17 @@ def parse_args(argv=None):
     a("--seed", type=int, default=1337)
     a("--log_every", type=int, default=10)
     a("--device", default="")
-    return ap.parse_args(argv)
+    args = ap.parse_args(argv)
+    if args.protocol == "pdn":                           # only where the user left the default
+        d = lambda k: getattr(args, k) == ap.get_default(k)
+        args.global_batch = 256 if d("global_batch") else args.global_batch
+        args.total_steps = 30000 if d("total_steps") else args.total_steps
+        args.skip_factor = 1e30 if d("skip_factor") else args.skip_factor
+        args.lr = 4e-4 if d("lr") else args.lr
+        args.min_lr = 0.1 * args.lr if d("min_lr") else args.min_lr
+        args.warmup_steps = 1024 if d("warmup_steps") else args.warmup_steps
+        args.wd_doctrine = args.wd_doctrine or "all"
+    return args
 
 
 def _dist_setup(device_arg):
@@ -159,9 +184,13 @@ def run(args):
         schedules, ekw = [k for _, k in rungs], dict(C=C)
     else:
         schedules, ekw = [uniform_chunks(T, c, min(c, k)) for c, k in rungs], {}
+    if args.sat_tau > 0:
+        ekw["sat_tau"] = args.sat_tau
     ekw.update(json.loads(args.engine_kwargs))
-    tr = Trainer(cfg, schedules, seq_len=T, micro_batch=micro, local_batch=local, lr=args.lr,
+    cooldown = args.cooldown_steps > 0
+    tr = Trainer(cfg, schedules, seq_len=T, micro_batch=micro, local_batch=local, lr=args.lr, eps=args.eps,
                  weight_decay=args.weight_decay, decay_all=args.decay_all, max_norm=args.max_norm,
+                 wd_doctrine=args.wd_doctrine or None, cooldown=cooldown, dm_accum=args.dm_accum, dm_lr=args.dm_lr,
                  optimizer=args.optimizer, device=dev, autocast_bf16=not args.fp32 and dev.type == "cuda",
                  use_graphs=not args.no_graphs, seed=args.seed, engine=engine, engine_kwargs=ekw,
                  rank_outlier_factor=args.rank_outlier_factor, rank_outlier_max=args.rank_outlier_max,
@@ -178,6 +207,25 @@ def run(args):
     log = MetricsLogger(args.out_dir, enabled=master)
     writer = AsyncCheckpointWriter() if args.async_ckpt and master else None
     step, applied, seed_offset, tokens_seen = 0, 0, 0, 0
+    hybrid = hasattr(tr.opt, "dm")
+    # the ctx operators: what the sharpness-aware step perturbs
+    sam_params = [p for n, p in tr.model.named_parameters() if "w_kctx" in n or "w_vctx" in n] if args.sam else []
+    tel_x = None
+
+    def checkpoint_now():
+        return build_checkpoint(tr.model, tr.opt.trunk if hybrid else tr.opt, step=step, applied=applied,
+                                extra=extra_state(), optimizer_dm=tr.opt.dm if hybrid else None)
+
+    def load_optimizer(ck):
+        """Optimizer state of a checkpoint into the current group layout; a cooldown starts its moments fresh."""
+        from ..parallel.hybrid_optim import regroup_state
+        if cooldown or "optimizer" not in ck:
+            return
+        halves = [(tr.opt.trunk, "optimizer"), (tr.opt.dm, "optimizer_dm")] if hybrid else [(tr.opt, "optimizer")]
+        for o, key in halves:
+            sd = ck.get(key) or ck["optimizer"]          # a one-optimizer checkpoint feeds both halves
+            groups = o.param_groups if hasattr(o, "layout") else o.opt.param_groups
+            o.load_state_dict(regroup_state(sd, tr.model, groups, args.weight_decay))
 
     def extra_state():
         return {**skip.state_dict(), **clip.state_dict(), **rewind.state_dict(), "seed_offset": seed_offset,
@@ -188,8 +236,7 @@ def run(args):
         nonlocal step, applied, seed_offset, tokens_seen
         with torch.no_grad():
             tr.model.load_state_dict(ck["model"])
-        if "optimizer" in ck:
-            tr.opt.load_state_dict(ck["optimizer"])
+        load_optimizer(ck)
         tr.engine.pack()
         skip.load_state_dict(ck)
         clip.load_state_dict(ck)
@@ -204,6 +251,7 @@ def run(args):
         log.tick = int(ck.get("wb_tick", 0))
         if master:
             print(f"resumed from {resume} at step {step}", flush=True)
+    cd_start = applied                                   # a cooldown counts applied steps from here
 
     def make_stream(start, seed):
         if args.synthetic or not args.data_bin:
@@ -233,15 +281,27 @@ def run(args):
 
     t_last, final_loss = time.time(), float("nan")
     while step < args.total_steps:
+        if cooldown and applied - cd_start >= args.cooldown_steps:
+            if master:
+                save_persist(args.out_dir, tr.model, step, name=f"snap_cooldown_{step:06d}.pt")
+                print(f"cooldown done after {applied - cd_start} applied steps", flush=True)
+            break
         sid, is_probe = ladder.sid_of(step)
         sid = min(sid, n_sid - 1)
         lr = cosine_lr(step, args.total_steps, args.warmup_steps, args.lr, args.min_lr) * (gov.mult if args.lr_gov else 1.0)
+        if cooldown:                                     # linear in applied steps
+            prog = min(1.0, (applied - cd_start) / max(1, args.cooldown_steps))
+            lr = args.cooldown_lr_start + (args.cooldown_lr_end - args.cooldown_lr_start) * prog
         thr = skip.threshold(is_probe)
         if inject.spiked(step, rewind.count) or step in inject.nans:
             thr = 1e-30                                      # the injected spike: every finite norm exceeds this
         tr.opt.skip_norm, tr.opt.max_norm = thr, clip.threshold(is_probe)
         t0 = time.time()
-        loss = tr.step(next(stream), sid=sid, lr=lr)
+        do_sam = bool(sam_params) and not is_probe and step % args.sam_every == 0
+        if do_sam:
+            loss = tr.sam_step(next(stream), sam_params, args.sam_rho, sid=sid, lr=lr)
+        else:
+            loss = tr.step(next(stream), sid=sid, lr=lr)
         ctrl = tr.opt.ctrl.tolist()
         gn, skipped = ctrl[0], ctrl[2] > 0.5
         gn_seen, loss_seen = inject.apply(step, gn, loss, rewind.count)
@@ -270,6 +330,12 @@ def run(args):
                "train/skipped_total": skip.skipped_total, "train/rank_excl": tr.rank_excluded,
                "train/applied": applied, "train/tokens": tokens_seen, "train/step_ms": step_ms,
                "train/breaker": rewarmed, "train/creep": creeping, "train/gov_mult": gov.mult}
+        if args.sam:
+            rec["train/sam_active"] = int(do_sam)
+            if do_sam:
+                rec["train/sam_sharp"] = tr.sam_sharpness
+        if hybrid:
+            rec["train/dm_stepped"], rec["train/dm_grad_norm"] = ctrl[3] > 0.5, tr.opt.last_dm_norm
         if dev.type == "cuda":
             rec["train/step_peak_gb"] = torch.cuda.max_memory_allocated(dev) / 2 ** 30
             rec["train/gpu_reserved_gb"] = torch.cuda.memory_reserved(dev) / 2 ** 30
@@ -278,6 +344,13 @@ def run(args):
             rec["val/loss"], rec["val/base_K"] = validate(base_sid), rung_of(base_sid)[1]
             rec["val/loss_deep"] = validate(n_sid - 1)
             rec["val/base_minus_deep"] = rec["val/loss"] - rec["val/loss_deep"]
+        if args.telemetry_every and step % args.telemetry_every == 0 and master:
+            from .curvature import gate_stats_layerwise
+            if tel_x is None:                            # one fixed batch, so the dials compare step to step
+                tel_x = next(make_stream(10 ** 9 + 99, args.seed))[:2, :min(T, 256)].to(dev)
+            mode, tr.model.cfg.attn_mode = tr.model.cfg.attn_mode, "sequential"
+            rec.update(gate_stats_layerwise(tr.model, tel_x))
+            tr.model.cfg.attn_mode = mode
         if args.curv_every and step % args.curv_every == 0 and step > 0:
             from .curvature import ctx_top_eig, layer_grad_norms
             rec.update(layer_grad_norms(tr.model, tr.opt.grad_buffers()))
@@ -296,7 +369,7 @@ def run(args):
         if args.auto_rewind:
             rewind.note(step, skipped)
             if rewind.want_snapshot(step):
-                ck = build_checkpoint(tr.model, tr.opt, step=step, applied=applied, extra=extra_state())
+                ck = checkpoint_now()
                 rewind.add_snapshot(step, AsyncCheckpointWriter.to_cpu(ck))       # resident, in host memory
             if rewind.wedged():
                 pick = rewind.choose(step, extra={"skips_in_window": sum(rewind.recent), "rho_ema": gov.rho_ema or 0.0})
@@ -315,7 +388,7 @@ def run(args):
                 continue
         # ---- checkpoints --------------------------------------------------------------------------------
         if args.ckpt_every and step > 0 and step % args.ckpt_every == 0:
-            ck = build_checkpoint(tr.model, tr.opt, step=step, applied=applied, extra=extra_state())   # collective
+            ck = checkpoint_now()                            # collective
             if master:
                 path = os.path.join(args.out_dir, "ckpt_latest.pt")
                 writer.submit(ck, path) if writer is not None else save_atomic(ck, path)

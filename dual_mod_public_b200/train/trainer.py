@@ -20,7 +20,9 @@ import torch.distributed as dist
 
 from ..engines.wavescan import WaveScanEngine
 from ..models import DualModLM
-from ..parallel.fused_optim import FusedDPAdamW, NcclAdamW, decay_groups, default_buckets
+from ..parallel.fused_optim import FusedDPAdamW, NcclAdamW, default_buckets
+from ..parallel.hybrid_optim import (DM_NAMES, HybridAdamW, matches, optimizer_groups, recall_only,
+                                     restrict_buckets)
 
 
 class Trainer:
@@ -28,7 +30,8 @@ class Trainer:
                  betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, decay_all=False, max_norm=1.0,
                  skip_norm=0.0, optimizer="fused", device=None, autocast_bf16=True, use_graphs=True,
                  overlap_buckets=True, process_group=None, seed=1337, engine="wavescan",
-                 engine_kwargs=None, model=None, rank_outlier_factor=0.0, rank_outlier_max=1, peer_watch=None):
+                 engine_kwargs=None, model=None, rank_outlier_factor=0.0, rank_outlier_max=1, peer_watch=None,
+                 wd_doctrine=None, cooldown=False, dm_accum=1, dm_lr=None):
         assert local_batch % micro_batch == 0, "local batch must be a whole number of micro-batches"
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
@@ -39,13 +42,28 @@ class Trainer:
             torch.manual_seed(seed)
             model = DualModLM(cfg)
         self.model = model.to(self.device)
-        groups = decay_groups(self.model, weight_decay, decay_all=decay_all)
+        # wd_doctrine: "split" (matrices decay), "all", "branch" (grown-branch parameters at 10x the decay);
+        # cooldown: only the write-law parameters move; dm_accum / dm_lr: two-speed optimizer
+        # (parallel/hybrid_optim.py)
+        doctrine = wd_doctrine or ("all" if decay_all else "split")
         common = dict(lr=lr, betas=betas, eps=eps, max_norm=max_norm, skip_norm=skip_norm,
                       grad_accum=self.accum, process_group=process_group)
-        if optimizer == "fused":
-            self.opt = FusedDPAdamW(groups, default_buckets(self.model), device=self.device, **common)
+
+        def make(only):
+            groups = optimizer_groups(self.model, doctrine, weight_decay, only=only)
+            if cooldown:
+                groups = recall_only(groups, self.model)
+            if optimizer == "fused":
+                owned = [p for g in groups for p in g["params"]]
+                return FusedDPAdamW(groups, restrict_buckets(default_buckets(self.model), owned),
+                                    device=self.device, **common)
+            return NcclAdamW(groups, **common)
+
+        if dm_accum > 1 or dm_lr is not None:
+            is_dm = lambda n: matches(n, DM_NAMES)
+            self.opt = HybridAdamW(make(lambda n: not is_dm(n)), make(is_dm), dm_accum=dm_accum, dm_lr=dm_lr)
         else:
-            self.opt = NcclAdamW(groups, **common)
+            self.opt = make(None)
         # per-rank rejection needs every rank's LOCAL norm before anything is reduced: no early buckets then
         self.rank_outlier = (rank_outlier_factor, rank_outlier_max) if rank_outlier_factor > 0 and self.world > 1 else None
         self.group, self.rank_excluded = process_group, 0
@@ -81,21 +99,21 @@ class Trainer:
         self._side.wait_stream(cur)
         self.opt.bucket_ready(b, stream=self._side)
 
-    def step(self, tokens, sid=0, lr=None, read_loss=True):
-        """tokens: [local_batch, T+1] int64 (host, ideally pinned) — inputs are
-        tokens[:, :-1], targets tokens[:, 1:].  Returns the mean loss over the rank's
-        micro-batches as a Python float (or the device tensor when read_loss=False)."""
+    def accumulate(self, tokens, sid=0, final=True):
+        """Zero the gradients, then forward + backward over the rank's micro-batches.  final=False: a pass
+        whose gradients will be recomputed (no bucket may start its reduction yet)."""
         mb, T = self.micro_batch, self.T
-        if self.peer_watch is not None:
-            self.peer_watch.sync(self.steps_done)            # raises PeerLost before anything is launched
         self.opt.zero_grad()
         self._loss_acc.zero_()
         nb = self.device.type == "cuda"
         for a in range(self.accum):
             blk = tokens[a * mb:(a + 1) * mb].to(self.device, non_blocking=nb)   # one contiguous H2D copy
             idx, tgt = blk[:, :T], blk[:, 1:T + 1]
-            self._last_micro = a == self.accum - 1
+            self._last_micro = final and a == self.accum - 1
             self._loss_acc += self.engine.train_step(idx, tgt, sid=sid)
+
+    def apply(self, lr=None):
+        """The optimizer step on what `accumulate` left, then the refreshed weight packs."""
         if self._side is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._side)
         keep_skip = self.opt.skip_norm
@@ -105,12 +123,58 @@ class Trainer:
         self.opt.grad_scale_override, self.opt.skip_norm = None, keep_skip
         self.engine.pack()
         self.steps_done += 1
+
+    def _read_loss(self, read_loss):
         if not read_loss:
             return self._loss_acc / self.accum
+        nb = self.device.type == "cuda"
         self._loss_host.copy_(self._loss_acc / self.accum, non_blocking=nb)
         if nb:
             torch.cuda.current_stream(self.device).synchronize()
         return float(self._loss_host)
+
+    def step(self, tokens, sid=0, lr=None, read_loss=True):
+        """tokens: [local_batch, T+1] int64 (host, ideally pinned) — inputs are
+        tokens[:, :-1], targets tokens[:, 1:].  Returns the mean loss over the rank's
+        micro-batches as a Python float (or the device tensor when read_loss=False)."""
+        if self.peer_watch is not None:
+            self.peer_watch.sync(self.steps_done)            # raises PeerLost before anything is launched
+        self.accumulate(tokens, sid)
+        self.apply(lr)
+        return self._read_loss(read_loss)
+
+    def sam_step(self, tokens, params, rho, sid=0, lr=None, read_loss=True):
+        """Sharpness-aware step (lm/train_340m/train_flagship.py:902-934): a first backward gives the mean
+        gradient g of `params`; they move to theta + rho g / |g|, a second backward gives the gradient the
+        optimizer uses, and theta comes back by copy (bit-exact, so ranks stay identical).  Also sets
+        `sam_sharpness` = <g / |g|, g' - g> / rho, the curvature along the gradient."""
+        if self.peer_watch is not None:
+            self.peer_watch.sync(self.steps_done)
+        G = self.opt.grad_buffers()
+        self.accumulate(tokens, sid, final=False)
+        with torch.no_grad():
+            g = torch.cat([G.get(p).reshape(-1).float() for p in params])
+            if self.world > 1:
+                dist.all_reduce(g, group=self.group)
+            g /= self.world * self.accum
+            gnorm = g.norm() + 1e-12
+            saved = [p.detach().clone() for p in params]
+            o = 0
+            for p in params:
+                p.add_(g[o:o + p.numel()].view_as(p).to(p.dtype), alpha=float(rho / gnorm))
+                o += p.numel()
+        self.engine.pack()
+        self.accumulate(tokens, sid, final=True)
+        with torch.no_grad():
+            g2 = torch.cat([G.get(p).reshape(-1).float() for p in params]) / (self.world * self.accum)
+            dot = (g2 * g).sum()
+            if self.world > 1:
+                dist.all_reduce(dot, group=self.group)
+            self.sam_sharpness = float((dot - (g * g).sum()) / (gnorm * rho))
+            for p, sv in zip(params, saved):
+                p.copy_(sv)
+        self.apply(lr)
+        return self._read_loss(read_loss)
 
     def _reject_outlier_ranks(self):
         """All-gather the local gradient norms; ranks far above the median zero their gradients and the

@@ -66,9 +66,10 @@ def save_snapshot(out_dir, ck, step):
     save_atomic(ck, os.path.join(out_dir, f"snap_{step:06d}.pt"), keep_prev=False)
 
 
-def save_persist(out_dir, model, step, anchor=False):
-    """Model-only file; `anchor` also hard-links it as `anchor_%07d.pt`."""
-    p = os.path.join(out_dir, f"persist_{step:07d}.pt")
+def save_persist(out_dir, model, step, anchor=False, name=None):
+    """Model-only file (`persist_%07d.pt` unless `name` is given); `anchor` also hard-links it as
+    `anchor_%07d.pt`."""
+    p = os.path.join(out_dir, name or f"persist_{step:07d}.pt")
     save_atomic({"model": model.state_dict(), "model_cfg": model.cfg.to_dict(), "step": int(step)},
                 p, keep_prev=False)
     if anchor:

@@ -114,3 +114,130 @@ def test_injected_storm_is_skipped_and_rewound(tmp_path, monkeypatch):
     ticks = [x["tick"] for x in recs]
     assert ticks == sorted(ticks) and len(set(ticks)) == len(ticks)               # monotonic across the rewind
     assert r["step"] == 16
+
+
+TINY = ["--recipe", "tiny", "--synthetic", "--device", "cpu", "--warmup_steps", "2", "--log_every", "100",
+        "--probe_frac", "0"]
+
+
+def test_group_doctrines_and_state_regrouping():
+    from dual_mod_public_b200 import preset
+    from dual_mod_public_b200.models import DualModLM
+    from dual_mod_public_b200.parallel import hybrid_optim as H
+    from dual_mod_public_b200.parallel.fused_optim import FusedDPAdamW, default_buckets
+    torch.manual_seed(0)
+    m = DualModLM(preset("tiny_cpu"))
+    n_all = len(H.named_unique(m))
+    split, every = H.optimizer_groups(m, "split", 0.1), H.optimizer_groups(m, "all", 0.1)
+    assert len(split) == 2 and len(every) == 1 and len(every[0]["params"]) == n_all
+    assert all(p.dim() >= 2 for p in split[0]["params"]) and split[1]["weight_decay"] == 0.0
+    dm = H.optimizer_groups(m, "split", 0.1, only=lambda n: H.matches(n, H.DM_NAMES))
+    trunk = H.optimizer_groups(m, "split", 0.1, only=lambda n: not H.matches(n, H.DM_NAMES))
+    assert sum(len(g["params"]) for g in dm + trunk) == n_all and dm
+    cd = H.recall_only(split, m)
+    frozen = [p for g in cd if g["lr_mult"] == 0.0 for p in g["params"]]
+    assert any(p is m.blocks[0].mlp.w1.weight for p in frozen)
+    assert not any(p is m.blocks[0].attn.w_kctx.weight for p in frozen)
+    # one step under "all", then carry the moments into the "split" layout: same moments per parameter
+    o1 = FusedDPAdamW(every, default_buckets(m), lr=1e-3, use_kernel=False)
+    for p in m.parameters():
+        o1.grad_buffers().get(p).normal_()
+    o1.step()
+    sd = o1.state_dict()
+    o2 = FusedDPAdamW(split, default_buckets(m), lr=1e-3, use_kernel=False)
+    o2.load_state_dict(H.regroup_state(sd, m, o2.param_groups, 0.1))
+    sd2 = o2.state_dict()
+    old = {id(p): sd["state"][i]["exp_avg"] for i, p in enumerate(every[0]["params"])}
+    i = 0
+    for g in o2.param_groups:
+        for p in g["params"]:
+            assert torch.equal(sd2["state"][i]["exp_avg"], old[id(p)])
+            i += 1
+    assert H.regroup_state(sd2, m, o2.param_groups) is sd2
+
+
+def test_two_speed_optimizer_steps_the_dual_mod_half_on_the_mean_gradient(tmp_path):
+    out = str(tmp_path / "hyb")
+    r = train_main(TINY + ["--out_dir", out, "--total_steps", "6", "--dm_accum", "3", "--dm_lr", "1e-3",
+                           "--ckpt_every", "5", "--lr", "3e-3"])
+    recs = _records(out)
+    assert [x["train/dm_stepped"] for x in recs] == [False, False, True, False, False, True]
+    ck = torch.load(os.path.join(out, "ckpt_latest.pt"), weights_only=False)
+    assert "optimizer_dm" in ck and len(ck["optimizer_dm"]["state"]) > 0
+    assert r["applied"] == 6 and recs[-1]["train/loss"] < recs[0]["train/loss"]
+    # the same checkpoint resumes a one-optimizer run (moments regrouped) and a two-speed run
+    train_main(TINY + ["--out_dir", out, "--total_steps", "8", "--resume", "auto", "--dm_accum", "2"])
+
+
+def test_hybrid_halves_match_separate_adamw_on_accumulated_gradients():
+    from dual_mod_public_b200 import preset
+    from dual_mod_public_b200.models import DualModLM
+    from dual_mod_public_b200.parallel import hybrid_optim as H
+    from dual_mod_public_b200.parallel.fused_optim import NcclAdamW
+    torch.manual_seed(0)
+    m = DualModLM(preset("tiny_cpu"))
+    ref = {n: p.detach().clone() for n, p in m.named_parameters()}
+    is_dm = lambda n: H.matches(n, H.DM_NAMES)
+    mk = lambda only: NcclAdamW(H.optimizer_groups(m, "split", 0.0, only=only), lr=1e-2, max_norm=0.0)
+    hy = H.HybridAdamW(mk(lambda n: not is_dm(n)), mk(is_dm), dm_accum=2)
+    G_ = hy.grad_buffers()
+    grads = []
+    for it in range(2):
+        hy.zero_grad()
+        g = {n: torch.randn_like(p) * 0.01 for n, p in m.named_parameters()}
+        for n, p in m.named_parameters():
+            G_.get(p).add_(g[n])
+        grads.append(g)
+        ctrl = hy.step().tolist()
+        assert ctrl[3] == float(it == 1)
+    name = "blocks.0.attn.w_kctx.weight"
+    mean_g = 0.5 * (grads[0][name] + grads[1][name])
+    # first AdamW step from zero moments moves every entry by lr * g / (|g| + eps)
+    moved = dict(m.named_parameters())[name].detach() - ref[name]
+    assert torch.allclose(moved, -1e-2 * mean_g / (mean_g.abs() + 1e-8), atol=2e-5)
+    trunk = "blocks.0.mlp.w1.weight"
+    assert not torch.equal(dict(m.named_parameters())[trunk].detach(), ref[trunk])
+
+
+def test_cooldown_moves_only_the_write_law(tmp_path):
+    out = str(tmp_path / "cd")
+    train_main(TINY + ["--out_dir", out, "--total_steps", "3", "--ckpt_every", "2", "--lr", "3e-3"])
+    before = torch.load(os.path.join(out, "ckpt_latest.pt"), weights_only=False)["model"]
+    r = train_main(TINY + ["--out_dir", out, "--total_steps", "50", "--resume", "auto", "--cooldown_steps", "3",
+                           "--cooldown_lr_start", "1e-3", "--cooldown_lr_end", "1e-4"])
+    assert r["applied"] == 3 + 3
+    snaps = [f for f in os.listdir(out) if f.startswith("snap_cooldown_")]
+    assert len(snaps) == 1
+    after = torch.load(os.path.join(out, snaps[0]), weights_only=False)["model"]
+    assert torch.equal(after["blocks.0.mlp.w1.weight"], before["blocks.0.mlp.w1.weight"])
+    assert torch.equal(after["tok_emb.weight"], before["tok_emb.weight"])
+    assert not torch.equal(after["blocks.0.attn.w_kctx.weight"], before["blocks.0.attn.w_kctx.weight"])
+    lrs = [x["train/lr"] for x in _records(out)][-3:]
+    assert abs(lrs[0] - 1e-3) < 1e-9 and lrs[0] > lrs[1] > lrs[2] > 1e-4
+
+
+def test_sam_step_restores_the_weights_and_reports_sharpness(tmp_path):
+    from dual_mod_public_b200 import preset
+    from dual_mod_public_b200.engines.schedule import uniform_chunks
+    from dual_mod_public_b200.train import Trainer
+    cfg = preset("tiny_cpu")
+    mk = lambda: Trainer(cfg, [uniform_chunks(64, 16, 4)], seq_len=64, micro_batch=2, local_batch=4, lr=0.0,
+                         device="cpu", autocast_bf16=False, use_graphs=False, seed=3)
+    a, b = mk(), mk()
+    toks = torch.randint(0, cfg.vocab_size, (4, 65), generator=torch.Generator().manual_seed(1))
+    sam = [p for n, p in a.model.named_parameters() if "w_kctx" in n or "w_vctx" in n]
+    la = a.sam_step(toks, sam, rho=0.05)
+    lb = b.step(toks)
+    assert math.isfinite(a.sam_sharpness) and la != lb               # the reported loss is at theta + eps
+    # lr = 0: the weights must be exactly where they started
+    for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        assert torch.equal(p, q), n
+    # the gradient the optimizer saw differs from the plain one only through the perturbation
+    ga, gb = a.opt.grad_buffers().get(sam[0]), b.opt.grad_buffers().get(
+        [p for n, p in b.model.named_parameters() if "w_kctx" in n][0])
+    assert not torch.equal(ga, gb) and torch.allclose(ga, gb, atol=0.3 * gb.abs().max().item())
+    out = str(tmp_path / "sam")
+    train_main(TINY + ["--out_dir", out, "--total_steps", "3", "--sam", "--sam_every", "2", "--telemetry_every", "2"])
+    recs = _records(out)
+    assert [x["train/sam_active"] for x in recs] == [1, 0, 1] and "train/sam_sharp" in recs[0]
+    assert "gates/g_k_L00" in recs[0] and "vtail/p999_L00" in recs[2] and "telemetry/g_v_mean_all_layers" in recs[0]
