@@ -210,7 +210,9 @@ class DualModEval(_Base):
 
     @torch.no_grad()
     def _greedy(self, prompt_ids, max_new, stop_strs):
-        """Greedy continuation of one prompt -> text (cut at the first stop string)."""
+        """Greedy continuation of one prompt -> text (cut at the first stop string).  The budget is capped
+        at half the context, so a short context still keeps a prompt."""
+        max_new = min(max_new, max(1, self.max_length // 2))
         cap = self.max_length - max_new
         ids = trunc_keep_head(prompt_ids, max(1, cap))
         x = torch.tensor([ids], dtype=torch.long, device=self.dev)
@@ -269,10 +271,150 @@ class DualModEval(_Base):
         return out
 
 
-def run_lm_eval(ckpt, tasks, tokenizer, num_fewshot=0, limit=None, out_path=None, **kw):
-    """Drive `lm_eval.simple_evaluate` with a checkpoint (needs the `lm_eval` package)."""
+class WavefrontEval(DualModEval):
+    """Scoring AND generation through a training engine at K sweeps: the operator the model was trained
+    with (the wavefront engine at the last rung of its ladder), not the exact scan.
+
+      likelihood   rows are right-padded to `T_eval` (a whole number of chunks) and scored in batches of
+                   `batch_rows`; the engine's masks are causal, so padding never reaches a real position
+      generation   greedy, one engine forward over [prompt + generated so far, padding] per token; every
+                   row keeps its exact tokens at positions [0, len) and is read at its own last position;
+                   rows are bucketed by (padded length, stop strings, budget), `gen_rows` per forward
+      operator     `local_window` / other operator-defining engine arguments travel with the checkpoint
+                   (`engine_kwargs` saved by the trainer) and are applied unless overridden
+      cache        `GEN_CACHE_DIR`: the finished generations of one call are pickled per (tag, rank, world,
+                   request hash), so a rank that finished is not recomputed after a failed collective
+
+    Reference parity: lm/eval/lm_eval_adapter.py:605-781 (`Wave3DEval`)."""
+
+    OPERATOR_KEYS = ("local_window", "raw_diag")
+
+    def __init__(self, ckpt, K, T_eval=2048, C=64, engine="wave3d", gen_rows=4, engine_kwargs=None, **kw):
+        T_eval = -(-T_eval // C) * C
+        kw.setdefault("max_length", T_eval)
+        super().__init__(ckpt, **kw)
+        assert self.model.cfg.attn_mode != "vanilla", "engine scoring needs the Dual-Mod operator"
+        self.K, self.C, self.T_eval, self.engine_name, self.gen_rows = int(K), C, T_eval, engine, gen_rows
+        ekw = {k: v for k, v in (self.ckpt_engine_kwargs or {}).items() if k in self.OPERATOR_KEYS and v}
+        ekw.update(engine_kwargs or {})
+        ekw.pop("C", None)
+        self.engine_kwargs = ekw
+        self.max_length = min(self.max_length, T_eval)
+
+    def _engine(self, B, T):
+        key = (self.engine_name, B, T)
+        if key not in self._engines:
+            for k in [k for k in self._engines if k[0] == self.engine_name and k != key]:
+                del self._engines[k]                     # one engine of this kind resident at a time
+            common = dict(device=self.dev, keep_logits=True, autocast_bf16=torch.device(self.dev).type == "cuda",
+                          **self.engine_kwargs)
+            if self.engine_name == "wave3d":
+                from ..engines.wave3d import Wave3DEngine
+                eng = Wave3DEngine(self.model, [self.K], B, T, C=self.C, **common)
+            else:
+                from ..engines.schedule import uniform_chunks
+                from ..engines.wavescan import WaveScanEngine
+                eng = WaveScanEngine(self.model, [uniform_chunks(T, self.C, min(self.C, self.K))], B, T, **common)
+            eng.pack()
+            self._engines[key] = eng
+        return self._engines[key]
+
+    @torch.no_grad()
+    def _logits(self, x):
+        B, L = x.shape
+        T = -(-L // self.C) * self.C
+        rows = self.batch_rows
+        eng = self._engine(rows, T)
+        xp = torch.zeros(rows, T, dtype=torch.long, device=self.dev)
+        out = []
+        for b0 in range(0, B, rows):
+            n = min(rows, B - b0)
+            xp.zero_()
+            xp[:n, :L] = x[b0:b0 + n]
+            eng.forward(xp)
+            out.append(eng.logits[:n, :L].float().clone())
+        return torch.cat(out)
+
+    # ---- generation through the engine --------------------------------------------------------------
+    def generate_until(self, requests):
+        import pickle
+        cdir, cpath = os.environ.get("GEN_CACHE_DIR"), None
+        if cdir:
+            salt = f"{os.environ.get('GEN_TRUNC', 'tail')}:K{self.K}:"
+            h = hashlib.sha1((salt + repr([(_args(r)[0], sorted(dict(_args(r)[1] or {}).items(), key=str))
+                                           for r in requests])).encode()).hexdigest()[:12]
+            cpath = os.path.join(cdir, f"{os.environ.get('GEN_TAG', 'gen')}_w{self._world_size}_r{self._rank}_{h}.pkl")
+            if os.path.exists(cpath):
+                res = pickle.load(open(cpath, "rb"))
+                if len(res) == len(requests):
+                    return res
+        res = self._generate_engine(requests)
+        if cpath:
+            os.makedirs(cdir, exist_ok=True)
+            with open(cpath + ".tmp", "wb") as f:
+                pickle.dump(res, f)
+            os.replace(cpath + ".tmp", cpath)
+        return res
+
+    @torch.no_grad()
+    def _generate_engine(self, requests):
+        from collections import defaultdict
+        buckets = defaultdict(list)
+        for i, req in enumerate(requests):
+            prompt, kw = _args(req)[:2]
+            kw = dict(kw or {})
+            until = kw.get("until") or []
+            until = (until,) if isinstance(until, str) else tuple(until)
+            max_new = min(int(kw.get("max_gen_toks", kw.get("max_new_tokens", 128))), max(1, self.max_length // 2))
+            toks = trunc_keep_head([self.bos] + self.tok_encode(prompt), max(1, self.max_length - max_new))
+            T = min(self.max_length, -(-(len(toks) + max_new) // self.C) * self.C)
+            buckets[(T, until, max_new)].append((toks, i))
+        res, eos, R = [None] * len(requests), self.tok.eos_token_id, self.gen_rows
+        for (T, until, max_new), group in sorted(buckets.items(), key=lambda kv: kv[0][0]):
+            eng = self._engine(R, T)
+            group.sort(key=lambda it: len(it[0]))
+            for g0 in range(0, len(group), R):
+                sub = group[g0:g0 + R]
+                n = len(sub)
+                x = torch.zeros(R, T, dtype=torch.long, device=self.dev)
+                for b, (toks, _) in enumerate(sub):
+                    x[b, :len(toks)] = torch.tensor(toks, device=self.dev)
+                pos = torch.tensor([len(t) for t, _ in sub] + [1] * (R - n), device=self.dev)    # next slot per row
+                ar = torch.arange(R, device=self.dev)
+                outs, alive = [[] for _ in range(n)], [True] * n
+                for _ in range(max_new):
+                    eng.forward(x)
+                    nxt = eng.logits[ar, pos - 1].float().argmax(-1)
+                    for b in range(n):
+                        if not alive[b]:
+                            continue
+                        t = int(nxt[b])
+                        if t == eos:
+                            alive[b] = False
+                            continue
+                        outs[b].append(t)
+                        if until and any(u in self.tok.decode(outs[b][-16:]) for u in until):
+                            alive[b] = False
+                    if not any(alive) or int(pos[:n].max()) >= T:
+                        break
+                    wr = pos < T
+                    x[ar[wr], pos[wr]] = nxt[wr]
+                    pos = torch.clamp(pos + 1, max=T)
+                for b, (_, i) in enumerate(sub):
+                    text = self.tok.decode(outs[b])
+                    for u in until:
+                        if u in text:
+                            text = text[:text.index(u)]
+                    res[i] = text
+        return res
+
+
+def run_lm_eval(ckpt, tasks, tokenizer, num_fewshot=0, limit=None, out_path=None, wavefront_K=0, **kw):
+    """Drive `lm_eval.simple_evaluate` with a checkpoint (needs the `lm_eval` package).  wavefront_K > 0
+    scores and generates through the training engine at that K (`WavefrontEval`)."""
     import lm_eval
-    lm = DualModEval(ckpt, tokenizer=tokenizer, **kw)
+    lm = (WavefrontEval(ckpt, wavefront_K, tokenizer=tokenizer, **kw) if wavefront_K
+          else DualModEval(ckpt, tokenizer=tokenizer, **kw))
     res = lm_eval.simple_evaluate(model=lm, tasks=list(tasks), num_fewshot=num_fewshot, limit=limit)
     if out_path and lm.rank == 0:
         json.dump(res["results"], open(out_path, "w"), indent=1)

@@ -122,3 +122,94 @@ def test_loop_fixed_point_table():
     rows = analyse(m, x, torch.roll(x, -1, 1), torch.ones(3, 16, dtype=torch.bool), K=6, out=lambda s: None)
     assert len(rows) == 6 and rows[0][1] != rows[0][1] and all(0 <= r[2] <= 1 for r in rows)
     assert all(r[1] == r[1] for r in rows[1:])
+
+
+def test_engine_scoring_and_generation_at_exact_k_match_the_scan(tmp_path, monkeypatch):
+    from dual_mod_public_b200.eval.lm_eval_adapter import WavefrontEval
+    m = tiny()
+    save_checkpoint(str(tmp_path), m, step=3, extra={"engine_kwargs": {"C": 16}})
+    ck = os.path.join(tmp_path, "ckpt_latest.pt")
+    monkeypatch.setenv("EVAL_LEN_QUANT", "16")
+    ref = DualModEval(ck, tokenizer="bytes", device="cpu", batch_rows=2, max_length=48)
+    # 48 positions in chunks of 16: the wavefront is exact from K = 48 - 3 + 1 sweeps on
+    for engine, K in (("wave3d", 46), ("wavescan", 16)):
+        lm = WavefrontEval(ck, K, T_eval=48, C=16, engine=engine, gen_rows=2, tokenizer="bytes", device="cpu",
+                           batch_rows=2)
+        reqs = [("the cat", " sat"), ("a", " much longer continuation"), ("", "x"), ("hello wor", "ld"), ("ab", "c")]
+        for (lp, g), (lp_r, g_r) in zip(lm.loglikelihood(reqs), ref.loglikelihood(reqs)):
+            assert abs(lp - lp_r) < 2e-3 and g == g_r, (engine, lp, lp_r)
+        gen = [("abc", {"until": [], "max_gen_toks": 5}), ("hello there", {"until": [], "max_gen_toks": 5}),
+               ("x", {"until": [], "max_gen_toks": 3})]
+        assert lm.generate_until(gen) == ref.generate_until(gen), engine
+    # an approximate operator (few sweeps) still scores, and differs
+    few = WavefrontEval(ck, 2, T_eval=48, C=16, tokenizer="bytes", device="cpu", batch_rows=2)
+    a, b = few.loglikelihood(reqs[:2]), ref.loglikelihood(reqs[:2])
+    assert all(abs(x[0] - y[0]) < 5.0 for x, y in zip(a, b)) and any(abs(x[0] - y[0]) > 1e-6 for x, y in zip(a, b))
+    # per-rank generation cache
+    monkeypatch.setenv("GEN_CACHE_DIR", str(tmp_path / "gc"))
+    first = few.generate_until(gen[:2])
+    assert len(os.listdir(tmp_path / "gc")) == 1
+    few._generate_engine = None                                     # a second call must not generate
+    assert few.generate_until(gen[:2]) == first
+
+
+def test_recall_and_needle_protocols_run_from_local_files(tmp_path):
+    from dual_mod_public_b200.eval import collate, recall_tasks as R
+    from dual_mod_public_b200.eval.run_lm_eval import main as eval_main
+    tk = ByteTokenizer()
+    filler = "lorem ipsum dolor sit amet " * 40
+    doc = {"text": filler + "The serial number: QX-7731. " + filler, "key": "serial number", "value": "QX-7731"}
+    cut = R.cut_to_answer(doc, "text", ("key", "value"), tk, context_length=300, answer_length=50)
+    n = len(tk.encode(cut["text"]))
+    assert n <= 250 and "QX-7731" in cut["text"]
+    at = cut["text"].lower().index("serial number")
+    assert abs(at - 125) < 30                                        # the window is centred on the first match
+    head = R.cut_to_answer({"context": filler * 3, "question": "q?", "answers": ["x"]}, "context", (), tk, 300, 50)
+    assert head["context"] == (filler * 3).strip()[:250]
+    assert R.cut_to_answer({"text": "a b", "key": "k", "value": "7"}, "text", ("value",), tk) is None
+    p = R.recall_prompt("fda", {"text": "Device: X9.\nserial number:", "key": "serial number", "value": "X9"}, tk)
+    assert p == "Device: X9. Serial number:"
+    p = R.recall_prompt("swde", {"text": "Title: Alien. " + R.SUMMARY_MARK + " junk", "key": "title", "value": "Alien"}, tk)
+    assert p == "Title: Alien. Title:"
+    p = R.recall_prompt("triviaqa", {"context": "[DOC] Paris is in France. Where is Paris?", "question": " Where is Paris? ",
+                                     "answers": ["France"]}, tk)
+    assert p == "Paris is in France. Where is Paris?"
+    assert R.contains_score("it is FRANCE!", ["france", "gaul"]) == 1 and R.contains_score("spain", ["france"]) == 0
+    assert R.match_all("keys 12 and 99", ["12", "99", "7"]) == 2 / 3
+    assert R.shard(list(range(10)), "1/4") == [1, 5, 9]
+
+    class Echo:                                                      # answers with the tail of the prompt
+        tok = tk
+
+        def generate_until(self, reqs):
+            return [r[0][-40:] for r in reqs]
+
+    docs = [{"text": "The code is ABC.", "key": "code", "value": "ABC"}, {"text": "Nothing here.", "key": "code", "value": "ZZZ"}]
+    dump = str(tmp_path / "s0_TEXT.jsonl")
+    assert R.run_recall(Echo(), "fda", docs, tk, dump=dump) == {"contains": 0.5, "n": 2}
+    hits, n, lines = collate.pool([dump, dump])
+    assert (hits, n) == (2, 4) and lines[-1].startswith("POOLED contains = 50.00")
+    root = tmp_path / "ruler"
+    os.makedirs(root / "niah_single_1_1024")
+    with open(root / "niah_single_1_1024" / "validation.jsonl", "w") as f:
+        f.write(json.dumps({"input": "hay needle 4242 hay\n", "outputs": ["4242"], "answer_prefix": " The number is"}) + "\n")
+    nd = R.load_needles(str(root), "niah_single_1", [1024, 2048])
+    assert nd[0]["gen_prefix"] == "The number is" and R.run_needles(Echo(), nd) == {"1024": 1.0, "n": 1}
+    # the driver end to end on a checkpoint, local tasks only (no harness package needed)
+    m = tiny()
+    run = tmp_path / "runA"
+    save_checkpoint(str(run), m, step=7)
+    data = str(tmp_path / "fda.jsonl")
+    with open(data, "w") as f:
+        for d in docs:
+            f.write(json.dumps(d) + "\n")
+    out = str(tmp_path / "analysis")
+    res = eval_main(["--ckpt", str(run / "ckpt_latest.pt"), "--tasks", "jrt_fda,niah_single_1", "--local_data", data,
+                     "--ruler_root", str(root), "--ruler_lengths", "1024", "--device", "cpu", "--T_eval", "64",
+                     "--out_dir", out, "--tag", "t"])
+    assert set(res) == {"jrt_fda", "niah_single_1"} and res["jrt_fda"]["n"] == 2
+    files = sorted(os.listdir(out))
+    assert any(f.startswith("lmeval_runA_7_") and f.endswith("_t.json") for f in files)
+    assert any(f.endswith("_jrt_fda_TEXT.jsonl") for f in files)
+    lines = collate.table(out, "runA")
+    assert any("jrt_fda" in l for l in lines) and any("niah_single_1" in l for l in lines)
