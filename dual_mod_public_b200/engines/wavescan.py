@@ -22,6 +22,8 @@ engines/wavescan/engine/backward.py:87-206.
 
 from __future__ import annotations
 
+import os
+import time
 from types import SimpleNamespace
 
 import torch
@@ -254,6 +256,8 @@ class WaveScanEngine:
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self._graphs = {}
         self._graph_launches = {}
+        self.capture_seconds = {}
+        self.nvtx = os.environ.get("DMB_NVTX", "0") == "1" and self.device.type == "cuda"
 
     # =============================================================================
     # public API
@@ -385,6 +389,18 @@ class WaveScanEngine:
     # CUDA graphs
     # =============================================================================
     def _run(self, key, sid, body, replay_after_capture=False):
+        """Run one phase of the step (embedding, a layer's forward, the head, a layer's backward, ...):
+        eagerly, or as a CUDA graph recorded on first use.  With DMB_NVTX=1 every phase is an NVTX
+        range named after its key, so a timeline shows the engine's phases."""
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(f"dmb:{key}:sid{sid}")
+        try:
+            self._run_phase(key, sid, body, replay_after_capture)
+        finally:
+            if self.nvtx:
+                torch.cuda.nvtx.range_pop()
+
+    def _run_phase(self, key, sid, body, replay_after_capture):
         if not self.use_graphs:
             return body()
         gkey = (key, sid)
@@ -399,11 +415,14 @@ class WaveScanEngine:
         body()
         self._graph_launches[gkey] = self.ops.launches - n0
         torch.cuda.synchronize(self.device)
+        t0 = time.perf_counter()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, pool=self._graphs.get("pool")):
             body()
         self._graphs.setdefault("pool", g.pool())
         self._graphs[gkey] = g
+        # seconds spent recording, per schedule id (a trainer logs it once per rung)
+        self.capture_seconds[sid] = self.capture_seconds.get(sid, 0.0) + time.perf_counter() - t0
         if replay_after_capture:
             # tensors the body left for later bodies now live in the graph's pool and were not
             # written by the recording: run the (idempotent) body once more through the graph

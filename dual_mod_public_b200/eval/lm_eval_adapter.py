@@ -132,6 +132,28 @@ class DualModEval(_Base):
     def tok_encode(self, s):
         return list(self.tok.encode(s, add_special_tokens=False))
 
+    # what the harness calls between ranks when world_size > 1 (each a no-op on one rank)
+    def all_gather(self, tensor):
+        import torch.distributed as dist
+        if self._world_size == 1:
+            return tensor.unsqueeze(0)
+        out = [torch.zeros_like(tensor) for _ in range(self._world_size)]
+        dist.all_gather(out, tensor)
+        return torch.stack(out)
+
+    def gather_object(self, obj, dst=0):
+        import torch.distributed as dist
+        if self._world_size == 1:
+            return [obj]
+        out = [None] * self._world_size
+        dist.all_gather_object(out, obj)
+        return out if self._rank == dst else None
+
+    def barrier(self):
+        import torch.distributed as dist
+        if self._world_size > 1:
+            dist.barrier()
+
     # ---- scoring -----------------------------------------------------------------------------------
     def _amp(self):
         t = torch.device(self.dev).type

@@ -268,12 +268,23 @@ class MetricsLogger:
     """One JSON object per line in `<out_dir>/metrics.jsonl`.  `tick` increases by one per record
     whatever the step does, so plots stay monotonic across rewinds."""
 
-    def __init__(self, out_dir, enabled=True, tick=0):
+    def __init__(self, out_dir, enabled=True, tick=0, wandb_project="", wandb_name="", wandb_config=None):
+        """wandb_project: also mirror every record to that project (run `wandb_name`, resumable by name;
+        the record's tick is the x axis, because rewinds make steps non-monotonic).  The mirror is dropped
+        with a message when the package is missing or the service cannot be reached."""
         self.enabled, self.tick = enabled, tick
         self.path = os.path.join(out_dir, "metrics.jsonl")
+        self._wb = None
         if enabled:
             os.makedirs(out_dir, exist_ok=True)
             self._f = open(self.path, "a")
+            if wandb_project:
+                try:
+                    import wandb
+                    self._wb = wandb.init(project=wandb_project, name=wandb_name or os.path.basename(out_dir),
+                                          id=wandb_name or None, resume="allow", config=wandb_config or {})
+                except Exception as e:                           # optional mirror: never stop a run for it
+                    print(f"metrics mirror disabled: {e}", flush=True)
 
     def log(self, step, **kv):
         self.tick += 1
@@ -283,10 +294,14 @@ class MetricsLogger:
         rec.update({k: (float(v) if isinstance(v, (int, float)) and not isinstance(v, bool) else v) for k, v in kv.items()})
         self._f.write(json.dumps(rec) + "\n")
         self._f.flush()
+        if self._wb is not None:
+            self._wb.log({k: v for k, v in rec.items() if isinstance(v, (int, float, bool))}, step=self.tick)
 
     def close(self):
         if self.enabled:
             self._f.close()
+            if self._wb is not None:
+                self._wb.finish()
 
 
 # ---------------------------------------------------------------------------------------------------

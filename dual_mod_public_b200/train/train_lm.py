@@ -121,6 +121,8 @@ def parse_args(argv=None):
     a("--resume", default="", help="checkpoint path, or 'auto' for <out_dir>/ckpt_latest.pt")
     a("--seed", type=int, default=1337)
     a("--log_every", type=int, default=10)
+    a("--wandb_project", default="", help="mirror metrics.jsonl to this project")
+    a("--val_exact_K", type=int, default=0, help="> 0: also validate through the engine at this K (the chunk length is exact for the cell engine) and log val/loss_exact")
     a("--device", default="")
     args = ap.parse_args(argv)
     if args.protocol == "pdn":                           # only where the user left the default
@@ -184,6 +186,11 @@ def run(args):
         schedules, ekw = [k for _, k in rungs], dict(C=C)
     else:
         schedules, ekw = [uniform_chunks(T, c, min(c, k)) for c, k in rungs], {}
+    exact_sid = None
+    if args.val_exact_K > 0:                             # one more schedule, used by validation only
+        exact_sid = len(schedules)
+        schedules = schedules + ([args.val_exact_K] if engine == "wave3d"
+                                 else [uniform_chunks(T, rungs[-1][0], min(rungs[-1][0], args.val_exact_K))])
     if args.sat_tau > 0:
         ekw["sat_tau"] = args.sat_tau
     ekw.update(json.loads(args.engine_kwargs))
@@ -204,7 +211,9 @@ def run(args):
                             snap_interval=args.snap_interval, lookback=args.rewind_lookback,
                             max_rewinds=args.rewind_max, seed=args.seed,
                             log_path=os.path.join(args.out_dir, "rewind_events.jsonl") if master else None)
-    log = MetricsLogger(args.out_dir, enabled=master)
+    log = MetricsLogger(args.out_dir, enabled=master, wandb_project=args.wandb_project,
+                        wandb_name=os.path.basename(os.path.normpath(args.out_dir)), wandb_config=vars(args))
+    capt_seen = set()
     writer = AsyncCheckpointWriter() if args.async_ckpt and master else None
     step, applied, seed_offset, tokens_seen = 0, 0, 0, 0
     hybrid = hasattr(tr.opt, "dm")
@@ -330,6 +339,14 @@ def run(args):
                "train/skipped_total": skip.skipped_total, "train/rank_excl": tr.rank_excluded,
                "train/applied": applied, "train/tokens": tokens_seen, "train/step_ms": step_ms,
                "train/breaker": rewarmed, "train/creep": creeping, "train/gov_mult": gov.mult}
+        kind = "probe" if is_probe else "base"
+        rec[f"{kind}/loss"], rec[f"{kind}/grad_norm"] = loss, gn
+        if is_probe and skip.ema[False]:
+            rec["probe/gn_ratio_vs_base"] = gn / max(skip.ema[False], 1e-9)
+        for s_, sec in getattr(tr.engine, "capture_seconds", {}).items():
+            if s_ not in capt_seen and sec > 0:          # once per rung, when its graphs have been recorded
+                capt_seen.add(s_)
+                rec[f"engine/capture_K{rung_of(s_)[1]}_s"] = sec
         if args.sam:
             rec["train/sam_active"] = int(do_sam)
             if do_sam:
@@ -344,6 +361,9 @@ def run(args):
             rec["val/loss"], rec["val/base_K"] = validate(base_sid), rung_of(base_sid)[1]
             rec["val/loss_deep"] = validate(n_sid - 1)
             rec["val/base_minus_deep"] = rec["val/loss"] - rec["val/loss_deep"]
+            if exact_sid is not None:
+                rec["val/loss_exact"] = validate(exact_sid)
+                rec[f"val/base_minus_k{args.val_exact_K}"] = rec["val/loss"] - rec["val/loss_exact"]
         if args.telemetry_every and step % args.telemetry_every == 0 and master:
             from .curvature import gate_stats_layerwise
             if tel_x is None:                            # one fixed batch, so the dials compare step to step

@@ -241,3 +241,17 @@ def test_sam_step_restores_the_weights_and_reports_sharpness(tmp_path):
     recs = _records(out)
     assert [x["train/sam_active"] for x in recs] == [1, 0, 1] and "train/sam_sharp" in recs[0]
     assert "gates/g_k_L00" in recs[0] and "vtail/p999_L00" in recs[2] and "telemetry/g_v_mean_all_layers" in recs[0]
+
+
+def test_observability_keys(tmp_path):
+    out = str(tmp_path / "obs")
+    train_main(["--recipe", "tiny", "--synthetic", "--device", "cpu", "--warmup_steps", "2", "--log_every", "100",
+                "--out_dir", out, "--total_steps", "8", "--probe_frac", "0.5", "--val_every", "3", "--val_batches", "1",
+                "--val_exact_K", "16"])
+    recs = _records(out)
+    assert any("probe/loss" in r and "probe/grad_norm" in r for r in recs)
+    assert any("base/loss" in r for r in recs) and all(("probe/loss" in r) != ("base/loss" in r) for r in recs)
+    v = [r for r in recs if "val/loss" in r]
+    assert v and all("val/loss_exact" in r and "val/base_minus_k16" in r and "val/base_K" in r for r in v)
+    # at the deepest rung of the tiny recipe (c = K = 16) the base operator is the exact one
+    assert abs(v[-1]["val/loss_deep"] - v[-1]["val/loss_exact"]) < 1e-5
