@@ -311,6 +311,8 @@ class FaultInjector:
       DMB_FAKE_SPIKE_STEPS="120,121"   multiply the reported gradient norm at these steps by DMB_FAKE_SPIKE_X (1e4)
       DMB_FAKE_STORM="300:340"         the same for a whole range (a wedge)
       DMB_FAKE_NAN_STEPS="77"          report a non-finite loss at these steps
+      DMB_FAKE_RANK_SPIKE="50:1"       at step 50, rank 1 reports its local gradient norm multiplied by the same
+                                       factor to the per-rank outlier check (which then drops that rank)
 
     The injection acts on the values the governors see (and on the skip threshold the optimizer kernel
     receives), never on device memory."""
@@ -323,10 +325,16 @@ class FaultInjector:
         self.factor = float(env.get("DMB_FAKE_SPIKE_X", "1e4"))
         storm = env.get("DMB_FAKE_STORM", "")
         self.storm = tuple(int(x) for x in storm.split(":")) if storm else None
+        rs = env.get("DMB_FAKE_RANK_SPIKE", "")
+        self.rank_spike = tuple(int(x) for x in rs.split(":")) if rs else None
+
+    def rank_factor(self, step, rank):
+        """What `rank` multiplies its reported local norm by at `step` (1.0 = nothing injected)."""
+        return self.factor if self.rank_spike == (step, rank) else 1.0
 
     @property
     def active(self):
-        return bool(self.spikes or self.nans or self.storm)
+        return bool(self.spikes or self.nans or self.storm or self.rank_spike)
 
     def spiked(self, step, trajectory=0):
         """`trajectory` counts the rewinds so far: a storm belongs to the original data order, so the

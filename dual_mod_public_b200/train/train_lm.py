@@ -305,6 +305,7 @@ def run(args):
         if inject.spiked(step, rewind.count) or step in inject.nans:
             thr = 1e-30                                      # the injected spike: every finite norm exceeds this
         tr.opt.skip_norm, tr.opt.max_norm = thr, clip.threshold(is_probe)
+        tr.local_norm_factor = inject.rank_factor(step, rank)
         t0 = time.time()
         do_sam = bool(sam_params) and not is_probe and step % args.sam_every == 0
         if do_sam:

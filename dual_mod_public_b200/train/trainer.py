@@ -67,6 +67,7 @@ class Trainer:
         # per-rank rejection needs every rank's LOCAL norm before anything is reduced: no early buckets then
         self.rank_outlier = (rank_outlier_factor, rank_outlier_max) if rank_outlier_factor > 0 and self.world > 1 else None
         self.group, self.rank_excluded = process_group, 0
+        self.local_norm_factor = 1.0
         self.overlap = (overlap_buckets and optimizer == "fused" and self.opt.use_kernel and self.world > 1
                         and self.rank_outlier is None)
         self._side = torch.cuda.Stream(device=self.device) if self.overlap else None
@@ -182,7 +183,7 @@ class Trainer:
         step through the optimizer's skip predicate (train_hero_wave3d.py:894-920)."""
         from .governors import rank_outlier_mask
         flat = self.opt.grad_buffers().flat if not hasattr(self.opt, "flat_grads") else self.opt.flat_grads
-        mine = flat.norm().float().reshape(1)
+        mine = flat.norm().float().reshape(1) * self.local_norm_factor     # factor != 1: host-side fault injection
         allv = [torch.zeros_like(mine) for _ in range(self.world)]
         dist.all_gather(allv, mine, group=self.group)
         norms = [float(v) for v in torch.cat(allv).tolist()]

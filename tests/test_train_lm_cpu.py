@@ -255,3 +255,38 @@ def test_observability_keys(tmp_path):
     assert v and all("val/loss_exact" in r and "val/base_minus_k16" in r and "val/base_K" in r for r in v)
     # at the deepest rung of the tiny recipe (c = K = 16) the base operator is the exact one
     assert abs(v[-1]["val/loss_deep"] - v[-1]["val/loss_exact"]) < 1e-5
+
+
+def _lm_rank(rank, world, port, out, extra, env):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), **env)
+    train_main(["--recipe", "tiny", "--synthetic", "--device", "cpu", "--warmup_steps", "2", "--log_every", "100",
+                "--probe_frac", "0", "--out_dir", out, "--total_steps", "5", "--lr", "3e-3"] + extra)
+
+
+def _spawn_lm(tmp_path, name, extra, env=None, world=2):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / name)
+    ctx = mp.get_context("spawn")
+    port = 29800 + (os.getpid() % 150) + len(name)
+    procs = [ctx.Process(target=_lm_rank, args=(r, world, port, out, extra, env or {})) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+        assert p.exitcode == 0
+    return _records(out)
+
+
+def test_ranks_drop_a_spiking_rank_and_keep_training(tmp_path):
+    # four ranks: with two, the median of (1, spike) hides the spike
+    recs = _spawn_lm(tmp_path, "rs", ["--rank_outlier_factor", "4"], env={"DMB_FAKE_RANK_SPIKE": "3:1"}, world=4)
+    assert [r["train/rank_excl"] for r in recs] == [0, 0, 0, 1, 0]
+    assert not any(r["train/skipped"] for r in recs) and all(math.isfinite(r["train/loss"]) for r in recs)
+
+
+def test_two_ranks_two_speed_optimizer_and_sam(tmp_path):
+    recs = _spawn_lm(tmp_path, "hy", ["--dm_accum", "2", "--sam", "--sam_every", "2"])
+    assert [r["train/dm_stepped"] for r in recs] == [False, True, False, True, False]
+    assert [r["train/sam_active"] for r in recs] == [1, 0, 1, 0, 1]
+    assert recs[-1]["train/loss"] < recs[0]["train/loss"] + 0.05
