@@ -374,3 +374,63 @@ def test_prefix_read_with_a_gap_between_keys_and_queries(ops, window):
     ops.prefix_dq(qc, Kc, Vc, pos0, scale, window, lse_use, do, corr, dq, qoff=qoff)
     fm.prefix_dq(f(qc), f(Kc), f(Vc), pos0, scale, window, lse_use, f(do), corr, dq_r, qoff)
     close(dq, dq_r, rtol=3e-2, atol=3e-2, what="dq")
+
+
+def test_kernels_write_only_their_rows(ops):
+    """Every output a kernel is handed as a view sits between guard rows filled with a sentinel; after the
+    launch the guards still hold it (bounds of the row arithmetic, batch strides, group offsets)."""
+    B, c, H, dh, g = 2, 64, 4, 64, 64
+    d, T, pos0 = H * dh, 3 * 64, 64
+    scale = dh ** -0.5
+    SENT = 7.0
+
+    def guarded(*tail, dtype=torch.float32):
+        big = torch.full((B, g + c + g) + tail, SENT, dtype=dtype, device=DEV)
+        big[:, g:g + c] = 0
+        return big, big[:, g:g + c]
+
+    def intact(big, what):
+        assert (big[:, :g] == SENT).all() and (big[:, g + c:] == SENT).all(), what
+
+    q, ks, vr, Kc, Vc = _cell_inputs(B, c, H, dh, T)
+    r = slice(pos0, pos0 + c)
+    qc, ksc, vrc = q[:, r], ks[:, r], vr[:, r]
+    K_in, V_in = rnd(B, c, H, dh, seed=9), rnd(B, c, H, dh, seed=10)
+    n0 = ops.launches
+    o_c, lse_c = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, 0)
+    o, lse, ssq = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)
+    # tail backward: five accumulators
+    bigs, views = zip(*[guarded(H, dh), guarded(H, dh), guarded(H, dh), guarded(H, dh), guarded(H)])
+    dO = rnd(B, c, H, dh, dtype=torch.float32, seed=11)
+    ops.tail_bwd(dO, qc, ksc, vrc, K_in, V_in, o_c, lse_c, o.to(torch.bfloat16), lse, scale, 0, *views)
+    for i, b in enumerate(bigs):
+        intact(b, f"tail_bwd acc {i}")
+        assert views[i].abs().max() > 0
+    # committed-prefix backward, query side
+    big, dq = guarded(H, dh)
+    corr = rnd(B, c, H, dtype=torch.float32, seed=4)
+    ops.prefix_dq(qc, Kc, Vc, pos0, scale, 0, lse_c, rnd(B, c, H, dh, seed=3), corr, dq)
+    intact(big, "prefix_dq")
+    # refine forward into tape rows, refine backward into layer accumulators
+    cos, sin = build_rope_cache(T, dh, 10000.0, device=DEV)
+    raw, oo = rnd(B, c, 4 * d, scale=2.0), rnd(B, c, d, scale=1.5, seed=7)
+    ssq2 = oo.float().view(B, c, H, dh).square().sum(-1)
+    glx, k, v = rnd(B, c, 2 * d, seed=1), rnd(B, c, d, seed=2), rnd(B, c, d, seed=3)
+    bK, vK = guarded(H, dh, dtype=torch.bfloat16)
+    bV, vV = guarded(H, dh, dtype=torch.bfloat16)
+    ops.refine_fwd(raw, ssq2, glx, k, v, cos[r], sin[r], H, 0, out=(vK, vV))
+    intact(bK, "refine_fwd K"), intact(bV, "refine_fwd V")
+    assert vK.float().abs().max() > 0
+    acc = [guarded(d), guarded(d), guarded(2 * d), guarded(4 * d, dtype=torch.bfloat16), guarded(d, dtype=torch.bfloat16)]
+    dK, dV = rnd(B, c, H, dh, dtype=torch.float32, seed=4), rnd(B, c, H, dh, dtype=torch.float32, seed=5)
+    ops.refine_bwd(dK, dV, raw, ssq2, oo, glx, k, v, cos[r], sin[r], 0, *[a[1] for a in acc])
+    for i, (b, _) in enumerate(acc):
+        intact(b, f"refine_bwd out {i}")
+    # cell end: per-layer arrays by absolute position
+    arrs = [guarded(H, dh, dtype=torch.bfloat16), guarded(H), guarded(H), guarded(H, dh), guarded(H, dh)]
+    f32 = lambda *s, seed: rnd(*s, dtype=torch.float32, seed=seed)
+    ops.cell_finish(f32(B, c, H, dh, seed=1), f32(B, c, H, seed=2), f32(B, c, H, dh, seed=3), f32(B, c, H, seed=4),
+                    f32(B, c, H, dh, seed=5), f32(B, c, H, dh, seed=6), *[a[1] for a in arrs])
+    for i, (b, _) in enumerate(arrs):
+        intact(b, f"cell_finish out {i}")
+    assert ops.launches - n0 >= 7, "a torch fallback ran instead of a kernel"
