@@ -111,12 +111,39 @@ class _LayerPack:
         # [0 ; 0 ; 0 ; b_g] -- a single GEMM forward, a single dX and a single dW GEMM backward
         self.W_in, self.b_in = mk(n_in, d), torch.zeros(n_in, dtype=dtype, device=device)
         self.wq, self.wk, self.wv = self.W_in[:d], self.W_in[d:2 * d], self.W_in[2 * d:3 * d]
-        self.W_pack = mk(4 * d, d)        # [W_kctx ; W_vctx (mrk: V_map) ; W_gk[:, d:] ; W_gv[:, d:]]
+        # When every operator of the write law is factored (LoRA), the sweeps apply the factors instead of the
+        # composed d x d matrices: one GEMM onto the stacked down factors [sum of ranks, d], then one narrow
+        # GEMM per operator from its rank columns to its d output columns.  2 (r_k + r_v + 2 r_g) / 4d of the
+        # dense FLOPs, in the forward, the input gradient and the deferred weight gradients alike.
+        a = blk.attn
+        second = a.v_map if family == "mrk" else a.w_vctx
+        ops4 = (a.w_kctx, second, a.w_gk, a.w_gv)
+        self.factored = (all(isinstance(m, LoRALinear) for m in ops4[:2]) and all(isinstance(m, LoRAGate) for m in ops4[2:])
+                         and (family != "mrk" or isinstance(a.w_vctx, LoRALinear))
+                         and os.environ.get("DMB_DENSE_WRITE_LAW", "0") != "1")
+        if self.factored:
+            self.ranks = [a.w_kctx.down.weight.shape[0], second.down.weight.shape[0],
+                          a.w_gk.a.weight.shape[0], a.w_gv.a.weight.shape[0]]
+            self.factored = all(r % 8 == 0 for r in self.ranks) and (
+                family != "mrk" or a.w_vctx.down.weight.shape[0] % 8 == 0)
+        if self.factored:
+            self.roff = [0]
+            for r_ in self.ranks:
+                self.roff.append(self.roff[-1] + r_)
+            self.D_all = mk(self.roff[-1], d)                 # stacked down factors, context-norm gain folded in
+            self.U = [mk(d, r_) for r_ in self.ranks]         # up factors
+            self.W_pack = None
+        else:
+            self.W_pack = mk(4 * d, d)    # [W_kctx ; W_vctx (mrk: V_map) ; W_gk[:, d:] ; W_gv[:, d:]]
         self.W_gx = self.W_in[3 * d:5 * d]    # [W_gk[:, :d] ; W_gv[:, :d]]
         self.b_g = self.b_in[3 * d:5 * d]
         if family == "mrk":
             self.W_vgate, self.b_vgate = self.W_in[5 * d:], self.b_in[5 * d:]
-            self.W_vctx = mk(d, d)
+            if self.factored:
+                rv = a.w_vctx.down.weight.shape[0]
+                self.Dv, self.Uv, self.W_vctx = mk(rv, d), mk(d, rv), None
+            else:
+                self.W_vctx = mk(d, d)
             self.k_gain = torch.ones(cfg.n_heads, dtype=torch.float32, device=device)
 
     @torch.no_grad()
@@ -138,17 +165,27 @@ class _LayerPack:
         # the context-norm gain is folded into the packed weight's columns: the sweeps feed the
         # GEMM with the un-normalised read and apply 1/rms afterwards, row by row
         wc = a.norm_ctx.weight.float()[None, :]
-        self.W_pack[:d].copy_(a.w_kctx.weight.float() * wc)
+        second = a.v_map if self.family == "mrk" else a.w_vctx
+        if self.factored:
+            downs = (a.w_kctx.down.weight, second.down.weight, a.w_gk.a.weight[:, d:], a.w_gv.a.weight[:, d:])
+            ups = (a.w_kctx.up.weight, second.up.weight, a.w_gk.b.weight, a.w_gv.b.weight)
+            for i, (dn, up) in enumerate(zip(downs, ups)):
+                self.D_all[self.roff[i]:self.roff[i + 1]].copy_(dn.float() * wc)
+                self.U[i].copy_(up)
+        else:
+            self.W_pack[:d].copy_(a.w_kctx.weight.float() * wc)
+            self.W_pack[d:2 * d].copy_(second.weight.float() * wc)
+            self.W_pack[2 * d:3 * d].copy_(gk[:, d:].float() * wc)
+            self.W_pack[3 * d:].copy_(gv[:, d:].float() * wc)
         if self.family == "mrk":
-            self.W_pack[d:2 * d].copy_(a.v_map.weight.float() * wc)
-            self.W_vctx.copy_(a.w_vctx.weight)
+            if self.factored:
+                self.Dv.copy_(a.w_vctx.down.weight)
+                self.Uv.copy_(a.w_vctx.up.weight)
+            else:
+                self.W_vctx.copy_(a.w_vctx.weight)
             self.W_vgate.copy_(a.v_gate.weight)
             self.b_vgate.copy_(a.v_gate.bias)
             self.k_gain.copy_(a.k_gain)
-        else:
-            self.W_pack[d:2 * d].copy_(a.w_vctx.weight.float() * wc)
-        self.W_pack[2 * d:3 * d].copy_(gk[:, d:].float() * wc)
-        self.W_pack[3 * d:].copy_(gv[:, d:].float() * wc)
         self.W_gx[:d].copy_(gk[:, :d])
         self.W_gx[d:].copy_(gv[:, :d])
         self.b_g[:d].copy_(a.w_gk.bias)
@@ -223,14 +260,27 @@ class WaveScanEngine:
             self.emb_c = z(cfg.vocab_size, d)
             self.w_f = z(d)
             self.head_w = None if cfg.tie_embeddings else z(cfg.vocab_size, d)
-            self.dW_pack = z(4 * d, d, dt=torch.float32)
+            P0 = self.packs[0]
+            self.factored = self.packed_refine and P0.factored
             self.dW_in = z(6 * d, d, dt=torch.float32)
             self.dW_gx = self.dW_in[3 * d:5 * d]
+            if self.factored:
+                # gradients of the factors: the up factors and the (folded) stacked down factors
+                self.dU = [z(d, r_, dt=torch.float32) for r_ in P0.ranks]
+                self.dD_all = z(P0.roff[-1], d, dt=torch.float32)
+                self.dW_pack = None
+            elif self.packed_refine:
+                self.dW_pack = z(4 * d, d, dt=torch.float32)
             if refine_family(cfg) == "mrk":
-                self.dW_vctx = z(d, d, dt=torch.float32)
+                if self.factored:
+                    rv = P0.Dv.shape[0]
+                    self.dUv, self.dDv, self.dW_vctx = z(d, rv, dt=torch.float32), z(rv, d, dt=torch.float32), None
+                else:
+                    self.dW_vctx = z(d, d, dt=torch.float32)
                 self.dkgain_acc = z(cfg.n_heads, dt=torch.float32)
                 self.dwctx_acc = z(d, dt=torch.float32)
                 self._stash2 = {}
+            self._stash_fac = {}
             # committed-prefix partials of every cell, kept from the forward so the backward
             # does not redo the prefix pass: per schedule, [L][n_cells] dense slots
             self._prefix_saved = {}
@@ -512,6 +562,38 @@ class WaveScanEngine:
             self._sweep_saved[(sid, li)] = kept
 
     # ---- the write law of one sweep -------------------------------------------------------------------
+    # ---- the write law's two linear maps, dense or factored -----------------------------------------
+    def _pack_linear(self, P, o2):
+        """[k_ctx | v_ctx (mrk: v_map) | gate-k u-logits | gate-v u-logits] of the un-normalised read o2
+        [B, c, d] -> [B, c, 4d]."""
+        ops = self.ops
+        if not P.factored:
+            return ops.linear(o2, P.W_pack)
+        B, c, d = o2.shape
+        t = ops.linear(o2, P.D_all).view(B * c, -1)
+        raw = torch.empty(B, c, 4 * d, dtype=o2.dtype, device=o2.device)
+        raw2 = raw.view(B * c, 4 * d)
+        for i, U in enumerate(P.U):
+            ops.linear(t[:, P.roff[i]:P.roff[i + 1]], U, out=raw2[:, i * d:(i + 1) * d])
+        return raw
+
+    def _pack_linear_dx(self, P, dcg, dt_out=None):
+        """d (normalised read) [B, c, d] from d (packed logits) [B, c, 4d]; factored: also leaves
+        d (down outputs) [rows, sum of ranks] in `dt_out` for the deferred gradient of the down factors."""
+        ops = self.ops
+        if not P.factored:
+            return ops.linear_dx(dcg, P.W_pack)
+        B, c, d4 = dcg.shape
+        d = d4 // 4
+        dcg2 = dcg.view(B * c, d4)
+        dt = dt_out if dt_out is not None else torch.empty(B * c, P.roff[-1], dtype=dcg.dtype, device=dcg.device)
+        for i, U in enumerate(P.U):
+            ops.linear_dx(dcg2[:, i * d:(i + 1) * d], U, out=dt[:, P.roff[i]:P.roff[i + 1]])
+        return ops.linear_dx(dt, P.D_all).view(B, c, d)
+
+    def _vctx_linear(self, P, vin):
+        return self.ops.linear(vin, P.W_vctx) if not P.factored else self.ops.linear(self.ops.linear(vin, P.Dv), P.Uv)
+
     def _refine_fwd(self, S, r, o, ssq, out=None):
         """(k'', v'') rows [B, c, h, dh] from the read `o` of the rows `r` (key rotated), written into `out`
         when given.  Also returns what the backward wants besides (o, ssq): the packed ctx / gate logits
@@ -520,15 +602,15 @@ class WaveScanEngine:
         B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
         c = o.shape[1]
         if self.family == "packed":
-            raw = ops.linear(o.reshape(B, c, d), S.P.W_pack)
+            raw = self._pack_linear(S.P, o.reshape(B, c, d))
             K_new, V_new = ops.refine_fwd(raw, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h, S.pin,
                                           out=out)
             return K_new, V_new, raw
         if self.family == "mrk":
             o2 = o.reshape(B, c, d)
-            raw = ops.linear(o2, S.P.W_pack)
+            raw = self._pack_linear(S.P, o2)
             vin = ops.mrk_vin_fwd(raw, ssq, o2, S.P.w_ctx, S.vgx[:, r], cfg.mult_res_lambda)
-            vc = ops.linear(vin, S.P.W_vctx)
+            vc = self._vctx_linear(S.P, vin)
             K_new, V_new = ops.mrk_refine_fwd(raw, vc, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h,
                                               S.pin, S.P.k_gain, cfg.v_clamp_tau, out=out)
             return K_new, V_new, (raw, vc)
@@ -560,18 +642,31 @@ class WaveScanEngine:
                                S.pin, P.k_gain, cfg.v_clamp_tau, S.dk[:, r], S.dv[:, r], S.dglx[:, r], dcg,
                                S.u_stash[rows].view(B, c, d), dvc, S.dkg_stash[rows].view(B, c, h))
             dvin = S.dvin_stash[rows].view(B, c, d)
-            dvin.copy_(ops.linear_dx(dvc, P.W_vctx))
             # v_in again (cheap) for the deferred W_vctx gradient: one GEMM per layer over all sweeps' rows
-            S.vin_stash[rows].view(B, c, d).copy_(ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam))
+            vin = S.vin_stash[rows]
+            vin.view(B, c, d).copy_(ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam))
+            if P.factored:
+                # stashes of the factored deferred gradients: down outputs and their gradients
+                ops.linear(vin, P.Dv, out=S.tv_stash[rows])
+                ops.linear_dx(dvc.view(n, d), P.Uv, out=S.dtv_stash[rows])
+                ops.linear_dx(S.dtv_stash[rows], P.Dv, out=dvin.view(n, d))
+            else:
+                dvin.copy_(ops.linear_dx(dvc, P.W_vctx))
             du_hat = ops.mrk_vin_bwd(dvin, raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam, dcg, S.dvgx[:, r])
-            return ops.rmsn_bwd(ops.linear_dx(dcg, P.W_pack), o2, ssq, residual=residual, extra=du_hat)
+            du = self._pack_linear_dx(P, dcg, S.dt_stash[rows] if P.factored else None)
+            if P.factored:
+                ops.linear(S.u_stash[rows], P.D_all, out=S.t_stash[rows])
+            return ops.rmsn_bwd(du, o2, ssq, residual=residual, extra=du_hat)
         if self.family == "packed":
             n = B * c
             dcg = S.dcg_stash[stash_row:stash_row + n].view(B, c, 4 * d)
             ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), S.glx[:, r], S.k[:, r], S.v[:, r],
                            S.cos[r], S.sin[r], S.pin, S.dk[:, r], S.dv[:, r], S.dglx[:, r], dcg,
                            S.u_stash[stash_row:stash_row + n].view(B, c, d))
-            du = ops.linear_dx(dcg, S.P.W_pack)
+            rows = slice(stash_row, stash_row + n)
+            du = self._pack_linear_dx(S.P, dcg, S.dt_stash[rows] if S.P.factored else None)
+            if S.P.factored:
+                ops.linear(S.u_stash[rows], S.P.D_all, out=S.t_stash[rows])
             return ops.rmsn_bwd(du, o.reshape(B, c, d), ssq, residual=residual)
         from ..models.rope import apply_rope
         sh = S.P.shadow
@@ -633,6 +728,16 @@ class WaveScanEngine:
             d, z = self.cfg.d_model, lambda w, dt: torch.zeros(n, w, dtype=dt, device=self.device)
             self._stash2[sid] = (z(d, self.act), z(d, self.act), z(d, self.act), z(self.cfg.n_heads, torch.float32))
         return self._stash2[sid]
+
+    def _stash_fac_for(self, sid):
+        """Factored write law: (down outputs of the normalised read, their gradients) [rows, sum of ranks] and,
+        in the mult_res family, the same pair for the W_vctx factors [rows, rank] of every sweep of a layer."""
+        if sid not in self._stash_fac:
+            n, P = self._stash_for(sid)[0].shape[0], self.packs[0]
+            z = lambda w: torch.zeros(n, w, dtype=self.act, device=self.device)
+            rv = P.Dv.shape[0] if self.family == "mrk" else 0
+            self._stash_fac[sid] = (z(P.roff[-1]), z(P.roff[-1]), z(rv) if rv else None, z(rv) if rv else None)
+        return self._stash_fac[sid]
 
     def _head_weight(self):
         return self.emb_c if self.head_w is None else self.head_w
@@ -729,24 +834,39 @@ class WaveScanEngine:
             dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev) if packed else None
             dxhat_acc = None if packed else torch.zeros(B, T, d, dtype=f32, device=dev)
             dv4 = dv.view(B, T, h, dh)
-            if packed:
-                self.dW_pack.zero_()
-            else:
+            if not packed:
                 for acc in P.shadow_gacc:
                     acc.zero_()
+            elif self.factored:
+                for t_ in self.dU + [self.dD_all]:
+                    t_.zero_()
+            else:
+                self.dW_pack.zero_()
             S = SimpleNamespace(P=P, q_r=q_r, kself_r=kself_r, v4=v4, k=k, v=v, glx=glx, Kc=Kc, Vc=Vc,
                                 cos=cos, sin=sin, scale=scale, pin=pin, dO_all=dO_all, dq_r=dq_r, dks_r=dks_r,
                                 dk=dk, dv=dv, dglx=dglx, dv4=dv4, xhat=xhat, dxhat_acc=dxhat_acc, vgx=vgx)
             if mrk:
                 S.dvgx = torch.zeros(B, T, d, dtype=f32, device=dev)
                 S.dvc_stash, S.vin_stash, S.dvin_stash, S.dkg_stash = self._stash2_for(sid)
-                for t_ in (self.dW_vctx, self.dkgain_acc, self.dwctx_acc):
+                for t_ in ((self.dUv, self.dDv) if self.factored else (self.dW_vctx,)) + (self.dkgain_acc, self.dwctx_acc):
                     t_.zero_()
+            if self.factored:
+                S.t_stash, S.dt_stash, S.tv_stash, S.dtv_stash = self._stash_fac_for(sid)
             dcg_stash, u_stash = self._cells_bwd(li, sid, S, kept)
             if packed:
-                ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
+                if self.factored:
+                    # d U_i = d(logits_i)^T (down output_i);  d D' = d(down outputs)^T (normalised read)
+                    for i, dU in enumerate(self.dU):
+                        ops.linear_dw_acc(dU, dcg_stash[:, i * d:(i + 1) * d], S.t_stash[:, P.roff[i]:P.roff[i + 1]])
+                    ops.linear_dw_acc(self.dD_all, S.dt_stash, u_stash)
+                else:
+                    ops.linear_dw_acc(self.dW_pack, dcg_stash, u_stash)
                 if mrk:
-                    ops.linear_dw_acc(self.dW_vctx, S.dvc_stash, S.vin_stash)
+                    if self.factored:
+                        ops.linear_dw_acc(self.dUv, S.dvc_stash, S.tv_stash)
+                        ops.linear_dw_acc(self.dDv, S.dtv_stash, S.vin_stash)
+                    else:
+                        ops.linear_dw_acc(self.dW_vctx, S.dvc_stash, S.vin_stash)
                     # u enters v_in directly as well: d w_ctx += lam * sum_rows(d v_in * uhat); k_gain: sum of the rows
                     ops.col_dot_acc(self.dwctx_acc, S.dvin_stash, u_stash)
                     self.dwctx_acc.mul_(cfg.mult_res_lambda)
@@ -861,12 +981,19 @@ class WaveScanEngine:
         """dW_pack holds the gradient of the FOLDED weight W' = W * w_ctx (per column).  Recover
         d w_ctx = sum_rows dW' * W and dW = dW' * w_ctx."""
         d = self.cfg.d_model
-        gk, gv = _dense(a.w_gk), _dense(a.w_gv)
         second = a.v_map if self.family == "mrk" else a.w_vctx
-        W = torch.cat((a.w_kctx.weight, second.weight, gk[:, d:], gv[:, d:]), dim=0).float()
-        self.grads.get(a.norm_ctx.weight).add_((self.dW_pack * W).sum(0))
         if self.family == "mrk":
             self.grads.get(a.norm_ctx.weight).add_(self.dwctx_acc)      # u also enters v_in directly
+        if self.factored:
+            # the same for the folded down factors D' = D * w_ctx
+            D = torch.cat((a.w_kctx.down.weight, second.down.weight, a.w_gk.a.weight[:, d:], a.w_gv.a.weight[:, d:]),
+                          dim=0).float()
+            self.grads.get(a.norm_ctx.weight).add_((self.dD_all * D).sum(0))
+            self.dD_all.mul_(a.norm_ctx.weight.float()[None, :])
+            return
+        gk, gv = _dense(a.w_gk), _dense(a.w_gv)
+        W = torch.cat((a.w_kctx.weight, second.weight, gk[:, d:], gv[:, d:]), dim=0).float()
+        self.grads.get(a.norm_ctx.weight).add_((self.dW_pack * W).sum(0))
         self.dW_pack.mul_(a.norm_ctx.weight.float()[None, :])
 
     def _scatter_packed_grads(self, a, db_g):
@@ -874,6 +1001,21 @@ class WaveScanEngine:
         G, d = self.grads, self.cfg.d_model
         dWp, dWx = self.dW_pack, self.dW_gx
         second = a.v_map if self.family == "mrk" else a.w_vctx
+        if self.factored:
+            ro, dD = self.packs[0].roff, self.dD_all
+            for i, mod in enumerate((a.w_kctx, second)):
+                G.get(mod.up.weight).add_(self.dU[i])
+                G.get(mod.down.weight).add_(dD[ro[i]:ro[i + 1]])
+            for i, mod, rx in ((2, a.w_gk, slice(0, d)), (3, a.w_gv, slice(d, 2 * d))):
+                # gate logits = b (a_x x + a_u u) + bias: the u half went through the factors, the x half
+                # through the composed matrix of the layer's input projection
+                a_w, b_w = mod.a.weight.float(), mod.b.weight.float()
+                G.get(mod.b.weight).add_(self.dU[i] + dWx[rx] @ a_w[:, :d].t())
+                ga = G.get(mod.a.weight)
+                ga[:, :d].add_(b_w.t() @ dWx[rx])
+                ga[:, d:].add_(dD[ro[i]:ro[i + 1]])
+                G.get(mod.b.bias).add_(db_g[rx])
+            return
         for mod, rows in ((a.w_kctx, slice(0, d)), (second, slice(d, 2 * d))):
             self._add_linear_grad(mod, dWp[rows])
         for mod, ru, rx, rb in ((a.w_gk, slice(2 * d, 3 * d), slice(0, d), slice(0, d)),
@@ -904,7 +1046,11 @@ class WaveScanEngine:
         """Weights only the mult_res family has: W_vctx (deferred GEMM), the gate of the multiplicative branch
         (rows 5d:6d of the input projection's gradient, bias = column sums of its logits' gradient), k_gain."""
         d = self.cfg.d_model
-        self._add_linear_grad(a.w_vctx, self.dW_vctx)
+        if self.factored:
+            self.grads.get(a.w_vctx.up.weight).add_(self.dUv)
+            self.grads.get(a.w_vctx.down.weight).add_(self.dDv)
+        else:
+            self._add_linear_grad(a.w_vctx, self.dW_vctx)
         db = torch.zeros(d, dtype=torch.float32, device=self.device)
         self.ops.col_sum_acc(db, dvgx)
         self._add_linear_grad(a.v_gate, self.dW_in[5 * d:6 * d], db)

@@ -123,18 +123,19 @@ class CudaOps(TorchOps):
         return buf
 
     # ---- GEMMs -------------------------------------------------------------------------------
-    def linear(self, x, w, bias=None, out_dtype=None):
-        if self.gemm is not None and self.gemm.ok_tn(x, w) and (bias is None or bias.dtype == BF16):
-            y = self.gemm.linear(x, w, out_dtype or x.dtype, bias=bias)
+    def linear(self, x, w, bias=None, out_dtype=None, out=None):
+        if (self.gemm is not None and self.gemm.ok_tn(x, w) and (bias is None or bias.dtype == BF16)
+                and (out is None or self.gemm.ok_out(out, x, w.shape[0]))):
+            y = self.gemm.linear(x, w, out_dtype or x.dtype, bias=bias, out=out)
             self.launches += 1
             return y
-        return super().linear(x, w, bias, out_dtype)
+        return super().linear(x, w, bias, out_dtype, out)
 
-    def linear_dx(self, dy, w):
-        if self.gemm is not None and self.gemm.ok_nn(dy, w):
+    def linear_dx(self, dy, w, out=None):
+        if self.gemm is not None and self.gemm.ok_nn(dy, w) and (out is None or self.gemm.ok_out(out, dy, w.shape[1])):
             self.launches += 1
-            return self.gemm.linear_dx(dy, w)
-        return super().linear_dx(dy, w)
+            return self.gemm.linear_dx(dy, w, out=out)
+        return super().linear_dx(dy, w, out)
 
     def linear_dw_acc(self, dW, dy, x):
         if self.gemm is not None and self.gemm.ok_tn_dw(dW, dy, x):

@@ -72,9 +72,20 @@ class Tcgen05Gemm:
         return (K == w.shape[1] and N % 8 == 0 and K % 8 == 0 and _aligned(x, lda) and _aligned(w, K)
                 and M * N * K >= self.MIN_WORK)
 
-    def linear(self, x, w, out_dtype=BF16, bias=None):
+    def ok_out(self, out, x, N):
+        """`out`: a 2-D [rows, N] view with a dense last dim (bf16 or fp32), e.g. a column block of a wider
+        matrix; its row stride becomes the kernel's ldc."""
+        r = _rows(x)
+        return (out.dim() == 2 and out.stride(1) == 1 and out.dtype in (BF16, F32) and r is not None
+                and out.shape == (r[0], N) and out.data_ptr() % 16 == 0
+                and out.stride(0) % (8 if out.dtype == BF16 else 4) == 0)
+
+    def linear(self, x, w, out_dtype=BF16, bias=None, out=None):
         M, K, lda = _rows(x)
         N = w.shape[0]
+        if out is not None:
+            self._call(x, w, out, bias, M, N, K, lda, K, out.stride(0), 0, 0, int(out.dtype == F32), 0)
+            return out
         y = torch.empty(*x.shape[:-1], N, dtype=out_dtype, device=x.device)
         self._call(x, w, y, bias, M, N, K, lda, K, N, 0, 0, int(out_dtype == F32), 0)
         return y
@@ -90,9 +101,12 @@ class Tcgen05Gemm:
         return (Kd == w.shape[0] and w.shape[1] % 8 == 0 and Kd % 8 == 0 and _aligned(dy, lda)
                 and _aligned(w, w.shape[1]) and M * Kd * w.shape[1] >= self.MIN_WORK)
 
-    def linear_dx(self, dy, w):
+    def linear_dx(self, dy, w, out=None):
         M, Kd, lda = _rows(dy)
         N = w.shape[1]
+        if out is not None:
+            self._call(dy, w, out, None, M, N, Kd, lda, N, out.stride(0), 0, 1, int(out.dtype == F32), 0)
+            return out
         dx = torch.empty(*dy.shape[:-1], N, dtype=BF16, device=dy.device)
         self._call(dy, w, dx, None, M, N, Kd, lda, N, N, 0, 1, 0, 0)
         return dx

@@ -14,15 +14,22 @@ class TorchOps:
     launches = 0                      # custom-kernel launch counter (0 here by construction)
 
     # ---- GEMMs ------------------------------------------------------------------
-    def linear(self, x, w, bias=None, out_dtype=None):
-        """x [..., k] @ w[n, k]^T (+ bias)."""
+    def linear(self, x, w, bias=None, out_dtype=None, out=None):
+        """x [..., k] @ w[n, k]^T (+ bias).  `out`: a [rows, n] view (dense last dim, any row stride, e.g. a
+        column block of a wider matrix) to write into instead of a fresh tensor."""
         y = x @ w.t()
         if bias is not None:
             y = y + bias.to(y.dtype)
+        if out is not None:
+            out.copy_(y.reshape(out.shape))
+            return out
         return y if out_dtype is None else y.to(out_dtype)
 
-    def linear_dx(self, dy, w):
-        """dy [..., n] @ w[n, k] -> [..., k]"""
+    def linear_dx(self, dy, w, out=None):
+        """dy [..., n] @ w[n, k] -> [..., k] (`out` as for `linear`)"""
+        if out is not None:
+            out.copy_((dy @ w).reshape(out.shape))
+            return out
         return dy @ w
 
     def linear_dw_acc(self, dW, dy, x):

@@ -278,3 +278,31 @@ def test_schedule_pool_covers_sequence():
     for sched in pool:
         assert sum(c for _, c, _ in sched) == 100
         assert all(1 <= k <= c for _, c, k in sched)
+
+
+@pytest.mark.parametrize("kw", [dict(gate_rank=8, ctx_rank=8),
+                                dict(ctx_mod="mult_res", gate_rank=8, ctx_rank=16, k_ctx_norm="rms", kmod_vraw_heads=1,
+                                     v_clamp_tau=0.8)])
+def test_factored_write_law_equals_composed_matrices(kw, monkeypatch):
+    """With every operator of the write law factored, the sweeps apply the factors (down GEMM onto the
+    stacked ranks, one narrow up GEMM per operator) and accumulate the factors' gradients directly; the
+    result equals the path through the composed d x d matrices and autograd through the same forward."""
+    cfg, m = build(**kw)
+    B, T = 2, 32
+    g = torch.Generator().manual_seed(6)
+    idx = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    sched = uniform_chunks(T, 8, 3)
+    e_f = WaveScanEngine(m, [sched], B, T, backend="fused", ops=TorchOps())
+    assert e_f.factored and e_f.packs[0].W_pack is None
+    lf, gf = _engine_grads(m, e_f, idx, tgt)
+    monkeypatch.setenv("DMB_DENSE_WRITE_LAW", "1")
+    e_d = WaveScanEngine(m, [sched], B, T, backend="fused", ops=TorchOps())
+    assert not e_d.factored and e_d.packs[0].W_pack is not None
+    ld, gd = _engine_grads(m, e_d, idx, tgt)
+    e_g = WaveScanEngine(m, [sched], B, T, backend="generic", ops=TorchOps())
+    lg, gg = _engine_grads(m, e_g, idx, tgt)
+    assert abs(lf.item() - ld.item()) < 1e-5 and abs(lf.item() - lg.item()) < 1e-5
+    for n in gg:
+        assert relerr(gf[n], gd[n]) < 1e-4, n
+        assert relerr(gf[n], gg[n]) < 1e-4, n

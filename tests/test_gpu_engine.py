@@ -43,7 +43,7 @@ def grads_of(eng, model, idx, tgt):
 
 
 @pytest.mark.parametrize("kw,c,K", [(dict(), 64, 4), (dict(kmod_vraw_heads=1), 32, 32), (dict(local_window=100), 64, 2),
-                                    (MRK, 64, 3)])
+                                    (MRK, 64, 3), (dict(gate_rank=16, ctx_rank=24), 64, 3)])
 def test_kernel_engine_matches_fp32_torch_engine(kw, c, K):
     cfg, m = build(**kw)
     B, T = 4, 256

@@ -71,3 +71,44 @@ def test_strided_rows(gemm):
     xs = big.view(-1, 1024)[:, :512]                 # row stride 1024, 512 wide
     y = gemm.linear(xs, w)
     check(y, xs.float() @ w.float().t(), "strided x")
+
+
+@pytest.mark.parametrize("rows,d,R", [(4096, 2304, 144), (512, 256, 16), (1000, 1024, 72)])
+def test_factor_gemms_into_column_blocks(gemm, rows, d, R):
+    """The shapes of a factored write law: a down GEMM onto 4R stacked rank columns, narrow up GEMMs from a
+    rank-column block of one matrix into a d-column block of another (`out=` views with their own row
+    strides), the transposed pair for the input gradient, and the weight gradients of both factors."""
+    x = rnd(rows, d)
+    D = rnd(4 * R, d, seed=1) * 0.05
+    U = [rnd(d, R, seed=2 + i) * 0.05 for i in range(4)]
+    assert gemm.ok_tn(x, D)
+    t = gemm.linear(x, D)
+    check(t, x.float() @ D.float().t(), "down")
+    raw = torch.full((rows, 4 * d), 7.0, dtype=torch.bfloat16, device=DEV)
+    for i in (0, 2, 3):                                       # block 1 stays untouched
+        ti, oi = t[:, i * R:(i + 1) * R], raw[:, i * d:(i + 1) * d]
+        assert gemm.ok_tn(ti, U[i]) and gemm.ok_out(oi, ti, d)
+        gemm.linear(ti, U[i], out=oi)
+        check(oi, ti.float() @ U[i].float().t(), f"up {i}")
+    assert (raw[:, d:2 * d] == 7.0).all()
+    dcg = rnd(rows, 4 * d, seed=9)
+    dt = torch.full((rows, 4 * R), 7.0, dtype=torch.bfloat16, device=DEV)
+    for i in (0, 1, 3):
+        gi, oi = dcg[:, i * d:(i + 1) * d], dt[:, i * R:(i + 1) * R]
+        assert gemm.ok_nn(gi, U[i]) and gemm.ok_out(oi, gi, R)
+        gemm.linear_dx(gi, U[i], out=oi)
+        check(oi, gi.float() @ U[i].float(), f"d down-out {i}")
+    assert (dt[:, 2 * R:3 * R] == 7.0).all()
+    dt[:, 2 * R:3 * R] = 0
+    du = gemm.linear_dx(dt, D)
+    check(du, dt.float() @ D.float(), "d read")
+    dU = torch.ones(d, R, device=DEV)
+    gi, ti = dcg[:, d:2 * d], t[:, R:2 * R]
+    assert gemm.ok_tn_dw(dU, gi, ti)
+    gemm.linear_dw_acc(dU, gi, ti)
+    check(dU, 1 + gi.float().t() @ ti.float(), "dU")
+    dD = torch.ones(4 * R, d, device=DEV)
+    assert gemm.ok_tn_dw(dD, dt, x)
+    gemm.linear_dw_acc(dD, dt, x)
+    check(dD, 1 + dt.float().t() @ x.float(), "dD")
+    gemm.check()
