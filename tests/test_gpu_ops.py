@@ -377,12 +377,14 @@ def test_prefix_read_with_a_gap_between_keys_and_queries(ops, window):
 
 
 def test_kernels_write_only_their_rows(ops):
-    """Every output a kernel is handed as a view sits between guard rows filled with a sentinel; after the
-    launch the guards still hold it (bounds of the row arithmetic, batch strides, group offsets)."""
+    """Every output a kernel accepts as a strided view (rows of a per-layer array or of the tape) sits between
+    guard rows filled with a sentinel; after the launch the guards still hold it (bounds of the row
+    arithmetic, batch strides)."""
     B, c, H, dh, g = 2, 64, 4, 64, 64
     d, T, pos0 = H * dh, 3 * 64, 64
     scale = dh ** -0.5
     SENT = 7.0
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
 
     def guarded(*tail, dtype=torch.float32):
         big = torch.full((B, g + c + g) + tail, SENT, dtype=dtype, device=DEV)
@@ -399,18 +401,13 @@ def test_kernels_write_only_their_rows(ops):
     n0 = ops.launches
     o_c, lse_c = ops.prefix_fwd(qc, Kc, Vc, pos0, scale, 0)
     o, lse, ssq = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)
-    # tail backward: five accumulators
-    bigs, views = zip(*[guarded(H, dh), guarded(H, dh), guarded(H, dh), guarded(H, dh), guarded(H)])
+    # tail backward: the raw-row accumulators are rows of per-layer arrays
+    (b_ks, v_ks), (b_v, v_v) = guarded(H, dh), guarded(H, dh)
     dO = rnd(B, c, H, dh, dtype=torch.float32, seed=11)
-    ops.tail_bwd(dO, qc, ksc, vrc, K_in, V_in, o_c, lse_c, o.to(torch.bfloat16), lse, scale, 0, *views)
-    for i, b in enumerate(bigs):
-        intact(b, f"tail_bwd acc {i}")
-        assert views[i].abs().max() > 0
-    # committed-prefix backward, query side
-    big, dq = guarded(H, dh)
-    corr = rnd(B, c, H, dtype=torch.float32, seed=4)
-    ops.prefix_dq(qc, Kc, Vc, pos0, scale, 0, lse_c, rnd(B, c, H, dh, seed=3), corr, dq)
-    intact(big, "prefix_dq")
+    ops.tail_bwd(dO, qc, ksc, vrc, K_in, V_in, o_c, lse_c, o.to(torch.bfloat16), lse, scale, 0,
+                 z(B, c, H, dh), v_ks, v_v, z(B, c, H, dh), z(B, c, H))
+    intact(b_ks, "tail_bwd dks"), intact(b_v, "tail_bwd dv")
+    assert v_ks.abs().max() > 0 and v_v.abs().max() > 0
     # refine forward into tape rows, refine backward into layer accumulators
     cos, sin = build_rope_cache(T, dh, 10000.0, device=DEV)
     raw, oo = rnd(B, c, 4 * d, scale=2.0), rnd(B, c, d, scale=1.5, seed=7)
@@ -421,11 +418,12 @@ def test_kernels_write_only_their_rows(ops):
     ops.refine_fwd(raw, ssq2, glx, k, v, cos[r], sin[r], H, 0, out=(vK, vV))
     intact(bK, "refine_fwd K"), intact(bV, "refine_fwd V")
     assert vK.float().abs().max() > 0
-    acc = [guarded(d), guarded(d), guarded(2 * d), guarded(4 * d, dtype=torch.bfloat16), guarded(d, dtype=torch.bfloat16)]
+    acc = [guarded(d), guarded(d), guarded(2 * d)]
     dK, dV = rnd(B, c, H, dh, dtype=torch.float32, seed=4), rnd(B, c, H, dh, dtype=torch.float32, seed=5)
-    ops.refine_bwd(dK, dV, raw, ssq2, oo, glx, k, v, cos[r], sin[r], 0, *[a[1] for a in acc])
+    ops.refine_bwd(dK, dV, raw, ssq2, oo, glx, k, v, cos[r], sin[r], 0, *[a[1] for a in acc],
+                   z(B, c, 4 * d, dt=torch.bfloat16), z(B, c, d, dt=torch.bfloat16))
     for i, (b, _) in enumerate(acc):
-        intact(b, f"refine_bwd out {i}")
+        intact(b, f"refine_bwd acc {i}")
     # cell end: per-layer arrays by absolute position
     arrs = [guarded(H, dh, dtype=torch.bfloat16), guarded(H), guarded(H), guarded(H, dh), guarded(H, dh)]
     f32 = lambda *s, seed: rnd(*s, dtype=torch.float32, seed=seed)
@@ -433,4 +431,4 @@ def test_kernels_write_only_their_rows(ops):
                     f32(B, c, H, dh, seed=5), f32(B, c, H, dh, seed=6), *[a[1] for a in arrs])
     for i, (b, _) in enumerate(arrs):
         intact(b, f"cell_finish out {i}")
-    assert ops.launches - n0 >= 7, "a torch fallback ran instead of a kernel"
+    assert ops.launches - n0 == 6, "a torch fallback ran instead of a kernel"
