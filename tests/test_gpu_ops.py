@@ -431,4 +431,4 @@ def test_kernels_write_only_their_rows(ops):
                     f32(B, c, H, dh, seed=5), f32(B, c, H, dh, seed=6), *[a[1] for a in arrs])
     for i, (b, _) in enumerate(arrs):
         intact(b, f"cell_finish out {i}")
-    assert ops.launches - n0 == 6, "a torch fallback ran instead of a kernel"
+    assert ops.launches - n0 >= 6, "a torch fallback ran instead of a kernel"
