@@ -25,6 +25,7 @@ import numpy as np
 import torch
 
 from . import harness as H
+from . import tasks as T
 from .tasks import step_rng
 
 
@@ -59,6 +60,20 @@ def parse(argv=None):
     a("--snap_interval", type=int, default=0)
     a("--engine", choices=["eager", "wavescan"], default="eager")
     a("--ws_chunk", type=int, default=16)
+    a("--no_fused", action="store_true", help="engine path: whole cells under autograd instead of the kernel table")
+    a("--tag", default=None, help="run tag (default: built from the task options)")
+    a("--eval_bsz", type=int, default=0, help="alias of --eval_rows")
+    a("--no_kmod", action="store_true", help="alias of --no_key_mod")
+    a("--attn_logn_ref", type=int, default=0, help="alias of --logn_ref")
+    # warm starts
+    a("--newkey_init", default="none", choices=["none", "mean"],
+      help="keyed warm start: key rows beyond the source run's K start from the mean of the trained key rows (+ noise)")
+    a("--init_stack", action="store_true", help="warm start from a shallower model: the extra blocks start as identity")
+    a("--freeze_body_steps", type=int, default=0, help="warm start: only the embedding / head move for this many steps")
+    a("--n_max", type=int, default=0, help="cvp: gates the vocabulary layout has room for (default n_ops x largest factor)")
+    a("--cvp_gate", default="xormaj", choices=["xormaj", "copy", "xor2"], help="cvp gate function (control ablations)")
+    a("--cvp_leak", type=int, default=0,
+      help="cvp curriculum: stage s of cvp_leak + 1 leaks every 2^s-th gate value as an input token, the last stage none")
     # curricula
     a("--curriculum", action="store_true")
     a("--curriculum_start", type=int, default=0)
@@ -90,6 +105,8 @@ def parse(argv=None):
 
 
 def run_tag(args):
+    if args.tag:
+        return args.tag
     t = args.task
     core = {"group": f"{args.group}_{args.format}", "keyed": f"keyed_{args.group}_K{args.K}_D{args.D}",
             "dfa": f"dfa_{args.dfa}", "ca": f"ca{args.ca_rule}_w{args.ca_w}_{args.ca_format}",
@@ -130,19 +147,62 @@ def word_lengths(mul, n):
     return dist
 
 
-def load_warm_start(model, path):
-    """strict=False load; embedding / head rows grow when the new vocab is larger."""
-    sd = torch.load(path, map_location="cpu", weights_only=False)["model"]
+def load_warm_start(model, path, args=None, n_elem=0):
+    """strict=False load of a checkpoint of the same or a smaller problem.  Embedding / head rows grow with
+    the vocabulary, keeping the layout: cvp = [ids of inputs and gates | 4 value tokens] (the tail moves to
+    the new tail), keyed = [base | keys 0..K_max-1 | 2n group tokens] (likewise, when the source was a keyed
+    run), anything else = prefix.  Options of `args`: `newkey_init=mean` (keyed: key rows the source never
+    trained start from the mean of its trained key rows + 0.3 sd noise), `init_stack` (blocks the source
+    does not have start as identity: zero output projections).
+    Reference parity: formal_language/harness/train_statetrack_ws.py:166-215."""
+    ck = torch.load(path, map_location="cpu", weights_only=False)
+    sd, src_args = dict(ck.get("model", ck)), ck.get("args", {}) or {}
     own = model.state_dict()
+    task = getattr(args, "task", None)
+    tail = 4 if task == "cvp" else (2 * n_elem if task == "keyed" and "K" in src_args
+                                    and src_args.get("task", "keyed") == "keyed" else 0)
     for k, v in list(sd.items()):
-        if k in own and v.shape != own[k].shape and v.dim() == 2 and v.shape[1] == own[k].shape[1] \
-                and v.shape[0] < own[k].shape[0]:
-            grown = own[k].clone()
-            grown[:v.shape[0]] = v
+        if k not in own or v.shape == own[k].shape:
+            continue
+        if v.dim() == 2 and v.shape[1] == own[k].shape[1] and v.shape[0] < own[k].shape[0]:
+            grown, ns = own[k].clone(), v.shape[0]
+            if tail and k in ("tok_emb.weight", "lm_head.weight") and ns > tail:
+                grown[:ns - tail] = v[:ns - tail]
+                grown[-tail:] = v[-tail:]
+            else:
+                grown[:ns] = v
             sd[k] = grown
-        elif k in own and v.shape != own[k].shape:
+        else:
             del sd[k]
-    return model.load_state_dict(sd, strict=False)
+    res = model.load_state_dict(sd, strict=False)
+    if args is not None and getattr(args, "newkey_init", "none") == "mean" and task == "keyed":
+        K_src, K_max = int(src_args.get("K", 0) or 0), args.K_max or args.K
+        if 0 < K_src < K_max:
+            with torch.no_grad():
+                for name in {"tok_emb.weight", "lm_head.weight"}:
+                    W = dict(model.named_parameters()).get(name)
+                    if W is None:
+                        continue
+                    old = W[T.BASE:T.BASE + K_src]
+                    mu, sd_ = old.mean(0, keepdim=True), old.std(0, keepdim=True)
+                    new = W[T.BASE + K_src:T.BASE + K_max]
+                    new.copy_(mu + 0.3 * sd_ * torch.randn_like(new))
+    if args is not None and getattr(args, "init_stack", False) and hasattr(model, "blocks"):
+        have = {int(k.split(".")[1]) for k in sd if k.startswith("blocks.")}
+        with torch.no_grad():
+            for i, blk in enumerate(model.blocks):
+                if i not in have:
+                    blk.attn.wo.weight.zero_()
+                    blk.mlp.w2.weight.zero_()
+    return res
+
+
+def freeze_body(model):
+    """Zero every gradient but the embedding's and the head's (the first steps of a warm start let new
+    vocabulary rows settle before the body moves)."""
+    for n, p in model.named_parameters():
+        if p.grad is not None and not (n.startswith("tok_emb") or n.startswith("lm_head")):
+            p.grad.zero_()
 
 
 def sample_loop_k(args, kind, n_ops_t):
@@ -182,11 +242,16 @@ def train_size(args, step):
 
 def main(argv=None):
     args = parse(argv)
+    args.eval_rows = args.eval_bsz or args.eval_rows
+    args.no_key_mod = args.no_key_mod or args.no_kmod
+    args.logn_ref = args.logn_ref or args.attn_logn_ref
+    if args.task == "cvp":
+        T.CVP_GATE[0] = args.cvp_gate
     dev = torch.device(args.device)
     torch.manual_seed(args.seed)
     tid = H.TASK_ID[args.task]
     factors = [int(f) for f in args.gen_factors.split(",")]
-    args.max_ops = max(args.max_ops, args.n_ops * max(factors))
+    args.max_ops = max(args.max_ops, args.n_ops * max(factors), args.n_max)
     mul, n_elem = H.task_tables(args)
     vocab = H.vocab_of(args, n_elem)
     # fixed eval sets (split 0), one per length factor
@@ -196,13 +261,15 @@ def main(argv=None):
                                    args.n_ops * f, evaluating=True)
         evals[f] = (x.to(dev), None if tg is None else tg.to(dev), m.to(dev), d)
         max_T = max(max_T, x.shape[1])
+    if args.task == "cvp" and args.cvp_leak:
+        max_T += 2 * args.n_ops                               # room for the leaked [id, value] pairs of stage 0
     model, kind = H.build_model(args.arch, vocab, max_T + 8, scale=args.scale, deq_sweeps=args.deq_sweeps,
                                 ctx_mod=args.ctx_mod, n_layers=args.n_layers, nope=args.nope,
                                 loop_layers=args.loop_layers, loop_k=args.loop_k, key_mod=not args.no_key_mod,
                                 logn_ref=args.logn_ref, fbt_sched=args.fbt_sched,
                                 loop_emb_scale=args.loop_emb_scale, loop_huginn=args.loop_huginn, loop_bp=args.loop_bp)
     if args.init_from:
-        print("warm start:", load_warm_start(model, args.init_from), flush=True)
+        print("warm start:", load_warm_start(model, args.init_from, args, n_elem), flush=True)
     model = model.to(dev)
     n_par = sum(p.numel() for p in model.parameters())
     tag = run_tag(args)
@@ -254,12 +321,16 @@ def main(argv=None):
         if args.task == "keyed" and args.K_curriculum:
             fr = min(1.0, step / max(1, args.curriculum_end or args.steps // 2))
             args._K_t = max(args.K_curriculum, min(args.K, int(round(args.K_curriculum + (args.K - args.K_curriculum) * fr))))
+        if args.task == "cvp" and args.cvp_leak:              # leak doubling: stage s leaks every 2^s-th gate
+            end = args.curriculum_end or args.steps // 2
+            stage = min(args.cvp_leak, int(step * (args.cvp_leak + 1) / max(1, end)))
+            args.cvp_leak_every = 0 if stage >= args.cvp_leak else 2 ** stage
         x, tg, m, _ = H.make_batch(args, mul, n_elem, step_rng(tid, args.seed, 1, step), args.bsz, n_ops_t,
                                    D_override=D_t)
         x, m = x.to(dev), m.to(dev)
         tg = None if tg is None else tg.to(dev)
         if engine is not None:
-            loss_v = engine.step(x, tg, m, lr)
+            loss_v = engine.step(x, tg, m, lr, freeze=step < args.freeze_body_steps)
         else:
             for g in opt.param_groups:
                 g["lr"] = lr
@@ -268,6 +339,8 @@ def main(argv=None):
                 logits = H.logits_of(kind, model, x, K=loop_k[0])
             loss = H.masked_loss(logits, x, tg, m)
             loss.backward()
+            if step < args.freeze_body_steps:
+                freeze_body(model)
             torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
             loss_v = loss.item()
             skip = False

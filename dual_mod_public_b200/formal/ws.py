@@ -33,7 +33,8 @@ class EngineTrainer:
             c = self.args.ws_chunk
             self._engines[key] = WaveScanEngine(
                 self.model, [uniform_chunks(T, c)], B, T, device=self.device, keep_logits=True,
-                autocast_bf16=self.device.type == "cuda", use_graphs=False, grads=self.grads)
+                autocast_bf16=self.device.type == "cuda", use_graphs=False, grads=self.grads,
+                backend="generic" if getattr(self.args, "no_fused", False) else "auto")
         eng = self._engines[key]
         return eng
 
@@ -43,12 +44,17 @@ class EngineTrainer:
         eng.forward(x)
         return eng.logits
 
-    def step(self, x, tgt, msk, lr):
+    def step(self, x, tgt, msk, lr, freeze=False):
+        """freeze: only the embedding / head move this step (every other gradient is zeroed)."""
         eng = self._engine(*x.shape)
         self.opt.zero_grad()
         eng.pack()
         eng.forward(x)
         loss, d = H.masked_dlogits(eng.logits, x, tgt, msk)
         eng.backward(d_logits=d)
+        if freeze:
+            for n, p in self.model.named_parameters():
+                if not (n.startswith("tok_emb") or n.startswith("lm_head")):
+                    self.grads.get(p).zero_()
         self.opt.step(lr=lr)
         return float(loss)

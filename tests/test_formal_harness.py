@@ -59,3 +59,48 @@ def test_engine_path_trains(tmp_path):
                      "--eval_rows", "16", "--gen_factors", "1", "--engine", "wavescan", "--ws_chunk", "8",
                      "--eval_every", "15", "--out_root", str(tmp_path)])
     assert final[1] >= 0.0
+
+
+def test_warm_starts_keep_the_vocabulary_layout(tmp_path):
+    """Keyed K = 2 -> K_max 8: base + key rows stay in place, the 2n group rows move to the new tail, untrained
+    key rows start near the mean of the trained ones; a deeper model's extra block starts as identity; the
+    body stays frozen for the first steps; cvp grows by moving its 4 value tokens to the new tail."""
+    from dual_mod_public_b200.formal import tasks as T
+    common = ["--task", "keyed", "--group", "z10", "--D", "2", "--arch", "dualmod", "--bsz", "8", "--lr", "3e-3",
+              "--device", "cpu", "--eval_rows", "8", "--gen_factors", "1", "--eval_every", "50",
+              "--out_root", str(tmp_path), "--eval_dump"]
+    TS.main(common + ["--K", "2", "--K_max", "4", "--n_layers", "1", "--steps", "3", "--tag", "src"])
+    src = torch.load(tmp_path / "out" / "statetrack_ckpts" / "src_dualmod.pt", weights_only=False)
+    assert src["args"]["K"] == 2 and src["args"]["tag"] == "src"
+    n = 10
+    args = TS.parse(common + ["--K", "4", "--K_max", "8", "--n_layers", "2", "--newkey_init", "mean", "--init_stack"])
+    mul, n_elem = H.task_tables(args)
+    model, _ = H.build_model("dualmod", H.vocab_of(args, n_elem), 64, scale=args.scale, n_layers=2)
+    before = model.tok_emb.weight.detach().clone()
+    TS.load_warm_start(model, str(tmp_path / "out" / "statetrack_ckpts" / "src_dualmod.pt"), args, n_elem)
+    W, S = model.tok_emb.weight.detach(), src["model"]["tok_emb.weight"]
+    assert S.shape[0] == T.BASE + 4 + 2 * n and W.shape[0] == T.BASE + 8 + 2 * n
+    assert torch.equal(W[:T.BASE + 2], S[:T.BASE + 2]) and torch.equal(W[-2 * n:], S[-2 * n:])
+    new_keys, trained = W[T.BASE + 2:T.BASE + 8], S[T.BASE:T.BASE + 2]
+    assert not torch.equal(new_keys, before[T.BASE + 2:T.BASE + 8])
+    assert (new_keys.mean(0) - trained.mean(0)).abs().max() < 3 * trained.std(0).max() + 1e-3
+    assert model.blocks[1].attn.wo.weight.abs().max() == 0 and model.blocks[1].mlp.w2.weight.abs().max() == 0
+    assert model.blocks[0].attn.wo.weight.abs().max() > 0
+    # frozen body (gradients zeroed; no weight decay here): after two steps only the embedding (tied head) has moved
+    for engine in ([], ["--engine", "wavescan", "--ws_chunk", "8"]):
+        TS.main(common + ["--K", "2", "--K_max", "4", "--n_layers", "1", "--steps", "2", "--freeze_body_steps", "5", "--wd", "0",
+                          "--init_from", str(tmp_path / "out" / "statetrack_ckpts" / "src_dualmod.pt"), "--tag", "frz"]
+                + engine)
+        frz = torch.load(tmp_path / "out" / "statetrack_ckpts" / "frz_dualmod.pt", weights_only=False)["model"]
+        assert torch.equal(frz["blocks.0.attn.wq.weight"], src["model"]["blocks.0.attn.wq.weight"]), engine
+        assert not torch.equal(frz["tok_emb.weight"], src["model"]["tok_emb.weight"]), engine
+    # cvp: 6 -> 12 gates
+    cv = ["--task", "cvp", "--cvp_inputs", "4", "--arch", "dualmod", "--n_layers", "1", "--bsz", "4", "--device", "cpu",
+          "--eval_rows", "4", "--gen_factors", "1", "--eval_every", "50", "--out_root", str(tmp_path), "--eval_dump"]
+    TS.main(cv + ["--n_ops", "6", "--max_ops", "6", "--steps", "2", "--tag", "cv6", "--cvp_leak", "2", "--curriculum"])
+    s6 = torch.load(tmp_path / "out" / "statetrack_ckpts" / "cv6_dualmod.pt", weights_only=False)["model"]["tok_emb.weight"]
+    a12 = TS.parse(cv + ["--n_ops", "12", "--max_ops", "12"])
+    m12, _ = H.build_model("dualmod", H.vocab_of(a12, 0), 128, scale=a12.scale, n_layers=1)
+    TS.load_warm_start(m12, str(tmp_path / "out" / "statetrack_ckpts" / "cv6_dualmod.pt"), a12, 0)
+    W12 = m12.tok_emb.weight.detach()
+    assert W12.shape[0] == s6.shape[0] + 6 and torch.equal(W12[-4:], s6[-4:]) and torch.equal(W12[:s6.shape[0] - 4], s6[:-4])
