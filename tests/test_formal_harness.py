@@ -104,3 +104,29 @@ def test_warm_starts_keep_the_vocabulary_layout(tmp_path):
     TS.load_warm_start(m12, str(tmp_path / "out" / "statetrack_ckpts" / "cv6_dualmod.pt"), a12, 0)
     W12 = m12.tok_emb.weight.detach()
     assert W12.shape[0] == s6.shape[0] + 6 and torch.equal(W12[-4:], s6[-4:]) and torch.equal(W12[:s6.shape[0] - 4], s6[:-4])
+
+
+def test_checkpoint_reevaluation_and_composition_statistics(tmp_path):
+    import numpy as np
+    from dual_mod_public_b200.formal import analysis as A
+    from dual_mod_public_b200.formal import tasks as T
+    TS.main(["--task", "group", "--group", "s3", "--format", "tagged", "--n_ops", "8", "--arch", "dualmod", "--n_layers", "1",
+             "--steps", "30", "--bsz", "16", "--lr", "3e-3", "--device", "cpu", "--eval_rows", "16", "--gen_factors", "1",
+             "--eval_every", "100", "--out_root", str(tmp_path), "--eval_dump", "--tag", "g"])
+    ck = str(tmp_path / "out" / "statetrack_ckpts" / "g_dualmod.pt")
+    r = A.reeval(ck, factor=2, rows=16)
+    assert 0.0 <= r[2] <= 1.0 and r["state_dict_mismatch"] == {"missing": 0, "unexpected": 0} and len(r["x2_by_pos8"]) >= 7
+    c = A.composition(ck, rows=16)
+    assert c["n_states"] == 6 and c["all"]["n"] == 16 * 8 and 0 <= c["all"]["top1"] <= c["all"]["top5"] <= 1
+    assert len(c["octiles"]) == 8 and sum(o["n"] for o in c["octiles"]) == c["all"]["n"]
+    # the statistics on made-up logits: gold always second -> rank 1, and a fixed correction element
+    mul, n = T.cayley("z5")
+    inv = A.inverse_table(np.asarray(mul))
+    assert all(mul[g][inv[g]] == 0 for g in range(n))
+    gold = np.arange(20) % n
+    lg = np.zeros((20, n))
+    lg[np.arange(20), gold] = 1.0
+    lg[np.arange(20), (gold + 1) % n] = 2.0                      # predicts gold + 1: correction = -1, word length 1
+    s = A.composition_stats(lg, gold, np.arange(20), 20, np.asarray(mul))
+    assert s["all"]["top1"] == 0.0 and s["all"]["top5"] == 1.0 and s["all"]["mean_rank"] == 1.0
+    assert s["all"]["p_wordlen_le2"] == 1.0 and s["all"]["entropy_ratio"] == 0.0 and abs(s["all"]["top5_mass"] - 1.0) < 1e-9
