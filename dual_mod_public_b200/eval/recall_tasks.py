@@ -112,8 +112,21 @@ def _strip_question(text, question):
     return text
 
 
-def recall_prompt(name, doc, tok, keep_lead=False, prepend_spaces=0, **cut):
-    """The prompt of one document of recall task `name`."""
+def env_options():
+    """Protocol switches from the environment: JRT_CONTEXT_LENGTH / JRT_ANSWER_LENGTH (window size), JRT_NO_STRIP=1
+    (keep the document's leading whitespace), JRT_PREPEND_SPACES=N (strip, then prepend N spaces)."""
+    e = os.environ
+    return dict(context_length=int(e.get("JRT_CONTEXT_LENGTH", 2048)), answer_length=int(e.get("JRT_ANSWER_LENGTH", 50)),
+                keep_lead=e.get("JRT_NO_STRIP", "0") == "1", prepend_spaces=int(e.get("JRT_PREPEND_SPACES", "0")))
+
+
+def recall_prompt(name, doc, tok, keep_lead=None, prepend_spaces=None, **cut):
+    """The prompt of one document of recall task `name` (unset options come from `env_options`)."""
+    env = env_options()
+    keep_lead = env["keep_lead"] if keep_lead is None else keep_lead
+    prepend_spaces = env["prepend_spaces"] if prepend_spaces is None else prepend_spaces
+    cut.setdefault("context_length", env["context_length"])
+    cut.setdefault("answer_length", env["answer_length"])
     _, text_key, answer_keys, kind = RECALL[name]
     d = cut_to_answer(doc, text_key, answer_keys, tok, keep_lead=keep_lead, **cut) or doc
     text = d[text_key]

@@ -15,6 +15,11 @@ OUT=${OUT:-out/dm1p3b}
 DATA_BIN=${DATA_BIN:-}
 STEPS=${STEPS:-190650}
 WARMUP=${WARMUP:-2000}
+# SMOKE=1: a 20-step end-to-end run on synthetic tokens before a long run
+if [ "${SMOKE:-0}" = 1 ]; then STEPS=20; WARMUP=5; OUT=${OUT}_smoke; DATA_BIN=; set -- --log_every 1 "$@"; fi
+# WINDOW=2048: sliding-window attention of that many tokens (the operator then travels with the checkpoints)
+WINDOW_ARGS=()
+[ -n "${WINDOW:-}" ] && WINDOW_ARGS=(--model_overrides "{\"local_window\": ${WINDOW}}")
 export TORCH_NCCL_ASYNC_ERROR_HANDLING=1
 export PYTORCH_CUDA_ALLOC_CONF=${PYTORCH_CUDA_ALLOC_CONF:-expandable_segments:True}
 DATA_ARGS=(--synthetic)
@@ -23,4 +28,4 @@ exec python -m torch.distributed.run --nnodes="$NNODES" --node-rank="$NODE_RANK"
   --master-addr "$MASTER" --master-port "$PORT" \
   -m dual_mod_public_b200.train.train_lm --recipe "$RECIPE" --out_dir "$OUT" --total_steps "$STEPS" \
   --warmup_steps "$WARMUP" --clip_mult 2.0 --gn_hard 50 --rank_outlier_factor 4 --ckpt_every 250 --async_ckpt \
-  --persist_every 5000 --resume auto --auto_rewind "${DATA_ARGS[@]}" "$@"
+  --persist_every 5000 --resume auto --auto_rewind "${WINDOW_ARGS[@]}" "${DATA_ARGS[@]}" "$@"

@@ -1,6 +1,8 @@
 #!/usr/bin/env bash
 # 340M Dual-Mod run on one node (cell engine, c=64, K-ladder 8/16/32 with K=64 probes).
 #   DATA_BIN=/data/slimpj_train.bin VAL_BIN=/data/slimpj_val.bin OUT=out/dm340 NGPU=8 bash launch_340m.sh
+#   SMOKE=1 NGPU=2 bash launch_340m.sh          # 20 steps on synthetic tokens
+#   add --protocol pdn for the batch-256 / 30k-step / lr 4e-4 protocol, --model_overrides for another shape
 # Every knob is an environment variable with a default; extra flags are passed through ("$@").
 # Reference parity: lm/train_340m/scripts/launch_dm_d960.sh, scripts/launch_torchrun.sh.
 set -euo pipefail
@@ -10,6 +12,8 @@ DATA_BIN=${DATA_BIN:-}
 VAL_BIN=${VAL_BIN:-}
 STEPS=${STEPS:-30000}
 WARMUP=${WARMUP:-1000}
+# SMOKE=1: a 20-step end-to-end run on synthetic tokens (graphs captured, one checkpoint written) before a long run
+if [ "${SMOKE:-0}" = 1 ]; then STEPS=20; WARMUP=5; OUT=${OUT}_smoke; DATA_BIN=; VAL_BIN=; set -- --ckpt_every 10 --log_every 1 "$@"; fi
 PORT=${PORT:-29500}
 export TORCH_NCCL_ASYNC_ERROR_HANDLING=1
 export PYTORCH_CUDA_ALLOC_CONF=${PYTORCH_CUDA_ALLOC_CONF:-expandable_segments:True}
