@@ -122,6 +122,10 @@ def parse_args(argv=None):
     a("--seed", type=int, default=1337)
     a("--log_every", type=int, default=10)
     a("--wandb_project", default="", help="mirror metrics.jsonl to this project")
+    a("--eager_val_every", type=int, default=0,
+      help="> 0 (needs --val_exact_K): every this many steps score one validation batch both through the engine at the exact setting and through the eager scan, and log the pair")
+    a("--eager_val_rows", type=int, default=2)
+    a("--eager_val_len", type=int, default=256, help="tokens of the cross-check slice (the eager scan is slow)")
     a("--val_exact_K", type=int, default=0, help="> 0: also validate through the engine at this K (the chunk length is exact for the cell engine) and log val/loss_exact")
     a("--device", default="")
     args = ap.parse_args(argv)
@@ -321,6 +325,17 @@ def run(args):
             dist.all_reduce(lt)
             loss = lt.item() / world
         rewarmed = skip.update(gn_seen, loss_seen, is_probe, skipped)
+        if (not math.isfinite(gn) or gn > 1e3) and hasattr(tr.engine, "debug_scan"):
+            # every rank scans its own persistent buffers (a residue on one rank only would otherwise go unseen)
+            bad = tr.engine.debug_scan()[:6]
+            found = [None] * world
+            if world > 1:
+                dist.all_gather_object(found, (rank, bad))
+            else:
+                found = [(0, bad)]
+            if master:
+                print(f"DEBUG-SCAN step {step}: gn {gn:.3g}; non-finite buffers by rank: "
+                      f"{[(r, b) for r, b in found if b] or 'none'}", flush=True)
         if not skipped:
             applied += 1
             clip.update(gn, is_probe)
@@ -365,6 +380,26 @@ def run(args):
             if exact_sid is not None:
                 rec["val/loss_exact"] = validate(exact_sid)
                 rec[f"val/base_minus_k{args.val_exact_K}"] = rec["val/loss"] - rec["val/loss_exact"]
+        if (args.eager_val_every and exact_sid is not None and val_stream is not None and step > 0
+                and step % args.eager_val_every == 0):
+            # same rows through the engine at the exact setting and through the eager scan: the two agree to
+            # rounding when the engine is healthy.  The eager scan sees only a prefix slice, so the engine's
+            # loss is taken on the same positions (targets beyond the slice are masked).
+            n_tok, rows_x = min(T, args.eager_val_len), min(micro, args.eager_val_rows)
+            b = val_stream[0][:micro].to(dev)
+            tg = b[:, 1:T + 1].clone()
+            tg[rows_x:] = -1
+            tg[:, n_tok:] = -1
+            rec["val/loss_engine_xcheck"] = float(tr.engine.forward(b[:, :T], tg, sid=exact_sid, train=False))
+            mode, tr.model.cfg.attn_mode = tr.model.cfg.attn_mode, "sequential"
+            was = tr.model.training
+            tr.model.eval()
+            with torch.no_grad(), torch.autocast(dev.type, dtype=torch.bfloat16, enabled=dev.type == "cuda" and not args.fp32):
+                lg = tr.model(b[:rows_x, :n_tok])[0]
+            rec["val/loss_eager_xcheck"] = float(torch.nn.functional.cross_entropy(
+                lg.float().flatten(0, 1), b[:rows_x, 1:n_tok + 1].reshape(-1)))
+            tr.model.train(was)
+            tr.model.cfg.attn_mode = mode
         if args.telemetry_every and step % args.telemetry_every == 0 and master:
             from .curvature import gate_stats_layerwise
             if tel_x is None:                            # one fixed batch, so the dials compare step to step

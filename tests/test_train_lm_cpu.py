@@ -247,8 +247,10 @@ def test_observability_keys(tmp_path):
     out = str(tmp_path / "obs")
     train_main(["--recipe", "tiny", "--synthetic", "--device", "cpu", "--warmup_steps", "2", "--log_every", "100",
                 "--out_dir", out, "--total_steps", "8", "--probe_frac", "0.5", "--val_every", "3", "--val_batches", "1",
-                "--val_exact_K", "16"])
+                "--val_exact_K", "16", "--eager_val_every", "3", "--eager_val_len", "40"])
     recs = _records(out)
+    x = [r for r in recs if "val/loss_eager_xcheck" in r]
+    assert x and all(abs(r["val/loss_eager_xcheck"] - r["val/loss_engine_xcheck"]) < 1e-4 for r in x)
     assert any("probe/loss" in r and "probe/grad_norm" in r for r in recs)
     assert any("base/loss" in r for r in recs) and all(("probe/loss" in r) != ("base/loss" in r) for r in recs)
     v = [r for r in recs if "val/loss" in r]
@@ -290,3 +292,14 @@ def test_two_ranks_two_speed_optimizer_and_sam(tmp_path):
     assert [r["train/dm_stepped"] for r in recs] == [False, True, False, True, False]
     assert [r["train/sam_active"] for r in recs] == [1, 0, 1, 0, 1]
     assert recs[-1]["train/loss"] < recs[0]["train/loss"] + 0.05
+
+
+def test_wild_norm_triggers_a_buffer_scan(tmp_path, monkeypatch, capsys):
+    monkeypatch.setenv("DMB_FAKE_NAN_STEPS", "2")
+    out = str(tmp_path / "scan")
+    # a non-finite loss voids the step; the norm itself stays finite, so force the scan through the norm as well
+    monkeypatch.setenv("DMB_FAKE_SPIKE_STEPS", "3")
+    monkeypatch.setenv("DMB_FAKE_SPIKE_X", "1e9")
+    train_main(TINY + ["--out_dir", out, "--total_steps", "5"])
+    recs = _records(out)
+    assert recs[2]["train/skipped"] and recs[3]["train/skipped"]
