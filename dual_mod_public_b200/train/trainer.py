@@ -66,6 +66,8 @@ class Trainer:
             self.opt = make(None)
         # per-rank rejection needs every rank's LOCAL norm before anything is reduced: no early buckets then
         self.rank_outlier = (rank_outlier_factor, rank_outlier_max) if rank_outlier_factor > 0 and self.world > 1 else None
+        if self.rank_outlier is not None and isinstance(self.opt, HybridAdamW):
+            raise NotImplementedError("per-rank outlier rejection reads one flat gradient array; the two-speed optimizer has two")
         self.group, self.rank_excluded = process_group, 0
         self.local_norm_factor = 1.0
         self.overlap = (overlap_buckets and optimizer == "fused" and self.opt.use_kernel and self.world > 1
