@@ -100,85 +100,83 @@ class GraphDecoder:
         self.V[l].index_copy_(1, self.pos, vpp.view(B, 1, h, dh).to(self.dt))
         return attn.wo(o_cat)
 
-    def _step(self):
-        m = self.m
-        cos_p, sin_p = m.rope_cos.index_select(0, self.pos), m.rope_sin.index_select(0, self.pos)
-        x = m.tok_emb(self.tok)
-        for l, blk in enumerate(m.blocks):
-            x = x + self._attn(blk.attn, blk.attn_norm(x), l, cos_p, sin_p)
-            x = x + blk.mlp(blk.mlp_norm(x))
-        lg = m.lm_head(m.norm_f(x))
-        self.logits.copy_(lg.float())
-        self.next.copy_(lg.argmax(-1))
-        self.pos += 1
-        self.pos32 += 1
+    def _decode_token(self):
+        """One token through every layer at the device-side position; leaves the fp32 logits and the
+        arg-max in the static outputs and advances the position counters."""
+        model, at = self.m, self.pos
+        cos_p, sin_p = model.rope_cos.index_select(0, at), model.rope_sin.index_select(0, at)
+        stream = model.tok_emb(self.tok)
+        for l, blk in enumerate(model.blocks):
+            stream = stream + self._attn(blk.attn, blk.attn_norm(stream), l, cos_p, sin_p)
+            stream = stream + blk.mlp(blk.mlp_norm(stream))
+        scores = model.lm_head(model.norm_f(stream)).float()
+        self.logits.copy_(scores)
+        torch.argmax(scores, dim=-1, out=self.next)
+        for counter in (self.pos, self.pos32):
+            counter.add_(1)
 
-    def _run_step(self):
-        amp = self.dev.type == "cuda" and self.dt == torch.bfloat16
-        with torch.no_grad(), torch.autocast(self.dev.type, dtype=torch.bfloat16, enabled=amp, cache_enabled=False):
-            self._step()
+    def _eager_token(self):
+        on_gpu = self.dev.type == "cuda" and self.dt == torch.bfloat16
+        with torch.no_grad(), torch.autocast(self.dev.type, dtype=torch.bfloat16, enabled=on_gpu, cache_enabled=False):
+            self._decode_token()
 
-    def capture(self):
-        if self.dev.type != "cuda":
-            return self
-        side = torch.cuda.Stream(device=self.dev)
-        side.wait_stream(torch.cuda.current_stream(self.dev))
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                self._run_step()
-        torch.cuda.current_stream(self.dev).wait_stream(side)
-        self.reset()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self._run_step()
-        self.reset()
-        self.graph = g
+    def capture(self, warm_tokens=3):
+        """Record one decode step as a CUDA graph (a no-op on CPU).  A few eager tokens on a side stream
+        first, so lazy initialisation (library handles, autotuned plans) stays out of the recording."""
+        if self.dev.type == "cuda":
+            main, side = torch.cuda.current_stream(self.dev), torch.cuda.Stream(device=self.dev)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                for _ in range(warm_tokens):
+                    self._eager_token()
+            main.wait_stream(side)
+            self.reset()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._eager_token()
+            self.reset()
         return self
 
     def reset(self):
-        self.pos.zero_()
-        self.pos32.zero_()
-        for Kb, Vb in zip(self.K, self.V):
-            Kb.zero_()
-            Vb.zero_()
+        """Empty tape, position 0."""
+        for t in [self.pos, self.pos32, *self.K, *self.V]:
+            t.zero_()
 
     def step(self):
-        if self.graph is not None:
-            self.graph.replay()
-        else:
-            self._run_step()
+        """Consume `self.tok` at the current position (graph replay when recorded)."""
+        (self._eager_token if self.graph is None else self.graph.replay)()
 
     @torch.no_grad()
     def prefill(self, prompt):
         """Token-by-token prefill (the tape is recurrent: row t depends on the read at t)."""
-        for p in range(prompt.shape[1]):
-            self.tok.copy_(prompt[:, p:p + 1])
+        for column in prompt.split(1, dim=1):
+            self.tok.copy_(column)
             self.step()
 
     @torch.no_grad()
     def generate(self, prompt, max_new, eos_id=None, stop_fn=None, check_every=16):
         """Greedy continuation.  prompt [B, L] on the device, all rows the same length.
         Returns (gen [B, k] on CPU, k = steps run).  `stop_fn(gen_cpu) -> bool [B]` marks
-        finished rows; generation ends when every row is finished."""
-        B, L = prompt.shape
-        assert B == self.B and L + max_new <= self.P, (B, L, max_new, self.P)
+        finished rows; generation ends when every row is finished.  The host looks at the
+        generated tokens only every `check_every` steps, so the launches in between queue freely."""
+        rows, plen = prompt.shape
+        if rows != self.B or plen + max_new > self.P:
+            raise ValueError(f"prompt {tuple(prompt.shape)} + {max_new} new tokens does not fit [{self.B}, {self.P}]")
         self.reset()
         self.prefill(prompt)
-        gen = torch.zeros(B, max_new, dtype=torch.long, device=self.dev)
-        done = torch.zeros(B, dtype=torch.bool)
-        k = 0
-        while k < max_new:
-            gen[:, k].copy_(self.next[:, 0])
-            k += 1
-            if k % check_every == 0 or k == max_new:
-                g_cpu = gen[:, :k].cpu()
+        out = torch.zeros(rows, max_new, dtype=torch.long, device=self.dev)
+        finished = torch.zeros(rows, dtype=torch.bool)
+        for n in range(1, max_new + 1):
+            out[:, n - 1] = self.next[:, 0]                    # the prediction made by the previous step
+            if n % check_every == 0 or n == max_new:
+                seen = out[:, :n].cpu()
                 if eos_id is not None:
-                    done |= (g_cpu == eos_id).any(1)
+                    finished |= (seen == eos_id).any(dim=1)
                 if stop_fn is not None:
-                    done |= stop_fn(g_cpu)
-                if bool(done.all()):
-                    break
-            if k < max_new:
+                    finished |= stop_fn(seen)
+                if finished.all():
+                    return seen, n
+            if n < max_new:
                 self.tok.copy_(self.next)
                 self.step()
-        return gen[:, :k].cpu(), k
+        return out.cpu(), max_new
