@@ -213,3 +213,13 @@ def test_recall_and_needle_protocols_run_from_local_files(tmp_path):
     assert any(f.endswith("_jrt_fda_TEXT.jsonl") for f in files)
     lines = collate.table(out, "runA")
     assert any("jrt_fda" in l for l in lines) and any("niah_single_1" in l for l in lines)
+
+
+def test_shell_drivers_parse():
+    import glob
+    import subprocess
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "dual_mod_public_b200")
+    scripts = sorted(glob.glob(os.path.join(root, "**", "*.sh"), recursive=True))
+    assert len(scripts) >= 7
+    for s in scripts:
+        assert subprocess.run(["bash", "-n", s], capture_output=True).returncode == 0, s
