@@ -223,3 +223,10 @@ def test_shell_drivers_parse():
     assert len(scripts) >= 7
     for s in scripts:
         assert subprocess.run(["bash", "-n", s], capture_output=True).returncode == 0, s
+
+
+def test_profile_tool_shapes_are_valid_configs():
+    from dual_mod_public_b200.ops import profile_step as P
+    for name, sh in P.SHAPES.items():
+        cfg = DualModConfig(n_layers=2, vocab_size=32000, gate_bias_init=0.0, **sh["cfg"])
+        assert sh["T"] % 64 == 0 and cfg.d_model % cfg.n_heads == 0 and sh["engine"] in ("wavescan", "wave3d"), name
