@@ -223,7 +223,8 @@ class WaveScanEngine:
         if ops is None:
             from ..ops import default_ops
             ops = default_ops(self.device)
-        self.ops = ops
+        from ..ops.checked import maybe_checked
+        self.ops = maybe_checked(ops)                    # DMB_CHECK_ARGS=1: every launch's arguments are validated
 
         dev, act = self.device, self.act
         L, h, dh, d = self.L, cfg.n_heads, cfg.head_dim, cfg.d_model
