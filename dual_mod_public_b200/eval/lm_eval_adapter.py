@@ -79,7 +79,7 @@ def trunc_keep_head(toks, cap):
 
 class DualModEval(_Base):
     def __init__(self, ckpt, tokenizer=None, batch_rows=16, device=None, max_length=2048, ctx_len=None,
-                 engine_K=0, engine_chunk=64, model=None):
+                 engine_K=0, engine_chunk=64, model=None, gen_rows=8):
         if _Base is not object:
             super().__init__()
         self.dev = device or ("cuda" if torch.cuda.is_available() else "cpu")
@@ -99,6 +99,7 @@ class DualModEval(_Base):
         self.tok = load_tokenizer(tokenizer)
         self.bos = self.tok.bos_token_id if self.tok.bos_token_id is not None else 1
         self.batch_rows, self.engine_K, self.engine_chunk = batch_rows, engine_K, engine_chunk
+        self.gen_rows = gen_rows
         self.len_quant = int(os.environ.get("EVAL_LEN_QUANT", "64"))
         self._engines = {}
         self._rank, self._world_size = 0, 1
@@ -230,66 +231,90 @@ class DualModEval(_Base):
     def _gen_key(self, prompt, until, max_new):
         return hashlib.md5(json.dumps([prompt, until, max_new]).encode()).hexdigest()
 
-    @torch.no_grad()
-    def _greedy(self, prompt_ids, max_new, stop_strs):
-        """Greedy continuation of one prompt -> text (cut at the first stop string).  The budget is capped
-        at half the context, so a short context still keeps a prompt."""
-        max_new = min(max_new, max(1, self.max_length // 2))
-        cap = self.max_length - max_new
-        ids = trunc_keep_head(prompt_ids, max(1, cap))
-        x = torch.tensor([ids], dtype=torch.long, device=self.dev)
-        gen = []
-        if torch.device(self.dev).type == "cuda":
-            from .graph_decode import GraphDecoder
-            P = len(ids) + max_new
-            key = ("dec", -(-P // 256) * 256)
-            if key not in self._engines:
-                self._engines[key] = GraphDecoder(self.model, 1, min(key[1], self.model.cfg.max_seq_len)).capture()
-            dec = self._engines[key]
-
-            def stop_fn(g_cpu):
-                text = self.tok.decode(g_cpu[0].tolist())
-                return torch.tensor([any(s in text for s in stop_strs)])
-            g, k = dec.generate(x, max_new, eos_id=self.tok.eos_token_id, stop_fn=stop_fn if stop_strs else None)
-            gen = g[0, :k].tolist()
-        else:
-            caches, logits = self.model.decode_init(), None
-            for t in range(x.shape[1]):
-                logits = self.model.decode_step(x[:, t:t + 1], t, caches)
-            for j in range(max_new):
-                nxt = int(logits[0, -1].argmax())
-                gen.append(nxt)
-                text = self.tok.decode(gen)
-                if nxt == self.tok.eos_token_id or any(s in text for s in stop_strs):
-                    break
-                logits = self.model.decode_step(torch.tensor([[nxt]], device=self.dev), x.shape[1] + j, caches)
-        text = self.tok.decode(gen)
+    def _cut(self, ids, stop_strs):
+        """Token ids of one row -> text, cut at the end-of-sequence id and at the first stop string."""
+        eos = self.tok.eos_token_id
+        if eos in ids:
+            ids = ids[:ids.index(eos)]
+        text = self.tok.decode(ids)
         for s in stop_strs:
             if s in text:
                 text = text[:text.index(s)]
         return text
 
+    @torch.no_grad()
+    def _greedy_batch(self, prompts, max_new, stop_strs):
+        """Greedy continuations of prompts of ONE length (so a single position serves the whole batch) ->
+        texts.  On a GPU: the static-tape `GraphDecoder` at a fixed batch of `gen_rows` rows (short batches are
+        filled with copies of the last row, so one recorded graph serves every batch); on CPU: `decode_step`.
+        The budget is capped at half the context, so a short context still keeps a prompt."""
+        n, eos = len(prompts), self.tok.eos_token_id
+        x = torch.tensor(prompts, dtype=torch.long, device=self.dev)
+        plen = x.shape[1]
+
+        def finished(rows_cpu):
+            return torch.tensor([eos in r or any(s in self.tok.decode(r) for s in stop_strs)
+                                 for r in rows_cpu.tolist()])
+
+        if torch.device(self.dev).type == "cuda":
+            from .graph_decode import GraphDecoder
+            rows = max(self.gen_rows, n)
+            P = min(-(-(plen + max_new) // 256) * 256, self.model.cfg.max_seq_len)
+            key = ("dec", rows, P)
+            if key not in self._engines:
+                self._engines[key] = GraphDecoder(self.model, rows, P).capture()
+            if rows > n:
+                x = torch.cat((x, x[-1:].expand(rows - n, plen)), dim=0)
+            gen, k = self._engines[key].generate(x, max_new, eos_id=eos, stop_fn=finished)
+            toks = gen[:n, :k].tolist()
+        else:
+            caches, logits = self.model.decode_init(), None
+            for t in range(plen):
+                logits = self.model.decode_step(x[:, t:t + 1], t, caches)
+            toks = [[] for _ in range(n)]
+            for j in range(max_new):
+                nxt = logits[:, -1].argmax(-1)
+                for r in range(n):
+                    toks[r].append(int(nxt[r]))
+                if bool(finished(torch.tensor(toks)).all()) or j == max_new - 1:
+                    break
+                logits = self.model.decode_step(nxt[:, None], plen + j, caches)
+        return [self._cut(t, stop_strs) for t in toks]
+
+    def _greedy(self, prompt_ids, max_new, stop_strs):
+        max_new = min(max_new, max(1, self.max_length // 2))
+        ids = trunc_keep_head(prompt_ids, max(1, self.max_length - max_new))
+        return self._greedy_batch([ids], max_new, stop_strs)[0]
+
     def generate_until(self, requests):
-        out = []
-        for req in requests:
+        """Greedy generation.  Requests are grouped by (prompt length in tokens, stop strings, budget): rows of
+        one group share their position counter, so they decode as one batch of up to `gen_rows` rows."""
+        from collections import defaultdict
+        out, groups = [None] * len(requests), defaultdict(list)
+        for i, req in enumerate(requests):
             prompt, kw = _args(req)[:2]
             kw = dict(kw or {})
             until = kw.get("until") or []
-            until = [until] if isinstance(until, str) else list(until)
+            until = (until,) if isinstance(until, str) else tuple(until)
             max_new = int(kw.get("max_gen_toks", kw.get("max_new_tokens", 64)))
-            key = self._gen_key(prompt, until, max_new)
+            key = self._gen_key(prompt, list(until), max_new)
             if key in self._gcache:
-                out.append(self._gcache[key])
-                continue
-            if self._gcache_only:
-                out.append("<UNCACHED>")
-                continue
-            text = self._greedy([self.bos] + self.tok_encode(prompt), max_new, until)
-            self._gcache[key] = text
-            if self._gcache_path:
-                with open(self._gcache_path, "a") as f:
-                    f.write(json.dumps({"k": key, "g": text}) + "\n")
-            out.append(text)
+                out[i] = self._gcache[key]
+            elif self._gcache_only:
+                out[i] = "<UNCACHED>"
+            else:
+                max_new = min(max_new, max(1, self.max_length // 2))
+                ids = trunc_keep_head([self.bos] + self.tok_encode(prompt), max(1, self.max_length - max_new))
+                groups[(len(ids), until, max_new)].append((i, key, ids))
+        for (_, until, max_new), items in sorted(groups.items(), key=lambda kv: kv[0][0]):
+            for b0 in range(0, len(items), self.gen_rows):
+                part = items[b0:b0 + self.gen_rows]
+                texts = self._greedy_batch([ids for _, _, ids in part], max_new, list(until))
+                for (i, key, _), text in zip(part, texts):
+                    out[i] = self._gcache[key] = text
+                    if self._gcache_path:
+                        with open(self._gcache_path, "a") as f:
+                            f.write(json.dumps({"k": key, "g": text}) + "\n")
         return out
 
 

@@ -230,3 +230,21 @@ def test_profile_tool_shapes_are_valid_configs():
     for name, sh in P.SHAPES.items():
         cfg = DualModConfig(n_layers=2, vocab_size=32000, gate_bias_init=0.0, **sh["cfg"])
         assert sh["T"] % 64 == 0 and cfg.d_model % cfg.n_heads == 0 and sh["engine"] in ("wavescan", "wave3d"), name
+
+
+def test_generation_batches_by_prompt_length_and_matches_row_by_row(tmp_path):
+    m = tiny()
+    save_checkpoint(str(tmp_path), m, step=1)
+    ck = os.path.join(tmp_path, "ckpt_latest.pt")
+    one = DualModEval(ck, tokenizer="bytes", device="cpu", max_length=64, gen_rows=1)
+    many = DualModEval(ck, tokenizer="bytes", device="cpu", max_length=64, gen_rows=3)
+    calls = []
+    inner = many._greedy_batch
+    many._greedy_batch = lambda prompts, max_new, stops: (calls.append(len(prompts)), inner(prompts, max_new, stops))[1]
+    reqs = [("abc", {"until": [], "max_gen_toks": 6}), ("xyz", {"until": [], "max_gen_toks": 6}),
+            ("hello", {"until": ["e"], "max_gen_toks": 6}), ("qrs", {"until": [], "max_gen_toks": 6}),
+            ("tuv", {"until": [], "max_gen_toks": 6}), ("world", {"until": ["e"], "max_gen_toks": 6}),
+            ("abc", {"until": [], "max_gen_toks": 4})]
+    assert many.generate_until(reqs) == one.generate_until(reqs)
+    # four 3-byte prompts with one budget -> batches of 3 + 1; the two 5-byte prompts together; the odd budget alone
+    assert sorted(calls) == [1, 1, 2, 3]
