@@ -93,3 +93,33 @@ def test_telemetry_runs():
     m.train()
     m(x, targets=x)[1].backward()
     assert "telemetry/L0/gradnorm_ratio_kctx_over_raw" in grad_norm_ratios(m)
+
+
+def test_corpus_tokeniser_writes_what_the_stream_reads(tmp_path):
+    import gzip
+    import json
+    import numpy as np
+    from dual_mod_public_b200.data.packed import memmap_stream
+    from dual_mod_public_b200.data.tokenize_corpus import main as tok_main
+    docs = [f"document number {i} " + "word " * (5 + i % 7) for i in range(40)]
+    with open(tmp_path / "a.jsonl", "w") as f:
+        for d in docs[:20]:
+            f.write(json.dumps({"text": d}) + "\n")
+    with gzip.open(tmp_path / "b.txt.gz", "wt") as f:
+        f.write("\n\n".join(docs[20:]) + "\n")
+    out, val = str(tmp_path / "train.bin"), str(tmp_path / "val.bin")
+    res = tok_main(["--inputs", str(tmp_path / "a.jsonl"), str(tmp_path / "b.txt.gz"), "--out", out, "--val_out", val,
+                    "--val_docs", "4", "--vocab_size", "300"])
+    assert res["val"][0] == 4 and res["train"][0] == 36
+    arr = np.fromfile(out, dtype=np.uint16)
+    assert len(arr) == res["train"][1] and json.load(open(out + ".meta.json"))["dtype"] == "uint16"
+    first = bytes(int(t) - 3 for t in arr[:len(docs[4].encode())]).decode()
+    assert first == docs[4] and arr[len(docs[4].encode())] == 2          # document, then the end-of-sequence id
+    two = tok_main(["--inputs", str(tmp_path / "*.jsonl"), str(tmp_path / "*.gz"), "--out", str(tmp_path / "t2.bin"),
+                    "--workers", "2", "--vocab_size", "300", "--budget_tokens", "400"])
+    a2 = np.fromfile(tmp_path / "t2.bin", dtype=np.uint16)
+    n0 = len(docs[0].encode())
+    assert 0 < two["train"][1] <= 400 and len(a2) == two["train"][1]
+    assert bytes(int(t) - 3 for t in a2[:n0]).decode() == docs[0] and a2[n0] == 2      # input order kept across workers
+    blk = next(memmap_stream(out, 16, 2, 0, 1))
+    assert blk.shape == (2, 17) and int(blk.max()) < 300
