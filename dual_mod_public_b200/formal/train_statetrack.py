@@ -111,7 +111,8 @@ def run_tag(args):
     core = {"group": f"{args.group}_{args.format}", "keyed": f"keyed_{args.group}_K{args.K}_D{args.D}",
             "dfa": f"dfa_{args.dfa}", "ca": f"ca{args.ca_rule}_w{args.ca_w}_{args.ca_format}",
             "matinv": f"mi_{args.mi_out}_p{args.mi_p}", "cvp": f"cvp_{args.cvp_format}_m{args.cvp_inputs}"}.get(t, t)
-    return f"{core}_n{args.n_ops}_{args.scale}_s{args.seed}{args.tag_suffix}"
+    depth = f"_L{args.n_layers}" if args.n_layers else ""
+    return f"{core}_n{args.n_ops}_{args.scale}{depth}_s{args.seed}{args.tag_suffix}"
 
 
 def word_lengths(mul, n):
@@ -378,6 +379,7 @@ def main(argv=None):
     out = os.path.join(args.out_root, "analysis", f"statetrack_{tag}_{args.arch}.json")
     with open(out, "w") as fh:
         json.dump({"task": tag, "arch": args.arch, "params": n_par, "n_ops": args.n_ops, "factors": factors,
+                   "layers": args.n_layers, "seed": args.seed,
                    "final": {str(k): v for k, v in final.items()},
                    "hist": [(s, l, {str(k): v for k, v in a.items()}) for s, l, a in hist]}, fh, indent=1)
     print(f"FINAL {tag} {args.arch}: {final} -> {out}", flush=True)

@@ -130,3 +130,18 @@ def test_checkpoint_reevaluation_and_composition_statistics(tmp_path):
     s = A.composition_stats(lg, gold, np.arange(20), 20, np.asarray(mul))
     assert s["all"]["top1"] == 0.0 and s["all"]["top5"] == 1.0 and s["all"]["mean_rank"] == 1.0
     assert s["all"]["p_wordlen_le2"] == 1.0 and s["all"]["entropy_ratio"] == 0.0 and abs(s["all"]["top5_mass"] - 1.0) < 1e-9
+
+
+def test_result_tables(tmp_path):
+    from dual_mod_public_b200.formal import summarize as S
+    for L, seed in ((1, 0), (1, 1), (2, 0)):
+        TS.main(["--task", "group", "--group", "z10", "--format", "tagged", "--n_ops", "6", "--arch", "dualmod",
+                 "--n_layers", str(L), "--steps", "3", "--bsz", "8", "--device", "cpu", "--eval_rows", "8",
+                 "--gen_factors", "1,2", "--eval_every", "50", "--seed", str(seed), "--out_root", str(tmp_path)])
+    runs = S.load(str(tmp_path / "analysis"))
+    assert len(runs) == 3 and {r["layers"] for r in runs} == {1, 2}
+    assert len(S.listing(runs)) == 4 and "x2=" in S.listing(runs)[1]
+    grid = S.depth_grid(runs, "z10", solved=0.0)
+    assert any("T=6" in l and "2/2" in l and "1/1" in l for l in grid)          # two seeds at depth 1, one at depth 2
+    assert "shallowest solving depth: {6: 1}" in grid[-1]
+    assert S.by_sidecar(runs, "pos8") and S.main([str(tmp_path / "analysis")])
