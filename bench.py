@@ -273,6 +273,70 @@ def run_reference(args):
             print(json.dumps({"impl": "reference", "unavailable": msg}), flush=True)
 
 
+def run_cpu_scan(args):
+    """BASELINE configuration 1 on the CPU, fp32: 1-layer Dual-Mod LM (d 128, 4 heads of 32, ffn 344, vocab 64,
+    tied, RoPE), T = 16, batch 8, exact sequential scan forward + backward.  Prints milliseconds per
+    forward + backward, and checks that the closed-gate model equals a vanilla Transformer layer and that
+    incremental decode equals teacher forcing.  `--impl reference` times the reference's own model."""
+    import copy
+    import time
+
+    import torch
+    ref_arm = args.impl == "reference"
+    if ref_arm:
+        ref = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref, "models", "dualmod")):
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed"}))
+            return
+        sys.path.insert(0, ref)
+        from models.dualmod.config import DualModConfig
+        from models.dualmod.model import DualModLM
+    else:
+        from dual_mod_public_b200 import DualModConfig
+        from dual_mod_public_b200.models import DualModLM
+    shape = dict(d_model=128, n_layers=1, n_heads=4, mlp_hidden_override=344, vocab_size=64, max_seq_len=64,
+                 attn_mode="sequential", checkpoint_chunk=0)
+    torch.manual_seed(0)
+    model = DualModLM(DualModConfig(**shape))
+    g = torch.Generator().manual_seed(1234)
+    idx, tgt = torch.randint(0, 64, (8, 16), generator=g), torch.randint(0, 64, (8, 16), generator=g)
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        _, loss = model(idx, tgt)
+        loss.backward()
+        return loss
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(max(50, args.steps)):
+        step()
+    ms = (time.perf_counter() - t0) * 1e3 / max(50, args.steps)
+    # closed gates == vanilla layer; decode == teacher forcing
+    with torch.no_grad():
+        closed = copy.deepcopy(model)
+        for blk in closed.blocks:
+            for gate in (blk.attn.w_gk, blk.attn.w_gv):
+                gate.weight.zero_()
+                gate.bias.fill_(20.0)
+        full = closed(idx)[0]
+        closed.cfg.attn_mode = "vanilla"
+        err_vanilla = float((closed(idx)[0] - full).abs().max())
+        teacher = model(idx)[0]
+        caches = model.decode_init()
+        dec = torch.cat([model.decode_step(idx[:, t:t + 1], t, caches) for t in range(idx.shape[1])], dim=1)
+        err_decode = float((dec - teacher).abs().max())
+    print(json.dumps({"metric": "cpu_exact_scan_fwd_bwd_ms", "value": round(ms, 3), "unit": "ms", "n_gpus": 0,
+                      "steps": max(50, args.steps), "warmup": max(3, args.warmup), "ms_per_step": round(ms, 3),
+                      "higher_is_better": False, "dtype": "fp32", "impl": args.impl,
+                      "data": "synthetic uniform token ids, random-init weights", "vs_baseline": None,
+                      "config": {"model": "1L d128 4x32 ffn344 vocab64 tied RoPE", "seq_len": 16, "batch": 8,
+                                 "threads": torch.get_num_threads()},
+                      "checks": {"closed_gates_vs_vanilla_max_abs": err_vanilla, "decode_vs_teacher_forcing_max_abs": err_decode,
+                                 "ok": err_vanilla < 1e-4 and err_decode < 1e-4}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -282,7 +346,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("DMB_MICRO_BATCH", 32)))
     ap.add_argument("--optimizer", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--config", default="340m", choices=["340m", "1p3b", "hero"],
+    ap.add_argument("--config", default="340m", choices=["340m", "1p3b", "hero", "cpu_scan"],
                     help="340m: 24L d1024 wavescan c=64 K=4 at 256 x 2048 tokens per step (the headline); "
                          "1p3b: 24L d2048 16x128 ffn5632 wavefront engine c=64 at 256 x 4096 tokens per step; "
                          "hero: the reference's 1.3B recipe (18L d2304 36x64, rank-144 mult_res write law) on the "
@@ -294,6 +358,8 @@ def main():
     ap.add_argument("--profile-seqs", type=int, default=0,
                     help="PROFILING ONLY: global batch in sequences")
     args = ap.parse_args()
+    if args.config == "cpu_scan":
+        return run_cpu_scan(args)
     global GLOBAL_SEQS, SEQ, SWEEPS, MODEL_NAME, PUBLISHED_TOK_S_PER_GPU, PUBLISHED_REF
     if args.config in ("1p3b", "hero"):
         # the reference's 1.3B step time in its engine's comments: 1.062 s per 16 384 tokens at K = 8 on one B300
