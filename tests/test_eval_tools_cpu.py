@@ -248,3 +248,15 @@ def test_generation_batches_by_prompt_length_and_matches_row_by_row(tmp_path):
     assert many.generate_until(reqs) == one.generate_until(reqs)
     # four 3-byte prompts with one budget -> batches of 3 + 1; the two 5-byte prompts together; the odd budget alone
     assert sorted(calls) == [1, 1, 2, 3]
+
+
+def test_step_model_arithmetic():
+    from dual_mod_public_b200.ops import step_model as M
+    rows = M.model()
+    N, d, ffn, K = 32 * 2048, 1024, 2816, 4
+    per_layer = 2 * N * (4 * (6 * d * d + 3 * d * ffn) + K * 3 * 4 * d * d)
+    assert rows["GEMM (layers)"][0] == per_layer * 24 * 8
+    fact = M.model(ranks=(16, 16, 16))
+    assert fact["GEMM (layers)"][0] < rows["GEMM (layers)"][0] and fact["attention"] == rows["attention"]
+    lines, total = M.report(rows, measured_ms=8000.0)
+    assert 1.0 < total < 8.0 and "of it" in lines[-1]
