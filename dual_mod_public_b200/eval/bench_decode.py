@@ -112,12 +112,17 @@ def time_decode(model, B, prompt_len, gen, dtype, device, rank, world, decoder_c
 
 
 @torch.no_grad()
-def validate(model, B, L, dtype, device):
-    """(argmax agreement graph vs eager, max |dlogit| graph vs eager, argmax agreement graph vs teacher
-    forcing, max |dlogit| vs teacher forcing) over L positions."""
+def validate(model, B, L, dtype, device, toks=None, gen=16):
+    """Graph decode against eager `decode_step` and against teacher forcing over L positions: arg-max agreement
+    and max |dlogit| for both, the drift profile (max |dlogit| vs eager per position octile), and how many of the
+    B greedy continuations of `gen` tokens are identical between the graph and the eager decoder.  `accept`
+    applies the reference validator's bar (agreement >= 99.9 %, max |dlogit| < 0.1, at least B - 1 identical
+    continuations; lm/eval/validate_graph_decode.py:97).  toks: [B, L] prompt ids (default: uniform random)."""
     cfg = model.cfg
-    g = torch.Generator().manual_seed(5)
-    toks = torch.randint(0, cfg.vocab_size, (B, L), generator=g).to(device)
+    if toks is None:
+        g = torch.Generator().manual_seed(5)
+        toks = torch.randint(0, cfg.vocab_size, (B, L), generator=g)
+    toks = toks[:B, :L].to(device)
     dec = GraphDecoder(model, B, L, dtype=dtype).capture()
     dec.reset()
     lg_graph = []
@@ -140,8 +145,26 @@ def validate(model, B, L, dtype, device):
            "max_dlogit_tf": (lg_graph - lg_tf).abs().max().item()}
     if lg_eager:
         lg_eager = torch.stack(lg_eager, 1)
+        diff = (lg_graph - lg_eager).abs().amax(dim=(0, 2))                      # per position
         out.update(agree_eager=(lg_graph.argmax(-1) == lg_eager.argmax(-1)).float().mean().item(),
-                   max_dlogit_eager=(lg_graph - lg_eager).abs().max().item())
+                   max_dlogit_eager=diff.max().item(),
+                   drift_by_octile=[round(c.max().item(), 5) for c in diff.chunk(min(8, L))])
+        # greedy continuations: graph decoder vs eager decode_step from the same prompt
+        plen = max(1, L - gen)
+        g_graph, k = dec.generate(toks[:, :plen], min(gen, L - plen))
+        with torch.autocast(torch.device(device).type, dtype=torch.bfloat16, enabled=amp):
+            caches, lg = model.decode_init(), None
+            for t in range(plen):
+                lg = model.decode_step(toks[:, t:t + 1], t, caches)
+            g_eager = []
+            for j in range(k):
+                nxt = lg[:, -1].argmax(-1, keepdim=True)
+                g_eager.append(nxt)
+                if j < k - 1:
+                    lg = model.decode_step(nxt, plen + j, caches)
+        same = int((g_graph.to(device) == torch.cat(g_eager, 1)).all(dim=1).sum()) if k else B
+        out.update(identical_continuations=same, continuations=B,
+                   accept=bool(out["agree_eager"] >= 0.999 and out["max_dlogit_eager"] < 0.1 and same >= B - 1))
     return out
 
 
@@ -152,6 +175,9 @@ def main(argv=None):
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--gen", type=int, default=512)
     ap.add_argument("--validate", action="store_true")
+    ap.add_argument("--ckpt", default="", help="validate / time the model of this checkpoint instead of a random-init preset")
+    ap.add_argument("--tokens_bin", default="", help="--validate: prompts from this flat token file instead of random ids")
+    ap.add_argument("--val_len", type=int, default=96, help="--validate: positions compared")
     ap.add_argument("--device", default="")
     ap.add_argument("--arms", default="dualmod,vanilla")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
@@ -173,10 +199,23 @@ def main(argv=None):
             except Exception as e:
                 out = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
                 break
+        elif args.ckpt:
+            from ..utils.checkpoint import load_checkpoint, model_from_checkpoint
+            model = model_from_checkpoint(load_checkpoint(args.ckpt), device=device, ctx_len=args.prompt + args.gen)
+            cfg, dt = model.cfg, (torch.bfloat16 if "cuda" in device else torch.float32)
+            if mode == "vanilla" and cfg.attn_mode != "vanilla":
+                continue                                     # a checkpoint has one operator: no control arm
+            out["model"] = args.ckpt
         else:
             cfg, model, dt = build(args.model, mode, device, args.prompt + args.gen)
         if args.validate:
-            out[arm] = validate(model, min(args.batch, 4), min(args.prompt + args.gen, 96), dt, device)
+            toks = None
+            if args.tokens_bin:
+                import numpy as np
+                n, L = min(args.batch, 4), min(args.prompt + args.gen, args.val_len)
+                arr = np.fromfile(args.tokens_bin, dtype=np.uint16, count=n * L).astype(np.int64)
+                toks = torch.from_numpy(arr).view(n, L) % cfg.vocab_size
+            out[arm] = validate(model, min(args.batch, 4), min(args.prompt + args.gen, args.val_len), dt, device, toks)
         else:
             out[arm] = {k: (round(v, 4) if isinstance(v, float) else v)
                         for k, v in time_decode(model, args.batch, args.prompt, args.gen, dt, device, rank, world, dec_cls).items()}

@@ -103,6 +103,8 @@ def test_decode_validator_and_engine_validator():
     for arm in ("dualmod", "vanilla"):
         assert out[arm]["agree_tf"] >= 0.999 and out[arm]["max_dlogit_tf"] < 1e-4
         assert out[arm]["agree_eager"] >= 0.999 and out[arm]["max_dlogit_eager"] < 1e-4
+        assert out[arm]["accept"] and out[arm]["identical_continuations"] == out[arm]["continuations"]
+        assert len(out[arm]["drift_by_octile"]) == 8
     from dual_mod_public_b200.train.validate_engine import main as val_main
     lines = []
     res = val_main(["--engine", "wavescan", "--T", "32", "--C", "8", "--d", "64", "--W", "12", "--ladder", "2",
@@ -260,3 +262,14 @@ def test_step_model_arithmetic():
     assert fact["GEMM (layers)"][0] < rows["GEMM (layers)"][0] and fact["attention"] == rows["attention"]
     lines, total = M.report(rows, measured_ms=8000.0)
     assert 1.0 < total < 8.0 and "of it" in lines[-1]
+
+
+def test_decode_validator_takes_a_checkpoint_and_real_tokens(tmp_path):
+    import numpy as np
+    from dual_mod_public_b200.eval.bench_decode import main as dec_main
+    m = tiny(vocab=300, T=128)
+    save_checkpoint(str(tmp_path), m, step=2)
+    np.arange(2000, dtype=np.uint16).tofile(tmp_path / "toks.bin")
+    out = dec_main(["--ckpt", os.path.join(tmp_path, "ckpt_latest.pt"), "--validate", "--device", "cpu", "--val_len", "40",
+                    "--prompt", "32", "--gen", "8", "--tokens_bin", str(tmp_path / "toks.bin")])
+    assert "vanilla" not in out and out["dualmod"]["accept"] and out["model"].endswith("ckpt_latest.pt")
