@@ -198,6 +198,8 @@ def preset(name: str, **overrides) -> DualModConfig:
     `dm_1p3b`   24 x d=2048, 16 heads x 128, ffn 5632, vocab 32000
     `hero_1p3b` the reference's 18 x d=2304 rank-144 mult_res recipe
                 (engines/wave3d/config_1p3b.py:18-51)
+    `dm_d960`   the reference's 340M run: 26 x d=960, 15 heads x 64, rank-120 mult_res write law, per-head key
+                norm, one raw-pinned head, value clamp 150 (lm/train_340m/scripts/launch_dm_d960.sh:17-24)
     """
     shapes = {
         "tiny_cpu": dict(d_model=128, n_layers=1, n_heads=4, mlp_hidden_override=344,
@@ -212,6 +214,9 @@ def preset(name: str, **overrides) -> DualModConfig:
                           max_seq_len=4096, ctx_mod="mult_res", gate_rank=144, ctx_rank=144,
                           k_ctx_norm="rms", kmod_vraw_heads=1, v_clamp_tau=150.0,
                           gate_bias_init=4.0),
+        "dm_d960": dict(d_model=960, n_layers=26, n_heads=15, vocab_size=32000, max_seq_len=2048,
+                        ctx_mod="mult_res", gate_rank=120, ctx_rank=120, k_ctx_norm="rms", k_gain_init=1.75,
+                        kmod_vraw_heads=1, v_clamp_tau=150.0, gate_bias_init=0.0),
     }
     kw = dict(shapes[name])
     kw.update(overrides)

@@ -7,6 +7,12 @@
 # Reference parity: lm/train_340m/scripts/launch_dm_d960.sh, scripts/launch_torchrun.sh.
 set -euo pipefail
 NGPU=${NGPU:-8}
+# RECIPE=340m: the benchmark shape (24 x d1024, dense linear write law).  RECIPE=d960: the reference's own 340M run
+# (26 x d960, rank-120 mult_res write law) under its protocol: batch 256, 30k steps, lr 4e-4 trunk / 3e-4 Dual-Mod
+# parameters, calibrated clip at 2x, skip factor 20 (lm/train_340m/scripts/launch_dm_d960.sh).
+RECIPE=${RECIPE:-340m}
+RECIPE_ARGS=()
+[ "$RECIPE" = d960 ] && RECIPE_ARGS=(--protocol pdn --dm_lr 3e-4 --clip_mult 2.0 --skip_factor 20 --seed 42)
 OUT=${OUT:-out/dm340}
 DATA_BIN=${DATA_BIN:-}
 VAL_BIN=${VAL_BIN:-}
@@ -21,6 +27,6 @@ DATA_ARGS=(--synthetic)
 [ -n "$DATA_BIN" ] && DATA_ARGS=(--data_bin "$DATA_BIN")
 [ -n "$VAL_BIN" ] && DATA_ARGS+=(--val_bin "$VAL_BIN" --val_every 500)
 exec python -m torch.distributed.run --nnodes=1 --nproc-per-node "$NGPU" --master-addr 127.0.0.1 --master-port "$PORT" \
-  -m dual_mod_public_b200.train.train_lm --recipe 340m --out_dir "$OUT" --total_steps "$STEPS" \
+  -m dual_mod_public_b200.train.train_lm --recipe "$RECIPE" "${RECIPE_ARGS[@]}" --out_dir "$OUT" --total_steps "$STEPS" \
   --warmup_steps "$WARMUP" --weight_decay 0.01 --ckpt_every 500 --async_ckpt --resume auto --auto_rewind \
   "${DATA_ARGS[@]}" "$@"

@@ -48,6 +48,8 @@ RECIPES = {
     # name: (model preset, engine, seq_len, global sequences, rungs (c, K), phase bounds, micro-batch)
     "tiny": ("tiny_cpu", "wavescan", 64, 8, ((16, 2), (16, 4), (16, 16)), (0.3, 0.7), 4),
     "340m": ("dm_340m", "wavescan", 2048, 256, ((64, 8), (64, 16), (64, 32), (64, 64)), (0.075, 0.70), 32),
+    # the reference's own 340M run (its launch script passes --protocol pdn --dm_lr 3e-4 --clip_mult 2 --skip_factor 20)
+    "d960": ("dm_d960", "wavescan", 2048, 256, ((64, 8), (64, 16), (64, 32), (64, 64)), (0.075, 0.70), 32),
     "1p3b": ("dm_1p3b", "wave3d", 4096, 256, ((64, 2), (64, 4), (64, 8)), (0.10, 0.60), 16),
     "hero": ("hero_1p3b", "wave3d", 4096, 128, ((64, 8), (64, 16), (64, 24)), (0.10, 0.60), 16),
 }

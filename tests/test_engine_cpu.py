@@ -306,3 +306,26 @@ def test_factored_write_law_equals_composed_matrices(kw, monkeypatch):
     for n in gg:
         assert relerr(gf[n], gd[n]) < 1e-4, n
         assert relerr(gf[n], gg[n]) < 1e-4, n
+
+
+def test_odd_head_count_of_the_d960_recipe():
+    """15 heads at d = 960 in the reference's 340M run: a head count that is not a multiple of 4, with factored
+    mult_res operators.  Scaled down (3 heads of 32), fused statement against autograd."""
+    from dual_mod_public_b200 import preset
+    from dual_mod_public_b200.engines.wavescan import refine_family
+    full = preset("dm_d960")
+    assert full.n_heads == 15 and full.head_dim == 64 and refine_family(full) == "mrk"
+    cfg, m = build(d_model=96, n_heads=3, ctx_mod="mult_res", gate_rank=8, ctx_rank=8, k_ctx_norm="rms", kmod_vraw_heads=1,
+                   v_clamp_tau=2.0)
+    B, T = 2, 24
+    g = torch.Generator().manual_seed(9)
+    idx = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    sched = uniform_chunks(T, 8, 3)
+    e_f = WaveScanEngine(m, [sched], B, T, backend="fused", ops=TorchOps())
+    e_g = WaveScanEngine(m, [sched], B, T, backend="generic", ops=TorchOps())
+    lf, gf = _engine_grads(m, e_f, idx, tgt)
+    lg, gg = _engine_grads(m, e_g, idx, tgt)
+    assert e_f.factored and abs(lf.item() - lg.item()) < 1e-5
+    for n in gg:
+        assert relerr(gf[n], gg[n]) < 1e-4, n
