@@ -96,7 +96,8 @@ def run(inputs, tokenizer, out, val_out="", val_docs=0, budget_tokens=0, workers
             counts[split][1] += len(ids)
 
     if workers > 1:
-        with ProcessPoolExecutor(max_workers=workers) as ex:
+        import multiprocessing
+        with ProcessPoolExecutor(max_workers=workers, mp_context=multiprocessing.get_context("spawn")) as ex:
             for docs in ex.map(encode_file, jobs):                  # results come back in input order
                 consume(docs)
                 if done:
