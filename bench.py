@@ -346,7 +346,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("DMB_MICRO_BATCH", 32)))
     ap.add_argument("--optimizer", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--config", default="340m", choices=["340m", "1p3b", "hero", "cpu_scan"],
+    ap.add_argument("--config", default="340m", choices=["340m", "1p3b", "hero", "d960", "cpu_scan"],
                     help="340m: 24L d1024 wavescan c=64 K=4 at 256 x 2048 tokens per step (the headline); "
                          "1p3b: 24L d2048 16x128 ffn5632 wavefront engine c=64 at 256 x 4096 tokens per step; "
                          "hero: the reference's 1.3B recipe (18L d2304 36x64, rank-144 mult_res write law) on the "
@@ -379,6 +379,13 @@ def main():
         MODEL_NAME = "hero_1p3b (18L d2304 36x64 rank-144 mult_res, k_ctx_norm rms, v_clamp 150, 1 raw head)"
         if "DMB_MICRO_BATCH" not in os.environ and args.micro_batch == 32:
             args.micro_batch = 16                       # 8 % faster per token than 8; about 95 GB at 18 layers
+    if args.config == "d960":
+        # the reference's own 340M run (26 x d960, 15 heads x 64, rank-120 mult_res write law) on the cell engine
+        MODEL.clear()
+        MODEL.update(d_model=960, n_layers=26, n_heads=15, vocab_size=32000, max_seq_len=2048, ctx_mod="mult_res",
+                     gate_rank=120, ctx_rank=120, k_ctx_norm="rms", k_gain_init=1.75, kmod_vraw_heads=1,
+                     v_clamp_tau=150.0, gate_bias_init=0.0)
+        MODEL_NAME = "dm_d960 (26L d960 15x64 rank-120 mult_res, k_ctx_norm rms, v_clamp 150, 1 raw head)"
     if args.sweeps:
         SWEEPS = args.sweeps
     global PROFILING
