@@ -116,6 +116,31 @@ def timed_steps(torch, dist, world, fn, steps):
     return ms.item() / steps
 
 
+def params_checksum(torch, dist, world, tensors):
+    """64-bit sum of the parameters' bit patterns on this rank, and whether every rank holds the same
+    one (all-reduce MAX and MIN agree).  A bitwise statement: data-parallel ranks never re-synchronise,
+    so equal bytes after the timed steps is what shows the distributed update computed one model."""
+    tot = torch.zeros((), dtype=torch.int64, device="cuda")
+    for t in tensors:
+        tot += t.detach().contiguous().view(-1).view(torch.int32).to(torch.int64).sum()
+    if world == 1:
+        return int(tot), None
+    hi, lo = tot.clone(), tot.clone()
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    return int(tot), bool(hi == lo)
+
+
+def shared_config(world, micro, graphs):
+    """The facts both arms share, in the same words (arm-specific text goes under `impl_detail`)."""
+    return {"model": MODEL_NAME + (" PROFILING SHAPE, NOT A BENCH VALUE" if PROFILING else ""),
+            "chunk": CHUNK, "sweeps": SWEEPS, "global_batch": GLOBAL_SEQS, "seq_len": SEQ, "micro_batch": micro,
+            "parallelism": f"dp{world}", "optimizer": "AdamW lr 3e-4 betas (0.9, 0.95) wd 0.01 on matrices, clip 1.0",
+            "cuda_graphs": graphs,
+            "l2": "per-step working set is tens of GB (>> 126 MB L2); no explicit flush",
+            "vs_baseline_ref": PUBLISHED_REF}
+
+
 def synthetic_tokens(torch, local_seqs, rank, n_sets, vocab):
     g = torch.Generator().manual_seed(1234 + rank)
     return [torch.randint(0, vocab, (local_seqs, SEQ + 1), generator=g).pin_memory() for _ in range(n_sets)]
@@ -140,8 +165,10 @@ def run_ours(args):
                  engine="wave3d" if wave3d else "wavescan", engine_kwargs=dict(C=CHUNK) if wave3d else None)
     host = synthetic_tokens(torch, local_seqs, rank, 2, cfg.vocab_size)
     dev = [t.cuda() for t in host]
+    loss_first = None
     for i in range(args.warmup):
-        tr.step(host[i % 2])
+        loss = tr.step(host[i % 2])
+        loss_first = loss if loss_first is None else loss_first
     tr.opt.check_status() if hasattr(tr.opt, "check_status") else None
     ops = tr.engine.ops
     sampler = ClockSampler(local)
@@ -150,10 +177,13 @@ def run_ours(args):
     l0 = ops.launches
     ms = timed_steps(torch, dist, world, lambda i: tr.step(dev[i % 2], read_loss=False), args.steps)
     launches = (ops.launches - l0) if not tr.engine.use_graphs else None
-    ms_e2e = timed_steps(torch, dist, world, lambda i: tr.step(host[i % 2]), args.steps)
+    losses = []
+    ms_e2e = timed_steps(torch, dist, world, lambda i: losses.append(tr.step(host[i % 2])), args.steps)
     clocks = sampler.stop() if rank == 0 else None
     if hasattr(tr.opt, "check_status"):
         tr.opt.check_status()
+    flat = [tr.opt.flat_params] if hasattr(tr.opt, "flat_params") else list(tr.model.parameters())
+    checksum, identical = params_checksum(torch, dist, world, flat)
     tokens = GLOBAL_SEQS * SEQ
     if launches is None:          # under graph replay the table is not called: count graph nodes instead
         launches = tr.engine.graph_kernel_count() * tr.accum * args.steps
@@ -165,14 +195,14 @@ def run_ours(args):
                "vs_baseline": round(value / (PUBLISHED_TOK_S_PER_GPU * world), 3),
                "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
                "impl": "ours",
-               "config": {"model": MODEL_NAME
-                          + (" PROFILING SHAPE, NOT A BENCH VALUE" if PROFILING else ""),
-                          "engine": f"{'wavefront (wave3d operator)' if wave3d else 'wavescan'} c={CHUNK} K={SWEEPS}",
-                          "global_batch": GLOBAL_SEQS, "seq_len": SEQ,
-                          "micro_batch": micro, "parallelism": f"dp{world}", "optimizer": args.optimizer,
-                          "cuda_graphs": tr.engine.use_graphs,
-                          "l2": "per-step working set is tens of GB (>> 126 MB L2); no explicit flush",
-                          "vs_baseline_ref": PUBLISHED_REF},
+               "config": shared_config(world, micro, tr.engine.use_graphs),
+               "impl_detail": {"engine": ("Wave3DEngine (wavefront operator)" if wave3d else "WaveScanEngine")
+                                         + ", hand-written sm_100a kernels",
+                               "optimizer": {"fused": "one kernel: P2P reduce-scatter + clip + AdamW + all-gather",
+                                             "nccl": "NCCL all-reduce + torch fused AdamW"}[args.optimizer]},
+               "loss_first": round(loss_first, 4) if loss_first is not None else None,
+               "loss_last": round(losses[-1], 4) if losses else None,
+               "params_checksum": checksum, "params_identical_across_ranks": identical,
                "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
                        "ms_per_step": round(ms_e2e, 2),
                        "h2d_bytes_per_step": tr.h2d_bytes_per_step(), "d2h_bytes_per_step": tr.d2h_bytes_per_step()},
@@ -240,14 +270,18 @@ def run_reference(args):
                 torch.cuda.current_stream().synchronize()
                 return float(loss_host)
 
+        loss_first = None
         for i in range(args.warmup):
-            step(host[i % 2], True)
+            loss = step(host[i % 2], True)
+            loss_first = loss if loss_first is None else loss_first
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
         ms = timed_steps(torch, dist, world, lambda i: step(dev[i % 2], False), args.steps)
-        ms_e2e = timed_steps(torch, dist, world, lambda i: step(host[i % 2], True), args.steps)
+        losses = []
+        ms_e2e = timed_steps(torch, dist, world, lambda i: losses.append(step(host[i % 2], True)), args.steps)
         clocks = sampler.stop() if rank == 0 else None
+        checksum, identical = params_checksum(torch, dist, world, params)
         tokens = GLOBAL_SEQS * SEQ
         if rank == 0:
             value = tokens / (ms / 1e3)
@@ -257,10 +291,13 @@ def run_reference(args):
                 "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": round(value / (PUBLISHED_TOK_S_PER_GPU * world), 3), "dtype": "bf16",
                 "data": "synthetic uniform token ids, random-init weights", "impl": "reference",
-                "config": {"model": "dm_340m (24L d1024 16x64 ffn2816 vocab32000 tied)",
-                           "engine": "reference WaveScanEngine fused_sweep c=64 K=4", "global_batch": GLOBAL_SEQS,
-                           "seq_len": SEQ, "micro_batch": micro, "parallelism": f"dp{world}",
-                           "cuda_graphs": not args.no_graphs},
+                "config": shared_config(world, micro, not args.no_graphs),
+                "impl_detail": {"engine": "reference WaveScanEngine(autocast_bf16, use_graphs, fused_sweep, "
+                                          "share_layer_pools), Triton sweeps + cuBLAS",
+                                "optimizer": "finish_grads (NCCL reduce + broadcast) + clip_grad_norm_ + torch AdamW"},
+                "loss_first": round(loss_first, 4) if loss_first is not None else None,
+                "loss_last": round(losses[-1], 4) if losses else None,
+                "params_checksum": checksum, "params_identical_across_ranks": identical,
                 "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 2),
                         "h2d_bytes_per_step": local_seqs * (SEQ + 1) * 8, "d2h_bytes_per_step": 4},
                 "clocks": clocks}), flush=True)
@@ -270,6 +307,113 @@ def run_reference(args):
     except Exception as e:  # the reference pins torch 2.12 / triton 3.7; report why it cannot run here
         if int(os.environ.get("RANK", 0)) == 0:
             msg = f"{type(e).__name__}: {e}".replace("\n", " ")[:300]
+            print(json.dumps({"impl": "reference", "unavailable": msg}), flush=True)
+
+
+def run_reference_wave3d(args):
+    """The unmodified reference (baseline/_ref) on its own 1.3B recipe: `build_config` (18L d2304 36x64,
+    rank-144 mult_res), `make_engine(model, B, T, engine="x", C=64, graphs=True)` through the trainer's own
+    `build_engine`, and the step of lm/train_1p3b/train_hero_wave3d.py:848-997 without its governors:
+    micro-batches of B sequences under bf16 autocast, loss / accum, backward, `GradAllReducer`, clip at 1.0,
+    fused torch AdamW on fp32 parameters."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    src = os.path.join(ref, "lm", "train_1p3b", "train_hero_wave3d.py")
+    if not os.path.isfile(src):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed"}))
+        return
+    sys.path.insert(0, ref)
+    os.environ.setdefault("REPO_ROOT", ref)
+    try:
+        import importlib.util
+
+        import torch
+        import torch.distributed as dist
+        rank, world, local = dist_setup(args.gpus)
+        spec = importlib.util.spec_from_file_location("ref_train_hero_wave3d", src)
+        hero = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(hero)
+        local_seqs = GLOBAL_SEQS // world
+        micro = min(args.ref_micro_batch, local_seqs)
+        accum = local_seqs // micro
+        torch.manual_seed(1337)
+        cfg = hero.build_config(seq_len=SEQ)
+        cfg.gate_init_seed, cfg.gate_bias_init = 1337, 0.0            # as the trainer sets them
+        model = hero.DualModLM(cfg).cuda().float()
+        decay = [p for p in model.parameters() if p.dim() >= 2]
+        nodecay = [p for p in model.parameters() if p.dim() < 2]
+        opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.01},
+                                 {"params": nodecay, "weight_decay": 0.0}], lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
+                                fused=True)
+        kw = {"graphs": not args.no_graphs}
+        if args.ref_attn:
+            kw["attn_impl"] = args.ref_attn
+        engine = hero.build_engine(model, micro, SEQ, "x", kw, args.ref_compile, cudnn_ws_gb=1.0)
+        reducer = hero.GradAllReducer(model.parameters(), world)
+        params = list(model.parameters())
+        host = synthetic_tokens(torch, local_seqs, rank, 2, cfg.vocab_size)
+        dev = [t.cuda() for t in host]
+        loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+        model.train()
+        opt.zero_grad(set_to_none=True)
+
+        def step(tokens, read_loss):
+            loss_acc = torch.zeros((), device="cuda")
+            for a in range(accum):
+                blk = tokens[a * micro:(a + 1) * micro].cuda(non_blocking=True)
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss_t = engine.forward(blk[:, :SEQ], blk[:, 1:SEQ + 1], SWEEPS)
+                (loss_t * (1.0 / accum)).backward()
+                loss_acc += loss_t.detach()
+            reducer()
+            torch.nn.utils.clip_grad_norm_(params, 1.0)
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            if read_loss:
+                loss_host.copy_(loss_acc / accum, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                return float(loss_host)
+
+        loss_first = None
+        for i in range(args.warmup):
+            loss = step(host[i % 2], True)
+            loss_first = loss if loss_first is None else loss_first
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        ms = timed_steps(torch, dist, world, lambda i: step(dev[i % 2], False), args.steps)
+        losses = []
+        ms_e2e = timed_steps(torch, dist, world, lambda i: losses.append(step(host[i % 2], True)), args.steps)
+        clocks = sampler.stop() if rank == 0 else None
+        checksum, identical = params_checksum(torch, dist, world, params)
+        tokens = GLOBAL_SEQS * SEQ
+        if rank == 0:
+            value = tokens / (ms / 1e3)
+            print(json.dumps({
+                "metric": "train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 2),
+                "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": round(value / (PUBLISHED_TOK_S_PER_GPU * world), 3), "dtype": "bf16",
+                "data": "synthetic uniform token ids, random-init weights", "impl": "reference",
+                "config": shared_config(world, micro, not args.no_graphs),
+                "impl_detail": {"engine": f"reference Wave3DX via make_engine(engine='x', C=64, graphs, "
+                                          f"attn_impl={args.ref_attn or 'cudnn_fe'}, fused_refine), "
+                                          f"set_compile('{args.ref_compile}')",
+                                "optimizer": "GradAllReducer (NCCL all-reduce AVG) + clip_grad_norm_ + fused torch AdamW",
+                                "engine_mem": {k: (round(v, 2) if isinstance(v, float) else v)
+                                               for k, v in getattr(engine, "mem", {}).items()
+                                               if isinstance(v, (int, float))}},
+                "loss_first": round(loss_first, 4) if loss_first is not None else None,
+                "loss_last": round(losses[-1], 4) if losses else None,
+                "params_checksum": checksum, "params_identical_across_ranks": identical,
+                "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 2),
+                        "h2d_bytes_per_step": local_seqs * (SEQ + 1) * 8, "d2h_bytes_per_step": 4},
+                "clocks": clocks, "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+    except Exception as e:
+        if int(os.environ.get("RANK", 0)) == 0:
+            msg = f"{type(e).__name__}: {e}".replace("\n", " ")[:400]
             print(json.dumps({"impl": "reference", "unavailable": msg}), flush=True)
 
 
@@ -352,6 +496,11 @@ def main():
                          "hero: the reference's 1.3B recipe (18L d2304 36x64, rank-144 mult_res write law) on the "
                          "wavefront engine at 128 x 4096 tokens per step, K=8")
     ap.add_argument("--sweeps", type=int, default=0, help="sweeps K (default 4; the 1.3B ladder is 2 / 4 / 8)")
+    ap.add_argument("--ref-micro-batch", type=int, default=4,
+                    help="hero reference arm: sequences per engine call (the reference's own runs use 4)")
+    ap.add_argument("--ref-compile", default="all", choices=["none", "refine", "all"],
+                    help="hero reference arm: the trainer's --engine_compile (its default is all)")
+    ap.add_argument("--ref-attn", default="", help="hero reference arm: attn_impl override (cudnn_fe | cudnn | flash)")
     ap.add_argument("--profile-layers", type=int, default=0,
                     help="PROFILING ONLY: shrink the model to this many layers (the printed line is then "
                          "not a benchmark value and says so)")
@@ -396,7 +545,18 @@ def main():
         GLOBAL_SEQS = args.profile_seqs
     if not profiling:
         args.warmup = max(args.warmup, 3)
-    (run_reference if args.impl == "reference" else run_ours)(args)
+    if args.impl == "reference":
+        if args.config == "hero":
+            return run_reference_wave3d(args)
+        if args.config == "1p3b":
+            # the reference's wavefront engine refuses this model (check_cfg, engines/wave3d/wave3d_ops.py:31-43:
+            # mult_res write law with LoRA gates and operators only), and its cell engine was never run at 1.3B
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "the reference wave3d engine accepts only its mult_res / LoRA configuration family "
+                              "(check_cfg); use --config hero for a same-box 1.3B comparison"}), flush=True)
+            return
+        return run_reference(args)
+    run_ours(args)
 
 
 if __name__ == "__main__":

@@ -20,7 +20,11 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libdmb200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-O3"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-O3"]
+# Fast math (approximate exp / division / sqrt, flush-to-zero) is a choice for the bf16 activation kernels,
+# whose results are rounded to 8 mantissa bits anyway.  The optimizer updates fp32 master weights and
+# moments and is compiled with IEEE division and square root.
+PRECISE = {"fused_optim.cu"}
 
 
 def _nvcc() -> str:
@@ -46,7 +50,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for s in sources:
         src, obj = os.path.join(SRC, s), os.path.join(OBJ, s[:-3] + ".o")
         if force or _stale(obj, [src] + headers):
-            jobs.append([nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj])
+            fast = [] if s in PRECISE else ["--use_fast_math"]
+            jobs.append([nvcc] + NVCC_FLAGS + fast + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj])
 
     def run(cmd):
         r = subprocess.run(cmd, capture_output=True, text=True)

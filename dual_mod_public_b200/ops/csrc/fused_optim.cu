@@ -46,7 +46,7 @@ struct DmbOptPlan {
 };
 
 struct DmbOptHyper {
-  float lr, beta1, beta2, eps, bias1, bias2;   // bias_i = 1 - beta_i^t
+  float lr, beta1, beta2, eps;
   float grad_scale;                            // 1 / (world * accum)
   float max_norm;                              // <= 0: no clipping
   float skip_norm;                             // > 0: skip the update when gnorm exceeds it
@@ -55,8 +55,12 @@ struct DmbOptHyper {
 };
 
 // status word layout (host-visible): [0] error code (0 ok, 1 start barrier, 2 norm exchange,
-// 3 end barrier), [1] peer that was missing, [2] skipped flag, [3] spare
-// ctrl floats: [0] global grad norm, [1] clip coefficient, [2] skip (0/1)
+// 3 end barrier), [1] peer that was missing, [2] skipped flag, [3] number of APPLIED updates so far
+// (the AdamW step t: a skipped step does not advance it, as with torch.optim.AdamW when step() is
+// not called)
+// ctrl floats: [0] global grad norm, [1] clip coefficient, [2] skip (0/1), [3] spare (callers),
+// [4] t, [5] 1 - beta1^t, [6] 1 - beta2^t, [7] the error code of status[0], so that one host copy of
+// ctrl carries the verdict of the step and the health of the waits
 
 namespace {
 
@@ -174,7 +178,7 @@ __global__ void __launch_bounds__(512) fused_step_kernel(
     int n_early_partials, float* __restrict__ ctrl, unsigned* __restrict__ status) {
   cg::grid_group grid = cg::this_grid();
   __shared__ float sred[32];
-  __shared__ float s_coef, s_skip;
+  __shared__ float s_coef, s_skip, s_bias1, s_bias2;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
 
@@ -216,22 +220,33 @@ __global__ void __launch_bounds__(512) fused_step_kernel(
       const bool skip = !isfinite(gn) || (hp.skip_norm > 0.f && gn > hp.skip_norm) || status[0] != 0;
       ctrl[0] = gn; ctrl[1] = coef; ctrl[2] = skip ? 1.f : 0.f;
       status[2] = skip ? 1u : 0u;
+      unsigned t = status[3];
+      if (!skip) status[3] = ++t;
+      const double td = t ? (double)t : 1.0;
+      ctrl[4] = (float)t;
+      ctrl[5] = (float)(1.0 - pow((double)hp.beta1, td));
+      ctrl[6] = (float)(1.0 - pow((double)hp.beta2, td));
+      ctrl[7] = (float)status[0];
       __threadfence();
     }
   }
   grid.sync();
-  if (threadIdx.x == 0) { s_coef = ctrl[1]; s_skip = ctrl[2]; }
+  if (threadIdx.x == 0) { s_coef = ctrl[1]; s_skip = ctrl[2]; s_bias1 = ctrl[5]; s_bias2 = ctrl[6]; }
   __syncthreads();
   const float coef = s_coef;
 
   // ---- phase 3: AdamW on the owned slices + all-gather by peer stores -----------------------------
   if (s_skip == 0.f) {
-    const float step_size = hp.lr / hp.bias1, inv_sqrt_b2 = rsqrtf(hp.bias2);
+    const float step_size = hp.lr / s_bias1, inv_sqrt_b2 = rsqrtf(s_bias2);
     for (int b = 0; b < plan.n_buckets; ++b) {
       const long long slice = plan.bucket_len[b] / c.world;
       const long long base = plan.bucket_off[b] + (long long)c.rank * slice, mo = plan.moment_off[b];
+      // one binary search per thread and bucket; after it the thread's index only grows, so the
+      // parameter it falls into is found by walking forward (a float4 never straddles two parameters:
+      // every parameter starts on a 64-element boundary)
+      int sg = tid * 4 < slice ? find_seg(seg_start, plan.n_segs, base + tid * 4) : 0;
       for (long long i = tid * 4; i < slice; i += nthreads * 4) {
-        const int sg = find_seg(seg_start, plan.n_segs, base + i);
+        while (sg + 1 < plan.n_segs && seg_start[sg + 1] <= base + i) ++sg;
         const float wd = seg_wd[sg], lrm = seg_lr[sg];
         float4 g = *reinterpret_cast<const float4*>(c.grads[c.rank] + base + i);
         float4 p = *reinterpret_cast<const float4*>(c.params[c.rank] + base + i);
@@ -262,6 +277,8 @@ __global__ void __launch_bounds__(512) fused_step_kernel(
   if (blockIdx.x == 0) {
     int miss = flag_barrier(c, 2, hp.epoch, hp.wait_cycles);
     if (miss >= 0 && status[0] == 0) { status[0] = 3; status[1] = miss; }
+    __syncthreads();
+    if (threadIdx.x == 0) ctrl[7] = (float)status[0];
   }
 }
 

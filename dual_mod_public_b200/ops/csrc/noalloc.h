@@ -42,7 +42,8 @@ extern "C" {
 int dmb_col_reduce_acc_noalloc(const void* dy, int dy_f32, const void* x, long long xs, const float* rstd,
                                float* out, int rows, int d, cudaStream_t st);
 
-// Text of the last refusal of dmb_col_reduce_acc_noalloc on this host thread's process ("" if none).
+// Text of the calling host thread's last refusal by dmb_col_reduce_acc_noalloc ("" if its last call was
+// accepted).  The buffer is per host thread; the pointer stays valid for that thread's lifetime.
 const char* dmb_noalloc_last_error();
 
 // The ordinary entry point, with caller-provided scratch of nsplit * d floats.

@@ -296,8 +296,10 @@ int dmb_col_reduce_acc(const void* dy, int dy_f32, const void* x, long long xs, 
 // memory.  Every entry the second kernel reads is written by the first one in the same call, so
 // nothing in the array has to start at zero and the previous call's contents do not matter.
 static __device__ __align__(256) float g_noalloc_partials[DMB_NOALLOC_MAX_SPLIT * DMB_NOALLOC_MAX_COLS];
+// per-device address cache: two host threads that race through the first call on a device both
+// store the same address, so the slot needs no lock
 static float* g_noalloc_ptr[DMB_NOALLOC_MAX_DEVICES] = {nullptr};
-static char g_noalloc_err[256] = "";
+static thread_local char g_noalloc_err[256] = "";   // one message buffer per calling host thread
 
 const char* dmb_noalloc_last_error() { return g_noalloc_err; }
 

@@ -57,7 +57,7 @@ class _Plan(ctypes.Structure):
 
 class _Hyper(ctypes.Structure):
     _fields_ = [("lr", ctypes.c_float), ("beta1", ctypes.c_float), ("beta2", ctypes.c_float),
-                ("eps", ctypes.c_float), ("bias1", ctypes.c_float), ("bias2", ctypes.c_float),
+                ("eps", ctypes.c_float),
                 ("grad_scale", ctypes.c_float), ("max_norm", ctypes.c_float),
                 ("skip_norm", ctypes.c_float), ("epoch", ctypes.c_uint),
                 ("wait_cycles", ctypes.c_longlong)]
@@ -69,6 +69,10 @@ class _RawCuda:
     def __init__(self, ptr, nbytes):
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
                                          "version": 2}
+
+
+class PeerWaitExpired(RuntimeError):
+    """A bounded cross-GPU wait of the optimizer kernels ran out (a peer is lost or far behind)."""
 
 
 def _ck(rc, what):
@@ -214,6 +218,10 @@ class FusedDPAdamW:
         assert grouped == {id(p) for p in self.layout.params}, "groups and buckets must cover the same parameters"
         self.device = torch.device(device) if device is not None else self.layout.params[0].device
         self.use_kernel = self.device.type == "cuda" if use_kernel is None else use_kernel
+        # AdamW's t counts APPLIED updates only (a step voided by the skip predicate does not advance it,
+        # as torch.optim.AdamW's `step` does not when step() is not called).  On the kernel path the
+        # counter lives on the device (status[3]) because the skip decision is taken there; the host
+        # attribute mirrors it for the host statement and is refreshed by `applied_steps()`.
         self.step_count = 0
         self.epoch = 0
         # set for one step by a caller that excluded ranks from the average (their gradients zeroed):
@@ -245,7 +253,8 @@ class FusedDPAdamW:
         self.m = torch.zeros(n_own, dtype=torch.float32, device=self.device)
         self.v = torch.zeros(n_own, dtype=torch.float32, device=self.device)
         self._build_segments()
-        self.ctrl = torch.zeros(4, dtype=torch.float32, device=self.device)
+        # ctrl: [grad norm, clip coefficient, skipped, spare, t, 1 - beta1^t, 1 - beta2^t, wait error code]
+        self.ctrl = torch.zeros(8, dtype=torch.float32, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._reduced = [0] * len(self.layout.buckets)
         self._early_partials = 0
@@ -312,14 +321,20 @@ class FusedDPAdamW:
         self._early_partials = 0
 
     # ---- the step ------------------------------------------------------------------------------------
+    def _grad_scale(self):
+        return self.grad_scale_override or 1.0 / (self.world * self.grad_accum)
+
     def _hyper(self, lr):
-        self.step_count += 1
         self.epoch += 1
         b1, b2 = self.betas
-        scale = self.grad_scale_override or 1.0 / (self.world * self.grad_accum)
-        return dict(lr=lr, beta1=b1, beta2=b2, eps=self.eps, bias1=1 - b1 ** self.step_count,
-                    bias2=1 - b2 ** self.step_count, grad_scale=scale,
+        return dict(lr=lr, beta1=b1, beta2=b2, eps=self.eps, grad_scale=self._grad_scale(),
                     max_norm=self.max_norm or 0.0, skip_norm=self.skip_norm or 0.0)
+
+    def applied_steps(self):
+        """Number of updates applied so far (AdamW's t).  Kernel path: a host read of the device counter."""
+        if self.use_kernel:
+            self.step_count = int(self.status[3].item())
+        return self.step_count
 
     def bucket_ready(self, b, stream=None):
         """Announce that this rank's gradients of bucket b are final and start its
@@ -332,7 +347,7 @@ class FusedDPAdamW:
         off, ln = self.layout.bucket_off[b], self.layout.bucket_len[b]
         part = self.partial[self._early_partials:]
         _ck(self.lib.dmb_opt_reduce_bucket(ctypes.byref(self._comm), off, ln,
-                                           1.0 / (self.world * self.grad_accum), part.data_ptr(),
+                                           self._grad_scale(), part.data_ptr(),
                                            self.bucket_blocks, epoch, SLOT_BUCKET0 + b, self._wait_cycles,
                                            self.status.data_ptr(), st), "reduce_bucket")
         self._early_partials += self.bucket_blocks
@@ -364,12 +379,17 @@ class FusedDPAdamW:
         self._early_partials = 0
         return self.ctrl
 
-    def check_status(self):
-        """Host read of the kernel status word; raises if a cross-GPU wait ran out."""
-        code, peer = self.status[0].item(), self.status[1].item()
+    def check_status(self, code=None):
+        """Raises `PeerWaitExpired` if a cross-GPU wait of the kernels ran out.  `code`: the error code already
+        on the host (ctrl[7] of the last step, read together with the step's verdict); None reads the status
+        word from the device.  The word is sticky: once a wait has run out every later step is voided, so
+        the caller should checkpoint from host state and stop."""
+        if code is None:
+            code = self.status[0].item()
         if code:
-            where = {1: "opening barrier", 2: "norm exchange", 3: "closing barrier"}.get(code, "?")
-            raise RuntimeError(f"fused optimizer: rank {self.rank} gave up waiting for rank {peer} at the {where}")
+            peer = self.status[1].item()
+            where = {1: "opening barrier", 2: "norm exchange", 3: "closing barrier"}.get(int(code), "?")
+            raise PeerWaitExpired(f"fused optimizer: rank {self.rank} gave up waiting for rank {peer} at the {where}")
 
     @torch.no_grad()
     def _step_host(self, h):
@@ -392,9 +412,15 @@ class FusedDPAdamW:
         gn = tot.sqrt()
         coef = torch.clamp(h["max_norm"] / (gn + 1e-6), max=1.0) if h["max_norm"] > 0 else torch.ones_like(gn)
         skip = (~torch.isfinite(gn)) | ((gn > h["skip_norm"]) if h["skip_norm"] > 0 else torch.zeros_like(gn, dtype=torch.bool))
+        skip = skip | bool(self.status[0] != 0)
         self.ctrl[0], self.ctrl[1], self.ctrl[2] = gn, coef, skip.float()
+        self.ctrl[7] = self.status[0].float()
         if bool(skip):
             return
+        self.step_count += 1
+        self.status[3] = self.step_count
+        h = dict(h, bias1=1 - h["beta1"] ** self.step_count, bias2=1 - h["beta2"] ** self.step_count)
+        self.ctrl[4], self.ctrl[5], self.ctrl[6] = float(self.step_count), h["bias1"], h["bias2"]
         wd_full, lr_full = self._expand_segments()
         for b in range(len(self.layout.buckets)):
             lo, hi = self.layout.slice_of(b, r)
@@ -435,6 +461,7 @@ class FusedDPAdamW:
         """Unsharded state in the layout of `torch.optim.AdamW.state_dict()`; parameter
         indices follow the order of `param_groups`."""
         m_full, v_full = self._gather_moments(self.m), self._gather_moments(self.v)
+        self.applied_steps()
         state, groups, idx = {}, [], 0
         for g in self.param_groups:
             ids = []
@@ -460,6 +487,7 @@ class FusedDPAdamW:
                     self.layout.view(v_full, p).copy_(st["exp_avg_sq"])
                     self.step_count = int(float(st["step"]))
                 idx += 1
+        self.status[3] = self.step_count
         for b in range(len(self.layout.buckets)):
             lo, hi = self.layout.slice_of(b, self.rank)
             mo = self.moment_off[b]

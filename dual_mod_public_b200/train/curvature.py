@@ -65,13 +65,30 @@ def ctx_top_eig(model, xb, yb, params=None, n_iter=5, seed=0):
 
 
 @torch.no_grad()
-def layer_grad_norms(model, grads):
-    """{"gradnorm/L00": ..., ...} from a `GradBuffers`-like object with `.get(param)`."""
-    out = {}
+def layer_grad_norms(model, grads, opt=None):
+    """{"gradnorm/L00": ..., ...}: norm of each layer's gradient as the optimizer step saw it (the mean over
+    ranks and micro-batches).  `grads`: a `GradBuffers`-like object with `.get(param)`.  `opt`: the sharded
+    optimizer, when there is one and more than one rank: after its step only the slice a rank OWNS of each
+    bucket holds the reduced mean (the rest still holds that rank's raw local sums), so every rank sums the
+    squares of its owned part of each parameter and the ranks add them up."""
+    sharded = opt is not None and getattr(opt, "world", 1) > 1 and hasattr(opt, "layout")
+    sq = torch.zeros(len(model.blocks), dtype=torch.float32, device=next(model.parameters()).device)
+    if sharded:
+        lay, flat = opt.layout, opt.flat_grads
+        bucket_of = {id(p): b for b, ps in enumerate(lay.buckets) for p in ps}
     for li, blk in enumerate(model.blocks):
-        sq = sum(grads.get(p).float().pow(2).sum() for p in blk.parameters())
-        out[f"gradnorm/L{li:02d}"] = float(torch.sqrt(sq))
-    return out
+        for p in blk.parameters():
+            if not sharded:
+                sq[li] += grads.get(p).float().pow(2).sum()
+                continue
+            lo, hi = lay.slice_of(bucket_of[id(p)], opt.rank)
+            a, b = max(lo, lay.offsets[id(p)]), min(hi, lay.offsets[id(p)] + p.numel())
+            if b > a:
+                sq[li] += flat[a:b].float().pow(2).sum()
+    if sharded:
+        import torch.distributed as dist
+        dist.all_reduce(sq, group=opt.group)
+    return {f"gradnorm/L{li:02d}": float(v) for li, v in enumerate(torch.sqrt(sq).tolist())}
 
 
 @torch.no_grad()

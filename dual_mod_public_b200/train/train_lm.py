@@ -320,6 +320,24 @@ def run(args):
             loss = tr.step(next(stream), sid=sid, lr=lr)
         ctrl = tr.opt.ctrl.tolist()
         gn, skipped = ctrl[0], ctrl[2] > 0.5
+        # a bounded cross-GPU wait of the optimizer kernels that ran out voids this and every later step
+        # (the status word is sticky): name the peer and the phase, keep the newest resident snapshot, stop
+        wait_code = ctrl[7] if len(ctrl) > 7 else 0.0
+        if wait_code or (skipped and hasattr(tr.opt, "check_status")):
+            try:
+                tr.opt.check_status(int(wait_code)) if len(ctrl) > 7 else tr.opt.check_status()
+            except RuntimeError as e:
+                if rewind.ring:
+                    snap_step, ck = rewind.ring[-1]
+                    path = os.path.join(args.out_dir, f"ckpt_emergency_rank{rank}.pt")
+                    save_atomic(ck, path)
+                    print(f"[rank {rank}] step {step}: {e}; resident snapshot of step {snap_step} -> {path}", flush=True)
+                else:
+                    print(f"[rank {rank}] step {step}: {e}; no resident snapshot (resume from ckpt_latest.pt)", flush=True)
+                if writer is not None:
+                    writer.close()
+                log.close()
+                raise
         gn_seen, loss_seen = inject.apply(step, gn, loss, rewind.count)
         step_ms = (time.time() - t0) * 1e3
         if world > 1:
@@ -411,7 +429,7 @@ def run(args):
             tr.model.cfg.attn_mode = mode
         if args.curv_every and step % args.curv_every == 0 and step > 0:
             from .curvature import ctx_top_eig, layer_grad_norms
-            rec.update(layer_grad_norms(tr.model, tr.opt.grad_buffers()))
+            rec.update(layer_grad_norms(tr.model, tr.opt.grad_buffers(), tr.opt if getattr(tr.opt, "use_kernel", False) else None))
             if master:
                 blk = next(make_stream(10 ** 9 + 77, args.seed))[:2, :args.curv_len + 1].to(dev)
                 mode, tr.model.cfg.attn_mode = tr.model.cfg.attn_mode, "sequential"

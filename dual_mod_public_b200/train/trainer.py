@@ -167,7 +167,9 @@ class Trainer:
                 p.add_(g[o:o + p.numel()].view_as(p).to(p.dtype), alpha=float(rho / gnorm))
                 o += p.numel()
         self.engine.pack()
-        self.accumulate(tokens, sid, final=True)
+        # no bucket starts its reduction during this pass: g2 below is read from the flat array on the main
+        # stream and must still be this rank's plain local gradient (the fused step reduces every bucket)
+        self.accumulate(tokens, sid, final=False)
         with torch.no_grad():
             g2 = torch.cat([G.get(p).reshape(-1).float() for p in params]) / (self.world * self.accum)
             dot = (g2 * g).sum()

@@ -64,6 +64,55 @@ def test_skip_predicate_leaves_parameters_untouched():
     assert opt.step()[2] == 1 and torch.equal(before, opt.flat_params)
 
 
+def test_skipped_steps_do_not_advance_adamw_time():
+    """Two voided steps, then two applied ones: parameters, moments and the saved `step` equal
+    torch.optim.AdamW's, whose step() is simply not called on a voided step."""
+    cfg = small_cfg()
+    m1, m2 = make_model(cfg), make_model(cfg)
+    opt = FusedDPAdamW(decay_groups(m1, 0.1), default_buckets(m1), lr=1e-2, max_norm=0.0, use_kernel=False)
+    G = opt.grad_buffers()
+    ref = torch.optim.AdamW([{"params": g["params"], "weight_decay": g["weight_decay"]}
+                             for g in decay_groups(m2, 0.1)], lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    uniq2 = [p for g in ref.param_groups for p in g["params"]]
+    order1 = [p for g in decay_groups(m1, 0.1) for p in g["params"]]
+    for step in range(4):
+        gs = _grads_like(order1, step)
+        opt.zero_grad()
+        for p, g in zip(order1, gs):
+            G.get(p).copy_(g)
+        void = step < 2
+        opt.skip_norm = 1e-30 if void else 0.0          # every finite norm exceeds 1e-30
+        ctrl = opt.step()
+        assert bool(ctrl[2]) == void
+        if not void:
+            for p, g in zip(uniq2, gs):
+                p.grad = g.clone()
+            ref.step()
+    assert opt.applied_steps() == 2 and float(opt.ctrl[4]) == 2.0
+    for a, b in zip(order1, uniq2):
+        assert (a - b).abs().max() < 1e-6
+    sd, rsd = opt.state_dict(), ref.state_dict()
+    assert float(sd["state"][0]["step"]) == float(rsd["state"][0]["step"]) == 2.0
+
+
+def test_expired_wait_is_reported_with_the_step_verdict():
+    """The status word set by hand (as the kernels set it when a bounded wait runs out): the step is
+    voided, the code rides in ctrl[7], and check_status names the peer and the phase."""
+    from dual_mod_public_b200.parallel.fused_optim import PeerWaitExpired
+    cfg = small_cfg()
+    m = make_model(cfg)
+    opt = FusedDPAdamW(decay_groups(m, 0.0), default_buckets(m), lr=1e-2, use_kernel=False)
+    opt.flat_grads.fill_(1e-3)
+    assert opt.step()[2] == 0
+    opt.check_status(int(opt.ctrl[7]))
+    before = opt.flat_params.clone()
+    opt.status[0], opt.status[1] = 2, 5
+    ctrl = opt.step()
+    assert ctrl[2] == 1 and ctrl[7] == 2 and torch.equal(before, opt.flat_params)
+    with pytest.raises(PeerWaitExpired, match="rank 5 at the norm exchange"):
+        opt.check_status(int(ctrl[7]))
+
+
 def _rank_main(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)

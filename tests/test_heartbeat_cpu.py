@@ -1,7 +1,7 @@
 """Failure detection on the host, among CPU ranks: a rank that leaves between steps (or raises) is
 reported to the survivors as PeerLost before their next launch; healthy ranks pass."""
 
-import os
+import socket
 import time
 
 import pytest
@@ -13,7 +13,10 @@ from dual_mod_public_b200.parallel.heartbeat import PeerLost, PeerWatch
 
 def _rank(rank, world, port, leave_at, q):
     store = dist.TCPStore("127.0.0.1", port, world, is_master=rank == 0, timeout=__import__("datetime").timedelta(seconds=20))
-    w = PeerWatch(store, rank, world, timeout=1.0)
+    # start-up is slow and uneven for spawned processes: meet once with a long limit, so that in the steps
+    # below only the rank that leaves can exceed the watch's limit
+    PeerWatch(store, rank, world, timeout=60.0, prefix="start").sync(0)
+    w = PeerWatch(store, rank, world, timeout=5.0)
     try:
         for step in range(5):
             if rank == 1 and step == leave_at:
@@ -25,7 +28,7 @@ def _rank(rank, world, port, leave_at, q):
     except PeerLost as e:
         q.put((rank, "lost", (e.ranks, e.step)))
     if rank == 0:
-        time.sleep(1.5)                                      # keep the store up until the others are done
+        time.sleep(6.5)                                      # keep the store up until the others are done
 
 
 @pytest.mark.parametrize("leave_at", [2, 99])
@@ -33,7 +36,9 @@ def test_lost_peer_is_reported_on_the_host(leave_at):
     world = 3
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + (os.getpid() % 200) + (0 if leave_at == 2 else 1)
+    with socket.socket() as sk:                              # a port the system says is free
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     procs = [ctx.Process(target=_rank, args=(r, world, port, leave_at, q)) for r in range(world)]
     for p in procs:
         p.start()

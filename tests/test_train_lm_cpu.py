@@ -303,3 +303,28 @@ def test_wild_norm_triggers_a_buffer_scan(tmp_path, monkeypatch, capsys):
     train_main(TINY + ["--out_dir", out, "--total_steps", "5"])
     recs = _records(out)
     assert recs[2]["train/skipped"] and recs[3]["train/skipped"]
+
+
+def test_trainer_stops_when_a_peer_wait_ran_out(tmp_path, monkeypatch, capsys):
+    """The optimizer's status word set by hand at step 5 (what its kernels do when a bounded wait for a peer
+    runs out): the loop names the peer and the phase, writes its newest resident snapshot and stops."""
+    import pytest
+
+    from dual_mod_public_b200.parallel.fused_optim import PeerWaitExpired
+    from dual_mod_public_b200.train.trainer import Trainer
+    out = str(tmp_path / "lost")
+    real_step = Trainer.step
+
+    def step(self, tokens, **kw):
+        if self.steps_done == 5:
+            self.opt.status[0], self.opt.status[1] = 1, 3
+        return real_step(self, tokens, **kw)
+
+    monkeypatch.setattr(Trainer, "step", step)
+    with pytest.raises(PeerWaitExpired, match="rank 3 at the opening barrier"):
+        train_main(TINY + ["--out_dir", out, "--total_steps", "12", "--auto_rewind", "--snap_interval", "2"])
+    assert "resident snapshot of step 4" in capsys.readouterr().out
+    ck = torch.load(os.path.join(out, "ckpt_emergency_rank0.pt"), weights_only=False)
+    assert ck["step"] == 4 and "model" in ck and "optimizer" in ck
+    steps = [x["step"] for x in _records(out)]
+    assert steps == [0, 1, 2, 3, 4]                                                # nothing logged as trained after it
