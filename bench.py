@@ -162,7 +162,8 @@ def run_ours(args):
     tr = Trainer(cfg, [SWEEPS] if wave3d else [uniform_chunks(SEQ, CHUNK, SWEEPS)], seq_len=SEQ, micro_batch=micro,
                  local_batch=local_seqs, lr=3e-4, weight_decay=0.01, max_norm=1.0,
                  optimizer=args.optimizer, device=f"cuda:{local}", use_graphs=not args.no_graphs,
-                 engine="wave3d" if wave3d else "wavescan", engine_kwargs=dict(C=CHUNK) if wave3d else None)
+                 engine="wave3d" if wave3d else "wavescan",
+                 engine_kwargs=dict(C=CHUNK) if wave3d else dict(keep_sweeps=args.keep_sweeps))
     host = synthetic_tokens(torch, local_seqs, rank, 2, cfg.vocab_size)
     dev = [t.cuda() for t in host]
     loss_first = None
@@ -344,10 +345,6 @@ def run_reference_wave3d(args):
         opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.01},
                                  {"params": nodecay, "weight_decay": 0.0}], lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
                                 fused=True)
-        kw = {"graphs": not args.no_graphs}
-        if args.ref_attn:
-            kw["attn_impl"] = args.ref_attn
-        engine = hero.build_engine(model, micro, SEQ, "x", kw, args.ref_compile, cudnn_ws_gb=1.0)
         reducer = hero.GradAllReducer(model.parameters(), world)
         params = list(model.parameters())
         host = synthetic_tokens(torch, local_seqs, rank, 2, cfg.vocab_size)
@@ -355,6 +352,31 @@ def run_reference_wave3d(args):
         loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
         model.train()
         opt.zero_grad(set_to_none=True)
+        # the engine's attention adapters in its own order of preference (cudnn_fe is its default; the
+        # others are its documented alternatives): the first one that gets through a forward + backward
+        # on this image's library versions runs the benchmark, the failures are reported with the result
+        engine, tried = None, {}
+        for attn in ([args.ref_attn] if args.ref_attn else ["cudnn_fe", "cudnn", "flash"]):
+            try:
+                kw = {"graphs": not args.no_graphs, "attn_impl": attn}
+                engine = hero.build_engine(model, micro, SEQ, "x", kw, args.ref_compile, cudnn_ws_gb=1.0)
+                blk = dev[0][:micro]
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    engine.forward(blk[:, :SEQ], blk[:, 1:SEQ + 1], SWEEPS).backward()
+                opt.zero_grad(set_to_none=True)
+                args.ref_attn = attn
+                break
+            except Exception as e:
+                import traceback
+                traceback.print_exc(file=sys.stderr)
+                tried[attn] = f"{type(e).__name__}: {e}".replace("\n", " ")[:200]
+                engine = None
+                opt.zero_grad(set_to_none=True)
+                import gc
+                gc.collect()
+                torch.cuda.empty_cache()
+        if engine is None:
+            raise RuntimeError(f"no attention adapter of the reference engine runs here: {tried}")
 
         def step(tokens, read_loss):
             loss_acc = torch.zeros((), device="cuda")
@@ -399,6 +421,7 @@ def run_reference_wave3d(args):
                                           f"attn_impl={args.ref_attn or 'cudnn_fe'}, fused_refine), "
                                           f"set_compile('{args.ref_compile}')",
                                 "optimizer": "GradAllReducer (NCCL all-reduce AVG) + clip_grad_norm_ + fused torch AdamW",
+                                "attn_impl_failed_here": tried,
                                 "engine_mem": {k: (round(v, 2) if isinstance(v, float) else v)
                                                for k, v in getattr(engine, "mem", {}).items()
                                                if isinstance(v, (int, float))}},
@@ -412,8 +435,10 @@ def run_reference_wave3d(args):
             dist.barrier()
             dist.destroy_process_group()
     except Exception as e:
+        import traceback
+        traceback.print_exc(file=sys.stderr)
         if int(os.environ.get("RANK", 0)) == 0:
-            msg = f"{type(e).__name__}: {e}".replace("\n", " ")[:400]
+            msg = f"{type(e).__name__}: {e}".replace("\n", " ")[:600]
             print(json.dumps({"impl": "reference", "unavailable": msg}), flush=True)
 
 
@@ -496,6 +521,9 @@ def main():
                          "hero: the reference's 1.3B recipe (18L d2304 36x64, rank-144 mult_res write law) on the "
                          "wavefront engine at 128 x 4096 tokens per step, K=8")
     ap.add_argument("--sweeps", type=int, default=0, help="sweeps K (default 4; the 1.3B ladder is 2 / 4 / 8)")
+    ap.add_argument("--keep-sweeps", default="auto", type=lambda v: v if v == "auto" else int(v),
+                    help="cell engine: layers whose sweep states a training forward keeps for the backward "
+                         "(auto: as many as fit in half of the device memory; 0: the backward re-runs the sweeps)")
     ap.add_argument("--ref-micro-batch", type=int, default=4,
                     help="hero reference arm: sequences per engine call (the reference's own runs use 4)")
     ap.add_argument("--ref-compile", default="all", choices=["none", "refine", "all"],

@@ -31,7 +31,8 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = BN == 256 ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;              // two accumulators
-  static constexpr int bar_off = STAGES * STAGE_BYTES;  // tiles first (1024-byte aligned base), barriers after
+  static constexpr int stage_out_off = STAGES * STAGE_BYTES;      // epilogue staging: 4 warps x 2 slots x 4 KB
+  static constexpr int bar_off = stage_out_off + 4 * 2 * 4096;    // tiles first (1024-byte aligned base), barriers after
   static constexpr int total = bar_off + 256;
 };
 constexpr unsigned long long WAIT_NS = 2000000000ull;  // every pipeline wait gives up after 2 s
@@ -75,6 +76,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -124,7 +130,8 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 
 template <int A_MN, int B_MN, int OUT_F32, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
-    const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout,
+    const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+    const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cout,
     const bf16* __restrict__ bias, int M, int N, int K, long long ldc, int accumulate, int* __restrict__ gerr,
     int splits, float* __restrict__ ws) {
   using C = Cfg<BN>;
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
-    uint32_t ti = 0;
+    uint32_t ti = 0, n_out = 0;          // n_out: staging slots handed to TMA stores so far (parity picks the slot)
     bool alive = true;
     for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++ti) {
       const int t2 = tile / splits, ks = tile - t2 * splits;
@@ -242,14 +249,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
       if (!mbar_wait(tmem_full(acc), (ti >> 1) & 1, serr)) { alive = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = m0 + q * 32 + lane;
+      if (OUT_F32) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int col = n0 + c0;
-        if (row < M && col < N) {
-          if (OUT_F32) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int col = n0 + c0;
+          if (row < M && col < N) {
             float* dst = splits > 1 ? ws + ((long long)ks * M + row) * N + col
                                     : reinterpret_cast<float*>(Cout) + (long long)row * ldc + col;
 #pragma unroll
@@ -267,22 +274,47 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
                 *reinterpret_cast<float4*>(dst + j) = v;
               }
             }
-          } else {
-            bf16* dst = reinterpret_cast<bf16*>(Cout) + (long long)row * ldc + col;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col + j < N) {
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  f[e] = __uint_as_float(r[j + e]);
-                  if (bias) f[e] += __bfloat162float(bias[col + j + e]);
-                }
-                uint4 o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
-                *reinterpret_cast<uint4*>(dst + j) = o;
-              }
-            }
           }
+        }
+      } else {
+        // bf16: 64 columns at a time through this warp's two staging slots
+        const bool rows_live = m0 + q * 32 < M;           // warp-uniform
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          const int col = n0 + c0;
+          if (col >= N) break;                             // warp-uniform: the rest of the tile is outside C
+          uint32_t r[64];
+          {
+            uint32_t (&ra)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+            uint32_t (&rb)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, ra);
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0 + 32, rb);
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (!rows_live) continue;
+          uint8_t* slot = base_ptr + C::stage_out_off + (q * 2 + (n_out & 1)) * 4096;
+          // the store that last read this slot (two chunks ago) must have drained it
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              f[e] = __uint_as_float(r[j * 8 + e]);
+              if (bias && col + j * 8 + e < N) f[e] += __bfloat162float(bias[col + j * 8 + e]);
+            }
+            const uint4 o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+            // 128-byte swizzle: 16-byte chunk j of row `lane` sits at chunk j ^ (lane & 7)
+            *reinterpret_cast<uint4*>(slot + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, smem_u32(slot), col, m0 + q * 32);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          ++n_out;
         }
       }
       // this warp has read its quarter of the accumulator: hand it back to the MMA issuer
@@ -290,6 +322,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty(acc));
     }
+    if (!OUT_F32 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -353,7 +386,7 @@ constexpr size_t WS_BYTES = (size_t)64 << 20;    // split-K workspace, one per d
 float* g_ws[16] = {};
 
 template <int A_MN, int B_MN, int OUT_F32, int BN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* bias, int M, int N, int K,
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* bias, int M, int N, int K,
            long long ldc, int accumulate, int* gerr, float* ws, int splits, cudaStream_t st) {
   auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, BN>;
   static bool configured = false;
@@ -365,7 +398,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* bi
   }
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   const int items = tiles * splits;
-  kern<<<items < g_sms ? items : g_sms, NTHREADS, smem, st>>>(ta, tb, C, (const bf16*)bias, M, N, K, ldc, accumulate,
+  kern<<<items < g_sms ? items : g_sms, NTHREADS, smem, st>>>(ta, tb, tc, C, (const bf16*)bias, M, N, K, ldc, accumulate,
                                                              gerr, splits, ws);
   DMB_CHECK_LAUNCH();
   if (splits > 1) {
@@ -433,15 +466,18 @@ int dmb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
       }
     }
   }
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   int rc;
   rc = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM);
   if (rc) return rc;
   rc = b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc;
+  // bf16 results leave through TMA stores of 32-row x 64-column boxes (fp32 results are stored directly)
+  if (out_f32) tc = ta;
+  else if ((rc = make_map(&tc, C, N, M, ldc, 64, 32))) return rc;
 #define GO(a, b, o)                                                                               \
-  return bn == 256 ? launch<a, b, o, 256>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)    \
-                   : launch<a, b, o, 128>(ta, tb, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)
+  return bn == 256 ? launch<a, b, o, 256>(ta, tb, tc, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)    \
+                   : launch<a, b, o, 128>(ta, tb, tc, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)
   if (!a_mn && !b_mn) { if (out_f32) GO(0, 0, 1); else GO(0, 0, 0); }
   if (!a_mn && b_mn) { if (out_f32) GO(0, 1, 1); else GO(0, 1, 0); }
   if (out_f32) GO(1, 1, 1); else GO(1, 1, 0);
