@@ -355,16 +355,40 @@ def run_reference_wave3d(args):
         # the engine's attention adapters in its own order of preference (cudnn_fe is its default; the
         # others are its documented alternatives): the first one that gets through a forward + backward
         # on this image's library versions runs the benchmark, the failures are reported with the result
-        engine, tried = None, {}
-        for attn in ([args.ref_attn] if args.ref_attn else ["cudnn_fe", "cudnn", "flash"]):
+        # This image's cudnn-frontend (1.18) builds graph tensors through DLPack, which refuses tensors that
+        # require grad; its own wrapper detaches first (cudnn/wrapper.py).  The reference calls
+        # `pygraph.tensor_like` on autograd inputs directly, so the library method is wrapped here to pass a
+        # detached alias of the same storage.  The reference's files are not touched.
+        try:
+            import cudnn as _fe
+            _orig_like = _fe.pygraph.tensor_like
+
+            def _tensor_like(self, t, *a, **k):
+                return _orig_like(self, t.detach() if isinstance(t, torch.Tensor) and t.requires_grad else t, *a, **k)
+            _fe.pygraph.tensor_like = _tensor_like
+        except Exception:
+            pass
+        # engine settings in the reference's own order of preference: its default (cudnn_fe, grouped path with
+        # the (o, lse) stash, CUDA graphs), then its documented alternatives (per-layer path without the stash
+        # over the aten cuDNN / flash kernels; eager instead of graphs).  The first one that gets through a
+        # forward + backward here runs the benchmark; the failures are reported with the result.
+        G_ = not args.no_graphs
+        plans = [dict(attn_impl="cudnn_fe", graphs=G_), dict(attn_impl="cudnn", stash_attn=False, graphs=G_),
+                 dict(attn_impl="flash", stash_attn=False, graphs=G_)]
+        if G_:
+            plans += [dict(attn_impl="cudnn_fe", graphs=False), dict(attn_impl="flash", stash_attn=False, graphs=False)]
+        if args.ref_attn:
+            plans = [p_ for p_ in plans if p_["attn_impl"] == args.ref_attn]
+        engine, tried, used = None, {}, None
+        for kw in plans:
+            attn = json.dumps(kw, sort_keys=True)
             try:
-                kw = {"graphs": not args.no_graphs, "attn_impl": attn}
-                engine = hero.build_engine(model, micro, SEQ, "x", kw, args.ref_compile, cudnn_ws_gb=1.0)
+                engine = hero.build_engine(model, micro, SEQ, "x", dict(kw), args.ref_compile, cudnn_ws_gb=1.0)
                 blk = dev[0][:micro]
                 with torch.autocast("cuda", dtype=torch.bfloat16):
                     engine.forward(blk[:, :SEQ], blk[:, 1:SEQ + 1], SWEEPS).backward()
                 opt.zero_grad(set_to_none=True)
-                args.ref_attn = attn
+                used = kw
                 break
             except Exception as e:
                 import traceback
@@ -416,10 +440,9 @@ def run_reference_wave3d(args):
                 "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": round(value / (PUBLISHED_TOK_S_PER_GPU * world), 3), "dtype": "bf16",
                 "data": "synthetic uniform token ids, random-init weights", "impl": "reference",
-                "config": shared_config(world, micro, not args.no_graphs),
-                "impl_detail": {"engine": f"reference Wave3DX via make_engine(engine='x', C=64, graphs, "
-                                          f"attn_impl={args.ref_attn or 'cudnn_fe'}, fused_refine), "
-                                          f"set_compile('{args.ref_compile}')",
+                "config": shared_config(world, micro, bool(used.get("graphs"))),
+                "impl_detail": {"engine": f"reference Wave3DX via make_engine(engine='x', C=64, fused_refine, "
+                                          f"{json.dumps(used, sort_keys=True)}), set_compile('{args.ref_compile}')",
                                 "optimizer": "GradAllReducer (NCCL all-reduce AVG) + clip_grad_norm_ + fused torch AdamW",
                                 "attn_impl_failed_here": tried,
                                 "engine_mem": {k: (round(v, 2) if isinstance(v, float) else v)

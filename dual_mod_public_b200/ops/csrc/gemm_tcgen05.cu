@@ -15,9 +15,9 @@
 // columns), so the epilogue of tile i overlaps the main loop of tile i+1.  Each CTA
 // loads its own tiles.  Every mbarrier wait is bounded in time: on expiry the kernel raises a flag in global
 // memory, stops waiting and runs to its end so TMEM is released.
-#include <cuda.h>
+#include "tc05.cuh"
 
-#include "common.cuh"
+using namespace tc05;
 
 namespace {
 
@@ -35,99 +35,6 @@ struct Cfg {
   static constexpr int bar_off = stage_out_off + 4 * 2 * 4096;    // tiles first (1024-byte aligned base), barriers after
   static constexpr int total = bar_off + 256;
 };
-constexpr unsigned long long WAIT_NS = 2000000000ull;  // every pipeline wait gives up after 2 s
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// wait bounded in time (WAIT_NS); returns false when it ran out or another role already gave up
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* err) {
-  const unsigned long long t0 = global_ns();
-  for (uint32_t it = 0;; ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if (*err) return false;
-    if ((it & 63) == 63 && global_ns() - t0 > WAIT_NS) break;
-  }
-  *err = 1;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
-                                            int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(map), "r"(src), "r"(c0), "r"(c1)
-               : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-// 64-bit shared-memory matrix descriptor, 128-byte swizzle
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;   // descriptor version (sm_100)
-  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
-  return d;
-}
-
-template <int A_MN, int B_MN, int BN>
-__device__ __forceinline__ constexpr uint32_t instr_desc() {
-  return (1u << 4)                      // D = fp32
-         | (1u << 7) | (1u << 10)       // A, B = bf16
-         | ((uint32_t)A_MN << 15) | ((uint32_t)B_MN << 16)
-         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
 template <int A_MN, int B_MN, int OUT_F32, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -169,8 +76,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(C::TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -210,7 +116,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc<A_MN, B_MN, BN>();
+      constexpr uint32_t idesc = instr_desc(BM, BN, A_MN, B_MN);
       uint32_t it = 0, ti = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++ti) {
@@ -328,7 +234,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_kernel(
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
   if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
 }
@@ -351,34 +257,6 @@ __global__ void splitk_reduce_kernel(float* __restrict__ Cout, const float* __re
     }
     *reinterpret_cast<float4*>(dst) = a;
   }
-}
-
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeFn g_encode = nullptr;
-
-int get_encode() {
-  if (g_encode) return 0;
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return -10;
-  g_encode = (EncodeFn)fn;
-  return 0;
-}
-
-// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of stride ld elements
-int make_map(CUtensorMap* m, const void* ptr, long long inner, long long outer, long long ld, int box_inner,
-             int box_outer) {
-  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -11;
 }
 
 int g_sms = 0;
@@ -421,7 +299,7 @@ extern "C" {
 int dmb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                   long long ldb, long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, int* gerr,
                   cudaStream_t st) {
-  if (get_encode()) return -10;
+  if (!encode_fn()) return -10;
   if (N % 8 || (accumulate && !out_f32) || (a_mn && !b_mn)) return -1;
   if (!g_sms) {
     int dev = 0;
@@ -468,13 +346,13 @@ int dmb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
   }
   CUtensorMap ta, tb, tc;
   int rc;
-  rc = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM);
+  rc = a_mn ? make_map_2d(&ta, A, M, K, lda, 64, BK) : make_map_2d(&ta, A, K, M, lda, BK, BM);
   if (rc) return rc;
-  rc = b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, bn);
+  rc = b_mn ? make_map_2d(&tb, B, N, K, ldb, 64, BK) : make_map_2d(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc;
   // bf16 results leave through TMA stores of 32-row x 64-column boxes (fp32 results are stored directly)
   if (out_f32) tc = ta;
-  else if ((rc = make_map(&tc, C, N, M, ldc, 64, 32))) return rc;
+  else if ((rc = make_map_2d(&tc, C, N, M, ldc, 64, 32))) return rc;
 #define GO(a, b, o)                                                                               \
   return bn == 256 ? launch<a, b, o, 256>(ta, tb, tc, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)    \
                    : launch<a, b, o, 128>(ta, tb, tc, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)

@@ -72,6 +72,8 @@ class _Sigs:
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
+    dmb_attn_fwd_tc = [_p, _v, _i, _p, _p, _v, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
+                       _i, _i, _p, _p]
 
 
 BF16 = torch.bfloat16
@@ -371,6 +373,35 @@ class CudaOps(TorchOps):
             out[1].copy_(lse_c)
             return out
         return o_c, lse_c
+
+    # lane layout of the M = 64 accumulator in tensor memory (0: sixteen rows per 32-lane quarter)
+    TC_LANE_MODE = int(os.environ.get("DMB_TC_LANE_MODE", "0"))
+
+    def attn_fwd_tc(self, q, Kc, Vc, lo, hi, qbase, scale, window=0, causal=False, causal_excl=1, Lq=None, G=1,
+                    grow=0, bm=None, out_dtype=F32, lane_mode=None):
+        """Attention forward on tcgen05 (csrc/attn_tc.cu).  q: [B, rows, h, dh] bf16 view; group z (of G) takes
+        its rows [z*grow, z*grow + Lq), sits at positions qbase + z*grow + i and reads the tape rows
+        max(0, lo + z*grow) <= j < hi + z*grow of Kc / Vc [B, T, h, dh], under the causal rule
+        j <= position - causal_excl and the sliding window j > position - window.
+        Returns (o [B, G, Lq, h, dh] in out_dtype, lse [B, G, Lq, h] fp32)."""
+        B, rows, h, dh = q.shape
+        Lq = rows if Lq is None else Lq
+        bm = bm or (128 if Lq >= 128 else 64)
+        o = torch.empty(B, G, Lq, h, dh, dtype=out_dtype, device=q.device)
+        lse = torch.empty(B, G, Lq, h, dtype=F32, device=q.device)
+        if not hasattr(self, "_tc_err"):
+            self._tc_err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._ck(self.lib.dmb_attn_fwd_tc(
+            q.data_ptr(), _tv(q), rows, Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), Kc.shape[1], o.data_ptr(),
+            int(out_dtype == BF16), lse.data_ptr(), B, G, Lq, h, dh, lo, hi, qbase, grow, scale, window,
+            int(causal), causal_excl, bm, self.TC_LANE_MODE if lane_mode is None else lane_mode,
+            self._tc_err.data_ptr(), self._st()), "attn_fwd_tc")
+        return o, lse
+
+    def tc_check(self):
+        """Host read of the tcgen05 attention kernels' error flag (a pipeline wait that ran out)."""
+        if hasattr(self, "_tc_err") and self._tc_err.item() != 0:
+            raise RuntimeError("tcgen05 attention: a pipeline wait ran out (kernel aborted its tile loop)")
 
     def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff=0):
         from ..engines.fused_math import prefix_lo

@@ -1,0 +1,103 @@
+"""tcgen05 attention forward (ops/csrc/attn_tc.cu) against a plain fp32 statement of the same read:
+whole-prefix reads of chunk groups (M = 64 tiles), lower-right causal reads of long query blocks
+(M = 128 tiles), sliding windows, ragged row / key counts, head dims 64 and 128, and agreement with the
+warp-MMA `prefix_fwd` kernel it replaces."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from dual_mod_public_b200.ops.cuda_ops import CudaOps
+    return CudaOps(torch.device(DEV))
+
+
+def rnd(*s, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(s))
+    return (torch.randn(*s, generator=g) * scale).to(DEV).bfloat16()
+
+
+def reference(q, K, V, lo, hi, qbase, scale, window, causal, causal_excl, Lq, G, grow):
+    """fp32: (o [B,G,Lq,h,dh], lse [B,G,Lq,h]); rows without any allowed key: o = 0, lse = -1e30."""
+    B, _, h, dh = q.shape
+    o = torch.zeros(B, G, Lq, h, dh, device=q.device)
+    lse = torch.full((B, G, Lq, h), -1e30, device=q.device)
+    for z in range(G):
+        lo_z, hi_z = max(0, lo + z * grow), hi + z * grow
+        qz = q[:, z * grow:z * grow + Lq].float()
+        if hi_z <= lo_z:
+            continue
+        Kz, Vz = K[:, lo_z:hi_z].float(), V[:, lo_z:hi_z].float()
+        s = torch.einsum("bihd,bjhd->bhij", qz, Kz) * scale
+        pos = (qbase + z * grow + torch.arange(Lq, device=q.device))[:, None]
+        j = torch.arange(lo_z, hi_z, device=q.device)[None, :]
+        ok = torch.ones(Lq, hi_z - lo_z, dtype=torch.bool, device=q.device)
+        if causal:
+            ok &= j <= pos - causal_excl
+        if window:
+            ok &= j > pos - window
+        s = s.masked_fill(~ok, float("-inf"))
+        l = torch.logsumexp(s, dim=-1)                                  # [B,h,Lq]
+        p = torch.exp(s - l.masked_fill(l == float("-inf"), 0.0)[..., None])
+        p = p.masked_fill(~ok, 0.0)
+        o[:, z] = torch.einsum("bhij,bjhd->bihd", p, Vz)
+        lse[:, z] = torch.where(l == float("-inf"), torch.full_like(l, -1e30), l).permute(0, 2, 1)
+    return o, lse
+
+
+def check(got, ref, what, tol=2e-2):
+    o, lse = got
+    o_ref, lse_ref = ref
+    live = lse_ref > -1e29
+    assert torch.equal(lse > -1e29, live), f"{what}: empty rows differ"
+    e_o = (o.float() - o_ref).abs().max().item()
+    e_l = (lse - lse_ref)[live].abs().max().item() if live.any() else 0.0
+    assert e_o < tol and e_l < tol, f"{what}: |do| {e_o:.4g} |dlse| {e_l:.4g}"
+
+
+CASES = [
+    # B, T, h, dh, Lq, G, grow, lo, hi, qbase, window, causal, excl, bm
+    (2, 1024, 4, 64, 64, 1, 0, 0, 640, 640, 0, False, 1, 64),          # a cell's whole-prefix read
+    (2, 1024, 4, 64, 64, 3, 64, 0, 200, 200, 0, False, 1, 64),         # three chunk groups, ragged key count
+    (2, 1024, 2, 64, 64, 2, 64, 0, 448, 448, 300, False, 1, 64),       # sliding window over the prefix
+    (1, 1024, 2, 64, 256, 1, 0, 0, 1024, 768, 0, True, 0, 128),        # lower-right causal, diagonal included
+    (2, 768, 2, 64, 200, 1, 0, 0, 700, 500, 0, True, 1, 128),          # ragged rows and keys, strictly causal
+    (1, 1024, 2, 64, 256, 1, 0, 0, 1024, 768, 333, True, 0, 128),      # causal + window
+    (2, 512, 2, 128, 64, 2, 64, 0, 256, 256, 0, False, 1, 64),         # head dim 128, cells
+    (1, 1024, 2, 128, 256, 1, 0, 0, 1024, 768, 0, True, 0, 128),       # head dim 128, long block
+    (1, 512, 2, 64, 64, 1, 0, 100, 100, 100, 0, False, 1, 64),         # empty key range
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_attn_fwd_tc_matches_fp32(ops, case):
+    B, T, h, dh, Lq, G, grow, lo, hi, qbase, window, causal, excl, bm = case
+    rows = (G - 1) * grow + Lq
+    q = rnd(B, rows, h, dh, seed=1)
+    K, V = rnd(B, T, h, dh, seed=2), rnd(B, T, h, dh, seed=3)
+    scale = dh ** -0.5
+    got = ops.attn_fwd_tc(q, K, V, lo, hi, qbase, scale, window, causal, excl, Lq=Lq, G=G, grow=grow, bm=bm)
+    ops.tc_check()
+    ref = reference(q, K, V, lo, hi, qbase, scale, window, causal, excl, Lq, G, grow)
+    check(got, ref, f"case {case}")
+    got16 = ops.attn_fwd_tc(q, K, V, lo, hi, qbase, scale, window, causal, excl, Lq=Lq, G=G, grow=grow, bm=bm,
+                            out_dtype=torch.bfloat16)
+    check(got16, ref, f"case {case} (bf16 out)", tol=3e-2)
+
+
+def test_strided_query_view_and_agreement_with_prefix_fwd(ops):
+    """q is a chunk slice of a full-sequence tensor (row offset, batch stride of the parent), as the engines
+    pass it; the result equals the warp-MMA prefix kernel's."""
+    B, T, h, dh, c, pos0 = 4, 512, 4, 64, 64, 320
+    q_all = rnd(B, T, h, dh, seed=5)
+    K, V = rnd(B, T, h, dh, seed=6), rnd(B, T, h, dh, seed=7)
+    scale = dh ** -0.5
+    qv = q_all[:, pos0:pos0 + c]
+    o_tc, lse_tc = ops.attn_fwd_tc(qv, K, V, 0, pos0, pos0, scale, Lq=c, bm=64)
+    ops.tc_check()
+    o_mma, lse_mma = ops.prefix_fwd(qv, K, V, pos0, scale)
+    assert (o_tc[:, 0] - o_mma).abs().max() < 2e-2 and (lse_tc[:, 0] - lse_mma).abs().max() < 2e-2
