@@ -138,6 +138,50 @@ class Wave3DEngine(WaveScanEngine):
             self.DLf_all = z(B, T, h, dt=torch.float32)
             self._versions = {}
 
+    # ---- the reference engine's calling surface (engines/wave3d/wave3d.py:203 `make_engine`,
+    #      wave3d_x.py:1292 `forward_logits`, :1287-1289 `stats`, :1383-1398 `mem`) ---------------------
+    def sid_of_K(self, K):
+        """Schedule id of sweep count K; a K outside the ladder is added as a new rung (its graphs are
+        recorded on first use, like every rung's)."""
+        K = int(K)
+        if K not in self.ladder:
+            self.ladder.append(K)
+            self.schedules.append([(p, self.C, K) for p in range(0, self.T, self.C)])
+        return self.ladder.index(K)
+
+    def forward_K(self, idx, targets, K, train=False):
+        """`forward(idx, targets, K)` of the reference engine: the mean CE at sweep count K (fp32 scalar
+        tensor).  With train=True, `backward()` then accumulates the gradients (the reference calls
+        `.backward()` on the returned loss; here the reverse pass is explicit)."""
+        return self.forward(idx, targets, sid=self.sid_of_K(K), train=train)
+
+    def forward_logits(self, idx, K):
+        """Logits [B, T, V] of a no-grad forward at sweep count K (needs keep_logits=True)."""
+        assert self.keep_logits, "forward_logits needs an engine built with keep_logits=True"
+        self.forward(idx, None, sid=self.sid_of_K(K), train=False)
+        return self.logits
+
+    def set_compile(self, mode="all", dynamic=False):
+        """Accepted for interface parity; there is no tracing compiler on this engine's path."""
+        return self
+
+    @property
+    def mem(self):
+        """Capture seconds per rung and the allocator's view of the device, as the reference's `engine.mem`."""
+        out = {f"capture_K{self.ladder[s]}_s": round(sec, 2) for s, sec in self.capture_seconds.items()
+               if s < len(self.ladder)}
+        if self.device.type == "cuda":
+            out["peak_gb"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+            out["reserved_gb"] = torch.cuda.memory_reserved(self.device) / 2 ** 30
+        return out
+
+    def wave_stats(self, K):
+        """Schedule counters of one layer's wavefront at sweep count K (`engine.stats` of the reference):
+        steps per layer, the largest window and the rows swept per step."""
+        n = self.T // self.C
+        return {"steps": n + K - 1, "max_active": min(K, n), "rows_per_step": self.B * self.C * min(K, n),
+                "layers": self.L, "chunks": n}
+
     def _window_store(self, K):
         """What every step read from the tape's window (K_in, V_in of all window chunks, the entering chunk
         raw): [steps, B, K*C, h, dh] x 2 for the layer in flight.  Rolling the tape back one step in the
@@ -310,3 +354,25 @@ class Wave3DEngine(WaveScanEngine):
                 self.dVp[:, wk] += dV
             self.stats["bwd_cells"] += G
         return dcg_stash, u_stash
+
+
+def make_engine(model, B, T, engine="x", C=64, ladder=(8, 16, 32), **kw):
+    """Factory with the reference's signature (engines/wave3d/wave3d.py:203): returns the wavefront engine
+    for micro-batches of B sequences of length T.  `engine` is accepted for compatibility ("x" and "vmap"
+    name two implementations of one operator in the reference; there is one here).  Keyword arguments of
+    the reference that steer its memory policy or library kernels (`seg_steps`, `use_ckpt`, `attn_impl`,
+    `n_snapshots`, `sac`, `store_frac`, `compile_bodies`, `fused`, `reentrant`, `stash_attn`, `defer_dw`,
+    `fused_refine`) have no counterpart and are ignored; `graphs` maps to `use_graphs`, `local_window` must
+    agree with the model's config (the window is part of the operator), `raw_diag` must be true or absent
+    (a position always reads its own raw key / value here, which is what makes K = C consistent with the
+    sequential scan's convention)."""
+    ignored = ("seg_steps", "use_ckpt", "attn_impl", "n_snapshots", "sac", "store_frac", "compile_bodies", "fused",
+               "reentrant", "stash_attn", "defer_dw", "fused_refine")
+    kw = {k: v for k, v in kw.items() if k not in ignored}
+    if "graphs" in kw:
+        kw["use_graphs"] = bool(kw.pop("graphs"))
+    assert kw.pop("raw_diag", True), "the refined-diagonal variant of the reference operator is not implemented"
+    lw = kw.pop("local_window", None)
+    assert not lw or int(lw) == int(model.cfg.local_window or 0), "local_window is read from the model's config"
+    kw.setdefault("autocast_bf16", next(model.parameters()).is_cuda)
+    return Wave3DEngine(model, list(ladder), B, T, C=C, **kw)

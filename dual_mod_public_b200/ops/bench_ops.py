@@ -103,8 +103,17 @@ def main():
     o, lse, ssq = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)
     z = lambda *s: torch.zeros(*s, device=DEV)
     att_f = 4.0 * B * h * c * dh          # flops per key for QK^T + PV
+
+    def both(name, fn, flops):
+        """The op through the tcgen05 kernel and through the warp-MMA kernel it replaces."""
+        for tag_, flag in (("tcgen05", True), ("mma.sync", False)):
+            ops.ATTN_TC = flag
+            report(f"{name} [{tag_}]", T(fn), flops=flops)
+        ops.ATTN_TC = type(ops).ATTN_TC
+        ops.tc_check()
+
     if want("prefix_fwd"):
-        report("prefix_fwd", T(lambda: ops.prefix_fwd(qc, Kc, Vc, pos0, scale, 0)), flops=att_f * pos0)
+        both("prefix_fwd", lambda: ops.prefix_fwd(qc, Kc, Vc, pos0, scale, 0), att_f * pos0)
     if want("tail_fwd"):
         report("tail_fwd", T(lambda: ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)), flops=att_f * c / 2)
     dO = rnd(B, c, h, dh, dtype=torch.float32)
@@ -115,16 +124,39 @@ def main():
                flops=2.5 * att_f * c / 2)
     if want("prefix_dq"):
         doc_c, corr = rnd(B, c, h, dh), rnd(B, c, h, dtype=torch.float32)
-        report("prefix_dq", T(lambda: ops.prefix_dq(qc, Kc, Vc, pos0, scale, 0, lse_c, doc_c, corr, acc[0])),
-               flops=1.5 * att_f * pos0)
+        both("prefix_dq", lambda: ops.prefix_dq(qc, Kc, Vc, pos0, scale, 0, lse_c, doc_c, corr, acc[0]),
+             1.5 * att_f * pos0)
     if want("prefix_dkv"):
         Tq = 2048
         qa, da = rnd(B, Tq, h, dh), rnd(B, Tq, h, dh)
         Ka, Va = rnd(B, Tq, h, dh), rnd(B, Tq, h, dh)
         ca, la = rnd(B, Tq, h, dtype=torch.float32), rnd(B, Tq, h, dtype=torch.float32) + 8.0
         p0 = Tq - pos0 - c                       # as many later query rows as `pos0` keys elsewhere
-        report("prefix_dkv", T(lambda: ops.prefix_dkv(qa, da, ca, la, Ka, Va, p0, c, p0 + c, scale, 0)),
-               flops=2.0 * att_f * (Tq - p0 - c))
+        both("prefix_dkv", lambda: ops.prefix_dkv(qa, da, ca, la, Ka, Va, p0, c, p0 + c, scale, 0),
+             2.0 * att_f * (Tq - p0 - c))
+    if want("bar"):
+        # one lower-right causal read of a block of 1024 query rows over 4096 tape rows (the window read of a
+        # layer-batched wavefront step), next to torch's fused attention backends on the same mask
+        import torch.nn.functional as F
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        for (Bb, hb, dhb) in ((4, 36, 64), (4, 16, 128)):
+            Lq, Lk = 1024, 4096
+            qb, Kb, Vb = rnd(Bb, Lq, hb, dhb), rnd(Bb, Lk, hb, dhb), rnd(Bb, Lk, hb, dhb)
+            sc = dhb ** -0.5
+            fl = 4.0 * Bb * hb * dhb * sum(Lk - Lq + i + 1 for i in range(Lq))
+            report(f"attn fwd tcgen05 {Bb}x{hb}x{dhb} {Lq}x{Lk}",
+                   T(lambda: ops.attn_fwd_tc(qb, Kb, Vb, 0, Lk, Lk - Lq, sc, 0, True, 0, Lq=Lq, bm=128, out_dtype=BF)),
+                   flops=fl)
+            qt, kt, vt = (x.transpose(1, 2) for x in (qb, Kb, Vb))
+            mask = torch.ones(Lq, Lk, dtype=torch.bool, device=DEV).tril(Lk - Lq)
+            for be in (SDPBackend.CUDNN_ATTENTION, SDPBackend.EFFICIENT_ATTENTION):
+                try:
+                    with sdpa_kernel(be):
+                        report(f"  torch sdpa {be.name.lower()} (same mask)",
+                               T(lambda: F.scaled_dot_product_attention(qt, kt, vt, attn_mask=mask, scale=sc)), flops=fl)
+                except Exception as e:                     # backend not offered for this case
+                    print(f"  torch sdpa {be.name.lower()}: not available ({str(e)[:60]})", flush=True)
+        ops.tc_check()
     # ---- refine / norms
     cos, sin = build_rope_cache(Tlen, dh, 10000.0, device=DEV)
     cg, glx, k, v = rnd(B, c, 4 * d), rnd(B, Tlen, 2 * d), rnd(B, Tlen, d), rnd(B, Tlen, d)

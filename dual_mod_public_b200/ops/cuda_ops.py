@@ -72,6 +72,8 @@ class _Sigs:
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
+    dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
+    dmb_attn_dkv_tc = [_p, _p, _p, _p, _i, _p, _p, _v, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p]
     dmb_attn_fwd_tc = [_p, _v, _i, _p, _p, _v, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
                        _i, _i, _p, _p]
 
@@ -104,6 +106,7 @@ class CudaOps(TorchOps):
         self.launches = 0
         self._scratch = {}
         self.gemm = None                       # set by enable_gemm()
+        self._tc_err = torch.zeros(1, dtype=torch.int32, device=self.device)   # raised by the tcgen05 attention kernels
         if os.environ.get("DMB_GEMM", "tcgen05") == "tcgen05":
             from .gemm import Tcgen05Gemm
             self.gemm = Tcgen05Gemm(self.lib, self.device)
@@ -365,6 +368,13 @@ class CudaOps(TorchOps):
         else:
             o_c = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
             lse_c = torch.empty(B, c, h, dtype=F32, device=q_r.device)
+        if self.ATTN_TC and c == 64 and self._tc_ok(q_r, Kc, Vc):
+            self.attn_fwd_tc(q_r, Kc, Vc, lo, pos0, pos0 + qoff, scale, window, Lq=c, bm=64, out=(o_c, lse_c))
+            if out is not None and o_c is not out[0]:
+                out[0].copy_(o_c)
+                out[1].copy_(lse_c)
+                return out
+            return o_c, lse_c
         self._ck(self.lib.dmb_prefix_fwd(q_r.data_ptr(), _tv(q_r), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          o_c.data_ptr(), lse_c.data_ptr(), B, c, h, dh, lo, pos0,
                                          scale, window, 1, 0, qoff, self._st()), "prefix_fwd")
@@ -377,8 +387,11 @@ class CudaOps(TorchOps):
     # lane layout of the M = 64 accumulator in tensor memory (0: sixteen rows per 32-lane quarter)
     TC_LANE_MODE = int(os.environ.get("DMB_TC_LANE_MODE", "0"))
 
+    # reads of the committed tape go through the tcgen05 kernel (DMB_ATTN_TC=0: the warp-MMA kernels)
+    ATTN_TC = os.environ.get("DMB_ATTN_TC", "1") == "1"
+
     def attn_fwd_tc(self, q, Kc, Vc, lo, hi, qbase, scale, window=0, causal=False, causal_excl=1, Lq=None, G=1,
-                    grow=0, bm=None, out_dtype=F32, lane_mode=None):
+                    grow=0, bm=None, out_dtype=F32, lane_mode=None, out=None):
         """Attention forward on tcgen05 (csrc/attn_tc.cu).  q: [B, rows, h, dh] bf16 view; group z (of G) takes
         its rows [z*grow, z*grow + Lq), sits at positions qbase + z*grow + i and reads the tape rows
         max(0, lo + z*grow) <= j < hi + z*grow of Kc / Vc [B, T, h, dh], under the causal rule
@@ -387,10 +400,12 @@ class CudaOps(TorchOps):
         B, rows, h, dh = q.shape
         Lq = rows if Lq is None else Lq
         bm = bm or (128 if Lq >= 128 else 64)
-        o = torch.empty(B, G, Lq, h, dh, dtype=out_dtype, device=q.device)
-        lse = torch.empty(B, G, Lq, h, dtype=F32, device=q.device)
-        if not hasattr(self, "_tc_err"):
-            self._tc_err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if out is not None:                                  # dense buffers of B*G*Lq rows
+            o, lse = out
+            out_dtype = o.dtype
+        else:
+            o = torch.empty(B, G, Lq, h, dh, dtype=out_dtype, device=q.device)
+            lse = torch.empty(B, G, Lq, h, dtype=F32, device=q.device)
         self._ck(self.lib.dmb_attn_fwd_tc(
             q.data_ptr(), _tv(q), rows, Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), Kc.shape[1], o.data_ptr(),
             int(out_dtype == BF16), lse.data_ptr(), B, G, Lq, h, dh, lo, hi, qbase, grow, scale, window,
@@ -398,9 +413,43 @@ class CudaOps(TorchOps):
             self._tc_err.data_ptr(), self._st()), "attn_fwd_tc")
         return o, lse
 
+    def attn_dq_tc(self, q, do_c, Kc, Vc, lo, hi, qbase, scale, window, lse, corr, dq, G=1, grow=0, accumulate=True):
+        """Query side of a tape read's backward on tcgen05: dq [B, G*64, h, dh] fp32 (dense) += dS K, with
+        dS = exp(s - lse) (d o . v - corr) scale; group z reads tape rows max(0, lo + z*grow) <= j < hi + z*grow.
+        lse, corr: dense [B, G*64, h] fp32."""
+        B, rows, h, dh = q.shape
+        self._ck(self.lib.dmb_attn_dq_tc(
+            q.data_ptr(), _tv(q), do_c.data_ptr(), _tv(do_c), rows, Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), Kc.shape[1],
+            lse.data_ptr(), corr.data_ptr(), dq.data_ptr(), B, G, h, dh, lo, hi, qbase, grow, scale, window,
+            int(accumulate), self._tc_err.data_ptr(), self._st()), "attn_dq_tc")
+
+    def attn_dkv_tc(self, q_all, doc_all, corr_all, lse_all, Kc, Vc, pos0, q_start, q_end, scale, window=0, G=1,
+                    grow=0, span=1 << 30, out=None):
+        """Key side on tcgen05: (dK, dV) [B, G*64, h, dh] fp32 of the tape rows [pos0 + z*grow, +64) gathered
+        over the query positions [max(q_start, chunk end), min(q_end, chunk start + span))."""
+        B, T, h, dh = q_all.shape
+        if out is None:
+            out = (torch.empty(B, G * 64, h, dh, dtype=F32, device=q_all.device),
+                   torch.empty(B, G * 64, h, dh, dtype=F32, device=q_all.device))
+        self._ck(self.lib.dmb_attn_dkv_tc(
+            q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(), lse_all.data_ptr(), T, Kc.data_ptr(),
+            Vc.data_ptr(), _tv(Kc), Kc.shape[1], out[0].data_ptr(), out[1].data_ptr(), B, G, h, dh, pos0, q_start,
+            q_end, grow, span, scale, window, self._tc_err.data_ptr(), self._st()), "attn_dkv_tc")
+        return out
+
+    @staticmethod
+    def _tc_ok(q, Kc, Vc):
+        """Operands the tensor maps can describe: bf16, 16-byte aligned, rows of h*dh dense elements, strides in
+        whole 16-byte units, K and V tapes laid out alike."""
+        def ok(t):
+            return (t.dtype == BF16 and t.dim() == 4 and t.data_ptr() % 16 == 0 and _dense_tail(t, 2)
+                    and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0)
+        return (ok(q) and ok(Kc) and ok(Vc) and q.shape[3] in (64, 128) and Kc.stride() == Vc.stride()
+                and Kc.shape == Vc.shape)
+
     def tc_check(self):
         """Host read of the tcgen05 attention kernels' error flag (a pipeline wait that ran out)."""
-        if hasattr(self, "_tc_err") and self._tc_err.item() != 0:
+        if self._tc_err.item() != 0:
             raise RuntimeError("tcgen05 attention: a pipeline wait ran out (kernel aborted its tile loop)")
 
     def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff=0):
@@ -414,6 +463,8 @@ class CudaOps(TorchOps):
         if not ok:
             return super().prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff)
         lse_c, corr = lse_c.contiguous(), corr.contiguous()
+        if self.ATTN_TC and c == 64 and self._tc_ok(q_r, Kc, Vc) and self._tc_ok(do_c, Kc, Vc):
+            return self.attn_dq_tc(q_r, do_c, Kc, Vc, lo, pos0, pos0 + qoff, scale, window, lse_c, corr, dq_acc)
         self._ck(self.lib.dmb_prefix_dq(q_r.data_ptr(), _tv(q_r), do_c.data_ptr(), _tv(do_c), Kc.data_ptr(),
                                         Vc.data_ptr(), _tv(Kc), lse_c.data_ptr(), corr.data_ptr(),
                                         dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, 1, 0, qoff, self._st()),
@@ -429,6 +480,9 @@ class CudaOps(TorchOps):
             return super().prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end)
         dK = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
         dV = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
+        if self.ATTN_TC and c == 64 and self._tc_ok(q_all, Kc, Vc):
+            return self.attn_dkv_tc(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, q_start, q_end, scale, window,
+                                    out=(dK, dV))
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(),
                                          lsec_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          dK.data_ptr(), dV.data_ptr(), B, T, c, h, dh, pos0, q_start, q_end, scale,
@@ -479,6 +533,9 @@ class CudaOps(TorchOps):
             return super().win_near_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window)
         dK = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
         dV = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
+        if self.ATTN_TC and C == 64 and self._tc_ok(q_all, Kc, Vc):
+            return self.attn_dkv_tc(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0 * C, q_lo, min(q_hi, T), scale,
+                                    window, G=G, grow=C, span=span, out=(dK, dV))
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), docn_all.data_ptr(), corrn_all.data_ptr(),
                                          lsen_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), dK.data_ptr(),
                                          dV.data_ptr(), B, T, C, h, dh, j0 * C, q_lo, min(q_hi, T), scale, window,
@@ -547,6 +604,10 @@ class CudaOps(TorchOps):
         B, rows, h, dh = q_win.shape
         o_n = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
         lse_n = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
+        if self.ATTN_TC and C == 64 and self._tc_ok(q_win, Kc, Vc):
+            self.attn_fwd_tc(q_win, Kc, Vc, lo, pos0, pos0, scale, window, Lq=C, G=rows // C, grow=C, bm=64,
+                             out=(o_n, lse_n))
+            return o_n, lse_n
         self._ck(self.lib.dmb_prefix_fwd(q_win.data_ptr(), _tv(q_win), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          o_n.data_ptr(), lse_n.data_ptr(), B, C, h, dh, lo, pos0, scale, window,
                                          rows // C, C, 0, self._st()), "win_near_fwd")
@@ -558,6 +619,9 @@ class CudaOps(TorchOps):
         if not ok:
             return super().win_near_dq(q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window)
         B, rows, h, dh = q_win.shape
+        if self.ATTN_TC and C == 64 and self._tc_ok(q_win, Kc, Vc) and self._tc_ok(do_n, Kc, Vc):
+            return self.attn_dq_tc(q_win, do_n, Kc, Vc, lo, pos0, pos0, scale, window, lse_n, corr_n, dq_acc,
+                                   G=rows // C, grow=C)
         self._ck(self.lib.dmb_prefix_dq(q_win.data_ptr(), _tv(q_win), do_n.data_ptr(), _tv(do_n), Kc.data_ptr(),
                                         Vc.data_ptr(), _tv(Kc), lse_n.data_ptr(), corr_n.data_ptr(),
                                         dq_acc.data_ptr(), B, C, h, dh, lo, pos0, scale, window, rows // C, C, 0,

@@ -99,5 +99,96 @@ def test_strided_query_view_and_agreement_with_prefix_fwd(ops):
     qv = q_all[:, pos0:pos0 + c]
     o_tc, lse_tc = ops.attn_fwd_tc(qv, K, V, 0, pos0, pos0, scale, Lq=c, bm=64)
     ops.tc_check()
-    o_mma, lse_mma = ops.prefix_fwd(qv, K, V, pos0, scale)
+    was, ops.ATTN_TC = ops.ATTN_TC, False                  # the warp-MMA kernel behind the same op
+    try:
+        o_mma, lse_mma = ops.prefix_fwd(qv, K, V, pos0, scale)
+    finally:
+        ops.ATTN_TC = was
     assert (o_tc[:, 0] - o_mma).abs().max() < 2e-2 and (lse_tc[:, 0] - lse_mma).abs().max() < 2e-2
+
+
+def _cells(ops, B, T, h, dh, window, seed):
+    """Per-cell whole-prefix reads of a random tape and random upstream gradients, laid out by absolute
+    position as the engines keep them: q, d o_c (bf16), lse_c, corr (fp32)."""
+    from dual_mod_public_b200.ops.torch_ops import TorchOps
+    ref = TorchOps()
+    c, scale = 64, dh ** -0.5
+    q_all, K, V = rnd(B, T, h, dh, seed=seed), rnd(B, T, h, dh, seed=seed + 1), rnd(B, T, h, dh, seed=seed + 2)
+    doc_all = rnd(B, T, h, dh, seed=seed + 3, scale=0.1)
+    lse_all = torch.zeros(B, T, h, device=DEV)
+    corr_all = torch.zeros(B, T, h, device=DEV)
+    for pos0 in range(c, T, c):
+        r = slice(pos0, pos0 + c)
+        o_c, lse_c = ref.prefix_fwd(q_all[:, r], K, V, pos0, scale, window)
+        dlse = rnd(B, c, h, seed=seed + pos0, scale=0.1).float()
+        lse_all[:, r] = lse_c
+        corr_all[:, r] = (doc_all[:, r].float() * o_c).sum(-1) - dlse
+    return ref, q_all, K, V, doc_all, lse_all, corr_all, scale
+
+
+def _close(got, ref, what, tol=2e-2):
+    err = (got.float() - ref.float()).abs().max().item()
+    scale = ref.float().abs().max().item()
+    assert err <= tol * scale + 1e-4, f"{what}: err {err:.4g} scale {scale:.4g}"
+
+
+@pytest.mark.parametrize("dh,window", [(64, 0), (64, 150), (128, 0)])
+def test_backward_query_side_matches_torch_statement(ops, dh, window):
+    B, T, h, c = 2, 512, 2, 64
+    ref, q_all, K, V, doc_all, lse_all, corr_all, scale = _cells(ops, B, T, h, dh, window, 11)
+    for pos0 in (64, 320, 448):
+        r = slice(pos0, pos0 + c)
+        lse_c, corr = lse_all[:, r].contiguous(), corr_all[:, r].contiguous()
+        dq_ref = torch.ones(B, c, h, dh, device=DEV)
+        ref.prefix_dq(q_all[:, r], K, V, pos0, scale, window, lse_c, doc_all[:, r], corr, dq_ref)
+        dq = torch.ones(B, c, h, dh, device=DEV)
+        ops.prefix_dq(q_all[:, r], K, V, pos0, scale, window, lse_c, doc_all[:, r], corr, dq)
+        ops.tc_check()
+        _close(dq, dq_ref, f"dq at pos0 {pos0}")
+
+
+@pytest.mark.parametrize("dh,window", [(64, 0), (64, 150), (128, 0)])
+def test_backward_key_side_matches_torch_statement(ops, dh, window):
+    B, T, h, c = 2, 512, 2, 64
+    ref, q_all, K, V, doc_all, lse_all, corr_all, scale = _cells(ops, B, T, h, dh, window, 21)
+    for pos0 in (0, 192, 384):
+        dK_ref, dV_ref = ref.prefix_dkv(q_all, doc_all, corr_all, lse_all, K, V, pos0, c, pos0 + c, scale, window)
+        dK, dV = ops.prefix_dkv(q_all, doc_all, corr_all, lse_all, K, V, pos0, c, pos0 + c, scale, window)
+        ops.tc_check()
+        _close(dK, dK_ref, f"dK of chunk at {pos0}")
+        _close(dV, dV_ref, f"dV of chunk at {pos0}")
+    # a bounded reader range, as the wavefront engine's near reads use it
+    dK_ref, dV_ref = ref.prefix_dkv(q_all, doc_all, corr_all, lse_all, K, V, 128, c, 256, scale, window, q_end=400)
+    dK, dV = ops.prefix_dkv(q_all, doc_all, corr_all, lse_all, K, V, 128, c, 256, scale, window, q_end=400)
+    _close(dK, dK_ref, "dK, bounded readers")
+    _close(dV, dV_ref, "dV, bounded readers")
+
+
+def test_window_group_launches_match_the_per_chunk_statement(ops):
+    """The wavefront engine's one-launch-per-window forms (grid z = chunk of the window)."""
+    from dual_mod_public_b200.ops.torch_ops import TorchOps
+    ref = TorchOps()
+    B, T, h, dh, C, G = 2, 640, 2, 64, 64, 3
+    q_all, K, V = rnd(B, T, h, dh, seed=31), rnd(B, T, h, dh, seed=32), rnd(B, T, h, dh, seed=33)
+    scale, lo_c, K_sw = dh ** -0.5, 4, 3
+    w = slice(lo_c * C, (lo_c + G) * C)
+    o_ref, lse_ref = ref.win_near_fwd(q_all[:, w], K, V, lo_c * C, (lo_c - K_sw + 1) * C, C, scale)
+    o, lse = ops.win_near_fwd(q_all[:, w], K, V, lo_c * C, (lo_c - K_sw + 1) * C, C, scale)
+    ops.tc_check()
+    _close(o, o_ref, "near o")
+    _close(lse, lse_ref, "near lse")
+    do_n = rnd(B, G * C, h, dh, seed=34, scale=0.1)
+    corr = ((do_n.float() * o_ref).sum(-1) - rnd(B, G * C, h, seed=35, scale=0.1).float()).contiguous()
+    dq_ref, dq = torch.zeros(B, G * C, h, dh, device=DEV), torch.zeros(B, G * C, h, dh, device=DEV)
+    ref.win_near_dq(q_all[:, w], K, V, lo_c * C, (lo_c - K_sw + 1) * C, C, scale, lse_ref, do_n, corr, dq_ref)
+    ops.win_near_dq(q_all[:, w], K, V, lo_c * C, (lo_c - K_sw + 1) * C, C, scale, lse_ref.contiguous(), do_n, corr, dq)
+    ops.tc_check()
+    _close(dq, dq_ref, "near dq")
+    doc_all, lse_all, corr_all = torch.zeros_like(q_all), torch.zeros(B, T, h, device=DEV), torch.zeros(B, T, h, device=DEV)
+    doc_all[:, w], lse_all[:, w], corr_all[:, w] = do_n, lse_ref, corr
+    j0, Gk = lo_c - K_sw + 1, G + K_sw - 2
+    dK_ref, dV_ref = ref.win_near_dkv(q_all, doc_all, corr_all, lse_all, K, V, j0, Gk, C, lo_c * C, (lo_c + G) * C, K_sw * C, scale)
+    dK, dV = ops.win_near_dkv(q_all, doc_all, corr_all, lse_all, K, V, j0, Gk, C, lo_c * C, (lo_c + G) * C, K_sw * C, scale)
+    ops.tc_check()
+    _close(dK, dK_ref, "near dK")
+    _close(dV, dV_ref, "near dV")

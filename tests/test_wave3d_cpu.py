@@ -89,3 +89,24 @@ def test_wavefront_reaches_the_exact_scan():
             errs.append((wavefront_model_forward(m, idx, C, K) - ref).abs().max().item())
     assert errs[-1] < 1e-5, errs
     assert errs[2] < 0.5 * errs[0] and errs[2] > 1e-4, errs
+
+
+def test_make_engine_surface_of_the_reference():
+    """`make_engine(model, B, T, engine="x", **kw)` with the reference's keyword arguments, then its calls:
+    forward at a sweep count K (one outside the ladder becomes a new rung), `forward_logits`, `mem`, stats."""
+    from dual_mod_public_b200.engines.wave3d import make_engine
+    cfg, m = build()
+    idx, tgt = _data(cfg, 2, 16, 5)
+    eng = make_engine(m, 2, 16, engine="x", C=4, ladder=(2, 3), graphs=True, attn_impl="cudnn_fe", stash_attn=True,
+                      fused_refine=True, raw_diag=True, keep_logits=True, ops=TorchOps())
+    eng.pack()
+    assert eng.ladder == [2, 3] and eng.set_compile("all") is eng
+    loss3 = eng.forward_K(idx, tgt, 3).clone()
+    ref = wavefront_model_forward(m, idx, 4, 3)
+    ref_loss = torch.nn.functional.cross_entropy(ref.float().view(-1, ref.shape[-1]), tgt.view(-1))
+    assert abs(float(loss3) - float(ref_loss.detach())) < 1e-5
+    logits5 = eng.forward_logits(idx, 5)                      # K = 5 is not on the ladder
+    assert eng.ladder == [2, 3, 5]
+    assert relerr(logits5, wavefront_model_forward(m, idx, 4, 5)) < 1e-5
+    assert eng.wave_stats(3) == {"steps": 6, "max_active": 3, "rows_per_step": 24, "layers": cfg.n_layers, "chunks": 4}
+    assert isinstance(eng.mem, dict)
