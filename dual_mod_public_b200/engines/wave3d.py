@@ -253,8 +253,7 @@ class Wave3DEngine(WaveScanEngine):
             o_f, lse_f = ops.prefix_fwd(S.q_r[:, r], S.Kc, S.Vc, fe, S.scale, self.window, qoff=s * C - fe)
             self.ofar_all[:, r] = o_f
             self.lsefar_all[:, r] = lse_f
-            S.Kc[:, r] = S.kself_r[:, r]
-            S.Vc[:, r] = S.v4[:, r]
+            # (the chunk's raw rows are on the tape already: `_raw_tape` put every chunk's there before step 0)
         K_in, V_in = S.Kc[:, w], S.Vc[:, w]
         if win is not None:
             win[0][s][:, :G * C] = K_in
@@ -271,8 +270,16 @@ class Wave3DEngine(WaveScanEngine):
             save[s] = (o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n)
         self.stats["fwd_cells"] += G
 
+    @staticmethod
+    def _raw_tape(S):
+        """Every chunk enters the wavefront raw.  No step reads tape rows at or beyond its window's last
+        chunk, so all raw rows go onto the tape in one copy per tape before step 0 instead of one per step."""
+        S.Kc.copy_(S.kself_r)
+        S.Vc.copy_(S.v4)
+
     def _cells_fwd(self, li, sid, S, keep):
         K = self.ladder[sid]
+        self._raw_tape(S)
         for s in range(self.T // self.C + K - 1):
             self._wave_step(S, s, K)
 
@@ -290,6 +297,7 @@ class Wave3DEngine(WaveScanEngine):
         rows = lambda i: slice(i * C, (i + 1) * C)
         # ---- forward re-run of this layer, keeping what every step read and produced
         save = {}
+        self._raw_tape(S)
         for s in range(n + K - 1):
             self._wave_step(S, s, K, save, win)
         for t in (self.dKp, self.dVp, self.DOf_all, self.DLf_all):

@@ -357,8 +357,8 @@ int launch(const void* q, TView vq, int q_rows, const void* Kc, const void* Vc, 
   int rc;
   if ((rc = make_map_3d(&tq, q, cols, q_rows, B, vq.rs, B > 1 ? vq.bs : (long long)q_rows * vq.rs, 64, 64))) return rc;
   // rows at and beyond the end of the largest key range are outside the map: the copy engine zero-fills them
-  const int k_rows = min(tape_rows, g.hi + (G - 1) * g.grow);
-  if (k_rows <= 0) return -1;
+  // (an empty range for every group still needs a valid map: one row, never loaded)
+  const int k_rows = max(1, min(tape_rows, g.hi + (G - 1) * g.grow));
   const long long kbs = B > 1 ? vc.bs : (long long)tape_rows * vc.rs;
   if ((rc = make_map_3d(&tk, Kc, cols, k_rows, B, vc.rs, kbs, 64, 64))) return rc;
   if ((rc = make_map_3d(&tv, Vc, cols, k_rows, B, vc.rs, kbs, 64, 64))) return rc;
@@ -749,8 +749,7 @@ int dmb_attn_dq_tc(const void* q, TView vq, const void* do_c, TView vdo, int q_r
   g.H = H; g.C = BT; g.lo = lo; g.hi = hi; g.qbase = qbase; g.grow = grow; g.window = window; g.accumulate = accumulate;
   g.scale = scale; g.scale_log2 = scale * 1.4426950408889634f;
   const long long cols = (long long)H * dh;
-  const int k_rows = min(tape_rows, hi + (G - 1) * grow);
-  if (k_rows <= 0) return -1;
+  const int k_rows = max(1, min(tape_rows, hi + (G - 1) * grow));
   CUtensorMap a1, a2, y1, y2;
   int rc;
   if ((rc = make_map_3d(&a1, q, cols, q_rows, B, vq.rs, B > 1 ? vq.bs : (long long)q_rows * vq.rs, 64, 64))) return rc;
@@ -781,8 +780,9 @@ int dmb_attn_dkv_tc(const void* q_all, const void* doc_all, const float* corr_al
   if ((rc = make_map_3d(&a1, Kc, cols, tape_rows, B, vc.rs, kbs, 64, 64))) return rc;
   if ((rc = make_map_3d(&a2, Vc, cols, tape_rows, B, vc.rs, kbs, 64, 64))) return rc;
   // query rows at and beyond q_end are outside the maps: zero-filled
-  if ((rc = make_map_3d(&y1, q_all, cols, g.q_end, B, cols, (long long)T * cols, 64, 64))) return rc;
-  if ((rc = make_map_3d(&y2, doc_all, cols, g.q_end, B, cols, (long long)T * cols, 64, 64))) return rc;
+  const int y_rows = max(1, g.q_end);
+  if ((rc = make_map_3d(&y1, q_all, cols, y_rows, B, cols, (long long)T * cols, 64, 64))) return rc;
+  if ((rc = make_map_3d(&y2, doc_all, cols, y_rows, B, cols, (long long)T * cols, 64, 64))) return rc;
   if (dh == 64) return launch_bwd<64, 1>(a1, a2, y1, y2, lse_all, corr_all, dK, dV, B, G, g, gerr, st);
   return launch_bwd<128, 1>(a1, a2, y1, y2, lse_all, corr_all, dK, dV, B, G, g, gerr, st);
 }

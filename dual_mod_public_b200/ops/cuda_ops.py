@@ -387,8 +387,13 @@ class CudaOps(TorchOps):
     # lane layout of the M = 64 accumulator in tensor memory (0: sixteen rows per 32-lane quarter)
     TC_LANE_MODE = int(os.environ.get("DMB_TC_LANE_MODE", "0"))
 
-    # reads of the committed tape go through the tcgen05 kernel (DMB_ATTN_TC=0: the warp-MMA kernels)
-    ATTN_TC = os.environ.get("DMB_ATTN_TC", "1") == "1"
+    # DMB_ATTN_TC=1 sends the 64-row reads of the committed tape (a cell's prefix read, the wavefront's far and
+    # near reads and their backward) through the tcgen05 kernels of csrc/attn_tc.cu.  Default off: at 64 query rows
+    # per (batch, head) an M = 64 accumulator fills only 16 of a math warp's 32 lanes, and measured at the 340M
+    # cell shape (32 x 16 heads, 1024 keys) the warp-MMA kernels are faster (prefix_fwd 66 vs 82 us, prefix_dq
+    # 87 vs 93, prefix_dkv 111 vs 115).  Reads of 128 rows and more (`attn_fwd_tc` with bm=128) are where the
+    # tcgen05 kernel wins: 454 us for a 1024 x 4096 lower-right block at 4 x 36 heads of 64.
+    ATTN_TC = os.environ.get("DMB_ATTN_TC", "0") == "1"
 
     def attn_fwd_tc(self, q, Kc, Vc, lo, hi, qbase, scale, window=0, causal=False, causal_excl=1, Lq=None, G=1,
                     grow=0, bm=None, out_dtype=F32, lane_mode=None, out=None):

@@ -13,7 +13,9 @@ DEV = "cuda:0"
 @pytest.fixture(scope="module")
 def ops():
     from dual_mod_public_b200.ops.cuda_ops import CudaOps
-    return CudaOps(torch.device(DEV))
+    o = CudaOps(torch.device(DEV))
+    o.ATTN_TC = True                 # the ops below go through the tcgen05 kernels whatever the process default is
+    return o
 
 
 def rnd(*s, seed=0, scale=1.0):

@@ -42,6 +42,37 @@ def grads_of(eng, model, idx, tgt):
     return loss, {n: eng.grads.get(p).clone() for n, p in model.named_parameters()}
 
 
+def _rel(a, b):
+    a, b = a.flatten().double(), b.flatten().double()
+    return float((a - b).norm() / (b.norm() + 1e-30))
+
+
+def assert_within_bf16_noise(make, m, idx, tgt, tc=False):
+    """The acceptance rule of the reference's validator (lm/train_1p3b/validate_rawdiag.py:76-88): every
+    gradient group of the bf16 KERNEL engine is within 5e-2 relative of the fp32 engine, or within twice the
+    bf16 noise floor, which is measured here as the same engine in bf16 through the plain-torch op table
+    (same operator, same rounding points, no hand-written kernel) against fp32."""
+    e_k = make(True, None)
+    assert e_k.ops.name == "sm100a"
+    e_f, e_r = make(True, TorchOps()), make(False, TorchOps())
+    n0 = e_k.ops.launches
+    was, e_k.ops.ATTN_TC = e_k.ops.ATTN_TC, tc             # the table is shared by the process: restore it
+    try:
+        lk, gk = grads_of(e_k, m, idx, tgt)
+    finally:
+        e_k.ops.ATTN_TC = was
+    assert e_k.ops.launches - n0 > 50, "the kernel table was not used"
+    lf, gf = grads_of(e_f, m, idx, tgt)
+    lr, gr = grads_of(e_r, m, idx, tgt)
+    assert abs(lk.item() - lr.item()) < max(3e-3, 2 * abs(lf.item() - lr.item())), (lk.item(), lf.item(), lr.item())
+    for n in gr:
+        floor, got = _rel(gf[n], gr[n]), _rel(gk[n], gr[n])
+        assert got < 5e-2 or got < 2 * floor, f"{n}: kernel {got:.4f} vs bf16 noise floor {floor:.4f}"
+    if hasattr(e_k.ops, "tc_check"):
+        e_k.ops.tc_check()
+    return e_k
+
+
 @pytest.mark.parametrize("kw,c,K", [(dict(), 64, 4), (dict(kmod_vraw_heads=1), 32, 32), (dict(local_window=100), 64, 2),
                                     (MRK, 64, 3), (dict(gate_rank=16, ctx_rank=24), 64, 3)])
 def test_kernel_engine_matches_fp32_torch_engine(kw, c, K):
@@ -49,19 +80,8 @@ def test_kernel_engine_matches_fp32_torch_engine(kw, c, K):
     B, T = 4, 256
     idx, tgt = batch(cfg, B, T)
     sched = uniform_chunks(T, c, K)
-    e_k = WaveScanEngine(m, [sched], B, T, autocast_bf16=True, backend="fused")
-    assert e_k.ops.name == "sm100a"
-    e_r = WaveScanEngine(m, [sched], B, T, autocast_bf16=False, backend="fused", ops=TorchOps())
-    n0 = e_k.ops.launches
-    lk, gk = grads_of(e_k, m, idx, tgt)
-    assert e_k.ops.launches - n0 > 50, "the kernel table was not used"
-    lr, gr = grads_of(e_r, m, idx, tgt)
-    assert abs(lk.item() - lr.item()) < 3e-2, (lk.item(), lr.item())
-    for n in gr:
-        a, b = gk[n].flatten().double(), gr[n].flatten().double()
-        cos = (a @ b) / (a.norm() * b.norm() + 1e-30)
-        assert cos > 0.98, f"{n}: cos {cos:.4f}"
-        assert (a.norm() / (b.norm() + 1e-30) - 1).abs() < 0.1, n
+    make = lambda bf16, ops: WaveScanEngine(m, [sched], B, T, autocast_bf16=bf16, backend="fused", ops=ops)
+    e_k = assert_within_bf16_noise(make, m, idx, tgt)
     assert e_k.debug_scan() == []
 
 
@@ -71,18 +91,25 @@ def test_wavefront_kernel_engine_matches_fp32_torch_engine(dh, K, kw):
     cfg, m = build(d=256, heads=256 // dh, **kw)
     B, T = 4, 256
     idx, tgt = batch(cfg, B, T)
-    e_k = Wave3DEngine(m, [K], B, T, C=64, autocast_bf16=True, backend="fused")
-    e_r = Wave3DEngine(m, [K], B, T, C=64, autocast_bf16=False, backend="fused", ops=TorchOps())
-    n0 = e_k.ops.launches
-    lk, gk = grads_of(e_k, m, idx, tgt)
-    assert e_k.ops.launches - n0 > 50, "the kernel table was not used"
-    lr, gr = grads_of(e_r, m, idx, tgt)
-    assert abs(lk.item() - lr.item()) < 3e-2, (lk.item(), lr.item())
-    for n in gr:
-        a, b = gk[n].flatten().double(), gr[n].flatten().double()
-        cos = (a @ b) / (a.norm() * b.norm() + 1e-30)
-        assert cos > 0.98, f"{n}: cos {cos:.4f}"
-        assert (a.norm() / (b.norm() + 1e-30) - 1).abs() < 0.1, n
+    make = lambda bf16, ops: Wave3DEngine(m, [K], B, T, C=64, autocast_bf16=bf16, backend="fused", ops=ops)
+    assert_within_bf16_noise(make, m, idx, tgt)
+
+
+@pytest.mark.parametrize("engine,dh,K,kw", [("cell", 64, 4, dict()), ("cell", 64, 2, dict(local_window=100)),
+                                            ("wave", 64, 3, dict()), ("wave", 128, 2, dict()),
+                                            ("wave", 64, 3, dict(local_window=100))])
+def test_engines_on_the_tcgen05_attention_kernels(engine, dh, K, kw):
+    """Both engines with their tape reads (and the reads' backward) routed through the tcgen05 kernels."""
+    from dual_mod_public_b200.engines.wave3d import Wave3DEngine
+    cfg, m = build(d=256, heads=256 // dh, **kw)
+    B, T = 4, 256
+    idx, tgt = batch(cfg, B, T)
+    if engine == "cell":
+        make = lambda bf16, ops: WaveScanEngine(m, [uniform_chunks(T, 64, K)], B, T, autocast_bf16=bf16,
+                                                backend="fused", ops=ops)
+    else:
+        make = lambda bf16, ops: Wave3DEngine(m, [K], B, T, C=64, autocast_bf16=bf16, backend="fused", ops=ops)
+    assert_within_bf16_noise(make, m, idx, tgt, tc=True)
 
 
 @pytest.mark.parametrize("kw", [dict(), MRK])
