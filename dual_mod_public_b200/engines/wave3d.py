@@ -302,33 +302,32 @@ class Wave3DEngine(WaveScanEngine):
             self._wave_step(S, s, K, save, win)
         for t in (self.dKp, self.dVp, self.DOf_all, self.DLf_all):
             t.zero_()
+        # per-step scratch of the partial's gradient: written (not accumulated) by the tail kernel
+        do_c_buf = torch.empty(B, K * C, h, dh, dtype=f32, device=dev)
+        dlse_c_buf = torch.empty(B, K * C, h, dtype=f32, device=dev)
         for s in range(n + K - 2, -1, -1):
             lo, hi = max(0, s - K + 1), min(s, n - 1)
             G, w, j = hi - lo + 1, slice(lo * C, (hi + 1) * C), s - K + 1
-            # the chunk whose commit is this step: gather the far reads of its final rows (still on the tape)
-            far_grad = None
+            # the chunk whose commit is this step: the far reads of its final rows (still on the tape) are
+            # gathered straight into the pending gradient of those rows
             if j >= 0 and (j + K) * C < self.T:
-                far_grad = ops.prefix_dkv(S.q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc,
-                                          j * C, C, (j + K) * C, scale, self.window)
+                ops.prefix_dkv(S.q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc, j * C, C, (j + K) * C, scale,
+                               self.window, out=(self.dKp[:, rows(j)], self.dVp[:, rows(j)]), accumulate=True)
             Kc[:, w] = win[0][s][:, :G * C]                     # the tape as step s read it
             Vc[:, w] = win[1][s][:, :G * C]
             o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n = save.pop(s)
-            dK_out, dV_out = self.dKp[:, w].clone(), self.dVp[:, w].clone()
-            if far_grad is not None:
-                dK_out[:, :C] += far_grad[0]
-                dV_out[:, :C] += far_grad[1]
-            d_o = self._refine_bwd(S, w, o, ssq, raw, dK_out, dV_out, offs[s], None)
+            # gradient of the rows this step wrote: read in place (window views of the pending arrays)
+            d_o = self._refine_bwd(S, w, o, ssq, raw, self.dKp[:, w], self.dVp[:, w], offs[s], None)
             if j >= 0:                                          # chunk j's K-th read is the layer's output
                 d_o[:, :C] += S.dO_all[:, rows(j)].reshape(B, C, d)
             d_o = d_o.view(B, G * C, h, dh)
-            do_c = torch.zeros(B, G * C, h, dh, dtype=f32, device=dev)
-            dlse_c = torch.zeros(B, G * C, h, dtype=f32, device=dev)
-            dq_w = torch.zeros(B, G * C, h, dh, dtype=f32, device=dev)
-            dK_in, dV_in = ops.win_tail_bwd(d_o, S.q_r[:, w], S.kself_r[:, w], S.v4[:, w], Kc[:, w], Vc[:, w],
-                                            o_c, lse_c, o, lse, C, scale, dq_w, S.dks_r[:, w], S.dv4[:, w],
-                                            do_c, dlse_c, self.window)
-            self.dKp[:, w] = dK_in                              # gradient of what step s read = rows of step s-1
-            self.dVp[:, w] = dV_in
+            do_c = do_c_buf[:, :G * C] if G == K else torch.empty(B, G * C, h, dh, dtype=f32, device=dev)
+            dlse_c = dlse_c_buf[:, :G * C] if G == K else torch.empty(B, G * C, h, dtype=f32, device=dev)
+            # gradient of what step s read = rows of step s-1: replaces the pending gradient of the window's
+            # rows; d q goes straight into the layer's array
+            ops.win_tail_bwd(d_o, S.q_r[:, w], S.kself_r[:, w], S.v4[:, w], Kc[:, w], Vc[:, w], o_c, lse_c, o, lse, C,
+                             scale, S.dq_r[:, w], S.dks_r[:, w], S.dv4[:, w], do_c, dlse_c, self.window, init=2,
+                             dkv_out=(self.dKp[:, w], self.dVp[:, w]))
             if s < n:                                           # chunk s entered here: it read its raw rows
                 r = rows(s)
                 S.dks_r[:, r] += self.dKp[:, r]
@@ -340,26 +339,22 @@ class Wave3DEngine(WaveScanEngine):
                                self.DLf_all[:, w], self.docn_all[:, w], self.corrn_all[:, w], self.lsen_all[:, w])
             corr_n = self.corrn_all[:, w].contiguous()
             ops.win_near_dq(S.q_r[:, w], Kc, Vc, lo * C, (lo - K + 1) * C, C, scale, lse_n.contiguous(),
-                            self.docn_all[:, w], corr_n, dq_w, self.window)
-            S.dq_r[:, w] += dq_w
+                            self.docn_all[:, w], corr_n, S.dq_r[:, w], self.window)
             if s < n:                                           # every sweep of chunk s has been processed
                 r, fe = rows(s), max(0, s - K + 1) * C
                 corr_f = ((self.DOf_all[:, r] * self.ofar_all[:, r]).sum(-1) - self.DLf_all[:, r]).contiguous()
                 self.doc_all[:, r] = self.DOf_all[:, r]
                 self.corr_all[:, r] = corr_f
                 self.lsec_all[:, r] = self.lsefar_all[:, r]
-                dq_s = torch.zeros(B, C, h, dh, dtype=f32, device=dev)
                 ops.prefix_dq(S.q_r[:, r], Kc, Vc, fe, scale, self.window, self.lsefar_all[:, r].contiguous(),
-                              self.doc_all[:, r], corr_f, dq_s, qoff=s * C - fe)
-                S.dq_r[:, r] += dq_s
+                              self.doc_all[:, r], corr_f, S.dq_r[:, r], qoff=s * C - fe)
             # near reads of this step, key side: chunk jk was read by the window chunks in (jk, jk+K-1]
             j0 = max(0, lo - K + 1)
             if hi > j0:
                 wk = slice(j0 * C, hi * C)
-                dK, dV = ops.win_near_dkv(S.q_r, self.docn_all, self.corrn_all, self.lsen_all, Kc, Vc, j0, hi - j0, C,
-                                          lo * C, (hi + 1) * C, K * C, scale, self.window)
-                self.dKp[:, wk] += dK
-                self.dVp[:, wk] += dV
+                ops.win_near_dkv(S.q_r, self.docn_all, self.corrn_all, self.lsen_all, Kc, Vc, j0, hi - j0, C,
+                                 lo * C, (hi + 1) * C, K * C, scale, self.window,
+                                 out=(self.dKp[:, wk], self.dVp[:, wk]), accumulate=True)
             self.stats["bwd_cells"] += G
         return dcg_stash, u_stash
 

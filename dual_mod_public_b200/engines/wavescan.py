@@ -828,7 +828,9 @@ class WaveScanEngine:
             kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos, sin)
             v4 = v.unflatten(-1, (h, dh))
             Kc, Vc = self.K_caches[li], self.V_caches[li]
-            dq_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
+            # every cell's first backward sweep WRITES its rows of dq_r in the cell engine; the wavefront engine
+            # accumulates into it from the first step on and needs the zeros
+            dq_r = (torch.empty if type(self) is WaveScanEngine else torch.zeros)(B, T, h, dh, dtype=f32, device=dev)
             dks_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
             dk = torch.zeros(B, T, d, dtype=f32, device=dev)
             dv = torch.zeros(B, T, d, dtype=f32, device=dev)
@@ -942,22 +944,21 @@ class WaveScanEngine:
             d_o = dO_all[:, r].float()
             if self.sat_tau > 0 or self.track_rho:
                 dK_out, dV_out = self._saturate_carry(dK_out, dV_out, d_o)
-            nv = B * c * h * dh                                 # one zeroed scratch, three accumulators
-            acc = torch.zeros(2 * nv + B * c * h, dtype=f32, device=dev)
-            do_c, dq_c = acc[:nv].view(B, c, h, dh), acc[nv:2 * nv].view(B, c, h, dh)
-            dlse_c = acc[2 * nv:].view(B, c, h)
+            # the cell's accumulators: the first sweep processed writes them (no zero fill); d q accumulates
+            # straight into the cell's rows of the layer's array
+            do_c = torch.empty(B, c, h, dh, dtype=f32, device=dev)
+            dlse_c = torch.empty(B, c, h, dtype=f32, device=dev)
             for s in range(n_sweeps - 1, -1, -1):
                 K_in, V_in, o, lse, ssq, raw = st[s]
                 d_o = self._refine_bwd(S, r, o, ssq, raw, dK_out, dV_out, stash_off[(ci, s)],
                                        d_o.view(B, c, d) if s == n_sweeps - 1 else None).view(B, c, h, dh)
                 dK_out, dV_out = ops.tail_bwd(
                     d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
-                    dq_c, dks_r[:, r], dv4[:, r], do_c, dlse_c)
+                    dq_r[:, r], dks_r[:, r], dv4[:, r], do_c, dlse_c, init=3 if s == n_sweeps - 1 else 0)
             # sweep 0 read the raw rows; publish this cell's (d o_c, corr, lse_c) for the earlier cells' gathers
             corr = ops.cell_finish(do_c, dlse_c, o_c, lse_c, dK_out, dV_out, self.doc_all[:, r],
                                    self.corr_all[:, r], self.lsec_all[:, r], dks_r[:, r], dv4[:, r])
-            ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_c)
-            dq_r[:, r] = dq_c
+            ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_r[:, r])
             self.stats["bwd_cells"] += 1
         return dcg_stash, u_stash
 

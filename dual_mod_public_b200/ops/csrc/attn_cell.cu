@@ -156,9 +156,13 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
     TView vks, const bf16* __restrict__ vr, TView vvr, const bf16* __restrict__ Kin, TView vKin,
     const bf16* __restrict__ Vin, TView vVin, const float* __restrict__ o_c,
     const float* __restrict__ lse_c, const bf16* __restrict__ o, const float* __restrict__ lse,
-    float* __restrict__ dq_acc, float* __restrict__ dks_acc, TView vdks, float* __restrict__ dv_acc,
+    float* __restrict__ dq_acc, TView vdq, float* __restrict__ dks_acc, TView vdks, float* __restrict__ dv_acc,
     TView vdv, float* __restrict__ doc_acc, float* __restrict__ dlsec_acc, float* __restrict__ dKin,
-    float* __restrict__ dVin, int H, float scale, int window, int grow) {
+    float* __restrict__ dVin, TView vdkin, int H, float scale, int window, int grow, int flags) {
+  // flags: bit 0 = dq_acc is written instead of added to; bit 1 = the same for doc_acc / dlsec_acc (the
+  // first sweep processed of a cell initialises its accumulators, so nobody has to zero them).  dq_acc and
+  // dKin / dVin are (batch stride, row stride) views: they may be windows of [B, T, h, dh] arrays.
+  const bool init_dq = flags & 1, init_doc = flags & 2;
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = C / 8, PC = C + 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
@@ -174,7 +178,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
   {
     const long long go = (long long)blockIdx.z * grow;
     q += go * vq.rs; ks += go * vks.rs; vr += go * vvr.rs; Kin += go * vKin.rs; Vin += go * vVin.rs;
-    dks_acc += go * vdks.rs; dv_acc += go * vdv.rs;
+    dks_acc += go * vdks.rs; dv_acc += go * vdv.rs; dq_acc += go * vdq.rs; dKin += go * vdkin.rs; dVin += go * vdkin.rs;
   }
   const long long dense_rs = (long long)H * DH;  // contiguous [B,C,H,DH] tensors
   const long long dense_b = (long long)bd * C * dense_rs + hoff;
@@ -201,8 +205,8 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
   const float doc1 = quad_dot_f32<DH>(dO1, o_c + orow1 * DH, t);
   const float dss0 = ps0 * (dsv0 - delta0) * scale, dss1 = ps1 * (dsv1 - delta1) * scale;
   if (t == 0) {
-    dlsec_acc[orow0] += pc0 * (doc0 - delta0);
-    dlsec_acc[orow1] += pc1 * (doc1 - delta1);
+    dlsec_acc[orow0] = (init_doc ? 0.f : dlsec_acc[orow0]) + pc0 * (doc0 - delta0);
+    dlsec_acc[orow1] = (init_doc ? 0.f : dlsec_acc[orow1]) + pc1 * (doc1 - delta1);
   }
   load_tile_bf16<DH, NT>(sQ, q + b * vq.bs + hoff, vq.rs, C, tid);
   load_tile_bf16<DH, NT>(sK, Kin + b * vKin.bs + hoff, vKin.rs, C, tid);
@@ -272,8 +276,8 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
     }
   }
   {
-    float* dq0 = dq_acc + orow0 * DH;
-    float* dq1 = dq_acc + orow1 * DH;
+    float* dq0 = dq_acc + b * vdq.bs + i0 * vdq.rs + hoff;
+    float* dq1 = dq_acc + b * vdq.bs + i1 * vdq.rs + hoff;
     float* dk0 = dks_acc + b * vdks.bs + i0 * vdks.rs + hoff;
     float* dk1 = dks_acc + b * vdks.bs + i1 * vdks.rs + hoff;
     float* dv0 = dv_acc + b * vdv.bs + i0 * vdv.rs + hoff;
@@ -290,10 +294,10 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
       float2 g0 = *reinterpret_cast<const float2*>(dO0 + d);
       float2 g1 = *reinterpret_cast<const float2*>(dO1 + d);
       float2 x;
-      x = *reinterpret_cast<float2*>(dq0 + d);
+      x = init_dq ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dq0 + d);
       x.x += A[n][0] + dss0 * k0v.x; x.y += A[n][1] + dss0 * k0v.y;
       *reinterpret_cast<float2*>(dq0 + d) = x;
-      x = *reinterpret_cast<float2*>(dq1 + d);
+      x = init_dq ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dq1 + d);
       x.x += A[n][2] + dss1 * k1v.x; x.y += A[n][3] + dss1 * k1v.y;
       *reinterpret_cast<float2*>(dq1 + d) = x;
       x = *reinterpret_cast<float2*>(dk0 + d);
@@ -308,10 +312,10 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
       x = *reinterpret_cast<float2*>(dv1 + d);
       x.x += ps1 * g1.x; x.y += ps1 * g1.y;
       *reinterpret_cast<float2*>(dv1 + d) = x;
-      x = *reinterpret_cast<float2*>(dc0 + d);
+      x = init_doc ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dc0 + d);
       x.x += pc0 * g0.x; x.y += pc0 * g0.y;
       *reinterpret_cast<float2*>(dc0 + d) = x;
-      x = *reinterpret_cast<float2*>(dc1 + d);
+      x = init_doc ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dc1 + d);
       x.x += pc1 * g1.x; x.y += pc1 * g1.y;
       *reinterpret_cast<float2*>(dc1 + d) = x;
     }
@@ -342,10 +346,10 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
       }
     }
   }
-  float* gk0 = dKin + orow0 * DH;
-  float* gk1 = dKin + orow1 * DH;
-  float* gv0 = dVin + orow0 * DH;
-  float* gv1 = dVin + orow1 * DH;
+  float* gk0 = dKin + b * vdkin.bs + i0 * vdkin.rs + hoff;
+  float* gk1 = dKin + b * vdkin.bs + i1 * vdkin.rs + hoff;
+  float* gv0 = dVin + b * vdkin.bs + i0 * vdkin.rs + hoff;
+  float* gv1 = dVin + b * vdkin.bs + i1 * vdkin.rs + hoff;
 #pragma unroll
   for (int n = 0; n < DH / 8; ++n) {
     int d = n * 8 + 2 * t;
@@ -528,17 +532,17 @@ int dmb_tail_fwd(const void* q, TView vq, const void* ks, TView vks, const void*
 int dmb_tail_bwd(const float* dO, const void* q, TView vq, const void* ks, TView vks, const void* vr,
                  TView vvr, const void* Kin, TView vKin, const void* Vin, TView vVin,
                  const float* o_c, const float* lse_c, const void* o, const float* lse, float* dq_acc,
-                 float* dks_acc, TView vdks, float* dv_acc, TView vdv, float* doc_acc,
-                 float* dlsec_acc, float* dKin, float* dVin, int B, int c, int H, int dh, float scale,
-                 int window, int G, int grow, cudaStream_t st) {
+                 TView vdq, float* dks_acc, TView vdks, float* dv_acc, TView vdv, float* doc_acc,
+                 float* dlsec_acc, float* dKin, float* dVin, TView vdkin, int B, int c, int H, int dh, float scale,
+                 int window, int G, int grow, int flags, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)4 * C * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
     auto kern = tail_bwd_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
                                             vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
-                                            lse_c, (const bf16*)o, lse, dq_acc, dks_acc, vdks, dv_acc, vdv,
-                                            doc_acc, dlsec_acc, dKin, dVin, H, scale, window, grow);
+                                            lse_c, (const bf16*)o, lse, dq_acc, vdq, dks_acc, vdks, dv_acc, vdv,
+                                            doc_acc, dlsec_acc, dKin, dVin, vdkin, H, scale, window, grow, flags);
   })
   DMB_CHECK_LAUNCH();
   return 0;

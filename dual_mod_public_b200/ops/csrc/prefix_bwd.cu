@@ -23,8 +23,8 @@ template <int DH, int C>
 __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dkv_kernel(
     const bf16* __restrict__ q_all, const bf16* __restrict__ doc_all, const float* __restrict__ corr_all,
     const float* __restrict__ lsec_all, const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc,
-    float* __restrict__ dK, float* __restrict__ dV, int T, int H, int pos0, int q_start, int q_end,
-    float scale, int window, int grow, int span) {
+    float* __restrict__ dK, float* __restrict__ dV, TView vdkv, int accumulate, int T, int H, int pos0, int q_start,
+    int q_end, float scale, int window, int grow, int span) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = C / 8, PC = C + 8, QT = C;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sK = reinterpret_cast<bf16*>(smem_raw);
@@ -40,7 +40,6 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dkv_kernel(
   const int g = lane >> 2, t4 = lane & 3;
   // groups (gridDim.z > 1): key chunk z of a run of consecutive chunks; its readers are the query rows
   // [max(q_start, chunk end), min(q_end, chunk start + span)); outputs are dense [B, G, C, H, DH]
-  const int bd = b * gridDim.z + blockIdx.z;
   pos0 += blockIdx.z * grow;
   q_start = max(q_start, pos0 + C);
   q_end = min(q_end, pos0 + span);
@@ -149,18 +148,24 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dkv_kernel(
     }
     __syncthreads();   // sP / sdS and this stage's tiles are free again
   }
+  // outputs: (batch stride, row stride) views, group z at rows [z * grow, z * grow + C); added to when
+  // `accumulate` (the rows may be a window of a pending-gradient array)
   const int ka = row0 + g, kb = ka + 8;
-  float* k0p = dK + (((long long)bd * C + ka) * H + h) * DH;
-  float* k1p = dK + (((long long)bd * C + kb) * H + h) * DH;
-  float* v0p = dV + (((long long)bd * C + ka) * H + h) * DH;
-  float* v1p = dV + (((long long)bd * C + kb) * H + h) * DH;
+  const long long ob = b * vdkv.bs + (long long)blockIdx.z * grow * vdkv.rs + hoff;
+  float* outs[4] = {dK + ob + ka * vdkv.rs, dK + ob + kb * vdkv.rs, dV + ob + ka * vdkv.rs, dV + ob + kb * vdkv.rs};
 #pragma unroll
   for (int n = 0; n < DH / 8; ++n) {
     const int d = n * 8 + 2 * t4;
-    *reinterpret_cast<float2*>(k0p + d) = make_float2(GK[n][0], GK[n][1]);
-    *reinterpret_cast<float2*>(k1p + d) = make_float2(GK[n][2], GK[n][3]);
-    *reinterpret_cast<float2*>(v0p + d) = make_float2(GV[n][0], GV[n][1]);
-    *reinterpret_cast<float2*>(v1p + d) = make_float2(GV[n][2], GV[n][3]);
+    float2 vals[4] = {make_float2(GK[n][0], GK[n][1]), make_float2(GK[n][2], GK[n][3]),
+                      make_float2(GV[n][0], GV[n][1]), make_float2(GV[n][2], GV[n][3])};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (accumulate) {
+        const float2 o = *reinterpret_cast<const float2*>(outs[u] + d);
+        vals[u].x += o.x; vals[u].y += o.y;
+      }
+      *reinterpret_cast<float2*>(outs[u] + d) = vals[u];
+    }
   }
 }
 
@@ -171,7 +176,7 @@ template <int DH, int C>
 __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
     const bf16* __restrict__ q, TView vq, const bf16* __restrict__ do_c, TView vdo,
     const bf16* __restrict__ Kc, const bf16* __restrict__ Vc, TView vc, const float* __restrict__ lse_c,
-    const float* __restrict__ corr, float* __restrict__ dq_acc, int H, int lo, int pos0, float scale,
+    const float* __restrict__ corr, float* __restrict__ dq_acc, TView vdq, int H, int lo, int pos0, float scale,
     int window, int grow, int qoff) {
   constexpr int P = Tile<DH>::PITCH, NT = C * 2, NB = KT / 8;
   constexpr int ST = 2;            // key / value tiles are double-buffered
@@ -283,8 +288,9 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
     }
     __syncthreads();
   }
-  float* dq0 = dq_acc + orow0 * DH;
-  float* dq1 = dq_acc + orow1 * DH;
+  // dq_acc: a (batch stride, row stride) view, group z at rows [z * grow, z * grow + C)
+  float* dq0 = dq_acc + b * vdq.bs + ((long long)blockIdx.z * grow + i0) * vdq.rs + hoff;
+  float* dq1 = dq_acc + b * vdq.bs + ((long long)blockIdx.z * grow + i1) * vdq.rs + hoff;
 #pragma unroll
   for (int n = 0; n < DH / 8; ++n) {
     const int d = n * 8 + 2 * t4;
@@ -302,31 +308,31 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) prefix_dq_kernel(
 extern "C" {
 
 int dmb_prefix_dkv(const void* q_all, const void* doc_all, const float* corr_all, const float* lsec_all,
-                   const void* Kc, const void* Vc, TView vc, float* dK, float* dV, int B, int T, int c, int H,
-                   int dh, int pos0, int q_start, int q_end, float scale, int window, int G, int grow, int span,
-                   cudaStream_t st) {
+                   const void* Kc, const void* Vc, TView vc, float* dK, float* dV, TView vdkv, int accumulate, int B,
+                   int T, int c, int H, int dh, int pos0, int q_start, int q_end, float scale, int window, int G,
+                   int grow, int span, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     constexpr int ST = DH <= 64 ? 1 : 2;
     size_t smem = (((size_t)2 * C + 2 * ST * C) * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
     auto kern = prefix_dkv_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q_all, (const bf16*)doc_all, corr_all, lsec_all,
-                                         (const bf16*)Kc, (const bf16*)Vc, vc, dK, dV, T, H, pos0, q_start,
-                                         q_end < T ? q_end : T, scale, window, grow, span);
+                                         (const bf16*)Kc, (const bf16*)Vc, vc, dK, dV, vdkv, accumulate, T, H, pos0,
+                                         q_start, q_end < T ? q_end : T, scale, window, grow, span);
   })
   DMB_CHECK_LAUNCH();
   return 0;
 }
 
 int dmb_prefix_dq(const void* q, TView vq, const void* do_c, TView vdo, const void* Kc, const void* Vc, TView vc,
-                  const float* lse_c, const float* corr, float* dq_acc, int B, int c, int H, int dh, int lo,
+                  const float* lse_c, const float* corr, float* dq_acc, TView vdq, int B, int c, int H, int dh, int lo,
                   int pos0, float scale, int window, int G, int grow, int qoff, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)2 * C + 4 * KT) * Tile<DH>::PITCH * sizeof(bf16);
     auto kern = prefix_dq_kernel<DH, C>;
     if (set_smem(kern, smem)) return -2;
     kern<<<dim3(H, B, G), C * 2, smem, st>>>((const bf16*)q, vq, (const bf16*)do_c, vdo, (const bf16*)Kc,
-                                         (const bf16*)Vc, vc, lse_c, corr, dq_acc, H, lo, pos0, scale, window, grow, qoff);
+                                         (const bf16*)Vc, vc, lse_c, corr, dq_acc, vdq, H, lo, pos0, scale, window, grow, qoff);
   })
   DMB_CHECK_LAUNCH();
   return 0;

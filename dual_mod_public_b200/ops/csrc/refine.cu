@@ -55,7 +55,7 @@ __global__ void refine_fwd_kernel(const bf16* __restrict__ raw, const float* __r
 
 // dK / dV fp32 dense [B,C,H,DH]; writes dcg (bf16 [rows,4d], gradient w.r.t. cg = rstd*raw) and
 // uhat = o * rstd (bf16 [rows,d]); accumulates dk_acc / dv_acc [.., d] and dglx_acc [.., 2d] (fp32, +=).
-__global__ void refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV,
+__global__ void refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV, TView vdo,
                                   const bf16* __restrict__ raw, const float* __restrict__ ssq,
                                   const bf16* __restrict__ o, const bf16* __restrict__ glx, TView vg,
                                   const bf16* __restrict__ k, TView vk, const bf16* __restrict__ v, TView vv,
@@ -77,8 +77,9 @@ __global__ void refine_bwd_kernel(const float* __restrict__ dK, const float* __r
   float* dgr = dglx_acc + w.b * vdg.bs + w.t * vdg.rs;
   const V8 cs = ld8f(cosb + w.t * half + w.p0), sn = ld8f(sinb + w.t * half + w.p0);
   const long long ob = w.row * d;
-  const V8 a = ld8f(dK + ob + w.c0), bq = ld8f(dK + ob + w.c1);
-  V8 dkpp[2], dvpp[2] = {ld8f(dV + ob + w.c0), ld8f(dV + ob + w.c1)};
+  const long long gb = w.b * vdo.bs + w.t * vdo.rs;       // dK / dV may be a window of a longer [B, T, d] array
+  const V8 a = ld8f(dK + gb + w.c0), bq = ld8f(dK + gb + w.c1);
+  V8 dkpp[2], dvpp[2] = {ld8f(dV + gb + w.c0), ld8f(dV + gb + w.c1)};
 #pragma unroll
   for (int i = 0; i < 8; ++i) {            // transpose of the rotation
     dkpp[0].x[i] = a.x[i] * cs.x[i] + bq.x[i] * sn.x[i];
@@ -170,7 +171,7 @@ extern "C" {
 int dmb_refine_fwd(const void* raw, const float* ssq, const void* glx, TView vg, const void* k, TView vk,
                    const void* v, TView vv, const float* cosb, const float* sinb, void* Kout, void* Vout, TView vo,
                    int B, int C, int H, int DH, int pin_cols, float eps, cudaStream_t st) {
-  if (DH % 16 || H % 4) return -1;
+  if (DH % 16) return -1;
   long long total = (long long)B * C * H * (DH / 16);
   refine_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
       (const bf16*)raw, ssq, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv, cosb, sinb,
@@ -179,15 +180,15 @@ int dmb_refine_fwd(const void* raw, const float* ssq, const void* glx, TView vg,
   return 0;
 }
 
-int dmb_refine_bwd(const float* dK, const float* dV, const void* raw, const float* ssq, const void* o,
+int dmb_refine_bwd(const float* dK, const float* dV, TView vdo, const void* raw, const float* ssq, const void* o,
                    const void* glx, TView vg, const void* k, TView vk, const void* v, TView vv, const float* cosb,
                    const float* sinb, void* dcg, void* uhat, float* dk_acc, TView vdk, float* dv_acc, TView vdv,
                    float* dglx_acc, TView vdg, int B, int C, int H, int DH, int pin_cols, float eps,
                    cudaStream_t st) {
-  if (DH % 16 || H % 4) return -1;
+  if (DH % 16) return -1;
   long long total = (long long)B * C * H * (DH / 16);
   refine_bwd_kernel<<<(unsigned)((total + 127) / 128), 128, 0, st>>>(
-      dK, dV, (const bf16*)raw, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv,
+      dK, dV, vdo, (const bf16*)raw, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv,
       cosb, sinb, (bf16*)dcg, (bf16*)uhat, dk_acc, vdk, dv_acc, vdv, dglx_acc, vdg, B, C, H, DH, pin_cols, eps);
   DMB_CHECK_LAUNCH();
   return 0;
@@ -195,7 +196,7 @@ int dmb_refine_bwd(const float* dK, const float* dV, const void* raw, const floa
 
 int dmb_rmsn_bwd(const void* du, const void* o, const float* ssq, const void* residual, const float* extra, void* out,
                  int out_f32, int rows, int d, int H, float eps, cudaStream_t st) {
-  if (d % 8 || H % 4) return -1;
+  if (d % 8) return -1;
   dim3 grid((rows + 7) / 8), blk(256);
   if (out_f32)
     rmsn_bwd_kernel<float><<<grid, blk, 0, st>>>((const bf16*)du, (const bf16*)o, ssq, (const float*)residual, extra, (float*)out, rows, d, H, eps);

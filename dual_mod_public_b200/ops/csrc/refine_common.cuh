@@ -33,11 +33,17 @@ __device__ __forceinline__ void acc8f(float* p, const V8& v) {
   for (int i = 0; i < 8; ++i) o.x[i] += v.x[i];
   st8f(p, o);
 }
+// the row's 1/rms from its H per-head sums of squares: 16-byte loads when the head count keeps the rows
+// 16-byte aligned, scalar loads otherwise (e.g. 15 heads)
 __device__ __forceinline__ float row_rstd(const float* ssq_row, int H, int d, float eps) {
   float s = 0.f;
-  for (int i = 0; i < H; i += 4) {
-    float4 v = *reinterpret_cast<const float4*>(ssq_row + i);
-    s += v.x + v.y + v.z + v.w;
+  if ((H & 3) == 0) {
+    for (int i = 0; i < H; i += 4) {
+      float4 v = *reinterpret_cast<const float4*>(ssq_row + i);
+      s += v.x + v.y + v.z + v.w;
+    }
+  } else {
+    for (int i = 0; i < H; ++i) s += ssq_row[i];
   }
   return rsqrtf(s / d + eps);
 }

@@ -182,7 +182,8 @@ __global__ void mrk_refine_fwd_kernel(const bf16* __restrict__ raw, const bf16* 
 // dK / dV fp32 dense [B,C,H,DH].  Writes dcg blocks 0, 2, 3 (bf16 [rows,4d]; block 1 = d v_m comes from
 // mrk_vin_bwd), uhat = o * rstd, dvc (bf16 [rows,d]) and the per-(row, head) k_gain gradient dkg [rows,H];
 // accumulates dk_acc / dv_acc [.., d] and dglx_acc [.., 2d] (fp32, +=).
-__global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV, const bf16* __restrict__ raw,
+__global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV, TView vdo,
+                                      const bf16* __restrict__ raw,
                                       const bf16* __restrict__ vc, const float* __restrict__ ssq, const bf16* __restrict__ o,
                                       const bf16* __restrict__ glx, TView vg, const bf16* __restrict__ k, TView vk,
                                       const bf16* __restrict__ v, TView vv, const float* __restrict__ cosb,
@@ -199,8 +200,9 @@ __global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float*
                     v + w.b * vv.bs + w.t * vv.rs, k_gain, H, DH, pin_cols, tau, eps);
   const V8 cs = ld8f(cosb + w.t * half + w.p0), sn = ld8f(sinb + w.t * half + w.p0);
   const long long ob = w.row * d;
-  const V8 a = ld8f(dK + ob + w.c0), bq = ld8f(dK + ob + w.c1);
-  V8 dkpp[2], dvo[2] = {ld8f(dV + ob + w.c0), ld8f(dV + ob + w.c1)};
+  const long long gb = w.b * vdo.bs + w.t * vdo.rs;       // dK / dV may be a window of a longer [B, T, d] array
+  const V8 a = ld8f(dK + gb + w.c0), bq = ld8f(dK + gb + w.c1);
+  V8 dkpp[2], dvo[2] = {ld8f(dV + gb + w.c0), ld8f(dV + gb + w.c1)};
 #pragma unroll
   for (int i = 0; i < 8; ++i) {            // transpose of the rotation
     dkpp[0].x[i] = a.x[i] * cs.x[i] + bq.x[i] * sn.x[i];
@@ -279,7 +281,7 @@ static inline unsigned mrk_blocks(int B, int C, int H, int DH, int threads) {
 
 int dmb_mrk_vin_fwd(const void* raw, const float* ssq, const void* o, const void* w_ctx, const void* vgx, TView vx,
                     void* vin, int B, int C, int H, int DH, float lam, float eps, cudaStream_t st) {
-  if (DH % 16 || H % 4) return -1;
+  if (DH % 16) return -1;
   mrk_vin_fwd_kernel<<<mrk_blocks(B, C, H, DH, 256), 256, 0, st>>>((const bf16*)raw, ssq, (const bf16*)o, (const bf16*)w_ctx,
                                                                  (const bf16*)vgx, vx, (bf16*)vin, B, C, H, DH, lam, eps);
   DMB_CHECK_LAUNCH();
@@ -289,7 +291,7 @@ int dmb_mrk_vin_fwd(const void* raw, const float* ssq, const void* o, const void
 int dmb_mrk_vin_bwd(const void* dvin, const void* raw, const float* ssq, const void* w_ctx, const void* vgx, TView vx,
                     void* dcg, float* dvgx_acc, TView vdx, float* du_hat, int B, int C, int H, int DH, float lam, float eps,
                     cudaStream_t st) {
-  if (DH % 16 || H % 4) return -1;
+  if (DH % 16) return -1;
   mrk_vin_bwd_kernel<<<mrk_blocks(B, C, H, DH, 256), 256, 0, st>>>((const bf16*)dvin, (const bf16*)raw, ssq, (const bf16*)w_ctx,
                                                                  (const bf16*)vgx, vx, (bf16*)dcg, dvgx_acc, vdx, du_hat, B, C,
                                                                  H, DH, lam, eps);
@@ -300,7 +302,7 @@ int dmb_mrk_vin_bwd(const void* dvin, const void* raw, const float* ssq, const v
 int dmb_mrk_refine_fwd(const void* raw, const void* vc, const float* ssq, const void* glx, TView vg, const void* k, TView vk,
                        const void* v, TView vv, const float* cosb, const float* sinb, const float* k_gain, void* Kout,
                        void* Vout, TView vo, int B, int C, int H, int DH, int pin_cols, float tau, float eps, cudaStream_t st) {
-  if (DH % 16 || H % 4) return -1;
+  if (DH % 16) return -1;
   mrk_refine_fwd_kernel<<<mrk_blocks(B, C, H, DH, 128), 128, 0, st>>>(
       (const bf16*)raw, (const bf16*)vc, ssq, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv, cosb, sinb, k_gain,
       (bf16*)Kout, (bf16*)Vout, vo, B, C, H, DH, pin_cols, tau, eps);
@@ -308,14 +310,14 @@ int dmb_mrk_refine_fwd(const void* raw, const void* vc, const float* ssq, const 
   return 0;
 }
 
-int dmb_mrk_refine_bwd(const float* dK, const float* dV, const void* raw, const void* vc, const float* ssq, const void* o,
+int dmb_mrk_refine_bwd(const float* dK, const float* dV, TView vdo, const void* raw, const void* vc, const float* ssq, const void* o,
                        const void* glx, TView vg, const void* k, TView vk, const void* v, TView vv, const float* cosb,
                        const float* sinb, const float* k_gain, void* dcg, void* uhat, void* dvc, float* dkg, float* dk_acc,
                        TView vdk, float* dv_acc, TView vdv, float* dglx_acc, TView vdg, int B, int C, int H, int DH,
                        int pin_cols, float tau, float eps, cudaStream_t st) {
-  if (DH % 16 || H % 4) return -1;
+  if (DH % 16) return -1;
   mrk_refine_bwd_kernel<<<mrk_blocks(B, C, H, DH, 128), 128, 0, st>>>(
-      dK, dV, (const bf16*)raw, (const bf16*)vc, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v,
+      dK, dV, vdo, (const bf16*)raw, (const bf16*)vc, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v,
       vv, cosb, sinb, k_gain, (bf16*)dcg, (bf16*)uhat, (bf16*)dvc, dkg, dk_acc, vdk, dv_acc, vdv, dglx_acc, vdg, B, C, H, DH,
       pin_cols, tau, eps);
   DMB_CHECK_LAUNCH();

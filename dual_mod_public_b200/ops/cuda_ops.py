@@ -52,26 +52,26 @@ class _Sigs:
     dmb_embed_bwd_sorted = [_p, _p, _p, _i, _p, _i, _i, _p]
     dmb_rope = [_p, _i, _ll, _ll, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]
     dmb_refine_fwd = [_p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _f, _p]
-    dmb_refine_bwd = [_p, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
+    dmb_refine_bwd = [_p, _p, _v, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
                       _i, _i, _i, _i, _i, _f, _p]
     dmb_rmsn_bwd = [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p]
     dmb_mrk_vin_fwd = [_p, _p, _p, _p, _p, _v, _p, _i, _i, _i, _i, _f, _f, _p]
     dmb_mrk_vin_bwd = [_p, _p, _p, _p, _p, _v, _p, _p, _v, _p, _i, _i, _i, _i, _f, _f, _p]
     dmb_mrk_refine_fwd = [_p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _f, _f, _p]
-    dmb_mrk_refine_bwd = [_p, _p, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _p, _p, _v, _p, _v,
+    dmb_mrk_refine_bwd = [_p, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _p, _p, _v, _p, _v,
                           _p, _v, _i, _i, _i, _i, _i, _f, _f, _p]
     dmb_swiglu_fwd = [_p, _p, _p, _ll, _p]
     dmb_swiglu_bwd = [_p, _p, _p, _p, _p, _ll, _p]
     dmb_ce = [_p, _p, _p, _p, _p, _i, _i, _p]
     dmb_tail_fwd = [_p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p]
-    dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _p, _v, _p, _v,
-                    _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p]
+    dmb_tail_bwd = [_p, _p, _v, _p, _v, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
+                    _p, _p, _p, _p, _v, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_prefix_fwd = [_p, _v, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
-    dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
+    dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_cell_finish = [_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
-    dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
+    dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
     dmb_attn_dkv_tc = [_p, _p, _p, _p, _i, _p, _p, _v, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p]
     dmb_attn_fwd_tc = [_p, _v, _i, _p, _p, _v, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
@@ -232,7 +232,7 @@ class CudaOps(TorchOps):
         h = ssq.shape[-1]
         dh = d // h
         if not (self._mrk_ok(o, raw, vgx) and o.is_contiguous() and ssq.is_contiguous() and w_ctx.dtype == BF16
-                and vgx.dtype == BF16 and dh % 16 == 0 and h % 4 == 0):
+                and vgx.dtype == BF16 and dh % 16 == 0):
             return super().mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
         vin = torch.empty(B, c, d, dtype=BF16, device=o.device)
         self._ck(self.lib.dmb_mrk_vin_fwd(raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), w_ctx.data_ptr(), vgx.data_ptr(),
@@ -246,7 +246,7 @@ class CudaOps(TorchOps):
         dh = d // h
         ok = (self._mrk_ok(o, raw, vgx, dvgx_acc) and dvin.dtype == BF16 and dvin.is_contiguous() and dcg.is_contiguous()
               and dcg.dtype == BF16 and ssq.is_contiguous() and w_ctx.dtype == BF16 and vgx.dtype == BF16
-              and dvgx_acc.dtype == F32 and dh % 16 == 0 and h % 4 == 0)
+              and dvgx_acc.dtype == F32 and dh % 16 == 0)
         if not ok:
             return super().mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc)
         du_hat = torch.empty(B, c, d, dtype=F32, device=o.device)
@@ -260,7 +260,7 @@ class CudaOps(TorchOps):
         B, c, d = k.shape
         dh = d // h
         ok = (self._mrk_ok(k, raw, glx, v) and vc.dtype == BF16 and vc.is_contiguous() and cos.is_contiguous()
-              and ssq.is_contiguous() and k_gain.dtype == F32 and dh % 16 == 0 and h % 4 == 0)
+              and ssq.is_contiguous() and k_gain.dtype == F32 and dh % 16 == 0)
         if not ok:
             return super().mrk_refine_fwd(raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, out)
         if (out is not None and all(t.dtype == BF16 and _dense_tail(t, 2) for t in out)
@@ -287,15 +287,15 @@ class CudaOps(TorchOps):
         dh = d // h
         ok = (self._mrk_ok(k, raw, glx, v, dk_acc, dv_acc, dglx_acc) and vc.dtype == BF16 and vc.is_contiguous()
               and o.dtype == BF16 and o.is_contiguous() and dK_out.dtype == F32 and dV_out.dtype == F32
-              and dK_out.is_contiguous() and dV_out.is_contiguous() and ssq.is_contiguous()
+              and _dense_tail(dK_out, 2) and dK_out.stride() == dV_out.stride() and ssq.is_contiguous()
               and all(t.is_contiguous() and t.dtype == BF16 for t in (dcg_out, uhat_out, dvc_out))
               and dkg_out.is_contiguous() and dkg_out.dtype == F32 and k_gain.dtype == F32
-              and dh % 16 == 0 and h % 4 == 0)
+              and dh % 16 == 0)
         if not ok:
             return super().mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, pin_cols, k_gain, tau,
                                           dk_acc, dv_acc, dglx_acc, dcg_out, uhat_out, dvc_out, dkg_out)
         self._ck(self.lib.dmb_mrk_refine_bwd(
-            dK_out.data_ptr(), dV_out.data_ptr(), raw.data_ptr(), vc.data_ptr(), ssq.data_ptr(), o.data_ptr(),
+            dK_out.data_ptr(), dV_out.data_ptr(), _tv(dK_out), raw.data_ptr(), vc.data_ptr(), ssq.data_ptr(), o.data_ptr(),
             glx.data_ptr(), _tv(glx), k.data_ptr(), _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
             k_gain.data_ptr(), dcg_out.data_ptr(), uhat_out.data_ptr(), dvc_out.data_ptr(), dkg_out.data_ptr(),
             dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(), _tv(dv_acc), dglx_acc.data_ptr(), _tv(dglx_acc),
@@ -463,35 +463,43 @@ class CudaOps(TorchOps):
         lo = prefix_lo(pos0, window, qoff)
         if pos0 - lo <= 0:
             return
-        ok = (self._cell_ok(q_r) and do_c.dtype == BF16 and dq_acc.is_contiguous() and _dense_tail(q_r, 2)
-              and _dense_tail(do_c, 2) and _dense_tail(Kc, 2))
+        ok = (self._cell_ok(q_r) and do_c.dtype == BF16 and dq_acc.dtype == F32 and _dense_tail(dq_acc, 2)
+              and _dense_tail(q_r, 2) and _dense_tail(do_c, 2) and _dense_tail(Kc, 2))
         if not ok:
             return super().prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff)
         lse_c, corr = lse_c.contiguous(), corr.contiguous()
-        if self.ATTN_TC and c == 64 and self._tc_ok(q_r, Kc, Vc) and self._tc_ok(do_c, Kc, Vc):
+        if (self.ATTN_TC and c == 64 and dq_acc.is_contiguous() and self._tc_ok(q_r, Kc, Vc)
+                and self._tc_ok(do_c, Kc, Vc)):
             return self.attn_dq_tc(q_r, do_c, Kc, Vc, lo, pos0, pos0 + qoff, scale, window, lse_c, corr, dq_acc)
         self._ck(self.lib.dmb_prefix_dq(q_r.data_ptr(), _tv(q_r), do_c.data_ptr(), _tv(do_c), Kc.data_ptr(),
                                         Vc.data_ptr(), _tv(Kc), lse_c.data_ptr(), corr.data_ptr(),
-                                        dq_acc.data_ptr(), B, c, h, dh, lo, pos0, scale, window, 1, 0, qoff, self._st()),
-                 "prefix_dq")
+                                        dq_acc.data_ptr(), _tv(dq_acc), B, c, h, dh, lo, pos0, scale, window, 1, 0, qoff,
+                                        self._st()), "prefix_dq")
 
-    def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
+    def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None,
+                   out=None, accumulate=False):
         B, T, h, dh = q_all.shape
         q_end = T if q_end is None else min(q_end, T)
         ok = (q_all.dtype == BF16 and doc_all.dtype == BF16 and dh in (64, 128) and c in (16, 32, 64)
               and q_all.is_contiguous() and doc_all.is_contiguous() and corr_all.is_contiguous()
-              and lsec_all.is_contiguous() and _dense_tail(Kc, 2))
+              and lsec_all.is_contiguous() and _dense_tail(Kc, 2) and (out is None or self._dkv_view_ok(out)))
         if not ok:
-            return super().prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end)
-        dK = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
-        dV = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
-        if self.ATTN_TC and c == 64 and self._tc_ok(q_all, Kc, Vc):
+            return super().prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end,
+                                      out, accumulate)
+        if out is not None:
+            dK, dV = out
+        else:
+            dK = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
+            dV = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
+            accumulate = False
+        if (self.ATTN_TC and c == 64 and not accumulate and dK.is_contiguous() and dV.is_contiguous()
+                and self._tc_ok(q_all, Kc, Vc)):
             return self.attn_dkv_tc(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, q_start, q_end, scale, window,
                                     out=(dK, dV))
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(),
                                          lsec_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
-                                         dK.data_ptr(), dV.data_ptr(), B, T, c, h, dh, pos0, q_start, q_end, scale,
-                                         window, 1, 0, 1 << 30, self._st()), "prefix_dkv")
+                                         dK.data_ptr(), dV.data_ptr(), _tv(dK), int(accumulate), B, T, c, h, dh, pos0,
+                                         q_start, q_end, scale, window, 1, 0, 1 << 30, self._st()), "prefix_dkv")
         return dK, dV
 
     def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
@@ -510,41 +518,59 @@ class CudaOps(TorchOps):
         return o, lse, ssq
 
     def tail_bwd(self, dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window,
-                 dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
+                 dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, init=0, dkv_out=None):
         ok = (self._cell_ok(q_r) and dO.dtype == F32 and dO.is_contiguous() and o.is_contiguous()
-              and dq_acc.is_contiguous() and doc_acc.is_contiguous() and dlsec_acc.is_contiguous()
-              and all(_dense_tail(t, 2) for t in (q_r, kself_r, v_raw, K_in, V_in, dks_acc, dv_acc)))
+              and doc_acc.is_contiguous() and dlsec_acc.is_contiguous()
+              and all(_dense_tail(t, 2) for t in (q_r, kself_r, v_raw, K_in, V_in, dks_acc, dv_acc, dq_acc))
+              and (dkv_out is None or self._dkv_view_ok(dkv_out)))
         if not ok:
             return super().tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale,
-                                    window, dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc)
+                                    window, dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, init, dkv_out)
         B, c, h, dh = q_r.shape
-        dK_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
-        dV_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+        if dkv_out is not None:
+            dK_in, dV_in = dkv_out
+        else:
+            dK_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+            dV_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
         o_c, lse_c, lse = o_c.contiguous(), lse_c.contiguous(), lse.contiguous()
         self._ck(self.lib.dmb_tail_bwd(
             dO.data_ptr(), q_r.data_ptr(), _tv(q_r), kself_r.data_ptr(), _tv(kself_r), v_raw.data_ptr(),
             _tv(v_raw), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), o_c.data_ptr(),
-            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), dks_acc.data_ptr(),
+            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), _tv(dq_acc), dks_acc.data_ptr(),
             _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc), doc_acc.data_ptr(), dlsec_acc.data_ptr(),
-            dK_in.data_ptr(), dV_in.data_ptr(), B, c, h, dh, scale, window, 1, 0, self._st()), "tail_bwd")
+            dK_in.data_ptr(), dV_in.data_ptr(), _tv(dK_in), B, c, h, dh, scale, window, 1, 0, int(init), self._st()),
+            "tail_bwd")
         return dK_in, dV_in
 
-    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window=0):
+    @staticmethod
+    def _dkv_view_ok(pair):
+        a, b = pair
+        return (a.dtype == F32 and b.dtype == F32 and _dense_tail(a, 2) and a.stride() == b.stride()
+                and a.data_ptr() % 8 == 0 and b.data_ptr() % 8 == 0)
+
+    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window=0,
+                     out=None, accumulate=False):
         B, T, h, dh = q_all.shape
         ok = (q_all.dtype == BF16 and docn_all.dtype == BF16 and dh in (64, 128) and C in (16, 32, 64)
               and q_all.is_contiguous() and docn_all.is_contiguous() and corrn_all.is_contiguous()
-              and lsen_all.is_contiguous() and _dense_tail(Kc, 2))
+              and lsen_all.is_contiguous() and _dense_tail(Kc, 2) and (out is None or self._dkv_view_ok(out)))
         if not ok:
-            return super().win_near_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window)
-        dK = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
-        dV = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
-        if self.ATTN_TC and C == 64 and self._tc_ok(q_all, Kc, Vc):
+            return super().win_near_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale,
+                                        window, out, accumulate)
+        if out is not None:
+            dK, dV = out
+        else:
+            dK = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
+            dV = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
+            accumulate = False
+        if (self.ATTN_TC and C == 64 and not accumulate and dK.is_contiguous() and dV.is_contiguous()
+                and self._tc_ok(q_all, Kc, Vc)):
             return self.attn_dkv_tc(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0 * C, q_lo, min(q_hi, T), scale,
                                     window, G=G, grow=C, span=span, out=(dK, dV))
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), docn_all.data_ptr(), corrn_all.data_ptr(),
                                          lsen_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), dK.data_ptr(),
-                                         dV.data_ptr(), B, T, C, h, dh, j0 * C, q_lo, min(q_hi, T), scale, window,
-                                         G, C, span, self._st()), "win_near_dkv")
+                                         dV.data_ptr(), _tv(dK), int(accumulate), B, T, C, h, dh, j0 * C, q_lo,
+                                         min(q_hi, T), scale, window, G, C, span, self._st()), "win_near_dkv")
         return dK, dV
 
     @staticmethod
@@ -619,18 +645,19 @@ class CudaOps(TorchOps):
         return o_n, lse_n
 
     def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window=0):
-        ok = (self._win_ok(q_win, C, Kc, do_n) and do_n.dtype == BF16 and dq_acc.is_contiguous()
+        ok = (self._win_ok(q_win, C, Kc, do_n) and do_n.dtype == BF16 and dq_acc.dtype == F32 and _dense_tail(dq_acc, 2)
               and lse_n.is_contiguous() and corr_n.is_contiguous())
         if not ok:
             return super().win_near_dq(q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window)
         B, rows, h, dh = q_win.shape
-        if self.ATTN_TC and C == 64 and self._tc_ok(q_win, Kc, Vc) and self._tc_ok(do_n, Kc, Vc):
+        if (self.ATTN_TC and C == 64 and dq_acc.is_contiguous() and self._tc_ok(q_win, Kc, Vc)
+                and self._tc_ok(do_n, Kc, Vc)):
             return self.attn_dq_tc(q_win, do_n, Kc, Vc, lo, pos0, pos0, scale, window, lse_n, corr_n, dq_acc,
                                    G=rows // C, grow=C)
         self._ck(self.lib.dmb_prefix_dq(q_win.data_ptr(), _tv(q_win), do_n.data_ptr(), _tv(do_n), Kc.data_ptr(),
                                         Vc.data_ptr(), _tv(Kc), lse_n.data_ptr(), corr_n.data_ptr(),
-                                        dq_acc.data_ptr(), B, C, h, dh, lo, pos0, scale, window, rows // C, C, 0,
-                                        self._st()), "win_near_dq")
+                                        dq_acc.data_ptr(), _tv(dq_acc), B, C, h, dh, lo, pos0, scale, window, rows // C,
+                                        C, 0, self._st()), "win_near_dq")
 
     def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale, window=0):
         if not self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in) or not (o_c.is_contiguous() and lse_c.is_contiguous()):
@@ -647,28 +674,33 @@ class CudaOps(TorchOps):
         return o, lse, ssq
 
     def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0):
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0, init=0, dkv_out=None):
         ok = (self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in, dks_acc, dv_acc) and dO.dtype == F32
-              and all(t.is_contiguous() for t in (dO, o, o_c, lse_c, lse, dq_acc, doc_acc, dlsec_acc)))
+              and all(t.is_contiguous() for t in (dO, o, o_c, lse_c, lse, doc_acc, dlsec_acc))
+              and _dense_tail(dq_acc, 2) and (dkv_out is None or self._dkv_view_ok(dkv_out)))
         if not ok:
             return super().win_tail_bwd(dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                                        dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window)
+                                        dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window, init, dkv_out)
         B, rows, h, dh = q_win.shape
-        dK_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
-        dV_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
+        if dkv_out is not None:
+            dK_in, dV_in = dkv_out
+        else:
+            dK_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
+            dV_in = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
         self._ck(self.lib.dmb_tail_bwd(
             dO.data_ptr(), q_win.data_ptr(), _tv(q_win), ks_win.data_ptr(), _tv(ks_win), vr_win.data_ptr(),
             _tv(vr_win), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), o_c.data_ptr(),
-            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), dks_acc.data_ptr(),
+            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), _tv(dq_acc), dks_acc.data_ptr(),
             _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc), doc_acc.data_ptr(), dlsec_acc.data_ptr(),
-            dK_in.data_ptr(), dV_in.data_ptr(), B, C, h, dh, scale, window, rows // C, C, self._st()), "win_tail_bwd")
+            dK_in.data_ptr(), dV_in.data_ptr(), _tv(dK_in), B, C, h, dh, scale, window, rows // C, C, int(init),
+            self._st()), "win_tail_bwd")
         return dK_in, dV_in
 
     def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):
         B, c, d = k.shape
         dh = d // h
         ok = (k.dtype == BF16 and raw.dtype == BF16 and raw.is_contiguous() and cos.is_contiguous()
-              and ssq.is_contiguous() and dh % 16 == 0 and h % 4 == 0
+              and ssq.is_contiguous() and dh % 16 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v)))
         if not ok:
             return super().refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols, out)
@@ -694,16 +726,16 @@ class CudaOps(TorchOps):
         h = dK_out.shape[2]
         dh = d // h
         ok = (k.dtype == BF16 and raw.dtype == BF16 and o.dtype == BF16 and dK_out.dtype == F32
-              and dV_out.dtype == F32 and dK_out.is_contiguous() and dV_out.is_contiguous()
+              and dV_out.dtype == F32 and _dense_tail(dK_out, 2) and dK_out.stride() == dV_out.stride()
               and raw.is_contiguous() and o.is_contiguous() and ssq.is_contiguous() and cos.is_contiguous()
               and dcg_out.is_contiguous() and uhat_out.is_contiguous() and dcg_out.dtype == BF16
-              and dh % 16 == 0 and h % 4 == 0
+              and dh % 16 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v, dk_acc, dv_acc, dglx_acc)))
         if not ok:
             return super().refine_bwd(dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc,
                                       dglx_acc, dcg_out, uhat_out)
         self._ck(self.lib.dmb_refine_bwd(
-            dK_out.data_ptr(), dV_out.data_ptr(), raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), glx.data_ptr(),
+            dK_out.data_ptr(), dV_out.data_ptr(), _tv(dK_out), raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), glx.data_ptr(),
             _tv(glx), k.data_ptr(), _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
             dcg_out.data_ptr(), uhat_out.data_ptr(), dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(),
             _tv(dv_acc), dglx_acc.data_ptr(), _tv(dglx_acc), B, c, h, dh, pin_cols, 1e-5, self._st()),
@@ -713,7 +745,7 @@ class CudaOps(TorchOps):
         d = o.shape[-1]
         h = ssq.shape[-1]
         ok = (du.dtype == BF16 and o.dtype == BF16 and du.is_contiguous() and o.is_contiguous()
-              and ssq.is_contiguous() and d % 8 == 0 and h % 4 == 0 and out_dtype in (BF16, F32)
+              and ssq.is_contiguous() and d % 8 == 0 and out_dtype in (BF16, F32)
               and (residual is None or (residual.is_contiguous() and residual.dtype == out_dtype))
               and (extra is None or (extra.is_contiguous() and extra.dtype == F32)))
         if not ok:

@@ -9,6 +9,18 @@ import torch
 from ..engines import fused_math as fm
 
 
+def _into(out, vals, accumulate):
+    """`vals` as they are, or written into (added to, when `accumulate`) the tensors `out` and those returned."""
+    if out is None:
+        return vals
+    for o, v in zip(out, vals):
+        if accumulate:
+            o += v
+        else:
+            o.copy_(v)
+    return tuple(out)
+
+
 class TorchOps:
     name = "torch"
     launches = 0                      # custom-kernel launch counter (0 here by construction)
@@ -83,8 +95,11 @@ class TorchOps:
     def prefix_dq(self, q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff=0):
         fm.prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff)
 
-    def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None):
-        return fm.prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end)
+    def prefix_dkv(self, q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window=0, q_end=None,
+                   out=None, accumulate=False):
+        """`out`: optional (dK, dV) fp32 views [B, c, h, dh] to write into, or to add to when `accumulate`."""
+        dK, dV = fm.prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end)
+        return _into(out, (dK, dV), accumulate)
 
     # ---- window ops: G consecutive chunks of C rows of the same sequences (statement: a loop over the
     # chunks; the kernel table does each in one launch).  Window tensors are [B, G*C, ...]; group z reads
@@ -111,26 +126,28 @@ class TorchOps:
         return tuple(torch.cat([t[i] for t in outs], 1) for i in range(3))
 
     def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0):
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0, init=0, dkv_out=None):
         dKs, dVs = [], []
         for z in range(q_win.shape[1] // C):
             r = slice(z * C, (z + 1) * C)
             dk, dv = self.tail_bwd(dO[:, r], q_win[:, r], ks_win[:, r], vr_win[:, r], K_in[:, r], V_in[:, r],
                                    o_c[:, r], lse_c[:, r], o[:, r], lse[:, r], scale, window, dq_acc[:, r],
-                                   dks_acc[:, r], dv_acc[:, r], doc_acc[:, r], dlsec_acc[:, r])
+                                   dks_acc[:, r], dv_acc[:, r], doc_acc[:, r], dlsec_acc[:, r], init=init)
             dKs.append(dk)
             dVs.append(dv)
-        return torch.cat(dKs, 1), torch.cat(dVs, 1)
+        return _into(dkv_out, (torch.cat(dKs, 1), torch.cat(dVs, 1)), False)
 
-    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window=0):
+    def win_near_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale, window=0,
+                     out=None, accumulate=False):
         """Key side of the near reads of one step for the G key chunks j0 .. j0+G-1: chunk j is read by the
-        query rows [max(q_lo, (j+1)C), min(q_hi, jC + span)).  Returns dense (dK, dV) [B, G*C, h, dh]."""
+        query rows [max(q_lo, (j+1)C), min(q_hi, jC + span)).  Returns (dK, dV) [B, G*C, h, dh]: dense, or the
+        views `out` written (added to when `accumulate`)."""
         outs = []
         for z in range(G):
             p0 = (j0 + z) * C
-            outs.append(self.prefix_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, p0, C, max(q_lo, p0 + C), scale,
-                                        window, q_end=min(q_hi, p0 + span)))
-        return torch.cat([a for a, _ in outs], 1), torch.cat([b for _, b in outs], 1)
+            outs.append(TorchOps.prefix_dkv(self, q_all, docn_all, corrn_all, lsen_all, Kc, Vc, p0, C, max(q_lo, p0 + C),
+                                            scale, window, q_end=min(q_hi, p0 + span)))
+        return _into(out, (torch.cat([a for a, _ in outs], 1), torch.cat([b for _, b in outs], 1)), accumulate)
 
     def cell_finish(self, do_c, dlse_c, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv):
         """End of a cell's backward: doc = d o_c, corr = d o_c . o_c - d lse_c, lsec = lse_c at the cell's rows
@@ -167,17 +184,26 @@ class TorchOps:
         return fm.tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window)
 
     def tail_bwd(self, dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window,
-                 dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc):
-        """Accumulates (+=) into the fp32 buffers dq_acc / dks_acc / dv_acc [B,c,h,dh],
-        doc_acc [B,c,h,dh], dlsec_acc [B,c,h]; returns fp32 (dK_in, dV_in)."""
+                 dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, init=0, dkv_out=None):
+        """Accumulates (+=) into the fp32 buffers dq_acc / dks_acc / dv_acc [B,c,h,dh] (views allowed),
+        doc_acc [B,c,h,dh], dlsec_acc [B,c,h]; returns fp32 (dK_in, dV_in), written into the views `dkv_out`
+        when given.  `init`: bit 0 = dq_acc is overwritten instead of added to, bit 1 = the same for doc_acc and
+        dlsec_acc (the first sweep processed of a cell initialises the cell's accumulators)."""
         dq, dks, dvr, dK_in, dV_in, doc, dlse = fm.tail_bwd(
             dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, window)
-        dq_acc += dq
+        if init & 1:
+            dq_acc.copy_(dq)
+        else:
+            dq_acc += dq
         dks_acc += dks
         dv_acc += dvr
-        doc_acc += doc
-        dlsec_acc += dlse
-        return dK_in, dV_in
+        if init & 2:
+            doc_acc.copy_(doc)
+            dlsec_acc.copy_(dlse)
+        else:
+            doc_acc += doc
+            dlsec_acc += dlse
+        return _into(dkv_out, (dK_in, dV_in), False)
 
     def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):
         """`out`: optional (K, V) [B,c,h,dh] views to write into (e.g. the cell's rows of the tape)."""

@@ -303,10 +303,13 @@ def test_cell_finish(ops, dh):
         close(x, y, rtol=1e-2, atol=1e-4, what=n_)
 
 
-@pytest.mark.parametrize("dh,pin,tau", [(64, 64, 0.8), (128, 0, 0.0), (64, 0, 50.0)])
-def test_mult_res_write_law_kernels(ops, dh, pin, tau):
-    """The four pointwise kernels of the mult_res family against their fp32 torch statement."""
-    B, c, H = 2, 64, 4
+@pytest.mark.parametrize("dh,pin,tau,H", [(64, 64, 0.8, 4), (128, 0, 0.0, 4), (64, 0, 50.0, 4), (64, 64, 0.8, 3),
+                                          (64, 64, 150.0, 15)])
+def test_mult_res_write_law_kernels(ops, dh, pin, tau, H):
+    """The four pointwise kernels of the mult_res family against their fp32 torch statement; head counts
+    that are not a multiple of four included (15 heads of 64: the reference's own 340M run)."""
+    B, c = 2, 64
+    n0 = ops.launches
     d = H * dh
     T = 128
     r = slice(32, 32 + c)
@@ -340,6 +343,7 @@ def test_mult_res_write_law_kernels(ops, dh, pin, tau):
     ref = run(REF, f, torch.float32)
     for a, b_, n_ in zip(got, ref, ("dk", "dv", "dglx", "dcg", "uhat", "dvc", "dkg", "dvgx", "du_hat")):
         close(a, b_, rtol=3e-2, atol=3e-2, what=n_)
+    assert ops.launches - n0 >= 4, "the write-law kernels did not run (fell back to the torch statement)"
     # column dot and the norm backward with the extra term
     a_, b2 = rnd(4096, d, seed=12), rnd(4096, d, seed=13)
     out1, out2 = z(d), z(d)
