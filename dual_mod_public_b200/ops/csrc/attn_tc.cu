@@ -6,11 +6,14 @@
 //   warp 0      TMA producer: Q once, then K / V tiles into a two-stage ring (128-byte swizzle)
 //   warp 1      one thread issues  S = Q K^T  (tcgen05.mma, M = BM, N = 128, fp32 in TMEM) and
 //               O_t = P V  (M = BM, N = DH) per key tile; the accumulators live in tensor memory
-//   warps 2..5  softmax: every thread owns one query row (its TMEM lane).  It reads S with
-//               tcgen05.ld, masks, keeps the running maximum and sum in the log2 domain, writes
+//   warps 2..5  softmax.  BM = 128: every thread owns one query row (its TMEM lane).  BM = 64: the
+//               accumulator's 64 rows sit in lanes 0..15 of each 32-lane quarter; they are read with the
+//               16-lane x 256-bit shape of tcgen05.ld, which gives every thread of the warp a warp-MMA
+//               accumulator fragment (two rows, column pairs), so all 32 lanes work.  Either way the
+//               threads mask, keep the running maximum and sum in the log2 domain, write
 //               P = exp2(S - m) as bf16 into shared memory in the operand layout of the second
-//               product, and folds the product of the previous tile (read back from TMEM, two buffers)
-//               into its fp32 output row with the usual rescale.
+//               product (BM = 64: with stmatrix), and fold the product of the previous tile (read back
+//               from TMEM, two buffers) into their fp32 output rows with the usual rescale.
 //
 // S of tile t+1 is issued as soon as the softmax warps have read S of tile t, so the tensor pipe works
 // on the next scores and the previous P V while the exponentials run; at head dimension 64 two CTAs fit
@@ -47,7 +50,7 @@ struct Cfg {
 };
 
 struct Geo {
-  int H, Lq, lo, hi, qbase, grow, window, causal, causal_excl, tiles_q, lane_mode, o_bf16;
+  int H, Lq, lo, hi, qbase, grow, window, causal, causal_excl, tiles_q, o_bf16;
   float scale_log2;
 };
 
@@ -191,21 +194,144 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
   } else {
     // ---------------- softmax / output: one query row per thread ----------------
     const int q = warp & 3;                                  // the TMEM lane quarter this warp may read
-    // row of the tile held by this thread's TMEM lane.  M = 128: lane l of the accumulator is row l.
-    // M = 64: lane_mode 0: rows 16q..16q+15 sit in lanes 32q..32q+15; lane_mode 1: row r sits in lane r.
-    int row;
-    bool has_row;
-    if (BM == 128) {
-      row = q * 32 + lane;
-      has_row = true;
-    } else if (g.lane_mode == 0) {
-      row = q * 16 + lane;
-      has_row = lane < 16;
-    } else {
-      row = q * 32 + lane;
-      has_row = q < 2;
-    }
     const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+    if constexpr (BM == 64) {
+      // M = 64: the accumulator's rows 16q .. 16q+15 sit in lanes 0..15 of quarter q.  They are read with the
+      // 16-lane x 256-bit shape, which hands every thread of the warp the accumulator fragment of a warp-level
+      // MMA: thread t owns rows rA = 16q + t/4 and rB = rA + 8, columns 8j + 2(t%4), +1 of every 8-column
+      // group j.  All 32 lanes work; row maxima are reduced over the 4 threads of a quad, the running sum
+      // stays a per-thread partial until the end, and P goes to shared memory with stmatrix (the fragment is
+      // its register layout; one 16-byte row per 8-column group, at its swizzled place).
+      const int t4 = lane & 3, rA = q * 16 + (lane >> 2), rB = rA + 8;
+      int jloA = lo_z, jhiA = hi_z, jloB = lo_z, jhiB = hi_z;
+      if (g.window) { jloA = max(jloA, qpos0 + rA - g.window + 1); jloB = max(jloB, qpos0 + rB - g.window + 1); }
+      if (g.causal) { jhiA = min(jhiA, qpos0 + rA - g.causal_excl + 1); jhiB = min(jhiB, qpos0 + rB - g.causal_excl + 1); }
+      float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f, aprevA = 1.f, aprevB = 1.f;
+      float OA[DH / 4], OB[DH / 4];                          // this thread's pairs of both rows
+#pragma unroll
+      for (int i = 0; i < DH / 4; ++i) OA[i] = OB[i] = 0.f;
+      // stmatrix row address of this thread: matrix lane/8 of each x4 store, row lane%8
+      const int smat = lane >> 3, srow = q * 16 + (smat & 1) * 8 + (lane & 7);
+      bool alive = n_tiles > 0;
+      auto wwait = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, serr)); };
+      auto fold = [&](int u, float alA, float alB) {         // O = O * alpha + (P V) of tile u
+        const int s = u & 1;
+        if (!wwait(pvfull(s), (u >> 1) & 1)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < DH; c0 += 64) {
+          uint32_t r[32];
+          tmem_ld_16x256b_x8(tlane + KT + s * DH + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int o = (c0 >> 2) + 2 * j;
+            OA[o] = OA[o] * alA + __uint_as_float(r[4 * j]);
+            OA[o + 1] = OA[o + 1] * alA + __uint_as_float(r[4 * j + 1]);
+            OB[o] = OB[o] * alB + __uint_as_float(r[4 * j + 2]);
+            OB[o + 1] = OB[o + 1] * alB + __uint_as_float(r[4 * j + 3]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pvfree(s));
+        return true;
+      };
+      for (int t = 0; t < n_tiles && alive; ++t) {
+        const int k0 = k_begin + t * KT;
+        if (!wwait(sfull, t & 1)) { alive = false; break; }
+        tc_fence_after();
+        const bool mask = (k0 + KT > k_end) || (g.causal && k0 + KT - 1 > qpos0 - g.causal_excl) ||
+                          (g.window && k0 < qpos0 + rows_here - 1 - g.window + 1);
+        uint32_t r[64];
+        tmem_ld_16x256b_x16(tlane, r);
+        tmem_ld_wait();
+        // S is in registers: the next tile's scores may be issued
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sfree);
+        float mxA = -INFINITY, mxB = -INFINITY;
+        if (mask) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int kj = k0 + 8 * j + 2 * t4 + e;
+              if (!(kj >= jloA && kj < jhiA)) r[4 * j + e] = 0xff800000u;          // -inf
+              if (!(kj >= jloB && kj < jhiB)) r[4 * j + 2 + e] = 0xff800000u;
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          mxA = fmaxf(mxA, fmaxf(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1])));
+          mxB = fmaxf(mxB, fmaxf(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+        }
+        mxA = quad_max(mxA);
+        mxB = quad_max(mxB);
+        const float mnA = fmaxf(mA, mxA * g.scale_log2), mnB = fmaxf(mB, mxB * g.scale_log2);
+        const float subA = mnA == -INFINITY ? 0.f : mnA, subB = mnB == -INFINITY ? 0.f : mnB;
+        const float alA = exp2f(mA - subA), alB = exp2f(mB - subB);
+        mA = mnA;
+        mB = mnB;
+        // P of tile t-1 must have been read by its product before P of tile t overwrites it
+        if (t >= 1 && !fold(t - 1, aprevA, aprevB)) { alive = false; break; }
+        float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {                         // 16 keys per stmatrix.x4
+          uint32_t pk[4];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int j = 2 * n + u;
+            const float a0 = exp2f(fmaf(__uint_as_float(r[4 * j]), g.scale_log2, -subA));      // exp2(-inf) = 0
+            const float a1 = exp2f(fmaf(__uint_as_float(r[4 * j + 1]), g.scale_log2, -subA));
+            const float b0 = exp2f(fmaf(__uint_as_float(r[4 * j + 2]), g.scale_log2, -subB));
+            const float b1 = exp2f(fmaf(__uint_as_float(r[4 * j + 3]), g.scale_log2, -subB));
+            sumA += a0 + a1;
+            sumB += b0 + b1;
+            pk[2 * u] = pack_bf16(a0, a1);                   // matrix 2u: rows rA.., key group j
+            pk[2 * u + 1] = pack_bf16(b0, b1);               // matrix 2u+1: rows rB.., key group j
+          }
+          const int jg = 2 * n + (smat >> 1);                 // the 8-key group whose row this thread addresses
+          stsm_x4(sP + (jg >> 3) * (BM * 128) + srow * 128 + (((jg & 7) ^ (srow & 7)) << 4), pk[0], pk[1], pk[2], pk[3]);
+        }
+        lA = lA * alA + sumA;
+        lB = lB * alB + sumB;
+        aprevA = alA;
+        aprevB = alB;
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pfull);
+      }
+      if (alive && n_tiles > 0) alive = fold(n_tiles - 1, aprevA, aprevB);
+      lA = quad_sum(lA);
+      lB = quad_sum(lB);
+      if (alive || n_tiles == 0) {
+        const int G_ = (int)(gridDim.z / g.tiles_q);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int row = half ? rB : rA;
+          if (row >= rows_here) continue;
+          const float l = half ? lB : lA, m = half ? mB : mA;
+          const float* O = half ? OB : OA;
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          const long long orow = ((long long)((b * G_ + z) * g.Lq + row0 + row) * g.H + h);
+#pragma unroll
+          for (int j = 0; j < DH / 8; ++j) {
+            const int d = 8 * j + 2 * t4;
+            if (g.o_bf16)
+              *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(o_out) + orow * DH + d) =
+                  pack_bf16(O[2 * j] * inv, O[2 * j + 1] * inv);
+            else
+              *reinterpret_cast<float2*>(reinterpret_cast<float*>(o_out) + orow * DH + d) =
+                  make_float2(O[2 * j] * inv, O[2 * j + 1] * inv);
+          }
+          if (t4 == 0) lse_out[orow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : DMB_NEG;
+        }
+      }
+    } else {
+    const int row = q * 32 + lane;
+    const bool has_row = true;
     const int qpos = qpos0 + row;
     int jlo = lo_z, jhi = hi_z;                              // allowed keys of this row: jlo <= j < jhi
     if (g.window) jlo = max(jlo, qpos - g.window + 1);
@@ -216,9 +342,10 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
     for (int d = 0; d < DH; ++d) O[d] = 0.f;
     uint8_t* pP = base_ptr + C::p_off;
     bool alive = n_tiles > 0;
+    auto wwait = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, serr)); };
     auto fold = [&](int u, float alpha) {                    // O = O * alpha + (P V) of tile u
       const int s = u & 1;
-      if (!mbar_wait(pvfull(s), (u >> 1) & 1, serr)) return false;
+      if (!wwait(pvfull(s), (u >> 1) & 1)) return false;
       tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < DH; c0 += 64) {
@@ -236,7 +363,7 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
     };
     for (int t = 0; t < n_tiles && alive; ++t) {
       const int k0 = k_begin + t * KT;
-      if (!mbar_wait(sfull, t & 1, serr)) { alive = false; break; }
+      if (!wwait(sfull, t & 1)) { alive = false; break; }
       tc_fence_after();
       // a tile needs per-element masks only where it crosses a row's range
       const bool mask = (k0 + KT > k_end) || (k0 < lo_z) || (g.causal && k0 + KT - 1 > qpos0 - g.causal_excl) ||
@@ -330,6 +457,7 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
       }
       lse_out[orow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : DMB_NEG;
     }
+    }   // BM == 128
   }
   tc_fence_before();
   __syncthreads();
@@ -378,18 +506,17 @@ extern "C" {
 //   o, lse       dense [B, G, Lq, H, DH] (fp32, or bf16 when o_bf16) and [B, G, Lq, H] fp32
 //   keys of group z: max(0, lo + z*grow) <= j < hi + z*grow; query row i sits at qbase + z*grow + i;
 //   causal: j <= position - causal_excl; window > 0: j > position - window
-//   bm: 64 or 128 query rows per CTA.  lane_mode: how the M = 64 accumulator maps to TMEM lanes (0: 16 rows
-//   per 32-lane quarter).  gerr: device int, set to 1 if a pipeline wait ran out.
+//   bm: 64 or 128 query rows per CTA.  gerr: device int, set to 1 if a pipeline wait ran out.
 // Requirements: 16-byte aligned pointers, strides multiples of 8 elements, dh 64 or 128.
 int dmb_attn_fwd_tc(const void* q, TView vq, int q_rows, const void* Kc, const void* Vc, TView vc, int tape_rows,
                     void* o, int o_bf16, float* lse, int B, int G, int Lq, int H, int dh, int lo, int hi, int qbase,
-                    int grow, float scale, int window, int causal, int causal_excl, int bm, int lane_mode, int* gerr,
+                    int grow, float scale, int window, int causal, int causal_excl, int bm, int* gerr,
                     cudaStream_t st) {
   if (!encode_fn()) return -10;
   if ((dh != 64 && dh != 128) || (bm != 64 && bm != 128) || Lq <= 0 || B <= 0 || G <= 0) return -1;
   Geo g;
   g.H = H; g.Lq = Lq; g.lo = lo; g.hi = hi; g.qbase = qbase; g.grow = grow; g.window = window;
-  g.causal = causal; g.causal_excl = causal_excl; g.tiles_q = (Lq + bm - 1) / bm; g.lane_mode = lane_mode;
+  g.causal = causal; g.causal_excl = causal_excl; g.tiles_q = (Lq + bm - 1) / bm;
   g.o_bf16 = o_bf16; g.scale_log2 = scale * 1.4426950408889634f;
   if (dh == 64) {
     if (bm == 64) return launch<64, 64>(q, vq, q_rows, Kc, Vc, vc, tape_rows, o, lse, B, G, g, gerr, st);
@@ -415,8 +542,8 @@ int dmb_attn_fwd_tc(const void* q, TView vq, int q_rows, const void* Kc, const v
 // corr = d o . o - d lse of the read.  The streamed tile serves twice from one shared-memory copy: K-major
 // as the B operand of the score products and, through a descriptor that walks its rows, as the
 // row-major B operand of the gradient products.  M = 64 products: the accumulator's 64 rows sit in lanes
-// 0..15 of each 32-lane quarter, so lanes 16..31 of the four math warps only take part in the collective
-// tensor-memory loads.  Tensor memory: S 64 | dP 64 | accumulators: 256 columns at head dim 64 (two CTAs
+// 0..15 of each 32-lane quarter and are read as warp-MMA fragments (16-lane x 256-bit tcgen05.ld), dS and
+// P go back to shared memory with stmatrix.  Tensor memory: S 64 | dP 64 | accumulators: 256 columns at head dim 64 (two CTAs
 // per SM), 512 at head dim 128 on the key side.
 namespace {
 
@@ -585,22 +712,24 @@ __global__ void __launch_bounds__(NTHREADS, (BCfg<DH, KEYSIDE>::TMEM_COLS == 256
       }
     }
   } else {
-    // ---------------- gradient math: one owner row per thread ----------------
-    const int q = warp & 3;
-    const int row = q * 16 + lane;
-    const bool has_row = lane < 16;
+    // ---------------- gradient math ----------------
+    // The M = 64 accumulators are read as warp-MMA fragments (16-lane x 256-bit loads): thread t of the warp
+    // of quarter q owns the owner rows rA = 16q + t/4 and rB = rA + 8 and the streamed columns 8j + 2(t%4), +1.
+    const int q = warp & 3, t4 = lane & 3, rA = q * 16 + (lane >> 2), rB = rA + 8;
     const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int rpos = own_pos + row;                          // absolute position of this owner row
-    // dense per-row arrays of the query side: [B, G, C, H]
-    const long long orow = ((long long)((b * G + z) * g.C + row) * g.H + h);
-    float L2r = 0.f, cr = 0.f;
-    if (!KEYSIDE && has_row) {
-      L2r = lse[orow] * 1.4426950408889634f;
-      cr = corr[orow];
+    auto wwait = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, serr)); };
+    // dense per-row arrays: [B, G, C, H]
+    const long long orowA = ((long long)((b * G + z) * g.C + rA) * g.H + h), orowB = orowA + 8ll * g.H;
+    float L2A = 0.f, L2B = 0.f, cA = 0.f, cB = 0.f;
+    if (!KEYSIDE) {
+      L2A = lse[orowA] * 1.4426950408889634f;
+      L2B = lse[orowB] * 1.4426950408889634f;
+      cA = corr[orowA];
+      cB = corr[orowB];
     }
     // every math warp stages its own copy of the per-column scalars, so no barrier spans the warps
     float* sc = reinterpret_cast<float*>(base_ptr + C::sc_off) + q * 256;
-    uint8_t* pdS = base_ptr + C::ds_off;
+    const int smat = lane >> 3, srow = q * 16 + (smat & 1) * 8 + (lane & 7);   // stmatrix row this thread addresses
     bool alive = n_tiles > 0;
     for (int t = 0; t < n_tiles && alive; ++t) {
       const int c0pos = s_begin + t * BT;                    // position / tape row of streamed column 0
@@ -621,86 +750,91 @@ __global__ void __launch_bounds__(NTHREADS, (BCfg<DH, KEYSIDE>::TMEM_COLS == 256
         }
         __syncwarp();
       }
-      if (!mbar_wait(sdfull, t & 1, serr)) { alive = false; break; }
+      if (!wwait(sdfull, t & 1)) { alive = false; break; }
       tc_fence_after();
-      uint32_t rs[64], rd[64];
-      tmem_ld32(tlane, *reinterpret_cast<uint32_t (*)[32]>(&rs[0]));
-      tmem_ld32(tlane + 32, *reinterpret_cast<uint32_t (*)[32]>(&rs[32]));
-      tmem_ld32(tlane + 64, *reinterpret_cast<uint32_t (*)[32]>(&rd[0]));
-      tmem_ld32(tlane + 96, *reinterpret_cast<uint32_t (*)[32]>(&rd[32]));
+      uint32_t rs[32], rd[32];
+      tmem_ld_16x256b_x8(tlane, rs);
+      tmem_ld_16x256b_x8(tlane + 64, rd);
       tmem_ld_wait();
       // S and dP are in registers: the next tile's score products may overwrite them
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(sdfree);
       const bool mask = (c0pos + BT > s_end) || g.window != 0;
-      uint32_t pds[32], pp[32];
       const float* scL = sc + (t & 1) * 128;
+      uint32_t pds[16], pp[16];                              // [8-column group j][row A, row B]
 #pragma unroll
-      for (int e = 0; e < 64; e += 2) {
-        float v[2], w[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const float L2 = KEYSIDE ? scL[e + u] : L2r, cc = KEYSIDE ? scL[64 + e + u] : cr;
-          float p = exp2f(fmaf(__uint_as_float(rs[e + u]), g.scale_log2, -L2));
-          if (mask) {
-            const int cpos = c0pos + e + u;
-            const int key = KEYSIDE ? rpos : cpos, qp = KEYSIDE ? cpos : rpos;
-            if (cpos >= s_end || (g.window && key <= qp - g.window)) p = 0.f;
-          }
-          v[u] = p;
-          w[u] = p * (__uint_as_float(rd[e + u]) - cc) * g.scale;
+      for (int j = 0; j < 8; ++j) {
+        const int c = 8 * j + 2 * t4;
+        float2 L2c = make_float2(0.f, 0.f), ccc = make_float2(0.f, 0.f);
+        if (KEYSIDE) {
+          L2c = *reinterpret_cast<const float2*>(scL + c);
+          ccc = *reinterpret_cast<const float2*>(scL + 64 + c);
         }
-        pds[e >> 1] = pack_bf16(w[0], w[1]);
-        if (KEYSIDE) pp[e >> 1] = pack_bf16(v[0], v[1]);
+        float p[4], w[4];                                    // (A, c), (A, c+1), (B, c), (B, c+1)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = e & 1, rowB = e >> 1;
+          const float L2 = KEYSIDE ? (col ? L2c.y : L2c.x) : (rowB ? L2B : L2A);
+          const float cc = KEYSIDE ? (col ? ccc.y : ccc.x) : (rowB ? cB : cA);
+          float pe = exp2f(fmaf(__uint_as_float(rs[4 * j + e]), g.scale_log2, -L2));
+          if (mask) {
+            const int cpos = c0pos + c + col, rp = own_pos + (rowB ? rB : rA);
+            const int key = KEYSIDE ? rp : cpos, qp = KEYSIDE ? cpos : rp;
+            if (cpos >= s_end || (g.window && key <= qp - g.window)) pe = 0.f;
+          }
+          p[e] = pe;
+          w[e] = pe * (__uint_as_float(rd[4 * j + e]) - cc) * g.scale;
+        }
+        pds[2 * j] = pack_bf16(w[0], w[1]);
+        pds[2 * j + 1] = pack_bf16(w[2], w[3]);
+        if (KEYSIDE) {
+          pp[2 * j] = pack_bf16(p[0], p[1]);
+          pp[2 * j + 1] = pack_bf16(p[2], p[3]);
+        }
       }
       // the gradient products of the previous tile must have read dS (and P) before they are overwritten
-      if (t > 0 && !mbar_wait(dsfree, (t - 1) & 1, serr)) { alive = false; break; }
-      if (has_row) {
-        uint8_t* rowp = pdS + row * 128;
+      if (t > 0 && !wwait(dsfree, (t - 1) & 1)) { alive = false; break; }
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          *reinterpret_cast<uint4*>(rowp + ((c ^ (row & 7)) << 4)) =
-              make_uint4(pds[4 * c], pds[4 * c + 1], pds[4 * c + 2], pds[4 * c + 3]);
-          if (KEYSIDE)
-            *reinterpret_cast<uint4*>(rowp + BT * 128 + ((c ^ (row & 7)) << 4)) =
-                make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
-        }
+      for (int n = 0; n < 4; ++n) {                           // 16 streamed columns per stmatrix.x4
+        const int jg = 2 * n + (smat >> 1);
+        const uint32_t a = sdS + srow * 128 + (((jg & 7) ^ (srow & 7)) << 4);
+        stsm_x4(a, pds[4 * n], pds[4 * n + 1], pds[4 * n + 2], pds[4 * n + 3]);
+        if (KEYSIDE) stsm_x4(a + BT * 128, pp[4 * n], pp[4 * n + 1], pp[4 * n + 2], pp[4 * n + 3]);
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(dsfull);
     }
     // ---- the accumulated gradients ----
-    if (alive && n_tiles > 0) alive = mbar_wait(accdone, 0, serr);
+    if (alive && n_tiles > 0) alive = wwait(accdone, 0);
     if (alive || n_tiles == 0) {
       if (n_tiles > 0) tc_fence_after();
-      const long long drow = orow * DH;                      // dense [B, G, C, H, DH] for both sides
 #pragma unroll 1
       for (int a = 0; a < (KEYSIDE ? 2 : 1); ++a) {
-        float* dst = (a == 0 ? out1 : out2) + drow;
+        float* dstA = (a == 0 ? out1 : out2) + orowA * DH;
+        float* dstB = (a == 0 ? out1 : out2) + orowB * DH;
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 64) {
-          uint32_t r[64];
+          uint32_t r[32];
           if (n_tiles > 0) {
-            tmem_ld32(tlane + 128 + a * DH + c0, *reinterpret_cast<uint32_t (*)[32]>(&r[0]));
-            tmem_ld32(tlane + 128 + a * DH + c0 + 32, *reinterpret_cast<uint32_t (*)[32]>(&r[32]));
+            tmem_ld_16x256b_x8(tlane + 128 + a * DH + c0, r);
             tmem_ld_wait();
           } else {
 #pragma unroll
-            for (int e = 0; e < 64; ++e) r[e] = 0u;
+            for (int e = 0; e < 32; ++e) r[e] = 0u;
           }
-          if (has_row) {
 #pragma unroll
-            for (int e = 0; e < 64; e += 4) {
-              float4 v = make_float4(__uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
-                                     __uint_as_float(r[e + 3]));
-              if (g.accumulate) {
-                const float4 o = *reinterpret_cast<const float4*>(dst + c0 + e);
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              *reinterpret_cast<float4*>(dst + c0 + e) = v;
+          for (int j = 0; j < 8; ++j) {
+            const int d = c0 + 8 * j + 2 * t4;
+            float2 vA = make_float2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]));
+            float2 vB = make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            if (g.accumulate) {
+              const float2 oA = *reinterpret_cast<const float2*>(dstA + d), oB = *reinterpret_cast<const float2*>(dstB + d);
+              vA.x += oA.x; vA.y += oA.y; vB.x += oB.x; vB.y += oB.y;
             }
+            *reinterpret_cast<float2*>(dstA + d) = vA;
+            *reinterpret_cast<float2*>(dstB + d) = vB;
           }
         }
       }

@@ -75,7 +75,7 @@ class _Sigs:
     dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
     dmb_attn_dkv_tc = [_p, _p, _p, _p, _i, _p, _p, _v, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p]
     dmb_attn_fwd_tc = [_p, _v, _i, _p, _p, _v, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
-                       _i, _i, _p, _p]
+                       _i, _p, _p]
 
 
 BF16 = torch.bfloat16
@@ -384,9 +384,6 @@ class CudaOps(TorchOps):
             return out
         return o_c, lse_c
 
-    # lane layout of the M = 64 accumulator in tensor memory (0: sixteen rows per 32-lane quarter)
-    TC_LANE_MODE = int(os.environ.get("DMB_TC_LANE_MODE", "0"))
-
     # DMB_ATTN_TC=1 sends the 64-row reads of the committed tape (a cell's prefix read, the wavefront's far and
     # near reads and their backward) through the tcgen05 kernels of csrc/attn_tc.cu.  Default off: at 64 query rows
     # per (batch, head) an M = 64 accumulator fills only 16 of a math warp's 32 lanes, and measured at the 340M
@@ -396,7 +393,7 @@ class CudaOps(TorchOps):
     ATTN_TC = os.environ.get("DMB_ATTN_TC", "0") == "1"
 
     def attn_fwd_tc(self, q, Kc, Vc, lo, hi, qbase, scale, window=0, causal=False, causal_excl=1, Lq=None, G=1,
-                    grow=0, bm=None, out_dtype=F32, lane_mode=None, out=None):
+                    grow=0, bm=None, out_dtype=F32, out=None):
         """Attention forward on tcgen05 (csrc/attn_tc.cu).  q: [B, rows, h, dh] bf16 view; group z (of G) takes
         its rows [z*grow, z*grow + Lq), sits at positions qbase + z*grow + i and reads the tape rows
         max(0, lo + z*grow) <= j < hi + z*grow of Kc / Vc [B, T, h, dh], under the causal rule
@@ -414,8 +411,7 @@ class CudaOps(TorchOps):
         self._ck(self.lib.dmb_attn_fwd_tc(
             q.data_ptr(), _tv(q), rows, Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), Kc.shape[1], o.data_ptr(),
             int(out_dtype == BF16), lse.data_ptr(), B, G, Lq, h, dh, lo, hi, qbase, grow, scale, window,
-            int(causal), causal_excl, bm, self.TC_LANE_MODE if lane_mode is None else lane_mode,
-            self._tc_err.data_ptr(), self._st()), "attn_fwd_tc")
+            int(causal), causal_excl, bm, self._tc_err.data_ptr(), self._st()), "attn_fwd_tc")
         return o, lse
 
     def attn_dq_tc(self, q, do_c, Kc, Vc, lo, hi, qbase, scale, window, lse, corr, dq, G=1, grow=0, accumulate=True):
