@@ -564,6 +564,7 @@ struct BCfg {
 
 struct BGeo {
   int H, T, C, lo, hi, qbase, grow, window, span, accumulate, q_start, q_end;
+  long long o_bs, o_rs;          // output view: element (b, row, col) at b * o_bs + row * o_rs + col; group z at rows z * 64
   float scale, scale_log2;
 };
 
@@ -812,8 +813,8 @@ __global__ void __launch_bounds__(NTHREADS, (BCfg<DH, KEYSIDE>::TMEM_COLS == 256
       if (n_tiles > 0) tc_fence_after();
 #pragma unroll 1
       for (int a = 0; a < (KEYSIDE ? 2 : 1); ++a) {
-        float* dstA = (a == 0 ? out1 : out2) + orowA * DH;
-        float* dstB = (a == 0 ? out1 : out2) + orowB * DH;
+        float* dstA = (a == 0 ? out1 : out2) + b * g.o_bs + (long long)(z * BT + rA) * g.o_rs + (long long)h * DH;
+        float* dstB = dstA + 8 * g.o_rs;
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 64) {
           uint32_t r[32];
@@ -872,15 +873,16 @@ extern "C" {
 
 // Query side of the read's backward.  q, do_c: bf16 views [B, rows, H, DH] (group z: rows [z*grow, z*grow + 64));
 // keys of group z: tape rows max(0, lo + z*grow) <= j < hi + z*grow; query row i sits at qbase + z*grow + i;
-// lse, corr: dense [B, G, 64, H] fp32; dq: dense [B, G, 64, H, DH] fp32, added to when accumulate != 0.
+// lse, corr: dense [B, G, 64, H] fp32; dq: fp32 view [B, G*64, H, DH] with strides vdq, added to when accumulate != 0.
 int dmb_attn_dq_tc(const void* q, TView vq, const void* do_c, TView vdo, int q_rows, const void* Kc, const void* Vc,
-                   TView vc, int tape_rows, const float* lse, const float* corr, float* dq, int B, int G, int H, int dh,
-                   int lo, int hi, int qbase, int grow, float scale, int window, int accumulate, int* gerr,
+                   TView vc, int tape_rows, const float* lse, const float* corr, float* dq, TView vdq, int B, int G, int H,
+                   int dh, int lo, int hi, int qbase, int grow, float scale, int window, int accumulate, int* gerr,
                    cudaStream_t st) {
   if (!encode_fn()) return -10;
   if ((dh != 64 && dh != 128) || B <= 0 || G <= 0) return -1;
   BGeo g = {};
   g.H = H; g.C = BT; g.lo = lo; g.hi = hi; g.qbase = qbase; g.grow = grow; g.window = window; g.accumulate = accumulate;
+  g.o_bs = vdq.bs; g.o_rs = vdq.rs;
   g.scale = scale; g.scale_log2 = scale * 1.4426950408889634f;
   const long long cols = (long long)H * dh;
   const int k_rows = max(1, min(tape_rows, hi + (G - 1) * grow));
@@ -897,16 +899,17 @@ int dmb_attn_dq_tc(const void* q, TView vq, const void* do_c, TView vdo, int q_r
 
 // Key side.  Chunk z owns the tape rows [pos0 + z*grow, + 64) of Kc / Vc; its readers are the query positions
 // [max(q_start, chunk end), min(q_end, chunk start + span)) of q_all / doc_all (dense [B, T, H, DH] bf16) with
-// lse_all / corr_all dense [B, T, H] fp32.  dK, dV: dense [B, G, 64, H, DH] fp32, written.
+// lse_all / corr_all dense [B, T, H] fp32.  dK, dV: fp32 views [B, G*64, H, DH] with strides vdkv (chunk z at rows
+// z*64), written, or added to when accumulate != 0.
 int dmb_attn_dkv_tc(const void* q_all, const void* doc_all, const float* corr_all, const float* lse_all, int T,
-                    const void* Kc, const void* Vc, TView vc, int tape_rows, float* dK, float* dV, int B, int G, int H,
-                    int dh, int pos0, int q_start, int q_end, int grow, int span, float scale, int window, int* gerr,
-                    cudaStream_t st) {
+                    const void* Kc, const void* Vc, TView vc, int tape_rows, float* dK, float* dV, TView vdkv, int accumulate,
+                    int B, int G, int H, int dh, int pos0, int q_start, int q_end, int grow, int span, float scale,
+                    int window, int* gerr, cudaStream_t st) {
   if (!encode_fn()) return -10;
   if ((dh != 64 && dh != 128) || B <= 0 || G <= 0) return -1;
   BGeo g = {};
   g.H = H; g.T = T; g.C = BT; g.lo = pos0; g.grow = grow; g.window = window; g.span = span;
-  g.q_start = q_start; g.q_end = min(q_end, T); g.scale = scale; g.scale_log2 = scale * 1.4426950408889634f;
+  g.q_start = q_start; g.q_end = min(q_end, T); g.accumulate = accumulate; g.o_bs = vdkv.bs; g.o_rs = vdkv.rs; g.scale = scale; g.scale_log2 = scale * 1.4426950408889634f;
   const long long cols = (long long)H * dh;
   CUtensorMap a1, a2, y1, y2;
   int rc;

@@ -72,8 +72,8 @@ class _Sigs:
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
-    dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
-    dmb_attn_dkv_tc = [_p, _p, _p, _p, _i, _p, _p, _v, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p]
+    dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
+    dmb_attn_dkv_tc = [_p, _p, _p, _p, _i, _p, _p, _v, _i, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p]
     dmb_attn_fwd_tc = [_p, _v, _i, _p, _p, _v, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
                        _i, _p, _p]
 
@@ -368,7 +368,7 @@ class CudaOps(TorchOps):
         else:
             o_c = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
             lse_c = torch.empty(B, c, h, dtype=F32, device=q_r.device)
-        if self.ATTN_TC and c == 64 and self._tc_ok(q_r, Kc, Vc):
+        if self._tc("fwd") and c == 64 and self._tc_ok(q_r, Kc, Vc):
             self.attn_fwd_tc(q_r, Kc, Vc, lo, pos0, pos0 + qoff, scale, window, Lq=c, bm=64, out=(o_c, lse_c))
             if out is not None and o_c is not out[0]:
                 out[0].copy_(o_c)
@@ -384,13 +384,19 @@ class CudaOps(TorchOps):
             return out
         return o_c, lse_c
 
-    # DMB_ATTN_TC=1 sends the 64-row reads of the committed tape (a cell's prefix read, the wavefront's far and
-    # near reads and their backward) through the tcgen05 kernels of csrc/attn_tc.cu.  Default off: at 64 query rows
-    # per (batch, head) an M = 64 accumulator fills only 16 of a math warp's 32 lanes, and measured at the 340M
-    # cell shape (32 x 16 heads, 1024 keys) the warp-MMA kernels are faster (prefix_fwd 66 vs 82 us, prefix_dq
-    # 87 vs 93, prefix_dkv 111 vs 115).  Reads of 128 rows and more (`attn_fwd_tc` with bm=128) are where the
-    # tcgen05 kernel wins: 454 us for a 1024 x 4096 lower-right block at 4 x 36 heads of 64.
-    ATTN_TC = os.environ.get("DMB_ATTN_TC", "0") == "1"
+    # Which of the 64-row tape reads (a cell's prefix read, the wavefront's far and near reads) and their
+    # backward sides go through the tcgen05 kernels of csrc/attn_tc.cu instead of the warp-MMA kernels.
+    # Default: the sides where tcgen05 measured faster at the 340M cell shape (32 sequences x 16 heads of 64,
+    # 1024 keys / later queries): forward 47 vs 66 us, key side 81 vs 109 us; the query side stays on the
+    # warp-MMA kernel (95 vs 89 us).  DMB_ATTN_TC: comma list of fwd / dq / dkv, "1" or "all" = all, "0" = none.
+    _tc_env = os.environ.get("DMB_ATTN_TC", "fwd,dkv").lower()
+    ATTN_TC = (frozenset(("fwd", "dq", "dkv")) if _tc_env in ("1", "all") else
+               frozenset() if _tc_env in ("0", "", "none") else frozenset(x.strip() for x in _tc_env.split(",")))
+
+    def _tc(self, side):
+        """ATTN_TC may also be set to True / False on an instance (tests, benchmarks): all sides / none."""
+        a = self.ATTN_TC
+        return a if isinstance(a, bool) else side in a
 
     def attn_fwd_tc(self, q, Kc, Vc, lo, hi, qbase, scale, window=0, causal=False, causal_excl=1, Lq=None, G=1,
                     grow=0, bm=None, out_dtype=F32, out=None):
@@ -421,11 +427,11 @@ class CudaOps(TorchOps):
         B, rows, h, dh = q.shape
         self._ck(self.lib.dmb_attn_dq_tc(
             q.data_ptr(), _tv(q), do_c.data_ptr(), _tv(do_c), rows, Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), Kc.shape[1],
-            lse.data_ptr(), corr.data_ptr(), dq.data_ptr(), B, G, h, dh, lo, hi, qbase, grow, scale, window,
+            lse.data_ptr(), corr.data_ptr(), dq.data_ptr(), _tv(dq), B, G, h, dh, lo, hi, qbase, grow, scale, window,
             int(accumulate), self._tc_err.data_ptr(), self._st()), "attn_dq_tc")
 
     def attn_dkv_tc(self, q_all, doc_all, corr_all, lse_all, Kc, Vc, pos0, q_start, q_end, scale, window=0, G=1,
-                    grow=0, span=1 << 30, out=None):
+                    grow=0, span=1 << 30, out=None, accumulate=False):
         """Key side on tcgen05: (dK, dV) [B, G*64, h, dh] fp32 of the tape rows [pos0 + z*grow, +64) gathered
         over the query positions [max(q_start, chunk end), min(q_end, chunk start + span))."""
         B, T, h, dh = q_all.shape
@@ -434,8 +440,9 @@ class CudaOps(TorchOps):
                    torch.empty(B, G * 64, h, dh, dtype=F32, device=q_all.device))
         self._ck(self.lib.dmb_attn_dkv_tc(
             q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(), lse_all.data_ptr(), T, Kc.data_ptr(),
-            Vc.data_ptr(), _tv(Kc), Kc.shape[1], out[0].data_ptr(), out[1].data_ptr(), B, G, h, dh, pos0, q_start,
-            q_end, grow, span, scale, window, self._tc_err.data_ptr(), self._st()), "attn_dkv_tc")
+            Vc.data_ptr(), _tv(Kc), Kc.shape[1], out[0].data_ptr(), out[1].data_ptr(), _tv(out[0]), int(accumulate),
+            B, G, h, dh, pos0, q_start, q_end, grow, span, scale, window, self._tc_err.data_ptr(), self._st()),
+            "attn_dkv_tc")
         return out
 
     @staticmethod
@@ -464,7 +471,7 @@ class CudaOps(TorchOps):
         if not ok:
             return super().prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff)
         lse_c, corr = lse_c.contiguous(), corr.contiguous()
-        if (self.ATTN_TC and c == 64 and dq_acc.is_contiguous() and self._tc_ok(q_r, Kc, Vc)
+        if (self._tc("dq") and c == 64 and self._tc_ok(q_r, Kc, Vc)
                 and self._tc_ok(do_c, Kc, Vc)):
             return self.attn_dq_tc(q_r, do_c, Kc, Vc, lo, pos0, pos0 + qoff, scale, window, lse_c, corr, dq_acc)
         self._ck(self.lib.dmb_prefix_dq(q_r.data_ptr(), _tv(q_r), do_c.data_ptr(), _tv(do_c), Kc.data_ptr(),
@@ -488,10 +495,9 @@ class CudaOps(TorchOps):
             dK = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
             dV = torch.empty(B, c, h, dh, dtype=F32, device=q_all.device)
             accumulate = False
-        if (self.ATTN_TC and c == 64 and not accumulate and dK.is_contiguous() and dV.is_contiguous()
-                and self._tc_ok(q_all, Kc, Vc)):
+        if self._tc("dkv") and c == 64 and self._tc_ok(q_all, Kc, Vc):
             return self.attn_dkv_tc(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, q_start, q_end, scale, window,
-                                    out=(dK, dV))
+                                    out=(dK, dV), accumulate=accumulate)
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), doc_all.data_ptr(), corr_all.data_ptr(),
                                          lsec_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          dK.data_ptr(), dV.data_ptr(), _tv(dK), int(accumulate), B, T, c, h, dh, pos0,
@@ -559,10 +565,9 @@ class CudaOps(TorchOps):
             dK = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
             dV = torch.empty(B, G * C, h, dh, dtype=F32, device=q_all.device)
             accumulate = False
-        if (self.ATTN_TC and C == 64 and not accumulate and dK.is_contiguous() and dV.is_contiguous()
-                and self._tc_ok(q_all, Kc, Vc)):
+        if self._tc("dkv") and C == 64 and self._tc_ok(q_all, Kc, Vc):
             return self.attn_dkv_tc(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0 * C, q_lo, min(q_hi, T), scale,
-                                    window, G=G, grow=C, span=span, out=(dK, dV))
+                                    window, G=G, grow=C, span=span, out=(dK, dV), accumulate=accumulate)
         self._ck(self.lib.dmb_prefix_dkv(q_all.data_ptr(), docn_all.data_ptr(), corrn_all.data_ptr(),
                                          lsen_all.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), dK.data_ptr(),
                                          dV.data_ptr(), _tv(dK), int(accumulate), B, T, C, h, dh, j0 * C, q_lo,
@@ -631,7 +636,7 @@ class CudaOps(TorchOps):
         B, rows, h, dh = q_win.shape
         o_n = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
         lse_n = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
-        if self.ATTN_TC and C == 64 and self._tc_ok(q_win, Kc, Vc):
+        if self._tc("fwd") and C == 64 and self._tc_ok(q_win, Kc, Vc):
             self.attn_fwd_tc(q_win, Kc, Vc, lo, pos0, pos0, scale, window, Lq=C, G=rows // C, grow=C, bm=64,
                              out=(o_n, lse_n))
             return o_n, lse_n
@@ -646,7 +651,7 @@ class CudaOps(TorchOps):
         if not ok:
             return super().win_near_dq(q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window)
         B, rows, h, dh = q_win.shape
-        if (self.ATTN_TC and C == 64 and dq_acc.is_contiguous() and self._tc_ok(q_win, Kc, Vc)
+        if (self._tc("dq") and C == 64 and self._tc_ok(q_win, Kc, Vc)
                 and self._tc_ok(do_n, Kc, Vc)):
             return self.attn_dq_tc(q_win, do_n, Kc, Vc, lo, pos0, pos0, scale, window, lse_n, corr_n, dq_acc,
                                    G=rows // C, grow=C)

@@ -194,3 +194,39 @@ def test_window_group_launches_match_the_per_chunk_statement(ops):
     ops.tc_check()
     _close(dK, dK_ref, "near dK")
     _close(dV, dV_ref, "near dV")
+
+
+def test_backward_outputs_into_windows_of_longer_arrays(ops):
+    """The engines hand the backward kernels windows of [B, T, h, dh] gradient arrays: dq added in place, the
+    key side added to the pending gradient of its rows."""
+    B, T, h, dh, c = 2, 512, 2, 64, 64
+    ref, q_all, K, V, doc_all, lse_all, corr_all, scale = _cells(ops, B, T, h, dh, 0, 41)
+    pos0 = 256
+    r = slice(pos0, pos0 + c)
+    dq_ref = torch.full((B, T, h, dh), 0.5, device=DEV)
+    dq = dq_ref.clone()
+    lse_c, corr = lse_all[:, r].contiguous(), corr_all[:, r].contiguous()
+    ref.prefix_dq(q_all[:, r], K, V, pos0, scale, 0, lse_c, doc_all[:, r], corr, dq_ref[:, r])
+    ops.prefix_dq(q_all[:, r], K, V, pos0, scale, 0, lse_c, doc_all[:, r], corr, dq[:, r])
+    _close(dq, dq_ref, "dq into a window")
+    pend_ref = (torch.full((B, T, h, dh), 0.25, device=DEV), torch.full((B, T, h, dh), -0.25, device=DEV))
+    pend = (pend_ref[0].clone(), pend_ref[1].clone())
+    ref.prefix_dkv(q_all, doc_all, corr_all, lse_all, K, V, pos0, c, pos0 + c, scale, 0,
+                   out=(pend_ref[0][:, r], pend_ref[1][:, r]), accumulate=True)
+    ops.prefix_dkv(q_all, doc_all, corr_all, lse_all, K, V, pos0, c, pos0 + c, scale, 0,
+                   out=(pend[0][:, r], pend[1][:, r]), accumulate=True)
+    ops.tc_check()
+    _close(pend[0], pend_ref[0], "dK added to a window")
+    _close(pend[1], pend_ref[1], "dV added to a window")
+    # the same through the warp-MMA kernels
+    was, ops.ATTN_TC = ops.ATTN_TC, False
+    try:
+        pend2 = (torch.full((B, T, h, dh), 0.25, device=DEV), torch.full((B, T, h, dh), -0.25, device=DEV))
+        ops.prefix_dkv(q_all, doc_all, corr_all, lse_all, K, V, pos0, c, pos0 + c, scale, 0,
+                       out=(pend2[0][:, r], pend2[1][:, r]), accumulate=True)
+        dq2 = torch.full((B, T, h, dh), 0.5, device=DEV)
+        ops.prefix_dq(q_all[:, r], K, V, pos0, scale, 0, lse_c, doc_all[:, r], corr, dq2[:, r])
+    finally:
+        ops.ATTN_TC = was
+    _close(pend2[0], pend_ref[0], "dK added to a window (warp MMA)")
+    _close(dq2, dq_ref, "dq into a window (warp MMA)")
