@@ -640,7 +640,7 @@ class WaveScanEngine:
             dcg = S.dcg_stash[rows].view(B, c, 4 * d)
             dvc = S.dvc_stash[rows].view(B, c, d)
             ops.mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o2, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r],
-                               S.pin, P.k_gain, cfg.v_clamp_tau, S.dk[:, r], S.dv[:, r], S.dglx[:, r], dcg,
+                               S.pin, P.k_gain, cfg.v_clamp_tau, S.dk[:, r], S.dv[:, r], (S.dglx[:, r] if S.dglx is not None else None), dcg,
                                S.u_stash[rows].view(B, c, d), dvc, S.dkg_stash[rows].view(B, c, h))
             dvin = S.dvin_stash[rows].view(B, c, d)
             # v_in again (cheap) for the deferred W_vctx gradient: one GEMM per layer over all sweeps' rows
@@ -662,7 +662,7 @@ class WaveScanEngine:
             n = B * c
             dcg = S.dcg_stash[stash_row:stash_row + n].view(B, c, 4 * d)
             ops.refine_bwd(dK_out, dV_out, raw, ssq, o.reshape(B, c, d), S.glx[:, r], S.k[:, r], S.v[:, r],
-                           S.cos[r], S.sin[r], S.pin, S.dk[:, r], S.dv[:, r], S.dglx[:, r], dcg,
+                           S.cos[r], S.sin[r], S.pin, S.dk[:, r], S.dv[:, r], (S.dglx[:, r] if S.dglx is not None else None), dcg,
                            S.u_stash[stash_row:stash_row + n].view(B, c, d))
             rows = slice(stash_row, stash_row + n)
             du = self._pack_linear_dx(S.P, dcg, S.dt_stash[rows] if S.P.factored else None)
@@ -834,7 +834,14 @@ class WaveScanEngine:
             dks_r = torch.zeros(B, T, h, dh, dtype=f32, device=dev)
             dk = torch.zeros(B, T, d, dtype=f32, device=dev)
             dv = torch.zeros(B, T, d, dtype=f32, device=dev)
-            dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev) if packed else None
+            # gradient of the gates' x-logits: equal, sweep by sweep, to the gate columns of the stashed
+            # d(ctx / gate logits).  With a uniform schedule (every cell c rows, K sweeps: the stash rows are
+            # ordered cell, sweep, batch, row) it is summed from the stash once per layer; otherwise the
+            # refine backward accumulates it per sweep.
+            sch = self.schedules[sid]
+            from_stash = (packed and type(self) is WaveScanEngine and len({(c_, k_) for _, c_, k_ in sch}) == 1
+                          and [p_ for p_, _, _ in sch] == list(range(0, T, sch[0][1])))
+            dglx = torch.zeros(B, T, 2 * d, dtype=f32, device=dev) if packed and not from_stash else None
             dxhat_acc = None if packed else torch.zeros(B, T, d, dtype=f32, device=dev)
             dv4 = dv.view(B, T, h, dh)
             if not packed:
@@ -882,6 +889,8 @@ class WaveScanEngine:
             dY[..., d:2 * d] = dk + ops.unrope(dks_r, cos, sin).reshape(B, T, d)
             dY[..., 2 * d:3 * d] = dv
             if packed:
+                if from_stash:
+                    dglx = ops.stash_gate_sum(dcg_stash, B, T, sch[0][1], sch[0][2])
                 dY[..., 3 * d:5 * d] = dglx
             if mrk:
                 dY[..., 5 * d:] = S.dvgx

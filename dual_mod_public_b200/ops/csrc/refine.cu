@@ -112,8 +112,33 @@ __global__ void refine_bwd_kernel(const float* __restrict__ dK, const float* __r
     st8(uhat + ob + col, uh);
     acc8f(dkr + col, dkk);
     acc8f(dvr + col, dvv);
-    acc8f(dgr + col, dgk);
-    acc8f(dgr + d + col, dgv);
+    if (dglx_acc) {             // null: the caller sums the gate columns of the stashed dcg once per layer instead
+      acc8f(dgr + col, dgk);
+      acc8f(dgr + d + col, dgv);
+    }
+  }
+}
+
+// out[b, t, :] (bf16, 2d wide, dense) = sum over the K sweeps of the gate-logit columns [2d, 4d) of the stashed
+// d(ctx / gate logits): the rows of sweep s of cell ci sit at ((ci * K + s) * B + b) * c + i.  The gradient of a
+// gate's x-logit equals that of its u-logit, so it is not accumulated per sweep but read back once per layer.
+__global__ void stash_gate_sum_kernel(const bf16* __restrict__ stash, bf16* __restrict__ out, int B, int T, int c,
+                                      int K, int d) {
+  const int per_row = (2 * d) >> 3;
+  const long long total = (long long)B * T * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int col = (int)(i % per_row) << 3;
+    const long long row = i / per_row;
+    const int t = (int)(row % T), b = (int)(row / T);
+    const int ci = t / c, ii = t - ci * c;
+    V8 acc = {};
+    for (int s = 0; s < K; ++s) {
+      const long long sr = (((long long)ci * K + s) * B + b) * c + ii;
+      const V8 v = ld8(stash + sr * 4 * d + 2 * d + col);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc.x[e] += v.x[e];
+    }
+    st8(out + row * 2 * d + col, acc);
   }
 }
 
@@ -190,6 +215,13 @@ int dmb_refine_bwd(const float* dK, const float* dV, TView vdo, const void* raw,
   refine_bwd_kernel<<<(unsigned)((total + 127) / 128), 128, 0, st>>>(
       dK, dV, vdo, (const bf16*)raw, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, vv,
       cosb, sinb, (bf16*)dcg, (bf16*)uhat, dk_acc, vdk, dv_acc, vdv, dglx_acc, vdg, B, C, H, DH, pin_cols, eps);
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+int dmb_stash_gate_sum(const void* stash, void* out, int B, int T, int c, int K, int d, cudaStream_t st) {
+  if (d % 8 || T % c) return -1;
+  stash_gate_sum_kernel<<<1184, 256, 0, st>>>((const bf16*)stash, (bf16*)out, B, T, c, K, d);
   DMB_CHECK_LAUNCH();
   return 0;
 }

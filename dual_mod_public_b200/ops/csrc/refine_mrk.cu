@@ -263,8 +263,10 @@ __global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float*
       st8(uhat + ob + col, uh);
       acc8f(dkr + col, dkk);
       acc8f(dvr + col, dvv);
-      acc8f(dgr + col, dgk);
-      acc8f(dgr + d + col, dgv);
+      if (dglx_acc) {
+        acc8f(dgr + col, dgk);
+        acc8f(dgr + d + col, dgv);
+      }
     }
   }
   if (L.ok && (threadIdx.x % L.per_head) == 0) dkg[w.row * H + L.h] = s_g;

@@ -54,6 +54,7 @@ class _Sigs:
     dmb_refine_fwd = [_p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _v, _i, _i, _i, _i, _i, _f, _p]
     dmb_refine_bwd = [_p, _p, _v, _p, _p, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _v, _p, _v, _p, _v,
                       _i, _i, _i, _i, _i, _f, _p]
+    dmb_stash_gate_sum = [_p, _p, _i, _i, _i, _i, _i, _p]
     dmb_rmsn_bwd = [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p]
     dmb_mrk_vin_fwd = [_p, _p, _p, _p, _p, _v, _p, _i, _i, _i, _i, _f, _f, _p]
     dmb_mrk_vin_bwd = [_p, _p, _p, _p, _p, _v, _p, _p, _v, _p, _i, _i, _i, _i, _f, _f, _p]
@@ -285,7 +286,8 @@ class CudaOps(TorchOps):
         B, c, d = k.shape
         h = dK_out.shape[2]
         dh = d // h
-        ok = (self._mrk_ok(k, raw, glx, v, dk_acc, dv_acc, dglx_acc) and vc.dtype == BF16 and vc.is_contiguous()
+        views = (glx, v, dk_acc, dv_acc) + ((dglx_acc,) if dglx_acc is not None else ())
+        ok = (self._mrk_ok(k, raw, *views) and vc.dtype == BF16 and vc.is_contiguous()
               and o.dtype == BF16 and o.is_contiguous() and dK_out.dtype == F32 and dV_out.dtype == F32
               and _dense_tail(dK_out, 2) and dK_out.stride() == dV_out.stride() and ssq.is_contiguous()
               and all(t.is_contiguous() and t.dtype == BF16 for t in (dcg_out, uhat_out, dvc_out))
@@ -298,7 +300,9 @@ class CudaOps(TorchOps):
             dK_out.data_ptr(), dV_out.data_ptr(), _tv(dK_out), raw.data_ptr(), vc.data_ptr(), ssq.data_ptr(), o.data_ptr(),
             glx.data_ptr(), _tv(glx), k.data_ptr(), _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
             k_gain.data_ptr(), dcg_out.data_ptr(), uhat_out.data_ptr(), dvc_out.data_ptr(), dkg_out.data_ptr(),
-            dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(), _tv(dv_acc), dglx_acc.data_ptr(), _tv(dglx_acc),
+            dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(), _tv(dv_acc),
+            dglx_acc.data_ptr() if dglx_acc is not None else None,
+            _tv(dglx_acc) if dglx_acc is not None else TView(0, 0),
             B, c, h, dh, pin_cols, float(tau or 0.0), 1e-5, self._st()), "mrk_refine_bwd")
         self.launches += 1
 
@@ -731,16 +735,28 @@ class CudaOps(TorchOps):
               and raw.is_contiguous() and o.is_contiguous() and ssq.is_contiguous() and cos.is_contiguous()
               and dcg_out.is_contiguous() and uhat_out.is_contiguous() and dcg_out.dtype == BF16
               and dh % 16 == 0
-              and all(_dense_tail(t, 1) for t in (glx, k, v, dk_acc, dv_acc, dglx_acc)))
+              and all(_dense_tail(t, 1) for t in (glx, k, v, dk_acc, dv_acc))
+              and (dglx_acc is None or _dense_tail(dglx_acc, 1)))
         if not ok:
             return super().refine_bwd(dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc,
                                       dglx_acc, dcg_out, uhat_out)
+        dg_ptr, dg_view = (dglx_acc.data_ptr(), _tv(dglx_acc)) if dglx_acc is not None else (None, TView(0, 0))
         self._ck(self.lib.dmb_refine_bwd(
             dK_out.data_ptr(), dV_out.data_ptr(), _tv(dK_out), raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), glx.data_ptr(),
             _tv(glx), k.data_ptr(), _tv(k), v.data_ptr(), _tv(v), cos.data_ptr(), sin.data_ptr(),
             dcg_out.data_ptr(), uhat_out.data_ptr(), dk_acc.data_ptr(), _tv(dk_acc), dv_acc.data_ptr(),
-            _tv(dv_acc), dglx_acc.data_ptr(), _tv(dglx_acc), B, c, h, dh, pin_cols, 1e-5, self._st()),
+            _tv(dv_acc), dg_ptr, dg_view, B, c, h, dh, pin_cols, 1e-5, self._st()),
             "refine_bwd")
+
+    def stash_gate_sum(self, dcg_stash, B, T, c, K):
+        d = dcg_stash.shape[1] // 4
+        if not (dcg_stash.dtype == BF16 and dcg_stash.is_contiguous() and d % 8 == 0 and T % c == 0
+                and dcg_stash.shape[0] == (T // c) * K * B * c):
+            return super().stash_gate_sum(dcg_stash, B, T, c, K)
+        out = torch.empty(B, T, 2 * d, dtype=BF16, device=dcg_stash.device)
+        self._ck(self.lib.dmb_stash_gate_sum(dcg_stash.data_ptr(), out.data_ptr(), B, T, c, K, d, self._st()),
+                 "stash_gate_sum")
+        return out
 
     def rmsn_bwd(self, du, o, ssq, residual=None, out_dtype=F32, extra=None):
         d = o.shape[-1]

@@ -246,7 +246,8 @@ class TorchOps:
                                                          pin_cols, k_gain, tau)
         dk_acc += dk
         dv_acc += dv
-        dglx_acc += dcg[..., 2 * d:]
+        if dglx_acc is not None:                         # None: the caller uses `stash_gate_sum` once per layer
+            dglx_acc += dcg[..., 2 * d:]
         dkg_out.copy_(dkg)
         blk = dcg_out[..., d:2 * d].clone()
         dcg_out.copy_(dcg)
@@ -263,9 +264,18 @@ class TorchOps:
         d = k.shape[-1]
         dk_acc += dk
         dv_acc += dv
-        dglx_acc += dcg[..., 2 * d:]
+        if dglx_acc is not None:                         # None: the caller uses `stash_gate_sum` once per layer
+            dglx_acc += dcg[..., 2 * d:]
         dcg_out.copy_(dcg)
         uhat_out.copy_(uhat)
+
+    def stash_gate_sum(self, dcg_stash, B, T, c, K):
+        """Gradient of the gates' x-logits [B, T, 2d] (activation dtype) from the layer's stash of d(ctx / gate
+        logits) [n_cells * K * B * c, 4d], whose rows are ordered (cell, sweep, batch, row): the sum over the
+        sweeps of the gate columns (a gate's x-logit and u-logit share one gradient)."""
+        d = dcg_stash.shape[1] // 4
+        g = dcg_stash.view(T // c, K, B, c, 4 * d)[..., 2 * d:].float().sum(1)        # [cells, B, c, 2d]
+        return g.permute(1, 0, 2, 3).reshape(B, T, 2 * d).to(dcg_stash.dtype)
 
     def embed_bwd(self, gw, idx, dx):
         """gw (fp32 [V, d]) += scatter of dx rows [N, d] by token id idx [N]."""

@@ -436,3 +436,13 @@ def test_kernels_write_only_their_rows(ops):
     for i, (b, _) in enumerate(arrs):
         intact(b, f"cell_finish out {i}")
     assert ops.launches - n0 >= 6, "a torch fallback ran instead of a kernel"
+
+
+def test_stash_gate_sum_matches_torch_statement(ops):
+    """Gradient of the gates' x-logits read back from the layer's stash of d(ctx / gate logits)."""
+    B, T, c, K, d = 3, 256, 64, 4, 128
+    stash = rnd((T // c) * K * B * c, 4 * d, seed=21)
+    got = ops.stash_gate_sum(stash, B, T, c, K)
+    ref = REF.stash_gate_sum(stash.float(), B, T, c, K)
+    assert got.shape == (B, T, 2 * d) and got.dtype == torch.bfloat16
+    close(got, ref, rtol=1e-2, atol=2e-2, what="gate x-logit gradient")
