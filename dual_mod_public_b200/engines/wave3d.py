@@ -313,6 +313,7 @@ class Wave3DEngine(WaveScanEngine):
             if j >= 0 and (j + K) * C < self.T:
                 ops.prefix_dkv(S.q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc, j * C, C, (j + K) * C, scale,
                                self.window, out=(self.dKp[:, rows(j)], self.dVp[:, rows(j)]), accumulate=True)
+            self._join_beside()                                 # the far d q of step s+1 read rows this window rolls back
             Kc[:, w] = win[0][s][:, :G * C]                     # the tape as step s read it
             Vc[:, w] = win[1][s][:, :G * C]
             o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n = save.pop(s)
@@ -346,8 +347,13 @@ class Wave3DEngine(WaveScanEngine):
                 self.doc_all[:, r] = self.DOf_all[:, r]
                 self.corr_all[:, r] = corr_f
                 self.lsec_all[:, r] = self.lsefar_all[:, r]
-                ops.prefix_dq(S.q_r[:, r], Kc, Vc, fe, scale, self.window, self.lsefar_all[:, r].contiguous(),
-                              self.doc_all[:, r], corr_f, S.dq_r[:, r], qoff=s * C - fe)
+                # d q of the far read: it writes only chunk s's rows of dq_r, which no later step of the reverse pass
+                # touches, and runs on the second stream beside the key-side gathers that follow; it is joined
+                # before the next step rolls tape rows back (some of its keys lie in that window)
+                lse_f = self.lsefar_all[:, r].contiguous()
+                with self._beside(keep=(corr_f, lse_f)):
+                    ops.prefix_dq(S.q_r[:, r], Kc, Vc, fe, scale, self.window, lse_f, self.doc_all[:, r], corr_f,
+                                  S.dq_r[:, r], qoff=s * C - fe)
             # near reads of this step, key side: chunk jk was read by the window chunks in (jk, jk+K-1]
             j0 = max(0, lo - K + 1)
             if hi > j0:
@@ -356,6 +362,7 @@ class Wave3DEngine(WaveScanEngine):
                                  lo * C, (hi + 1) * C, K * C, scale, self.window,
                                  out=(self.dKp[:, wk], self.dVp[:, wk]), accumulate=True)
             self.stats["bwd_cells"] += G
+        self._join_beside()
         return dcg_stash, u_stash
 
 

@@ -302,6 +302,8 @@ class WaveScanEngine:
             self.dK = z(B, h, T, dh, dt=torch.float32)
             self.dV = z(B, h, T, dh, dt=torch.float32)
         self._sid = 0
+        self._side, self._side_keep, self._side_used = None, [], False
+        self.side_stream_ok = os.environ.get("DMB_SIDE_STREAM", "1") == "1"
         self._have_dx_top = False
         self.stats = {"fwd_cells": 0, "bwd_cells": 0}
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
@@ -967,9 +969,35 @@ class WaveScanEngine:
             # sweep 0 read the raw rows; publish this cell's (d o_c, corr, lse_c) for the earlier cells' gathers
             corr = ops.cell_finish(do_c, dlse_c, o_c, lse_c, dK_out, dV_out, self.doc_all[:, r],
                                    self.corr_all[:, r], self.lsec_all[:, r], dks_r[:, r], dv4[:, r])
-            ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_r[:, r])
+            # d q of the cell's prefix read touches only this cell's rows of dq_r and nothing the earlier cells
+            # wait for: it runs beside their backward on a second stream (a parallel branch of the layer's graph)
+            with self._beside(keep=(corr, lse_c)):
+                ops.prefix_dq(qc, Kc, Vc, pos0, scale, self.window, lse_c, self.doc_all[:, r], corr, dq_r[:, r])
             self.stats["bwd_cells"] += 1
+        self._join_beside()
         return dcg_stash, u_stash
+
+    # ---- a second stream for work nothing downstream waits for ------------------------------------------
+    def _beside(self, keep=()):
+        """Context: launches inside run on the engine's side stream, ordered after everything launched so far on
+        the main stream.  `keep`: tensors the side work reads that would otherwise be freed (and their memory
+        reused by main-stream work) before it ran; they are held until `_join_beside`.  On CPU: a no-op."""
+        import contextlib
+        if self.device.type != "cuda" or not self.side_stream_ok:
+            return contextlib.nullcontext()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        self._side.wait_stream(torch.cuda.current_stream(self.device))
+        self._side_keep.extend(keep)
+        self._side_used = True
+        return torch.cuda.stream(self._side)
+
+    def _join_beside(self):
+        """The main stream waits for the side stream's work (before anyone reads what it wrote)."""
+        if self._side_used:
+            torch.cuda.current_stream(self.device).wait_stream(self._side)
+            self._side_keep.clear()
+            self._side_used = False
 
     def _saturate_carry(self, dK, dV, d_o):
         """Gradient carried into a cell's committed rows from all later cells, measured against the

@@ -9,14 +9,16 @@
 
 namespace {
 
+constexpr int DEC_WARPS = 8;        // 8 warps x 4 key steps x 32 bytes of K and of V in flight per thread
+
 template <int DH>
-__global__ void __launch_bounds__(128) decode_attend_kernel(
+__global__ void __launch_bounds__(DEC_WARPS * 32) decode_attend_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ kself, const bf16* __restrict__ vself,
     const bf16* __restrict__ K, const bf16* __restrict__ V, const int* __restrict__ pos_ptr,
     bf16* __restrict__ out, int P, int H, float scale, int window) {
   constexpr int LPK = DH / 8;        // lanes per key (each lane owns 8 contiguous dims)
   constexpr int KPW = 32 / LPK;      // keys per warp step
-  constexpr int NW = 4;
+  constexpr int NW = DEC_WARPS;
   __shared__ float s_m[NW * KPW], s_l[NW * KPW];
   __shared__ float s_acc[NW * KPW][DH];
   const int h = blockIdx.x, b = blockIdx.y;
@@ -109,9 +111,9 @@ int dmb_decode_attend(const void* q, const void* kself, const void* vself, const
                       cudaStream_t st) {
   dim3 grid(H, B);
   if (dh == 64)
-    decode_attend_kernel<64><<<grid, 128, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, P, H, scale, window);
+    decode_attend_kernel<64><<<grid, DEC_WARPS * 32, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, P, H, scale, window);
   else if (dh == 128)
-    decode_attend_kernel<128><<<grid, 128, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, P, H, scale, window);
+    decode_attend_kernel<128><<<grid, DEC_WARPS * 32, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, P, H, scale, window);
   else
     return -1;
   DMB_CHECK_LAUNCH();
