@@ -248,18 +248,22 @@ class Wave3DEngine(WaveScanEngine):
         lo, hi = max(0, s - K + 1), min(s, n - 1)
         G, w = hi - lo + 1, slice(lo * C, (hi + 1) * C)
         if s < n:
+            # the entering chunk's far partial: it reads rows committed before this step and is needed by the merge
+            # only, so it runs on the second stream beside the window's near read
             r = slice(s * C, (s + 1) * C)
             fe = max(0, s - K + 1) * C
-            o_f, lse_f = ops.prefix_fwd(S.q_r[:, r], S.Kc, S.Vc, fe, S.scale, self.window, qoff=s * C - fe)
-            self.ofar_all[:, r] = o_f
-            self.lsefar_all[:, r] = lse_f
+            with self._beside():
+                o_f, lse_f = ops.prefix_fwd(S.q_r[:, r], S.Kc, S.Vc, fe, S.scale, self.window, qoff=s * C - fe)
+                self.ofar_all[:, r] = o_f
+                self.lsefar_all[:, r] = lse_f
+                del o_f, lse_f
             # (the chunk's raw rows are on the tape already: `_raw_tape` put every chunk's there before step 0)
         K_in, V_in = S.Kc[:, w], S.Vc[:, w]
         if win is not None:
-            win[0][s][:, :G * C] = K_in
-            win[1][s][:, :G * C] = V_in
+            ops.copy_pair(win[0][s][:, :G * C], K_in, win[1][s][:, :G * C], V_in)
         qw = S.q_r[:, w]
         o_n, lse_n = ops.win_near_fwd(qw, S.Kc, S.Vc, lo * C, (lo - K + 1) * C, C, S.scale, self.window)
+        self._join_beside()
         o_c, lse_c, w_f, w_n = ops.merge_partials(self.ofar_all[:, w], self.lsefar_all[:, w], o_n, lse_n)
         o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale, self.window)
         # every window chunk's new rows replace the old ones (all reads of this step are done)
@@ -314,8 +318,7 @@ class Wave3DEngine(WaveScanEngine):
                 ops.prefix_dkv(S.q_r, self.doc_all, self.corr_all, self.lsec_all, Kc, Vc, j * C, C, (j + K) * C, scale,
                                self.window, out=(self.dKp[:, rows(j)], self.dVp[:, rows(j)]), accumulate=True)
             self._join_beside()                                 # the far d q of step s+1 read rows this window rolls back
-            Kc[:, w] = win[0][s][:, :G * C]                     # the tape as step s read it
-            Vc[:, w] = win[1][s][:, :G * C]
+            ops.copy_pair(Kc[:, w], win[0][s][:, :G * C], Vc[:, w], win[1][s][:, :G * C])   # the tape as step s read it
             o, lse, ssq, raw, o_c, lse_c, o_n, lse_n, w_f, w_n = save.pop(s)
             # gradient of the rows this step wrote: read in place (window views of the pending arrays)
             d_o = self._refine_bwd(S, w, o, ssq, raw, self.dKp[:, w], self.dVp[:, w], offs[s], None)
@@ -329,28 +332,24 @@ class Wave3DEngine(WaveScanEngine):
             ops.win_tail_bwd(d_o, S.q_r[:, w], S.kself_r[:, w], S.v4[:, w], Kc[:, w], Vc[:, w], o_c, lse_c, o, lse, C,
                              scale, S.dq_r[:, w], S.dks_r[:, w], S.dv4[:, w], do_c, dlse_c, self.window, init=2,
                              dkv_out=(self.dKp[:, w], self.dVp[:, w]))
-            if s < n:                                           # chunk s entered here: it read its raw rows
-                r = rows(s)
-                S.dks_r[:, r] += self.dKp[:, r]
-                S.dv4[:, r] += self.dVp[:, r]
-                self.dKp[:, r] = 0
-                self.dVp[:, r] = 0
             # split d(o_c, lse_c) between the far and the near partial
+            corr_n = torch.empty(B, G * C, h, dtype=f32, device=dev)
             ops.split_partials(do_c, dlse_c, self.ofar_all[:, w], o_c, o_n, lse_n, w_f, w_n, self.DOf_all[:, w],
-                               self.DLf_all[:, w], self.docn_all[:, w], self.corrn_all[:, w], self.lsen_all[:, w])
-            corr_n = self.corrn_all[:, w].contiguous()
+                               self.DLf_all[:, w], self.docn_all[:, w], self.corrn_all[:, w], self.lsen_all[:, w],
+                               corrn_dense=corr_n)
             ops.win_near_dq(S.q_r[:, w], Kc, Vc, lo * C, (lo - K + 1) * C, C, scale, lse_n.contiguous(),
                             self.docn_all[:, w], corr_n, S.dq_r[:, w], self.window)
-            if s < n:                                           # every sweep of chunk s has been processed
+            if s < n:
+                # chunk s entered at this step and every sweep of it has now been processed: what this step read of
+                # it were its raw rows (their pending gradient moves to the raw-row gradients), and its far read's
+                # gradient is complete
                 r, fe = rows(s), max(0, s - K + 1) * C
-                corr_f = ((self.DOf_all[:, r] * self.ofar_all[:, r]).sum(-1) - self.DLf_all[:, r]).contiguous()
-                self.doc_all[:, r] = self.DOf_all[:, r]
-                self.corr_all[:, r] = corr_f
-                self.lsec_all[:, r] = self.lsefar_all[:, r]
+                corr_f, lse_f = ops.chunk_finish(self.DOf_all[:, r], self.DLf_all[:, r], self.ofar_all[:, r],
+                                                 self.lsefar_all[:, r], self.dKp[:, r], self.dVp[:, r], S.dks_r[:, r],
+                                                 S.dv4[:, r], self.doc_all[:, r], self.corr_all[:, r], self.lsec_all[:, r])
                 # d q of the far read: it writes only chunk s's rows of dq_r, which no later step of the reverse pass
                 # touches, and runs on the second stream beside the key-side gathers that follow; it is joined
                 # before the next step rolls tape rows back (some of its keys lie in that window)
-                lse_f = self.lsefar_all[:, r].contiguous()
                 with self._beside(keep=(corr_f, lse_f)):
                     ops.prefix_dq(S.q_r[:, r], Kc, Vc, fe, scale, self.window, lse_f, self.doc_all[:, r], corr_f,
                                   S.dq_r[:, r], qoff=s * C - fe)

@@ -206,6 +206,28 @@ def main():
         report("gemm dw layer", T(lambda: g.linear_dw_acc(dWb, dyb, xb)), flops=fb)
         report("  cublas dw layer", T(lambda: dWb.add_(torch.mm(dyb.t(), xb, out_dtype=torch.float32))), flops=fb)
         g.check()
+    # ---- the skinny GEMMs of the rank-144 factored write law (18 x d2304 recipe: 8192 window rows per step)
+    if want("gemm_lora") and ops.gemm is not None:
+        g = ops.gemm
+        M, dm, rk, nop = 8192, 2304, 144, 4
+        u, t_all, raw = rnd(M, dm), rnd(M, nop * rk), rnd(M, 4 * dm)
+        D_all, U = rnd(nop * rk, dm), rnd(dm, rk)
+        t1, raw1 = t_all[:, rk:2 * rk], raw[:, dm:2 * dm]
+        f = 2.0 * M * dm * nop * rk
+        report("gemm tn down (4 operators)", T(lambda: g.linear(u, D_all, BF, out=t_all)), flops=f)
+        report("  cublas down", T(lambda: torch.mm(u, D_all.t(), out=t_all)), flops=f)
+        f1 = 2.0 * M * dm * rk
+        report("gemm tn up (one operator)", T(lambda: g.linear(t1, U, BF, out=raw1)), flops=f1, bytes_=M * dm * 2)
+        report("  cublas up", T(lambda: torch.mm(t1, U.t(), out=raw1)), flops=f1, bytes_=M * dm * 2)
+        Dv, tv = rnd(rk, dm), rnd(M, rk)
+        report("gemm tn down (one operator)", T(lambda: g.linear(u, Dv, BF, out=tv)), flops=f1, bytes_=M * dm * 2)
+        report("  cublas down one", T(lambda: torch.mm(u, Dv.t(), out=tv)), flops=f1, bytes_=M * dm * 2)
+        report("gemm nn d(down out) (one operator)", T(lambda: g.linear_dx(raw1, U, out=t1)), flops=f1, bytes_=M * dm * 2)
+        report("  cublas d(down out)", T(lambda: torch.mm(raw1, U, out=t1)), flops=f1, bytes_=M * dm * 2)
+        du = rnd(M, dm)
+        report("gemm nn d(read) (4 operators)", T(lambda: g.linear_dx(t_all, D_all, out=du)), flops=f)
+        report("  cublas d(read)", T(lambda: torch.mm(t_all, D_all, out=du)), flops=f)
+        g.check()
     return rows
 
 

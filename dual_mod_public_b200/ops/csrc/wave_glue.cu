@@ -64,8 +64,8 @@ __global__ void __launch_bounds__(256) split_bwd_kernel(
     const float* __restrict__ do_c, const float* __restrict__ dlse_c, const float* __restrict__ o_c,
     const float* __restrict__ o_n, const float* __restrict__ lse_n, const float* __restrict__ w_f,
     const float* __restrict__ w_n, const float* __restrict__ o_f, float* __restrict__ DOf,
-    float* __restrict__ DLf, TD* __restrict__ docn, float* __restrict__ corrn, float* __restrict__ lsen,
-    long long bs_vec, long long bs_sca, int B, int R, int H) {
+    float* __restrict__ DLf, TD* __restrict__ docn, float* __restrict__ corrn, float* __restrict__ corrn_dense,
+    float* __restrict__ lsen, long long bs_vec, long long bs_sca, int B, int R, int H) {
   const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)B * R * H) return;
@@ -98,7 +98,9 @@ __global__ void __launch_bounds__(256) split_bwd_kernel(
   }
   if (lane == 0) {
     DLf[s_abs] += wf * (dotf + dl);
-    corrn[s_abs] = wn * donon - wn * (dotn + dl);
+    const float cn = wn * donon - wn * (dotn + dl);
+    corrn[s_abs] = cn;
+    if (corrn_dense) corrn_dense[wid] = cn;
     lsen[s_abs] = lse_n[wid];
   }
 }
@@ -141,6 +143,67 @@ __global__ void __launch_bounds__(256) cell_finish_kernel(
     corr_dense[wid] = cv;
     lsec[s_abs] = lse_c[wid];
   }
+}
+
+// End of a wavefront chunk's backward (every sweep of the chunk has been processed).  All arrays are indexed by
+// absolute position and start at the chunk's first row (batch strides bs_vec / bs_sca).  The far read's
+// accumulated gradient (DOf, DLf) becomes what the prefix backward kernels consume: doc = DOf (compute dtype),
+// corr = DOf . o_f - DLf (also dense [B, R, H]), lsec = lse_f (also dense); the pending gradient of the rows the
+// chunk's first sweep read (its raw rows) moves into the raw-row gradients: dks += dKp, dv += dVp, dKp = dVp = 0.
+template <int DH, typename TD>
+__global__ void __launch_bounds__(256) chunk_finish_kernel(
+    const float* __restrict__ DOf, const float* __restrict__ DLf, const float* __restrict__ o_f,
+    const float* __restrict__ lse_f, float* __restrict__ dKp, float* __restrict__ dVp, float* __restrict__ dks,
+    float* __restrict__ dv, TD* __restrict__ doc, float* __restrict__ corr, float* __restrict__ lsec,
+    float* __restrict__ corr_dense, float* __restrict__ lse_dense, long long bs_vec, long long bs_sca, int B, int R,
+    int H) {
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)B * R * H) return;
+  const int h = (int)(wid % H);
+  const long long br = wid / H;
+  const int r = (int)(br % R), b = (int)(br / R);
+  const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
+  const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
+  constexpr int PER = DH / 32;
+  float dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const long long i = v_abs + lane + 32 * e;
+    const float g = DOf[i];
+    dot += g * o_f[i];
+    doc[i] = cvt<TD>(g);
+    dks[i] += dKp[i];
+    dv[i] += dVp[i];
+    dKp[i] = 0.f;
+    dVp[i] = 0.f;
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) {
+    const float cv = dot - DLf[s_abs], l = lse_f[s_abs];
+    corr[s_abs] = cv;
+    corr_dense[wid] = cv;
+    lsec[s_abs] = l;
+    lse_dense[wid] = l;
+  }
+}
+
+// Two block copies of the same geometry in one launch: [B, n16] 16-byte words each, per-tensor batch strides.
+__global__ void __launch_bounds__(256) copy_pair_kernel(const uint4* __restrict__ s0, uint4* __restrict__ d0,
+                                                        const uint4* __restrict__ s1, uint4* __restrict__ d1,
+                                                        long long sbs, long long dbs, long long n16) {
+  const uint4* s = (blockIdx.z ? s1 : s0) + (long long)blockIdx.y * sbs;
+  uint4* d = (blockIdx.z ? d1 : d0) + (long long)blockIdx.y * dbs;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * step < n16; i += 4 * step) {
+    const uint4 a = s[i], b = s[i + step], c = s[i + 2 * step], e = s[i + 3 * step];
+    d[i] = a;
+    d[i + step] = b;
+    d[i + 2 * step] = c;
+    d[i + 3 * step] = e;
+  }
+  for (; i < n16; i += step) d[i] = s[i];
 }
 
 }  // namespace
@@ -186,13 +249,13 @@ int dmb_wave_merge_fwd(const float* o_f, const float* lse_f, long long bs_vec, l
 // docn_bf16: 1 = the near d o buffer is bf16, 0 = fp32
 int dmb_wave_split_bwd(const float* do_c, const float* dlse_c, const float* o_c, const float* o_n, const float* lse_n,
                        const float* w_f, const float* w_n, const float* o_f, float* DOf, float* DLf, void* docn,
-                       int docn_bf16, float* corrn, float* lsen, long long bs_vec, long long bs_sca, int B, int R,
-                       int H, int DH, cudaStream_t st) {
+                       int docn_bf16, float* corrn, float* corrn_dense, float* lsen, long long bs_vec, long long bs_sca,
+                       int B, int R, int H, int DH, cudaStream_t st) {
   const long long warps = (long long)B * R * H;
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
 #define GO(D, T)                                                                                              \
   split_bwd_kernel<D, T><<<blocks, 256, 0, st>>>(do_c, dlse_c, o_c, o_n, lse_n, w_f, w_n, o_f, DOf, DLf,      \
-                                                 (T*)docn, corrn, lsen, bs_vec, bs_sca, B, R, H)
+                                                 (T*)docn, corrn, corrn_dense, lsen, bs_vec, bs_sca, B, R, H)
   if (DH == 64) {
     if (docn_bf16) GO(64, bf16); else GO(64, float);
   } else if (DH == 128) {
@@ -201,6 +264,42 @@ int dmb_wave_split_bwd(const float* do_c, const float* dlse_c, const float* o_c,
     return -1;
   }
 #undef GO
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+int dmb_wave_chunk_finish(const float* DOf, const float* DLf, const float* o_f, const float* lse_f, float* dKp,
+                          float* dVp, float* dks, float* dv, void* doc, int doc_bf16, float* corr, float* lsec,
+                          float* corr_dense, float* lse_dense, long long bs_vec, long long bs_sca, int B, int R, int H,
+                          int DH, cudaStream_t st) {
+  const long long warps = (long long)B * R * H;
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+#define GO(D, T)                                                                                                 \
+  chunk_finish_kernel<D, T><<<blocks, 256, 0, st>>>(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, (T*)doc, corr, lsec, \
+                                                    corr_dense, lse_dense, bs_vec, bs_sca, B, R, H)
+  if (DH == 64) {
+    if (doc_bf16) GO(64, bf16); else GO(64, float);
+  } else if (DH == 128) {
+    if (doc_bf16) GO(128, bf16); else GO(128, float);
+  } else {
+    return -1;
+  }
+#undef GO
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+// src / dst: 16-byte aligned, row_bytes a multiple of 16; strides in bytes (multiples of 16).
+int dmb_copy_pair(const void* s0, void* d0, const void* s1, void* d1, long long src_bs, long long dst_bs,
+                  long long row_bytes, int B, cudaStream_t st) {
+  if ((row_bytes | src_bs | dst_bs) & 15) return -1;
+  const long long n16 = row_bytes >> 4;
+  long long bx = (n16 + 256 * 4 - 1) / (256 * 4);
+  if (bx < 1) bx = 1;
+  if (bx > 1024) bx = 1024;
+  dim3 grid((unsigned)bx, (unsigned)B, 2);
+  copy_pair_kernel<<<grid, 256, 0, st>>>((const uint4*)s0, (uint4*)d0, (const uint4*)s1, (uint4*)d1, src_bs >> 4,
+                                         dst_bs >> 4, n16);
   DMB_CHECK_LAUNCH();
   return 0;
 }

@@ -71,7 +71,9 @@ class _Sigs:
     dmb_prefix_dkv = [_p, _p, _p, _p, _p, _p, _v, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_cell_finish = [_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
-    dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_wave_chunk_finish = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_copy_pair = [_p, _p, _p, _p, _ll, _ll, _ll, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
     dmb_attn_dkv_tc = [_p, _p, _p, _p, _i, _p, _p, _v, _i, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p]
@@ -612,21 +614,59 @@ class CudaOps(TorchOps):
                                              w_f.data_ptr(), w_n.data_ptr(), B, R, h, dh, self._st()), "merge_partials")
         return o_c, lse_c, w_f, w_n
 
-    def split_partials(self, do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen):
+    def split_partials(self, do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen, corrn_dense=None):
         B, R, h, dh = o_n.shape
         vec = (o_f, DOf)
         ok = (dh in (64, 128) and all(self._abs_view_ok(t, 2) for t in vec) and _dense_tail(docn, 2)
               and docn.dtype in (BF16, F32) and all(self._abs_view_ok(t, 1) for t in (DLf, corrn, lsen))
               and len({o_f.stride(0), DOf.stride(0), docn.stride(0)}) == 1
               and len({DLf.stride(0), corrn.stride(0), lsen.stride(0)}) == 1
-              and all(t.is_contiguous() and t.dtype == F32 for t in (do_c, dlse_c, o_c, o_n, lse_n, w_f, w_n)))
+              and all(t.is_contiguous() and t.dtype == F32 for t in (do_c, dlse_c, o_c, o_n, lse_n, w_f, w_n))
+              and (corrn_dense is None or (corrn_dense.is_contiguous() and corrn_dense.dtype == F32
+                                           and corrn_dense.shape == lse_n.shape)))
         if not ok:
-            return super().split_partials(do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen)
+            return super().split_partials(do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen,
+                                          corrn_dense)
         self._ck(self.lib.dmb_wave_split_bwd(do_c.data_ptr(), dlse_c.data_ptr(), o_c.data_ptr(), o_n.data_ptr(),
                                              lse_n.data_ptr(), w_f.data_ptr(), w_n.data_ptr(), o_f.data_ptr(),
                                              DOf.data_ptr(), DLf.data_ptr(), docn.data_ptr(), int(docn.dtype == BF16),
-                                             corrn.data_ptr(), lsen.data_ptr(), o_f.stride(0), DLf.stride(0), B, R, h, dh,
+                                             corrn.data_ptr(), corrn_dense.data_ptr() if corrn_dense is not None else None,
+                                             lsen.data_ptr(), o_f.stride(0), DLf.stride(0), B, R, h, dh,
                                              self._st()), "split_partials")
+
+    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec):
+        B, R, h, dh = DOf.shape
+        vec, sca = (DOf, o_f, dKp, dVp, dks, dv), (DLf, lse_f, corr, lsec)
+        ok = (dh in (64, 128) and DOf.is_cuda and doc.dtype in (BF16, F32) and _dense_tail(doc, 2)
+              and doc.stride(1) == h * dh
+              and all(self._abs_view_ok(t, 2) and t.dtype == F32 for t in vec)
+              and all(self._abs_view_ok(t, 1) and t.dtype == F32 for t in sca)
+              and len({t.stride(0) for t in vec + (doc,)}) == 1 and len({t.stride(0) for t in sca}) == 1)
+        if not ok:
+            return super().chunk_finish(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec)
+        cv = torch.empty(B, R, h, dtype=F32, device=DOf.device)
+        ls = torch.empty(B, R, h, dtype=F32, device=DOf.device)
+        self._ck(self.lib.dmb_wave_chunk_finish(DOf.data_ptr(), DLf.data_ptr(), o_f.data_ptr(), lse_f.data_ptr(),
+                                                dKp.data_ptr(), dVp.data_ptr(), dks.data_ptr(), dv.data_ptr(),
+                                                doc.data_ptr(), int(doc.dtype == BF16), corr.data_ptr(), lsec.data_ptr(),
+                                                cv.data_ptr(), ls.data_ptr(), DOf.stride(0), DLf.stride(0), B, R, h, dh,
+                                                self._st()), "chunk_finish")
+        return cv, ls
+
+    def copy_pair(self, d0, s0, d1, s1):
+        """d0 <- s0 and d1 <- s1 in one launch: same shape and dtype, every batch row one contiguous block."""
+        B = d0.shape[0]
+        row = d0[0].numel() * d0.element_size()
+        blk = lambda t: t.dim() >= 2 and t[0].is_contiguous() and t.data_ptr() % 16 == 0
+        ok = (d0.is_cuda and all(blk(t) for t in (d0, s0, d1, s1)) and row % 16 == 0
+              and d0.shape == s0.shape == d1.shape == s1.shape and d0.dtype == s0.dtype == d1.dtype == s1.dtype
+              and s0.stride(0) == s1.stride(0) and d0.stride(0) == d1.stride(0)
+              and (s0.stride(0) * s0.element_size()) % 16 == 0 and (d0.stride(0) * d0.element_size()) % 16 == 0)
+        if not ok:
+            return super().copy_pair(d0, s0, d1, s1)
+        es = d0.element_size()
+        self._ck(self.lib.dmb_copy_pair(s0.data_ptr(), d0.data_ptr(), s1.data_ptr(), d1.data_ptr(), s0.stride(0) * es,
+                                        d0.stride(0) * es, row, B, self._st()), "copy_pair")
 
     # ---- window ops: G consecutive chunks of the same sequences in one launch ----------------------------
     def _win_ok(self, q_win, C, *views):

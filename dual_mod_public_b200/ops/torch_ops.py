@@ -168,9 +168,10 @@ class TorchOps:
         wf, wn = torch.exp(lse_f - lse), torch.exp(lse_n - lse)
         return wf.unsqueeze(-1) * o_f + wn.unsqueeze(-1) * o_n, lse, wf, wn
 
-    def split_partials(self, do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen):
+    def split_partials(self, do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen, corrn_dense=None):
         """Backward of `merge_partials`: accumulates the far gradients into DOf / DLf (+=) and writes the
-        near read's (d o, corr, lse) into docn / corrn / lsen (views by absolute position)."""
+        near read's (d o, corr, lse) into docn / corrn / lsen (views by absolute position); `corrn_dense`
+        (contiguous, optional) receives a second copy of corr."""
         g_f = (do_c * (o_f - o_c)).sum(-1) + dlse_c
         g_n = (do_c * (o_n - o_c)).sum(-1) + dlse_c
         DOf += w_f.unsqueeze(-1) * do_c
@@ -178,7 +179,28 @@ class TorchOps:
         do_n = w_n.unsqueeze(-1) * do_c
         docn.copy_(do_n)
         corrn.copy_((do_n * o_n).sum(-1) - w_n * g_n)
+        if corrn_dense is not None:
+            corrn_dense.copy_(corrn)
         lsen.copy_(lse_n)
+
+    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec):
+        """End of a wavefront chunk's backward, all arguments views of the chunk's rows in per-layer arrays:
+        the far read's accumulated gradient becomes the prefix kernels' inputs (doc = DOf, corr = DOf . o_f -
+        DLf, lsec = lse_f) and the pending gradient of the chunk's raw rows moves out (dks += dKp, dv += dVp,
+        dKp = dVp = 0).  Returns contiguous copies of (corr, lse_f)."""
+        cv = ((DOf * o_f).sum(-1) - DLf).contiguous()
+        doc.copy_(DOf)
+        corr.copy_(cv)
+        lsec.copy_(lse_f)
+        dks += dKp
+        dv += dVp
+        dKp.zero_()
+        dVp.zero_()
+        return cv, lse_f.contiguous()
+
+    def copy_pair(self, d0, s0, d1, s1):
+        d0.copy_(s0)
+        d1.copy_(s1)
 
     def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
         return fm.tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window)

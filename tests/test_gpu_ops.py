@@ -270,6 +270,11 @@ def test_window_ops_match_per_chunk_statement(ops, dh, C, G, lo_chunk, K):
                        R_[3][:, w], R_[4][:, w])
     for a, b_, n_ in zip((DOf, DLf, docn, corrn, lsen), R_, ("DOf", "DLf", "docn", "corrn", "lsen")):
         close(a, b_, rtol=1e-2, atol=1e-3, what=n_)
+    # the optional dense copy of corr_n
+    dense = torch.full((B, G * C, H), 7.0, device=DEV)
+    ops.split_partials(accr[3], accr[4], ofar[:, w], o_c, o_nr, lse_nr, w_f, w_n, DOf[:, w].clone(), DLf[:, w].clone(),
+                       docn[:, w], corrn[:, w], lsen[:, w], corrn_dense=dense)
+    close(dense, R_[3][:, w], rtol=1e-2, atol=1e-3, what="corrn dense")
     dq, dqr = z(B, G * C, H, dh), z(B, G * C, H, dh)
     ops.win_near_dq(q[:, w], Kc, Vc, pos0, lo, C, scale, lse_nr, R_[2][:, w], R_[3][:, w].contiguous(), dq)
     REF.win_near_dq(f(q[:, w]), f(Kc), f(Vc), pos0, lo, C, scale, lse_nr, R_[2][:, w].float(), R_[3][:, w].contiguous(), dqr)
@@ -301,6 +306,55 @@ def test_cell_finish(ops, dh):
     close(cv, cr, rtol=1e-4, atol=1e-4, what="corr")
     for x, y, n_ in zip(a, b_, ("doc", "corr_all", "lsec", "dks", "dv")):
         close(x, y, rtol=1e-2, atol=1e-4, what=n_)
+
+
+@pytest.mark.parametrize("dh,doc_dtype", [(64, torch.bfloat16), (128, torch.float32)])
+def test_chunk_finish(ops, dh, doc_dtype):
+    """End of a wavefront chunk's backward (one launch) against its torch statement, on views by absolute position."""
+    B, T, c, H, pos0 = 2, 192, 64, 3, 64
+    r = slice(pos0, pos0 + c)
+    f = lambda *s, seed: rnd(*s, dtype=torch.float32, seed=seed)
+
+    def arrays():
+        # DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec
+        return [f(B, T, H, dh, seed=1), f(B, T, H, seed=2), f(B, T, H, dh, seed=3), f(B, T, H, seed=4),
+                f(B, T, H, dh, seed=5), f(B, T, H, dh, seed=6), f(B, T, H, dh, seed=7), f(B, T, H, dh, seed=8),
+                torch.zeros(B, T, H, dh, device=DEV, dtype=doc_dtype), torch.zeros(B, T, H, device=DEV),
+                torch.zeros(B, T, H, device=DEV)]
+    a, b_ = arrays(), arrays()
+    before = [t.clone() for t in a]
+    cv, ls = ops.chunk_finish(*[t[:, r] for t in a])
+    cr, lr = REF.chunk_finish(*[t[:, r] for t in b_])
+    close(cv, cr, rtol=1e-4, atol=1e-4, what="corr")
+    close(ls, lr, rtol=0, atol=0, what="lse")
+    assert cv.is_contiguous() and ls.is_contiguous()
+    names = ("DOf", "DLf", "o_f", "lse_f", "dKp", "dVp", "dks", "dv", "doc", "corr", "lsec")
+    for x, y, n_ in zip(a, b_, names):
+        close(x, y, rtol=1e-2, atol=1e-4, what=n_)
+    assert (a[4][:, r] == 0).all() and (a[5][:, r] == 0).all()
+    out = torch.ones(T, dtype=torch.bool, device=DEV)
+    out[r] = False
+    for x, y, n_ in zip(a, before, names):                       # rows of other chunks are untouched
+        assert torch.equal(x[:, out], y[:, out]), n_
+
+
+def test_copy_pair(ops):
+    B, T, H, dh = 3, 320, 5, 64
+    tape = [rnd(B, T, H, dh, seed=i) for i in (1, 2)]
+    store = [torch.zeros(B, 192, H, dh, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    w = slice(64, 192)
+    ops.copy_pair(store[0][:, :128], tape[0][:, w], store[1][:, :128], tape[1][:, w])
+    for i in range(2):
+        assert torch.equal(store[i][:, :128], tape[i][:, w]) and (store[i][:, 128:] == 0).all()
+    back = [torch.zeros_like(t) for t in tape]
+    ops.copy_pair(back[0][:, w], store[0][:, :128], back[1][:, w], store[1][:, :128])
+    for i in range(2):
+        assert torch.equal(back[i][:, w], tape[i][:, w]) and (back[i][:, :64] == 0).all() and (back[i][:, 192:] == 0).all()
+    # a shape the kernel refuses (row bytes not a multiple of 16) falls back to two plain copies
+    a, b_ = rnd(2, 3, 5, seed=3), rnd(2, 3, 5, seed=4)
+    c, d = torch.zeros_like(a), torch.zeros_like(b_)
+    ops.copy_pair(c, a, d, b_)
+    assert torch.equal(c, a) and torch.equal(d, b_)
 
 
 @pytest.mark.parametrize("dh,pin,tau,H", [(64, 64, 0.8, 4), (128, 0, 0.0, 4), (64, 0, 50.0, 4), (64, 64, 0.8, 3),
