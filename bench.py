@@ -207,7 +207,8 @@ def run_ours(args):
                "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s",
                        "ms_per_step": round(ms_e2e, 2),
                        "h2d_bytes_per_step": tr.h2d_bytes_per_step(), "d2h_bytes_per_step": tr.d2h_bytes_per_step()},
-               "gpu_launches": int(launches), "clocks": clocks,
+               "gpu_launches": int(launches), "torch_fallbacks": dict(getattr(ops, "fallbacks", {})),
+               "clocks": clocks,
                "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}
         print(json.dumps(out), flush=True)
     if world > 1:

@@ -202,6 +202,44 @@ def tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, win
     return dq, dkself, dvraw, dK_in, dV_in, do_c, dlse_c
 
 
+def tail_bwd_sweep(dO, q_r, kself_r, K_in, V_in, lse_c, o, lse, scale, window=0):
+    """The per-sweep part of `tail_bwd` when the row-scalar x row products are deferred to the end of the cell:
+    returns fp32 (dq_intra, dK_in, dV_in, p_self, p_c, delta); dq_intra lacks the self-column term."""
+    c = q_r.shape[1]
+    dOf = dO.float()
+    s_in = torch.einsum("bchd,bjhd->bhcj", q_r, K_in).float() * scale
+    s_in = s_in.masked_fill(~_intra_mask(c, window, q_r.device), NEG)
+    s_self = (q_r.float() * kself_r.float()).sum(-1) * scale            # [B,c,h]
+    p_in = torch.exp(s_in - lse.permute(0, 2, 1).unsqueeze(-1))         # [B,h,c,c]
+    p_self = torch.exp(s_self - lse)
+    p_c = torch.exp(lse_c - lse)
+    delta = (dOf * o.float()).sum(-1)
+    dov = torch.einsum("bchd,bjhd->bhcj", dOf, V_in.float())
+    ds = p_in * (dov - delta.permute(0, 2, 1).unsqueeze(-1)) * scale
+    dq = torch.einsum("bhcj,bjhd->bchd", ds, K_in.float())
+    dK_in = torch.einsum("bhcj,bchd->bjhd", ds, q_r.float())
+    dV_in = torch.einsum("bhcj,bchd->bjhd", p_in, dOf)
+    return dq, dK_in, dV_in, p_self, p_c, delta
+
+
+def cell_finish_sweeps(dOs, scal, q_r, kself_r, v_raw, o_c, scale):
+    """The deferred sums of a cell's sweeps.  dOs: the sweeps' d o [B,c,h,dh]; scal [K,3,B,c,h] = their
+    (p_self, p_c, delta).  Returns fp32 (dq_self, dkself, dvraw, do_c, dlse_c) summed over the sweeps."""
+    vf, of = v_raw.float(), o_c.float()
+    dss = torch.zeros_like(scal[0, 0])
+    dl = torch.zeros_like(dss)
+    dvraw = torch.zeros_like(of)
+    do_c = torch.zeros_like(of)
+    for k in range(len(dOs) - 1, -1, -1):
+        g = dOs[k].float()
+        ps, pc, delta = scal[k, 0], scal[k, 1], scal[k, 2]
+        dss = dss + ps * ((g * vf).sum(-1) - delta) * scale
+        dl = dl + pc * ((g * of).sum(-1) - delta)
+        dvraw = dvraw + ps.unsqueeze(-1) * g
+        do_c = do_c + pc.unsqueeze(-1) * g
+    return dss.unsqueeze(-1) * kself_r.float(), dss.unsqueeze(-1) * q_r.float(), dvraw, do_c, dl
+
+
 # ---- RMSNorm ------------------------------------------------------------------------------------
 
 def rms_fwd(x, w, eps=1e-5):

@@ -955,20 +955,23 @@ class WaveScanEngine:
             d_o = dO_all[:, r].float()
             if self.sat_tau > 0 or self.track_rho:
                 dK_out, dV_out = self._saturate_carry(dK_out, dV_out, d_o)
-            # the cell's accumulators: the first sweep processed writes them (no zero fill); d q accumulates
-            # straight into the cell's rows of the layer's array
-            do_c = torch.empty(B, c, h, dh, dtype=f32, device=dev)
-            dlse_c = torch.empty(B, c, h, dtype=f32, device=dev)
+            # per sweep only the intra-block products run (d q accumulates straight into the cell's rows of the layer's
+            # array, the first sweep processed writes it); the row-scalar x row sums over the sweeps (d v_raw, d o_c,
+            # d lse_c, the self column) are formed once, at the end of the cell, from the sweeps' kept d o
+            scal = torch.empty(n_sweeps, 3, B, c, h, dtype=f32, device=dev)
+            d_os = [None] * n_sweeps
             for s in range(n_sweeps - 1, -1, -1):
                 K_in, V_in, o, lse, ssq, raw = st[s]
                 d_o = self._refine_bwd(S, r, o, ssq, raw, dK_out, dV_out, stash_off[(ci, s)],
                                        d_o.view(B, c, d) if s == n_sweeps - 1 else None).view(B, c, h, dh)
-                dK_out, dV_out = ops.tail_bwd(
-                    d_o, qc, ksc, vc4, K_in, V_in, o_c, lse_c, o, lse, scale, self.window,
-                    dq_r[:, r], dks_r[:, r], dv4[:, r], do_c, dlse_c, init=3 if s == n_sweeps - 1 else 0)
+                d_os[s] = d_o
+                dK_out, dV_out = ops.tail_bwd_sweep(d_o, qc, ksc, K_in, V_in, lse_c, o, lse, scale, self.window,
+                                                    dq_r[:, r], s == n_sweeps - 1, scal[s])
             # sweep 0 read the raw rows; publish this cell's (d o_c, corr, lse_c) for the earlier cells' gathers
-            corr = ops.cell_finish(do_c, dlse_c, o_c, lse_c, dK_out, dV_out, self.doc_all[:, r],
-                                   self.corr_all[:, r], self.lsec_all[:, r], dks_r[:, r], dv4[:, r])
+            corr = ops.cell_finish_sweeps(d_os, scal, qc, ksc, vc4, o_c, lse_c, dK_out, dV_out, self.doc_all[:, r],
+                                          self.corr_all[:, r], self.lsec_all[:, r], dks_r[:, r], dv4[:, r], dq_r[:, r],
+                                          scale)
+            del d_os
             # d q of the cell's prefix read touches only this cell's rows of dq_r and nothing the earlier cells
             # wait for: it runs beside their backward on a second stream (a parallel branch of the layer's graph)
             with self._beside(keep=(corr, lse_c)):

@@ -122,6 +122,17 @@ def main():
         report("tail_bwd", T(lambda: ops.tail_bwd(dO, qc, ksc, vrc, K_in, V_in, o_c, lse_c, o, lse, scale, 0,
                                                   acc[0], acc[1][:, r], acc[2][:, r], acc[3], acc[4])),
                flops=2.5 * att_f * c / 2)
+        # the same sweep with the row-scalar x row sums deferred to the end of the cell (4 sweeps per cell)
+        scal = torch.empty(4, 3, B, c, h, device=DEV)
+        report("tail_bwd_sweep (deferred)", T(lambda: ops.tail_bwd_sweep(dO, qc, ksc, K_in, V_in, lse_c, o, lse, scale, 0,
+                                                                       acc[0], False, scal[0])),
+               flops=2.5 * att_f * c / 2)
+        dOs = [rnd(B, c, h, dh, dtype=torch.float32) for _ in range(4)]
+        doc_a, cr_a, ls_a = torch.zeros(B, Tlen, h, dh, device=DEV, dtype=BF), z(B, Tlen, h), z(B, Tlen, h)
+        dq_a = z(B, Tlen, h, dh)
+        report("cell_finish_sweeps (4 sweeps)", T(lambda: ops.cell_finish_sweeps(
+            dOs, scal, qc, ksc, vrc, o_c, lse_c, acc[0], acc[3], doc_a[:, r], cr_a[:, r], ls_a[:, r], acc[1][:, r],
+            acc[2][:, r], dq_a[:, r], scale)), bytes_=B * c * h * dh * (4 * 4 + 3 * 2 + 3 * 4 + 3 * 8 + 2))
     if want("prefix_dq"):
         doc_c, corr = rnd(B, c, h, dh), rnd(B, c, h, dtype=torch.float32)
         both("prefix_dq", lambda: ops.prefix_dq(qc, Kc, Vc, pos0, scale, 0, lse_c, doc_c, corr, acc[0]),

@@ -150,7 +150,11 @@ __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
 // =============================================================================================
 // tail backward
 // =============================================================================================
-template <int DH, int C>
+// DEFER: the sweep's row-scalar x row products (d v_raw = p_self dO, d o_c = p_c dO, the self-column terms and
+// d lse_c) are left to the cell-end kernel, which forms them for all sweeps of the cell at once from the kept dO
+// rows; this kernel then only stashes (p_self, p_c, delta) per (row, head) in `dlsec_acc` = [3][rows] and touches
+// neither dks_acc, dv_acc, doc_acc nor v_raw / o_c.
+template <int DH, int C, bool DEFER>
 __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
     const float* __restrict__ dO, const bf16* __restrict__ q, TView vq, const bf16* __restrict__ ks,
     TView vks, const bf16* __restrict__ vr, TView vvr, const bf16* __restrict__ Kin, TView vKin,
@@ -200,13 +204,23 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
   const float pc0 = __expf(lse_c[orow0] - L0), pc1 = __expf(lse_c[orow1] - L1);
   const float delta0 = quad_dot_f32_bf16<DH>(dO0, o + orow0 * DH, t);
   const float delta1 = quad_dot_f32_bf16<DH>(dO1, o + orow1 * DH, t);
-  const float dsv0 = quad_dot_f32_bf16<DH>(dO0, vr0, t), dsv1 = quad_dot_f32_bf16<DH>(dO1, vr1, t);
-  const float doc0 = quad_dot_f32<DH>(dO0, o_c + orow0 * DH, t);
-  const float doc1 = quad_dot_f32<DH>(dO1, o_c + orow1 * DH, t);
-  const float dss0 = ps0 * (dsv0 - delta0) * scale, dss1 = ps1 * (dsv1 - delta1) * scale;
-  if (t == 0) {
-    dlsec_acc[orow0] = (init_doc ? 0.f : dlsec_acc[orow0]) + pc0 * (doc0 - delta0);
-    dlsec_acc[orow1] = (init_doc ? 0.f : dlsec_acc[orow1]) + pc1 * (doc1 - delta1);
+  float dss0 = 0.f, dss1 = 0.f;
+  if constexpr (DEFER) {
+    if (t == 0) {
+      const long long n_rows = (long long)gridDim.y * gridDim.z * C * H;
+      dlsec_acc[orow0] = ps0; dlsec_acc[n_rows + orow0] = pc0; dlsec_acc[2 * n_rows + orow0] = delta0;
+      dlsec_acc[orow1] = ps1; dlsec_acc[n_rows + orow1] = pc1; dlsec_acc[2 * n_rows + orow1] = delta1;
+    }
+  } else {
+    const float dsv0 = quad_dot_f32_bf16<DH>(dO0, vr0, t), dsv1 = quad_dot_f32_bf16<DH>(dO1, vr1, t);
+    const float doc0 = quad_dot_f32<DH>(dO0, o_c + orow0 * DH, t);
+    const float doc1 = quad_dot_f32<DH>(dO1, o_c + orow1 * DH, t);
+    dss0 = ps0 * (dsv0 - delta0) * scale;
+    dss1 = ps1 * (dsv1 - delta1) * scale;
+    if (t == 0) {
+      dlsec_acc[orow0] = (init_doc ? 0.f : dlsec_acc[orow0]) + pc0 * (doc0 - delta0);
+      dlsec_acc[orow1] = (init_doc ? 0.f : dlsec_acc[orow1]) + pc1 * (doc1 - delta1);
+    }
   }
   load_tile_bf16<DH, NT>(sQ, q + b * vq.bs + hoff, vq.rs, C, tid);
   load_tile_bf16<DH, NT>(sK, Kin + b * vKin.bs + hoff, vKin.rs, C, tid);
@@ -275,7 +289,20 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
       }
     }
   }
-  {
+  if constexpr (DEFER) {
+    float* dq0 = dq_acc + b * vdq.bs + i0 * vdq.rs + hoff;
+    float* dq1 = dq_acc + b * vdq.bs + i1 * vdq.rs + hoff;
+#pragma unroll
+    for (int n = 0; n < DH / 8; ++n) {
+      const int d = n * 8 + 2 * t;
+      float2 x = init_dq ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dq0 + d);
+      x.x += A[n][0]; x.y += A[n][1];
+      *reinterpret_cast<float2*>(dq0 + d) = x;
+      x = init_dq ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dq1 + d);
+      x.x += A[n][2]; x.y += A[n][3];
+      *reinterpret_cast<float2*>(dq1 + d) = x;
+    }
+  } else {
     float* dq0 = dq_acc + b * vdq.bs + i0 * vdq.rs + hoff;
     float* dq1 = dq_acc + b * vdq.bs + i1 * vdq.rs + hoff;
     float* dk0 = dks_acc + b * vdks.bs + i0 * vdks.rs + hoff;
@@ -537,12 +564,21 @@ int dmb_tail_bwd(const float* dO, const void* q, TView vq, const void* ks, TView
                  int window, int G, int grow, int flags, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)4 * C * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
-    auto kern = tail_bwd_kernel<DH, C>;
-    if (set_smem(kern, smem)) return -2;
-    kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
-                                            vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
-                                            lse_c, (const bf16*)o, lse, dq_acc, vdq, dks_acc, vdks, dv_acc, vdv,
-                                            doc_acc, dlsec_acc, dKin, dVin, vdkin, H, scale, window, grow, flags);
+    if (flags & 4) {
+      auto kern = tail_bwd_kernel<DH, C, true>;
+      if (set_smem(kern, smem)) return -2;
+      kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
+                                              vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
+                                              lse_c, (const bf16*)o, lse, dq_acc, vdq, dks_acc, vdks, dv_acc, vdv,
+                                              doc_acc, dlsec_acc, dKin, dVin, vdkin, H, scale, window, grow, flags);
+    } else {
+      auto kern = tail_bwd_kernel<DH, C, false>;
+      if (set_smem(kern, smem)) return -2;
+      kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
+                                              vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
+                                              lse_c, (const bf16*)o, lse, dq_acc, vdq, dks_acc, vdks, dv_acc, vdv,
+                                              doc_acc, dlsec_acc, dKin, dVin, vdkin, H, scale, window, grow, flags);
+    }
   })
   DMB_CHECK_LAUNCH();
   return 0;

@@ -145,6 +145,88 @@ __global__ void __launch_bounds__(256) cell_finish_kernel(
   }
 }
 
+// End of a cell's backward when the sweeps deferred their row-scalar x row products (tail backward in DEFER
+// mode).  sp.dO[k]: the gradient of sweep k's read, dense [B, R, H, DH] fp32; scal: [K][3][B*R*H] = (p_self, p_c,
+// delta) of every sweep.  q, ks, vr: the cell's rotated query, raw rotated key and raw value rows (bf16 views with
+// their own batch / row strides).  Forms, per (row, head):
+//   d v_raw  += sum_k p_self,k dO_k + dV0          d o_c = sum_k p_c,k dO_k   (-> doc in the compute dtype)
+//   dss       = sum_k p_self,k (dO_k . v_raw - delta_k) scale
+//   d k_self += dss q + dK0                        d q  += dss k_self
+//   d lse_c   = sum_k p_c,k (dO_k . o_c - delta_k)   corr = d o_c . o_c - d lse_c,   lsec = lse_c
+// Sweeps are summed in the order the reverse pass met them (k = K-1 first).
+struct SweepPtrs {
+  const float* dO[64];
+};
+
+template <int DH, typename TD>
+__global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
+    SweepPtrs sp, int K, const float* __restrict__ scal, const bf16* __restrict__ q, TView vq,
+    const bf16* __restrict__ ks, TView vks, const bf16* __restrict__ vr, TView vvr, const float* __restrict__ o_c, const float* __restrict__ lse_c,
+    const float* __restrict__ dK0, const float* __restrict__ dV0, TD* __restrict__ doc, float* __restrict__ corr,
+    float* __restrict__ corr_dense, float* __restrict__ lsec, float* __restrict__ dks, float* __restrict__ dv,
+    float* __restrict__ dq, float scale, long long bs_vec, long long bs_sca, int B, int R, int H) {
+  const long long n = (long long)B * R * H;
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= n) return;
+  const int h = (int)(wid % H);
+  const long long br = wid / H;
+  const int r = (int)(br % R), b = (int)(br / R);
+  const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
+  const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
+  constexpr int PER = DH / 32;
+  const bf16* q_row = q + b * vq.bs + r * vq.rs + (long long)h * DH;
+  const bf16* ks_row = ks + b * vks.bs + r * vks.rs + (long long)h * DH;
+  const bf16* vr_row = vr + b * vvr.bs + r * vvr.rs + (long long)h * DH;
+  float vv[PER], oc[PER], av[PER], ac[PER];
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    vv[e] = __bfloat162float(vr_row[lane + 32 * e]);
+    oc[e] = o_c[wid * DH + lane + 32 * e];
+    av[e] = ac[e] = 0.f;
+  }
+  float dss = 0.f, dl = 0.f;
+  for (int k = K - 1; k >= 0; --k) {
+    const float* g_ = sp.dO[k] + wid * DH;
+    const float* sc = scal + (long long)k * 3 * n + wid;
+    const float ps = sc[0], pc = sc[n], delta = sc[2 * n];
+    float g[PER], dsv = 0.f, dc = 0.f;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      g[e] = g_[lane + 32 * e];
+      dsv += g[e] * vv[e];
+      dc += g[e] * oc[e];
+      av[e] += ps * g[e];
+      ac[e] += pc * g[e];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      dsv += __shfl_xor_sync(0xffffffffu, dsv, o);
+      dc += __shfl_xor_sync(0xffffffffu, dc, o);
+    }
+    dss += ps * (dsv - delta) * scale;
+    dl += pc * (dc - delta);
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int d = lane + 32 * e;
+    const long long i = v_abs + d;
+    dot += ac[e] * oc[e];
+    doc[i] = cvt<TD>(ac[e]);
+    dks[i] += dK0[wid * DH + d] + dss * __bfloat162float(q_row[d]);
+    dv[i] += dV0[wid * DH + d] + av[e];
+    dq[i] += dss * __bfloat162float(ks_row[d]);
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) {
+    const float cv = dot - dl;
+    corr[s_abs] = cv;
+    corr_dense[wid] = cv;
+    lsec[s_abs] = lse_c[wid];
+  }
+}
+
 // End of a wavefront chunk's backward (every sweep of the chunk has been processed).  All arrays are indexed by
 // absolute position and start at the chunk's first row (batch strides bs_vec / bs_sca).  The far read's
 // accumulated gradient (DOf, DLf) becomes what the prefix backward kernels consume: doc = DOf (compute dtype),
@@ -260,6 +342,33 @@ int dmb_wave_split_bwd(const float* do_c, const float* dlse_c, const float* o_c,
     if (docn_bf16) GO(64, bf16); else GO(64, float);
   } else if (DH == 128) {
     if (docn_bf16) GO(128, bf16); else GO(128, float);
+  } else {
+    return -1;
+  }
+#undef GO
+  DMB_CHECK_LAUNCH();
+  return 0;
+}
+
+// dO_ptrs: K host-side pointers (K <= 64) to the sweeps' dense fp32 gradients
+int dmb_cell_finish_sweeps(const float* const* dO_ptrs, int K, const float* scal, const void* q, TView vq,
+                           const void* ks, TView vks, const void* vr, TView vvr, const float* o_c, const float* lse_c, const float* dK0, const float* dV0,
+                           void* doc, int doc_bf16, float* corr, float* corr_dense, float* lsec, float* dks, float* dv,
+                           float* dq, float scale, long long bs_vec, long long bs_sca, int B, int R, int H, int DH,
+                           cudaStream_t st) {
+  if (K < 1 || K > 64) return -1;
+  SweepPtrs sp;
+  for (int k = 0; k < 64; ++k) sp.dO[k] = dO_ptrs[k < K ? k : K - 1];
+  const long long warps = (long long)B * R * H;
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+#define GO(D, T)                                                                                                    \
+  cell_finish_sweeps_kernel<D, T><<<blocks, 256, 0, st>>>(sp, K, scal, (const bf16*)q, vq, (const bf16*)ks, vks,    \
+                                                          (const bf16*)vr, vvr, o_c, lse_c, dK0, dV0, (T*)doc, corr, \
+                                                          corr_dense, lsec, dks, dv, dq, scale, bs_vec, bs_sca, B, R, H)
+  if (DH == 64) {
+    if (doc_bf16) GO(64, bf16); else GO(64, float);
+  } else if (DH == 128) {
+    if (doc_bf16) GO(128, bf16); else GO(128, float);
   } else {
     return -1;
   }

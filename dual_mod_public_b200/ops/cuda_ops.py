@@ -72,6 +72,8 @@ class _Sigs:
     dmb_cell_finish = [_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_cell_finish_sweeps = [_p, _i, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _f, _ll,
+                              _ll, _i, _i, _i, _i, _p]
     dmb_wave_chunk_finish = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_copy_pair = [_p, _p, _p, _p, _ll, _ll, _ll, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
@@ -107,14 +109,23 @@ class CudaOps(TorchOps):
         self.device = torch.device(device)
         self.lib = load_library()
         self.launches = 0
+        self.fallbacks = {}                    # op name -> calls that took the torch statement instead of a kernel
         self._scratch = {}
         self.gemm = None                       # set by enable_gemm()
+        self.strict = os.environ.get("DMB_STRICT_OPS", "0") == "1"
         self._tc_err = torch.zeros(1, dtype=torch.int32, device=self.device)   # raised by the tcgen05 attention kernels
         if os.environ.get("DMB_GEMM", "tcgen05") == "tcgen05":
             from .gemm import Tcgen05Gemm
             self.gemm = Tcgen05Gemm(self.lib, self.device)
 
     # ---- helpers ---------------------------------------------------------------------------
+    def _fell_back(self, name):
+        """A call whose arguments the kernel does not take (layout, dtype, size) runs the torch statement; it is
+        counted so that a hot path that silently left the kernels shows up (`fallbacks`, `DMB_STRICT_OPS=1` raises)."""
+        self.fallbacks[name] = self.fallbacks.get(name, 0) + 1
+        if self.strict:
+            raise RuntimeError(f"{name}: arguments not accepted by the sm_100a kernel (DMB_STRICT_OPS=1)")
+
     def _st(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
@@ -137,24 +148,28 @@ class CudaOps(TorchOps):
             y = self.gemm.linear(x, w, out_dtype or x.dtype, bias=bias, out=out)
             self.launches += 1
             return y
+        self._fell_back("linear")
         return super().linear(x, w, bias, out_dtype, out)
 
     def linear_dx(self, dy, w, out=None):
         if self.gemm is not None and self.gemm.ok_nn(dy, w) and (out is None or self.gemm.ok_out(out, dy, w.shape[1])):
             self.launches += 1
             return self.gemm.linear_dx(dy, w, out=out)
+        self._fell_back("linear_dx")
         return super().linear_dx(dy, w, out)
 
     def linear_dw_acc(self, dW, dy, x):
         if self.gemm is not None and self.gemm.ok_tn_dw(dW, dy, x):
             self.launches += 1
             return self.gemm.linear_dw_acc(dW, dy, x)
+        self._fell_back("linear_dw_acc")
         return super().linear_dw_acc(dW, dy, x)
 
     # ---- norms ------------------------------------------------------------------------------------
     def rms_fwd(self, x, w, eps=1e-5):
         d = x.shape[-1]
         if x.dtype != BF16 or d % 8:
+            self._fell_back("rms_fwd")
             return super().rms_fwd(x, w, eps)
         if not x.is_contiguous():
             x = x.contiguous()
@@ -172,6 +187,7 @@ class CudaOps(TorchOps):
               and x.is_contiguous() and dy.is_contiguous()
               and (residual is None or (residual.is_contiguous() and residual.dtype == out_dtype)))
         if not ok:
+            self._fell_back("rms_bwd")
             return super().rms_bwd(dy, x, w, rstd, dw_acc, residual, out_dtype)
         rows = x.numel() // d
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
@@ -192,6 +208,7 @@ class CudaOps(TorchOps):
     def col_sum_acc(self, out, dy):
         n = dy.shape[-1]
         if dy.dtype not in (BF16, F32) or not dy.is_contiguous():
+            self._fell_back("col_sum_acc")
             return super().col_sum_acc(out, dy)
         rows = dy.numel() // n
         nsplit = max(1, min(64, rows // 64))
@@ -204,6 +221,7 @@ class CudaOps(TorchOps):
     def embed_bwd(self, gw, idx, dx):
         d = dx.shape[-1]
         if dx.dtype not in (BF16, F32) or not dx.is_contiguous() or not gw.is_contiguous() or d % 4:
+            self._fell_back("embed_bwd")
             return super().embed_bwd(gw, idx, dx)
         tok, order = torch.sort(idx.reshape(-1), stable=True)
         self._ck(self.lib.dmb_embed_bwd_sorted(tok.data_ptr(), order.data_ptr(), dx.data_ptr(), int(dx.dtype == F32),
@@ -212,6 +230,7 @@ class CudaOps(TorchOps):
     def col_dot_acc(self, out, a, b):
         n = a.shape[-1]
         if a.dtype != BF16 or b.dtype != BF16 or not a.is_contiguous() or not b.is_contiguous():
+            self._fell_back("col_dot_acc")
             return super().col_dot_acc(out, a, b)
         rows = a.numel() // n
         nsplit = max(1, min(64, rows // 64))
@@ -236,6 +255,7 @@ class CudaOps(TorchOps):
         dh = d // h
         if not (self._mrk_ok(o, raw, vgx) and o.is_contiguous() and ssq.is_contiguous() and w_ctx.dtype == BF16
                 and vgx.dtype == BF16 and dh % 16 == 0):
+            self._fell_back("mrk_vin_fwd")
             return super().mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
         vin = torch.empty(B, c, d, dtype=BF16, device=o.device)
         self._ck(self.lib.dmb_mrk_vin_fwd(raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), w_ctx.data_ptr(), vgx.data_ptr(),
@@ -251,6 +271,7 @@ class CudaOps(TorchOps):
               and dcg.dtype == BF16 and ssq.is_contiguous() and w_ctx.dtype == BF16 and vgx.dtype == BF16
               and dvgx_acc.dtype == F32 and dh % 16 == 0)
         if not ok:
+            self._fell_back("mrk_vin_bwd")
             return super().mrk_vin_bwd(dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc)
         du_hat = torch.empty(B, c, d, dtype=F32, device=o.device)
         self._ck(self.lib.dmb_mrk_vin_bwd(dvin.data_ptr(), raw.data_ptr(), ssq.data_ptr(), w_ctx.data_ptr(), vgx.data_ptr(),
@@ -265,6 +286,7 @@ class CudaOps(TorchOps):
         ok = (self._mrk_ok(k, raw, glx, v) and vc.dtype == BF16 and vc.is_contiguous() and cos.is_contiguous()
               and ssq.is_contiguous() and k_gain.dtype == F32 and dh % 16 == 0)
         if not ok:
+            self._fell_back("mrk_refine_fwd")
             return super().mrk_refine_fwd(raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, out)
         if (out is not None and all(t.dtype == BF16 and _dense_tail(t, 2) for t in out)
                 and out[0].stride() == out[1].stride()):
@@ -296,6 +318,7 @@ class CudaOps(TorchOps):
               and dkg_out.is_contiguous() and dkg_out.dtype == F32 and k_gain.dtype == F32
               and dh % 16 == 0)
         if not ok:
+            self._fell_back("mrk_refine_bwd")
             return super().mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, pin_cols, k_gain, tau,
                                           dk_acc, dv_acc, dglx_acc, dcg_out, uhat_out, dvc_out, dkg_out)
         self._ck(self.lib.dmb_mrk_refine_bwd(
@@ -330,6 +353,7 @@ class CudaOps(TorchOps):
     # ---- swiglu ------------------------------------------------------------------------------------------
     def swiglu_fwd(self, h1, h3):
         if h1.dtype != BF16 or not (h1.is_contiguous() and h3.is_contiguous()) or h1.numel() % 8:
+            self._fell_back("swiglu_fwd")
             return super().swiglu_fwd(h1, h3)
         g = torch.empty_like(h1)
         self._ck(self.lib.dmb_swiglu_fwd(h1.data_ptr(), h3.data_ptr(), g.data_ptr(), h1.numel(),
@@ -339,6 +363,7 @@ class CudaOps(TorchOps):
     def swiglu_bwd(self, dg, h1, h3):
         if h1.dtype != BF16 or dg.dtype != BF16 or h1.numel() % 8 or not (
                 dg.is_contiguous() and h1.is_contiguous() and h3.is_contiguous()):
+            self._fell_back("swiglu_bwd")
             return super().swiglu_bwd(dg, h1, h3)
         d1, d3 = torch.empty_like(h1), torch.empty_like(h3)
         self._ck(self.lib.dmb_swiglu_bwd(dg.data_ptr(), h1.data_ptr(), h3.data_ptr(), d1.data_ptr(),
@@ -348,6 +373,7 @@ class CudaOps(TorchOps):
     # ---- CE ---------------------------------------------------------------------------------------------------
     def ce_chunk(self, logits, targets, inv_n):
         if logits.dtype != BF16 or not logits.is_contiguous() or not torch.is_tensor(inv_n):
+            self._fell_back("ce_chunk")
             return super().ce_chunk(logits, targets, inv_n)
         n, V = logits.shape
         row_loss = torch.empty(n, dtype=F32, device=logits.device)
@@ -368,6 +394,7 @@ class CudaOps(TorchOps):
         B, c, h, dh = q_r.shape
         lo = prefix_lo(pos0, window, qoff)
         if not self._cell_ok(q_r) or pos0 - lo <= 0 or not (_dense_tail(q_r, 2) and _dense_tail(Kc, 2)):
+            self._fell_back("prefix_fwd")
             return super().prefix_fwd(q_r, Kc, Vc, pos0, scale, window, out, qoff)
         if out is not None and out[0].is_contiguous() and out[1].is_contiguous() and out[0].dtype == F32:
             o_c, lse_c = out
@@ -475,6 +502,7 @@ class CudaOps(TorchOps):
         ok = (self._cell_ok(q_r) and do_c.dtype == BF16 and dq_acc.dtype == F32 and _dense_tail(dq_acc, 2)
               and _dense_tail(q_r, 2) and _dense_tail(do_c, 2) and _dense_tail(Kc, 2))
         if not ok:
+            self._fell_back("prefix_dq")
             return super().prefix_dq(q_r, Kc, Vc, pos0, scale, window, lse_c, do_c, corr, dq_acc, qoff)
         lse_c, corr = lse_c.contiguous(), corr.contiguous()
         if (self._tc("dq") and c == 64 and self._tc_ok(q_r, Kc, Vc)
@@ -493,6 +521,7 @@ class CudaOps(TorchOps):
               and q_all.is_contiguous() and doc_all.is_contiguous() and corr_all.is_contiguous()
               and lsec_all.is_contiguous() and _dense_tail(Kc, 2) and (out is None or self._dkv_view_ok(out)))
         if not ok:
+            self._fell_back("prefix_dkv")
             return super().prefix_dkv(q_all, doc_all, corr_all, lsec_all, Kc, Vc, pos0, c, q_start, scale, window, q_end,
                                       out, accumulate)
         if out is not None:
@@ -512,6 +541,7 @@ class CudaOps(TorchOps):
 
     def tail_fwd(self, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window=0):
         if not self._cell_ok(q_r) or not all(_dense_tail(t, 2) for t in (q_r, kself_r, v_raw, K_in, V_in)):
+            self._fell_back("tail_fwd")
             return super().tail_fwd(q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, scale, window)
         B, c, h, dh = q_r.shape
         o = torch.empty(B, c, h, dh, dtype=BF16, device=q_r.device)
@@ -532,6 +562,7 @@ class CudaOps(TorchOps):
               and all(_dense_tail(t, 2) for t in (q_r, kself_r, v_raw, K_in, V_in, dks_acc, dv_acc, dq_acc))
               and (dkv_out is None or self._dkv_view_ok(dkv_out)))
         if not ok:
+            self._fell_back("tail_bwd")
             return super().tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale,
                                     window, dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, init, dkv_out)
         B, c, h, dh = q_r.shape
@@ -550,6 +581,54 @@ class CudaOps(TorchOps):
             "tail_bwd")
         return dK_in, dV_in
 
+    def tail_bwd_sweep(self, dO, q_r, kself_r, K_in, V_in, lse_c, o, lse, scale, window, dq_acc, init, scal):
+        B, c, h, dh = q_r.shape
+        ok = (self._cell_ok(q_r) and dO.dtype == F32 and dO.is_contiguous() and o.is_contiguous()
+              and scal.is_contiguous() and scal.dtype == F32 and scal.shape == (3, B, c, h)
+              and all(_dense_tail(t, 2) for t in (q_r, kself_r, K_in, V_in, dq_acc)))
+        if not ok:
+            self._fell_back("tail_bwd_sweep")
+            return super().tail_bwd_sweep(dO, q_r, kself_r, K_in, V_in, lse_c, o, lse, scale, window, dq_acc, init, scal)
+        dK_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+        dV_in = torch.empty(B, c, h, dh, dtype=F32, device=q_r.device)
+        lse_c, lse = lse_c.contiguous(), lse.contiguous()
+        # deferred mode (flag bit 2): the raw value, o_c and the dks / dv / d o_c accumulators are not touched
+        self._ck(self.lib.dmb_tail_bwd(
+            dO.data_ptr(), q_r.data_ptr(), _tv(q_r), kself_r.data_ptr(), _tv(kself_r), kself_r.data_ptr(),
+            _tv(kself_r), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), None,
+            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), _tv(dq_acc), None,
+            _tv(dq_acc), None, _tv(dq_acc), None, scal.data_ptr(),
+            dK_in.data_ptr(), dV_in.data_ptr(), _tv(dK_in), B, c, h, dh, scale, window, 1, 0, 4 | (1 if init else 0),
+            self._st()), "tail_bwd_sweep")
+        return dK_in, dV_in
+
+    def cell_finish_sweeps(self, dOs, scal, q_r, kself_r, v_raw, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv, dq,
+                           scale):
+        B, R, h, dh = o_c.shape
+        K = len(dOs)
+        absf, absb = (dks, dv, dq), (q_r, kself_r, v_raw)
+        ok = (dh in (64, 128) and o_c.is_cuda and 1 <= K <= 64 and doc.dtype in (BF16, F32) and _dense_tail(doc, 2)
+              and doc.stride(1) == h * dh and scal.is_contiguous() and scal.shape == (K, 3, B, R, h)
+              and all(t.is_contiguous() and t.dtype == F32 and t.shape == o_c.shape for t in tuple(dOs) + (o_c, dK0, dV0))
+              and lse_c.is_contiguous() and lse_c.dtype == F32
+              and all(self._abs_view_ok(t, 2) for t in absf)
+              and all(t.dtype == BF16 and _dense_tail(t, 2) for t in absb)
+              and all(self._abs_view_ok(t, 1) for t in (corr, lsec)) and corr.stride(0) == lsec.stride(0)
+              and len({t.stride(0) for t in absf + (doc,)}) == 1)
+        if not ok:
+            self._fell_back("cell_finish_sweeps")
+            return super().cell_finish_sweeps(dOs, scal, q_r, kself_r, v_raw, o_c, lse_c, dK0, dV0, doc, corr, lsec,
+                                              dks, dv, dq, scale)
+        cv = torch.empty(B, R, h, dtype=F32, device=o_c.device)
+        ptrs = (ctypes.c_void_p * K)(*[t.data_ptr() for t in dOs])
+        self._ck(self.lib.dmb_cell_finish_sweeps(
+            ctypes.cast(ptrs, ctypes.c_void_p), K, scal.data_ptr(), q_r.data_ptr(), _tv(q_r), kself_r.data_ptr(),
+            _tv(kself_r), v_raw.data_ptr(), _tv(v_raw), o_c.data_ptr(),
+            lse_c.data_ptr(), dK0.data_ptr(), dV0.data_ptr(), doc.data_ptr(), int(doc.dtype == BF16), corr.data_ptr(),
+            cv.data_ptr(), lsec.data_ptr(), dks.data_ptr(), dv.data_ptr(), dq.data_ptr(), scale, dks.stride(0),
+            corr.stride(0), B, R, h, dh, self._st()), "cell_finish_sweeps")
+        return cv
+
     @staticmethod
     def _dkv_view_ok(pair):
         a, b = pair
@@ -563,6 +642,7 @@ class CudaOps(TorchOps):
               and q_all.is_contiguous() and docn_all.is_contiguous() and corrn_all.is_contiguous()
               and lsen_all.is_contiguous() and _dense_tail(Kc, 2) and (out is None or self._dkv_view_ok(out)))
         if not ok:
+            self._fell_back("win_near_dkv")
             return super().win_near_dkv(q_all, docn_all, corrn_all, lsen_all, Kc, Vc, j0, G, C, q_lo, q_hi, span, scale,
                                         window, out, accumulate)
         if out is not None:
@@ -593,6 +673,7 @@ class CudaOps(TorchOps):
               and doc.stride(1) == h * dh and len({doc.stride(0), dks.stride(0), dv.stride(0)}) == 1
               and corr.stride(0) == lsec.stride(0))
         if not ok:
+            self._fell_back("cell_finish")
             return super().cell_finish(do_c, dlse_c, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv)
         cv = torch.empty(B, R, h, dtype=F32, device=do_c.device)
         self._ck(self.lib.dmb_cell_finish(do_c.data_ptr(), dlse_c.data_ptr(), o_c.data_ptr(), lse_c.data_ptr(),
@@ -606,6 +687,7 @@ class CudaOps(TorchOps):
         ok = (dh in (64, 128) and self._abs_view_ok(o_f, 2) and self._abs_view_ok(lse_f, 1)
               and o_n.is_contiguous() and lse_n.is_contiguous() and o_n.dtype == F32 and o_n.is_cuda)
         if not ok:
+            self._fell_back("merge_partials")
             return super().merge_partials(o_f, lse_f, o_n, lse_n)
         o_c, lse_c = torch.empty_like(o_n), torch.empty_like(lse_n)
         w_f, w_n = torch.empty_like(lse_n), torch.empty_like(lse_n)
@@ -625,6 +707,7 @@ class CudaOps(TorchOps):
               and (corrn_dense is None or (corrn_dense.is_contiguous() and corrn_dense.dtype == F32
                                            and corrn_dense.shape == lse_n.shape)))
         if not ok:
+            self._fell_back("split_partials")
             return super().split_partials(do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen,
                                           corrn_dense)
         self._ck(self.lib.dmb_wave_split_bwd(do_c.data_ptr(), dlse_c.data_ptr(), o_c.data_ptr(), o_n.data_ptr(),
@@ -643,6 +726,7 @@ class CudaOps(TorchOps):
               and all(self._abs_view_ok(t, 1) and t.dtype == F32 for t in sca)
               and len({t.stride(0) for t in vec + (doc,)}) == 1 and len({t.stride(0) for t in sca}) == 1)
         if not ok:
+            self._fell_back("chunk_finish")
             return super().chunk_finish(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec)
         cv = torch.empty(B, R, h, dtype=F32, device=DOf.device)
         ls = torch.empty(B, R, h, dtype=F32, device=DOf.device)
@@ -663,6 +747,7 @@ class CudaOps(TorchOps):
               and s0.stride(0) == s1.stride(0) and d0.stride(0) == d1.stride(0)
               and (s0.stride(0) * s0.element_size()) % 16 == 0 and (d0.stride(0) * d0.element_size()) % 16 == 0)
         if not ok:
+            self._fell_back("copy_pair")
             return super().copy_pair(d0, s0, d1, s1)
         es = d0.element_size()
         self._ck(self.lib.dmb_copy_pair(s0.data_ptr(), d0.data_ptr(), s1.data_ptr(), d1.data_ptr(), s0.stride(0) * es,
@@ -676,6 +761,7 @@ class CudaOps(TorchOps):
 
     def win_near_fwd(self, q_win, Kc, Vc, pos0, lo, C, scale, window=0):
         if not self._win_ok(q_win, C, Kc):
+            self._fell_back("win_near_fwd")
             return super().win_near_fwd(q_win, Kc, Vc, pos0, lo, C, scale, window)
         B, rows, h, dh = q_win.shape
         o_n = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
@@ -693,6 +779,7 @@ class CudaOps(TorchOps):
         ok = (self._win_ok(q_win, C, Kc, do_n) and do_n.dtype == BF16 and dq_acc.dtype == F32 and _dense_tail(dq_acc, 2)
               and lse_n.is_contiguous() and corr_n.is_contiguous())
         if not ok:
+            self._fell_back("win_near_dq")
             return super().win_near_dq(q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window)
         B, rows, h, dh = q_win.shape
         if (self._tc("dq") and C == 64 and self._tc_ok(q_win, Kc, Vc)
@@ -706,6 +793,7 @@ class CudaOps(TorchOps):
 
     def win_tail_fwd(self, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale, window=0):
         if not self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in) or not (o_c.is_contiguous() and lse_c.is_contiguous()):
+            self._fell_back("win_tail_fwd")
             return super().win_tail_fwd(q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, C, scale, window)
         B, rows, h, dh = q_win.shape
         o = torch.empty(B, rows, h, dh, dtype=BF16, device=q_win.device)
@@ -724,6 +812,7 @@ class CudaOps(TorchOps):
               and all(t.is_contiguous() for t in (dO, o, o_c, lse_c, lse, doc_acc, dlsec_acc))
               and _dense_tail(dq_acc, 2) and (dkv_out is None or self._dkv_view_ok(dkv_out)))
         if not ok:
+            self._fell_back("win_tail_bwd")
             return super().win_tail_bwd(dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
                                         dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window, init, dkv_out)
         B, rows, h, dh = q_win.shape
@@ -748,6 +837,7 @@ class CudaOps(TorchOps):
               and ssq.is_contiguous() and dh % 16 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v)))
         if not ok:
+            self._fell_back("refine_fwd")
             return super().refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols, out)
         if (out is not None and all(t.dtype == BF16 and _dense_tail(t, 2) for t in out)
                 and out[0].stride() == out[1].stride()):
@@ -778,6 +868,7 @@ class CudaOps(TorchOps):
               and all(_dense_tail(t, 1) for t in (glx, k, v, dk_acc, dv_acc))
               and (dglx_acc is None or _dense_tail(dglx_acc, 1)))
         if not ok:
+            self._fell_back("refine_bwd")
             return super().refine_bwd(dK_out, dV_out, raw, ssq, o, glx, k, v, cos, sin, pin_cols, dk_acc, dv_acc,
                                       dglx_acc, dcg_out, uhat_out)
         dg_ptr, dg_view = (dglx_acc.data_ptr(), _tv(dglx_acc)) if dglx_acc is not None else (None, TView(0, 0))
@@ -792,6 +883,7 @@ class CudaOps(TorchOps):
         d = dcg_stash.shape[1] // 4
         if not (dcg_stash.dtype == BF16 and dcg_stash.is_contiguous() and d % 8 == 0 and T % c == 0
                 and dcg_stash.shape[0] == (T // c) * K * B * c):
+            self._fell_back("stash_gate_sum")
             return super().stash_gate_sum(dcg_stash, B, T, c, K)
         out = torch.empty(B, T, 2 * d, dtype=BF16, device=dcg_stash.device)
         self._ck(self.lib.dmb_stash_gate_sum(dcg_stash.data_ptr(), out.data_ptr(), B, T, c, K, d, self._st()),
@@ -806,6 +898,7 @@ class CudaOps(TorchOps):
               and (residual is None or (residual.is_contiguous() and residual.dtype == out_dtype))
               and (extra is None or (extra.is_contiguous() and extra.dtype == F32)))
         if not ok:
+            self._fell_back("rmsn_bwd")
             return super().rmsn_bwd(du, o, ssq, residual, out_dtype, extra)
         rows = o.numel() // d
         out = torch.empty(o.shape, dtype=out_dtype, device=o.device)

@@ -227,6 +227,31 @@ class TorchOps:
             dlsec_acc += dlse
         return _into(dkv_out, (dK_in, dV_in), False)
 
+    def tail_bwd_sweep(self, dO, q_r, kself_r, K_in, V_in, lse_c, o, lse, scale, window, dq_acc, init, scal):
+        """`tail_bwd` with the row-scalar x row products deferred to `cell_finish_sweeps`: accumulates only the
+        intra-block d q into dq_acc (written when `init`), stores this sweep's (p_self, p_c, delta) in `scal`
+        [3, B, c, h] and returns fp32 (dK_in, dV_in)."""
+        dq, dK_in, dV_in, ps, pc, delta = fm.tail_bwd_sweep(dO, q_r, kself_r, K_in, V_in, lse_c, o, lse, scale, window)
+        if init:
+            dq_acc.copy_(dq)
+        else:
+            dq_acc += dq
+        scal[0].copy_(ps)
+        scal[1].copy_(pc)
+        scal[2].copy_(delta)
+        return dK_in, dV_in
+
+    def cell_finish_sweeps(self, dOs, scal, q_r, kself_r, v_raw, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv, dq,
+                           scale):
+        """End of a cell's backward after deferred sweeps (`tail_bwd_sweep`): the sums over the sweeps of d v_raw,
+        d o_c, d lse_c and the self-column terms are formed here from the kept d o of every sweep, then `cell_finish`:
+        doc, corr, lsec at the cell's rows (views by absolute position), dks / dv / dq += (views).  Returns corr dense."""
+        dq_s, dks_s, dv_s, do_c, dlse_c = fm.cell_finish_sweeps(dOs, scal, q_r, kself_r, v_raw, o_c, scale)
+        dq += dq_s
+        dks += dks_s
+        dv += dv_s
+        return self.cell_finish(do_c, dlse_c, o_c, lse_c, dK0, dV0, doc, corr, lsec, dks, dv)
+
     def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):
         """`out`: optional (K, V) [B,c,h,dh] views to write into (e.g. the cell's rows of the tape)."""
         K, V = fm.refine_fwd(raw, ssq, glx, k, v, cos, sin, h, pin_cols)

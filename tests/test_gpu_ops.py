@@ -143,6 +143,62 @@ def test_prefix_and_tail_fwd_bwd(ops, c, dh, pos0, window):
     close(dq_acc, dq_r, rtol=3e-2, atol=3e-2, what="prefix dq")
 
 
+@pytest.mark.parametrize("c,dh,window,H,n_sweeps", [(64, 64, 0, 4, 3), (64, 128, 0, 3, 2), (32, 64, 20, 5, 4), (16, 64, 0, 4, 1)])
+def test_deferred_sweeps_equal_per_sweep_accumulation(ops, c, dh, window, H, n_sweeps):
+    """`tail_bwd_sweep` per sweep + `cell_finish_sweeps` once per cell against the per-sweep fp32 statement
+    (`tail_bwd` accumulating every sweep, then `cell_finish`)."""
+    B, pos0 = 2, 2 * c
+    T = pos0 + 2 * c
+    scale = dh ** -0.5
+    q, ks, vr, Kc, Vc = _cell_inputs(B, c, H, dh, T)
+    r = slice(pos0, pos0 + c)
+    qc, ksc, vrc = q[:, r], ks[:, r], vr[:, r]
+    f = lambda t: t.float()
+    o_c, lse_c = fm.prefix_fwd(f(qc), f(Kc), f(Vc), pos0, scale, window)
+    z = lambda *s: torch.zeros(*s, device=DEV)
+    sweeps = []
+    for s_ in range(n_sweeps):
+        K_in, V_in = rnd(B, c, H, dh, seed=20 + s_), rnd(B, c, H, dh, seed=40 + s_)
+        o, lse, _ = fm.tail_fwd(f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c, lse_c, scale, window)
+        sweeps.append((K_in, V_in, o.to(torch.bfloat16), lse, rnd(B, c, H, dh, dtype=torch.float32, seed=60 + s_)))
+    dK0, dV0 = rnd(B, c, H, dh, dtype=torch.float32, seed=5), rnd(B, c, H, dh, dtype=torch.float32, seed=6)
+
+    def arrays():      # doc, corr, lsec, dks, dv, dq by absolute position (dks / dv / dq start non-zero)
+        return [torch.zeros(B, T, H, dh, device=DEV, dtype=torch.bfloat16), z(B, T, H), z(B, T, H),
+                rnd(B, T, H, dh, dtype=torch.float32, seed=7), rnd(B, T, H, dh, dtype=torch.float32, seed=8),
+                rnd(B, T, H, dh, dtype=torch.float32, seed=9)]
+    # statement: every sweep accumulates, then cell_finish
+    a = arrays()
+    do_c, dlse_c = z(B, c, H, dh), z(B, c, H)
+    dq_cell = z(B, c, H, dh)
+    for K_in, V_in, o, lse, dO in reversed(sweeps):
+        REF.tail_bwd(dO, f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c, lse_c, o.float(), lse, scale, window,
+                     dq_cell, a[3][:, r], a[4][:, r], do_c, dlse_c)
+    a[5][:, r] = dq_cell                      # the first sweep processed writes the cell's d q
+    cv_ref = REF.cell_finish(do_c, dlse_c, o_c, lse_c, dK0, dV0, a[0][:, r], a[1][:, r], a[2][:, r], a[3][:, r], a[4][:, r])
+    # kernels: deferred
+    b_ = arrays()
+    scal = torch.empty(n_sweeps, 3, B, c, H, device=DEV)
+    outs = []
+    for s_ in range(n_sweeps - 1, -1, -1):
+        K_in, V_in, o, lse, dO = sweeps[s_]
+        outs.append(ops.tail_bwd_sweep(dO, qc, ksc, K_in, V_in, lse_c, o, lse, scale, window, b_[5][:, r],
+                                       s_ == n_sweeps - 1, scal[s_]))
+        ref = fm.tail_bwd(dO, f(qc), f(ksc), f(vrc), f(K_in), f(V_in), o_c, lse_c, o.float(), lse, scale, window)
+        close(outs[-1][0], ref[3], rtol=3e-2, atol=3e-2, what="dK_in")
+        close(outs[-1][1], ref[4], rtol=3e-2, atol=3e-2, what="dV_in")
+    cv = ops.cell_finish_sweeps([t[4] for t in sweeps], scal, qc, ksc, vrc, o_c, lse_c, dK0, dV0, b_[0][:, r],
+                                b_[1][:, r], b_[2][:, r], b_[3][:, r], b_[4][:, r], b_[5][:, r], scale)
+    close(cv, cv_ref, rtol=3e-2, atol=3e-2, what="corr")
+    for x, y, n_ in zip(b_, a, ("doc", "corr", "lsec", "dks", "dv", "dq")):
+        close(x, y, rtol=3e-2, atol=3e-2, what=n_)
+    out = torch.ones(T, dtype=torch.bool, device=DEV)
+    out[r] = False
+    fresh = arrays()
+    for x, y in zip(b_, fresh):
+        assert torch.equal(x[:, out], y[:, out])
+
+
 @pytest.mark.parametrize("c,dh,pos0,T,window", [(64, 64, 128, 512, 0), (64, 128, 64, 300, 0), (32, 64, 32, 200, 0),
                                                 (16, 64, 48, 128, 0), (64, 64, 128, 512, 150), (64, 64, 448, 512, 0)])
 def test_prefix_dkv_owner_computes(ops, c, dh, pos0, T, window):
