@@ -202,6 +202,15 @@ def tail_bwd(dO, q_r, kself_r, v_raw, K_in, V_in, o_c, lse_c, o, lse, scale, win
     return dq, dkself, dvraw, dK_in, dV_in, do_c, dlse_c
 
 
+def tail_self_scalars(dO, q_r, kself_r, v_raw, o, lse, scale):
+    """The self column's per-(row, head) scalars of `tail_bwd`: (p_self, dss) with d v_raw = p_self dO,
+    d k_self = dss q, and dss k_self the self column's part of d q."""
+    dOf = dO.float()
+    p_self = torch.exp((q_r.float() * kself_r.float()).sum(-1) * scale - lse)
+    delta = (dOf * o.float()).sum(-1)
+    return p_self, p_self * ((dOf * v_raw.float()).sum(-1) - delta) * scale
+
+
 def tail_bwd_sweep(dO, q_r, kself_r, K_in, V_in, lse_c, o, lse, scale, window=0):
     """The per-sweep part of `tail_bwd` when the row-scalar x row products are deferred to the end of the cell:
     returns fp32 (dq_intra, dK_in, dV_in, p_self, p_c, delta); dq_intra lacks the self-column term."""

@@ -309,6 +309,10 @@ class Wave3DEngine(WaveScanEngine):
         # per-step scratch of the partial's gradient: written (not accumulated) by the tail kernel
         do_c_buf = torch.empty(B, K * C, h, dh, dtype=f32, device=dev)
         dlse_c_buf = torch.empty(B, K * C, h, dtype=f32, device=dev)
+        # d o and the self column's scalars (p_self, dss) of the last K steps: a chunk's raw-row gradients
+        # (d v_raw = sum over its sweeps of p_self dO, d k_self = (sum dss) q) are formed once, when its last sweep
+        # has been processed, instead of read-modify-written by every step
+        ring = {}
         for s in range(n + K - 2, -1, -1):
             lo, hi = max(0, s - K + 1), min(s, n - 1)
             G, w, j = hi - lo + 1, slice(lo * C, (hi + 1) * C), s - K + 1
@@ -329,9 +333,11 @@ class Wave3DEngine(WaveScanEngine):
             dlse_c = dlse_c_buf[:, :G * C] if G == K else torch.empty(B, G * C, h, dtype=f32, device=dev)
             # gradient of what step s read = rows of step s-1: replaces the pending gradient of the window's
             # rows; d q goes straight into the layer's array
+            stash = torch.empty(2, B, G * C, h, dtype=f32, device=dev)
+            ring[s] = (d_o, stash, lo)
             ops.win_tail_bwd(d_o, S.q_r[:, w], S.kself_r[:, w], S.v4[:, w], Kc[:, w], Vc[:, w], o_c, lse_c, o, lse, C,
                              scale, S.dq_r[:, w], S.dks_r[:, w], S.dv4[:, w], do_c, dlse_c, self.window, init=2,
-                             dkv_out=(self.dKp[:, w], self.dVp[:, w]))
+                             dkv_out=(self.dKp[:, w], self.dVp[:, w]), raw_stash=stash)
             # split d(o_c, lse_c) between the far and the near partial
             corr_n = torch.empty(B, G * C, h, dtype=f32, device=dev)
             ops.split_partials(do_c, dlse_c, self.ofar_all[:, w], o_c, o_n, lse_n, w_f, w_n, self.DOf_all[:, w],
@@ -344,9 +350,16 @@ class Wave3DEngine(WaveScanEngine):
                 # it were its raw rows (their pending gradient moves to the raw-row gradients), and its far read's
                 # gradient is complete
                 r, fe = rows(s), max(0, s - K + 1) * C
+                sweeps = []
+                for k in range(K):                              # sweep k of chunk s ran at step s + k
+                    g_o, g_st, g_lo = ring[s + k]
+                    gr = rows(s - g_lo)
+                    sweeps.append((g_o[:, gr], g_st[0][:, gr], g_st[1][:, gr]))
                 corr_f, lse_f = ops.chunk_finish(self.DOf_all[:, r], self.DLf_all[:, r], self.ofar_all[:, r],
                                                  self.lsefar_all[:, r], self.dKp[:, r], self.dVp[:, r], S.dks_r[:, r],
-                                                 S.dv4[:, r], self.doc_all[:, r], self.corr_all[:, r], self.lsec_all[:, r])
+                                                 S.dv4[:, r], self.doc_all[:, r], self.corr_all[:, r], self.lsec_all[:, r],
+                                                 sweeps=sweeps, q=S.q_r[:, r])
+                del sweeps
                 # d q of the far read: it writes only chunk s's rows of dq_r, which no later step of the reverse pass
                 # touches, and runs on the second stream beside the key-side gathers that follow; it is joined
                 # before the next step rolls tape rows back (some of its keys lie in that window)
@@ -360,6 +373,7 @@ class Wave3DEngine(WaveScanEngine):
                 ops.win_near_dkv(S.q_r, self.docn_all, self.corrn_all, self.lsen_all, Kc, Vc, j0, hi - j0, C,
                                  lo * C, (hi + 1) * C, K * C, scale, self.window,
                                  out=(self.dKp[:, wk], self.dVp[:, wk]), accumulate=True)
+            ring.pop(s + K - 1, None)                           # chunk s - 1 needs the steps s - 1 .. s + K - 2 only
             self.stats["bwd_cells"] += G
         self._join_beside()
         return dcg_stash, u_stash

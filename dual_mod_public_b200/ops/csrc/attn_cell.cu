@@ -150,11 +150,13 @@ __global__ void __launch_bounds__(C * 2) tail_fwd_kernel(
 // =============================================================================================
 // tail backward
 // =============================================================================================
-// DEFER: the sweep's row-scalar x row products (d v_raw = p_self dO, d o_c = p_c dO, the self-column terms and
+// DEFER = 1: the sweep's row-scalar x row products (d v_raw = p_self dO, d o_c = p_c dO, the self-column terms and
 // d lse_c) are left to the cell-end kernel, which forms them for all sweeps of the cell at once from the kept dO
 // rows; this kernel then only stashes (p_self, p_c, delta) per (row, head) in `dlsec_acc` = [3][rows] and touches
 // neither dks_acc, dv_acc, doc_acc nor v_raw / o_c.
-template <int DH, int C, bool DEFER>
+// DEFER = 2: only the raw-row gradients are left to the chunk-end kernel (d v_raw = sum p_self dO, d k_self = (sum dss) q):
+// dv_acc is not touched and `dks_acc` receives the stash [2][rows] = (p_self, dss); d q, d o_c, d lse_c as in mode 0.
+template <int DH, int C, int DEFER>
 __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
     const float* __restrict__ dO, const bf16* __restrict__ q, TView vq, const bf16* __restrict__ ks,
     TView vks, const bf16* __restrict__ vr, TView vvr, const bf16* __restrict__ Kin, TView vKin,
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
   const float delta0 = quad_dot_f32_bf16<DH>(dO0, o + orow0 * DH, t);
   const float delta1 = quad_dot_f32_bf16<DH>(dO1, o + orow1 * DH, t);
   float dss0 = 0.f, dss1 = 0.f;
-  if constexpr (DEFER) {
+  if constexpr (DEFER == 1) {
     if (t == 0) {
       const long long n_rows = (long long)gridDim.y * gridDim.z * C * H;
       dlsec_acc[orow0] = ps0; dlsec_acc[n_rows + orow0] = pc0; dlsec_acc[2 * n_rows + orow0] = delta0;
@@ -220,6 +222,11 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
     if (t == 0) {
       dlsec_acc[orow0] = (init_doc ? 0.f : dlsec_acc[orow0]) + pc0 * (doc0 - delta0);
       dlsec_acc[orow1] = (init_doc ? 0.f : dlsec_acc[orow1]) + pc1 * (doc1 - delta1);
+      if constexpr (DEFER == 2) {
+        const long long n_rows = (long long)gridDim.y * gridDim.z * C * H;
+        dks_acc[orow0] = ps0; dks_acc[n_rows + orow0] = dss0;
+        dks_acc[orow1] = ps1; dks_acc[n_rows + orow1] = dss1;
+      }
     }
   }
   load_tile_bf16<DH, NT>(sQ, q + b * vq.bs + hoff, vq.rs, C, tid);
@@ -289,7 +296,7 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
       }
     }
   }
-  if constexpr (DEFER) {
+  if constexpr (DEFER == 1) {
     float* dq0 = dq_acc + b * vdq.bs + i0 * vdq.rs + hoff;
     float* dq1 = dq_acc + b * vdq.bs + i1 * vdq.rs + hoff;
 #pragma unroll
@@ -327,18 +334,20 @@ __global__ void __launch_bounds__(C * 2, DH <= 64 ? 4 : 2) tail_bwd_kernel(
       x = init_dq ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dq1 + d);
       x.x += A[n][2] + dss1 * k1v.x; x.y += A[n][3] + dss1 * k1v.y;
       *reinterpret_cast<float2*>(dq1 + d) = x;
-      x = *reinterpret_cast<float2*>(dk0 + d);
-      x.x += dss0 * q0v.x; x.y += dss0 * q0v.y;
-      *reinterpret_cast<float2*>(dk0 + d) = x;
-      x = *reinterpret_cast<float2*>(dk1 + d);
-      x.x += dss1 * q1v.x; x.y += dss1 * q1v.y;
-      *reinterpret_cast<float2*>(dk1 + d) = x;
-      x = *reinterpret_cast<float2*>(dv0 + d);
-      x.x += ps0 * g0.x; x.y += ps0 * g0.y;
-      *reinterpret_cast<float2*>(dv0 + d) = x;
-      x = *reinterpret_cast<float2*>(dv1 + d);
-      x.x += ps1 * g1.x; x.y += ps1 * g1.y;
-      *reinterpret_cast<float2*>(dv1 + d) = x;
+      if constexpr (DEFER == 0) {
+        x = *reinterpret_cast<float2*>(dk0 + d);
+        x.x += dss0 * q0v.x; x.y += dss0 * q0v.y;
+        *reinterpret_cast<float2*>(dk0 + d) = x;
+        x = *reinterpret_cast<float2*>(dk1 + d);
+        x.x += dss1 * q1v.x; x.y += dss1 * q1v.y;
+        *reinterpret_cast<float2*>(dk1 + d) = x;
+        x = *reinterpret_cast<float2*>(dv0 + d);
+        x.x += ps0 * g0.x; x.y += ps0 * g0.y;
+        *reinterpret_cast<float2*>(dv0 + d) = x;
+        x = *reinterpret_cast<float2*>(dv1 + d);
+        x.x += ps1 * g1.x; x.y += ps1 * g1.y;
+        *reinterpret_cast<float2*>(dv1 + d) = x;
+      }
       x = init_doc ? make_float2(0.f, 0.f) : *reinterpret_cast<float2*>(dc0 + d);
       x.x += pc0 * g0.x; x.y += pc0 * g0.y;
       *reinterpret_cast<float2*>(dc0 + d) = x;
@@ -564,15 +573,22 @@ int dmb_tail_bwd(const float* dO, const void* q, TView vq, const void* ks, TView
                  int window, int G, int grow, int flags, cudaStream_t st) {
   DISPATCH_DH_C(dh, c, {
     size_t smem = ((size_t)4 * C * Tile<DH>::PITCH + (size_t)2 * C * (C + 8)) * sizeof(bf16);
-    if (flags & 4) {
-      auto kern = tail_bwd_kernel<DH, C, true>;
+    if (flags & 8) {
+      auto kern = tail_bwd_kernel<DH, C, 2>;
+      if (set_smem(kern, smem)) return -2;
+      kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
+                                              vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
+                                              lse_c, (const bf16*)o, lse, dq_acc, vdq, dks_acc, vdks, dv_acc, vdv,
+                                              doc_acc, dlsec_acc, dKin, dVin, vdkin, H, scale, window, grow, flags);
+    } else if (flags & 4) {
+      auto kern = tail_bwd_kernel<DH, C, 1>;
       if (set_smem(kern, smem)) return -2;
       kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
                                               vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,
                                               lse_c, (const bf16*)o, lse, dq_acc, vdq, dks_acc, vdks, dv_acc, vdv,
                                               doc_acc, dlsec_acc, dKin, dVin, vdkin, H, scale, window, grow, flags);
     } else {
-      auto kern = tail_bwd_kernel<DH, C, false>;
+      auto kern = tail_bwd_kernel<DH, C, 0>;
       if (set_smem(kern, smem)) return -2;
       kern<<<dim3(H, B, G), C * 2, smem, st>>>(dO, (const bf16*)q, vq, (const bf16*)ks, vks, (const bf16*)vr,
                                               vvr, (const bf16*)Kin, vKin, (const bf16*)Vin, vVin, o_c,

@@ -227,18 +227,30 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
   }
 }
 
-// End of a wavefront chunk's backward (every sweep of the chunk has been processed).  All arrays are indexed by
+// End of a wavefront chunk's backward (every sweep of the chunk has been processed).  The arrays are indexed by
 // absolute position and start at the chunk's first row (batch strides bs_vec / bs_sca).  The far read's
 // accumulated gradient (DOf, DLf) becomes what the prefix backward kernels consume: doc = DOf (compute dtype),
 // corr = DOf . o_f - DLf (also dense [B, R, H]), lsec = lse_f (also dense); the pending gradient of the rows the
 // chunk's first sweep read (its raw rows) moves into the raw-row gradients: dks += dKp, dv += dVp, dKp = dVp = 0.
+// With K > 0 the raw-row gradients of the chunk's K sweeps were deferred (tail backward, mode 2): sweep k left its
+// d o rows (sw.dO[k], batch stride sw.bs_vec[k]) and per-(row, head) scalars p_self (sw.ps[k]) and dss (sw.dss[k],
+// batch stride sw.bs_sca[k]); here dv += sum_k p_self,k dO_k and dks += (sum_k dss_k) q (q: the chunk's rotated
+// query rows, bf16 view).
+struct ChunkSweeps {
+  const float* dO[64];
+  const float* ps[64];
+  const float* dss[64];
+  long long bs_vec[64];
+  long long bs_sca[64];
+};
+
 template <int DH, typename TD>
 __global__ void __launch_bounds__(256) chunk_finish_kernel(
     const float* __restrict__ DOf, const float* __restrict__ DLf, const float* __restrict__ o_f,
     const float* __restrict__ lse_f, float* __restrict__ dKp, float* __restrict__ dVp, float* __restrict__ dks,
     float* __restrict__ dv, TD* __restrict__ doc, float* __restrict__ corr, float* __restrict__ lsec,
     float* __restrict__ corr_dense, float* __restrict__ lse_dense, long long bs_vec, long long bs_sca, int B, int R,
-    int H) {
+    int H, const __grid_constant__ ChunkSweeps sw, int K, const bf16* __restrict__ q, TView vq) {
   const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)B * R * H) return;
@@ -248,6 +260,18 @@ __global__ void __launch_bounds__(256) chunk_finish_kernel(
   const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
   const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
   constexpr int PER = DH / 32;
+  float av[PER], dss = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) av[e] = 0.f;
+  for (int k = K - 1; k >= 0; --k) {
+    const long long so = (long long)b * sw.bs_sca[k] + (long long)r * H + h;
+    const float* g_ = sw.dO[k] + (long long)b * sw.bs_vec[k] + ((long long)r * H + h) * DH;
+    const float ps = sw.ps[k][so];
+    dss += sw.dss[k][so];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) av[e] += ps * g_[lane + 32 * e];
+  }
+  const bf16* q_row = K > 0 ? q + b * vq.bs + r * vq.rs + (long long)h * DH : nullptr;
   float dot = 0.f;
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
@@ -255,8 +279,8 @@ __global__ void __launch_bounds__(256) chunk_finish_kernel(
     const float g = DOf[i];
     dot += g * o_f[i];
     doc[i] = cvt<TD>(g);
-    dks[i] += dKp[i];
-    dv[i] += dVp[i];
+    dks[i] += dKp[i] + (K > 0 ? dss * __bfloat162float(q_row[lane + 32 * e]) : 0.f);
+    dv[i] += dVp[i] + av[e];
     dKp[i] = 0.f;
     dVp[i] = 0.f;
   }
@@ -377,15 +401,28 @@ int dmb_cell_finish_sweeps(const float* const* dO_ptrs, int K, const float* scal
   return 0;
 }
 
+// sweeps: K (0..64) deferred sweeps; dO_ptrs / ps_ptrs / dss_ptrs and the two stride arrays have K entries (host)
 int dmb_wave_chunk_finish(const float* DOf, const float* DLf, const float* o_f, const float* lse_f, float* dKp,
                           float* dVp, float* dks, float* dv, void* doc, int doc_bf16, float* corr, float* lsec,
                           float* corr_dense, float* lse_dense, long long bs_vec, long long bs_sca, int B, int R, int H,
-                          int DH, cudaStream_t st) {
+                          int DH, int K, const float* const* dO_ptrs, const float* const* ps_ptrs,
+                          const float* const* dss_ptrs, const long long* sw_bs_vec, const long long* sw_bs_sca,
+                          const void* q, TView vq, cudaStream_t st) {
+  if (K < 0 || K > 64) return -1;
+  ChunkSweeps sw = {};
+  for (int k = 0; k < K; ++k) {
+    sw.dO[k] = dO_ptrs[k];
+    sw.ps[k] = ps_ptrs[k];
+    sw.dss[k] = dss_ptrs[k];
+    sw.bs_vec[k] = sw_bs_vec[k];
+    sw.bs_sca[k] = sw_bs_sca[k];
+  }
   const long long warps = (long long)B * R * H;
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
 #define GO(D, T)                                                                                                 \
   chunk_finish_kernel<D, T><<<blocks, 256, 0, st>>>(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, (T*)doc, corr, lsec, \
-                                                    corr_dense, lse_dense, bs_vec, bs_sca, B, R, H)
+                                                    corr_dense, lse_dense, bs_vec, bs_sca, B, R, H, sw, K,        \
+                                                    (const bf16*)q, vq)
   if (DH == 64) {
     if (doc_bf16) GO(64, bf16); else GO(64, float);
   } else if (DH == 128) {

@@ -74,7 +74,8 @@ class _Sigs:
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_cell_finish_sweeps = [_p, _i, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _f, _ll,
                               _ll, _i, _i, _i, _i, _p]
-    dmb_wave_chunk_finish = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_wave_chunk_finish = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _i, _p, _p,
+                             _p, _p, _p, _p, _v, _p]
     dmb_copy_pair = [_p, _p, _p, _p, _ll, _ll, _ll, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
@@ -717,24 +718,37 @@ class CudaOps(TorchOps):
                                              lsen.data_ptr(), o_f.stride(0), DLf.stride(0), B, R, h, dh,
                                              self._st()), "split_partials")
 
-    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec):
+    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps=None, q=None):
         B, R, h, dh = DOf.shape
         vec, sca = (DOf, o_f, dKp, dVp, dks, dv), (DLf, lse_f, corr, lsec)
+        sweeps = sweeps or []
         ok = (dh in (64, 128) and DOf.is_cuda and doc.dtype in (BF16, F32) and _dense_tail(doc, 2)
               and doc.stride(1) == h * dh
               and all(self._abs_view_ok(t, 2) and t.dtype == F32 for t in vec)
               and all(self._abs_view_ok(t, 1) and t.dtype == F32 for t in sca)
-              and len({t.stride(0) for t in vec + (doc,)}) == 1 and len({t.stride(0) for t in sca}) == 1)
+              and len({t.stride(0) for t in vec + (doc,)}) == 1 and len({t.stride(0) for t in sca}) == 1
+              and len(sweeps) <= 64
+              and all(self._abs_view_ok(g, 2) and g.shape == DOf.shape and self._abs_view_ok(ps, 1)
+                      and self._abs_view_ok(ds, 1) and ps.shape == DLf.shape and ps.stride(0) == ds.stride(0)
+                      for g, ps, ds in sweeps)
+              and (not sweeps or (q is not None and q.dtype == BF16 and _dense_tail(q, 2) and q.shape == DOf.shape)))
         if not ok:
             self._fell_back("chunk_finish")
-            return super().chunk_finish(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec)
+            return super().chunk_finish(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps, q)
         cv = torch.empty(B, R, h, dtype=F32, device=DOf.device)
         ls = torch.empty(B, R, h, dtype=F32, device=DOf.device)
-        self._ck(self.lib.dmb_wave_chunk_finish(DOf.data_ptr(), DLf.data_ptr(), o_f.data_ptr(), lse_f.data_ptr(),
-                                                dKp.data_ptr(), dVp.data_ptr(), dks.data_ptr(), dv.data_ptr(),
-                                                doc.data_ptr(), int(doc.dtype == BF16), corr.data_ptr(), lsec.data_ptr(),
-                                                cv.data_ptr(), ls.data_ptr(), DOf.stride(0), DLf.stride(0), B, R, h, dh,
-                                                self._st()), "chunk_finish")
+        K = len(sweeps)
+        arr = lambda ty, vals: ctypes.cast((ty * max(K, 1))(*vals), ctypes.c_void_p)
+        self._ck(self.lib.dmb_wave_chunk_finish(
+            DOf.data_ptr(), DLf.data_ptr(), o_f.data_ptr(), lse_f.data_ptr(), dKp.data_ptr(), dVp.data_ptr(),
+            dks.data_ptr(), dv.data_ptr(), doc.data_ptr(), int(doc.dtype == BF16), corr.data_ptr(), lsec.data_ptr(),
+            cv.data_ptr(), ls.data_ptr(), DOf.stride(0), DLf.stride(0), B, R, h, dh, K,
+            arr(ctypes.c_void_p, [g.data_ptr() for g, _, _ in sweeps]),
+            arr(ctypes.c_void_p, [ps.data_ptr() for _, ps, _ in sweeps]),
+            arr(ctypes.c_void_p, [ds.data_ptr() for _, _, ds in sweeps]),
+            arr(ctypes.c_longlong, [g.stride(0) for g, _, _ in sweeps]),
+            arr(ctypes.c_longlong, [ps.stride(0) for _, ps, _ in sweeps]),
+            q.data_ptr() if K else None, _tv(q) if K else TView(0, 0), self._st()), "chunk_finish")
         return cv, ls
 
     def copy_pair(self, d0, s0, d1, s1):
@@ -807,15 +821,18 @@ class CudaOps(TorchOps):
         return o, lse, ssq
 
     def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0, init=0, dkv_out=None):
-        ok = (self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in, dks_acc, dv_acc) and dO.dtype == F32
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0, init=0, dkv_out=None, raw_stash=None):
+        B, rows, h, dh = q_win.shape
+        raw_views = () if raw_stash is not None else (dks_acc, dv_acc)
+        ok = (self._win_ok(q_win, C, ks_win, vr_win, K_in, V_in, *raw_views) and dO.dtype == F32
               and all(t.is_contiguous() for t in (dO, o, o_c, lse_c, lse, doc_acc, dlsec_acc))
-              and _dense_tail(dq_acc, 2) and (dkv_out is None or self._dkv_view_ok(dkv_out)))
+              and _dense_tail(dq_acc, 2) and (dkv_out is None or self._dkv_view_ok(dkv_out))
+              and (raw_stash is None or (raw_stash.is_contiguous() and raw_stash.dtype == F32
+                                         and raw_stash.shape == (2, B, rows, h))))
         if not ok:
             self._fell_back("win_tail_bwd")
             return super().win_tail_bwd(dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                                        dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window, init, dkv_out)
-        B, rows, h, dh = q_win.shape
+                                        dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window, init, dkv_out, raw_stash)
         if dkv_out is not None:
             dK_in, dV_in = dkv_out
         else:
@@ -824,10 +841,13 @@ class CudaOps(TorchOps):
         self._ck(self.lib.dmb_tail_bwd(
             dO.data_ptr(), q_win.data_ptr(), _tv(q_win), ks_win.data_ptr(), _tv(ks_win), vr_win.data_ptr(),
             _tv(vr_win), K_in.data_ptr(), _tv(K_in), V_in.data_ptr(), _tv(V_in), o_c.data_ptr(),
-            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), _tv(dq_acc), dks_acc.data_ptr(),
-            _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc), doc_acc.data_ptr(), dlsec_acc.data_ptr(),
-            dK_in.data_ptr(), dV_in.data_ptr(), _tv(dK_in), B, C, h, dh, scale, window, rows // C, C, int(init),
-            self._st()), "win_tail_bwd")
+            lse_c.data_ptr(), o.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), _tv(dq_acc),
+            # raw-row gradients deferred (flag bit 3): the stash [2, B, rows, h] rides in the d k_self slot
+            *((raw_stash.data_ptr(), TView(0, 0), None, TView(0, 0)) if raw_stash is not None else
+              (dks_acc.data_ptr(), _tv(dks_acc), dv_acc.data_ptr(), _tv(dv_acc))),
+            doc_acc.data_ptr(), dlsec_acc.data_ptr(),
+            dK_in.data_ptr(), dV_in.data_ptr(), _tv(dK_in), B, C, h, dh, scale, window, rows // C, C,
+            int(init) | (8 if raw_stash is not None else 0), self._st()), "win_tail_bwd")
         return dK_in, dV_in
 
     def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):

@@ -126,7 +126,14 @@ class TorchOps:
         return tuple(torch.cat([t[i] for t in outs], 1) for i in range(3))
 
     def win_tail_bwd(self, dO, q_win, ks_win, vr_win, K_in, V_in, o_c, lse_c, o, lse, C, scale,
-                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0, init=0, dkv_out=None):
+                     dq_acc, dks_acc, dv_acc, doc_acc, dlsec_acc, window=0, init=0, dkv_out=None, raw_stash=None):
+        """`tail_bwd` for every chunk of a window.  With `raw_stash` [2, B, rows, h] the raw-row gradients are left to
+        `chunk_finish`: dks_acc / dv_acc are not touched and the stash receives (p_self, dss) per (row, head)."""
+        if raw_stash is not None:
+            ps, dss = fm.tail_self_scalars(dO, q_win, ks_win, vr_win, o, lse, scale)
+            raw_stash[0].copy_(ps)
+            raw_stash[1].copy_(dss)
+            dks_acc, dv_acc = torch.zeros_like(dO), torch.zeros_like(dO)        # discarded
         dKs, dVs = [], []
         for z in range(q_win.shape[1] // C):
             r = slice(z * C, (z + 1) * C)
@@ -183,11 +190,15 @@ class TorchOps:
             corrn_dense.copy_(corrn)
         lsen.copy_(lse_n)
 
-    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec):
+    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps=None, q=None):
         """End of a wavefront chunk's backward, all arguments views of the chunk's rows in per-layer arrays:
         the far read's accumulated gradient becomes the prefix kernels' inputs (doc = DOf, corr = DOf . o_f -
         DLf, lsec = lse_f) and the pending gradient of the chunk's raw rows moves out (dks += dKp, dv += dVp,
-        dKp = dVp = 0).  Returns contiguous copies of (corr, lse_f)."""
+        dKp = dVp = 0).  `sweeps`: (d o rows, p_self, dss) of every sweep of the chunk whose raw-row gradients
+        `win_tail_bwd` deferred: dv += sum p_self dO, dks += (sum dss) q.  Returns contiguous copies of (corr, lse_f)."""
+        for g, ps, dss in reversed(sweeps or []):
+            dv += ps.unsqueeze(-1) * g.float()
+            dks += dss.unsqueeze(-1) * q.float()
         cv = ((DOf * o_f).sum(-1) - DLf).contiguous()
         doc.copy_(DOf)
         corr.copy_(cv)

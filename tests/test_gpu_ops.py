@@ -316,6 +316,19 @@ def test_window_ops_match_per_chunk_statement(ops, dh, C, G, lo_chunk, K):
                                 lse_r, C, scale, accr[0], accr[1][:, w], accr[2][:, w], accr[3], accr[4])
     for a, b_, n_ in zip([dK, dV] + acc, [dKr, dVr] + accr, ("dK_in", "dV_in", "dq", "dks", "dv", "do_c", "dlse_c")):
         close(a, b_, rtol=3e-2, atol=3e-2, what=n_)
+    # the same launch with the raw-row gradients deferred: d k_self / d v_raw untouched, (p_self, dss) stashed
+    acc2 = [z(B, G * C, H, dh), torch.full((B, T, H, dh), 3.0, device=DEV), torch.full((B, T, H, dh), 5.0, device=DEV),
+            z(B, G * C, H, dh), z(B, G * C, H)]
+    stash = torch.empty(2, B, G * C, H, device=DEV)
+    dK2, dV2 = ops.win_tail_bwd(dO, q[:, w], ks[:, w], vr[:, w], Kc[:, w], Vc[:, w], o_c, lse_c, o_r.to(torch.bfloat16),
+                                lse_r, C, scale, acc2[0], acc2[1][:, w], acc2[2][:, w], acc2[3], acc2[4], raw_stash=stash)
+    ps_r, dss_r = fm.tail_self_scalars(dO, f(q[:, w]), f(ks[:, w]), f(vr[:, w]), o_r, lse_r, scale)
+    close(stash[0], ps_r, rtol=3e-2, atol=1e-3, what="stash p_self")
+    close(stash[1], dss_r, rtol=3e-2, atol=3e-2, what="stash dss")
+    assert (acc2[1] == 3.0).all() and (acc2[2] == 5.0).all()
+    for a, b_, n_ in zip([dK2, dV2, acc2[0], acc2[3], acc2[4]], [dKr, dVr, accr[0], accr[3], accr[4]],
+                         ("dK_in", "dV_in", "dq", "do_c", "dlse_c")):
+        close(a, b_, rtol=3e-2, atol=3e-2, what=n_ + " (raw deferred)")
     # split + near backward (query side and key side)
     DOf, DLf = z(B, T, H, dh), z(B, T, H)
     docn, corrn, lsen = torch.zeros(B, T, H, dh, device=DEV, dtype=torch.bfloat16), z(B, T, H), z(B, T, H)
@@ -392,6 +405,19 @@ def test_chunk_finish(ops, dh, doc_dtype):
     out[r] = False
     for x, y, n_ in zip(a, before, names):                       # rows of other chunks are untouched
         assert torch.equal(x[:, out], y[:, out]), n_
+    # with the raw-row gradients of three sweeps deferred to this kernel (views into windows of different widths)
+    a, b_ = arrays(), arrays()
+    q = rnd(B, T, H, dh, seed=30)
+    sweeps = []
+    for k, (G, g) in enumerate(((3, 2), (2, 0), (1, 0))):
+        d_o, st = f(B, G * c, H, dh, seed=40 + k), f(2, B, G * c, H, seed=50 + k)
+        gr = slice(g * c, (g + 1) * c)
+        sweeps.append((d_o[:, gr], st[0][:, gr], st[1][:, gr]))
+    cv, ls = ops.chunk_finish(*[t[:, r] for t in a], sweeps=sweeps, q=q[:, r])
+    cr, lr = REF.chunk_finish(*[t[:, r] for t in b_], sweeps=sweeps, q=q[:, r])
+    close(cv, cr, rtol=1e-4, atol=1e-4, what="corr (sweeps)")
+    for x, y, n_ in zip(a, b_, names):
+        close(x, y, rtol=1e-2, atol=1e-4, what=n_ + " (sweeps)")
 
 
 def test_copy_pair(ops):
