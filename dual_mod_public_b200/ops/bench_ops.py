@@ -195,27 +195,36 @@ def main():
         lg, tg = rnd(4096, 32000), torch.randint(0, 32000, (4096,), device=DEV)
         inv = torch.tensor(1.0 / 4096, device=DEV)
         report("ce slab 4096x32000", T(lambda: ops.ce_chunk(lg, tg, inv)), bytes_=4096 * 32000 * 2 * 2)
-    # ---- GEMMs: ours vs torch.matmul (cuBLAS)
+    # ---- GEMMs: ours (128 x BN tiles per CTA, and 256 x 256 tiles on CTA pairs) vs torch.matmul (cuBLAS)
     if want("gemm") and ops.gemm is not None:
         g = ops.gemm
+
+        def trio(name, fn, ref, flops):
+            for tag_, flag in (("1 CTA", False), ("CTA pair", True)):
+                g.pair = flag
+                report(f"gemm {name} [{tag_}]", T(fn), flops=flops)
+            g.pair = False
+            report(f"  cublas {name}", T(ref), flops=flops)
+
         shapes = [("sweep y=uW^T", 2048, 4096, 1024), ("qkv", 65536, 1024, 1024), ("mlp up", 65536, 2816, 1024),
                   ("mlp down", 65536, 1024, 2816), ("head", 4096, 32000, 1024)]
         for name, M, Nn, K in shapes:
             a, wt = rnd(M, K), rnd(Nn, K)
-            f = 2.0 * M * Nn * K
-            report(f"gemm tn {name}", T(lambda: g.linear(a, wt)), flops=f)
-            report(f"  cublas {name}", T(lambda: a @ wt.t()), flops=f)
+            trio("tn " + name, lambda: g.linear(a, wt), lambda: a @ wt.t(), 2.0 * M * Nn * K)
         dy, wt = rnd(2048, 4096), rnd(4096, 1024)
         f = 2.0 * 2048 * 4096 * 1024
-        report("gemm nn sweep du", T(lambda: g.linear_dx(dy, wt)), flops=f)
-        report("  cublas sweep du", T(lambda: dy @ wt), flops=f)
+        trio("nn sweep du", lambda: g.linear_dx(dy, wt), lambda: dy @ wt, f)
+        dyl, wl = rnd(65536, 2816), rnd(2816, 1024)
+        trio("nn layer dx", lambda: g.linear_dx(dyl, wl), lambda: dyl @ wl, 2.0 * 65536 * 2816 * 1024)
         dW, xx = z(4096, 1024), rnd(2048, 1024)
-        report("gemm dw sweep", T(lambda: g.linear_dw_acc(dW, dy, xx)), flops=f)
-        report("  cublas dw sweep", T(lambda: dW.add_(torch.mm(dy.t(), xx, out_dtype=torch.float32))), flops=f)
+        trio("dw sweep", lambda: g.linear_dw_acc(dW, dy, xx),
+             lambda: dW.add_(torch.mm(dy.t(), xx, out_dtype=torch.float32)), f)
         dyb, xb, dWb = rnd(65536, 1024), rnd(65536, 1024), z(1024, 1024)
-        fb = 2.0 * 65536 * 1024 * 1024
-        report("gemm dw layer", T(lambda: g.linear_dw_acc(dWb, dyb, xb)), flops=fb)
-        report("  cublas dw layer", T(lambda: dWb.add_(torch.mm(dyb.t(), xb, out_dtype=torch.float32))), flops=fb)
+        trio("dw layer", lambda: g.linear_dw_acc(dWb, dyb, xb),
+             lambda: dWb.add_(torch.mm(dyb.t(), xb, out_dtype=torch.float32)), 2.0 * 65536 * 1024 * 1024)
+        dyp, xp, dWp = rnd(262144, 4096), rnd(262144, 1024), z(4096, 1024)
+        trio("dw packed (262144 rows)", lambda: g.linear_dw_acc(dWp, dyp, xp),
+             lambda: dWp.add_(torch.mm(dyp.t(), xp, out_dtype=torch.float32)), 2.0 * 262144 * 4096 * 1024)
         g.check()
     # ---- the skinny GEMMs of the rank-144 factored write law (18 x d2304 recipe: 8192 window rows per step)
     if want("gemm_lora") and ops.gemm is not None:

@@ -9,6 +9,7 @@ needs, each in the operand layout it naturally has, so no transposes are materia
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -41,6 +42,10 @@ class Tcgen05Gemm:
         p, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         lib.dmb_gemm_bf16.restype = i
         lib.dmb_gemm_bf16.argtypes = [p, p, p, p, i, i, i, ll, ll, ll, i, i, i, i, p, p]
+        lib.dmb_gemm_bf16_pair.restype = i
+        lib.dmb_gemm_bf16_pair.argtypes = lib.dmb_gemm_bf16.argtypes
+        # 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) for problems with enough rows and columns
+        self.pair = os.environ.get("DMB_GEMM_PAIR", "0") == "1"
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         # probe: fails here (not mid-step) if the driver entry point for tensor maps is missing
         a = torch.zeros(128, 64, dtype=BF16, device=self.device)
@@ -54,7 +59,8 @@ class Tcgen05Gemm:
 
     def _call(self, A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, acc):
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        rc = self.lib.dmb_gemm_bf16(A.data_ptr(), B.data_ptr(), C.data_ptr(),
+        fn = self.lib.dmb_gemm_bf16_pair if (self.pair and M >= 512 and N >= 192) else self.lib.dmb_gemm_bf16
+        rc = fn(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                     bias.data_ptr() if bias is not None else None, M, N, K, lda, ldb, ldc,
                                     a_mn, b_mn, out_f32, acc, self.err.data_ptr(), st)
         if rc != 0:
