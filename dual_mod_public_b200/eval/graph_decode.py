@@ -12,6 +12,13 @@ plain-torch path masks instead and is what runs on CPU).  With the modulation of
 (`attn_mode="vanilla"`) the same class is a plain KV-cache Transformer decoder: the
 Transformer++ control.
 
+On a B200 the rest of the step runs on the training engines' kernels and weight packs as well
+(`fused=True`, the default there for the write laws with fused refine kernels): RMSNorm as one kernel, one
+input GEMM for q, k, v and the gates' x-logits, RoPE at the device-side position, the read (which also returns
+the per-head sum of squares the write law's norm needs), the packed context GEMM with the norm gain folded into
+its columns, one refine kernel for gates, blend and rotation, SwiGLU as one kernel: about twenty launches per
+layer instead of about seventy-five small framework kernels.
+
 Reference parity: `GraphDecoder` (lm/eval/graph_decode.py:15-125): static buffers,
 device-side `pos`, `capture / reset / step / generate(prompt, max_new, eos_id, stop_fn)`.
 """
@@ -25,8 +32,25 @@ import torch
 from ..models.rope import apply_rope
 
 
+class _Bag:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+class _DecodeRefine:
+    """The training engine's fused write law (`WaveScanEngine._refine_fwd`: packed context GEMM, dense or factored,
+    and the refine kernels of the packed and mult_res families) applied to the one row per sequence of a decode step."""
+
+    def __init__(self, ops, cfg, family, B):
+        self.ops, self.cfg, self.family, self.B = ops, cfg, family, B
+
+    from ..engines.wavescan import WaveScanEngine as _E
+    _refine_fwd, _pack_linear, _vctx_linear = _E._refine_fwd, _E._pack_linear, _E._vctx_linear
+    del _E
+
+
 class GraphDecoder:
-    def __init__(self, model, B, P_max, dtype=torch.bfloat16, use_kernel=None, cast_weights=True):
+    def __init__(self, model, B, P_max, dtype=torch.bfloat16, use_kernel=None, cast_weights=True, fused=None):
         self.dev = next(model.parameters()).device
         if (cast_weights and dtype == torch.bfloat16 and self.dev.type == "cuda"
                 and next(model.parameters()).dtype == torch.float32):
@@ -61,18 +85,48 @@ class GraphDecoder:
             self.lib = load_library()
             p, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
             self.lib.dmb_decode_attend.restype = i
-            self.lib.dmb_decode_attend.argtypes = [p, p, p, p, p, p, p, i, i, i, i, f, i, p]
+            self.lib.dmb_decode_attend.argtypes = [p, p, p, p, p, p, p, p, i, i, i, i, f, i, p]
+        # the whole step on the engines' kernels and weight packs (see the module docstring)
+        self.fused = False
+        if self.use_kernel and fused is not False:
+            from ..engines.wavescan import _LayerPack, fused_supported, refine_family
+            cfg = model.cfg
+            fam = refine_family(cfg) if cfg.attn_mode != "vanilla" and fused_supported(cfg) else None
+            plain = cfg.attn_mode == "vanilla" and cfg.v_norm == "none"
+            if fam in ("packed", "mrk") or plain:
+                from ..ops import default_ops
+                self.ops, self.family = default_ops(self.dev), fam
+                self.packs = []
+                for blk in self.m.blocks:
+                    if fam:
+                        P = _LayerPack(blk, cfg, dtype, self.dev, family=fam)
+                        P.pack(blk, cfg)
+                    else:                                   # plain KV cache: q, k, v as one input GEMM
+                        a, c_ = blk.attn, (lambda w: w.detach().to(dtype).contiguous())
+                        P = _Bag(w_an=c_(blk.attn_norm.weight), w_mn=c_(blk.mlp_norm.weight), b_in=None,
+                                 W_in=torch.cat([c_(a.wq.weight), c_(a.wk.weight), c_(a.wv.weight)], 0),
+                                 wo=c_(a.wo.weight), w1=c_(blk.mlp.w1.weight), w3=c_(blk.mlp.w3.weight),
+                                 w2=c_(blk.mlp.w2.weight))
+                    self.packs.append(P)
+                self.refine = _DecodeRefine(self.ops, cfg, fam, B) if fam else None
+                # the kernels read fp32 rotation tables (a model converted with .bfloat16() carries bf16 ones)
+                self.cos32, self.sin32 = self.m.rope_cos.float().contiguous(), self.m.rope_sin.float().contiguous()
+                self.fused = True
+        if fused and not self.fused:
+            raise ValueError("fused decode needs the kernel read and a write law with fused refine kernels")
 
     # ---- the read ---------------------------------------------------------------------------
-    def _read(self, attn, q_r, k_r, v, l):
-        """q_r, k_r, v: [B, h, dh] (rotated query, rotated RAW self key, RAW self value)."""
+    def _read(self, attn, q_r, k_r, v, l, ssq=None):
+        """q_r, k_r, v: [B, h, dh] (rotated query, rotated RAW self key, RAW self value); `ssq` (kernel path):
+        [B, h] fp32 that receives the sum of squares of every head's read."""
         Kb, Vb = self.K[l], self.V[l]
         if self.use_kernel:
+            assert q_r.is_contiguous() and k_r.is_contiguous() and v.is_contiguous()
             out = torch.empty_like(q_r)
             st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
             rc = self.lib.dmb_decode_attend(q_r.data_ptr(), k_r.data_ptr(), v.data_ptr(), Kb.data_ptr(), Vb.data_ptr(),
-                                            self.pos32.data_ptr(), out.data_ptr(), self.B, self.P, self.h, self.dh,
-                                            attn.scale, self.window, st)
+                                            self.pos32.data_ptr(), out.data_ptr(), ssq.data_ptr() if ssq is not None else None,
+                                            self.B, self.P, self.h, self.dh, attn.scale, self.window, st)
             if rc != 0:
                 raise RuntimeError(f"decode read failed ({rc})")
             self.kernel_launches += 1
@@ -100,13 +154,42 @@ class GraphDecoder:
         self.V[l].index_copy_(1, self.pos, vpp.view(B, 1, h, dh).to(self.dt))
         return attn.wo(o_cat)
 
+    def _fused_layer(self, blk, l, x, cos_p, sin_p):
+        """One layer of the step on the engines' kernels: x [B, 1, d] in the decode dtype -> the layer's output."""
+        ops, P, cfg = self.ops, self.packs[l], self.m.cfg
+        B, h, dh, d = self.B, self.h, self.dh, self.h * self.dh
+        xhat, _ = ops.rms_fwd(x, P.w_an)
+        qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
+        k, v = qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d]
+        q_r = ops.rope(qkvg[..., :d].unflatten(-1, (h, dh)), cos_p, sin_p)            # [B, 1, h, dh]
+        kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos_p, sin_p)
+        ssq = torch.empty(B, 1, h, dtype=torch.float32, device=self.dev) if self.refine else None
+        o = self._read(blk.attn, q_r.view(B, h, dh), kself_r.view(B, h, dh), v.reshape(B, h, dh).contiguous(), l, ssq)
+        if self.refine is not None:
+            S = _Bag(P=P, k=k, v=v, glx=qkvg[..., 3 * d:5 * d], vgx=qkvg[..., 5 * d:] if self.family == "mrk" else None,
+                     cos=cos_p, sin=sin_p, pin=cfg.kmod_vraw_heads * dh)
+            K_new, V_new, _ = self.refine._refine_fwd(S, slice(0, 1), o.view(B, 1, h, dh), ssq)
+        else:                                                                        # plain KV cache
+            K_new, V_new = kself_r, v.unflatten(-1, (h, dh))
+        self.K[l].index_copy_(1, self.pos, K_new)
+        self.V[l].index_copy_(1, self.pos, V_new)
+        x_mid = x + ops.linear(o.view(B, 1, d), P.wo)
+        xn, _ = ops.rms_fwd(x_mid, P.w_mn)
+        g = ops.swiglu_fwd(ops.linear(xn, P.w1), ops.linear(xn, P.w3))
+        return x_mid + ops.linear(g, P.w2)
+
     def _decode_token(self):
         """One token through every layer at the device-side position; leaves the fp32 logits and the
         arg-max in the static outputs and advances the position counters."""
         model, at = self.m, self.pos
         cos_p, sin_p = model.rope_cos.index_select(0, at), model.rope_sin.index_select(0, at)
         stream = model.tok_emb(self.tok)
+        if self.fused:
+            cos_f, sin_f = self.cos32.index_select(0, at), self.sin32.index_select(0, at)
         for l, blk in enumerate(model.blocks):
+            if self.fused:
+                stream = self._fused_layer(blk, l, stream.to(self.dt), cos_f, sin_f)
+                continue
             stream = stream + self._attn(blk.attn, blk.attn_norm(stream), l, cos_p, sin_p)
             stream = stream + blk.mlp(blk.mlp_norm(stream))
         scores = model.lm_head(model.norm_f(stream)).float()

@@ -2,6 +2,7 @@
 
   python -m dual_mod_public_b200.ops.bench_ops                 # every op
   python -m dual_mod_public_b200.ops.bench_ops --only tail_bwd --iters 3 --no-flush   # for a profiler
+  python -m dual_mod_public_b200.ops.bench_ops --only tail_fwd,refine_bwd             # several ops (substrings)
 
 Each op is timed with CUDA events on the launching stream after warm-up; between timed
 iterations a 512 MB buffer is written twice, so inputs come from HBM, not from the 126 MB L2, and the
@@ -92,7 +93,7 @@ def main():
         print(msg, flush=True)
         rows.append((name, us))
 
-    want = lambda n: not args.only or args.only in n
+    want = lambda n: not args.only or any(o and o in n for o in args.only.split(","))
     # ---- cell tensors
     q, ks, vr = rnd(B, Tlen, h, dh), rnd(B, Tlen, h, dh), rnd(B, Tlen, h, dh)
     Kc, Vc = rnd(B, Tlen, h, dh), rnd(B, Tlen, h, dh)
@@ -184,6 +185,36 @@ def main():
                bytes_=N * d * 68)
         du = rnd(B, c, d)
         report("rmsn_bwd", T(lambda: ops.rmsn_bwd(du, o2, ssq)), bytes_=N * d * 8)
+    if want("chain"):
+        # one forward sweep (tail read -> packed GEMM -> refine) and one backward sweep (refine -> GEMM -> norm -> tail)
+        # as their launches follow one another in a replayed CUDA graph of 16 sweeps, against the sum of the parts
+        Wp = rnd(4 * d, d, scale=0.03)
+        o2 = o.reshape(B, c, d)
+        dcg_o, uh_o = torch.empty_like(cg), rnd(B, c, d)
+        scal = torch.empty(3, B, c, h, device=DEV)
+
+        def fwd_sweep():
+            o_, lse_, ssq_ = ops.tail_fwd(qc, ksc, vrc, K_in, V_in, o_c, lse_c, scale, 0)
+            raw = ops.linear(o_.reshape(B, c, d), Wp)
+            ops.refine_fwd(raw, ssq_, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, 0)
+
+        def bwd_sweep():
+            ops.refine_bwd(dK, dV, cg, ssq, o2, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], 0, dk_a[:, r], dv_a[:, r],
+                           None, dcg_o, uh_o)
+            du_ = ops.linear_dx(dcg_o, Wp)
+            d_o = ops.rmsn_bwd(du_, o2, ssq)
+            ops.tail_bwd_sweep(d_o.view(B, c, h, dh), qc, ksc, K_in, V_in, lse_c, o, lse, scale, 0, acc[0], False, scal)
+
+        for name, fn, n_k in (("forward sweep chain (3 launches)", fwd_sweep, 3), ("backward sweep chain (4 launches)", bwd_sweep, 4)):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for _ in range(16):
+                    fn()
+            us = T(gr.replay) / 16
+            report(name + ", per sweep in a graph", us)
     x2, w = rnd(N, d), rnd(d) + 1
     if want("rms_fwd"):
         report("rms_fwd", T(lambda: ops.rms_fwd(x2, w)), bytes_=N * d * 4)

@@ -15,12 +15,13 @@ template <int DH>
 __global__ void __launch_bounds__(DEC_WARPS * 32) decode_attend_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ kself, const bf16* __restrict__ vself,
     const bf16* __restrict__ K, const bf16* __restrict__ V, const int* __restrict__ pos_ptr,
-    bf16* __restrict__ out, int P, int H, float scale, int window) {
+    bf16* __restrict__ out, float* __restrict__ ssq, int P, int H, float scale, int window) {
   constexpr int LPK = DH / 8;        // lanes per key (each lane owns 8 contiguous dims)
   constexpr int KPW = 32 / LPK;      // keys per warp step
   constexpr int NW = DEC_WARPS;
   __shared__ float s_m[NW * KPW], s_l[NW * KPW];
   __shared__ float s_acc[NW * KPW][DH];
+  __shared__ float s_sq[DH / 32];
   const int h = blockIdx.x, b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = lane / LPK, sub = lane % LPK;
@@ -97,7 +98,22 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_attend_kernel(
       Z += w * s_l[s];
       o += w * s_acc[s][t];
     }
-    out[so + t] = __float2bfloat16(o / Z);
+    const float val = o / Z;
+    out[so + t] = __float2bfloat16(val);
+    if (ssq) {                                     // sum of squares of the head's read (the row norm of the write law)
+      float sq = val * val;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+      if (lane == 0) s_sq[warp] = sq;
+    }
+  }
+  if (ssq) {
+    __syncthreads();
+    if (t == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < DH / 32; ++w) tot += s_sq[w];
+      ssq[(long long)b * H + h] = tot;
+    }
   }
 }
 
@@ -105,15 +121,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_attend_kernel(
 
 extern "C" {
 
-// q, kself, vself, out: [B, H, DH] bf16 contiguous; K, V: [B, P, H, DH] bf16 contiguous.
+// q, kself, vself, out: [B, H, DH] bf16 contiguous; K, V: [B, P, H, DH] bf16 contiguous; ssq: optional [B, H] fp32
+// (sum over the head's dims of out^2).
 int dmb_decode_attend(const void* q, const void* kself, const void* vself, const void* K, const void* V,
-                      const int* pos_ptr, void* out, int B, int P, int H, int dh, float scale, int window,
+                      const int* pos_ptr, void* out, float* ssq, int B, int P, int H, int dh, float scale, int window,
                       cudaStream_t st) {
   dim3 grid(H, B);
   if (dh == 64)
-    decode_attend_kernel<64><<<grid, DEC_WARPS * 32, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, P, H, scale, window);
+    decode_attend_kernel<64><<<grid, DEC_WARPS * 32, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, ssq, P, H, scale, window);
   else if (dh == 128)
-    decode_attend_kernel<128><<<grid, DEC_WARPS * 32, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, P, H, scale, window);
+    decode_attend_kernel<128><<<grid, DEC_WARPS * 32, 0, st>>>((const bf16*)q, (const bf16*)kself, (const bf16*)vself, (const bf16*)K, (const bf16*)V, pos_ptr, (bf16*)out, ssq, P, H, scale, window);
   else
     return -1;
   DMB_CHECK_LAUNCH();

@@ -284,7 +284,7 @@ class CudaOps(TorchOps):
     def mrk_refine_fwd(self, raw, vc, ssq, glx, k, v, cos, sin, h, pin_cols, k_gain, tau, out=None):
         B, c, d = k.shape
         dh = d // h
-        ok = (self._mrk_ok(k, raw, glx, v) and vc.dtype == BF16 and vc.is_contiguous() and cos.is_contiguous()
+        ok = (self._mrk_ok(k, raw, glx, v) and vc.dtype == BF16 and vc.is_contiguous() and cos.is_contiguous() and cos.dtype == F32 and sin.dtype == F32
               and ssq.is_contiguous() and k_gain.dtype == F32 and dh % 16 == 0)
         if not ok:
             self._fell_back("mrk_refine_fwd")
@@ -317,7 +317,7 @@ class CudaOps(TorchOps):
               and _dense_tail(dK_out, 2) and dK_out.stride() == dV_out.stride() and ssq.is_contiguous()
               and all(t.is_contiguous() and t.dtype == BF16 for t in (dcg_out, uhat_out, dvc_out))
               and dkg_out.is_contiguous() and dkg_out.dtype == F32 and k_gain.dtype == F32
-              and dh % 16 == 0)
+              and cos.is_contiguous() and cos.dtype == F32 and sin.dtype == F32 and dh % 16 == 0)
         if not ok:
             self._fell_back("mrk_refine_bwd")
             return super().mrk_refine_bwd(dK_out, dV_out, raw, vc, ssq, o, glx, k, v, cos, sin, pin_cols, k_gain, tau,
@@ -335,7 +335,8 @@ class CudaOps(TorchOps):
     # ---- rope -----------------------------------------------------------------------------------------
     def _rope(self, x, cos, sin, sign, out_dtype):
         B, T, H, DH = x.shape
-        if x.dtype not in (BF16, F32) or not _dense_tail(x, 2) or not cos.is_contiguous():
+        if (x.dtype not in (BF16, F32) or not _dense_tail(x, 2) or not cos.is_contiguous() or not sin.is_contiguous()
+                or cos.dtype != F32 or sin.dtype != F32):
             return None
         out = torch.empty(B, T, H, DH, dtype=out_dtype, device=x.device)
         self._ck(self.lib.dmb_rope(x.data_ptr(), int(x.dtype == F32), x.stride(0), x.stride(1),
@@ -853,7 +854,7 @@ class CudaOps(TorchOps):
     def refine_fwd(self, raw, ssq, glx, k, v, cos, sin, h, pin_cols=0, out=None):
         B, c, d = k.shape
         dh = d // h
-        ok = (k.dtype == BF16 and raw.dtype == BF16 and raw.is_contiguous() and cos.is_contiguous()
+        ok = (k.dtype == BF16 and raw.dtype == BF16 and raw.is_contiguous() and cos.is_contiguous() and cos.dtype == F32 and sin.dtype == F32
               and ssq.is_contiguous() and dh % 16 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v)))
         if not ok:
@@ -882,7 +883,7 @@ class CudaOps(TorchOps):
         dh = d // h
         ok = (k.dtype == BF16 and raw.dtype == BF16 and o.dtype == BF16 and dK_out.dtype == F32
               and dV_out.dtype == F32 and _dense_tail(dK_out, 2) and dK_out.stride() == dV_out.stride()
-              and raw.is_contiguous() and o.is_contiguous() and ssq.is_contiguous() and cos.is_contiguous()
+              and raw.is_contiguous() and o.is_contiguous() and ssq.is_contiguous() and cos.is_contiguous() and cos.dtype == F32 and sin.dtype == F32
               and dcg_out.is_contiguous() and uhat_out.is_contiguous() and dcg_out.dtype == BF16
               and dh % 16 == 0
               and all(_dense_tail(t, 1) for t in (glx, k, v, dk_acc, dv_acc))
