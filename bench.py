@@ -183,6 +183,17 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     if hasattr(tr.opt, "check_status"):
         tr.opt.check_status()
+    overlap = None
+    if getattr(args, "overlap_trace", False) and world > 1 and getattr(tr, "overlap", False):
+        ov = tr.trace_overlap(host[0])
+        worst = torch.tensor([ov["reduce_exposed"], ov["step_kernel"]], device=dev[0].device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        overlap = {"last_micro_batch_ms": round(ov["backward_end"], 2),
+                   "buckets": len(ov["buckets"]), "reduce_kernels_ms": round(ov["reduce_total"], 3),
+                   "first_bucket_start_ms": round(min(s_ for _, s_, _ in ov["buckets"]), 2),
+                   "last_bucket_end_ms": round(max(e_ for _, _, e_ in ov["buckets"]), 2),
+                   "exposed_after_backward_ms_max_over_ranks": round(float(worst[0]), 3),
+                   "fused_step_kernel_ms_max_over_ranks": round(float(worst[1]), 3)}
     flat = [tr.opt.flat_params] if hasattr(tr.opt, "flat_params") else list(tr.model.parameters())
     checksum, identical = params_checksum(torch, dist, world, flat)
     tokens = GLOBAL_SEQS * SEQ
@@ -210,6 +221,8 @@ def run_ours(args):
                "gpu_launches": int(launches), "torch_fallbacks": dict(getattr(ops, "fallbacks", {})),
                "clocks": clocks,
                "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}
+        if overlap is not None:
+            out["overlap"] = overlap
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
@@ -539,6 +552,9 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("DMB_MICRO_BATCH", 32)))
     ap.add_argument("--optimizer", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--overlap-trace", action="store_true",
+                    help="N > 1: after the timed steps, one more step with CUDA events around the gradient exchange; "
+                         "its timeline is added to the JSON line under \"overlap\"")
     ap.add_argument("--config", default="340m", choices=["340m", "1p3b", "hero", "d960", "cpu_scan"],
                     help="340m: 24L d1024 wavescan c=64 K=4 at 256 x 2048 tokens per step (the headline); "
                          "1p3b: 24L d2048 16x128 ffn5632 wavefront engine c=64 at 256 x 4096 tokens per step; "

@@ -14,8 +14,8 @@ The model counts, per micro-batch of B sequences of T tokens and per layer:
   attention     committed-prefix read of every chunk (T^2 / 2 keys per query overall) and the intra-chunk tail of
                 every sweep; backward 2.5x forward.  Tensor-core FLOPs, but these kernels are `mma.sync` code.
   pointwise     bytes moved by the refine chain (forward ~20 B, backward ~68 B per row element and sweep), the
-                tail kernels' fp32 accumulators (~66 B per row element and sweep in the backward), norms, RoPE,
-                SwiGLU and the cross-entropy slabs.
+                tail backward (~30 B per row element and sweep, plus the cell-end sums over the sweeps' kept d o:
+                ~15 B per sweep + 45 B per cell), norms, RoPE, SwiGLU and the cross-entropy slabs.
   head          unembedding GEMM forward + input / weight gradients.
 
 Times: FLOPs over the sustained bf16 GEMM rate, bytes over the copy bandwidth, both from MEASURED_PEAKS.json
@@ -50,7 +50,9 @@ def model(d=1024, heads=16, ffn=2816, vocab=32000, layers=24, T=2048, B=32, seqs
     att_fwd = 4.0 * B * heads * dh * (T * T / 2 + K * T * c / 2)
     att = att_fwd * 3.5                                      # forward + 2.5x backward
     elem = N * d
-    pointwise = elem * K * (20 + 68 + 66 + 24)               # refine fwd / bwd, tail backward accumulators, tail forward
+    # refine fwd / bwd, tail backward (per sweep: tiles in, d q read-modify-write, dK_in / dV_in out), tail forward;
+    # once per cell: the row-scalar sums over the sweeps' kept d o (d v_raw, d k_self, d o_c)
+    pointwise = elem * (K * (20 + 68 + 30 + 24) + 15 * K + 45)
     pointwise += elem * (2 * 4 * 4 + 6 * 2 * 3) + N * ffn * 2 * 9    # norms, RoPE, residual adds; SwiGLU fwd + bwd
     ce = N * vocab * 2 * 2
     per_micro = {

@@ -74,6 +74,7 @@ class Trainer:
                         and self.rank_outlier is None)
         self._side = torch.cuda.Stream(device=self.device) if self.overlap else None
         self._last_micro = False
+        self.trace = None                      # set by `trace_overlap`: CUDA events of one step's gradient exchange
         kw = dict(engine_kwargs or {})
         common_e = dict(device=self.device, autocast_bf16=autocast_bf16, use_graphs=use_graphs,
                         grads=self.opt.grad_buffers(),
@@ -100,7 +101,56 @@ class Trainer:
         b = 0 if li < 0 else 1 + (self.cfg.n_layers - 1 - li)
         cur = torch.cuda.current_stream(self.device)
         self._side.wait_stream(cur)
+        if self.trace is not None:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev[0].record(self._side)
+            self.opt.bucket_ready(b, stream=self._side)
+            ev[1].record(self._side)
+            self.trace["buckets"].append((b, ev[0], ev[1]))
+            return
         self.opt.bucket_ready(b, stream=self._side)
+
+    def trace_overlap(self, tokens, sid=0, lr=None):
+        """One optimizer step with CUDA events around the last micro-batch's backward, every bucket's early
+        reduce-scatter (second stream) and the fused optimizer step.  Returns a dict of milliseconds relative to
+        the start of the last micro-batch: `backward_end`, `buckets` = [(bucket, start, end)], `wait_start` (the main
+        stream starts waiting for the second stream), `opt_start`, `opt_end`, and the derived `reduce_total`
+        (sum of the buckets' kernel times), `reduce_exposed` (time the main stream waited for the last buckets
+        after its own backward was done) and `step_kernel` (the fused optimizer kernel)."""
+        if not self.overlap:
+            raise RuntimeError("no early buckets in this configuration (one rank, NCCL optimizer or per-rank rejection)")
+        E = lambda: torch.cuda.Event(enable_timing=True)
+        cur = torch.cuda.current_stream(self.device)
+        mb, T = self.micro_batch, self.T
+        self.opt.zero_grad()
+        self._loss_acc.zero_()
+        for a in range(self.accum):
+            blk = tokens[a * mb:(a + 1) * mb].to(self.device, non_blocking=True)
+            self._last_micro = a == self.accum - 1
+            if self._last_micro:
+                self.trace = {"buckets": []}
+                t0 = E()
+                t0.record(cur)
+            self._loss_acc += self.engine.train_step(blk[:, :T], blk[:, 1:T + 1], sid=sid)
+        t_bwd, t_wait, t_opt0, t_opt1 = E(), E(), E(), E()
+        t_bwd.record(cur)
+        t_wait.record(cur)
+        cur.wait_stream(self._side)
+        t_opt0.record(cur)
+        self.opt.step(lr=lr)
+        t_opt1.record(cur)
+        self.engine.pack()
+        self.steps_done += 1
+        torch.cuda.synchronize(self.device)
+        tr, self.trace = self.trace, None
+        ms = lambda e: t0.elapsed_time(e)
+        buckets = [(b, ms(e0), ms(e1)) for b, e0, e1 in tr["buckets"]]
+        out = {"backward_end": ms(t_bwd), "buckets": buckets, "wait_start": ms(t_wait), "opt_start": ms(t_opt0),
+               "opt_end": ms(t_opt1)}
+        out["reduce_total"] = sum(e - s for _, s, e in buckets)
+        out["reduce_exposed"] = out["opt_start"] - out["wait_start"]
+        out["step_kernel"] = out["opt_end"] - out["opt_start"]
+        return out
 
     def accumulate(self, tokens, sid=0, final=True):
         """Zero the gradients, then forward + backward over the rank's micro-batches.  final=False: a pass

@@ -36,7 +36,6 @@ def test_static_tape_decoder_equals_teacher_forcing(kw):
     assert torch.equal(gen[:, 0], lg[:, -1].argmax(-1))
 
 
-@pytest.mark.gpu
 def real_disagreements(a, b, tol=0.15):
     """Rows whose greedy tokens differ between two decoders although the reference's logits separate the two
     candidates by more than the logit tolerance (a difference inside it is a tie within bf16 noise)."""
@@ -49,6 +48,7 @@ def real_disagreements(a, b, tol=0.15):
     return int((gap > tol).sum())
 
 
+@pytest.mark.gpu
 @pytest.mark.parametrize("dh,window", [(64, 0), (128, 0), (64, 50)])
 def test_kernel_read_matches_torch_read(dh, window):
     from dual_mod_public_b200 import DualModConfig
