@@ -146,6 +146,14 @@ def main():
         p0 = Tq - pos0 - c                       # as many later query rows as `pos0` keys elsewhere
         both("prefix_dkv", lambda: ops.prefix_dkv(qa, da, ca, la, Ka, Va, p0, c, p0 + c, scale, 0),
              2.0 * att_f * (Tq - p0 - c))
+        if dh == 64:
+            was = ops.dkv_rows128(False)
+            ops.ATTN_TC = True
+            report("prefix_dkv [tcgen05, 64-reader tiles]",
+                   T(lambda: ops.prefix_dkv(qa, da, ca, la, Ka, Va, p0, c, p0 + c, scale, 0)), flops=2.0 * att_f * (Tq - p0 - c))
+            ops.ATTN_TC = type(ops).ATTN_TC
+            ops.dkv_rows128(was)
+            ops.tc_check()
     if want("bar"):
         # one lower-right causal read of a block of 1024 query rows over 4096 tape rows (the window read of a
         # layer-batched wavefront step), next to torch's fused attention backends on the same mask

@@ -850,6 +850,246 @@ __global__ void __launch_bounds__(NTHREADS, (BCfg<DH, KEYSIDE>::TMEM_COLS == 256
   if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Key side with 128 reader rows per tile (head dim 64).  The chunk's K and V (64 keys) stay in shared memory; the
+// readers' (q, d o) rows stream in tiles of 128.  Scores are formed with the READERS as the M dimension,
+//   S = Q_t K^T, dP = dO_t V^T      (M = 128, N = 64: full-rate MMAs, one accumulator row per thread)
+// every math thread owns one reader row (its lse and corr are two scalars, no per-column staging), writes its row
+// of P and dS (64 keys = one 128-byte swizzled line) into shared memory, and the gradient products read those
+// tiles as M-major A operands and the streamed (d o, q) tiles as N-major B operands:
+//   dV += P^T dO_t, dK += dS^T Q_t  (M = 64 keys, N = 64, K = 128 readers).
+// Half as many trips round the MMA -> tensor-memory load -> exponentials -> shared-memory store -> MMA chain as the
+// 64-reader kernel above.  Tensor memory: S 64 | dP 64 | dK 64 | dV 64 columns: two CTAs per SM.
+constexpr int QT = 128;
+
+struct KCfg {
+  static constexpr int KV_BYTES = BT * 64 * 2;          // the chunk's K (or V): 8 KB
+  static constexpr int Y_BYTES = QT * 64 * 2;           // one streamed tile of q (or d o): 16 KB
+  static constexpr int a_off = 0;
+  static constexpr int y_off = 2 * KV_BYTES;            // (q, d o) x two stages
+  static constexpr int ds_off = y_off + 4 * Y_BYTES;    // dS [128 readers][64 keys], then P
+  static constexpr int bar_off = ds_off + 2 * QT * 128;
+  static constexpr int total = bar_off + 256;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 2) attn_dkv128_tc_kernel(
+    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+    const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+    const float* __restrict__ lse, const float* __restrict__ corr, float* __restrict__ out1,
+    float* __restrict__ out2, const BGeo g, int* __restrict__ gerr) {
+  using C = KCfg;
+  constexpr int DH = 64;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicExch(gerr, 2);
+    return;
+  }
+  uint8_t* base_ptr = smem_raw;
+  const uint32_t bar0 = base + C::bar_off;
+  const uint32_t afull = bar0;
+  auto yfull = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto yempty = [&](int s) { return bar0 + 8u * (3 + s); };
+  const uint32_t sdfull = bar0 + 8u * 5, sdfree = bar0 + 8u * 6, dsfull = bar0 + 8u * 7, dsfree = bar0 + 8u * 8,
+                 accdone = bar0 + 8u * 9;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + C::bar_off + 8 * 10);
+  volatile int* serr = reinterpret_cast<volatile int*>(base_ptr + C::bar_off + 8 * 11);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
+  const int own_pos = g.lo + z * g.grow;                  // tape row of the chunk's first key
+  const int s_begin = max(g.q_start, own_pos + g.C);
+  int s_end = min(g.q_end, own_pos + g.span);
+  if (g.window) s_end = min(s_end, own_pos + BT - 1 + g.window);
+  const int n_tiles = s_end > s_begin ? (s_end - s_begin + QT - 1) / QT : 0;
+
+  if (threadIdx.x == 0) {
+    *serr = 0;
+    mbar_init(afull, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(yfull(s), 1);
+      mbar_init(yempty(s), 1);
+    }
+    mbar_init(sdfull, 1);
+    mbar_init(sdfree, 4);
+    mbar_init(dsfull, 4);
+    mbar_init(dsfree, 1);
+    mbar_init(accdone, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t sK = base + C::a_off, sV = sK + C::KV_BYTES, sY = base + C::y_off, sdS = base + C::ds_off,
+                 sPm = sdS + QT * 128;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdK = tmem_base + 128, tdV = tmem_base + 192;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(afull, 2 * C::KV_BYTES);
+      tma_load_3d(sK, &tmK, afull, h * DH, own_pos, b);
+      tma_load_3d(sV, &tmV, afull, h * DH, own_pos, b);
+      int t = 0;
+      for (; t < n_tiles; ++t) {
+        const int s = t & 1, r0 = s_begin + t * QT;
+        if (!mbar_wait(yempty(s), ((t >> 1) & 1) ^ 1, serr)) break;
+        mbar_expect_tx(yfull(s), 2 * C::Y_BYTES);
+        tma_load_3d(sY + (2 * s) * C::Y_BYTES, &tmQ, yfull(s), h * DH, r0, b);
+        tma_load_3d(sY + (2 * s + 1) * C::Y_BYTES, &tmDO, yfull(s), h * DH, r0, b);
+      }
+      if (*serr) {
+        volatile int ignore = 0;
+        for (int u = max(0, t - 2); u < t; ++u) mbar_wait(yfull(u & 1), (u >> 1) & 1, &ignore);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idS = instr_desc(QT, BT, 0, 0), idG = instr_desc(BT, DH, 1, 1);
+      auto issue_scores = [&](int s) {                      // S = Q_t K^T, dP = dO_t V^T
+        const uint32_t yq = sY + (2 * s) * C::Y_BYTES, yo = yq + C::Y_BYTES;
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k)
+          umma_bf16(tS, make_desc(yq + k * 32, 16, 1024), make_desc(sK + k * 32, 16, 1024), idS, k != 0);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k)
+          umma_bf16(tdP, make_desc(yo + k * 32, 16, 1024), make_desc(sV + k * 32, 16, 1024), idS, k != 0);
+        umma_commit(sdfull);
+      };
+      auto issue_grads = [&](int u) {                       // dV += P^T dO_t, dK += dS^T Q_t of tile u
+        const int s = u & 1;
+        const uint32_t yq = sY + (2 * s) * C::Y_BYTES, yo = yq + C::Y_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < QT / 16; ++kk)
+          umma_bf16(tdV, make_desc(sPm + kk * 2048, 8192, 1024), make_desc(yo + kk * 2048, 8192, 1024), idG,
+                    (u | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < QT / 16; ++kk)
+          umma_bf16(tdK, make_desc(sdS + kk * 2048, 8192, 1024), make_desc(yq + kk * 2048, 8192, 1024), idG,
+                    (u | kk) != 0);
+        umma_commit(dsfree);
+        umma_commit(yempty(s));
+      };
+      bool alive = mbar_wait(afull, 0, serr);
+      for (int t = 0; t < n_tiles && alive; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(yfull(s), (t >> 1) & 1, serr)) { alive = false; break; }
+        if (t > 0 && !mbar_wait(sdfree, (t - 1) & 1, serr)) { alive = false; break; }
+        tc_fence_after();
+        issue_scores(s);
+        if (t > 0) {
+          if (!mbar_wait(dsfull, (t - 1) & 1, serr)) { alive = false; break; }
+          tc_fence_after();
+          issue_grads(t - 1);
+        }
+      }
+      if (alive && mbar_wait(dsfull, (n_tiles - 1) & 1, serr)) {
+        tc_fence_after();
+        issue_grads(n_tiles - 1);
+        umma_commit(accdone);
+      }
+    }
+  } else {
+    // ---------------- gradient math: one reader row per thread ----------------
+    const int q = warp & 3, row = q * 32 + lane;
+    const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+    auto wwait = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, serr)); };
+    bool alive = n_tiles > 0;
+    for (int t = 0; t < n_tiles && alive; ++t) {
+      const int qp = s_begin + t * QT + row;               // this thread's reader position
+      const bool valid = qp < s_end;
+      float L2 = 0.f, cc = 0.f;
+      if (valid) {
+        const long long idx = ((long long)b * g.T + qp) * g.H + h;
+        L2 = lse[idx] * 1.4426950408889634f;
+        cc = corr[idx];
+      }
+      if (!wwait(sdfull, t & 1)) { alive = false; break; }
+      tc_fence_after();
+      uint32_t pp[32], pds[32];                            // the row's P and dS as bf16 pairs (keys 2i, 2i+1)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tlane + hf * 32, rs);
+        tmem_ld32(tlane + 64 + hf * 32, rd);
+        tmem_ld_wait();
+        if (hf == 1) {
+          // S and dP are in registers: the next tile's score products may overwrite them
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sdfree);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p[2], w[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float pe = valid ? exp2f(fmaf(__uint_as_float(rs[j + e]), g.scale_log2, -L2)) : 0.f;
+            if (g.window && own_pos + hf * 32 + j + e <= qp - g.window) pe = 0.f;
+            p[e] = pe;
+            w[e] = pe * (__uint_as_float(rd[j + e]) - cc) * g.scale;
+          }
+          pp[hf * 16 + (j >> 1)] = pack_bf16(p[0], p[1]);
+          pds[hf * 16 + (j >> 1)] = pack_bf16(w[0], w[1]);
+        }
+      }
+      // the gradient products of the previous tile must have read dS and P before they are overwritten
+      if (t > 0 && !wwait(dsfree, (t - 1) & 1)) { alive = false; break; }
+      uint8_t* ds_row = base_ptr + C::ds_off + row * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {                      // 16-byte chunk c8 = keys [8 c8, 8 c8 + 8), swizzled
+        const int off = (c8 ^ (row & 7)) << 4;
+        *reinterpret_cast<uint4*>(ds_row + off) = make_uint4(pds[4 * c8], pds[4 * c8 + 1], pds[4 * c8 + 2], pds[4 * c8 + 3]);
+        *reinterpret_cast<uint4*>(ds_row + QT * 128 + off) = make_uint4(pp[4 * c8], pp[4 * c8 + 1], pp[4 * c8 + 2], pp[4 * c8 + 3]);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dsfull);
+    }
+    // ---- the accumulated gradients (M = 64 accumulators: rows in lanes 0..15 of each quarter) ----
+    const int t4 = lane & 3, rA = q * 16 + (lane >> 2);
+    if (alive && n_tiles > 0) alive = wwait(accdone, 0);
+    if (alive || n_tiles == 0) {
+      if (n_tiles > 0) tc_fence_after();
+#pragma unroll 1
+      for (int a = 0; a < 2; ++a) {
+        float* dstA = (a == 0 ? out1 : out2) + b * g.o_bs + (long long)(z * BT + rA) * g.o_rs + (long long)h * DH;
+        float* dstB = dstA + 8 * g.o_rs;
+        uint32_t r[32];
+        if (n_tiles > 0) {
+          tmem_ld_16x256b_x8(tlane + 128 + a * DH, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int d = 8 * j + 2 * t4;
+          float2 vA = make_float2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]));
+          float2 vB = make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          if (g.accumulate) {
+            const float2 oA = *reinterpret_cast<const float2*>(dstA + d), oB = *reinterpret_cast<const float2*>(dstB + d);
+            vA.x += oA.x; vA.y += oA.y; vB.x += oB.x; vB.y += oB.y;
+          }
+          *reinterpret_cast<float2*>(dstA + d) = vA;
+          *reinterpret_cast<float2*>(dstB + d) = vB;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+  if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
+}
+
 template <int DH, int KEYSIDE>
 int launch_bwd(const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& y1, const CUtensorMap& y2,
                const float* lse, const float* corr, float* out1, float* out2, int B, int G, const BGeo& g, int* gerr,
@@ -866,6 +1106,8 @@ int launch_bwd(const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& 
   DMB_CHECK_LAUNCH();
   return 0;
 }
+
+int g_dkv_rows128 = 1;
 
 }  // namespace
 
@@ -920,8 +1162,29 @@ int dmb_attn_dkv_tc(const void* q_all, const void* doc_all, const float* corr_al
   const int y_rows = max(1, g.q_end);
   if ((rc = make_map_3d(&y1, q_all, cols, y_rows, B, cols, (long long)T * cols, 64, 64))) return rc;
   if ((rc = make_map_3d(&y2, doc_all, cols, y_rows, B, cols, (long long)T * cols, 64, 64))) return rc;
+  if (dh == 64 && g_dkv_rows128) {
+    // 128 reader rows per streamed tile: the same maps with a taller box
+    if ((rc = make_map_3d(&y1, q_all, cols, y_rows, B, cols, (long long)T * cols, 64, QT))) return rc;
+    if ((rc = make_map_3d(&y2, doc_all, cols, y_rows, B, cols, (long long)T * cols, 64, QT))) return rc;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_dkv128_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KCfg::total);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    attn_dkv128_tc_kernel<<<dim3(H, B, G), NTHREADS, KCfg::total, st>>>(a1, a2, y1, y2, lse_all, corr_all, dK, dV, g, gerr);
+    DMB_CHECK_LAUNCH();
+    return 0;
+  }
   if (dh == 64) return launch_bwd<64, 1>(a1, a2, y1, y2, lse_all, corr_all, dK, dV, B, G, g, gerr, st);
   return launch_bwd<128, 1>(a1, a2, y1, y2, lse_all, corr_all, dK, dV, B, G, g, gerr, st);
+}
+
+// 1 (default): the key side at head dim 64 streams its readers in tiles of 128 rows; 0: in tiles of 64
+int dmb_attn_dkv_rows128(int on) {
+  const int was = g_dkv_rows128;
+  if (on >= 0) g_dkv_rows128 = on;
+  return was;
 }
 
 }  // extern "C"

@@ -72,6 +72,7 @@ class _Sigs:
     dmb_cell_finish = [_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_attn_dkv_rows128 = [_i]
     dmb_cell_finish_sweeps = [_p, _i, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _f, _ll,
                               _ll, _i, _i, _i, _i, _p]
     dmb_wave_chunk_finish = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _i, _p, _p,
@@ -120,6 +121,11 @@ class CudaOps(TorchOps):
             self.gemm = Tcgen05Gemm(self.lib, self.device)
 
     # ---- helpers ---------------------------------------------------------------------------
+    def dkv_rows128(self, on=None):
+        """The key-side tcgen05 attention backward at head dim 64 streams its readers in tiles of 128 rows (default) or
+        of 64 (`on=False`); returns the previous setting.  A process-wide switch of the kernel library."""
+        return bool(self.lib.dmb_attn_dkv_rows128(-1 if on is None else int(bool(on))))
+
     def _fell_back(self, name):
         """A call whose arguments the kernel does not take (layout, dtype, size) runs the torch statement; it is
         counted so that a hot path that silently left the kernels shows up (`fallbacks`, `DMB_STRICT_OPS=1` raises)."""

@@ -149,8 +149,16 @@ def test_backward_query_side_matches_torch_statement(ops, dh, window):
         _close(dq, dq_ref, f"dq at pos0 {pos0}")
 
 
+@pytest.fixture(params=[True, False], ids=["readers128", "readers64"])
+def reader_tiles(request, ops):
+    """Both forms of the key-side kernel at head dim 64: readers streamed in tiles of 128 rows (default) and of 64."""
+    was = ops.dkv_rows128(request.param)
+    yield request.param
+    ops.dkv_rows128(was)
+
+
 @pytest.mark.parametrize("dh,window", [(64, 0), (64, 150), (128, 0)])
-def test_backward_key_side_matches_torch_statement(ops, dh, window):
+def test_backward_key_side_matches_torch_statement(ops, dh, window, reader_tiles):
     B, T, h, c = 2, 512, 2, 64
     ref, q_all, K, V, doc_all, lse_all, corr_all, scale = _cells(ops, B, T, h, dh, window, 21)
     for pos0 in (0, 192, 384):
@@ -166,7 +174,7 @@ def test_backward_key_side_matches_torch_statement(ops, dh, window):
     _close(dV, dV_ref, "dV, bounded readers")
 
 
-def test_window_group_launches_match_the_per_chunk_statement(ops):
+def test_window_group_launches_match_the_per_chunk_statement(ops, reader_tiles):
     """The wavefront engine's one-launch-per-window forms (grid z = chunk of the window)."""
     from dual_mod_public_b200.ops.torch_ops import TorchOps
     ref = TorchOps()
@@ -196,7 +204,7 @@ def test_window_group_launches_match_the_per_chunk_statement(ops):
     _close(dV, dV_ref, "near dV")
 
 
-def test_backward_outputs_into_windows_of_longer_arrays(ops):
+def test_backward_outputs_into_windows_of_longer_arrays(ops, reader_tiles):
     """The engines hand the backward kernels windows of [B, T, h, dh] gradient arrays: dq added in place, the
     key side added to the pending gradient of its rows."""
     B, T, h, dh, c = 2, 512, 2, 64, 64
