@@ -1090,6 +1090,232 @@ __global__ void __launch_bounds__(NTHREADS, 2) attn_dkv128_tc_kernel(
   if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Query side with 128 keys per tile (head dim 64): the mirror image of the kernel above.  The group's 64 query
+// rows (q, d o) stay in shared memory with their lse / corr (staged once: they do not change from tile to tile);
+// the tape's K / V rows stream in tiles of 128.  Scores are formed with the KEYS as the M dimension,
+//   S^T = K_t Q^T, dP^T = V_t dO^T    (M = 128, N = 64), one key row per thread,
+// dS^T goes to shared memory one 128-byte line per key, and  dQ += dS K_t  reads it as an M-major A operand
+// (M = 64 queries, K = 128 keys) against the K tile as an N-major B operand.  Tensor memory: 192 of 256 columns.
+struct QCfg {
+  static constexpr int O_BYTES = BT * 64 * 2;           // the group's q (or d o): 8 KB
+  static constexpr int Y_BYTES = QT * 64 * 2;           // one streamed tile of K (or V): 16 KB
+  static constexpr int a_off = 0;
+  static constexpr int y_off = 2 * O_BYTES;             // (K, V) x two stages
+  static constexpr int ds_off = y_off + 4 * Y_BYTES;    // dS^T [128 keys][64 queries]
+  static constexpr int sc_off = ds_off + QT * 128;      // lse (log2 domain) and corr of the 64 queries
+  static constexpr int bar_off = sc_off + 512;
+  static constexpr int total = bar_off + 256;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 2) attn_dq128_tc_kernel(
+    const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+    const float* __restrict__ lse, const float* __restrict__ corr, float* __restrict__ out1, const BGeo g,
+    int* __restrict__ gerr) {
+  using C = QCfg;
+  constexpr int DH = 64;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicExch(gerr, 2);
+    return;
+  }
+  uint8_t* base_ptr = smem_raw;
+  const uint32_t bar0 = base + C::bar_off;
+  const uint32_t afull = bar0;
+  auto yfull = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto yempty = [&](int s) { return bar0 + 8u * (3 + s); };
+  const uint32_t sdfull = bar0 + 8u * 5, sdfree = bar0 + 8u * 6, dsfull = bar0 + 8u * 7, dsfree = bar0 + 8u * 8,
+                 accdone = bar0 + 8u * 9;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + C::bar_off + 8 * 10);
+  volatile int* serr = reinterpret_cast<volatile int*>(base_ptr + C::bar_off + 8 * 11);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z, G = gridDim.z;
+  const int own_row0 = z * g.grow, own_pos = g.qbase + z * g.grow;
+  int s_begin = max(0, g.lo + z * g.grow);
+  const int s_end = g.hi + z * g.grow;
+  if (g.window) s_begin = min(s_end, max(s_begin, own_pos - g.window + 1));
+  const int n_tiles = s_end > s_begin ? (s_end - s_begin + QT - 1) / QT : 0;
+
+  if (threadIdx.x == 0) {
+    *serr = 0;
+    mbar_init(afull, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(yfull(s), 1);
+      mbar_init(yempty(s), 1);
+    }
+    mbar_init(sdfull, 1);
+    mbar_init(sdfree, 4);
+    mbar_init(dsfull, 4);
+    mbar_init(dsfree, 1);
+    mbar_init(accdone, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  // the 64 queries' lse (log2 domain) and corr: dense [B, G, 64, H]
+  float* sc = reinterpret_cast<float*>(base_ptr + C::sc_off);
+  if (threadIdx.x >= 64 && threadIdx.x < 128) {
+    const int r = threadIdx.x - 64;
+    const long long idx = ((long long)((b * G + z) * g.C + r) * g.H + h);
+    sc[r] = lse[idx] * 1.4426950408889634f;
+    sc[64 + r] = corr[idx];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t sQ = base + C::a_off, sdO = sQ + C::O_BYTES, sY = base + C::y_off, sdS = base + C::ds_off;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdQ = tmem_base + 128;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(afull, 2 * C::O_BYTES);
+      tma_load_3d(sQ, &tmQ, afull, h * DH, own_row0, b);
+      tma_load_3d(sdO, &tmDO, afull, h * DH, own_row0, b);
+      int t = 0;
+      for (; t < n_tiles; ++t) {
+        const int s = t & 1, r0 = s_begin + t * QT;
+        if (!mbar_wait(yempty(s), ((t >> 1) & 1) ^ 1, serr)) break;
+        mbar_expect_tx(yfull(s), 2 * C::Y_BYTES);
+        tma_load_3d(sY + (2 * s) * C::Y_BYTES, &tmK, yfull(s), h * DH, r0, b);
+        tma_load_3d(sY + (2 * s + 1) * C::Y_BYTES, &tmV, yfull(s), h * DH, r0, b);
+      }
+      if (*serr) {
+        volatile int ignore = 0;
+        for (int u = max(0, t - 2); u < t; ++u) mbar_wait(yfull(u & 1), (u >> 1) & 1, &ignore);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idS = instr_desc(QT, BT, 0, 0), idG = instr_desc(BT, DH, 1, 1);
+      auto issue_scores = [&](int s) {                      // S^T = K_t Q^T, dP^T = V_t dO^T
+        const uint32_t yk = sY + (2 * s) * C::Y_BYTES, yv = yk + C::Y_BYTES;
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k)
+          umma_bf16(tS, make_desc(yk + k * 32, 16, 1024), make_desc(sQ + k * 32, 16, 1024), idS, k != 0);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k)
+          umma_bf16(tdP, make_desc(yv + k * 32, 16, 1024), make_desc(sdO + k * 32, 16, 1024), idS, k != 0);
+        umma_commit(sdfull);
+      };
+      auto issue_grads = [&](int u) {                       // dQ += dS K_t of tile u
+        const int s = u & 1;
+        const uint32_t yk = sY + (2 * s) * C::Y_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < QT / 16; ++kk)
+          umma_bf16(tdQ, make_desc(sdS + kk * 2048, 8192, 1024), make_desc(yk + kk * 2048, 8192, 1024), idG,
+                    (u | kk) != 0);
+        umma_commit(dsfree);
+        umma_commit(yempty(s));
+      };
+      bool alive = mbar_wait(afull, 0, serr);
+      for (int t = 0; t < n_tiles && alive; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(yfull(s), (t >> 1) & 1, serr)) { alive = false; break; }
+        if (t > 0 && !mbar_wait(sdfree, (t - 1) & 1, serr)) { alive = false; break; }
+        tc_fence_after();
+        issue_scores(s);
+        if (t > 0) {
+          if (!mbar_wait(dsfull, (t - 1) & 1, serr)) { alive = false; break; }
+          tc_fence_after();
+          issue_grads(t - 1);
+        }
+      }
+      if (alive && mbar_wait(dsfull, (n_tiles - 1) & 1, serr)) {
+        tc_fence_after();
+        issue_grads(n_tiles - 1);
+        umma_commit(accdone);
+      }
+    }
+  } else {
+    // ---------------- gradient math: one key row per thread ----------------
+    const int q = warp & 3, row = q * 32 + lane;
+    const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+    auto wwait = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, serr)); };
+    bool alive = n_tiles > 0;
+    for (int t = 0; t < n_tiles && alive; ++t) {
+      const int kp = s_begin + t * QT + row;               // this thread's key (tape row)
+      const bool valid = kp < s_end;
+      if (!wwait(sdfull, t & 1)) { alive = false; break; }
+      tc_fence_after();
+      uint32_t pds[32];                                    // the key's dS over the 64 queries as bf16 pairs
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tlane + hf * 32, rs);
+        tmem_ld32(tlane + 64 + hf * 32, rd);
+        tmem_ld_wait();
+        if (hf == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sdfree);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const int c = hf * 32 + j;
+          const float2 L2 = *reinterpret_cast<const float2*>(sc + c), cc = *reinterpret_cast<const float2*>(sc + 64 + c);
+          float w[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float pe = valid ? exp2f(fmaf(__uint_as_float(rs[j + e]), g.scale_log2, -(e ? L2.y : L2.x))) : 0.f;
+            if (g.window && kp <= own_pos + c + e - g.window) pe = 0.f;
+            w[e] = pe * (__uint_as_float(rd[j + e]) - (e ? cc.y : cc.x)) * g.scale;
+          }
+          pds[hf * 16 + (j >> 1)] = pack_bf16(w[0], w[1]);
+        }
+      }
+      if (t > 0 && !wwait(dsfree, (t - 1) & 1)) { alive = false; break; }
+      uint8_t* ds_row = base_ptr + C::ds_off + row * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8)
+        *reinterpret_cast<uint4*>(ds_row + ((c8 ^ (row & 7)) << 4)) =
+            make_uint4(pds[4 * c8], pds[4 * c8 + 1], pds[4 * c8 + 2], pds[4 * c8 + 3]);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dsfull);
+    }
+    // ---- d q (M = 64 accumulator: rows in lanes 0..15 of each quarter) ----
+    const int t4 = lane & 3, rA = q * 16 + (lane >> 2);
+    if (alive && n_tiles > 0) alive = wwait(accdone, 0);
+    if (alive || n_tiles == 0) {
+      if (n_tiles > 0) tc_fence_after();
+      float* dstA = out1 + b * g.o_bs + (long long)(z * BT + rA) * g.o_rs + (long long)h * DH;
+      float* dstB = dstA + 8 * g.o_rs;
+      uint32_t r[32];
+      if (n_tiles > 0) {
+        tmem_ld_16x256b_x8(tlane + 128, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) r[e] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int d = 8 * j + 2 * t4;
+        float2 vA = make_float2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]));
+        float2 vB = make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        if (g.accumulate) {
+          const float2 oA = *reinterpret_cast<const float2*>(dstA + d), oB = *reinterpret_cast<const float2*>(dstB + d);
+          vA.x += oA.x; vA.y += oA.y; vB.x += oB.x; vB.y += oB.y;
+        }
+        *reinterpret_cast<float2*>(dstA + d) = vA;
+        *reinterpret_cast<float2*>(dstB + d) = vB;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+  if (threadIdx.x == 0 && *serr) atomicExch(gerr, 1);
+}
+
 template <int DH, int KEYSIDE>
 int launch_bwd(const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& y1, const CUtensorMap& y2,
                const float* lse, const float* corr, float* out1, float* out2, int B, int G, const BGeo& g, int* gerr,
@@ -1135,6 +1361,20 @@ int dmb_attn_dq_tc(const void* q, TView vq, const void* do_c, TView vdo, int q_r
   const long long kbs = B > 1 ? vc.bs : (long long)tape_rows * vc.rs;
   if ((rc = make_map_3d(&y1, Kc, cols, k_rows, B, vc.rs, kbs, 64, 64))) return rc;
   if ((rc = make_map_3d(&y2, Vc, cols, k_rows, B, vc.rs, kbs, 64, 64))) return rc;
+  if (dh == 64 && g_dkv_rows128) {
+    // 128 keys per streamed tile: the same tape maps with a taller box
+    if ((rc = make_map_3d(&y1, Kc, cols, k_rows, B, vc.rs, kbs, 64, QT))) return rc;
+    if ((rc = make_map_3d(&y2, Vc, cols, k_rows, B, vc.rs, kbs, 64, QT))) return rc;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_dq128_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg::total);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    attn_dq128_tc_kernel<<<dim3(H, B, G), NTHREADS, QCfg::total, st>>>(a1, a2, y1, y2, lse, corr, dq, g, gerr);
+    DMB_CHECK_LAUNCH();
+    return 0;
+  }
   if (dh == 64) return launch_bwd<64, 0>(a1, a2, y1, y2, lse, corr, dq, nullptr, B, G, g, gerr, st);
   return launch_bwd<128, 0>(a1, a2, y1, y2, lse, corr, dq, nullptr, B, G, g, gerr, st);
 }
@@ -1180,7 +1420,8 @@ int dmb_attn_dkv_tc(const void* q_all, const void* doc_all, const float* corr_al
   return launch_bwd<128, 1>(a1, a2, y1, y2, lse_all, corr_all, dK, dV, B, G, g, gerr, st);
 }
 
-// 1 (default): the key side at head dim 64 streams its readers in tiles of 128 rows; 0: in tiles of 64
+// 1 (default): at head dim 64 the key side streams its readers, and the query side its keys, in tiles of 128 rows;
+// 0: in tiles of 64
 int dmb_attn_dkv_rows128(int on) {
   const int was = g_dkv_rows128;
   if (on >= 0) g_dkv_rows128 = on;

@@ -427,10 +427,11 @@ class CudaOps(TorchOps):
 
     # Which of the 64-row tape reads (a cell's prefix read, the wavefront's far and near reads) and their
     # backward sides go through the tcgen05 kernels of csrc/attn_tc.cu instead of the warp-MMA kernels.
-    # Default: the sides where tcgen05 measured faster at the 340M cell shape (32 sequences x 16 heads of 64,
-    # 1024 keys / later queries): forward 47 vs 66 us, key side 81 vs 109 us; the query side stays on the
-    # warp-MMA kernel (95 vs 89 us).  DMB_ATTN_TC: comma list of fwd / dq / dkv, "1" or "all" = all, "0" = none.
-    _tc_env = os.environ.get("DMB_ATTN_TC", "fwd,dkv").lower()
+    # Default: all three; measured at the 340M cell shape (32 sequences x 16 heads of 64, 1024 keys / later
+    # queries), tcgen05 against warp MMA: forward 47 vs 66 us, key side 59 vs 109 us, query side 64 vs 90 us (the
+    # backward sides with their 128-row streamed tiles; with 64-row tiles the query side was slower than warp MMA).
+    # DMB_ATTN_TC: comma list of fwd / dq / dkv, "1" or "all" = all, "0" = none.
+    _tc_env = os.environ.get("DMB_ATTN_TC", "all").lower()
     ATTN_TC = (frozenset(("fwd", "dq", "dkv")) if _tc_env in ("1", "all") else
                frozenset() if _tc_env in ("0", "", "none") else frozenset(x.strip() for x in _tc_env.split(",")))
 

@@ -134,8 +134,16 @@ def _close(got, ref, what, tol=2e-2):
     assert err <= tol * scale + 1e-4, f"{what}: err {err:.4g} scale {scale:.4g}"
 
 
+@pytest.fixture(params=[True, False], ids=["readers128", "readers64"])
+def reader_tiles(request, ops):
+    """Both forms of the backward kernels at head dim 64: the streamed side in tiles of 128 rows (default) and of 64."""
+    was = ops.dkv_rows128(request.param)
+    yield request.param
+    ops.dkv_rows128(was)
+
+
 @pytest.mark.parametrize("dh,window", [(64, 0), (64, 150), (128, 0)])
-def test_backward_query_side_matches_torch_statement(ops, dh, window):
+def test_backward_query_side_matches_torch_statement(ops, dh, window, reader_tiles):
     B, T, h, c = 2, 512, 2, 64
     ref, q_all, K, V, doc_all, lse_all, corr_all, scale = _cells(ops, B, T, h, dh, window, 11)
     for pos0 in (64, 320, 448):
@@ -147,14 +155,6 @@ def test_backward_query_side_matches_torch_statement(ops, dh, window):
         ops.prefix_dq(q_all[:, r], K, V, pos0, scale, window, lse_c, doc_all[:, r], corr, dq)
         ops.tc_check()
         _close(dq, dq_ref, f"dq at pos0 {pos0}")
-
-
-@pytest.fixture(params=[True, False], ids=["readers128", "readers64"])
-def reader_tiles(request, ops):
-    """Both forms of the key-side kernel at head dim 64: readers streamed in tiles of 128 rows (default) and of 64."""
-    was = ops.dkv_rows128(request.param)
-    yield request.param
-    ops.dkv_rows128(was)
 
 
 @pytest.mark.parametrize("dh,window", [(64, 0), (64, 150), (128, 0)])
