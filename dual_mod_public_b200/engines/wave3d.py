@@ -48,6 +48,8 @@ stash, deferred dW), lm/train_1p3b/validate_rawdiag.py (exactness protocol, raw 
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..models.rope import apply_rope
@@ -117,9 +119,13 @@ class Wave3DEngine(WaveScanEngine):
         ladder = [int(k) for k in (ladder if isinstance(ladder, (list, tuple)) else [ladder])]
         assert T % C == 0, "sequence length must be a whole number of chunks"
         kw.setdefault("keep_sweeps", 0)
+        # every layer keeps the far partials (o_far, lse_far) of its chunks from the training forward, so the
+        # forward re-run inside the backward skips the far reads (fp32 [B, T, d] + [B, T, h] per layer)
+        keep_far = bool(kw.pop("keep_far", os.environ.get("DMB_KEEP_FAR", "1") == "1"))
         # sweeps may exceed the chunk length here (in-flight predecessors deepen the dependency chain)
         super().__init__(model, [[(p, C, k) for p in range(0, T, C)] for k in ladder], B, T, **kw)
         self.ladder, self.C = ladder, C
+        self.keep_far = keep_far and self.backend == "fused"
         if self.backend == "fused":
             cfg, dev = self.cfg, self.device
             z = lambda *s, dt: torch.zeros(*s, dtype=dt, device=dev)
@@ -132,8 +138,11 @@ class Wave3DEngine(WaveScanEngine):
             self.dKp = z(B, T, h, dh, dt=torch.float32)
             self.dVp = z(B, T, h, dh, dt=torch.float32)
             # far partial of every chunk (computed when it enters) and the accumulators of its gradient
-            self.ofar_all = z(B, T, h, dh, dt=torch.float32)
-            self.lsefar_all = z(B, T, h, dt=torch.float32)
+            self._far = [(z(B, T, h, dh, dt=torch.float32), z(B, T, h, dt=torch.float32))
+                         for _ in range(self.L if self.keep_far else 1)]
+            self.ofar_all, self.lsefar_all = self._far[0]
+            if self.keep_far:
+                self.keep_layers = self.L          # `kept` in the backward = this layer's far partials are the forward's
             self.DOf_all = z(B, T, h, dh, dt=torch.float32)
             self.DLf_all = z(B, T, h, dt=torch.float32)
             self._versions = {}
@@ -238,7 +247,10 @@ class Wave3DEngine(WaveScanEngine):
         G.get(m.tok_emb.weight).index_add_(0, self.idx.view(-1), dx.reshape(-1, self.cfg.d_model).float())
 
     # ---- forward ----------------------------------------------------------------------------------------
-    def _wave_step(self, S, s, K, save=None, win=None):
+    def _far_arrays(self, li):
+        self.ofar_all, self.lsefar_all = self._far[li if self.keep_far else 0]
+
+    def _wave_step(self, S, s, K, save=None, win=None, far_kept=False):
         """Step s of one layer: the chunk entering (if any) computes its far partial and puts its raw rows
         on the tape; then ALL window chunks do one sweep in one launch per op (window tensors are
         [B, G*C, ...], G = chunks in the window) and their new rows replace the old ones."""
@@ -247,7 +259,7 @@ class Wave3DEngine(WaveScanEngine):
         n = self.T // C
         lo, hi = max(0, s - K + 1), min(s, n - 1)
         G, w = hi - lo + 1, slice(lo * C, (hi + 1) * C)
-        if s < n:
+        if s < n and not far_kept:
             # the entering chunk's far partial: it reads rows committed before this step and is needed by the merge
             # only, so it runs on the second stream beside the window's near read
             r = slice(s * C, (s + 1) * C)
@@ -283,6 +295,7 @@ class Wave3DEngine(WaveScanEngine):
 
     def _cells_fwd(self, li, sid, S, keep):
         K = self.ladder[sid]
+        self._far_arrays(li)
         self._raw_tape(S)
         for s in range(self.T // self.C + K - 1):
             self._wave_step(S, s, K)
@@ -301,9 +314,10 @@ class Wave3DEngine(WaveScanEngine):
         rows = lambda i: slice(i * C, (i + 1) * C)
         # ---- forward re-run of this layer, keeping what every step read and produced
         save = {}
+        self._far_arrays(li)
         self._raw_tape(S)
         for s in range(n + K - 1):
-            self._wave_step(S, s, K, save, win)
+            self._wave_step(S, s, K, save, win, far_kept=bool(kept) and self.keep_far)
         for t in (self.dKp, self.dVp, self.DOf_all, self.DLf_all):
             t.zero_()
         # per-step scratch of the partial's gradient: written (not accumulated) by the tail kernel

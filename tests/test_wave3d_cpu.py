@@ -48,6 +48,30 @@ def test_fused_wavefront_matches_autograd(K, C, T, kw):
     assert torch.equal(l, l2) and all(torch.equal(g[n], g2[n]) for n in g)
 
 
+def test_kept_far_partials_change_nothing():
+    """The backward's forward re-run reuses the far partials the training forward left per layer (`keep_far`) or
+    computes them again: bitwise the same loss and gradients; an evaluation forward in between invalidates them."""
+    cfg, m = build(n_layers=2)
+    idx, tgt = _data(cfg, 2, 32, 5)
+    mk = lambda keep: Wave3DEngine(m, [3], 2, 32, C=4, backend="fused", ops=TorchOps(), loss_rows=16, keep_far=keep)
+    e1, e0 = mk(True), mk(False)
+    assert e1.keep_far and not e0.keep_far and len(e1._far) == 2 and len(e0._far) == 1
+    (l1, g1), (l0, g0) = _engine(m, e1, idx, tgt), _engine(m, e0, idx, tgt)
+    assert torch.equal(l1, l0) and all(torch.equal(g1[n], g0[n]) for n in g0)
+    calls = []
+    orig = e1.ops.prefix_fwd
+    e1.ops.prefix_fwd = lambda *a, **k: (calls.append(1), orig(*a, **k))[1]
+    e1.zero_grads()
+    e1.train_step(idx, tgt)
+    n_train = len(calls)                       # forward only: the re-run inside the backward adds none
+    e1.forward(idx, tgt, train=True)
+    assert len(calls) == 2 * n_train
+    e1.forward(idx, tgt)                       # an evaluation forward: the kept partials are no longer the training ones
+    e1.backward()
+    assert len(calls) == 4 * n_train           # eval forward + far reads of the re-run
+    del e1.ops.prefix_fwd
+
+
 def test_windowed_wavefront_reaches_the_windowed_scan():
     """With a sliding window the operator still converges to the exact scan of the windowed model."""
     cfg, m = build(local_window=6)
