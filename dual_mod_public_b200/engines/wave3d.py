@@ -327,6 +327,9 @@ class Wave3DEngine(WaveScanEngine):
         # (d v_raw = sum over its sweeps of p_self dO, d k_self = (sum dss) q) are formed once, when its last sweep
         # has been processed, instead of read-modify-written by every step
         ring = {}
+        # the gates' x-logit gradient is summed once per chunk from the stashed d(ctx / gate logits) of its K sweeps
+        # (chunk end) instead of being accumulated by every step's refine backward
+        dglx_full, S.dglx = S.dglx, None
         for s in range(n + K - 2, -1, -1):
             lo, hi = max(0, s - K + 1), min(s, n - 1)
             G, w, j = hi - lo + 1, slice(lo * C, (hi + 1) * C), s - K + 1
@@ -348,7 +351,7 @@ class Wave3DEngine(WaveScanEngine):
             # gradient of what step s read = rows of step s-1: replaces the pending gradient of the window's
             # rows; d q goes straight into the layer's array
             stash = torch.empty(2, B, G * C, h, dtype=f32, device=dev)
-            ring[s] = (d_o, stash, lo)
+            ring[s] = (d_o, stash, lo, dcg_stash[offs[s]:offs[s] + B * G * C].view(B, G * C, 4 * d))
             ops.win_tail_bwd(d_o, S.q_r[:, w], S.kself_r[:, w], S.v4[:, w], Kc[:, w], Vc[:, w], o_c, lse_c, o, lse, C,
                              scale, S.dq_r[:, w], S.dks_r[:, w], S.dv4[:, w], do_c, dlse_c, self.window, init=2,
                              dkv_out=(self.dKp[:, w], self.dVp[:, w]), raw_stash=stash)
@@ -366,13 +369,14 @@ class Wave3DEngine(WaveScanEngine):
                 r, fe = rows(s), max(0, s - K + 1) * C
                 sweeps = []
                 for k in range(K):                              # sweep k of chunk s ran at step s + k
-                    g_o, g_st, g_lo = ring[s + k]
+                    g_o, g_st, g_lo, g_dcg = ring[s + k]
                     gr = rows(s - g_lo)
-                    sweeps.append((g_o[:, gr], g_st[0][:, gr], g_st[1][:, gr]))
+                    sweeps.append((g_o[:, gr], g_st[0][:, gr], g_st[1][:, gr]) + ((g_dcg[:, gr],) if dglx_full is not None else ()))
                 corr_f, lse_f = ops.chunk_finish(self.DOf_all[:, r], self.DLf_all[:, r], self.ofar_all[:, r],
                                                  self.lsefar_all[:, r], self.dKp[:, r], self.dVp[:, r], S.dks_r[:, r],
                                                  S.dv4[:, r], self.doc_all[:, r], self.corr_all[:, r], self.lsec_all[:, r],
-                                                 sweeps=sweeps, q=S.q_r[:, r])
+                                                 sweeps=sweeps, q=S.q_r[:, r],
+                                                 dglx=dglx_full[:, r] if dglx_full is not None else None)
                 del sweeps
                 # d q of the far read: it writes only chunk s's rows of dq_r, which no later step of the reverse pass
                 # touches, and runs on the second stream beside the key-side gathers that follow; it is joined
@@ -390,6 +394,7 @@ class Wave3DEngine(WaveScanEngine):
             ring.pop(s + K - 1, None)                           # chunk s - 1 needs the steps s - 1 .. s + K - 2 only
             self.stats["bwd_cells"] += G
         self._join_beside()
+        S.dglx = dglx_full
         return dcg_stash, u_stash
 
 

@@ -235,11 +235,15 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
 // With K > 0 the raw-row gradients of the chunk's K sweeps were deferred (tail backward, mode 2): sweep k left its
 // d o rows (sw.dO[k], batch stride sw.bs_vec[k]) and per-(row, head) scalars p_self (sw.ps[k]) and dss (sw.dss[k],
 // batch stride sw.bs_sca[k]); here dv += sum_k p_self,k dO_k and dks += (sum_k dss_k) q (q: the chunk's rotated
-// query rows, bf16 view).
+// query rows, bf16 view).  With `dglx` the gates' x-logit gradient of the chunk's rows is formed here as well: it
+// equals, sweep by sweep, the gate columns [2d, 4d) of the stashed d(ctx / gate logits) (sw.dcg[k]), so it is
+// summed over the K sweeps once and written (fp32 [B, R, 2d] view, batch stride bs_dglx) instead of being
+// read-modify-written by every step's refine backward.
 struct ChunkSweeps {
   const float* dO[64];
   const float* ps[64];
   const float* dss[64];
+  const bf16* dcg[64];      // optional: the sweep's stashed d(ctx / gate logits) rows [B, R, 4d] (batch stride 4 bs_vec)
   long long bs_vec[64];
   long long bs_sca[64];
 };
@@ -250,7 +254,8 @@ __global__ void __launch_bounds__(256) chunk_finish_kernel(
     const float* __restrict__ lse_f, float* __restrict__ dKp, float* __restrict__ dVp, float* __restrict__ dks,
     float* __restrict__ dv, TD* __restrict__ doc, float* __restrict__ corr, float* __restrict__ lsec,
     float* __restrict__ corr_dense, float* __restrict__ lse_dense, long long bs_vec, long long bs_sca, int B, int R,
-    int H, const __grid_constant__ ChunkSweeps sw, int K, const bf16* __restrict__ q, TView vq) {
+    int H, const __grid_constant__ ChunkSweeps sw, int K, const bf16* __restrict__ q, TView vq,
+    float* __restrict__ dglx, long long bs_dglx) {
   const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)B * R * H) return;
@@ -260,9 +265,10 @@ __global__ void __launch_bounds__(256) chunk_finish_kernel(
   const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
   const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
   constexpr int PER = DH / 32;
-  float av[PER], dss = 0.f;
+  float av[PER], agk[PER], agv[PER], dss = 0.f;
 #pragma unroll
-  for (int e = 0; e < PER; ++e) av[e] = 0.f;
+  for (int e = 0; e < PER; ++e) av[e] = agk[e] = agv[e] = 0.f;
+  const long long d = (long long)H * DH;
   for (int k = K - 1; k >= 0; --k) {
     const long long so = (long long)b * sw.bs_sca[k] + (long long)r * H + h;
     const float* g_ = sw.dO[k] + (long long)b * sw.bs_vec[k] + ((long long)r * H + h) * DH;
@@ -270,6 +276,22 @@ __global__ void __launch_bounds__(256) chunk_finish_kernel(
     dss += sw.dss[k][so];
 #pragma unroll
     for (int e = 0; e < PER; ++e) av[e] += ps * g_[lane + 32 * e];
+    if (dglx) {
+      const bf16* c_ = sw.dcg[k] + (long long)b * 4 * sw.bs_vec[k] + (long long)r * 4 * d + 2 * d + (long long)h * DH;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) {
+        agk[e] += __bfloat162float(c_[lane + 32 * e]);
+        agv[e] += __bfloat162float(c_[d + lane + 32 * e]);
+      }
+    }
+  }
+  if (dglx) {
+    float* o_ = dglx + (long long)b * bs_dglx + (long long)r * 2 * d + (long long)h * DH;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      o_[lane + 32 * e] = agk[e];
+      o_[d + lane + 32 * e] = agv[e];
+    }
   }
   const bf16* q_row = K > 0 ? q + b * vq.bs + r * vq.rs + (long long)h * DH : nullptr;
   float dot = 0.f;
@@ -401,19 +423,22 @@ int dmb_cell_finish_sweeps(const float* const* dO_ptrs, int K, const float* scal
   return 0;
 }
 
-// sweeps: K (0..64) deferred sweeps; dO_ptrs / ps_ptrs / dss_ptrs and the two stride arrays have K entries (host)
+// sweeps: K (0..64) deferred sweeps; dO_ptrs / ps_ptrs / dss_ptrs (/ dcg_ptrs when dglx is given) and the two stride
+// arrays have K entries (host)
 int dmb_wave_chunk_finish(const float* DOf, const float* DLf, const float* o_f, const float* lse_f, float* dKp,
                           float* dVp, float* dks, float* dv, void* doc, int doc_bf16, float* corr, float* lsec,
                           float* corr_dense, float* lse_dense, long long bs_vec, long long bs_sca, int B, int R, int H,
                           int DH, int K, const float* const* dO_ptrs, const float* const* ps_ptrs,
                           const float* const* dss_ptrs, const long long* sw_bs_vec, const long long* sw_bs_sca,
-                          const void* q, TView vq, cudaStream_t st) {
+                          const void* q, TView vq, const void* const* dcg_ptrs, float* dglx, long long bs_dglx,
+                          cudaStream_t st) {
   if (K < 0 || K > 64) return -1;
   ChunkSweeps sw = {};
   for (int k = 0; k < K; ++k) {
     sw.dO[k] = dO_ptrs[k];
     sw.ps[k] = ps_ptrs[k];
     sw.dss[k] = dss_ptrs[k];
+    sw.dcg[k] = dglx ? (const bf16*)dcg_ptrs[k] : nullptr;
     sw.bs_vec[k] = sw_bs_vec[k];
     sw.bs_sca[k] = sw_bs_sca[k];
   }
@@ -422,7 +447,7 @@ int dmb_wave_chunk_finish(const float* DOf, const float* DLf, const float* o_f, 
 #define GO(D, T)                                                                                                 \
   chunk_finish_kernel<D, T><<<blocks, 256, 0, st>>>(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, (T*)doc, corr, lsec, \
                                                     corr_dense, lse_dense, bs_vec, bs_sca, B, R, H, sw, K,        \
-                                                    (const bf16*)q, vq)
+                                                    (const bf16*)q, vq, dglx, bs_dglx)
   if (DH == 64) {
     if (doc_bf16) GO(64, bf16); else GO(64, float);
   } else if (DH == 128) {

@@ -76,7 +76,7 @@ class _Sigs:
     dmb_cell_finish_sweeps = [_p, _i, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _f, _ll,
                               _ll, _i, _i, _i, _i, _p]
     dmb_wave_chunk_finish = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _i, _p, _p,
-                             _p, _p, _p, _p, _v, _p]
+                             _p, _p, _p, _p, _v, _p, _p, _ll, _p]
     dmb_copy_pair = [_p, _p, _p, _p, _ll, _ll, _ll, _i, _p]
     dmb_prefix_dq = [_p, _v, _p, _v, _p, _p, _v, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p]
     dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
@@ -726,7 +726,7 @@ class CudaOps(TorchOps):
                                              lsen.data_ptr(), o_f.stride(0), DLf.stride(0), B, R, h, dh,
                                              self._st()), "split_partials")
 
-    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps=None, q=None):
+    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps=None, q=None, dglx=None):
         B, R, h, dh = DOf.shape
         vec, sca = (DOf, o_f, dKp, dVp, dks, dv), (DLf, lse_f, corr, lsec)
         sweeps = sweeps or []
@@ -736,13 +736,18 @@ class CudaOps(TorchOps):
               and all(self._abs_view_ok(t, 1) and t.dtype == F32 for t in sca)
               and len({t.stride(0) for t in vec + (doc,)}) == 1 and len({t.stride(0) for t in sca}) == 1
               and len(sweeps) <= 64
-              and all(self._abs_view_ok(g, 2) and g.shape == DOf.shape and self._abs_view_ok(ps, 1)
-                      and self._abs_view_ok(ds, 1) and ps.shape == DLf.shape and ps.stride(0) == ds.stride(0)
-                      for g, ps, ds in sweeps)
-              and (not sweeps or (q is not None and q.dtype == BF16 and _dense_tail(q, 2) and q.shape == DOf.shape)))
+              and all(self._abs_view_ok(t[0], 2) and t[0].shape == DOf.shape and self._abs_view_ok(t[1], 1)
+                      and self._abs_view_ok(t[2], 1) and t[1].shape == DLf.shape and t[1].stride(0) == t[2].stride(0)
+                      for t in sweeps)
+              and (not sweeps or (q is not None and q.dtype == BF16 and _dense_tail(q, 2) and q.shape == DOf.shape))
+              and (dglx is None or (bool(sweeps) and dglx.dtype == F32 and dglx.shape == (B, R, 2 * h * dh)
+                                    and _dense_tail(dglx, 2)
+                                    and all(len(t) == 4 and t[3].dtype == BF16 and t[3].shape == (B, R, 4 * h * dh)
+                                            and _dense_tail(t[3], 2) and t[3].stride(0) == 4 * t[0].stride(0)
+                                            for t in sweeps))))
         if not ok:
             self._fell_back("chunk_finish")
-            return super().chunk_finish(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps, q)
+            return super().chunk_finish(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps, q, dglx)
         cv = torch.empty(B, R, h, dtype=F32, device=DOf.device)
         ls = torch.empty(B, R, h, dtype=F32, device=DOf.device)
         K = len(sweeps)
@@ -751,12 +756,15 @@ class CudaOps(TorchOps):
             DOf.data_ptr(), DLf.data_ptr(), o_f.data_ptr(), lse_f.data_ptr(), dKp.data_ptr(), dVp.data_ptr(),
             dks.data_ptr(), dv.data_ptr(), doc.data_ptr(), int(doc.dtype == BF16), corr.data_ptr(), lsec.data_ptr(),
             cv.data_ptr(), ls.data_ptr(), DOf.stride(0), DLf.stride(0), B, R, h, dh, K,
-            arr(ctypes.c_void_p, [g.data_ptr() for g, _, _ in sweeps]),
-            arr(ctypes.c_void_p, [ps.data_ptr() for _, ps, _ in sweeps]),
-            arr(ctypes.c_void_p, [ds.data_ptr() for _, _, ds in sweeps]),
-            arr(ctypes.c_longlong, [g.stride(0) for g, _, _ in sweeps]),
-            arr(ctypes.c_longlong, [ps.stride(0) for _, ps, _ in sweeps]),
-            q.data_ptr() if K else None, _tv(q) if K else TView(0, 0), self._st()), "chunk_finish")
+            arr(ctypes.c_void_p, [t[0].data_ptr() for t in sweeps]),
+            arr(ctypes.c_void_p, [t[1].data_ptr() for t in sweeps]),
+            arr(ctypes.c_void_p, [t[2].data_ptr() for t in sweeps]),
+            arr(ctypes.c_longlong, [t[0].stride(0) for t in sweeps]),
+            arr(ctypes.c_longlong, [t[1].stride(0) for t in sweeps]),
+            q.data_ptr() if K else None, _tv(q) if K else TView(0, 0),
+            arr(ctypes.c_void_p, [t[3].data_ptr() for t in sweeps]) if dglx is not None else None,
+            dglx.data_ptr() if dglx is not None else None, dglx.stride(0) if dglx is not None else 0,
+            self._st()), "chunk_finish")
         return cv, ls
 
     def copy_pair(self, d0, s0, d1, s1):

@@ -190,15 +190,23 @@ class TorchOps:
             corrn_dense.copy_(corrn)
         lsen.copy_(lse_n)
 
-    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps=None, q=None):
+    def chunk_finish(self, DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, doc, corr, lsec, sweeps=None, q=None, dglx=None):
         """End of a wavefront chunk's backward, all arguments views of the chunk's rows in per-layer arrays:
         the far read's accumulated gradient becomes the prefix kernels' inputs (doc = DOf, corr = DOf . o_f -
         DLf, lsec = lse_f) and the pending gradient of the chunk's raw rows moves out (dks += dKp, dv += dVp,
         dKp = dVp = 0).  `sweeps`: (d o rows, p_self, dss) of every sweep of the chunk whose raw-row gradients
-        `win_tail_bwd` deferred: dv += sum p_self dO, dks += (sum dss) q.  Returns contiguous copies of (corr, lse_f)."""
-        for g, ps, dss in reversed(sweeps or []):
+        `win_tail_bwd` deferred: dv += sum p_self dO, dks += (sum dss) q.  With `dglx` ([B, R, 2d] view, written) every
+        sweep tuple carries a 4th entry, the sweep's stashed d(ctx / gate logits) rows [B, R, 4d], whose gate columns
+        [2d, 4d) summed over the sweeps are the gates' x-logit gradient.  Returns contiguous copies of (corr, lse_f)."""
+        if dglx is not None:
+            dglx.zero_()
+        for t in reversed(sweeps or []):
+            g, ps, dss = t[:3]
             dv += ps.unsqueeze(-1) * g.float()
             dks += dss.unsqueeze(-1) * q.float()
+            if dglx is not None:
+                half = t[3].shape[-1] // 2
+                dglx += t[3][..., half:].float()
         cv = ((DOf * o_f).sum(-1) - DLf).contiguous()
         doc.copy_(DOf)
         corr.copy_(cv)

@@ -405,19 +405,29 @@ def test_chunk_finish(ops, dh, doc_dtype):
     out[r] = False
     for x, y, n_ in zip(a, before, names):                       # rows of other chunks are untouched
         assert torch.equal(x[:, out], y[:, out]), n_
-    # with the raw-row gradients of three sweeps deferred to this kernel (views into windows of different widths)
-    a, b_ = arrays(), arrays()
-    q = rnd(B, T, H, dh, seed=30)
-    sweeps = []
-    for k, (G, g) in enumerate(((3, 2), (2, 0), (1, 0))):
-        d_o, st = f(B, G * c, H, dh, seed=40 + k), f(2, B, G * c, H, seed=50 + k)
-        gr = slice(g * c, (g + 1) * c)
-        sweeps.append((d_o[:, gr], st[0][:, gr], st[1][:, gr]))
-    cv, ls = ops.chunk_finish(*[t[:, r] for t in a], sweeps=sweeps, q=q[:, r])
-    cr, lr = REF.chunk_finish(*[t[:, r] for t in b_], sweeps=sweeps, q=q[:, r])
-    close(cv, cr, rtol=1e-4, atol=1e-4, what="corr (sweeps)")
-    for x, y, n_ in zip(a, b_, names):
-        close(x, y, rtol=1e-2, atol=1e-4, what=n_ + " (sweeps)")
+    # with the raw-row gradients of three sweeps deferred to this kernel (views into windows of different widths), and
+    # with the gates' x-logit gradient summed from the sweeps' stashed d(ctx / gate logits) rows
+    for with_gates in (False, True):
+        a, b_ = arrays(), arrays()
+        q = rnd(B, T, H, dh, seed=30)
+        d = H * dh
+        sweeps = []
+        for k, (G, g) in enumerate(((3, 2), (2, 0), (1, 0))):
+            d_o, st = f(B, G * c, H, dh, seed=40 + k), f(2, B, G * c, H, seed=50 + k)
+            gr = slice(g * c, (g + 1) * c)
+            extra = (rnd(B, G * c, 4 * d, seed=60 + k)[:, gr],) if with_gates else ()
+            sweeps.append((d_o[:, gr], st[0][:, gr], st[1][:, gr]) + extra)
+        gl = [torch.full((B, T, 2 * d), 9.0, device=DEV) for _ in range(2)] if with_gates else [None, None]
+        view = lambda t: t[:, r] if t is not None else None
+        cv, ls = ops.chunk_finish(*[t[:, r] for t in a], sweeps=sweeps, q=q[:, r], dglx=view(gl[0]))
+        cr, lr = REF.chunk_finish(*[t[:, r] for t in b_], sweeps=sweeps, q=q[:, r], dglx=view(gl[1]))
+        close(cv, cr, rtol=1e-4, atol=1e-4, what="corr (sweeps)")
+        for x, y, n_ in zip(a, b_, names):
+            close(x, y, rtol=1e-2, atol=1e-4, what=n_ + " (sweeps)")
+        if with_gates:
+            close(gl[0], gl[1], rtol=1e-3, atol=1e-3, what="dglx")
+            assert (gl[0][:, out] == 9.0).all()
+    assert not ops.fallbacks.get("chunk_finish") or DEV == "cpu"
 
 
 def test_copy_pair(ops):
