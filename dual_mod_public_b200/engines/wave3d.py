@@ -276,6 +276,7 @@ class Wave3DEngine(WaveScanEngine):
         qw = S.q_r[:, w]
         o_n, lse_n = ops.win_near_fwd(qw, S.Kc, S.Vc, lo * C, (lo - K + 1) * C, C, S.scale, self.window)
         self._join_beside()
+        # (merging in the read kernel's epilogue, `win_near_merged`, measured slower than this kernel of its own)
         o_c, lse_c, w_f, w_n = ops.merge_partials(self.ofar_all[:, w], self.lsefar_all[:, w], o_n, lse_n)
         o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale, self.window)
         # every window chunk's new rows replace the old ones (all reads of this step are done)

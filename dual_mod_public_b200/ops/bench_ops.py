@@ -154,6 +154,28 @@ def main():
             ops.ATTN_TC = type(ops).ATTN_TC
             ops.dkv_rows128(was)
             ops.tc_check()
+    if want("near"):
+        # the near read of a full window of the 1.3B recipe: 16 sequences x 36 heads of 64, 8 chunks of 64 rows, each
+        # reading the 7 chunks before it; single chunks per tile against two chunks per 128-row tile, and the merge
+        # with the stored far partials as a kernel of its own against the read kernel's epilogue
+        Bn, hn, Gn, Kn, Cn = 16, 36, 8, 8, 64
+        lo_c = 16
+        Tn = (lo_c + Gn) * Cn
+        qn, Kt, Vt = rnd(Bn, Tn, hn, 64), rnd(Bn, Tn, hn, 64), rnd(Bn, Tn, hn, 64)
+        of_, lf_ = rnd(Bn, Tn, hn, 64, dtype=torch.float32), rnd(Bn, Tn, hn, dtype=torch.float32)
+        wn_ = slice(lo_c * Cn, (lo_c + Gn) * Cn)
+        a_ = (qn[:, wn_], Kt, Vt, lo_c * Cn, (lo_c - Kn + 1) * Cn, Cn, 0.125, 0)
+        fl = 4.0 * Bn * hn * 64 * Gn * Cn * (Kn - 1) * Cn
+        for pairs in (False, True):
+            ops.NEAR_PAIRS = pairs
+            tag2 = "two chunks per tile" if pairs else "one chunk per tile"
+            report(f"near read, {tag2}", T(lambda: ops.win_near_fwd(*a_)), flops=fl)
+            report(f"near read + merge kernel, {tag2}",
+                   T(lambda: ops.merge_partials(of_[:, wn_], lf_[:, wn_], *ops.win_near_fwd(*a_))), flops=fl)
+            report(f"near read merged in its epilogue, {tag2}",
+                   T(lambda: ops.win_near_merged(*a_, of_[:, wn_], lf_[:, wn_], keep_near=True)), flops=fl)
+        ops.NEAR_PAIRS = type(ops).NEAR_PAIRS
+        ops.tc_check()
     if want("bar"):
         # one lower-right causal read of a block of 1024 query rows over 4096 tape rows (the window read of a
         # layer-batched wavefront step), next to torch's fused attention backends on the same mask

@@ -51,8 +51,29 @@ struct Cfg {
 
 struct Geo {
   int H, Lq, lo, hi, qbase, grow, window, causal, causal_excl, tiles_q, o_bf16;
+  int pshift;      // > 0 (BM = 128 only): the tile holds TWO 64-row groups; rows 64.. read keys shifted by pshift rows
   float scale_log2;
+  // optional merge of this read with another partial of the same rows (o_f, lse_f: fp32, rows by absolute position
+  // from the launch's first row, batch strides mf_bs_vec / mf_bs_sca): the outputs become the merged partial
+  //   lse_c = log(exp(lse_f) + exp(lse_n)), o_c = w_f o_f + w_n o_n, w = exp(lse - lse_c)
+  // with w_f / w_n written beside them and, when on != null, this read's own (o_n, lse_n) as well
+  const float* mf_o;
+  const float* mf_lse;
+  long long mf_bs_vec, mf_bs_sca;
+  float* m_wf;
+  float* m_wn;
+  float* m_on;
+  float* m_lsen;
 };
+
+// one row's merge: returns lse_c and the two weights
+__device__ __forceinline__ float merge_weights(float lf, float ln, float& wf, float& wn) {
+  const float mm = fmaxf(lf, ln);
+  const float lc = mm + __logf(__expf(lf - mm) + __expf(ln - mm));
+  wf = __expf(lf - lc);
+  wn = __expf(ln - lc);
+  return lc;
+}
 
 template <int DH, int BM>
 __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kernel(
@@ -90,7 +111,9 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
   const int row0 = qt * BM, rows_here = min(BM, g.Lq - row0);
   const int lo_z = max(0, g.lo + z * g.grow), hi_z = g.hi + z * g.grow;
   const int qpos0 = g.qbase + z * g.grow + row0;                 // absolute position of the tile's first row
-  int k_begin = lo_z, k_end = hi_z;
+  // two groups in one tile: the union of their key ranges streams through, each row masks to its own
+  const int lo_2 = max(0, g.lo + z * g.grow + g.pshift);          // second group's first key (pshift > 0)
+  int k_begin = lo_z, k_end = hi_z + g.pshift;
   if (g.window) k_begin = max(k_begin, qpos0 - g.window + 1);
   if (g.causal) k_end = min(k_end, qpos0 + rows_here - 1 - g.causal_excl + 1);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + KT - 1) / KT : 0;
@@ -316,6 +339,29 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
           const float* O = half ? OB : OA;
           const float inv = l > 0.f ? 1.f / l : 0.f;
           const long long orow = ((long long)((b * G_ + z) * g.Lq + row0 + row) * g.H + h);
+          const float ln = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : DMB_NEG;
+          if (g.mf_o) {                                      // fp32 outputs: the merged partial
+            const long long wrow = (long long)z * g.Lq + row0 + row;          // row of the launch's window
+            const float* of = g.mf_o + b * g.mf_bs_vec + (wrow * g.H + h) * DH;
+            float wf, wn;
+            const float lc = merge_weights(g.mf_lse[b * g.mf_bs_sca + wrow * g.H + h], ln, wf, wn);
+#pragma unroll
+            for (int j = 0; j < DH / 8; ++j) {
+              const int d = 8 * j + 2 * t4;
+              const float2 f2 = *reinterpret_cast<const float2*>(of + d);
+              const float2 n2 = make_float2(O[2 * j] * inv, O[2 * j + 1] * inv);
+              *reinterpret_cast<float2*>(reinterpret_cast<float*>(o_out) + orow * DH + d) =
+                  make_float2(wf * f2.x + wn * n2.x, wf * f2.y + wn * n2.y);
+              if (g.m_on) *reinterpret_cast<float2*>(g.m_on + orow * DH + d) = n2;
+            }
+            if (t4 == 0) {
+              lse_out[orow] = lc;
+              g.m_wf[orow] = wf;
+              g.m_wn[orow] = wn;
+              if (g.m_lsen) g.m_lsen[orow] = ln;
+            }
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < DH / 8; ++j) {
             const int d = 8 * j + 2 * t4;
@@ -326,14 +372,15 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
               *reinterpret_cast<float2*>(reinterpret_cast<float*>(o_out) + orow * DH + d) =
                   make_float2(O[2 * j] * inv, O[2 * j + 1] * inv);
           }
-          if (t4 == 0) lse_out[orow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : DMB_NEG;
+          if (t4 == 0) lse_out[orow] = ln;
         }
       }
     } else {
     const int row = q * 32 + lane;
     const bool has_row = true;
     const int qpos = qpos0 + row;
-    int jlo = lo_z, jhi = hi_z;                              // allowed keys of this row: jlo <= j < jhi
+    const bool second = g.pshift && row >= 64;
+    int jlo = second ? lo_2 : lo_z, jhi = hi_z + (second ? g.pshift : 0);   // allowed keys of this row: jlo <= j < jhi
     if (g.window) jlo = max(jlo, qpos - g.window + 1);
     if (g.causal) jhi = min(jhi, qpos - g.causal_excl + 1);
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
@@ -367,7 +414,8 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
       tc_fence_after();
       // a tile needs per-element masks only where it crosses a row's range
       const bool mask = (k0 + KT > k_end) || (k0 < lo_z) || (g.causal && k0 + KT - 1 > qpos0 - g.causal_excl) ||
-                        (g.window && k0 < qpos0 + rows_here - 1 - g.window + 1);
+                        (g.window && k0 < qpos0 + rows_here - 1 - g.window + 1) ||
+                        (g.pshift && (k0 + KT > hi_z || k0 < lo_2));
       float mx = -INFINITY;
 #pragma unroll 1
       for (int c0 = 0; c0 < KT; c0 += 64) {                 // two loads in flight per wait
@@ -442,7 +490,26 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
     if (has_row && row < rows_here && (alive || n_tiles == 0)) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const long long orow = ((long long)((b * (int)(gridDim.z / g.tiles_q) + z) * g.Lq + row0 + row) * g.H + h);
-      if (g.o_bf16) {
+      const float ln = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : DMB_NEG;
+      if (g.mf_o) {                                          // fp32 outputs: the merged partial
+        const long long wrow = (long long)z * g.Lq + row0 + row;
+        const float* of = g.mf_o + b * g.mf_bs_vec + (wrow * g.H + h) * DH;
+        float wf, wn;
+        const float lc = merge_weights(g.mf_lse[b * g.mf_bs_sca + wrow * g.H + h], ln, wf, wn);
+        float* dst = reinterpret_cast<float*>(o_out) + orow * DH;
+#pragma unroll
+        for (int d = 0; d < DH; d += 4) {
+          const float4 f4 = *reinterpret_cast<const float4*>(of + d);
+          const float4 n4 = make_float4(O[d] * inv, O[d + 1] * inv, O[d + 2] * inv, O[d + 3] * inv);
+          *reinterpret_cast<float4*>(dst + d) =
+              make_float4(wf * f4.x + wn * n4.x, wf * f4.y + wn * n4.y, wf * f4.z + wn * n4.z, wf * f4.w + wn * n4.w);
+          if (g.m_on) *reinterpret_cast<float4*>(g.m_on + orow * DH + d) = n4;
+        }
+        lse_out[orow] = lc;
+        g.m_wf[orow] = wf;
+        g.m_wn[orow] = wn;
+        if (g.m_lsen) g.m_lsen[orow] = ln;
+      } else if (g.o_bf16) {
         bf16* dst = reinterpret_cast<bf16*>(o_out) + orow * DH;
 #pragma unroll
         for (int d = 0; d < DH; d += 8)
@@ -455,7 +522,7 @@ __global__ void __launch_bounds__(NTHREADS, (DH == 64 ? 2 : 1)) attn_fwd_tc_kern
         for (int d = 0; d < DH; d += 4)
           *reinterpret_cast<float4*>(dst + d) = make_float4(O[d] * inv, O[d + 1] * inv, O[d + 2] * inv, O[d + 3] * inv);
       }
-      lse_out[orow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : DMB_NEG;
+      if (!g.mf_o) lse_out[orow] = ln;
     }
     }   // BM == 128
   }
@@ -486,7 +553,7 @@ int launch(const void* q, TView vq, int q_rows, const void* Kc, const void* Vc, 
   if ((rc = make_map_3d(&tq, q, cols, q_rows, B, vq.rs, B > 1 ? vq.bs : (long long)q_rows * vq.rs, 64, 64))) return rc;
   // rows at and beyond the end of the largest key range are outside the map: the copy engine zero-fills them
   // (an empty range for every group still needs a valid map: one row, never loaded)
-  const int k_rows = max(1, min(tape_rows, g.hi + (G - 1) * g.grow));
+  const int k_rows = max(1, min(tape_rows, g.hi + (G - 1) * g.grow + g.pshift));
   const long long kbs = B > 1 ? vc.bs : (long long)tape_rows * vc.rs;
   if ((rc = make_map_3d(&tk, Kc, cols, k_rows, B, vc.rs, kbs, 64, 64))) return rc;
   if ((rc = make_map_3d(&tv, Vc, cols, k_rows, B, vc.rs, kbs, 64, 64))) return rc;
@@ -507,14 +574,26 @@ extern "C" {
 //   keys of group z: max(0, lo + z*grow) <= j < hi + z*grow; query row i sits at qbase + z*grow + i;
 //   causal: j <= position - causal_excl; window > 0: j > position - window
 //   bm: 64 or 128 query rows per CTA.  gerr: device int, set to 1 if a pipeline wait ran out.
+//   mf_o, mf_lse (optional): another partial of the same rows (fp32, rows by absolute position from the launch's
+//   first row, batch strides mf_bs_vec / mf_bs_sca); the outputs o / lse are then the MERGED partial, m_wf / m_wn
+//   [B, G, Lq, H] receive the two weights and m_on / m_lsen (optional, dense like o / lse) this read's own partial.
 // Requirements: 16-byte aligned pointers, strides multiples of 8 elements, dh 64 or 128.
-int dmb_attn_fwd_tc(const void* q, TView vq, int q_rows, const void* Kc, const void* Vc, TView vc, int tape_rows,
-                    void* o, int o_bf16, float* lse, int B, int G, int Lq, int H, int dh, int lo, int hi, int qbase,
-                    int grow, float scale, int window, int causal, int causal_excl, int bm, int* gerr,
-                    cudaStream_t st) {
+int dmb_attn_fwd_tc_merged(const void* q, TView vq, int q_rows, const void* Kc, const void* Vc, TView vc, int tape_rows,
+                           void* o, int o_bf16, float* lse, int B, int G, int Lq, int H, int dh, int lo, int hi,
+                           int qbase, int grow, float scale, int window, int causal, int causal_excl, int bm,
+                           int pair_shift, const float* mf_o, const float* mf_lse, long long mf_bs_vec,
+                           long long mf_bs_sca, float* m_wf, float* m_wn, float* m_on, float* m_lsen, int* gerr,
+                           cudaStream_t st) {
   if (!encode_fn()) return -10;
   if ((dh != 64 && dh != 128) || (bm != 64 && bm != 128) || Lq <= 0 || B <= 0 || G <= 0) return -1;
-  Geo g;
+  // pair_shift > 0: a "group" is two 64-row groups of one 128-row tile whose key ranges differ by pair_shift rows
+  if (pair_shift && (bm != 128 || Lq != 128 || causal)) return -1;
+  // merged outputs are fp32 and need both weight arrays
+  if (mf_o && (o_bf16 || !mf_lse || !m_wf || !m_wn || (m_on != nullptr) != (m_lsen != nullptr))) return -1;
+  Geo g = {};
+  g.pshift = pair_shift;
+  g.mf_o = mf_o; g.mf_lse = mf_lse; g.mf_bs_vec = mf_bs_vec; g.mf_bs_sca = mf_bs_sca;
+  g.m_wf = m_wf; g.m_wn = m_wn; g.m_on = m_on; g.m_lsen = m_lsen;
   g.H = H; g.Lq = Lq; g.lo = lo; g.hi = hi; g.qbase = qbase; g.grow = grow; g.window = window;
   g.causal = causal; g.causal_excl = causal_excl; g.tiles_q = (Lq + bm - 1) / bm;
   g.o_bf16 = o_bf16; g.scale_log2 = scale * 1.4426950408889634f;
@@ -524,6 +603,16 @@ int dmb_attn_fwd_tc(const void* q, TView vq, int q_rows, const void* Kc, const v
   }
   if (bm == 64) return launch<128, 64>(q, vq, q_rows, Kc, Vc, vc, tape_rows, o, lse, B, G, g, gerr, st);
   return launch<128, 128>(q, vq, q_rows, Kc, Vc, vc, tape_rows, o, lse, B, G, g, gerr, st);
+}
+
+// the plain read (no merge)
+int dmb_attn_fwd_tc(const void* q, TView vq, int q_rows, const void* Kc, const void* Vc, TView vc, int tape_rows,
+                    void* o, int o_bf16, float* lse, int B, int G, int Lq, int H, int dh, int lo, int hi, int qbase,
+                    int grow, float scale, int window, int causal, int causal_excl, int bm, int pair_shift,
+                    int* gerr, cudaStream_t st) {
+  return dmb_attn_fwd_tc_merged(q, vq, q_rows, Kc, Vc, vc, tape_rows, o, o_bf16, lse, B, G, Lq, H, dh, lo, hi, qbase, grow,
+                                scale, window, causal, causal_excl, bm, pair_shift, nullptr, nullptr, 0, 0, nullptr,
+                                nullptr, nullptr, nullptr, gerr, st);
 }
 
 }  // extern "C"

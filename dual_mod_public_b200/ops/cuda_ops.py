@@ -72,6 +72,8 @@ class _Sigs:
     dmb_cell_finish = [_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
     dmb_wave_merge_fwd = [_p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]
     dmb_wave_split_bwd = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p]
+    dmb_attn_fwd_tc_merged = [_p, _v, _i, _p, _p, _v, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
+                              _i, _i, _p, _p, _ll, _ll, _p, _p, _p, _p, _p, _p]
     dmb_attn_dkv_rows128 = [_i]
     dmb_cell_finish_sweeps = [_p, _i, _p, _p, _v, _p, _v, _p, _v, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _f, _ll,
                               _ll, _i, _i, _i, _i, _p]
@@ -82,7 +84,7 @@ class _Sigs:
     dmb_attn_dq_tc = [_p, _v, _p, _v, _i, _p, _p, _v, _i, _p, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]
     dmb_attn_dkv_tc = [_p, _p, _p, _p, _i, _p, _p, _v, _i, _p, _p, _v, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p]
     dmb_attn_fwd_tc = [_p, _v, _i, _p, _p, _v, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
-                       _i, _p, _p]
+                       _i, _i, _p, _p]
 
 
 BF16 = torch.bfloat16
@@ -435,17 +437,23 @@ class CudaOps(TorchOps):
     ATTN_TC = (frozenset(("fwd", "dq", "dkv")) if _tc_env in ("1", "all") else
                frozenset() if _tc_env in ("0", "", "none") else frozenset(x.strip() for x in _tc_env.split(",")))
 
+    # near reads of a window with two chunks per 128-row tile (the union of their key ranges streams through, each half
+    # masks to its own): measured no faster than one chunk per 64-row tile at the 1.3B recipe's window (192 vs 184 us),
+    # so off by default
+    NEAR_PAIRS = os.environ.get("DMB_NEAR_PAIRS", "0") == "1"
+
     def _tc(self, side):
         """ATTN_TC may also be set to True / False on an instance (tests, benchmarks): all sides / none."""
         a = self.ATTN_TC
         return a if isinstance(a, bool) else side in a
 
     def attn_fwd_tc(self, q, Kc, Vc, lo, hi, qbase, scale, window=0, causal=False, causal_excl=1, Lq=None, G=1,
-                    grow=0, bm=None, out_dtype=F32, out=None):
+                    grow=0, bm=None, out_dtype=F32, out=None, pair_shift=0):
         """Attention forward on tcgen05 (csrc/attn_tc.cu).  q: [B, rows, h, dh] bf16 view; group z (of G) takes
         its rows [z*grow, z*grow + Lq), sits at positions qbase + z*grow + i and reads the tape rows
         max(0, lo + z*grow) <= j < hi + z*grow of Kc / Vc [B, T, h, dh], under the causal rule
-        j <= position - causal_excl and the sliding window j > position - window.
+        j <= position - causal_excl and the sliding window j > position - window.  `pair_shift` (with Lq = bm = 128):
+        each group is two 64-row groups sharing a tile; the second one's key range is shifted by pair_shift rows.
         Returns (o [B, G, Lq, h, dh] in out_dtype, lse [B, G, Lq, h] fp32)."""
         B, rows, h, dh = q.shape
         Lq = rows if Lq is None else Lq
@@ -459,7 +467,7 @@ class CudaOps(TorchOps):
         self._ck(self.lib.dmb_attn_fwd_tc(
             q.data_ptr(), _tv(q), rows, Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), Kc.shape[1], o.data_ptr(),
             int(out_dtype == BF16), lse.data_ptr(), B, G, Lq, h, dh, lo, hi, qbase, grow, scale, window,
-            int(causal), causal_excl, bm, self._tc_err.data_ptr(), self._st()), "attn_fwd_tc")
+            int(causal), causal_excl, bm, pair_shift, self._tc_err.data_ptr(), self._st()), "attn_fwd_tc")
         return o, lse
 
     def attn_dq_tc(self, q, do_c, Kc, Vc, lo, hi, qbase, scale, window, lse, corr, dq, G=1, grow=0, accumulate=True):
@@ -797,13 +805,43 @@ class CudaOps(TorchOps):
         o_n = torch.empty(B, rows, h, dh, dtype=F32, device=q_win.device)
         lse_n = torch.empty(B, rows, h, dtype=F32, device=q_win.device)
         if self._tc("fwd") and C == 64 and self._tc_ok(q_win, Kc, Vc):
-            self.attn_fwd_tc(q_win, Kc, Vc, lo, pos0, pos0, scale, window, Lq=C, G=rows // C, grow=C, bm=64,
-                             out=(o_n, lse_n))
+            G = rows // C
+            if dh == 64 and G % 2 == 0 and self.NEAR_PAIRS:
+                # two window chunks per 128-row tile: their key ranges overlap in all but one chunk each
+                self.attn_fwd_tc(q_win, Kc, Vc, lo, pos0, pos0, scale, window, Lq=128, G=G // 2, grow=128, bm=128,
+                                 out=(o_n, lse_n), pair_shift=64)
+            else:
+                self.attn_fwd_tc(q_win, Kc, Vc, lo, pos0, pos0, scale, window, Lq=C, G=G, grow=C, bm=64,
+                                 out=(o_n, lse_n))
             return o_n, lse_n
         self._ck(self.lib.dmb_prefix_fwd(q_win.data_ptr(), _tv(q_win), Kc.data_ptr(), Vc.data_ptr(), _tv(Kc),
                                          o_n.data_ptr(), lse_n.data_ptr(), B, C, h, dh, lo, pos0, scale, window,
                                          rows // C, C, 0, self._st()), "win_near_fwd")
         return o_n, lse_n
+
+    def win_near_merged(self, q_win, Kc, Vc, pos0, lo, C, scale, window, o_f, lse_f, keep_near=True):
+        """The near read of a window merged with the chunks' far partials in the read kernel's epilogue."""
+        B, rows, h, dh = q_win.shape
+        G = rows // C
+        ok = (self._tc("fwd") and C == 64 and self._win_ok(q_win, C, Kc) and self._tc_ok(q_win, Kc, Vc)
+              and self._abs_view_ok(o_f, 2) and self._abs_view_ok(lse_f, 1) and o_f.shape == (B, rows, h, dh))
+        if not ok:
+            self._fell_back("win_near_merged")
+            return super().win_near_merged(q_win, Kc, Vc, pos0, lo, C, scale, window, o_f, lse_f, keep_near)
+        dev = q_win.device
+        o_c = torch.empty(B, rows, h, dh, dtype=F32, device=dev)
+        lse_c, w_f, w_n = (torch.empty(B, rows, h, dtype=F32, device=dev) for _ in range(3))
+        o_n = torch.empty(B, rows, h, dh, dtype=F32, device=dev) if keep_near else None
+        lse_n = torch.empty(B, rows, h, dtype=F32, device=dev) if keep_near else None
+        pair = dh == 64 and G % 2 == 0 and self.NEAR_PAIRS
+        Lq, Gz, grow, bm, shift = (128, G // 2, 128, 128, 64) if pair else (C, G, C, 64, 0)
+        self._ck(self.lib.dmb_attn_fwd_tc_merged(
+            q_win.data_ptr(), _tv(q_win), rows, Kc.data_ptr(), Vc.data_ptr(), _tv(Kc), Kc.shape[1], o_c.data_ptr(), 0,
+            lse_c.data_ptr(), B, Gz, Lq, h, dh, lo, pos0, pos0, grow, scale, window, 0, 1, bm, shift,
+            o_f.data_ptr(), lse_f.data_ptr(), o_f.stride(0), lse_f.stride(0), w_f.data_ptr(), w_n.data_ptr(),
+            o_n.data_ptr() if keep_near else None, lse_n.data_ptr() if keep_near else None,
+            self._tc_err.data_ptr(), self._st()), "win_near_merged")
+        return o_c, lse_c, w_f, w_n, o_n, lse_n
 
     def win_near_dq(self, q_win, Kc, Vc, pos0, lo, C, scale, lse_n, do_n, corr_n, dq_acc, window=0):
         ok = (self._win_ok(q_win, C, Kc, do_n) and do_n.dtype == BF16 and dq_acc.dtype == F32 and _dense_tail(dq_acc, 2)

@@ -175,6 +175,13 @@ class TorchOps:
         wf, wn = torch.exp(lse_f - lse), torch.exp(lse_n - lse)
         return wf.unsqueeze(-1) * o_f + wn.unsqueeze(-1) * o_n, lse, wf, wn
 
+    def win_near_merged(self, q_win, Kc, Vc, pos0, lo, C, scale, window, o_f, lse_f, keep_near=True):
+        """`win_near_fwd` followed by `merge_partials` with the chunks' far partials (o_f, lse_f: views by absolute
+        position): (o_c, lse_c, w_f, w_n, o_n, lse_n); the near partial is None when `keep_near` is false."""
+        o_n, lse_n = self.win_near_fwd(q_win, Kc, Vc, pos0, lo, C, scale, window)
+        o_c, lse_c, w_f, w_n = self.merge_partials(o_f, lse_f, o_n, lse_n)
+        return (o_c, lse_c, w_f, w_n) + ((o_n, lse_n) if keep_near else (None, None))
+
     def split_partials(self, do_c, dlse_c, o_f, o_c, o_n, lse_n, w_f, w_n, DOf, DLf, docn, corrn, lsen, corrn_dense=None):
         """Backward of `merge_partials`: accumulates the far gradients into DOf / DLf (+=) and writes the
         near read's (d o, corr, lse) into docn / corrn / lsen (views by absolute position); `corrn_dense`

@@ -174,6 +174,69 @@ def test_backward_key_side_matches_torch_statement(ops, dh, window, reader_tiles
     _close(dV, dV_ref, "dV, bounded readers")
 
 
+@pytest.mark.parametrize("G,lo_c,K_sw,window", [(2, 4, 3, 0), (4, 5, 8, 0), (8, 8, 8, 0), (4, 6, 4, 150), (6, 3, 8, 0), (2, 0, 3, 0)])
+def test_near_read_with_two_chunks_per_tile(ops, G, lo_c, K_sw, window):
+    """An even number of window chunks: the near read pairs them into 128-row tiles (the union of the two key
+    ranges streams through, each half masks to its own); against the per-chunk statement and the unpaired launch."""
+    from dual_mod_public_b200.ops.torch_ops import TorchOps
+    ref = TorchOps()
+    B, h, dh, C = 2, 3, 64, 64
+    T = (lo_c + G) * C
+    q_all, K, V = rnd(B, T, h, dh, seed=41), rnd(B, T, h, dh, seed=42), rnd(B, T, h, dh, seed=43)
+    scale = dh ** -0.5
+    w = slice(lo_c * C, (lo_c + G) * C)
+    args = (q_all[:, w], K, V, lo_c * C, (lo_c - K_sw + 1) * C, C, scale, window)
+    o_ref, lse_ref = ref.win_near_fwd(*args)
+    o1, lse1 = ops.win_near_fwd(*args)
+    ops.NEAR_PAIRS = True
+    try:
+        o, lse = ops.win_near_fwd(*args)
+    finally:
+        ops.NEAR_PAIRS = type(ops).NEAR_PAIRS
+    ops.tc_check()
+    _close(o, o_ref, "near o (pairs)")
+    live = lse_ref > -1e29
+    _close(lse[live], lse_ref[live], "near lse (pairs)")
+    assert (lse[~live] < -1e29).all()
+    _close(o, o1, "pairs vs single chunks", tol=1e-2)
+
+
+@pytest.mark.parametrize("G,lo_c,K_sw,keep_near", [(4, 5, 8, True), (3, 4, 3, True), (8, 8, 8, False), (2, 0, 3, True)])
+def test_near_read_merged_with_far_partials_in_the_epilogue(ops, G, lo_c, K_sw, keep_near):
+    """`win_near_merged` (the read kernel's epilogue merges with stored far partials) against the near read followed
+    by the merge statement; even group counts run as pairs, odd ones as single chunks."""
+    from dual_mod_public_b200.ops.torch_ops import TorchOps
+    ref = TorchOps()
+    B, h, dh, C = 2, 3, 64, 64
+    T = (lo_c + G + 1) * C
+    q_all, K, V = rnd(B, T, h, dh, seed=51), rnd(B, T, h, dh, seed=52), rnd(B, T, h, dh, seed=53)
+    ofar = rnd(B, T, h, dh, seed=54).float()
+    lsefar = rnd(B, T, h, seed=55).float() + 2.0
+    lsefar[:, :C] = -1e30                                    # chunks without a far prefix carry an empty partial
+    scale = dh ** -0.5
+    w = slice(lo_c * C, (lo_c + G) * C)
+    args = (q_all[:, w], K, V, lo_c * C, (lo_c - K_sw + 1) * C, C, scale, 0, ofar[:, w], lsefar[:, w])
+    want = ref.win_near_merged(*args, keep_near=keep_near)
+    ops.NEAR_PAIRS = G % 2 == 0
+    try:
+        got = ops.win_near_merged(*args, keep_near=keep_near)
+    finally:
+        ops.NEAR_PAIRS = type(ops).NEAR_PAIRS
+    ops.tc_check()
+    assert not ops.fallbacks.get("win_near_merged")
+    names = ("o_c", "lse_c", "w_f", "w_n", "o_n", "lse_n")
+    for a, b_, n_ in zip(got, want, names):
+        if b_ is None:
+            assert a is None, n_
+            continue
+        if n_.startswith("lse"):
+            live = b_ > -1e29
+            _close(a[live], b_[live], n_)
+            assert (a[~live] < -1e29).all(), n_
+        else:
+            _close(a, b_, n_)
+
+
 def test_window_group_launches_match_the_per_chunk_statement(ops, reader_tiles):
     """The wavefront engine's one-launch-per-window forms (grid z = chunk of the window)."""
     from dual_mod_public_b200.ops.torch_ops import TorchOps
