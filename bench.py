@@ -219,6 +219,7 @@ def run_ours(args):
                        "ms_per_step": round(ms_e2e, 2),
                        "h2d_bytes_per_step": tr.h2d_bytes_per_step(), "d2h_bytes_per_step": tr.d2h_bytes_per_step()},
                "gpu_launches": int(launches), "torch_fallbacks": dict(getattr(ops, "fallbacks", {})),
+               "library_gemm_calls_while_recording": int(getattr(ops, "lib_gemms", 0)),
                "clocks": clocks,
                "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}
         if overlap is not None:

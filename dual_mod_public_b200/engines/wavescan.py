@@ -573,11 +573,11 @@ class WaveScanEngine:
         if not P.factored:
             return ops.linear(o2, P.W_pack)
         B, c, d = o2.shape
-        t = ops.linear(o2, P.D_all).view(B * c, -1)
+        t = ops.linear(o2, P.D_all, narrow=True).view(B * c, -1)
         raw = torch.empty(B, c, 4 * d, dtype=o2.dtype, device=o2.device)
         raw2 = raw.view(B * c, 4 * d)
         for i, U in enumerate(P.U):
-            ops.linear(t[:, P.roff[i]:P.roff[i + 1]], U, out=raw2[:, i * d:(i + 1) * d])
+            ops.linear(t[:, P.roff[i]:P.roff[i + 1]], U, out=raw2[:, i * d:(i + 1) * d], narrow=True)
         return raw
 
     def _pack_linear_dx(self, P, dcg, dt_out=None):
@@ -591,11 +591,13 @@ class WaveScanEngine:
         dcg2 = dcg.view(B * c, d4)
         dt = dt_out if dt_out is not None else torch.empty(B * c, P.roff[-1], dtype=dcg.dtype, device=dcg.device)
         for i, U in enumerate(P.U):
-            ops.linear_dx(dcg2[:, i * d:(i + 1) * d], U, out=dt[:, P.roff[i]:P.roff[i + 1]])
-        return ops.linear_dx(dt, P.D_all).view(B, c, d)
+            ops.linear_dx(dcg2[:, i * d:(i + 1) * d], U, out=dt[:, P.roff[i]:P.roff[i + 1]], narrow=True)
+        return ops.linear_dx(dt, P.D_all, narrow=True).view(B, c, d)
 
     def _vctx_linear(self, P, vin):
-        return self.ops.linear(vin, P.W_vctx) if not P.factored else self.ops.linear(self.ops.linear(vin, P.Dv), P.Uv)
+        if not P.factored:
+            return self.ops.linear(vin, P.W_vctx)
+        return self.ops.linear(self.ops.linear(vin, P.Dv, narrow=True), P.Uv, narrow=True)
 
     def _refine_fwd(self, S, r, o, ssq, out=None):
         """(k'', v'') rows [B, c, h, dh] from the read `o` of the rows `r` (key rotated), written into `out`
@@ -650,15 +652,15 @@ class WaveScanEngine:
             vin.view(B, c, d).copy_(ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam))
             if P.factored:
                 # stashes of the factored deferred gradients: down outputs and their gradients
-                ops.linear(vin, P.Dv, out=S.tv_stash[rows])
-                ops.linear_dx(dvc.view(n, d), P.Uv, out=S.dtv_stash[rows])
-                ops.linear_dx(S.dtv_stash[rows], P.Dv, out=dvin.view(n, d))
+                ops.linear(vin, P.Dv, out=S.tv_stash[rows], narrow=True)
+                ops.linear_dx(dvc.view(n, d), P.Uv, out=S.dtv_stash[rows], narrow=True)
+                ops.linear_dx(S.dtv_stash[rows], P.Dv, out=dvin.view(n, d), narrow=True)
             else:
                 dvin.copy_(ops.linear_dx(dvc, P.W_vctx))
             du_hat = ops.mrk_vin_bwd(dvin, raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam, dcg, S.dvgx[:, r])
             du = self._pack_linear_dx(P, dcg, S.dt_stash[rows] if P.factored else None)
             if P.factored:
-                ops.linear(S.u_stash[rows], P.D_all, out=S.t_stash[rows])
+                ops.linear(S.u_stash[rows], P.D_all, out=S.t_stash[rows], narrow=True)
             return ops.rmsn_bwd(du, o2, ssq, residual=residual, extra=du_hat)
         if self.family == "packed":
             n = B * c
@@ -669,7 +671,7 @@ class WaveScanEngine:
             rows = slice(stash_row, stash_row + n)
             du = self._pack_linear_dx(S.P, dcg, S.dt_stash[rows] if S.P.factored else None)
             if S.P.factored:
-                ops.linear(S.u_stash[rows], S.P.D_all, out=S.t_stash[rows])
+                ops.linear(S.u_stash[rows], S.P.D_all, out=S.t_stash[rows], narrow=True)
             return ops.rmsn_bwd(du, o.reshape(B, c, d), ssq, residual=residual)
         from ..models.rope import apply_rope
         sh = S.P.shadow

@@ -113,6 +113,7 @@ class CudaOps(TorchOps):
         self.device = torch.device(device)
         self.lib = load_library()
         self.launches = 0
+        self.lib_gemms = 0                     # plain products handed to the library GEMM (see LIB_NARROW)
         self.fallbacks = {}                    # op name -> calls that took the torch statement instead of a kernel
         self._scratch = {}
         self.gemm = None                       # set by enable_gemm()
@@ -151,7 +152,33 @@ class CudaOps(TorchOps):
         return buf
 
     # ---- GEMMs -------------------------------------------------------------------------------
-    def linear(self, x, w, bias=None, out_dtype=None, out=None):
+    # The factor products of a low-rank write law (rank 120-144: an up factor has a reduction of 2.25 k-blocks, a down
+    # factor fills half an output tile) are plain bf16 GEMMs outside this kernel's tile shapes; callers mark them
+    # `narrow` and they go to the library GEMM (torch.mm: cuBLAS).  Measured at the 1.3B recipe's window of 8192 rows
+    # (`bench_ops --only gemm_lora`): own kernel / library = 52.7 / 33.8 us (stacked down factors), 25.8 / 19.8 (one
+    # up factor), 24.0 / 17.4 (one down factor), 25.0 / 17.4 and 30.6 / 28.2 (their input gradients).
+    # DMB_GEMM_NARROW=own keeps them on the tcgen05 kernel.
+    LIB_NARROW = os.environ.get("DMB_GEMM_NARROW", "lib") == "lib"
+
+    def _lib_mm(self, a, b, out, shape):
+        """a [M, K] @ b [K, N] through the library into `out` (a [M, N] view with a dense last dim) or a new tensor."""
+        self.lib_gemms += 1
+        if out is not None:
+            return torch.mm(a, b, out=out)
+        return torch.mm(a, b).view(shape)
+
+    @staticmethod
+    def _rows2d(t):
+        if t.dim() == 2:
+            return t if t.stride(1) == 1 else None
+        return t.reshape(-1, t.shape[-1]) if t.is_contiguous() else None
+
+    def linear(self, x, w, bias=None, out_dtype=None, out=None, narrow=False):
+        if (narrow and self.LIB_NARROW and bias is None and x.is_cuda and x.dtype == BF16 and w.dtype == BF16
+                and out_dtype in (None, BF16) and (out is None or out.dtype == BF16)):
+            x2 = self._rows2d(x)
+            if x2 is not None and (out is None or (out.dim() == 2 and out.stride(1) == 1)):
+                return self._lib_mm(x2, w.t(), out, x.shape[:-1] + (w.shape[0],))
         if (self.gemm is not None and self.gemm.ok_tn(x, w) and (bias is None or bias.dtype == BF16)
                 and (out is None or self.gemm.ok_out(out, x, w.shape[0]))):
             y = self.gemm.linear(x, w, out_dtype or x.dtype, bias=bias, out=out)
@@ -160,7 +187,12 @@ class CudaOps(TorchOps):
         self._fell_back("linear")
         return super().linear(x, w, bias, out_dtype, out)
 
-    def linear_dx(self, dy, w, out=None):
+    def linear_dx(self, dy, w, out=None, narrow=False):
+        if (narrow and self.LIB_NARROW and dy.is_cuda and dy.dtype == BF16 and w.dtype == BF16
+                and (out is None or out.dtype == BF16)):
+            d2 = self._rows2d(dy)
+            if d2 is not None and (out is None or (out.dim() == 2 and out.stride(1) == 1)):
+                return self._lib_mm(d2, w, out, dy.shape[:-1] + (w.shape[1],))
         if self.gemm is not None and self.gemm.ok_nn(dy, w) and (out is None or self.gemm.ok_out(out, dy, w.shape[1])):
             self.launches += 1
             return self.gemm.linear_dx(dy, w, out=out)

@@ -26,9 +26,10 @@ class TorchOps:
     launches = 0                      # custom-kernel launch counter (0 here by construction)
 
     # ---- GEMMs ------------------------------------------------------------------
-    def linear(self, x, w, bias=None, out_dtype=None, out=None):
+    def linear(self, x, w, bias=None, out_dtype=None, out=None, narrow=False):
         """x [..., k] @ w[n, k]^T (+ bias).  `out`: a [rows, n] view (dense last dim, any row stride, e.g. a
-        column block of a wider matrix) to write into instead of a fresh tensor."""
+        column block of a wider matrix) to write into instead of a fresh tensor.  `narrow`: the product is a factor of
+        a low-rank operator (a hint for the kernel table; no effect here)."""
         y = x @ w.t()
         if bias is not None:
             y = y + bias.to(y.dtype)
@@ -37,7 +38,7 @@ class TorchOps:
             return out
         return y if out_dtype is None else y.to(out_dtype)
 
-    def linear_dx(self, dy, w, out=None):
+    def linear_dx(self, dy, w, out=None, narrow=False):
         """dy [..., n] @ w[n, k] -> [..., k] (`out` as for `linear`)"""
         if out is not None:
             out.copy_((dy @ w).reshape(out.shape))

@@ -430,6 +430,31 @@ def test_chunk_finish(ops, dh, doc_dtype):
     assert not ops.fallbacks.get("chunk_finish") or DEV == "cpu"
 
 
+def test_narrow_products_through_the_library_and_the_own_kernel(ops):
+    """Factor products marked `narrow` (library GEMM by default) against the tcgen05 kernel and fp32, into column blocks."""
+    M, d, r_ = 2048, 768, 144
+    u, D, U = rnd(M, d, seed=1), rnd(4 * r_, d, seed=2, scale=0.05), rnd(d, r_, seed=3, scale=0.05)
+    raw = torch.zeros(M, 4 * d, device=DEV, dtype=torch.bfloat16)
+    outs = {}
+    for mode in (True, False):
+        ops.LIB_NARROW = mode
+        n0 = ops.lib_gemms
+        try:
+            t = ops.linear(u, D, narrow=True)
+            ops.linear(t[:, r_:2 * r_], U, out=raw[:, d:2 * d], narrow=True)
+            dt = ops.linear_dx(raw[:, d:2 * d], U, narrow=True)
+            du = ops.linear_dx(t, D, narrow=True)
+        finally:
+            ops.LIB_NARROW = type(ops).LIB_NARROW
+        assert (ops.lib_gemms - n0) == (4 if mode else 0)
+        outs[mode] = (t.clone(), raw[:, d:2 * d].clone(), dt, du)
+        assert (raw[:, :d] == 0).all() and (raw[:, 2 * d:] == 0).all()
+    ref_t = u.float() @ D.float().t()
+    close(outs[True][0], ref_t, what="t (library)")
+    for a, b_, n_ in zip(outs[True], outs[False], ("t", "up", "dt", "du")):
+        close(a, b_, rtol=2e-2, atol=2e-2, what=n_ + ": library vs own kernel")
+
+
 def test_copy_pair(ops):
     B, T, H, dh = 3, 320, 5, 64
     tape = [rnd(B, T, H, dh, seed=i) for i in (1, 2)]
