@@ -308,6 +308,15 @@ def main():
         du = rnd(M, dm)
         report("gemm nn d(read) (4 operators)", T(lambda: g.linear_dx(t_all, D_all, out=du)), flops=f)
         report("  cublas d(read)", T(lambda: torch.mm(t_all, D_all, out=du)), flops=f)
+        # the deferred weight gradients of the factors over all steps of a layer (71 steps x 8192 rows)
+        rows_l = 71 * M
+        dcg_l, t_l, u_l = rnd(rows_l, 4 * dm), rnd(rows_l, nop * rk), rnd(rows_l, dm)
+        dU, dD = z(dm, rk), z(nop * rk, dm)
+        fu, fd = 2.0 * rows_l * dm * rk, 2.0 * rows_l * nop * rk * dm
+        report("gemm dw up factor (581 632 rows)", T(lambda: g.linear_dw_acc(dU, dcg_l[:, dm:2 * dm], t_l[:, rk:2 * rk])), flops=fu)
+        report("  cublas dw up factor", T(lambda: dU.add_(torch.mm(dcg_l[:, dm:2 * dm].t(), t_l[:, rk:2 * rk], out_dtype=torch.float32))), flops=fu)
+        report("gemm dw stacked down factors", T(lambda: g.linear_dw_acc(dD, t_l, u_l)), flops=fd)
+        report("  cublas dw stacked down factors", T(lambda: dD.add_(torch.mm(t_l.t(), u_l, out_dtype=torch.float32))), flops=fd)
         g.check()
     return rows
 
