@@ -280,7 +280,9 @@ class Wave3DEngine(WaveScanEngine):
         o_c, lse_c, w_f, w_n = ops.merge_partials(self.ofar_all[:, w], self.lsefar_all[:, w], o_n, lse_n)
         o, lse, ssq = ops.win_tail_fwd(qw, S.kself_r[:, w], S.v4[:, w], K_in, V_in, o_c, lse_c, C, S.scale, self.window)
         # every window chunk's new rows replace the old ones (all reads of this step are done)
-        _, _, raw = self._refine_fwd(S, w, o, ssq, out=(S.Kc[:, w], S.Vc[:, w]))
+        # (a forward re-run inside the backward also leaves the deferred weight gradients' inputs in their stash rows)
+        _, _, raw = self._refine_fwd(S, w, o, ssq, out=(S.Kc[:, w], S.Vc[:, w]),
+                                     stash_row=S.step_offs[s] if save is not None else None)
         if s - K + 1 >= 0 and getattr(S, "o_all", None) is not None:
             S.o_all[:, lo * C:(lo + 1) * C] = o[:, :C].reshape(B, C, d)      # chunk lo's K-th read is final
         if save is not None:
@@ -315,6 +317,7 @@ class Wave3DEngine(WaveScanEngine):
         rows = lambda i: slice(i * C, (i + 1) * C)
         # ---- forward re-run of this layer, keeping what every step read and produced
         save = {}
+        S.step_offs, S.fwd_stashed = offs, True
         self._far_arrays(li)
         self._raw_tape(S)
         for s in range(n + K - 1):

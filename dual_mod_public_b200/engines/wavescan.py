@@ -31,6 +31,7 @@ import torch.nn.functional as F
 
 from ..models.layers import LoRAGate, LoRALinear
 from . import cell as gcell
+from . import fused_math as fm
 from .gradbuf import GradBuffers
 from .schedule import check_schedule
 
@@ -566,14 +567,14 @@ class WaveScanEngine:
 
     # ---- the write law of one sweep -------------------------------------------------------------------
     # ---- the write law's two linear maps, dense or factored -----------------------------------------
-    def _pack_linear(self, P, o2):
+    def _pack_linear(self, P, o2, t_out=None):
         """[k_ctx | v_ctx (mrk: v_map) | gate-k u-logits | gate-v u-logits] of the un-normalised read o2
-        [B, c, d] -> [B, c, 4d]."""
+        [B, c, d] -> [B, c, 4d].  Factored: the down outputs [rows, sum of ranks] are left in `t_out` when given."""
         ops = self.ops
         if not P.factored:
             return ops.linear(o2, P.W_pack)
         B, c, d = o2.shape
-        t = ops.linear(o2, P.D_all, narrow=True).view(B * c, -1)
+        t = ops.linear(o2.view(B * c, d), P.D_all, out=t_out, narrow=True).view(B * c, -1)
         raw = torch.empty(B, c, 4 * d, dtype=o2.dtype, device=o2.device)
         raw2 = raw.view(B * c, 4 * d)
         for i, U in enumerate(P.U):
@@ -594,28 +595,36 @@ class WaveScanEngine:
             ops.linear_dx(dcg2[:, i * d:(i + 1) * d], U, out=dt[:, P.roff[i]:P.roff[i + 1]], narrow=True)
         return ops.linear_dx(dt, P.D_all, narrow=True).view(B, c, d)
 
-    def _vctx_linear(self, P, vin):
+    def _vctx_linear(self, P, vin, tv_out=None):
         if not P.factored:
             return self.ops.linear(vin, P.W_vctx)
-        return self.ops.linear(self.ops.linear(vin, P.Dv, narrow=True), P.Uv, narrow=True)
+        B, c, d = vin.shape
+        tv = self.ops.linear(vin.view(B * c, d), P.Dv, out=tv_out, narrow=True)
+        return self.ops.linear(tv, P.Uv, narrow=True).view(B, c, d)
 
-    def _refine_fwd(self, S, r, o, ssq, out=None):
+    def _refine_fwd(self, S, r, o, ssq, out=None, stash_row=None):
         """(k'', v'') rows [B, c, h, dh] from the read `o` of the rows `r` (key rotated), written into `out`
         when given.  Also returns what the backward wants besides (o, ssq): the packed ctx / gate logits
-        in the packed family, nothing when the write law runs as module code."""
+        in the packed family, nothing when the write law runs as module code.  `stash_row` (a forward re-run inside
+        the backward): the deferred weight gradients' inputs that this forward computes anyway (the down outputs of the
+        factors and, in the mult_res family, v_in) go straight into their stash rows starting there, so the backward
+        of the same sweep does not compute them again (S.fwd_stashed)."""
         ops, cfg = self.ops, self.cfg
         B, h, dh, d = self.B, cfg.n_heads, cfg.head_dim, cfg.d_model
         c = o.shape[1]
+        rows = slice(stash_row, stash_row + B * c) if stash_row is not None else None
+        fac = rows is not None and S.P.factored
         if self.family == "packed":
-            raw = self._pack_linear(S.P, o.reshape(B, c, d))
+            raw = self._pack_linear(S.P, o.reshape(B, c, d), S.t_stash[rows] if fac else None)
             K_new, V_new = ops.refine_fwd(raw, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h, S.pin,
                                           out=out)
             return K_new, V_new, raw
         if self.family == "mrk":
             o2 = o.reshape(B, c, d)
-            raw = self._pack_linear(S.P, o2)
-            vin = ops.mrk_vin_fwd(raw, ssq, o2, S.P.w_ctx, S.vgx[:, r], cfg.mult_res_lambda)
-            vc = self._vctx_linear(S.P, vin)
+            raw = self._pack_linear(S.P, o2, S.t_stash[rows] if fac else None)
+            vin = ops.mrk_vin_fwd(raw, ssq, o2, S.P.w_ctx, S.vgx[:, r], cfg.mult_res_lambda,
+                                  out=S.vin_stash[rows].view(B, c, d) if rows is not None else None)
+            vc = self._vctx_linear(S.P, vin, S.tv_stash[rows] if fac else None)
             K_new, V_new = ops.mrk_refine_fwd(raw, vc, ssq, S.glx[:, r], S.k[:, r], S.v[:, r], S.cos[r], S.sin[r], h,
                                               S.pin, S.P.k_gain, cfg.v_clamp_tau, out=out)
             return K_new, V_new, (raw, vc)
@@ -628,6 +637,16 @@ class WaveScanEngine:
             out[1].copy_(V_new)
             return out[0], out[1], None
         return K_new, V_new, None
+
+    def _down_outputs_of_uhat(self, S, rows, ssq, stashed):
+        """t = D' uhat of one sweep's rows into the stash (input of the up factors' deferred weight gradient).  The
+        forward's down outputs are D' o of the un-normalised read; when the forward re-run left them in the stash they
+        only need the rows' 1 / rms, else the product is formed from the stashed uhat."""
+        if not stashed:
+            self.ops.linear(S.u_stash[rows], S.P.D_all, out=S.t_stash[rows], narrow=True)
+            return
+        rstd = fm.row_rstd(ssq.reshape(-1, ssq.shape[-1]), self.cfg.d_model)          # [rows, 1] fp32
+        S.t_stash[rows].mul_(rstd)                                                    # fp32 product, one rounding
 
     def _refine_bwd(self, S, r, o, ssq, raw, dK_out, dV_out, stash_row, residual):
         """Backward of `_refine_fwd` for one sweep: returns d loss / d o [B, c, d] fp32 (plus `residual`)
@@ -647,12 +666,16 @@ class WaveScanEngine:
                                S.pin, P.k_gain, cfg.v_clamp_tau, S.dk[:, r], S.dv[:, r], (S.dglx[:, r] if S.dglx is not None else None), dcg,
                                S.u_stash[rows].view(B, c, d), dvc, S.dkg_stash[rows].view(B, c, h))
             dvin = S.dvin_stash[rows].view(B, c, d)
-            # v_in again (cheap) for the deferred W_vctx gradient: one GEMM per layer over all sweeps' rows
+            # v_in for the deferred W_vctx gradient (one GEMM per layer over all sweeps' rows): the forward re-run left
+            # it in the stash, else it is formed again (cheap)
+            stashed = getattr(S, "fwd_stashed", False)
             vin = S.vin_stash[rows]
-            vin.view(B, c, d).copy_(ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam))
+            if not stashed:
+                ops.mrk_vin_fwd(raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam, out=vin.view(B, c, d))
             if P.factored:
                 # stashes of the factored deferred gradients: down outputs and their gradients
-                ops.linear(vin, P.Dv, out=S.tv_stash[rows], narrow=True)
+                if not stashed:
+                    ops.linear(vin, P.Dv, out=S.tv_stash[rows], narrow=True)
                 ops.linear_dx(dvc.view(n, d), P.Uv, out=S.dtv_stash[rows], narrow=True)
                 ops.linear_dx(S.dtv_stash[rows], P.Dv, out=dvin.view(n, d), narrow=True)
             else:
@@ -660,7 +683,7 @@ class WaveScanEngine:
             du_hat = ops.mrk_vin_bwd(dvin, raw, ssq, o2, P.w_ctx, S.vgx[:, r], lam, dcg, S.dvgx[:, r])
             du = self._pack_linear_dx(P, dcg, S.dt_stash[rows] if P.factored else None)
             if P.factored:
-                ops.linear(S.u_stash[rows], P.D_all, out=S.t_stash[rows], narrow=True)
+                self._down_outputs_of_uhat(S, rows, ssq, stashed)
             return ops.rmsn_bwd(du, o2, ssq, residual=residual, extra=du_hat)
         if self.family == "packed":
             n = B * c
@@ -671,7 +694,7 @@ class WaveScanEngine:
             rows = slice(stash_row, stash_row + n)
             du = self._pack_linear_dx(S.P, dcg, S.dt_stash[rows] if S.P.factored else None)
             if S.P.factored:
-                ops.linear(S.u_stash[rows], S.P.D_all, out=S.t_stash[rows], narrow=True)
+                self._down_outputs_of_uhat(S, rows, ssq, getattr(S, "fwd_stashed", False))
             return ops.rmsn_bwd(du, o.reshape(B, c, d), ssq, residual=residual)
         from ..models.rope import apply_rope
         sh = S.P.shadow

@@ -290,15 +290,16 @@ class CudaOps(TorchOps):
         return (k.dtype == BF16 and raw.dtype == BF16 and raw.is_contiguous()
                 and all(_dense_tail(t, 1) for t in (k,) + views))
 
-    def mrk_vin_fwd(self, raw, ssq, o, w_ctx, vgx, lam):
+    def mrk_vin_fwd(self, raw, ssq, o, w_ctx, vgx, lam, out=None):
         B, c, d = o.shape
         h = ssq.shape[-1]
         dh = d // h
         if not (self._mrk_ok(o, raw, vgx) and o.is_contiguous() and ssq.is_contiguous() and w_ctx.dtype == BF16
-                and vgx.dtype == BF16 and dh % 16 == 0):
+                and vgx.dtype == BF16 and dh % 16 == 0
+                and (out is None or (out.dtype == BF16 and out.is_contiguous() and out.shape == (B, c, d)))):
             self._fell_back("mrk_vin_fwd")
-            return super().mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
-        vin = torch.empty(B, c, d, dtype=BF16, device=o.device)
+            return super().mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam, out)
+        vin = out if out is not None else torch.empty(B, c, d, dtype=BF16, device=o.device)
         self._ck(self.lib.dmb_mrk_vin_fwd(raw.data_ptr(), ssq.data_ptr(), o.data_ptr(), w_ctx.data_ptr(), vgx.data_ptr(),
                                           _tv(vgx), vin.data_ptr(), B, c, h, dh, lam, 1e-5, self._st()), "mrk_vin_fwd")
         self.launches += 1

@@ -289,8 +289,10 @@ class TorchOps:
         return out
 
     # ---- write law of the mult_res family (engines/fused_math.py: mrk_*) ------------------------------------
-    def mrk_vin_fwd(self, raw, ssq, o, w_ctx, vgx, lam):
-        return fm.mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
+    def mrk_vin_fwd(self, raw, ssq, o, w_ctx, vgx, lam, out=None):
+        """`out`: optional contiguous [B, c, d] tensor to write into (e.g. the rows of a stash)."""
+        vin = fm.mrk_vin_fwd(raw, ssq, o, w_ctx, vgx, lam)
+        return vin if out is None else out.copy_(vin)
 
     def mrk_vin_bwd(self, dvin, raw, ssq, o, w_ctx, vgx, lam, dcg, dvgx_acc):
         """Writes d v_m into dcg[..., d:2d], accumulates dvgx_acc [B,c,d] (fp32, +=); returns the direct
