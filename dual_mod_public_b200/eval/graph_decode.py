@@ -45,8 +45,13 @@ class _DecodeRefine:
         self.ops, self.cfg, self.family, self.B = ops, cfg, family, B
 
     from ..engines.wavescan import WaveScanEngine as _E
-    _refine_fwd, _pack_linear, _vctx_linear = _E._refine_fwd, _E._pack_linear, _E._vctx_linear
+    _refine_fwd, _vctx_linear, _engine_pack_linear = _E._refine_fwd, _E._vctx_linear, _E._pack_linear
     del _E
+
+    def _pack_linear(self, P, o2, t_out=None):
+        if not P.factored and self.B <= 64:          # one row per sequence: see `GraphDecoder._fused_layer`
+            return self.ops.linear(o2, P.W_pack, narrow=True)
+        return self._engine_pack_linear(P, o2, t_out)
 
 
 class GraphDecoder:
@@ -158,8 +163,11 @@ class GraphDecoder:
         """One layer of the step on the engines' kernels: x [B, 1, d] in the decode dtype -> the layer's output."""
         ops, P, cfg = self.ops, self.packs[l], self.m.cfg
         B, h, dh, d = self.B, self.h, self.dh, self.h * self.dh
+        # one row per sequence: the products stream their weights once over a sliver of rows (half an MMA tile
+        # at batch 64), which is library-GEMM territory (`narrow`; 17.5 us per product on the own kernel)
+        lin = lambda x_, w_, b_=None: ops.linear(x_, w_, bias=b_, narrow=B <= 64)
         xhat, _ = ops.rms_fwd(x, P.w_an)
-        qkvg = ops.linear(xhat, P.W_in, bias=P.b_in)
+        qkvg = lin(xhat, P.W_in, P.b_in)
         k, v = qkvg[..., d:2 * d], qkvg[..., 2 * d:3 * d]
         q_r = ops.rope(qkvg[..., :d].unflatten(-1, (h, dh)), cos_p, sin_p)            # [B, 1, h, dh]
         kself_r = ops.rope(k.unflatten(-1, (h, dh)), cos_p, sin_p)
@@ -173,10 +181,10 @@ class GraphDecoder:
             K_new, V_new = kself_r, v.unflatten(-1, (h, dh))
         self.K[l].index_copy_(1, self.pos, K_new)
         self.V[l].index_copy_(1, self.pos, V_new)
-        x_mid = x + ops.linear(o.view(B, 1, d), P.wo)
+        x_mid = x + lin(o.view(B, 1, d), P.wo)
         xn, _ = ops.rms_fwd(x_mid, P.w_mn)
-        g = ops.swiglu_fwd(ops.linear(xn, P.w1), ops.linear(xn, P.w3))
-        return x_mid + ops.linear(g, P.w2)
+        g = ops.swiglu_fwd(lin(xn, P.w1), lin(xn, P.w3))
+        return x_mid + lin(g, P.w2)
 
     def _decode_token(self):
         """One token through every layer at the device-side position; leaves the fp32 logits and the

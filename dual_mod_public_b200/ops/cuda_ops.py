@@ -174,10 +174,14 @@ class CudaOps(TorchOps):
         return t.reshape(-1, t.shape[-1]) if t.is_contiguous() else None
 
     def linear(self, x, w, bias=None, out_dtype=None, out=None, narrow=False):
-        if (narrow and self.LIB_NARROW and bias is None and x.is_cuda and x.dtype == BF16 and w.dtype == BF16
-                and out_dtype in (None, BF16) and (out is None or out.dtype == BF16)):
+        if (narrow and self.LIB_NARROW and x.is_cuda and x.dtype == BF16 and w.dtype == BF16
+                and out_dtype in (None, BF16) and (out is None or out.dtype == BF16)
+                and (bias is None or (bias.dtype == BF16 and out is None))):
             x2 = self._rows2d(x)
             if x2 is not None and (out is None or (out.dim() == 2 and out.stride(1) == 1)):
+                if bias is not None:
+                    self.lib_gemms += 1
+                    return torch.addmm(bias, x2, w.t()).view(x.shape[:-1] + (w.shape[0],))
                 return self._lib_mm(x2, w.t(), out, x.shape[:-1] + (w.shape[0],))
         if (self.gemm is not None and self.gemm.ok_tn(x, w) and (bias is None or bias.dtype == BF16)
                 and (out is None or self.gemm.ok_out(out, x, w.shape[0]))):
