@@ -25,9 +25,30 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 
-template <typename T> __device__ __forceinline__ T cvt(float x);
-template <> __device__ __forceinline__ float cvt<float>(float x) { return x; }
-template <> __device__ __forceinline__ bf16 cvt<bf16>(float x) { return __float2bfloat16(x); }
+// Every lane of a (batch, row, head) warp owns PER = DH / 32 CONTIGUOUS elements of the head's row, read and written
+// as one 8- or 16-byte access (rows are DH floats: 256 / 512 bytes per warp instruction).
+template <int PER> __device__ __forceinline__ void ldf(const float* p, float (&r)[PER]) {
+  if constexpr (PER == 2) { const float2 v = *reinterpret_cast<const float2*>(p); r[0] = v.x; r[1] = v.y; }
+  else { const float4 v = *reinterpret_cast<const float4*>(p); r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w; }
+}
+template <int PER> __device__ __forceinline__ void stf(float* p, const float (&r)[PER]) {
+  if constexpr (PER == 2) *reinterpret_cast<float2*>(p) = make_float2(r[0], r[1]);
+  else *reinterpret_cast<float4*>(p) = make_float4(r[0], r[1], r[2], r[3]);
+}
+template <int PER> __device__ __forceinline__ void ldb(const bf16* p, float (&r)[PER]) {
+  if constexpr (PER == 2) { const float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(p)); r[0] = v.x; r[1] = v.y; }
+  else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+    r[0] = a.x; r[1] = a.y; r[2] = b.x; r[3] = b.y;
+  }
+}
+template <int PER> __device__ __forceinline__ void stb(bf16* p, const float (&r)[PER]) {
+  if constexpr (PER == 2) *reinterpret_cast<uint32_t*>(p) = pack_bf16(r[0], r[1]);
+  else *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]));
+}
+template <int PER> __device__ __forceinline__ void stv(float* p, const float (&r)[PER]) { stf<PER>(p, r); }
+template <int PER> __device__ __forceinline__ void stv(bf16* p, const float (&r)[PER]) { stb<PER>(p, r); }
 
 template <int DH>
 __global__ void __launch_bounds__(256) merge_fwd_kernel(
@@ -47,11 +68,12 @@ __global__ void __launch_bounds__(256) merge_fwd_kernel(
   const float lc = m + __logf(__expf(lf - m) + __expf(ln - m));
   const float wf = __expf(lf - lc), wn = __expf(ln - lc);
   constexpr int PER = DH / 32;
+  float f_[PER], n_[PER], c_[PER];
+  ldf<PER>(o_f + v_abs + lane * PER, f_);
+  ldf<PER>(o_n + wid * DH + lane * PER, n_);
 #pragma unroll
-  for (int e = 0; e < PER; ++e) {
-    const int d = lane + 32 * e;
-    o_c[wid * DH + d] = wf * o_f[v_abs + d] + wn * o_n[wid * DH + d];
-  }
+  for (int e = 0; e < PER; ++e) c_[e] = wf * f_[e] + wn * n_[e];
+  stf<PER>(o_c + wid * DH + lane * PER, c_);
   if (lane == 0) {
     lse_c[wid] = lc;
     w_f[wid] = wf;
@@ -76,26 +98,25 @@ __global__ void __launch_bounds__(256) split_bwd_kernel(
   const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
   const float wf = w_f[wid], wn = w_n[wid], dl = dlse_c[wid];
   constexpr int PER = DH / 32;
-  float g[PER], on[PER], dotf = 0.f, dotn = 0.f, donon = 0.f;
+  float g[PER], on[PER], oc[PER], of[PER], acc[PER], dn[PER], dotf = 0.f, dotn = 0.f, donon = 0.f;
+  ldf<PER>(do_c + wid * DH + lane * PER, g);
+  ldf<PER>(o_n + wid * DH + lane * PER, on);
+  ldf<PER>(o_c + wid * DH + lane * PER, oc);
+  ldf<PER>(o_f + v_abs + lane * PER, of);
+  ldf<PER>(DOf + v_abs + lane * PER, acc);
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int d = lane + 32 * e;
-    g[e] = do_c[wid * DH + d];
-    on[e] = o_n[wid * DH + d];
-    const float oc = o_c[wid * DH + d], of = o_f[v_abs + d];
-    dotf += g[e] * (of - oc);
-    dotn += g[e] * (on[e] - oc);
+    dotf += g[e] * (of[e] - oc[e]);
+    dotn += g[e] * (on[e] - oc[e]);
     donon += g[e] * on[e];
+    acc[e] += wf * g[e];
+    dn[e] = wn * g[e];
   }
   dotf = warp_sum(dotf);
   dotn = warp_sum(dotn);
   donon = warp_sum(donon);
-#pragma unroll
-  for (int e = 0; e < PER; ++e) {
-    const int d = lane + 32 * e;
-    DOf[v_abs + d] += wf * g[e];
-    docn[v_abs + d] = cvt<TD>(wn * g[e]);
-  }
+  stf<PER>(DOf + v_abs + lane * PER, acc);
+  stv<PER>(docn + v_abs + lane * PER, dn);
   if (lane == 0) {
     DLf[s_abs] += wf * (dotf + dl);
     const float cn = wn * donon - wn * (dotn + dl);
@@ -126,16 +147,22 @@ __global__ void __launch_bounds__(256) cell_finish_kernel(
   const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
   const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
   constexpr int PER = DH / 32;
-  float dot = 0.f;
+  float dot = 0.f, g[PER], oc[PER], k0[PER], v0[PER], ak[PER], av_[PER];
+  ldf<PER>(do_c + wid * DH + lane * PER, g);
+  ldf<PER>(o_c + wid * DH + lane * PER, oc);
+  ldf<PER>(dK0 + wid * DH + lane * PER, k0);
+  ldf<PER>(dV0 + wid * DH + lane * PER, v0);
+  ldf<PER>(dks + v_abs + lane * PER, ak);
+  ldf<PER>(dv + v_abs + lane * PER, av_);
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int d = lane + 32 * e;
-    const float g = do_c[wid * DH + d];
-    dot += g * o_c[wid * DH + d];
-    doc[v_abs + d] = cvt<TD>(g);
-    dks[v_abs + d] += dK0[wid * DH + d];
-    dv[v_abs + d] += dV0[wid * DH + d];
+    dot += g[e] * oc[e];
+    ak[e] += k0[e];
+    av_[e] += v0[e];
   }
+  stv<PER>(doc + v_abs + lane * PER, g);
+  stf<PER>(dks + v_abs + lane * PER, ak);
+  stf<PER>(dv + v_abs + lane * PER, av_);
   dot = warp_sum(dot);
   if (lane == 0) {
     const float cv = dot - dlse_c[wid];
@@ -179,21 +206,18 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
   const bf16* ks_row = ks + b * vks.bs + r * vks.rs + (long long)h * DH;
   const bf16* vr_row = vr + b * vvr.bs + r * vvr.rs + (long long)h * DH;
   float vv[PER], oc[PER], av[PER], ac[PER];
+  ldb<PER>(vr_row + lane * PER, vv);
+  ldf<PER>(o_c + wid * DH + lane * PER, oc);
 #pragma unroll
-  for (int e = 0; e < PER; ++e) {
-    vv[e] = __bfloat162float(vr_row[lane + 32 * e]);
-    oc[e] = o_c[wid * DH + lane + 32 * e];
-    av[e] = ac[e] = 0.f;
-  }
+  for (int e = 0; e < PER; ++e) av[e] = ac[e] = 0.f;
   float dss = 0.f, dl = 0.f;
   for (int k = K - 1; k >= 0; --k) {
-    const float* g_ = sp.dO[k] + wid * DH;
     const float* sc = scal + (long long)k * 3 * n + wid;
     const float ps = sc[0], pc = sc[n], delta = sc[2 * n];
     float g[PER], dsv = 0.f, dc = 0.f;
+    ldf<PER>(sp.dO[k] + wid * DH + lane * PER, g);
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
-      g[e] = g_[lane + 32 * e];
       dsv += g[e] * vv[e];
       dc += g[e] * oc[e];
       av[e] += ps * g[e];
@@ -207,17 +231,25 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
     dss += ps * (dsv - delta) * scale;
     dl += pc * (dc - delta);
   }
-  float dot = 0.f;
+  float dot = 0.f, qv[PER], kv[PER], k0[PER], v0[PER], a_k[PER], a_v[PER], a_q[PER];
+  ldb<PER>(q_row + lane * PER, qv);
+  ldb<PER>(ks_row + lane * PER, kv);
+  ldf<PER>(dK0 + wid * DH + lane * PER, k0);
+  ldf<PER>(dV0 + wid * DH + lane * PER, v0);
+  ldf<PER>(dks + v_abs + lane * PER, a_k);
+  ldf<PER>(dv + v_abs + lane * PER, a_v);
+  ldf<PER>(dq + v_abs + lane * PER, a_q);
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int d = lane + 32 * e;
-    const long long i = v_abs + d;
     dot += ac[e] * oc[e];
-    doc[i] = cvt<TD>(ac[e]);
-    dks[i] += dK0[wid * DH + d] + dss * __bfloat162float(q_row[d]);
-    dv[i] += dV0[wid * DH + d] + av[e];
-    dq[i] += dss * __bfloat162float(ks_row[d]);
+    a_k[e] += k0[e] + dss * qv[e];
+    a_v[e] += v0[e] + av[e];
+    a_q[e] += dss * kv[e];
   }
+  stv<PER>(doc + v_abs + lane * PER, ac);
+  stf<PER>(dks + v_abs + lane * PER, a_k);
+  stf<PER>(dv + v_abs + lane * PER, a_v);
+  stf<PER>(dq + v_abs + lane * PER, a_q);
   dot = warp_sum(dot);
   if (lane == 0) {
     const float cv = dot - dl;
@@ -271,41 +303,50 @@ __global__ void __launch_bounds__(256) chunk_finish_kernel(
   const long long d = (long long)H * DH;
   for (int k = K - 1; k >= 0; --k) {
     const long long so = (long long)b * sw.bs_sca[k] + (long long)r * H + h;
-    const float* g_ = sw.dO[k] + (long long)b * sw.bs_vec[k] + ((long long)r * H + h) * DH;
     const float ps = sw.ps[k][so];
     dss += sw.dss[k][so];
+    float g[PER];
+    ldf<PER>(sw.dO[k] + (long long)b * sw.bs_vec[k] + ((long long)r * H + h) * DH + lane * PER, g);
 #pragma unroll
-    for (int e = 0; e < PER; ++e) av[e] += ps * g_[lane + 32 * e];
+    for (int e = 0; e < PER; ++e) av[e] += ps * g[e];
     if (dglx) {
       const bf16* c_ = sw.dcg[k] + (long long)b * 4 * sw.bs_vec[k] + (long long)r * 4 * d + 2 * d + (long long)h * DH;
+      float gk[PER], gv[PER];
+      ldb<PER>(c_ + lane * PER, gk);
+      ldb<PER>(c_ + d + lane * PER, gv);
 #pragma unroll
       for (int e = 0; e < PER; ++e) {
-        agk[e] += __bfloat162float(c_[lane + 32 * e]);
-        agv[e] += __bfloat162float(c_[d + lane + 32 * e]);
+        agk[e] += gk[e];
+        agv[e] += gv[e];
       }
     }
   }
   if (dglx) {
     float* o_ = dglx + (long long)b * bs_dglx + (long long)r * 2 * d + (long long)h * DH;
-#pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      o_[lane + 32 * e] = agk[e];
-      o_[d + lane + 32 * e] = agv[e];
-    }
+    stf<PER>(o_ + lane * PER, agk);
+    stf<PER>(o_ + d + lane * PER, agv);
   }
-  const bf16* q_row = K > 0 ? q + b * vq.bs + r * vq.rs + (long long)h * DH : nullptr;
-  float dot = 0.f;
+  float dot = 0.f, g[PER], of[PER], kp[PER], vp[PER], a_k[PER], a_v[PER], qv[PER], zero[PER];
+#pragma unroll
+  for (int e = 0; e < PER; ++e) qv[e] = zero[e] = 0.f;
+  if (K > 0) ldb<PER>(q + b * vq.bs + r * vq.rs + (long long)h * DH + lane * PER, qv);
+  ldf<PER>(DOf + v_abs + lane * PER, g);
+  ldf<PER>(o_f + v_abs + lane * PER, of);
+  ldf<PER>(dKp + v_abs + lane * PER, kp);
+  ldf<PER>(dVp + v_abs + lane * PER, vp);
+  ldf<PER>(dks + v_abs + lane * PER, a_k);
+  ldf<PER>(dv + v_abs + lane * PER, a_v);
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const long long i = v_abs + lane + 32 * e;
-    const float g = DOf[i];
-    dot += g * o_f[i];
-    doc[i] = cvt<TD>(g);
-    dks[i] += dKp[i] + (K > 0 ? dss * __bfloat162float(q_row[lane + 32 * e]) : 0.f);
-    dv[i] += dVp[i] + av[e];
-    dKp[i] = 0.f;
-    dVp[i] = 0.f;
+    dot += g[e] * of[e];
+    a_k[e] += kp[e] + dss * qv[e];
+    a_v[e] += vp[e] + av[e];
   }
+  stv<PER>(doc + v_abs + lane * PER, g);
+  stf<PER>(dks + v_abs + lane * PER, a_k);
+  stf<PER>(dv + v_abs + lane * PER, a_v);
+  stf<PER>(dKp + v_abs + lane * PER, zero);
+  stf<PER>(dVp + v_abs + lane * PER, zero);
   dot = warp_sum(dot);
   if (lane == 0) {
     const float cv = dot - DLf[s_abs], l = lse_f[s_abs];
