@@ -89,6 +89,7 @@ class _LayerPack:
         mk = lambda *s: torch.empty(*s, dtype=dtype, device=device)
         self.family = family
         self.packed = packed = family != "module"
+        self.factored = False
         n_in = 6 * d if family == "mrk" else 5 * d          # mrk: + the x-logits of the multiplicative branch's gate
         self.w_an, self.w_mn, self.w_ctx = mk(d), mk(d), mk(d)
         self.wo = mk(d, d)
