@@ -256,15 +256,21 @@ def main():
         lg, tg = rnd(4096, 32000), torch.randint(0, 32000, (4096,), device=DEV)
         inv = torch.tensor(1.0 / 4096, device=DEV)
         report("ce slab 4096x32000", T(lambda: ops.ce_chunk(lg, tg, inv)), bytes_=4096 * 32000 * 2 * 2)
-    # ---- GEMMs: ours (128 x BN tiles per CTA, and 256 x 256 tiles on CTA pairs) vs torch.matmul (cuBLAS)
+    # ---- GEMMs: ours (128 x BN tiles per CTA, and 256 x 256 / 256 x 128 tiles on CTA pairs) vs torch.matmul (cuBLAS)
     if want("gemm") and ops.gemm is not None:
         g = ops.gemm
 
         def trio(name, fn, ref, flops):
-            for tag_, flag in (("1 CTA", False), ("CTA pair", True)):
+            for tag_, flag, bn in (("1 CTA", False, 0), ("CTA pair 256x256", True, 256), ("CTA pair 256x128", True, 128)):
                 g.pair = flag
+                g.pair_width(bn)
                 report(f"gemm {name} [{tag_}]", T(fn), flops=flops)
             g.pair = False
+            g.pair_width(0)
+            if g.ksplit:
+                g.ksplit = False
+                report(f"gemm {name} [1 CTA per tile, no K split across a CTA pair]", T(fn), flops=flops)
+                g.ksplit = True
             report(f"  cublas {name}", T(ref), flops=flops)
 
         shapes = [("sweep y=uW^T", 2048, 4096, 1024), ("qkv", 65536, 1024, 1024), ("mlp up", 65536, 2816, 1024),

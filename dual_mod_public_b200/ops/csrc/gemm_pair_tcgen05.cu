@@ -1,8 +1,11 @@
-// bf16 GEMM on CTA pairs: two CTAs of a cluster (two SMs) work on one 256 x 256 output tile with
-// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and only HALF of the B tile (128 of the 256
-// columns of C), so a k-block costs each SM 32 KB of shared-memory fill instead of 48 KB for a 128 x 256 tile of
-// its own, and the tensor cores of both SMs read both halves.  The accumulator rows of a CTA (its 128 rows x 256
-// fp32 columns) live in that CTA's tensor memory and are written out by its own epilogue warps.
+// bf16 GEMM on CTA pairs: two CTAs of a cluster (two SMs) work on one 256 x BNP output tile (BNP = 256 or 128)
+// with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and only HALF of the B tile (BNP / 2 of the
+// BNP columns of C), so a k-block costs each SM 32 KB (BNP = 256) or 24 KB (BNP = 128) of shared-memory fill
+// instead of 48 / 32 KB for a 128 x BNP tile of its own, and the tensor cores of both SMs read both halves.  The
+// accumulator rows of a CTA (its 128 rows x BNP fp32 columns) live in that CTA's tensor memory and are written
+// out by its own epilogue warps.  BNP = 128 is for problems with too few 256-wide tiles to fill the SMs (the
+// input gradient of a sweep, 2048 x 1024 outputs over K = 4096): a CTA of its own on a 128 x 128 tile reads
+// 8 KB of operands per 128 x 128 x 16 MMA from its shared memory, a CTA of a pair 6 KB.
 //
 //   C[M,N] (+)= op(A) . op(B)        same operand layouts and epilogues as the single-CTA kernel
 //
@@ -19,35 +22,21 @@ using namespace tc05;
 
 namespace {
 
-constexpr int BM = 128, BN_PAIR = 256, BN_HALF = 128, BK = 64, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 6;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int NTHREADS = 192;
-constexpr int TMEM_COLS = 512;
-constexpr int stage_out_off = STAGES * STAGE_BYTES;          // epilogue staging: 4 warps x 2 slots x 4 KB
-constexpr int bar_off = stage_out_off + 4 * 2 * 4096;
-constexpr int SMEM_TOTAL = bar_off + 256;
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// the address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-// every thread of both CTAs; callers reconverge their warps first (the role branches leave lanes apart)
-__device__ __forceinline__ void cluster_sync_all() {
-  __syncwarp();
-  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
+template <int BNP>
+struct PairCfg {
+  static constexpr int BN_HALF = BNP / 2;
+  static constexpr int B_BYTES = BN_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BNP == 256 ? 6 : 8;             // 192 KB of ring either way
+  static constexpr int TMEM_COLS = 2 * BNP;                     // two accumulators
+  static constexpr int stage_out_off = STAGES * STAGE_BYTES;    // epilogue staging: 4 warps x 2 slots x 4 KB
+  static constexpr int bar_off = stage_out_off + 4 * 2 * 4096;
+  static constexpr int SMEM_TOTAL = bar_off + 256;
+};
+
 // tile load whose completion bytes are counted on a barrier that may sit in the peer CTA of the pair
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0,
                                                  int c1) {
@@ -78,11 +67,14 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) 
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 
-template <int A_MN, int B_MN, int OUT_F32>
+template <int A_MN, int B_MN, int OUT_F32, int BNP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1) gemm_pair_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cout, const bf16* __restrict__ bias, int M, int N,
     int K, long long ldc, int accumulate, int* __restrict__ gerr, int splits, float* __restrict__ ws) {
+  using C = PairCfg<BNP>;
+  constexpr int BN_PAIR = BNP, BN_HALF = C::BN_HALF, STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
+  constexpr int TMEM_COLS = C::TMEM_COLS, stage_out_off = C::stage_out_off, bar_off = C::bar_off;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* base_ptr = smem_raw;
@@ -144,7 +136,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1) gemm_pa
             for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmA, lf, m0 + 64 * j, k0);
           }
           if (B_MN == 0) {
-            tma_load_2d_pair(sb, &tmB, lf, k0, n0);                       // box {64 k, 128 n}
+            tma_load_2d_pair(sb, &tmB, lf, k0, n0);                       // box {64 k, BNP / 2 n}
           } else {
 #pragma unroll
             for (int j = 0; j < BN_HALF / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tmB, lf, n0 + 64 * j, k0);
@@ -185,7 +177,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1) gemm_pa
       }
     }
   } else {
-    // ---------------- epilogue (both CTAs): this CTA's 128 rows x 256 columns ----------------
+    // ---------------- epilogue (both CTAs): this CTA's 128 rows x BNP columns ----------------
     const int q = warp & 3;
     uint32_t ti = 0, n_out = 0;
     bool alive = aligned;
@@ -299,20 +291,22 @@ __global__ void pair_splitk_reduce_kernel(float* __restrict__ Cout, const float*
 }
 
 int g_pair_sms = 0;
+int g_pair_bn = 0;                       // 0: chosen per problem; 128 / 256: forced (benchmarks, tests)
 constexpr size_t PAIR_WS_BYTES = (size_t)64 << 20;
 float* g_pair_ws[16] = {};
 
-template <int A_MN, int B_MN, int OUT_F32>
+template <int A_MN, int B_MN, int OUT_F32, int BNP>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* bias, int M,
                 int N, int K, long long ldc, int accumulate, int* gerr, float* ws, int splits, cudaStream_t st) {
-  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32>;
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32, BNP>;
+  constexpr int SMEM_TOTAL = PairCfg<BNP>::SMEM_TOTAL;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = ((N + BN_PAIR - 1) / BN_PAIR) * ((M + 2 * BM - 1) / (2 * BM));
+  const int tiles = ((N + BNP - 1) / BNP) * ((M + 2 * BM - 1) / (2 * BM));
   const int items = tiles * splits;
   const int pairs = items < g_pair_sms / 2 ? items : g_pair_sms / 2;
   kern<<<2 * pairs, NTHREADS, SMEM_TOTAL, st>>>(ta, tb, tc, C, (const bf16*)bias, M, N, K, ldc, accumulate, gerr, splits, ws);
@@ -328,7 +322,10 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
 
 extern "C" {
 
-// Same contract as dmb_gemm_bf16 (operand layouts, alignment, epilogues); 256 x 256 tiles on CTA pairs.
+// forces the pair tile's width (128 or 256); 0 gives the choice back to the cost model
+void dmb_gemm_pair_bn(int bn) { g_pair_bn = (bn == 128 || bn == 256) ? bn : 0; }
+
+// Same contract as dmb_gemm_bf16 (operand layouts, alignment, epilogues); 256 x 256 or 256 x 128 tiles on CTA pairs.
 int dmb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                        long long ldb, long long ldc, int a_mn, int b_mn, int out_f32, int accumulate, int* gerr,
                        cudaStream_t st) {
@@ -351,23 +348,30 @@ int dmb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, 
     }
     ws = g_pair_ws[dev];
   }
-  // K split for the weight-gradient shapes (few tiles, very long K; fp32 output only): work items of at least 16
-  // k-blocks, as many as keep every pair busy
-  int splits = 1;
+  // Tile width and K split from a small cost model in units of one 256 x 256 x 64 k-block of a pair: a work item
+  // costs kbs * a + e (a: k-block cost, e: epilogue), items run in ceil(items / pairs) rounds.  The K split is for
+  // the weight-gradient shapes (few tiles, very long K; fp32 output only): work items of at least 16 k-blocks.
+  int splits = 1, bnp = 256;
   {
     const int KBT = (K + BK - 1) / BK;
-    const long long tiles = (long long)((N + BN_PAIR - 1) / BN_PAIR) * ((M + 2 * BM - 1) / (2 * BM));
     const int pairs = g_pair_sms / 2;
-    if (ws && !bias && N % 4 == 0 && tiles < pairs) {
-      double best = 1e30;
-      for (int sp = 1; sp <= 32; ++sp) {
+    const long long tm = (M + 2 * BM - 1) / (2 * BM);
+    double best = 1e30;
+    for (int cand = 0; cand < 2; ++cand) {
+      const int w = cand ? 128 : 256;
+      if (g_pair_bn && w != g_pair_bn) continue;
+      if (!g_pair_bn && N <= 128 && w == 256) continue;
+      const long long tiles = (long long)((N + w - 1) / w) * tm;
+      const double a = w == 256 ? 1.0 : 0.55, e = w == 256 ? 8.0 : 5.0;
+      const int smax = (ws && !bias && N % 4 == 0 && tiles < pairs) ? 32 : 1;
+      for (int sp = 1; sp <= smax; ++sp) {
         if (sp > 1 && (KBT / sp < 16 || (size_t)sp * M * N * sizeof(float) > PAIR_WS_BYTES)) break;
         const int kbs = (KBT + sp - 1) / sp;
         if (sp > 1 && (KBT + kbs - 1) / kbs != sp) continue;
         const long long rounds = (tiles * sp + pairs - 1) / pairs;
-        double cost = rounds * (kbs * 1.0 + 8.0);
+        double cost = rounds * (kbs * a + e);
         if (sp > 1) cost += (sp + 1.0) * M * N * 4.0 / 5e12 / 0.3e-6;
-        if (cost < best) { best = cost; splits = sp; }
+        if (cost < best) { best = cost; splits = sp; bnp = w; }
       }
     }
   }
@@ -375,11 +379,13 @@ int dmb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, 
   int rc;
   rc = a_mn ? make_map_2d(&ta, A, M, K, lda, 64, BK) : make_map_2d(&ta, A, K, M, lda, BK, BM);
   if (rc) return rc;
-  rc = b_mn ? make_map_2d(&tb, B, N, K, ldb, 64, BK) : make_map_2d(&tb, B, K, N, ldb, BK, BN_HALF);
+  rc = b_mn ? make_map_2d(&tb, B, N, K, ldb, 64, BK) : make_map_2d(&tb, B, K, N, ldb, BK, bnp / 2);
   if (rc) return rc;
   if (out_f32) tc = ta;
   else if ((rc = make_map_2d(&tc, C, N, M, ldc, 64, 32))) return rc;
-#define GO(a, b, o) return launch_pair<a, b, o>(ta, tb, tc, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)
+#define GO(a, b, o)                                                                                                  \
+  return bnp == 256 ? launch_pair<a, b, o, 256>(ta, tb, tc, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st) \
+                    : launch_pair<a, b, o, 128>(ta, tb, tc, C, bias, M, N, K, ldc, accumulate, gerr, ws, splits, st)
   if (!a_mn && !b_mn) { if (out_f32) GO(0, 0, 1); else GO(0, 0, 0); }
   if (!a_mn && b_mn) { if (out_f32) GO(0, 1, 1); else GO(0, 1, 0); }
   if (out_f32) GO(1, 1, 1); else GO(1, 1, 0);

@@ -44,8 +44,18 @@ class Tcgen05Gemm:
         lib.dmb_gemm_bf16.argtypes = [p, p, p, p, i, i, i, ll, ll, ll, i, i, i, i, p, p]
         lib.dmb_gemm_bf16_pair.restype = i
         lib.dmb_gemm_bf16_pair.argtypes = lib.dmb_gemm_bf16.argtypes
-        # 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) for problems with enough rows and columns
-        self.pair = os.environ.get("DMB_GEMM_PAIR", "0") == "1"
+        lib.dmb_gemm_pair_bn.argtypes = [i]
+        lib.dmb_gemm_bf16_ksplit2.restype = i
+        lib.dmb_gemm_bf16_ksplit2.argtypes = lib.dmb_gemm_bf16.argtypes
+        # bf16 results with at most SMs / 2 tiles and a long reduction (the input gradient of a sweep): two CTAs of a
+        # cluster split the K range of each tile and add their accumulators through shared memory
+        self.ksplit = os.environ.get("DMB_GEMM_KSPLIT", "1") != "0"
+        # CTA pairs (tcgen05 cta_group::2): DMB_GEMM_PAIR = "1" / True for every problem with enough rows and columns
+        # (256 x 256 tiles, or 256 x 128 where those leave SMs idle), "narrow" only for bf16 results with too few
+        # 256-wide tiles to fill the SMs (256 x 128 pair tiles instead of 128 x 128 tiles per CTA), "0" never
+        mode = os.environ.get("DMB_GEMM_PAIR", "0")
+        self.pair = True if mode == "1" else ("narrow" if mode == "narrow" else False)
+        self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         # probe: fails here (not mid-step) if the driver entry point for tensor maps is missing
         a = torch.zeros(128, 64, dtype=BF16, device=self.device)
@@ -53,13 +63,25 @@ class Tcgen05Gemm:
         self._call(a, w, torch.empty(128, 256, dtype=BF16, device=self.device), None, 128, 256, 64, 64, 64, 256, 0, 0, 0, 0)
         self.check()
 
+    def pair_width(self, bn):
+        """Forces the CTA-pair kernel's tile width (128 or 256); 0 gives the choice back to its cost model."""
+        self.lib.dmb_gemm_pair_bn(int(bn))
+
     def check(self):
         if self.err.item() != 0:
             raise RuntimeError("tcgen05 GEMM: a pipeline wait ran out (kernel aborted its tile loop)")
 
     def _call(self, A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, acc):
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        fn = self.lib.dmb_gemm_bf16_pair if (self.pair and M >= 512 and N >= 192) else self.lib.dmb_gemm_bf16
+        if self.pair == "narrow":
+            use_pair = (not out_f32 and M >= 256 and N >= 128 and K >= 512
+                        and -(-M // 128) * -(-N // 256) <= self.sms // 2)
+        else:
+            use_pair = bool(self.pair) and M >= 512 and N >= 192
+        fn = self.lib.dmb_gemm_bf16_pair if use_pair else self.lib.dmb_gemm_bf16
+        if (self.ksplit and not use_pair and not out_f32 and not acc and K >= 2048
+                and 2 * (-(-M // 128) * -(-N // 256)) <= self.sms):
+            fn = self.lib.dmb_gemm_bf16_ksplit2
         rc = fn(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                     bias.data_ptr() if bias is not None else None, M, N, K, lda, ldb, ldc,
                                     a_mn, b_mn, out_f32, acc, self.err.data_ptr(), st)

@@ -52,6 +52,34 @@ def test_linear_dx(gemm, M, N, K):
     check(dx, dy.float() @ w.float(), "dx")
 
 
+# few output tiles and a long reduction with a bf16 result: the two CTAs of a cluster split each tile's K range and
+# add their accumulators through shared memory (the input gradient of a sweep is the first shape)
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 4096), (1000, 520, 4160), (512, 256, 8192), (128, 256, 2048 + 72)])
+def test_bf16_results_through_the_k_split(gemm, M, N, K):
+    x, w = rnd(M, K), rnd(N, K, seed=1)
+    ref = x.float() @ w.float().t()
+    assert gemm.ksplit
+    y_split = gemm.linear(x, w)
+    gemm.ksplit = False
+    y_plain = gemm.linear(x, w)
+    gemm.ksplit = True
+    gemm.check()
+    check(y_split, ref, "y, K split")
+    check(y_plain, ref, "y, one CTA per tile")
+    wide = torch.zeros(M, N + 64, device=DEV, dtype=torch.bfloat16)
+    gemm.linear(x, w, out=wide[:, 32:32 + N])
+    gemm.check()
+    check(wide[:, 32:32 + N], ref, "y into a column block")
+    assert wide[:, :32].abs().max().item() == 0 and wide[:, 32 + N:].abs().max().item() == 0
+    wn = rnd(K, N, seed=3)
+    check(gemm.linear_dx(x, wn), x.float() @ wn.float(), "dx, K split")
+    b = rnd(N, seed=4)
+    check(gemm.linear(x, w, bias=b), ref + b.float(), "y + bias, K split")
+    for _ in range(3):                                   # back-to-back launches: barriers and tensor memory start clean
+        check(gemm.linear(x, w), ref, "y, repeated")
+    gemm.check()
+
+
 # the last two have a long reduction and few output tiles: the split-K path with even and ragged slices
 @pytest.mark.parametrize("M,N,K", SHAPES[:5] + [(136, 264, 72), (16384, 512, 256), (8256, 264, 136)])
 def test_linear_dw_acc(gemm, M, N, K):

@@ -1,5 +1,5 @@
-"""The CTA-pair GEMM (tcgen05 cta_group::2, 256 x 256 tiles over two SMs) against torch.matmul in fp32, for the
-three operand layouts, ragged tails, bias, fp32 accumulate and the split-K path."""
+"""The CTA-pair GEMM (tcgen05 cta_group::2, 256 x 256 and 256 x 128 tiles over two SMs) against torch.matmul in
+fp32, for the three operand layouts, ragged tails, bias, fp32 accumulate and the split-K path."""
 
 import pytest
 import torch
@@ -8,13 +8,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.fixture(scope="module")
-def gemm():
+@pytest.fixture(scope="module", params=[256, 128], ids=["pair256x256", "pair256x128"])
+def gemm(request):
     from dual_mod_public_b200.ops.cuda_ops import load_library
     from dual_mod_public_b200.ops.gemm import Tcgen05Gemm
     g = Tcgen05Gemm(load_library(), torch.device(DEV))
     g.pair = True
-    return g
+    g.pair_width(request.param)
+    yield g
+    g.pair_width(0)
 
 
 def rnd(*s, seed=0):
@@ -70,3 +72,16 @@ def test_repeated_launches_reuse_the_pipeline(gemm):
     for _ in range(5):
         check(gemm.linear(x, w), ref, "y")
     gemm.check()
+
+
+def test_the_narrow_route_takes_the_sweep_input_gradient():
+    """DMB_GEMM_PAIR=narrow: bf16 results with too few 256-wide tiles for the SMs go to 256 x 128 pair tiles."""
+    from dual_mod_public_b200.ops.cuda_ops import load_library
+    from dual_mod_public_b200.ops.gemm import Tcgen05Gemm
+    g = Tcgen05Gemm(load_library(), torch.device(DEV))
+    g.pair = "narrow"
+    dy, w = rnd(2048, 4096), rnd(4096, 1024, seed=1)
+    check(g.linear_dx(dy, w), dy.float() @ w.float(), "dx")
+    x, w2 = rnd(1024, 2304), rnd(2304, 2304, seed=2)
+    check(g.linear(x, w2), x.float() @ w2.float().t(), "y")
+    g.check()
