@@ -204,17 +204,44 @@ def main():
     cg, glx, k, v = rnd(B, c, 4 * d), rnd(B, Tlen, 2 * d), rnd(B, Tlen, d), rnd(B, Tlen, d)
     N = B * c
     if want("refine_fwd"):
-        report("refine_fwd", T(lambda: ops.refine_fwd(cg, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, 0)),
-               bytes_=N * d * 2 * 10)
+        for nt in (256, 128):
+            ops.lib.dmb_refine_fwd_threads(nt)
+            report(f"refine_fwd [{nt} threads per block]",
+                   T(lambda: ops.refine_fwd(cg, ssq, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], h, 0)), bytes_=N * d * 2 * 10)
     dK, dV = rnd(B, c, h, dh, dtype=torch.float32), rnd(B, c, h, dh, dtype=torch.float32)
     dk_a, dv_a, dg_a = z(B, Tlen, d), z(B, Tlen, d), z(B, Tlen, 2 * d)
     if want("refine_bwd"):
         dcg_o, uh_o, o2 = torch.empty_like(cg), rnd(B, c, d), o.reshape(B, c, d)
-        report("refine_bwd", T(lambda: ops.refine_bwd(dK, dV, cg, ssq, o2, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], 0,
-                                                      dk_a[:, r], dv_a[:, r], dg_a[:, r], dcg_o, uh_o)),
-               bytes_=N * d * 68)
+        for mb in (3, 4, 5):
+            ops.lib.dmb_refine_bwd_minblocks(mb)
+            report(f"refine_bwd [{mb} blocks per SM]",
+                   T(lambda: ops.refine_bwd(dK, dV, cg, ssq, o2, glx[:, r], k[:, r], v[:, r], cos[r], sin[r], 0,
+                                            dk_a[:, r], dv_a[:, r], dg_a[:, r], dcg_o, uh_o)), bytes_=N * d * 68)
+        ops.lib.dmb_refine_bwd_minblocks(4)
         du = rnd(B, c, d)
         report("rmsn_bwd", T(lambda: ops.rmsn_bwd(du, o2, ssq)), bytes_=N * d * 8)
+    # ---- write law of the mult_res family at the 18 x d2304 recipe's step: 16 sequences x a window of 512 rows, 36 heads
+    if want("mrk"):
+        Bm, cm, hm = 16, 512, 36
+        dm = hm * dh
+        Nm = Bm * cm
+        cosm, sinm = build_rope_cache(cm, dh, 10000.0, device=DEV)
+        raw_m, vc_m, o_m = rnd(Bm, cm, 4 * dm), rnd(Bm, cm, dm), rnd(Bm, cm, dm)
+        ssq_m = (o_m.float().view(Bm, cm, hm, dh) ** 2).sum(-1)
+        glx_m, k_m, v_m = rnd(Bm, cm, 2 * dm), rnd(Bm, cm, dm), rnd(Bm, cm, dm)
+        kg = torch.ones(hm, device=DEV)
+        report("mrk_refine_fwd", T(lambda: ops.mrk_refine_fwd(raw_m, vc_m, ssq_m, glx_m, k_m, v_m, cosm, sinm, hm, 0, kg, 1.0)),
+               bytes_=Nm * dm * 2 * 11)
+        dKm, dVm = rnd(Bm, cm, hm, dh, dtype=torch.float32), rnd(Bm, cm, hm, dh, dtype=torch.float32)
+        dka, dva = z(Bm, cm, dm), z(Bm, cm, dm)
+        dcg_m, uh_m, dvc_m, dkg_m = torch.empty_like(raw_m), torch.empty_like(o_m), torch.empty_like(o_m), z(Nm, hm)
+        for mb in (2, 3, 4):
+            ops.lib.dmb_mrk_refine_bwd_minblocks(mb)
+            report(f"mrk_refine_bwd [{mb} blocks per SM]",
+                   T(lambda: ops.mrk_refine_bwd(dKm, dVm, raw_m, vc_m, ssq_m, o_m, glx_m, k_m, v_m, cosm, sinm, 0, kg, 1.0,
+                                                dka, dva, None, dcg_m, uh_m, dvc_m, dkg_m)), bytes_=Nm * dm * 52)
+        ops.lib.dmb_mrk_refine_bwd_minblocks(4)
+        assert not ops.fallbacks, ops.fallbacks
     if want("chain"):
         # one forward sweep (tail read -> packed GEMM -> refine) and one backward sweep (refine -> GEMM -> norm -> tail)
         # as their launches follow one another in a replayed CUDA graph of 16 sweeps, against the sum of the parts

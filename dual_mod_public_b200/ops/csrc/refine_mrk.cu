@@ -96,8 +96,8 @@ __global__ void mrk_vin_bwd_kernel(const bf16* __restrict__ dvin, const bf16* __
 
 // ---- blend / norm / clamp / rope -------------------------------------------------------------------
 struct Fwd {
-  V8 kc[2], kn[2], gk[2], gv[2], vpre[2], kraw[2], vraw[2], vcv[2];
-  float rs, rh, nrm2, shrink;
+  V8 kc[2], gk[2], gv[2], vpre[2], kraw[2], vdiff[2];      // kc: rstd-scaled ctx key; vdiff = v_raw - v_c
+  float rs, rh, gain, nrm2, shrink;                        // normalised ctx key k_n = kc * rh * gain
 };
 // everything the forward computes for this thread's 16 elements (shared by forward and backward)
 __device__ __forceinline__ void mrk_forward_parts(Fwd& f, const Loc& L, const bf16* raw, const bf16* vc, const float* ssq,
@@ -108,14 +108,15 @@ __device__ __forceinline__ void mrk_forward_parts(Fwd& f, const Loc& L, const bf
   f.rs = row_rstd(ssq + w.row * H, H, d, eps);
   const bf16* rr = raw + w.row * 4 * d;
   float s2 = 0.f;
+  V8 vraw[2], vcv[2];
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int col = e ? w.c1 : w.c0;
     f.kc[e] = ld8(rr + col);
     const V8 gku = ld8(rr + 2 * d + col), gvu = ld8(rr + 3 * d + col), gxk = ld8(gr + col), gxv = ld8(gr + d + col);
     f.kraw[e] = ld8(kr + col);
-    f.vraw[e] = ld8(vr + col);
-    f.vcv[e] = ld8(vc + w.row * d + col);
+    vraw[e] = ld8(vr + col);
+    vcv[e] = ld8(vc + w.row * d + col);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       f.kc[e].x[i] *= f.rs;
@@ -125,16 +126,16 @@ __device__ __forceinline__ void mrk_forward_parts(Fwd& f, const Loc& L, const bf
     }
   }
   f.rh = rsqrtf(head_sum(s2, L.per_head) / DH + 1e-6f);
-  const float gain = k_gain[L.h];
+  f.gain = k_gain[L.h];
   float n2 = 0.f;
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int col = e ? w.c1 : w.c0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      f.kn[e].x[i] = f.kc[e].x[i] * f.rh * gain;
       const float gv = f.gv[e].x[i];
-      f.vpre[e].x[i] = (col + i < pin_cols) ? f.vraw[e].x[i] : gv * f.vraw[e].x[i] + (1.f - gv) * f.vcv[e].x[i];
+      f.vdiff[e].x[i] = vraw[e].x[i] - vcv[e].x[i];
+      f.vpre[e].x[i] = (col + i < pin_cols) ? vraw[e].x[i] : vcv[e].x[i] + gv * f.vdiff[e].x[i];
       n2 += f.vpre[e].x[i] * f.vpre[e].x[i];
     }
   }
@@ -161,7 +162,7 @@ __global__ void mrk_refine_fwd_kernel(const bf16* __restrict__ raw, const bf16* 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float gk = f.gk[e].x[i];
-      kk[e].x[i] = gk * f.kraw[e].x[i] + (1.f - gk) * f.kn[e].x[i];
+      kk[e].x[i] = gk * f.kraw[e].x[i] + (1.f - gk) * (f.kc[e].x[i] * f.rh * f.gain);
       vo[e].x[i] = f.vpre[e].x[i] * f.shrink;
     }
   V8 k0, k1;
@@ -182,7 +183,8 @@ __global__ void mrk_refine_fwd_kernel(const bf16* __restrict__ raw, const bf16* 
 // dK / dV fp32 dense [B,C,H,DH].  Writes dcg blocks 0, 2, 3 (bf16 [rows,4d]; block 1 = d v_m comes from
 // mrk_vin_bwd), uhat = o * rstd, dvc (bf16 [rows,d]) and the per-(row, head) k_gain gradient dkg [rows,H];
 // accumulates dk_acc / dv_acc [.., d] and dglx_acc [.., 2d] (fp32, +=).
-__global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV, TView vdo,
+template <int MINB>
+__global__ void __launch_bounds__(128, MINB) mrk_refine_bwd_kernel(const float* __restrict__ dK, const float* __restrict__ dV, TView vdo,
                                       const bf16* __restrict__ raw,
                                       const bf16* __restrict__ vc, const float* __restrict__ ssq, const bf16* __restrict__ o,
                                       const bf16* __restrict__ glx, TView vg, const bf16* __restrict__ k, TView vk,
@@ -217,21 +219,18 @@ __global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float*
   dot = head_sum(dot, L.per_head);
   const bool outside = f.shrink < 1.f;
   const float proj = dot / f.nrm2;
-  const float gain = k_gain[L.h];
-  float s_dx = 0.f, s_g = 0.f;
-  V8 dkn[2];
+  const float gain = f.gain;
+  float s_g = 0.f;
 #pragma unroll
   for (int e = 0; e < 2; ++e)
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if (outside) dvo[e].x[i] = f.shrink * (dvo[e].x[i] - f.vpre[e].x[i] * proj);
-      dkn[e].x[i] = dkpp[e].x[i] * (1.f - f.gk[e].x[i]);
-      const float xh = f.kc[e].x[i] * f.rh;            // normalised ctx key
-      s_g += dkn[e].x[i] * xh;
-      s_dx += dkn[e].x[i] * gain * xh;
+      const float dkn = dkpp[e].x[i] * (1.f - f.gk[e].x[i]);
+      s_g += dkn * (f.kc[e].x[i] * f.rh);              // d k_n . normalised ctx key
     }
   s_g = head_sum(s_g, L.per_head);
-  s_dx = head_sum(s_dx, L.per_head) / DH;
+  const float s_dx = s_g * gain / DH;
   bf16* dr = dcg + w.row * 4 * d;
   float* dkr = dk_acc + w.b * vdk.bs + w.t * vdk.rs;
   float* dvr = dv_acc + w.b * vdv.bs + w.t * vdv.rs;
@@ -247,9 +246,9 @@ __global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float*
       const bool pinned = col + i < pin_cols;
       const float dvp = pinned ? 0.f : dvo[e].x[i];
       const float xh = f.kc[e].x[i] * f.rh;
-      dkc.x[i] = f.rh * (dkn[e].x[i] * gain - xh * s_dx);
-      dgk.x[i] = dkpp[e].x[i] * (f.kraw[e].x[i] - f.kn[e].x[i]) * gk * (1.f - gk);
-      dgv.x[i] = dvp * (f.vraw[e].x[i] - f.vcv[e].x[i]) * gv * (1.f - gv);
+      dkc.x[i] = f.rh * (dkpp[e].x[i] * (1.f - gk) * gain - xh * s_dx);
+      dgk.x[i] = dkpp[e].x[i] * (f.kraw[e].x[i] - xh * gain) * gk * (1.f - gk);
+      dgv.x[i] = dvp * f.vdiff[e].x[i] * gv * (1.f - gv);
       dvcv.x[i] = dvp * (1.f - gv);
       dkk.x[i] = dkpp[e].x[i] * gk;
       dvv.x[i] = pinned ? dvo[e].x[i] : dvp * gv;
@@ -273,6 +272,8 @@ __global__ void mrk_refine_bwd_kernel(const float* __restrict__ dK, const float*
 }
 
 }  // namespace
+
+namespace { int g_mrk_bwd_minb = 4; }
 
 extern "C" {
 
@@ -312,16 +313,22 @@ int dmb_mrk_refine_fwd(const void* raw, const void* vc, const float* ssq, const 
   return 0;
 }
 
+// resident blocks per SM the compiler sizes the backward kernel's registers for (2, 3 or 4; measured at 8192 rows x
+// 2304: 274 / 226 / 216 us, the last with 128 registers and 180 bytes of spills)
+void dmb_mrk_refine_bwd_minblocks(int n) { g_mrk_bwd_minb = n; }
+
 int dmb_mrk_refine_bwd(const float* dK, const float* dV, TView vdo, const void* raw, const void* vc, const float* ssq, const void* o,
                        const void* glx, TView vg, const void* k, TView vk, const void* v, TView vv, const float* cosb,
                        const float* sinb, const float* k_gain, void* dcg, void* uhat, void* dvc, float* dkg, float* dk_acc,
                        TView vdk, float* dv_acc, TView vdv, float* dglx_acc, TView vdg, int B, int C, int H, int DH,
                        int pin_cols, float tau, float eps, cudaStream_t st) {
   if (DH % 16) return -1;
-  mrk_refine_bwd_kernel<<<mrk_blocks(B, C, H, DH, 128), 128, 0, st>>>(
-      dK, dV, vdo, (const bf16*)raw, (const bf16*)vc, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v,
-      vv, cosb, sinb, k_gain, (bf16*)dcg, (bf16*)uhat, (bf16*)dvc, dkg, dk_acc, vdk, dv_acc, vdv, dglx_acc, vdg, B, C, H, DH,
-      pin_cols, tau, eps);
+#define RB_GO(MB) mrk_refine_bwd_kernel<MB><<<mrk_blocks(B, C, H, DH, 128), 128, 0, st>>>( \
+      dK, dV, vdo, (const bf16*)raw, (const bf16*)vc, ssq, (const bf16*)o, (const bf16*)glx, vg, (const bf16*)k, vk, (const bf16*)v, \
+      vv, cosb, sinb, k_gain, (bf16*)dcg, (bf16*)uhat, (bf16*)dvc, dkg, dk_acc, vdk, dv_acc, vdv, dglx_acc, vdg, B, C, H, DH, \
+      pin_cols, tau, eps)
+  if (g_mrk_bwd_minb == 2) { RB_GO(2); } else if (g_mrk_bwd_minb == 3) { RB_GO(3); } else { RB_GO(4); }
+#undef RB_GO
   DMB_CHECK_LAUNCH();
   return 0;
 }
