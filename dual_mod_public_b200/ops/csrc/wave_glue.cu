@@ -185,7 +185,8 @@ struct SweepPtrs {
   const float* dO[64];
 };
 
-template <int DH, typename TD>
+// KT > 0: the sweep count as a compile-time constant (the loop unrolls and every sweep's loads are issued up front)
+template <int DH, typename TD, int KT>
 __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
     SweepPtrs sp, int K, const float* __restrict__ scal, const bf16* __restrict__ q, TView vq,
     const bf16* __restrict__ ks, TView vks, const bf16* __restrict__ vr, TView vvr, const float* __restrict__ o_c, const float* __restrict__ lse_c,
@@ -211,7 +212,10 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
 #pragma unroll
   for (int e = 0; e < PER; ++e) av[e] = ac[e] = 0.f;
   float dss = 0.f, dl = 0.f;
-  for (int k = K - 1; k >= 0; --k) {
+  const int Kn = KT > 0 ? KT : K;
+#pragma unroll
+  for (int kk = 0; kk < Kn; ++kk) {
+    const int k = Kn - 1 - kk;
     const float* sc = scal + (long long)k * 3 * n + wid;
     const float ps = sc[0], pc = sc[n], delta = sc[2 * n];
     float g[PER], dsv = 0.f, dc = 0.f;
@@ -449,9 +453,16 @@ int dmb_cell_finish_sweeps(const float* const* dO_ptrs, int K, const float* scal
   const long long warps = (long long)B * R * H;
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
 #define GO(D, T)                                                                                                    \
-  cell_finish_sweeps_kernel<D, T><<<blocks, 256, 0, st>>>(sp, K, scal, (const bf16*)q, vq, (const bf16*)ks, vks,    \
-                                                          (const bf16*)vr, vvr, o_c, lse_c, dK0, dV0, (T*)doc, corr, \
-                                                          corr_dense, lsec, dks, dv, dq, scale, bs_vec, bs_sca, B, R, H)
+  do {                                                                                                              \
+    if (K == 4)                                                                                                     \
+      cell_finish_sweeps_kernel<D, T, 4><<<blocks, 256, 0, st>>>(sp, K, scal, (const bf16*)q, vq, (const bf16*)ks, vks, \
+          (const bf16*)vr, vvr, o_c, lse_c, dK0, dV0, (T*)doc, corr, corr_dense, lsec, dks, dv, dq, scale, bs_vec,   \
+          bs_sca, B, R, H);                                                                                         \
+    else                                                                                                            \
+      cell_finish_sweeps_kernel<D, T, 0><<<blocks, 256, 0, st>>>(sp, K, scal, (const bf16*)q, vq, (const bf16*)ks, vks, \
+          (const bf16*)vr, vvr, o_c, lse_c, dK0, dV0, (T*)doc, corr, corr_dense, lsec, dks, dv, dq, scale, bs_vec,   \
+          bs_sca, B, R, H);                                                                                         \
+  } while (0)
   if (DH == 64) {
     if (doc_bf16) GO(64, bf16); else GO(64, float);
   } else if (DH == 128) {

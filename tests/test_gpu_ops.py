@@ -252,6 +252,24 @@ def test_refine_fwd_bwd(ops, pin):
     close(ops.rmsn_bwd(du, o, ssq, out_dtype=torch.bfloat16), fm.rmsn_bwd(f(du), f(o), ssq), what="rmsn_bwd bf16")
 
 
+@pytest.mark.parametrize("H", [16, 8])
+def test_norm_backward_at_the_sweep_shape(ops, H):
+    """d = 1024, 2048 rows and a ragged 1001, both result types, with and without the residual."""
+    from dual_mod_public_b200.engines import fused_math as fm
+    d = 1024
+    for rows in (2048, 1001):
+        du, o = rnd(1, rows, d, seed=21), rnd(1, rows, d, seed=22)
+        ssq = (o.float().view(1, rows, H, d // H) ** 2).sum(-1)
+        res = rnd(1, rows, d, dtype=torch.float32, seed=23)
+        ref = fm.rmsn_bwd(du.float(), o.float(), ssq)
+        close(ops.rmsn_bwd(du, o, ssq), ref, what="fp32 out")
+        close(ops.rmsn_bwd(du, o, ssq, residual=res), ref + res, what="fp32 out + residual")
+        close(ops.rmsn_bwd(du, o, ssq, out_dtype=torch.bfloat16), ref, what="bf16 out")
+        rb = res.bfloat16()
+        close(ops.rmsn_bwd(du, o, ssq, residual=rb, out_dtype=torch.bfloat16), ref + rb.float(), what="bf16 out + residual")
+    assert "rmsn_bwd" not in ops.fallbacks
+
+
 def test_col_sum(ops):
     x = rnd(1000, 2048, dtype=torch.float32)
     out = torch.ones(2048, device=DEV)
