@@ -14,6 +14,12 @@
 //            straight into every peer's parameter buffer (P2P stores)
 //   phase 4  closing flag barrier: every rank's parameters are complete
 //
+// NVLS variant (DmbOptComm::mc_grads / mc_params set; the two buffers then come from an allocation bound to an
+// NVLink multicast object): phase 1 is one multimem.ld_reduce.add per 16 bytes of the owned slice, the sum formed
+// inside the switch (its order is the switch's, but only the owner reduces an element and everyone receives the
+// owner's parameter, so all ranks still end with identical bytes); phase 3 is one multimem.st per 16 bytes.  Flags
+// and norm slots stay on plain peer stores, every wait stays bounded.
+//
 // Buckets whose reduce-scatter already ran (launched early, overlapped with the backward, by
 // dmb_opt_reduce_bucket) are skipped in phase 1.  Every cross-GPU wait is bounded in time; on
 // expiry the kernel records where it gave up in `status` and carries on without hanging, the host
@@ -35,6 +41,11 @@ struct DmbOptComm {
   float* params[DMB_MAX_WORLD];        // peer-mapped flat parameter buffers
   unsigned* flags[DMB_MAX_WORLD];      // peer-mapped flag pads: [n_slots][world]
   float* norms[DMB_MAX_WORLD];         // peer-mapped [2][world] partial squared norms (double buffered)
+  // NVLink multicast addresses of the gradient and parameter buffers (NVLS), or null.  With them phase 1 reads
+  // the sum over all ranks with one multimem.ld_reduce per 16 bytes (the switch adds) and phase 3 stores the
+  // updated parameters to every rank with one multimem.st, instead of `world` peer loads / stores.
+  float* mc_grads;
+  float* mc_params;
 };
 
 struct DmbOptPlan {
@@ -123,9 +134,16 @@ __device__ float reduce_slice(const DmbOptComm& c, long long off, long long len,
   float ss = 0.f;
   for (long long i = tid * 4; i < slice; i += nthreads * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < c.world; ++p) {
-      float4 g = *reinterpret_cast<const float4*>(c.grads[p] + base + i);
-      acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+    if (c.mc_grads) {
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
+                   : "l"(c.mc_grads + base + i)
+                   : "memory");
+    } else {
+      for (int p = 0; p < c.world; ++p) {
+        float4 g = *reinterpret_cast<const float4*>(c.grads[p] + base + i);
+        acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+      }
     }
     acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
     *reinterpret_cast<float4*>(c.grads[c.rank] + base + i) = acc;
@@ -263,9 +281,15 @@ __global__ void __launch_bounds__(512) fused_step_kernel(
         }
         *reinterpret_cast<float4*>(m + mo + i) = mm;
         *reinterpret_cast<float4*>(v + mo + i) = vv;
-        for (int q = 0; q < c.world; ++q) {
-          const int peer = (c.rank + q) % c.world;      // spread the store targets over the links
-          *reinterpret_cast<float4*>(c.params[peer] + base + i) = p;
+        if (c.mc_params) {
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                       ::"l"(c.mc_params + base + i), "f"(p.x), "f"(p.y), "f"(p.z), "f"(p.w)
+                       : "memory");
+        } else {
+          for (int q = 0; q < c.world; ++q) {
+            const int peer = (c.rank + q) % c.world;      // spread the store targets over the links
+            *reinterpret_cast<float4*>(c.params[peer] + base + i) = p;
+          }
         }
       }
     }

@@ -284,7 +284,8 @@ struct ChunkSweeps {
   long long bs_sca[64];
 };
 
-template <int DH, typename TD>
+// KT > 0: the sweep count as a compile-time constant (the loop unrolls and every sweep's loads are issued up front)
+template <int DH, typename TD, int KT>
 __global__ void __launch_bounds__(256) chunk_finish_kernel(
     const float* __restrict__ DOf, const float* __restrict__ DLf, const float* __restrict__ o_f,
     const float* __restrict__ lse_f, float* __restrict__ dKp, float* __restrict__ dVp, float* __restrict__ dks,
@@ -305,7 +306,10 @@ __global__ void __launch_bounds__(256) chunk_finish_kernel(
 #pragma unroll
   for (int e = 0; e < PER; ++e) av[e] = agk[e] = agv[e] = 0.f;
   const long long d = (long long)H * DH;
-  for (int k = K - 1; k >= 0; --k) {
+  const int Kn = KT > 0 ? KT : K;
+#pragma unroll
+  for (int kk = 0; kk < Kn; ++kk) {
+    const int k = Kn - 1 - kk;
     const long long so = (long long)b * sw.bs_sca[k] + (long long)r * H + h;
     const float ps = sw.ps[k][so];
     dss += sw.dss[k][so];
@@ -497,9 +501,14 @@ int dmb_wave_chunk_finish(const float* DOf, const float* DLf, const float* o_f, 
   const long long warps = (long long)B * R * H;
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
 #define GO(D, T)                                                                                                 \
-  chunk_finish_kernel<D, T><<<blocks, 256, 0, st>>>(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, (T*)doc, corr, lsec, \
-                                                    corr_dense, lse_dense, bs_vec, bs_sca, B, R, H, sw, K,        \
-                                                    (const bf16*)q, vq, dglx, bs_dglx)
+  do {                                                                                                           \
+    if (K == 8)                                                                                                  \
+      chunk_finish_kernel<D, T, 8><<<blocks, 256, 0, st>>>(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, (T*)doc, corr, \
+          lsec, corr_dense, lse_dense, bs_vec, bs_sca, B, R, H, sw, K, (const bf16*)q, vq, dglx, bs_dglx);       \
+    else                                                                                                         \
+      chunk_finish_kernel<D, T, 0><<<blocks, 256, 0, st>>>(DOf, DLf, o_f, lse_f, dKp, dVp, dks, dv, (T*)doc, corr, \
+          lsec, corr_dense, lse_dense, bs_vec, bs_sca, B, R, H, sw, K, (const bf16*)q, vq, dglx, bs_dglx);       \
+  } while (0)
   if (DH == 64) {
     if (doc_bf16) GO(64, bf16); else GO(64, float);
   } else if (DH == 128) {

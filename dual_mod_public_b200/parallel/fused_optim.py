@@ -19,7 +19,9 @@ Replaces the reference's unfused chain `finish_grads` (reduce + div + broadcast 
 one flat tensor, engines/wavescan/engine/graphs.py:768-792) or `GradAllReducer`
 (lm/train_1p3b/train_hero_wave3d.py:314-352), then `clip_grad_norm_`, the skip
 decision and `torch.optim.AdamW.step()`.  `NcclAdamW` is that baseline chain behind
-the same interface.  `state_dict()` gathers the sharded moments into the plain
+the same interface.  With `nvls=True` (or DMB_NVLS=1) the gradient and parameter arrays are bound to an NVLink
+multicast object instead and the two collective phases run as `multimem.ld_reduce` / `multimem.st` (the NVSwitch
+adds and replicates); flags, waits and the status word are the same.  `state_dict()` gathers the sharded moments into the plain
 torch AdamW layout, so checkpoints stay interchangeable.
 
 Without a CUDA device (CPU tests, gloo ranks) the same bucket / slice / segment
@@ -30,6 +32,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -44,7 +47,8 @@ ALIGN = 64
 class _Comm(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int),
                 ("grads", ctypes.c_void_p * MAX_WORLD), ("params", ctypes.c_void_p * MAX_WORLD),
-                ("flags", ctypes.c_void_p * MAX_WORLD), ("norms", ctypes.c_void_p * MAX_WORLD)]
+                ("flags", ctypes.c_void_p * MAX_WORLD), ("norms", ctypes.c_void_p * MAX_WORLD),
+                ("mc_grads", ctypes.c_void_p), ("mc_params", ctypes.c_void_p)]
 
 
 class _Plan(ctypes.Structure):
@@ -128,6 +132,34 @@ class PeerBuffer:
             self.own = None
 
 
+class MulticastBuffer:
+    """The same surface as `PeerBuffer`, with the memory taken from torch's symmetric-memory allocator and bound to
+    an NVLink multicast object: `mc` is the multicast address (one multimem.ld_reduce reads the sum over all ranks,
+    one multimem.st writes to all ranks), `ptrs[r]` rank r's copy as seen from this process.  Raises when the
+    group has no multicast mapping (no NVSwitch, or NVLS not available to this process)."""
+
+    def __init__(self, nbytes, device, group, rank, world):
+        import torch.distributed._symmetric_memory as symm
+        self.nbytes, self.rank, self.world = nbytes, rank, world
+        self.bytes_tensor = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.bytes_tensor.zero_()
+        self._hdl = symm.rendezvous(self.bytes_tensor, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        self.own = self.ptrs[rank]
+        self.mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0)
+        assert self.own == self.bytes_tensor.data_ptr()
+        if not self.mc:
+            raise RuntimeError("the process group has no NVLink multicast mapping (NVLS) for this allocation")
+
+    def view(self, dtype, numel=None):
+        t = self.bytes_tensor.view(dtype)
+        return t if numel is None else t[:numel]
+
+    def close(self):
+        self._hdl = None
+        self.own = None
+
+
 def _pad(n, m):
     return -(-n // m) * m
 
@@ -199,7 +231,7 @@ def decay_groups(model, weight_decay, decay_all=False):
 class FusedDPAdamW:
     def __init__(self, param_groups, buckets, *, lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
                  max_norm=1.0, skip_norm=0.0, grad_accum=1, process_group=None, device=None,
-                 wait_seconds=5.0, use_kernel=None):
+                 wait_seconds=5.0, use_kernel=None, nvls=None):
         self.group = process_group
         if dist.is_available() and dist.is_initialized():
             self.world, self.rank = dist.get_world_size(process_group), dist.get_rank(process_group)
@@ -228,6 +260,7 @@ class FusedDPAdamW:
         # 1 / (ranks kept * micro-batches); None = 1 / (world * micro-batches)
         self.grad_scale_override = None
         self.wait_seconds = wait_seconds
+        self.nvls = False
         n = self.layout.numel
         nslots = SLOT_BUCKET0 + len(self.layout.buckets)
         if self.use_kernel:
@@ -235,7 +268,15 @@ class FusedDPAdamW:
             self.lib = load_library()
             self._bind()
             mk = lambda nbytes: PeerBuffer(self.lib, nbytes, self.device, self.group, self.rank, self.world)
-            self._pb_grads, self._pb_params = mk(4 * n), mk(4 * n)
+            # NVLS variant (opt-in: `nvls=True` or DMB_NVLS=1): gradient and parameter buffers bound to an NVLink
+            # multicast object, reduce-scatter by multimem.ld_reduce and all-gather by multimem.st.  Not for runs in
+            # which a rank may leave while the others still hold the mapping.
+            self.nvls = bool(int(os.environ.get("DMB_NVLS", "0")) if nvls is None else nvls) and self.world > 1
+            if self.nvls:
+                mc = lambda nbytes: MulticastBuffer(nbytes, self.device, self.group, self.rank, self.world)
+                self._pb_grads, self._pb_params = mc(4 * n), mc(4 * n)
+            else:
+                self._pb_grads, self._pb_params = mk(4 * n), mk(4 * n)
             self._pb_flags, self._pb_norms = mk(4 * nslots * MAX_WORLD), mk(4 * 2 * MAX_WORLD)
             self.flat_grads = self._pb_grads.view(torch.float32, n)
             self.flat_params = self._pb_params.view(torch.float32, n)
@@ -271,6 +312,8 @@ class FusedDPAdamW:
             for r in range(self.world):
                 self._comm.grads[r], self._comm.params[r] = self._pb_grads.ptrs[r], self._pb_params.ptrs[r]
                 self._comm.flags[r], self._comm.norms[r] = self._pb_flags.ptrs[r], self._pb_norms.ptrs[r]
+            self._comm.mc_grads = self._pb_grads.mc if self.nvls else None
+            self._comm.mc_params = self._pb_params.mc if self.nvls else None
             sm_hz = 1.9e9
             self._wait_cycles = int(wait_seconds * sm_hz)
         if self.world > 1:
@@ -497,6 +540,8 @@ class FusedDPAdamW:
     def close(self):
         if self.use_kernel:
             torch.cuda.synchronize(self.device)
+            if self.nvls:
+                dist.barrier(group=self.group)       # nobody unmaps while a peer may still store through the multicast address
             for pb in (self._pb_grads, self._pb_params, self._pb_flags, self._pb_norms):
                 pb.close()
 

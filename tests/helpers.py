@@ -49,3 +49,11 @@ def perturb(model, seed=7, gate_bias=0.0, ctx_std=0.05):
 def rand_idx(cfg, B, T, device="cpu", seed=99):
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, cfg.vocab_size, (B, T), generator=g).to(device)
+
+
+def free_port():
+    """A TCP port nobody listens on right now (bound to 0 and released), for the rendezvous of spawned ranks."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]

@@ -12,7 +12,7 @@ import torch.multiprocessing as mp
 from dual_mod_public_b200.parallel.fused_optim import (FusedDPAdamW, NcclAdamW, decay_groups,
                                                        default_buckets)
 
-from helpers import make_model, rand_idx, small_cfg
+from helpers import free_port, make_model, rand_idx, small_cfg
 
 
 def _grads_like(params, seed):
@@ -141,7 +141,7 @@ def _rank_main(rank, world, port, q):
 def test_gloo_ranks_equal_single_process(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + world + (os.getpid() % 200)
+    port = free_port()
     procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()

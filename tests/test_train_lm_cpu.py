@@ -9,6 +9,7 @@ import torch
 
 from dual_mod_public_b200.train import governors as G
 from dual_mod_public_b200.train.train_lm import main as train_main
+from helpers import free_port
 
 
 def test_skip_rule_grace_threshold_breaker():
@@ -270,7 +271,7 @@ def _spawn_lm(tmp_path, name, extra, env=None, world=2):
     import torch.multiprocessing as mp
     out = str(tmp_path / name)
     ctx = mp.get_context("spawn")
-    port = 29800 + (os.getpid() % 150) + len(name)
+    port = free_port()
     procs = [ctx.Process(target=_lm_rank, args=(r, world, port, out, extra, env or {})) for r in range(world)]
     for p in procs:
         p.start()
