@@ -193,16 +193,19 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
     const float* __restrict__ dK0, const float* __restrict__ dV0, TD* __restrict__ doc, float* __restrict__ corr,
     float* __restrict__ corr_dense, float* __restrict__ lsec, float* __restrict__ dks, float* __restrict__ dv,
     float* __restrict__ dq, float scale, long long bs_vec, long long bs_sca, int B, int R, int H) {
+  // DH = 64: half a warp per (batch, row, head), 16 bytes per lane; DH = 128: a warp, 16 bytes per lane.  Lanes past
+  // the end stay in the shuffles (clamped to the last unit) and store nothing.
+  constexpr int LPH = DH == 64 ? 16 : 32, PER = DH / LPH;
   const long long n = (long long)B * R * H;
-  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (wid >= n) return;
+  const long long unit = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPH;
+  const bool live = unit < n;
+  const long long wid = live ? unit : n - 1;
+  const int lane = threadIdx.x & (LPH - 1);
   const int h = (int)(wid % H);
   const long long br = wid / H;
   const int r = (int)(br % R), b = (int)(br / R);
   const long long s_abs = (long long)b * bs_sca + (long long)r * H + h;
   const long long v_abs = (long long)b * bs_vec + ((long long)r * H + h) * DH;
-  constexpr int PER = DH / 32;
   const bf16* q_row = q + b * vq.bs + r * vq.rs + (long long)h * DH;
   const bf16* ks_row = ks + b * vks.bs + r * vks.rs + (long long)h * DH;
   const bf16* vr_row = vr + b * vvr.bs + r * vvr.rs + (long long)h * DH;
@@ -228,7 +231,7 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
       ac[e] += pc * g[e];
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = LPH / 2; o > 0; o >>= 1) {
       dsv += __shfl_xor_sync(0xffffffffu, dsv, o);
       dc += __shfl_xor_sync(0xffffffffu, dc, o);
     }
@@ -250,11 +253,13 @@ __global__ void __launch_bounds__(256) cell_finish_sweeps_kernel(
     a_v[e] += v0[e] + av[e];
     a_q[e] += dss * kv[e];
   }
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (!live) return;
   stv<PER>(doc + v_abs + lane * PER, ac);
   stf<PER>(dks + v_abs + lane * PER, a_k);
   stf<PER>(dv + v_abs + lane * PER, a_v);
   stf<PER>(dq + v_abs + lane * PER, a_q);
-  dot = warp_sum(dot);
   if (lane == 0) {
     const float cv = dot - dl;
     corr[s_abs] = cv;
@@ -454,8 +459,8 @@ int dmb_cell_finish_sweeps(const float* const* dO_ptrs, int K, const float* scal
   if (K < 1 || K > 64) return -1;
   SweepPtrs sp;
   for (int k = 0; k < 64; ++k) sp.dO[k] = dO_ptrs[k < K ? k : K - 1];
-  const long long warps = (long long)B * R * H;
-  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  const long long lanes = (long long)B * R * H * (DH == 64 ? 16 : 32);
+  const unsigned blocks = (unsigned)((lanes + 255) / 256);
 #define GO(D, T)                                                                                                    \
   do {                                                                                                              \
     if (K == 4)                                                                                                     \
