@@ -34,6 +34,23 @@ def _aligned(t, ld):
     return t.data_ptr() % 16 == 0 and ld % 8 == 0
 
 
+def gemm_kernel_for(M, N, K, out_f32, acc, pair, ksplit, sms):
+    """Name of the library entry point a problem goes to.  `pair`: False, True (every problem with enough rows and
+    columns on CTA pairs) or "narrow" (only bf16 results with too few 256-wide tiles for the SMs, on 256 x 128 pair
+    tiles); `ksplit`: bf16 results with at most sms / 2 tiles of 128 x 256 and K >= 2048 split K across the two CTAs of
+    a cluster (the input gradient of a sweep: 2048 x 1024 over K = 4096)."""
+    tiles = -(-M // 128) * -(-N // 256)
+    if pair == "narrow":
+        use_pair = not out_f32 and M >= 256 and N >= 128 and K >= 512 and tiles <= sms // 2
+    else:
+        use_pair = bool(pair) and M >= 512 and N >= 192
+    if use_pair:
+        return "dmb_gemm_bf16_pair"
+    if ksplit and not out_f32 and not acc and K >= 2048 and 2 * tiles <= sms:
+        return "dmb_gemm_bf16_ksplit2"
+    return "dmb_gemm_bf16"
+
+
 class Tcgen05Gemm:
     MIN_WORK = 1 << 18          # below this many MACs the launch is not worth a tensor-map encode
 
@@ -73,15 +90,7 @@ class Tcgen05Gemm:
 
     def _call(self, A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, acc):
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        if self.pair == "narrow":
-            use_pair = (not out_f32 and M >= 256 and N >= 128 and K >= 512
-                        and -(-M // 128) * -(-N // 256) <= self.sms // 2)
-        else:
-            use_pair = bool(self.pair) and M >= 512 and N >= 192
-        fn = self.lib.dmb_gemm_bf16_pair if use_pair else self.lib.dmb_gemm_bf16
-        if (self.ksplit and not use_pair and not out_f32 and not acc and K >= 2048
-                and 2 * (-(-M // 128) * -(-N // 256)) <= self.sms):
-            fn = self.lib.dmb_gemm_bf16_ksplit2
+        fn = getattr(self.lib, gemm_kernel_for(M, N, K, out_f32, acc, self.pair, self.ksplit, self.sms))
         rc = fn(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                     bias.data_ptr() if bias is not None else None, M, N, K, lda, ldb, ldc,
                                     a_mn, b_mn, out_f32, acc, self.err.data_ptr(), st)

@@ -97,3 +97,20 @@ def test_engines_wrap_their_table_on_request(monkeypatch):
     assert eng.ops.calls_checked > 50
     monkeypatch.delenv("DMB_CHECK_ARGS")
     assert not isinstance(WaveScanEngine(m, [uniform_chunks(32, 8, 2)], 2, 32, backend="fused", ops=TorchOps()).ops, CheckedOps)
+
+
+def test_gemm_routing_rule():
+    """Which kernel a GEMM goes to: the cluster K split only for bf16 results with few tiles and a long reduction."""
+    from dual_mod_public_b200.ops.gemm import gemm_kernel_for as route
+    sms = 148
+    assert route(2048, 1024, 4096, 0, 0, False, True, sms) == "dmb_gemm_bf16_ksplit2"      # input gradient of a sweep
+    assert route(2048, 4096, 1024, 0, 0, False, True, sms) == "dmb_gemm_bf16"              # forward GEMM of a sweep
+    assert route(2048, 1024, 4096, 1, 0, False, True, sms) == "dmb_gemm_bf16"              # fp32 result: workspace split-K
+    assert route(2048, 1024, 4096, 0, 0, False, False, sms) == "dmb_gemm_bf16"
+    assert route(65536, 1024, 2816, 0, 0, False, True, sms) == "dmb_gemm_bf16"             # many tiles
+    assert route(1024, 2304, 2304, 0, 0, False, True, sms) == "dmb_gemm_bf16_ksplit2"      # 72 tiles, 144 CTAs
+    assert route(1024, 2560, 2304, 0, 0, False, True, sms) == "dmb_gemm_bf16"              # 80 tiles: over half the SMs
+    assert route(65536, 1024, 1024, 0, 0, True, True, sms) == "dmb_gemm_bf16_pair"
+    assert route(256, 128, 64, 0, 0, True, True, sms) == "dmb_gemm_bf16"
+    assert route(2048, 1024, 4096, 0, 0, "narrow", True, sms) == "dmb_gemm_bf16_pair"
+    assert route(65536, 1024, 1024, 0, 0, "narrow", True, sms) == "dmb_gemm_bf16"
